@@ -1,0 +1,38 @@
+"""Gated feed-forward block (parity: torchtune/modules/feed_forward.py:14-54)."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+from torch import nn
+
+from .. import ops
+
+
+class FeedForward(nn.Module):
+    """``down(act(gate(x)) * up(x))``; attribute names are ``w1`` (gate), ``w2``
+    (down) and ``w3`` (up).  With SiLU and an up projection the activation and
+    product run as one fused SwiGLU kernel."""
+
+    def __init__(
+        self,
+        *,
+        gate_proj: nn.Module,
+        down_proj: nn.Module,
+        up_proj: Optional[nn.Module] = None,
+        activation: nn.Module = nn.SiLU(),
+    ):
+        super().__init__()
+        self.w1 = gate_proj
+        self.w2 = down_proj
+        self.w3 = up_proj
+        self.activation = activation
+        self._silu = isinstance(activation, nn.SiLU)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        g = self.w1(x)
+        if self.w3 is None:
+            return self.w2(self.activation(g))
+        u = self.w3(x)
+        h = ops.swiglu(g, u) if self._silu else self.activation(g) * u
+        return self.w2(h)

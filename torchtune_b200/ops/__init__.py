@@ -1,0 +1,156 @@
+"""Operator layer.
+
+Every operator has two statements: the sm_100a CUDA kernel (``_cuda``,
+compiled from ``csrc/``) used for CUDA tensors, and the plain PyTorch one in
+:mod:`.reference` used on CPU and as the numerical oracle.  On a CUDA device a
+missing extension is an error, never a silent fallback.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+from . import reference
+from .mask import AttentionMask
+
+__all__ = [
+    "linear",
+    "rms_norm",
+    "rope",
+    "swiglu",
+    "attention",
+    "linear_cross_entropy",
+    "token_logprobs",
+    "embedding",
+    "AttentionMask",
+    "reference",
+    "cuda_ops_enabled",
+]
+
+_FORCE_REFERENCE = False
+
+
+class use_reference_ops:
+    """Context manager that forces the PyTorch statements (used by parity tests)."""
+
+    def __enter__(self):
+        global _FORCE_REFERENCE
+        self._prev = _FORCE_REFERENCE
+        _FORCE_REFERENCE = True
+
+    def __exit__(self, *exc):
+        global _FORCE_REFERENCE
+        _FORCE_REFERENCE = self._prev
+
+
+def cuda_ops_enabled(t: torch.Tensor) -> bool:
+    return t.is_cuda and not _FORCE_REFERENCE
+
+
+def _native(t: torch.Tensor, dtypes=(torch.bfloat16,)) -> bool:
+    return t.is_cuda and not _FORCE_REFERENCE and t.dtype in dtypes
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x @ weight.T (+ bias)``; bf16 CUDA inputs run the tcgen05 GEMM (fwd, dgrad, wgrad)."""
+    if _native(x) and weight.dtype == torch.bfloat16:
+        from . import _cuda
+
+        return _cuda.linear(x, weight, bias)
+    return F.linear(x, weight, bias)
+
+
+def rms_norm(x: torch.Tensor, scale: Optional[torch.Tensor], eps: float = 1e-6) -> torch.Tensor:
+    if _native(x, (torch.bfloat16, torch.float32)):
+        from . import _cuda
+
+        return _cuda.rms_norm(x, scale, eps)
+    return reference.rms_norm(x, scale, eps)
+
+
+def rope(
+    x: torch.Tensor, cache: torch.Tensor, input_pos: Optional[torch.Tensor] = None, interleaved: bool = True
+) -> torch.Tensor:
+    """Rotary embedding on ``[b, s, h, d]``; ``cache`` ``[max_seq, d/2, 2]`` (cos, sin) fp32."""
+    if _native(x):
+        from . import _cuda
+
+        return _cuda.rope(x, cache, input_pos, interleaved)
+    fn = reference.rope_interleaved if interleaved else reference.rope_half
+    return fn(x, cache, input_pos)
+
+
+def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    if _native(gate):
+        from . import _cuda
+
+        return _cuda.swiglu(gate, up)
+    return reference.swiglu(gate, up)
+
+
+def attention(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    mask: Optional[AttentionMask] = None,
+    *,
+    scale: Optional[float] = None,
+    softcap: float = 0.0,
+    dropout_p: float = 0.0,
+) -> torch.Tensor:
+    """Grouped-query attention on ``[b, s, h, d]`` without materialising expanded KV heads."""
+    mask = mask if mask is not None else AttentionMask(causal=False)
+    if (
+        _native(q)
+        and mask.bool_mask is None
+        and dropout_p == 0.0
+        and q.shape[-1] in (64, 128)
+        and q.shape[1] == k.shape[1]
+    ):
+        from . import _cuda
+
+        return _cuda.attention(q, k, v, mask, scale, softcap)
+    return reference.attention(
+        q,
+        k,
+        v,
+        causal=mask.causal,
+        doc_ids=mask.doc_ids,
+        chunk=mask.chunk,
+        window=mask.window,
+        bool_mask=mask.bool_mask,
+        scale=scale,
+        softcap=softcap,
+        dropout_p=dropout_p,
+    )
+
+
+def linear_cross_entropy(
+    hidden: torch.Tensor,
+    weight: torch.Tensor,
+    labels: torch.Tensor,
+    ignore_index: int = -100,
+    num_chunks: int = 8,
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``(sum of CE, number of valid tokens)`` of ``hidden @ weight.T`` vs ``labels``."""
+    if _native(hidden) and weight.dtype == torch.bfloat16:
+        from . import _cuda
+
+        return _cuda.linear_cross_entropy(hidden, weight, labels, ignore_index, num_chunks)
+    return reference.linear_cross_entropy(hidden, weight, labels, ignore_index, num_chunks)
+
+
+def token_logprobs(
+    hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100, num_chunks: int = 8
+) -> torch.Tensor:
+    if _native(hidden) and weight.dtype == torch.bfloat16:
+        from . import _cuda
+
+        return _cuda.token_logprobs(hidden, weight, labels, ignore_index, num_chunks)
+    return reference.token_logprobs(hidden, weight, labels, ignore_index, num_chunks)
+
+
+def embedding(tokens: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    return F.embedding(tokens, weight)

@@ -1,0 +1,40 @@
+from . import metric_logging
+from ._grad_scaler import scale_grads, scale_grads_
+from ._model_util import disable_dropout
+from .checkpointing import (
+    ADAPTER_CONFIG,
+    ADAPTER_KEY,
+    DATALOADER_KEY,
+    EPOCHS_KEY,
+    MAX_STEPS_KEY,
+    MODEL_KEY,
+    OPT_KEY,
+    RNG_KEY,
+    SEED_KEY,
+    STEPS_KEY,
+    TOTAL_EPOCHS_KEY,
+    VAL_DATALOADER_KEY,
+    Checkpointer,
+    FormattedCheckpointFiles,
+    FullModelHFCheckpointer,
+    FullModelMetaCheckpointer,
+    FullModelTorchTuneCheckpointer,
+    ModelType,
+    update_state_dict_for_classifier,
+)
+from .lr_schedulers import get_cosine_schedule_with_warmup, get_lr
+from .memory import (
+    OptimizerInBackwardWrapper,
+    apply_selective_activation_checkpointing,
+    cleanup_before_training,
+    create_optim_in_bwd_wrapper,
+    get_memory_stats,
+    log_memory_stats,
+    register_optim_in_bwd_hooks,
+    set_activation_checkpointing,
+)
+from .pooling import get_unmasked_sequence_lengths
+from .precision import get_dtype, set_default_dtype, validate_expected_param_dtype
+from .seed import set_seed
+from ._activation_offloading import NoOpManager, OffloadActivations, get_act_offloading_ctx_manager
+from ._profiler import DummyProfiler, setup_torch_profiler

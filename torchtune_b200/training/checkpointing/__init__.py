@@ -1,0 +1,45 @@
+from ._checkpointer import (
+    FullModelHFCheckpointer,
+    FullModelMetaCheckpointer,
+    FullModelTorchTuneCheckpointer,
+)
+from ._utils import (
+    ADAPTER_CONFIG,
+    ADAPTER_KEY,
+    DATALOADER_KEY,
+    EPOCHS_KEY,
+    MAX_STEPS_KEY,
+    MODEL_KEY,
+    OPT_KEY,
+    RNG_KEY,
+    SEED_KEY,
+    STEPS_KEY,
+    TOTAL_EPOCHS_KEY,
+    VAL_DATALOADER_KEY,
+    FormattedCheckpointFiles,
+    ModelType,
+    update_state_dict_for_classifier,
+)
+
+Checkpointer = FullModelHFCheckpointer
+
+__all__ = [
+    "FullModelHFCheckpointer",
+    "FullModelMetaCheckpointer",
+    "FullModelTorchTuneCheckpointer",
+    "ModelType",
+    "FormattedCheckpointFiles",
+    "update_state_dict_for_classifier",
+    "ADAPTER_CONFIG",
+    "ADAPTER_KEY",
+    "EPOCHS_KEY",
+    "MAX_STEPS_KEY",
+    "MODEL_KEY",
+    "OPT_KEY",
+    "RNG_KEY",
+    "SEED_KEY",
+    "STEPS_KEY",
+    "TOTAL_EPOCHS_KEY",
+    "DATALOADER_KEY",
+    "VAL_DATALOADER_KEY",
+]

@@ -1,0 +1,249 @@
+"""Headline benchmark: Llama-3.1-8B full fine-tune step throughput (tokens/s, whole job).
+
+    python bench.py --gpus 1 --steps 5 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 5 --warmup 3
+
+Config (fixed by the baseline definition): 32 layers, dim 4096, 32 heads / 8 KV heads, FFN
+14336, vocab 128256, llama3 RoPE scaling; packed sequences of 2048 tokens with document
+boundaries every 512 tokens (block-causal mask), per-GPU batch 4, activation checkpointing
+on, AdamW lr 2e-5, bf16; synthetic uniform tokens and random-init weights.  Data parallel
+over N GPUs with sharded optimizer state and fp32 gradient reduction (weak scaling: the
+per-GPU batch is fixed).
+
+Prints ONE JSON line on rank 0.  ``value`` is device-timed (CUDA events, max over ranks)
+with device-resident inputs; ``e2e`` times the public ``TrainStep`` call including the
+pinned host→device input copy and the device→host loss read every step.
+``--impl reference`` runs the unmodified reference implementation installed under
+``baseline/_ref`` on the same config and prints the same line with ``"impl": "reference"``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+MODEL = dict(vocab_size=128_256, num_layers=32, num_heads=32, num_kv_heads=8, embed_dim=4096, max_seq_len=8192, intermediate_dim=14336, norm_eps=1e-5, rope_base=500_000)
+SEQ_LEN, DOC_LEN, BATCH_PER_GPU, LR = 2048, 512, 4, 2e-5
+BASELINE_TOKENS_PER_S = None  # the reference publishes no B200 number for this config
+
+
+class ClockSampler:
+    """Polls nvidia-smi during the timed region (SM clock, throttle reasons)."""
+
+    QUERY = "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.rows = []
+        self.proc = None
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200", "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self) -> None:
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def synthetic_batch(torch, batch: int, seed: int):
+    """Host-side (pinned) packed batch: uniform tokens, shifted labels, per-document positions."""
+    g = torch.Generator().manual_seed(seed)
+    tokens = torch.randint(0, MODEL["vocab_size"], (batch, SEQ_LEN), generator=g, dtype=torch.long)
+    labels = torch.roll(tokens, -1, dims=1)
+    labels[:, DOC_LEN - 1 :: DOC_LEN] = -100
+    n_docs = SEQ_LEN // DOC_LEN
+    pos = torch.arange(DOC_LEN).repeat(n_docs).unsqueeze(0).expand(batch, SEQ_LEN).contiguous()
+    doc_ids = torch.arange(n_docs, dtype=torch.int32).repeat_interleave(DOC_LEN).unsqueeze(0).expand(batch, SEQ_LEN).contiguous()
+    pin = (lambda t: t.pin_memory()) if torch.cuda.is_available() else (lambda t: t)
+    return {"tokens": pin(tokens), "labels": pin(labels), "input_pos": pin(pos), "doc_ids": pin(doc_ids)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    return rank, world, local
+
+
+def timed_loop(torch, dist, world, fn, steps: int):
+    """Barrier + sync on both sides, CUDA events, max over ranks → seconds."""
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    t = torch.tensor([e0.elapsed_time(e1) / 1e3], device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def run_ours(args) -> dict:
+    import torch
+    import torch.distributed as dist
+
+    from torchtune_b200 import training
+    from torchtune_b200.engine.train_step import TrainStep
+    from torchtune_b200.models.llama3_1 import llama3_1
+    from torchtune_b200.modules import TransformerSelfAttentionLayer
+    from torchtune_b200.modules.loss import LinearCrossEntropyLoss
+    from torchtune_b200.ops._lib import check_device_errors, lib
+    from torchtune_b200.ops.mask import AttentionMask
+    from torchtune_b200.optim import AdamW
+
+    rank, world, local = dist_env()
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    parallel = None
+    if world > 1:
+        from torchtune_b200 import parallel as par
+
+        dist.init_process_group("nccl", device_id=device)
+        parallel = par.DataParallelEngine(device=device)
+    torch.manual_seed(1234)  # identical initial weights on every rank
+    with training.set_default_dtype(torch.bfloat16), device:
+        model = llama3_1(**MODEL)
+        for p in model.parameters():
+            if p.dim() > 1:
+                torch.nn.init.normal_(p, std=0.02)
+    training.set_activation_checkpointing(model, {TransformerSelfAttentionLayer})
+    loss_fn = LinearCrossEntropyLoss(num_output_chunks=8)
+    loss_fn.set_model_output(model)
+    if parallel is not None:
+        model = parallel.prepare(model)
+        optimizer = parallel.build_optimizer(model, lr=LR)
+    else:
+        optimizer = AdamW(model.parameters(), lr=LR)
+    step = TrainStep(model, loss_fn, optimizer, device, parallel=parallel)
+
+    def to_model_batch(host):
+        dev = step.upload(host)
+        dev["mask"] = AttentionMask(causal=True, doc_ids=dev.pop("doc_ids"))
+        return dev
+
+    host_batches = [synthetic_batch(torch, BATCH_PER_GPU, seed=1000 * rank + i) for i in range(4)]
+    dev_batches = [to_model_batch(h) for h in host_batches]
+    tokens_per_step = BATCH_PER_GPU * SEQ_LEN * world
+    L = lib()
+
+    losses = []
+    for i in range(args.warmup):
+        losses.append(step.compute(dev_batches[i % 4]))
+    torch.cuda.synchronize()
+    check_device_errors()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = L.ttb_launch_count()
+    t_kernel = timed_loop(torch, dist, world, lambda i: losses.append(step.compute(dev_batches[i % 4])), args.steps)
+    launches = L.ttb_launch_count() - launches0
+
+    def e2e_step(i):
+        host = host_batches[i % 4]
+        dev = to_model_batch(host)  # pinned host -> device copy of this step's inputs
+        losses.append(float(step.compute(dev).item()))  # device -> host read of the loss
+
+    t_e2e = timed_loop(torch, dist, world, e2e_step, args.steps)
+    clocks = sampler.stop() if rank == 0 else {}
+    check_device_errors()
+    h2d = sum(t.numel() * t.element_size() for t in host_batches[0].values())
+    peak_gib = torch.cuda.max_memory_allocated() / 2**30
+    final_loss = float(losses[-1]) if losses else float("nan")
+    value = tokens_per_step * args.steps / t_kernel
+    out = {
+        "metric": "tokens_per_second",
+        "value": value,
+        "unit": "tokens/s",
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": 1e3 * t_kernel / args.steps,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": (value / BASELINE_TOKENS_PER_S) if BASELINE_TOKENS_PER_S else None,
+        "dtype": "bf16",
+        "data": "synthetic uniform tokens, random-init weights",
+        "impl": "ours",
+        "config": {
+            "model": "llama3_1_8b",
+            "global_batch": BATCH_PER_GPU * world,
+            "seq_len": SEQ_LEN,
+            "doc_len": DOC_LEN,
+            "parallelism": f"dp{world}" if world > 1 else "single",
+            "activation_checkpointing": True,
+            "optimizer": "AdamW lr 2e-5 (fused multi-tensor)",
+            "l2": "inputs larger than L2 (16 GB of weights streamed every step)",
+        },
+        "clocks": clocks,
+        "e2e": {"value": tokens_per_step * args.steps / t_e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
+        "gpu_launches": int(launches),
+        "peak_mem_gib": round(peak_gib, 2),
+        "final_loss": final_loss,
+    }
+    if world > 1:
+        dist.destroy_process_group()
+    return out if rank == 0 else {}
+
+
+def run_reference(args) -> dict:
+    from baseline.reference_arm import run as run_ref
+
+    return run_ref(args, MODEL, SEQ_LEN, DOC_LEN, BATCH_PER_GPU, LR, ClockSampler, timed_loop, dist_env)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    args = ap.parse_args()
+    rank, world, _ = dist_env()
+    if args.gpus > 1 and world == 1:
+        # convenience: re-launch under torchrun when called directly with --gpus N
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}", "--master-addr", "127.0.0.1", "--master-port", "29511", __file__, *sys.argv[1:]]
+        sys.exit(subprocess.call(cmd))
+    result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if rank == 0:
+        print(json.dumps(result), flush=True)
+
+
+if __name__ == "__main__":
+    main()

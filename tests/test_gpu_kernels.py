@@ -1,0 +1,275 @@
+"""Numerics of every sm_100a kernel against a plain PyTorch fp32 statement of the same op."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from torchtune_b200 import ops
+from torchtune_b200.ops import reference as ref
+from torchtune_b200.ops.mask import AttentionMask
+
+
+@pytest.fixture(autouse=True)
+def _check_device_errors():
+    yield
+    if torch.cuda.is_available():
+        from torchtune_b200.ops._lib import check_device_errors
+
+        torch.cuda.synchronize()
+        check_device_errors()
+
+
+def _rand(*shape, scale=1.0, seed=0, dtype=torch.bfloat16):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(*shape, generator=g, device="cuda") * scale).to(dtype)
+
+
+def _close(got, want, rtol, atol, what=""):
+    got, want = got.float(), want.float()
+    err = (got - want).abs()
+    tol = atol + rtol * want.abs()
+    bad = (err > tol).sum().item()
+    assert bad == 0, f"{what}: {bad}/{err.numel()} elements off, max err {err.max().item():.4g} (max ref {want.abs().max().item():.4g})"
+
+
+# ------------------------------------------------------------------ GEMM
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("M,N,K", [(128, 64, 64), (256, 256, 128), (200, 96, 320), (1024, 1024, 512), (384, 2048, 1088)])
+def test_gemm_layouts(M, N, K, a_mn, b_mn):
+    from torchtune_b200.ops._cuda import gemm
+
+    a = _rand(M, K, seed=1)
+    b = _rand(N, K, seed=2)
+    want = a.float() @ b.float().t()
+    a_in = a.t().contiguous() if a_mn else a
+    b_in = b.t().contiguous() if b_mn else b
+    got = gemm(a_in, b_in, a_mn=a_mn, b_mn=b_mn)
+    _close(got, want, 2e-2, 2e-2 * math.sqrt(K) / 8, f"gemm {M}x{N}x{K} a_mn={a_mn} b_mn={b_mn}")
+
+
+def test_gemm_epilogues():
+    from torchtune_b200.ops._cuda import gemm
+
+    a, b = _rand(512, 256, seed=3), _rand(384, 256, seed=4)
+    bias = _rand(384, seed=5)
+    want = a.float() @ b.float().t()
+    _close(gemm(a, b, bias=bias), want + bias.float(), 2e-2, 0.1, "bias")
+    out32 = gemm(a, b, out_dtype=torch.float32)
+    _close(out32, want, 1e-3, 1e-2, "fp32 out")
+    acc = out32.clone()
+    gemm(a, b, out=acc, accumulate=True)
+    _close(acc, 2 * want, 1e-3, 2e-2, "fp32 accumulate")
+    accb = gemm(a, b)
+    gemm(a, b, out=accb, accumulate=True, alpha=0.5)
+    _close(accb, 1.5 * want, 3e-2, 0.2, "bf16 accumulate + alpha")
+
+
+def test_gemm_large_matches_matmul():
+    from torchtune_b200.ops._cuda import gemm
+
+    a, b = _rand(4096, 4096, seed=6, scale=0.5), _rand(2048, 4096, seed=7, scale=0.5)
+    want = torch.matmul(a, b.t())
+    _close(gemm(a, b), want, 2e-2, 0.5, "large")
+
+
+def test_linear_autograd():
+    x = _rand(3, 40, 256, seed=8).requires_grad_()
+    w = _rand(512, 256, seed=9, scale=0.05).requires_grad_()
+    bias = _rand(512, seed=10).requires_grad_()
+    y = ops.linear(x, w, bias)
+    gy = _rand(3, 40, 512, seed=11)
+    y.backward(gy)
+    xr, wr, br = (t.detach().float().requires_grad_() for t in (x, w, bias))
+    yr = torch.nn.functional.linear(xr, wr, br)
+    yr.backward(gy.float())
+    _close(y, yr, 2e-2, 5e-2, "linear fwd")
+    _close(x.grad, xr.grad, 2e-2, 5e-2, "linear dx")
+    _close(w.grad, wr.grad, 2e-2, 0.3, "linear dw")
+    _close(bias.grad, br.grad, 2e-2, 0.3, "linear db")
+
+
+# ------------------------------------------------------------------ elementwise
+@pytest.mark.parametrize("rows,D", [(37, 256), (1024, 4096), (5, 8192)])
+def test_rmsnorm(rows, D):
+    x = _rand(rows, D, seed=1).requires_grad_()
+    scale = (1 + 0.1 * _rand(D, seed=2).float()).to(torch.bfloat16).requires_grad_()
+    y = ops.rms_norm(x, scale, 1e-5)
+    gy = _rand(rows, D, seed=3)
+    y.backward(gy)
+    xr, sr = x.detach().float().requires_grad_(), scale.detach().float().requires_grad_()
+    yr = ref.rms_norm(xr, sr, 1e-5)
+    yr.backward(gy.float())
+    _close(y, yr, 1e-2, 1e-2, "rmsnorm fwd")
+    _close(x.grad, xr.grad, 2e-2, 2e-2, "rmsnorm dx")
+    _close(scale.grad, sr.grad, 2e-2, 0.05 * math.sqrt(rows), "rmsnorm dscale")
+    # weight-less variant
+    y2 = ops.rms_norm(x.detach(), None, 1e-6)
+    _close(y2, ref.rms_norm(x.detach().float(), None, 1e-6), 1e-2, 1e-2, "rmsnorm no scale")
+
+
+@pytest.mark.parametrize("interleaved", [True, False])
+@pytest.mark.parametrize("use_pos", [False, True])
+def test_rope(interleaved, use_pos):
+    from torchtune_b200.modules import RotaryPositionalEmbeddings
+
+    b, s, h, d = 2, 48, 4, 128
+    rope = RotaryPositionalEmbeddings(d, max_seq_len=256, base=500000).cuda()
+    x = _rand(b, s, h, d, seed=1).requires_grad_()
+    pos = torch.randint(0, 256, (b, s), device="cuda") if use_pos else None
+    y = ops.rope(x, rope.cache, pos, interleaved=interleaved)
+    gy = _rand(b, s, h, d, seed=2)
+    y.backward(gy)
+    xr = x.detach().float().requires_grad_()
+    fn = ref.rope_interleaved if interleaved else ref.rope_half
+    yr = fn(xr, rope.cache, pos)
+    yr.backward(gy.float())
+    _close(y, yr, 1e-2, 1e-2, "rope fwd")
+    _close(x.grad, xr.grad, 1e-2, 1e-2, "rope bwd")
+
+
+def test_swiglu():
+    g = _rand(70, 1536, seed=1).requires_grad_()
+    u = _rand(70, 1536, seed=2).requires_grad_()
+    y = ops.swiglu(g, u)
+    gy = _rand(70, 1536, seed=3)
+    y.backward(gy)
+    gr, ur = g.detach().float().requires_grad_(), u.detach().float().requires_grad_()
+    yr = ref.swiglu(gr, ur)
+    yr.backward(gy.float())
+    _close(y, yr, 2e-2, 2e-2, "swiglu fwd")
+    _close(g.grad, gr.grad, 2e-2, 2e-2, "swiglu dg")
+    _close(u.grad, ur.grad, 2e-2, 2e-2, "swiglu du")
+
+
+# ------------------------------------------------------------------ loss
+@pytest.mark.parametrize("T,D,V", [(300, 256, 1024), (1000, 512, 32000)])
+def test_linear_cross_entropy(T, D, V):
+    h = _rand(T, D, seed=1).requires_grad_()
+    w = _rand(V, D, seed=2, scale=0.05).requires_grad_()
+    labels = torch.randint(0, V, (T,), device="cuda")
+    labels[::7] = -100
+    loss, n = ops.linear_cross_entropy(h, w, labels, -100, 8)
+    (loss / n).backward()
+    hr, wr = h.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    lr, nr = ref.linear_cross_entropy(hr, wr, labels, -100, 8)
+    (lr / nr).backward()
+    assert n.item() == nr.item()
+    _close(loss / n, lr / nr, 5e-3, 5e-3, "ce loss")
+    _close(h.grad, hr.grad, 5e-2, 2e-4, "ce dh")
+    _close(w.grad, wr.grad, 5e-2, 2e-4, "ce dw")
+
+
+def test_token_logprobs():
+    T, D, V = 200, 256, 2048
+    h = _rand(T, D, seed=1).requires_grad_()
+    w = _rand(V, D, seed=2, scale=0.05)
+    labels = torch.randint(0, V, (4, 50), device="cuda")
+    labels[:, :10] = -100
+    lp = ops.token_logprobs(h.view(4, 50, D), w, labels, -100, 4)
+    g = _rand(4, 50, seed=3, dtype=torch.float32)
+    (lp * g).sum().backward()
+    hr = h.detach().float().requires_grad_()
+    lpr = ref.token_logprobs(hr.view(4, 50, D), w.float(), labels, -100, 4)
+    (lpr * g).sum().backward()
+    _close(lp, lpr, 1e-2, 2e-2, "logprobs")
+    _close(h.grad, hr.grad, 5e-2, 5e-3, "logprobs dh")
+
+
+# ------------------------------------------------------------------ optimizer
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_adamw_matches_torch(dtype):
+    from torchtune_b200.optim import AdamW
+
+    shapes = [(1000,), (256, 512), (7,), (4097, 3)]
+    ps = [_rand(*s, seed=i, dtype=dtype) for i, s in enumerate(shapes)]
+    mine = [p.clone().requires_grad_() for p in ps]
+    theirs = [p.clone().requires_grad_() for p in ps]
+    o1 = AdamW(mine, lr=1e-2, weight_decay=0.1)
+    o2 = torch.optim.AdamW(theirs, lr=1e-2, weight_decay=0.1)
+    for step in range(3):
+        for i, (a, b) in enumerate(zip(mine, theirs)):
+            g = _rand(*a.shape, seed=100 + 10 * step + i, dtype=dtype)
+            a.grad, b.grad = g.clone(), g.clone()
+        o1.step()
+        o2.step()
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+    for a, b in zip(mine, theirs):
+        _close(a, b, tol, tol, "adamw")
+
+
+# ------------------------------------------------------------------ attention
+def _attn_case(b, s, hq, hkv, d, mask, seed=0):
+    q = _rand(b, s, hq, d, seed=seed).requires_grad_()
+    k = _rand(b, s, hkv, d, seed=seed + 1).requires_grad_()
+    v = _rand(b, s, hkv, d, seed=seed + 2).requires_grad_()
+    go = _rand(b, s, hq, d, seed=seed + 3)
+    o = ops.attention(q, k, v, mask)
+    o.backward(go)
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    orf = ref.attention(qr, kr, vr, causal=mask.causal, doc_ids=mask.doc_ids, chunk=mask.chunk, window=mask.window)
+    orf.backward(go.float())
+    _close(o, orf, 2e-2, 2e-2, "attn out")
+    _close(v.grad, vr.grad, 3e-2, 3e-2, "attn dv")
+    _close(k.grad, kr.grad, 3e-2, 5e-2, "attn dk")
+    _close(q.grad, qr.grad, 3e-2, 5e-2, "attn dq")
+
+
+@pytest.mark.parametrize("d", [128, 64])
+@pytest.mark.parametrize("s", [128, 384, 200])
+def test_attention_causal(s, d):
+    _attn_case(2, s, 4, 2, d, AttentionMask(causal=True))
+
+
+def test_attention_noncausal():
+    _attn_case(1, 256, 2, 2, 128, AttentionMask(causal=False))
+
+
+def test_attention_packed_documents():
+    mask = AttentionMask.from_seq_lens([[100, 156, 256], [512]]).to("cuda")
+    _attn_case(2, 512, 8, 2, 128, mask)
+
+
+def test_attention_chunk_and_window():
+    _attn_case(1, 512, 4, 4, 64, AttentionMask(causal=True, chunk=192))
+    _attn_case(1, 512, 4, 1, 128, AttentionMask(causal=True, window=100))
+
+
+def test_attention_long():
+    _attn_case(1, 2048, 8, 2, 128, AttentionMask(causal=True), seed=5)
+
+
+# ------------------------------------------------------------------ model level
+def test_tiny_llama_bf16_matches_fp32_reference():
+    from helpers import TINY, fixed_init_
+    from torchtune_b200.models.llama3_1 import llama3_1
+    from torchtune_b200.modules.loss import LinearCrossEntropyLoss
+
+    torch.manual_seed(0)
+    model = llama3_1(**TINY)
+    fixed_init_(model)
+    tokens = torch.randint(0, 1024, (2, 128))
+    labels = torch.randint(0, 1024, (2, 128))
+    labels[:, :16] = -100
+
+    def run(m, dev, use_ref):
+        m = m.to(dev)
+        loss_fn = LinearCrossEntropyLoss()
+        loss_fn.set_model_output(m)
+        ctx = ops.use_reference_ops() if use_ref else torch.enable_grad()
+        with ctx:
+            loss = loss_fn(m(tokens.to(dev)), labels.to(dev))
+            loss.backward()
+        m.skip_output_layer = False
+        return loss.item(), {n: p.grad.float().cpu() for n, p in m.named_parameters()}
+
+    import copy
+
+    l_ref, g_ref = run(copy.deepcopy(model), "cpu", True)
+    l_gpu, g_gpu = run(copy.deepcopy(model).to(torch.bfloat16), "cuda", False)
+    assert abs(l_ref - l_gpu) < 5e-2, (l_ref, l_gpu)
+    for n in g_ref:
+        denom = g_ref[n].norm().item() + 1e-6
+        rel = (g_ref[n] - g_gpu[n]).norm().item() / denom
+        assert rel < 0.08, f"{n}: relative grad error {rel:.3f}"

@@ -1,0 +1,399 @@
+"""CUDA execution path of :mod:`torchtune_b200.ops`: autograd functions over the sm_100a
+kernels in ``csrc/`` (loaded through :mod:`._lib`)."""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Any, Dict, List, Optional, Sequence, Tuple, Union
+
+import torch
+
+from . import _lib
+from ._lib import check, err_word, lib, stream_ptr
+from .mask import AttentionMask
+
+_BF16 = torch.bfloat16
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+# ======================================================================= GEMM
+def gemm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    *,
+    a_mn: bool = False,
+    b_mn: bool = False,
+    out: Optional[torch.Tensor] = None,
+    out_dtype: torch.dtype = _BF16,
+    accumulate: bool = False,
+    bias: Optional[torch.Tensor] = None,
+    alpha: float = 1.0,
+) -> torch.Tensor:
+    """``C[M,N] (+)= alpha * op(A) op(B)`` on the tcgen05 tensor cores.
+
+    ``a`` is ``[M,K]`` (``a_mn=False``) or ``[K,M]`` (``a_mn=True``); ``b`` is ``[N,K]``
+    (``b_mn=False``) or ``[K,N]`` (``b_mn=True``).  Both must be bf16 with unit inner stride
+    (row strides are free, multiples of 8).
+    """
+    assert a.dtype == _BF16 and b.dtype == _BF16 and a.dim() == 2 and b.dim() == 2
+    if a.stride(1) != 1 or a.stride(0) % 8 or a.data_ptr() % 16:
+        a = a.contiguous()
+    if b.stride(1) != 1 or b.stride(0) % 8 or b.data_ptr() % 16:
+        b = b.contiguous()
+    M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
+    N, Kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
+    if K != Kb:
+        raise ValueError(f"gemm contraction mismatch: {K} vs {Kb}")
+    if out is None:
+        if accumulate:
+            raise ValueError("accumulate=True needs an existing `out`")
+        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    else:
+        assert out.shape == (M, N) and out.stride(1) == 1
+    if M == 0 or N == 0:
+        return out
+    if K == 0:
+        return out if accumulate else out.zero_()
+    rc = lib().ttb_gemm_bf16(
+        a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, int(a_mn), int(b_mn),
+        a.stride(0), b.stride(0), out.stride(0), int(out.dtype == torch.float32), int(accumulate),
+        _ptr(bias), float(alpha), err_word(a.device).data_ptr(), stream_ptr(),
+    )
+    check(rc, f"gemm M={M} N={N} K={K} a_mn={a_mn} b_mn={b_mn}")
+    return out
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        x2 = x.reshape(-1, x.shape[-1])
+        ctx.save_for_backward(x2, weight)
+        ctx.has_bias = bias is not None
+        ctx.x_shape = x.shape
+        y = gemm(x2, weight, bias=bias)
+        return y.view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, weight, b_mn=True).view(ctx.x_shape)  # dX = dY · W
+        if ctx.needs_input_grad[1]:
+            dw = gemm(dy2, x2, a_mn=True, b_mn=True)  # dW = dYᵀ · X
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.sum(0)
+        return dx, dw, db
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    K, N = x.shape[-1], weight.shape[0]
+    if K % 8 or N % 8:  # TMA needs 16-byte row pitches; odd sizes (tiny classifier heads) use the library path
+        return torch.nn.functional.linear(x, weight, bias)
+    return _Linear.apply(x, weight, bias)
+
+
+# ======================================================================= RMSNorm
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, scale, eps):
+        D = x.shape[-1]
+        x2 = x.reshape(-1, D)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        rows = x2.shape[0]
+        y = torch.empty_like(x2)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        check(lib().ttb_rmsnorm_fwd(x2.data_ptr(), _ptr(scale), y.data_ptr(), rstd.data_ptr(), rows, D, float(eps), stream_ptr()), "rmsnorm_fwd")
+        ctx.save_for_backward(x2, scale, rstd)
+        ctx.has_scale = scale is not None
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, scale, rstd = ctx.saved_tensors
+        rows, D = x2.shape
+        dy2 = dy.reshape(rows, D)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = torch.empty_like(x2)
+        partial = None
+        if ctx.has_scale and ctx.needs_input_grad[1]:
+            n_part = lib().ttb_rmsnorm_bwd_partials(rows)
+            partial = torch.empty(n_part, D, dtype=torch.float32, device=x2.device)
+        check(lib().ttb_rmsnorm_bwd(dy2.data_ptr(), x2.data_ptr(), _ptr(scale), rstd.data_ptr(), dx.data_ptr(), _ptr(partial), rows, D, stream_ptr()), "rmsnorm_bwd")
+        dscale = partial.sum(0).to(scale.dtype) if partial is not None else None
+        return dx.view(dy.shape), dscale, None
+
+
+def rms_norm(x: torch.Tensor, scale: Optional[torch.Tensor], eps: float) -> torch.Tensor:
+    if x.dtype != _BF16 or x.shape[-1] % 8 or x.shape[-1] > 16384 or (scale is not None and scale.dtype != _BF16):
+        from . import reference
+
+        return reference.rms_norm(x, scale, eps)
+    return _RMSNorm.apply(x, scale, eps)
+
+
+# ======================================================================= RoPE
+def _rope_launch(x: torch.Tensor, cache: torch.Tensor, pos: Optional[torch.Tensor], interleaved: bool, inverse: bool) -> torch.Tensor:
+    b, s, h, d = x.shape
+    if not x.is_contiguous():
+        x = x.contiguous()
+    y = torch.empty_like(x)
+    check(lib().ttb_rope(x.data_ptr(), y.data_ptr(), cache.data_ptr(), _ptr(pos), b * s, h, d, s, int(interleaved), int(inverse), stream_ptr()), "rope")
+    return y
+
+
+class _RoPE(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cache, pos, interleaved):
+        ctx.save_for_backward(cache, pos)
+        ctx.interleaved = interleaved
+        return _rope_launch(x, cache, pos, interleaved, False)
+
+    @staticmethod
+    def backward(ctx, dy):
+        cache, pos = ctx.saved_tensors
+        # a rotation is orthogonal: its transpose is the rotation by the negative angle
+        return _rope_launch(dy, cache, pos, ctx.interleaved, True), None, None, None
+
+
+def rope(x: torch.Tensor, cache: torch.Tensor, input_pos: Optional[torch.Tensor], interleaved: bool) -> torch.Tensor:
+    b, s, h, d = x.shape
+    if d % 16 or cache.dtype != torch.float32 or not cache.is_contiguous():
+        from . import reference
+
+        return (reference.rope_interleaved if interleaved else reference.rope_half)(x, cache, input_pos)
+    pos = None
+    if input_pos is not None:
+        pos = input_pos.to(device=x.device, dtype=torch.int32)
+        pos = pos.expand(b, s).contiguous() if pos.dim() == 2 else pos.view(1, s).expand(b, s).contiguous()
+    return _RoPE.apply(x, cache, pos, interleaved)
+
+
+# ======================================================================= SwiGLU
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gate, up):
+        H = gate.shape[-1]
+        g2, u2 = gate.reshape(-1, H), up.reshape(-1, H)
+        if g2.stride(1) != 1:
+            g2 = g2.contiguous()
+        if u2.stride(1) != 1:
+            u2 = u2.contiguous()
+        y = torch.empty(g2.shape, dtype=gate.dtype, device=gate.device)
+        check(lib().ttb_swiglu_fwd(g2.data_ptr(), u2.data_ptr(), y.data_ptr(), g2.shape[0], H, g2.stride(0), u2.stride(0), y.stride(0), stream_ptr()), "swiglu_fwd")
+        ctx.save_for_backward(g2, u2)
+        return y.view(gate.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        g2, u2 = ctx.saved_tensors
+        rows, H = g2.shape
+        dy2 = dy.reshape(rows, H)
+        if dy2.stride(1) != 1:
+            dy2 = dy2.contiguous()
+        dg = torch.empty(rows, H, dtype=g2.dtype, device=g2.device)
+        du = torch.empty(rows, H, dtype=g2.dtype, device=g2.device)
+        check(lib().ttb_swiglu_bwd(dy2.data_ptr(), g2.data_ptr(), u2.data_ptr(), dg.data_ptr(), du.data_ptr(), rows, H, dy2.stride(0), g2.stride(0), u2.stride(0), H, H, stream_ptr()), "swiglu_bwd")
+        return dg.view(dy.shape), du.view(dy.shape)
+
+
+def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    if gate.shape[-1] % 8:
+        from . import reference
+
+        return reference.swiglu(gate, up)
+    return _SwiGLU.apply(gate, up)
+
+
+# ======================================================================= attention
+def attention(q, k, v, mask: AttentionMask, scale: Optional[float], softcap: float) -> torch.Tensor:
+    from ._cuda_attention import attention as _attn
+
+    return _attn(q, k, v, mask, scale, softcap)
+
+
+# ======================================================================= fused linear + CE
+def _ce_chunk_rows(T: int, num_chunks: int) -> int:
+    return max(1, -(-T // max(1, num_chunks)))
+
+
+class _LinearCE(torch.autograd.Function):
+    """Loss and both gradients in one forward sweep: per token chunk, logits = H·Wᵀ (bf16, as
+    the unfused bf16 projection produces), softmax-CE turns the chunk into dlogits in place,
+    then dH = dlogits·W and dW += dlogitsᵀ·H while the chunk is still hot in L2."""
+
+    @staticmethod
+    def forward(ctx, hidden, weight, labels, ignore_index, num_chunks):
+        D = hidden.shape[-1]
+        h2 = hidden.reshape(-1, D)
+        if not h2.is_contiguous():
+            h2 = h2.contiguous()
+        y = labels.reshape(-1).to(torch.int64).contiguous()
+        T, V = h2.shape[0], weight.shape[0]
+        need_h = ctx.needs_input_grad[0]
+        need_w = ctx.needs_input_grad[1]
+        rows = _ce_chunk_rows(T, num_chunks)
+        loss_rows = torch.empty(T, dtype=torch.float32, device=h2.device)
+        dh = torch.empty_like(h2) if need_h else None
+        dw = torch.zeros(V, D, dtype=torch.float32, device=h2.device) if need_w else None
+        buf = torch.empty(min(rows, T), V, dtype=_BF16, device=h2.device)
+        L = lib()
+        for start in range(0, T, rows):
+            n = min(rows, T - start)
+            hc = h2[start : start + n]
+            lg = buf[:n]
+            gemm(hc, weight, out=lg)
+            mode = 0 if (need_h or need_w) else 1
+            check(L.ttb_softmax_ce(lg.data_ptr(), y[start : start + n].data_ptr(), loss_rows[start : start + n].data_ptr(), None, n, V, lg.stride(0), int(ignore_index), mode, stream_ptr()), "softmax_ce")
+            if need_h:
+                gemm(lg, weight, b_mn=True, out=dh[start : start + n])
+            if need_w:
+                gemm(lg, hc, a_mn=True, b_mn=True, out=dw, accumulate=True)
+        ctx.save_for_backward(dh, dw)
+        ctx.h_shape = hidden.shape
+        ctx.w_dtype = weight.dtype
+        n_valid = (y != ignore_index).sum()
+        ctx.mark_non_differentiable(n_valid)
+        return loss_rows.sum(), n_valid
+
+    @staticmethod
+    def backward(ctx, g_loss, _g_count):
+        dh, dw = ctx.saved_tensors
+        gh = (dh * g_loss.to(dh.dtype)).view(ctx.h_shape) if dh is not None else None
+        gw = (dw * g_loss).to(ctx.w_dtype) if dw is not None else None
+        return gh, gw, None, None, None
+
+
+def linear_cross_entropy(hidden, weight, labels, ignore_index: int, num_chunks: int):
+    if hidden.shape[-1] % 8 or weight.shape[0] % 8:
+        from . import reference
+
+        return reference.linear_cross_entropy(hidden, weight, labels, ignore_index, num_chunks)
+    return _LinearCE.apply(hidden, weight, labels, ignore_index, num_chunks)
+
+
+class _TokenLogprobs(torch.autograd.Function):
+    """Per-token log p(label) through the output projection; backward recomputes each logits
+    chunk and scales the in-place softmax gradient by the incoming per-token gradient."""
+
+    @staticmethod
+    def forward(ctx, hidden, weight, labels, ignore_index, num_chunks):
+        D = hidden.shape[-1]
+        h2 = hidden.reshape(-1, D).contiguous()
+        y = labels.reshape(-1).to(torch.int64).contiguous()
+        T, V = h2.shape[0], weight.shape[0]
+        rows = _ce_chunk_rows(T, num_chunks)
+        nll = torch.empty(T, dtype=torch.float32, device=h2.device)
+        buf = torch.empty(min(rows, T), V, dtype=_BF16, device=h2.device)
+        for start in range(0, T, rows):
+            n = min(rows, T - start)
+            gemm(h2[start : start + n], weight, out=buf[:n])
+            check(lib().ttb_softmax_ce(buf.data_ptr(), y[start : start + n].data_ptr(), nll[start : start + n].data_ptr(), None, n, V, buf.stride(0), int(ignore_index), 1, stream_ptr()), "softmax_ce")
+        ctx.save_for_backward(h2, weight, y)
+        ctx.meta = (ignore_index, rows, hidden.shape, labels.shape)
+        return (-nll).view(labels.shape)
+
+    @staticmethod
+    def backward(ctx, g):
+        h2, weight, y = ctx.saved_tensors
+        ignore_index, rows, h_shape, _ = ctx.meta
+        T, V = h2.shape[0], weight.shape[0]
+        gs = g.reshape(-1).float().contiguous()
+        need_w = ctx.needs_input_grad[1]
+        dh = torch.empty_like(h2)
+        dw = torch.zeros(V, h2.shape[1], dtype=torch.float32, device=h2.device) if need_w else None
+        buf = torch.empty(min(rows, T), V, dtype=_BF16, device=h2.device)
+        for start in range(0, T, rows):
+            n = min(rows, T - start)
+            hc = h2[start : start + n]
+            gemm(hc, weight, out=buf[:n])
+            check(lib().ttb_softmax_ce(buf.data_ptr(), y[start : start + n].data_ptr(), None, gs[start : start + n].data_ptr(), n, V, buf.stride(0), int(ignore_index), 2, stream_ptr()), "softmax_ce")
+            gemm(buf[:n], weight, b_mn=True, out=dh[start : start + n])
+            if need_w:
+                gemm(buf[:n], hc, a_mn=True, b_mn=True, out=dw, accumulate=True)
+        return dh.view(h_shape), (dw.to(weight.dtype) if need_w else None), None, None, None
+
+
+def token_logprobs(hidden, weight, labels, ignore_index: int, num_chunks: int):
+    return _TokenLogprobs.apply(hidden, weight, labels, ignore_index, num_chunks)
+
+
+# ======================================================================= optimizer
+class _MetaTable:
+    """Device copy of the (param, grad, exp_avg, exp_avg_sq, master) pointer table; rebuilt
+    only when a pointer changes (e.g. gradients re-allocated after ``zero_grad``)."""
+
+    def __init__(self) -> None:
+        self.key: Optional[Tuple[int, ...]] = None
+        self.dev: Optional[torch.Tensor] = None
+        self.n = 0
+        self.chunks = 0
+
+    def update(self, items: Sequence[Tuple[torch.Tensor, torch.Tensor, Dict[str, Any]]], device: torch.device) -> None:
+        chunk = lib().ttb_optim_chunk()
+        rows: List[int] = []
+        total = 0
+        for p, g, st in items:
+            master = st.get("master")
+            rows += [p.data_ptr(), g.data_ptr(), st["exp_avg"].data_ptr(), st["exp_avg_sq"].data_ptr(), master.data_ptr() if master is not None else 0, p.numel(), total]
+            total += -(-p.numel() // chunk)
+        key = tuple(rows)
+        if key != self.key:
+            host = torch.tensor(rows, dtype=torch.int64).view(-1, 7)
+            self.dev = host.to(device, non_blocking=False)
+            self.key = key
+        self.n = len(items)
+        self.chunks = total
+
+
+_tables: Dict[Tuple[int, torch.dtype], _MetaTable] = {}
+
+
+def _table_for(items, tag: int) -> _MetaTable:
+    dtype = items[0][0].dtype
+    tbl = _tables.setdefault((tag, dtype), _MetaTable())
+    tbl.update(items, items[0][0].device)
+    return tbl
+
+
+def adamw_multi(items, lr: float, beta1: float, beta2: float, eps: float, weight_decay: float, grad_scale: Union[float, torch.Tensor] = 1.0, tag: int = 0) -> None:
+    """One kernel launch per dtype group over all ``(param, grad, state)`` triples."""
+    groups: Dict[torch.dtype, list] = {}
+    for it in items:
+        p, g, _ = it
+        if p.dtype not in (_BF16, torch.float32) or g.dtype != p.dtype or not p.is_contiguous() or not g.is_contiguous():
+            raise _lib.KernelError("adamw_multi needs contiguous bf16/fp32 params with same-dtype grads")
+        groups.setdefault(p.dtype, []).append(it)
+    scale_dev = None
+    scale_host = 1.0
+    if isinstance(grad_scale, torch.Tensor):
+        scale_dev = grad_scale.to(torch.float32).reshape(1)
+    else:
+        scale_host = float(grad_scale)
+    for dtype, its in groups.items():
+        step = its[0][2]["step"]
+        tbl = _table_for(its, tag)
+        inv_bc1 = 1.0 / (1.0 - beta1**step)
+        inv_sqrt_bc2 = 1.0 / math.sqrt(1.0 - beta2**step)
+        check(lib().ttb_adamw(tbl.dev.data_ptr(), tbl.n, tbl.chunks, int(dtype == _BF16), lr, beta1, beta2, eps, weight_decay, inv_bc1, inv_sqrt_bc2, _ptr(scale_dev), scale_host, stream_ptr()), "adamw")
+
+
+def grad_sumsq(items, tag: int = 1) -> torch.Tensor:
+    """Sum of squared gradient entries over all items (0-d fp32 tensor, no host sync)."""
+    groups: Dict[torch.dtype, list] = {}
+    for it in items:
+        groups.setdefault(it[0].dtype, []).append(it)
+    total = None
+    for dtype, its in groups.items():
+        tbl = _table_for(its, tag)
+        partials = torch.empty(lib().ttb_optim_grid(), dtype=torch.float32, device=its[0][0].device)
+        check(lib().ttb_grad_sumsq(tbl.dev.data_ptr(), tbl.n, tbl.chunks, int(dtype == _BF16), partials.data_ptr(), stream_ptr()), "grad_sumsq")
+        s = partials.sum()
+        total = s if total is None else total + s
+    return total

@@ -1,0 +1,92 @@
+"""ctypes loader for the in-tree kernel library ``_lib/libttb200.so``.
+
+The library is looked up next to this file; on a machine with a CUDA device a missing
+library is a hard error (operators never fall back silently), on CPU-only machines the
+loader is simply never invoked.
+"""
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+from typing import Optional
+
+import torch
+
+_HERE = Path(__file__).resolve().parent
+LIB_PATH = _HERE / "_lib" / "libttb200.so"
+_lib: Optional[ctypes.CDLL] = None
+_err_words = {}
+
+ERROR_NAMES = {-1: "bad shape or alignment", -2: "driver / launch failure", -3: "size beyond a static limit", -4: "device wait timed out"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise KernelError(
+                f"{LIB_PATH} is missing. Build it with `python -m torchtune_b200.ops.build` (needs nvcc); "
+                "CUDA tensors are never routed to a PyTorch fallback."
+            )
+        _lib = ctypes.CDLL(str(LIB_PATH))
+        _declare(_lib)
+    return _lib
+
+
+def _declare(L: ctypes.CDLL) -> None:
+    c = ctypes
+    vp, i32, i64, f32 = c.c_void_p, c.c_int, c.c_longlong, c.c_float
+    L.ttb_gemm_bf16.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i64, i64, i64, i32, i32, vp, f32, vp, vp]
+    L.ttb_rmsnorm_fwd.argtypes = [vp, vp, vp, vp, i32, i32, f32, vp]
+    L.ttb_rmsnorm_bwd_partials.argtypes = [i32]
+    L.ttb_rmsnorm_bwd.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, vp]
+    L.ttb_rope.argtypes = [vp, vp, vp, vp, i64, i32, i32, i32, i32, i32, vp]
+    L.ttb_swiglu_fwd.argtypes = [vp, vp, vp, i64, i32, i64, i64, i64, vp]
+    L.ttb_swiglu_bwd.argtypes = [vp, vp, vp, vp, vp, i64, i32, i64, i64, i64, i64, i64, vp]
+    L.ttb_adamw.argtypes = [vp, i32, i64, i32, f32, f32, f32, f32, f32, f32, f32, vp, f32, vp]
+    L.ttb_grad_sumsq.argtypes = [vp, i32, i64, i32, vp, vp]
+    L.ttb_softmax_ce.argtypes = [vp, vp, vp, vp, i32, i32, i64, i64, i32, vp]
+    L.ttb_attn_fwd.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, vp, vp]
+    L.ttb_attn_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, vp, vp]
+    L.ttb_attn_fwd.restype = i32
+    L.ttb_ensure_device.argtypes = [i32]
+    L.ttb_ensure_device.restype = i32
+    L.ttb_launch_count.restype = i64
+    L.ttb_attn_bwd.restype = i32
+    for fn in (L.ttb_gemm_bf16, L.ttb_rmsnorm_fwd, L.ttb_rmsnorm_bwd, L.ttb_rope, L.ttb_swiglu_fwd, L.ttb_swiglu_bwd, L.ttb_adamw, L.ttb_grad_sumsq, L.ttb_softmax_ce):
+        fn.restype = i32
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise KernelError(f"{what} failed: {ERROR_NAMES.get(rc, rc)}")
+
+
+def stream_ptr() -> int:
+    """Handle of torch's current stream.  Also binds the calling thread (autograd workers
+    included) to torch's current device inside the kernel library, whose CUDA runtime keeps
+    its own per-thread device state."""
+    lib().ttb_ensure_device(torch.cuda.current_device())
+    return torch.cuda.current_stream().cuda_stream
+
+
+def err_word(device: torch.device) -> torch.Tensor:
+    """Per-device int32 the kernels set when one of their bounded waits gives up."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _err_words:
+        _err_words[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _err_words[key]
+
+
+def check_device_errors(device: Optional[torch.device] = None) -> None:
+    """Synchronising check of the device error word; raises if any kernel timed out."""
+    for key, word in _err_words.items():
+        code = int(word.item())
+        if code != 0:
+            word.zero_()
+            raise KernelError(f"a kernel on cuda:{key} gave up waiting (site code {code}); results are invalid")
+

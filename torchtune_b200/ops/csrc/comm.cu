@@ -1,0 +1,195 @@
+// Peer-memory plumbing and the fused data-parallel optimizer kernel.
+//
+// One process drives one GPU.  Flat parameter and gradient buffers are allocated with
+// cudaMalloc, exported as CUDA IPC handles and mapped by every peer, so a kernel on any rank
+// can load/store any rank's buffer over NVLink (plain peer loads/stores; no TMA is involved).
+//
+// dp_reduce_adamw_bcast: the gradient reduce-scatter, the fp32 scale/cast, the sharded AdamW
+// update and the parameter all-gather of a ZeRO-style data-parallel step as ONE kernel.
+// The rank owning shard [begin, end) pulls the bf16 gradient slices of all peers (16-byte
+// peer loads), sums them in fp32, applies AdamW to its slice of the moments and pushes the
+// new bf16 parameters into every peer's parameter buffer (16-byte peer stores).  Reference
+// equivalents: FSDP2 reduce-scatter + `scale_grads_` + `torch.optim.AdamW(fused=True)` +
+// all-gather (recipes/full_finetune_distributed.py:1030-1050, training/_distributed.py:661-714).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string.h>
+
+#include "common/tmap.h"
+
+namespace ttb {
+
+static constexpr int kMaxRanks = 16;
+
+struct PeerTable {
+  const __nv_bfloat16* grad[kMaxRanks];  // every rank's flat gradient buffer
+  __nv_bfloat16* param[kMaxRanks];       // every rank's flat parameter buffer
+};
+
+__device__ __forceinline__ void unpack8f(const uint4& u, float (&f)[8]) {
+  const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(b[i]);
+    f[2 * i] = t.x, f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8f(const float (&f)[8]) {
+  uint4 u;
+  __nv_bfloat162* b = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) b[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return u;
+}
+
+// mode 0: reduce + AdamW + broadcast in one pass.
+// mode 1: reduce only -> reduced fp32 gradient into `gsum` (shard-local) and per-block partial
+//         sums of squares into `sumsq_partials` (for global-norm clipping).
+// mode 2: AdamW + broadcast reading the already reduced `gsum`.
+template <int WORLD>
+__global__ void __launch_bounds__(256)
+dp_reduce_adamw_bcast_kernel(PeerTable peers, int rank, long long begin, long long count, __nv_bfloat16* __restrict__ m,
+                             __nv_bfloat16* __restrict__ v, float* __restrict__ gsum, float* __restrict__ sumsq_partials,
+                             const float* __restrict__ scale_dev, float scale_host, float lr, float beta1, float beta2,
+                             float eps, float weight_decay, float inv_bc1, float inv_sqrt_bc2, int mode) {
+  __shared__ float red[8];
+  const float gs = scale_host * (scale_dev != nullptr ? *scale_dev : 1.f);
+  const long long nvec = count >> 3;  // shards are multiples of 8 elements
+  float sq = 0.f;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long e = begin + i * 8;
+    float g[8];
+    if (mode == 2) {
+      const float4 a = *reinterpret_cast<const float4*>(gsum + i * 8);
+      const float4 b = *reinterpret_cast<const float4*>(gsum + i * 8 + 4);
+      g[0] = a.x, g[1] = a.y, g[2] = a.z, g[3] = a.w, g[4] = b.x, g[5] = b.y, g[6] = b.z, g[7] = b.w;
+    } else {
+      uint4 raw[WORLD];
+#pragma unroll
+      for (int r = 0; r < WORLD; ++r) {
+        // start with the next rank so that the 8 ranks do not all hit the same peer at once
+        const int src = (rank + 1 + r) % WORLD;
+        raw[r] = *reinterpret_cast<const uint4*>(peers.grad[src] + e);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) g[j] = 0.f;
+#pragma unroll
+      for (int r = 0; r < WORLD; ++r) {
+        float f[8];
+        unpack8f(raw[r], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) g[j] += f[j];
+      }
+    }
+    if (mode == 1) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sq += g[j] * g[j];
+      *reinterpret_cast<float4*>(gsum + i * 8) = make_float4(g[0], g[1], g[2], g[3]);
+      *reinterpret_cast<float4*>(gsum + i * 8 + 4) = make_float4(g[4], g[5], g[6], g[7]);
+      continue;
+    }
+    float w[8], m1[8], v1[8];
+    unpack8f(*reinterpret_cast<const uint4*>(peers.param[rank] + e), w);
+    unpack8f(*reinterpret_cast<const uint4*>(m + i * 8), m1);
+    unpack8f(*reinterpret_cast<const uint4*>(v + i * 8), v1);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float grad = g[j] * gs;
+      m1[j] = beta1 * m1[j] + (1.f - beta1) * grad;
+      v1[j] = beta2 * v1[j] + (1.f - beta2) * grad * grad;
+      w[j] *= (1.f - lr * weight_decay);
+      w[j] -= lr * inv_bc1 * m1[j] / (sqrtf(v1[j]) * inv_sqrt_bc2 + eps);
+    }
+    *reinterpret_cast<uint4*>(m + i * 8) = pack8f(m1);
+    *reinterpret_cast<uint4*>(v + i * 8) = pack8f(v1);
+    const uint4 out = pack8f(w);
+#pragma unroll
+    for (int r = 0; r < WORLD; ++r) {
+      const int dst = (rank + r) % WORLD;
+      *reinterpret_cast<uint4*>(peers.param[dst] + e) = out;
+    }
+  }
+  if (mode == 1) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sq;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.f;
+      for (int i = 0; i < 8; ++i) t += red[i];
+      sumsq_partials[blockIdx.x] = t;
+    }
+  }
+  __threadfence_system();  // peer stores visible before the host-side barrier that follows
+}
+
+}  // namespace ttb
+
+using namespace ttb;
+
+// ----------------------------------------------------------------------------- IPC helpers
+extern "C" int ttb_ipc_alloc(long long bytes, void** out) {
+  return cudaMalloc(out, static_cast<size_t>(bytes)) == cudaSuccess ? kOk : kErrDriver;
+}
+extern "C" int ttb_ipc_free(void* p) { return cudaFree(p) == cudaSuccess ? kOk : kErrDriver; }
+// handle_out: 64 bytes
+extern "C" int ttb_ipc_get_handle(void* p, void* handle_out) {
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, p) != cudaSuccess) return kErrDriver;
+  memcpy(handle_out, &h, sizeof(h));
+  return kOk;
+}
+extern "C" int ttb_ipc_open(const void* handle, void** out) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  cudaError_t e = cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) {
+    fprintf(stderr, "[ttb] cudaIpcOpenMemHandle failed: %s\n", cudaGetErrorString(e));
+    return kErrDriver;
+  }
+  return kOk;
+}
+extern "C" int ttb_ipc_close(void* p) { return cudaIpcCloseMemHandle(p) == cudaSuccess ? kOk : kErrDriver; }
+extern "C" int ttb_dp_grid() { return sm_count() * 4; }
+
+// grad_ptrs / param_ptrs: host arrays of `world` device pointers (peer-mapped flat buffers).
+// [begin, begin+count) is this rank's shard (count % 8 == 0, begin % 8 == 0).
+extern "C" int ttb_dp_reduce_adamw_bcast(void* const* grad_ptrs, void* const* param_ptrs, int world, int rank,
+                                         long long begin, long long count, void* m, void* v, float* gsum,
+                                         float* sumsq_partials, const float* scale_dev, float scale_host, float lr,
+                                         float beta1, float beta2, float eps, float weight_decay, float inv_bc1,
+                                         float inv_sqrt_bc2, int mode, void* stream) {
+  if (world < 1 || world > kMaxRanks || (begin & 7) || (count & 7)) return kErrBadShape;
+  if (count == 0) return kOk;
+  PeerTable t{};
+  for (int r = 0; r < world; ++r) {
+    t.grad[r] = static_cast<const __nv_bfloat16*>(grad_ptrs[r]);
+    t.param[r] = static_cast<__nv_bfloat16*>(param_ptrs[r]);
+  }
+  const int grid = ttb_dp_grid();
+  auto s = static_cast<cudaStream_t>(stream);
+  auto mm = static_cast<__nv_bfloat16*>(m);
+  auto vv = static_cast<__nv_bfloat16*>(v);
+  TTB_COUNT_LAUNCH(1);
+#define TTB_DP_CASE(W)                                                                                              \
+  case W:                                                                                                           \
+    dp_reduce_adamw_bcast_kernel<W><<<grid, 256, 0, s>>>(t, rank, begin, count, mm, vv, gsum, sumsq_partials,       \
+                                                         scale_dev, scale_host, lr, beta1, beta2, eps, weight_decay, \
+                                                         inv_bc1, inv_sqrt_bc2, mode);                               \
+    break;
+  switch (world) {
+    TTB_DP_CASE(1)
+    TTB_DP_CASE(2)
+    TTB_DP_CASE(3)
+    TTB_DP_CASE(4)
+    TTB_DP_CASE(6)
+    TTB_DP_CASE(8)
+    TTB_DP_CASE(16)
+    default:
+      return kErrBadShape;
+  }
+#undef TTB_DP_CASE
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrDriver;
+}

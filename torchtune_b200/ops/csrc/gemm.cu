@@ -1,0 +1,360 @@
+// bf16 GEMM on the 5th-generation tensor cores (tcgen05) with TMEM accumulators.
+//
+//   C[M,N] (+)= alpha * op(A) * op(B)  (+ bias[N])
+//
+// Persistent, warp-specialised kernel, one CTA per SM:
+//   warp 0   TMA producer   (cp.async.bulk.tensor -> 128B-swizzled smem ring, mbarrier tx-count)
+//   warp 1   MMA issuer     (one lane issues tcgen05.mma, tcgen05.commit releases smem / signals epilogue)
+//   warp 2   TMEM allocator (2 x BN fp32 columns: the epilogue of tile i overlaps the main loop of tile i+1)
+//   warps 4-7 epilogue      (tcgen05.ld 32 lanes x 32 columns per warp -> registers -> bf16/fp32 global stores)
+//
+// Operand layouts: an operand is "K-major" when the contraction index is contiguous
+// (X[rows, K]) and "MN-major" when the row/column index is contiguous (X[K, rows]); both are
+// consumed directly through the shared-memory matrix descriptor, so forward (NT), dgrad (NN)
+// and wgrad (TN) need no transposes.  Serves every nn.Linear of the decoder
+// (reference call sites: torchtune/modules/attention.py:234,262-263,303,
+// torchtune/modules/feed_forward.py:50-53).
+#include "common/ptx.cuh"
+#include "common/tmap.h"
+
+namespace ttb {
+
+static constexpr int BM = 128;
+static constexpr int BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
+static constexpr int kThreads = 256;
+static constexpr int kGroupM = 16;  // m-tiles per scheduling group (L2 reuse of the B panel)
+
+struct GemmParams {
+  int M, N, K;
+  void* C;
+  long long ldc;
+  const __nv_bfloat16* bias;  // [N] or nullptr
+  float alpha;
+  int out_fp32;    // 0: bf16 C, 1: fp32 C
+  int accumulate;  // 1: C += result
+  int* err;        // device error word (0 = ok)
+};
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = (200 * 1024 / kStageBytes) > 8 ? 8 : (200 * 1024 / kStageBytes);
+  static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_blk, int& n_blk) {
+  const int per_group = kGroupM * num_n;
+  const int group = t / per_group;
+  const int first_m = group * kGroupM;
+  const int gsize = min(kGroupM, num_m - first_m);
+  const int r = t - group * per_group;
+  m_blk = first_m + r % gsize;
+  n_blk = r / gsize;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+  using Cfg = GemmCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + Cfg::kStages;
+  uint64_t* tfull = bars + 2 * Cfg::kStages;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_m = (p.M + BM - 1) / BM;
+  const int num_n = (p.N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < Cfg::kStages; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull[i], 1);
+      mbar_init(&tempty[i], 4);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x) {
+      int m_blk, n_blk;
+      tile_coords(t, num_m, num_n, m_blk, n_blk);
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!mbar_wait(&empty[stage], phase ^ 1)) {
+          *abort_flag = 1;
+          if (lane == 0) atomicExch(p.err, 101);
+          break;
+        }
+        if (lane == 0) {
+          uint8_t* sa = smem + stage * Cfg::kStageBytes;
+          uint8_t* sb = sa + Cfg::kABytes;
+          mbar_arrive_expect_tx(&full[stage], Cfg::kStageBytes);
+          if (A_MN) {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, &tmA, &full[stage], m_blk * BM + j * 64, kb * BK);
+          } else {
+            tma_load_2d(sa, &tmA, &full[stage], kb * BK, m_blk * BM);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tmB, &full[stage], n_blk * BN + j * 64, kb * BK);
+          } else {
+            tma_load_2d(sb, &tmB, &full[stage], kb * BK, n_blk * BN);
+          }
+        }
+        __syncwarp();
+        if (++stage == Cfg::kStages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+    int stage = 0;
+    uint32_t phase = 0;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x) {
+      if (!mbar_wait(&tempty[acc], acc_phase ^ 1)) {
+        *abort_flag = 1;
+        if (lane == 0) atomicExch(p.err, 102);
+        break;
+      }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + acc * BN;
+      bool ok = true;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!mbar_wait(&full[stage], phase)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
+          const uint32_t sb = sa + Cfg::kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            // K-major: 32 bytes per K=16 step inside the swizzled row; SBO = 8 rows * 128 B.
+            // MN-major: 16 k-rows = 2 swizzle atoms of 1024 B; LBO = one 64-wide box of BK rows.
+            const uint64_t da = A_MN ? make_smem_desc_sw128(sa + k * 2048, 8192, 1024)
+                                     : make_smem_desc_sw128(sa + k * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc_sw128(sb + k * 2048, 8192, 1024)
+                                     : make_smem_desc_sw128(sb + k * 32, 16, 1024);
+            umma_f16(d_tmem, da, db, idesc, (kb | k) != 0);
+          }
+          umma_commit(&empty[stage]);  // smem slot reusable once these MMAs retire
+        }
+        __syncwarp();
+        if (++stage == Cfg::kStages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        if (lane == 0) atomicExch(p.err, 103);
+        break;
+      }
+      if (lane == 0) umma_commit(&tfull[acc]);
+      __syncwarp();
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x) {
+      int m_blk, n_blk;
+      tile_coords(t, num_m, num_n, m_blk, n_blk);
+      if (!mbar_wait(&tfull[acc], acc_phase)) {
+        *abort_flag = 1;
+        if (lane == 0) atomicExch(p.err, 104);
+        break;
+      }
+      tc_fence_after();
+      const int row = m_blk * BM + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n_blk * BN + c * 32;
+        if (row < p.M && col0 < p.N) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < p.N) v[i] += __bfloat162float(__ldg(p.bias + col0 + i));
+          }
+          if (p.out_fp32) {
+            float* dst = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              if (col0 + g * 4 + 4 <= p.N) {
+                float4 o = make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+                if (p.accumulate) {
+                  const float4 old = *reinterpret_cast<const float4*>(dst + g * 4);
+                  o.x += old.x, o.y += old.y, o.z += old.z, o.w += old.w;
+                }
+                *reinterpret_cast<float4*>(dst + g * 4) = o;
+              }
+            }
+          } else {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              if (col0 + g * 8 + 8 <= p.N) {
+                if (p.accumulate) {
+                  const uint4 old = *reinterpret_cast<const uint4*>(dst + g * 8);
+                  const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&old);
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    const float2 f = __bfloat1622float2(ob[i]);
+                    v[g * 8 + 2 * i] += f.x;
+                    v[g * 8 + 2 * i + 1] += f.y;
+                  }
+                }
+                uint4 o;
+                o.x = pack_bf16x2(v[g * 8 + 0], v[g * 8 + 1]);
+                o.y = pack_bf16x2(v[g * 8 + 2], v[g * 8 + 3]);
+                o.z = pack_bf16x2(v[g * 8 + 4], v[g * 8 + 5]);
+                o.w = pack_bf16x2(v[g * 8 + 6], v[g * 8 + 7]);
+                *reinterpret_cast<uint4*>(dst + g * 8) = o;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 2) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+}
+
+template <int BN, bool A_MN, bool B_MN>
+static int launch_gemm(const void* A, const void* B, const GemmParams& p, long long lda, long long ldb,
+                       cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  CUtensorMap tmA, tmB;
+  int rc;
+  // K-major: tensor [rows, K], box [BM|BN rows, 64]; MN-major: tensor [K, rows], box [64 k-rows, 64].
+  if (A_MN)
+    rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.K, p.M, lda, BK, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+  else
+    rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.M, p.K, lda, BM, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != kOk) {
+    fprintf(stderr, "[ttb] gemm: tensor map for A failed (M=%d K=%d lda=%lld a_mn=%d ptr=%p)\n", p.M, p.K, lda, int(A_MN), A);
+    return rc;
+  }
+  if (B_MN)
+    rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.K, p.N, ldb, BK, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+  else
+    rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.N, p.K, ldb, BN, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != kOk) {
+    fprintf(stderr, "[ttb] gemm: tensor map for B failed (N=%d K=%d ldb=%lld b_mn=%d ptr=%p)\n", p.N, p.K, ldb, int(B_MN), B);
+    return rc;
+  }
+
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) {
+      fprintf(stderr, "[ttb] gemm: cudaFuncSetAttribute failed: %s\n", cudaGetErrorString(e));
+      return kErrDriver;
+    }
+    attr_set = true;
+  }
+  const int num_tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int grid = num_tiles < sm_count() ? num_tiles : sm_count();
+  TTB_COUNT_LAUNCH(1);
+  kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tmA, tmB, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    fprintf(stderr, "[ttb] gemm launch failed: %s (M=%d N=%d K=%d grid=%d)\n", cudaGetErrorString(e), p.M, p.N, p.K, grid);
+    return kErrDriver;
+  }
+  return kOk;
+}
+
+template <bool A_MN, bool B_MN>
+static int dispatch_bn(const void* A, const void* B, const GemmParams& p, long long lda, long long ldb,
+                       cudaStream_t stream) {
+  if (p.N > 128) return launch_gemm<256, A_MN, B_MN>(A, B, p, lda, ldb, stream);
+  if (p.N > 64) return launch_gemm<128, A_MN, B_MN>(A, B, p, lda, ldb, stream);
+  return launch_gemm<64, A_MN, B_MN>(A, B, p, lda, ldb, stream);
+}
+
+}  // namespace ttb
+
+// C ABI -------------------------------------------------------------------------------
+// a_mn = 0: A is [M, K] row-major (row stride lda); 1: A is [K, M] row-major.
+// b_mn = 0: B is [N, K] row-major (row stride ldb); 1: B is [K, N] row-major.
+// Requirements: all leading dimensions and the contiguous extents are multiples of 8
+// elements, base pointers 16-byte aligned.  `err` is a device int the kernel sets on a
+// bounded-wait timeout.
+extern "C" int ttb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int a_mn, int b_mn,
+                             long long lda, long long ldb, long long ldc, int out_fp32, int accumulate,
+                             const void* bias, float alpha, int* err, void* stream) {
+  using namespace ttb;
+  if (M <= 0 || N <= 0 || K <= 0) return kErrBadShape;
+  if ((lda & 7) || (ldb & 7) || (ldc & (out_fp32 ? 3 : 7)) || (N & 7)) return kErrBadShape;
+  if ((a_mn ? (M & 7) : (K & 7)) || (b_mn ? (N & 7) : (K & 7))) return kErrBadShape;
+  GemmParams p;
+  p.M = M, p.N = N, p.K = K, p.C = C, p.ldc = ldc;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.alpha = alpha, p.out_fp32 = out_fp32, p.accumulate = accumulate, p.err = err;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (!a_mn && !b_mn) return dispatch_bn<false, false>(A, B, p, lda, ldb, s);
+  if (!a_mn && b_mn) return dispatch_bn<false, true>(A, B, p, lda, ldb, s);
+  if (a_mn && b_mn) return dispatch_bn<true, true>(A, B, p, lda, ldb, s);
+  return dispatch_bn<true, false>(A, B, p, lda, ldb, s);
+}

@@ -48,12 +48,18 @@ class AdamW(Optimizer):
         return st
 
     @torch.no_grad()
-    def step(self, closure=None, grad_scale: Union[float, torch.Tensor, None] = None):
+    def step(self, closure=None, grad_scale: Union[float, torch.Tensor, None] = None, max_grad_norm: Optional[float] = None):
+        """``grad_scale`` multiplies every gradient inside the update (float or 0-d device
+        tensor, no host sync).  With ``max_grad_norm`` the global norm of the *scaled*
+        gradients is clipped to it; the norm is returned as ``self.last_grad_norm``."""
         loss = None
         if closure is not None:
             with torch.enable_grad():
                 loss = closure()
         scale = self.grad_scale if grad_scale is None else grad_scale
+        self.last_grad_norm = None
+        if max_grad_norm is not None:
+            scale = self._clip_scale(scale, float(max_grad_norm))
         for group in self.param_groups:
             b1, b2 = group["betas"]
             cuda_items: List[Tuple[torch.Tensor, torch.Tensor, Dict[str, Any]]] = []
@@ -72,3 +78,19 @@ class AdamW(Optimizer):
 
                 _cuda.adamw_multi(cuda_items, float(group["lr"]), b1, b2, group["eps"], group["weight_decay"], scale)
         return loss
+
+    def _clip_scale(self, scale, max_norm: float):
+        grads = [p.grad for g in self.param_groups for p in g["params"] if p.grad is not None]
+        if not grads:
+            return scale
+        if grads[0].is_cuda:
+            from ..ops import _cuda
+
+            items = [(p, p.grad, self._init_state(p, g)) for g in self.param_groups for p in g["params"] if p.grad is not None]
+            sumsq = _cuda.grad_sumsq(items)
+        else:
+            sumsq = torch.stack([g.float().pow(2).sum() for g in grads]).sum()
+        norm = sumsq.sqrt() * scale
+        self.last_grad_norm = norm
+        coef = torch.clamp(max_norm / (norm + 1e-6), max=1.0)
+        return coef * scale

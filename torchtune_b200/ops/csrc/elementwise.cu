@@ -354,3 +354,68 @@ extern "C" int ttb_swiglu_bwd(const void* dy, const void* g, const void* u, void
       static_cast<__nv_bfloat16*>(dg), static_cast<__nv_bfloat16*>(du), rows, H, lddy, ldg, ldu, lddg, lddu);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrDriver;
 }
+
+// ------------------------------------------------------------------------------------------
+// Allocation-free RMSNorm backward (declaration and contract: rmsnorm_bwd_noalloc.h).
+// The per-CTA partial sums of dscale live in a fixed array inside the library image.
+#include "rmsnorm_bwd_noalloc.h"
+
+static __device__ __align__(256) float g_rmsnorm_noalloc_partials[TTB_RMSNORM_NOALLOC_MAX_CTAS * TTB_RMSNORM_NOALLOC_MAX_D];
+
+namespace ttb {
+
+// dscale[c] = sum over the first `n_partials` rows of partials[:, c]
+__global__ void rmsnorm_noalloc_finalize_kernel(const float* __restrict__ partials, float* __restrict__ dscale,
+                                                int n_partials, int D) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= D) return;
+  float acc = 0.f;
+  for (int r = 0; r < n_partials; ++r) acc += partials[static_cast<long long>(r) * D + c];
+  dscale[c] = acc;
+}
+
+static constexpr int kNoAllocMaxDevices = 64;
+
+// In host code the array's name is only a stand-in for the symbol; the address usable by
+// kernels has to be looked up per device, with that device current.
+static float* noalloc_scratch_for_current_device() {
+  static float* cached[kNoAllocMaxDevices] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices) return nullptr;
+  if (cached[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_rmsnorm_noalloc_partials) != cudaSuccess) return nullptr;
+    cached[dev] = static_cast<float*>(p);
+  }
+  return cached[dev];
+}
+
+}  // namespace ttb
+
+extern "C" int ttb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* scale, const float* rstd, void* dx,
+                                       float* dscale, int rows, int D, void* stream) {
+  if (rows <= 0 || D <= 0 || (D & 7)) return kErrBadShape;
+  if (D > TTB_RMSNORM_NOALLOC_MAX_D) return kErrTooLarge;
+  if (scale != nullptr && dscale == nullptr) return kErrBadShape;
+  float* scratch = noalloc_scratch_for_current_device();
+  if (scratch == nullptr) return kErrDriver;
+  const int grid = rows < TTB_RMSNORM_NOALLOC_MAX_CTAS ? rows : TTB_RMSNORM_NOALLOC_MAX_CTAS;
+  const int nvec = D >> 3;
+  auto s = static_cast<cudaStream_t>(stream);
+  float* partials = scale != nullptr ? scratch : nullptr;
+  const __nv_bfloat16* dyp = static_cast<const __nv_bfloat16*>(dy);
+  const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
+  const __nv_bfloat16* sp = static_cast<const __nv_bfloat16*>(scale);
+  __nv_bfloat16* dxp = static_cast<__nv_bfloat16*>(dx);
+  TTB_COUNT_LAUNCH(1);
+  if (nvec <= 256) rmsnorm_bwd_kernel<1><<<grid, 256, 0, s>>>(dyp, xp, sp, rstd, dxp, partials, rows, D);
+  else if (nvec <= 512) rmsnorm_bwd_kernel<2><<<grid, 256, 0, s>>>(dyp, xp, sp, rstd, dxp, partials, rows, D);
+  else rmsnorm_bwd_kernel<4><<<grid, 256, 0, s>>>(dyp, xp, sp, rstd, dxp, partials, rows, D);
+  if (cudaGetLastError() != cudaSuccess) return kErrDriver;
+  if (scale != nullptr) {
+    TTB_COUNT_LAUNCH(1);
+    rmsnorm_noalloc_finalize_kernel<<<(D + 255) / 256, 256, 0, s>>>(scratch, dscale, grid, D);
+    if (cudaGetLastError() != cudaSuccess) return kErrDriver;
+  }
+  return kOk;
+}

@@ -273,3 +273,109 @@ def test_tiny_llama_bf16_matches_fp32_reference():
         denom = g_ref[n].norm().item() + 1e-6
         rel = (g_ref[n] - g_gpu[n]).norm().item() / denom
         assert rel < 0.08, f"{n}: relative grad error {rel:.3f}"
+
+
+# ------------------------------------------------------------------ data-parallel fused step
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_dp_reduce_adamw_bcast_emulated_ranks(world):
+    """All ranks' buffers live on one GPU; the kernel is launched once per emulated rank (the
+    launches do not wait on each other, so running them back to back is equivalent)."""
+    import ctypes
+
+    from torchtune_b200.ops._lib import check, lib, stream_ptr
+    from torchtune_b200.parallel.dp import _declare_dp
+
+    L = lib()
+    _declare_dp(L)
+    shard = 4096
+    total = shard * world
+    g = torch.Generator(device="cuda").manual_seed(world)
+    p0 = (torch.randn(total, generator=g, device="cuda") * 0.1).bfloat16()
+    params = [p0.clone() for _ in range(world)]
+    grads = [(torch.randn(total, generator=g, device="cuda")).bfloat16() for _ in range(world)]
+    m = [torch.zeros(shard, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    v = [torch.zeros(shard, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    gp = (ctypes.c_void_p * world)(*[t.data_ptr() for t in grads])
+    pp = (ctypes.c_void_p * world)(*[t.data_ptr() for t in params])
+    lr, b1, b2, eps, wd, scale = 1e-2, 0.9, 0.999, 1e-8, 0.1, 0.25
+    for r in range(world):
+        check(L.ttb_dp_reduce_adamw_bcast(gp, pp, world, r, r * shard, shard, m[r].data_ptr(), v[r].data_ptr(), None, None, None, scale, lr, b1, b2, eps, wd, 1.0 / (1 - b1), 1.0 / math.sqrt(1 - b2), 0, stream_ptr()), "dp kernel")
+    torch.cuda.synchronize()
+    gsum = torch.stack([t.float() for t in grads]).sum(0) * scale
+    want = p0.float().clone()
+    mm, vv = torch.zeros(total, device="cuda"), torch.zeros(total, device="cuda")
+    ref.adamw_step(want, gsum, mm, vv, 1, lr, b1, b2, eps, wd)
+    for r in range(world):
+        _close(params[r], want, 1e-2, 1e-3, f"params on rank {r}")
+    _close(torch.cat(m), mm, 2e-2, 1e-3, "exp_avg")
+
+    # clipped variant: reduce -> norm -> update
+    params2 = [p0.clone() for _ in range(world)]
+    pp2 = (ctypes.c_void_p * world)(*[t.data_ptr() for t in params2])
+    m2 = [torch.zeros(shard, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    v2 = [torch.zeros(shard, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    gs = [torch.empty(shard, dtype=torch.float32, device="cuda") for _ in range(world)]
+    parts = [torch.empty(L.ttb_dp_grid(), dtype=torch.float32, device="cuda") for _ in range(world)]
+    for r in range(world):
+        check(L.ttb_dp_reduce_adamw_bcast(gp, pp2, world, r, r * shard, shard, m2[r].data_ptr(), v2[r].data_ptr(), gs[r].data_ptr(), parts[r].data_ptr(), None, 1.0, lr, b1, b2, eps, wd, 1.0, 1.0, 1, stream_ptr()), "dp reduce")
+    norm = torch.stack([p.sum() for p in parts]).sum().sqrt() * scale
+    _close(norm, gsum.norm(), 1e-3, 1e-3, "global norm")
+    coef = (torch.clamp(1.0 / (norm + 1e-6), max=1.0) * scale).reshape(1).float()
+    for r in range(world):
+        check(L.ttb_dp_reduce_adamw_bcast(gp, pp2, world, r, r * shard, shard, m2[r].data_ptr(), v2[r].data_ptr(), gs[r].data_ptr(), None, coef.data_ptr(), 1.0, lr, b1, b2, eps, wd, 1.0 / (1 - b1), 1.0 / math.sqrt(1 - b2), 2, stream_ptr()), "dp update")
+    want2 = p0.float().clone()
+    mm, vv = torch.zeros(total, device="cuda"), torch.zeros(total, device="cuda")
+    ref.adamw_step(want2, gsum * float(torch.clamp(1.0 / (gsum.norm() + 1e-6), max=1.0)), mm, vv, 1, lr, b1, b2, eps, wd)
+    for r in range(world):
+        _close(params2[r], want2, 1e-2, 1e-3, f"clipped params on rank {r}")
+
+
+@pytest.mark.parametrize("side_stream", [False, True])
+def test_flat_engine_with_checkpointing_matches_plain_training(side_stream):
+    """Flat store + direct weight-gradient delivery (+ side stream) + activation checkpointing
+    give the same parameters after two steps as ordinary autograd with the multi-tensor AdamW."""
+    import copy
+
+    from helpers import TINY, fixed_init_
+    from torchtune_b200 import training
+    from torchtune_b200.engine.train_step import TrainStep
+    from torchtune_b200.models.llama3_1 import llama3_1
+    from torchtune_b200.modules import TransformerSelfAttentionLayer
+    from torchtune_b200.modules.loss import LinearCrossEntropyLoss
+    from torchtune_b200.ops import _cuda
+    from torchtune_b200.optim import AdamW
+    from torchtune_b200.parallel import DataParallelEngine
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    base = llama3_1(**TINY)
+    fixed_init_(base)
+    base = base.to(torch.bfloat16).to(dev)
+    tokens = torch.randint(0, 1024, (2, 128), device=dev)
+    labels = torch.roll(tokens, -1, 1)
+    batch = {"tokens": tokens, "labels": labels}
+
+    plain = copy.deepcopy(base)
+    lf1 = LinearCrossEntropyLoss()
+    lf1.set_model_output(plain)
+    s1 = TrainStep(plain, lf1, AdamW(plain.parameters(), lr=1e-3), dev)
+
+    flat_model = copy.deepcopy(base)
+    training.set_activation_checkpointing(flat_model, {TransformerSelfAttentionLayer})
+    lf2 = LinearCrossEntropyLoss()
+    lf2.set_model_output(flat_model)
+    eng = DataParallelEngine(dev)
+    eng.prepare(flat_model)
+    _cuda.enable_direct_wgrad(True, use_side_stream=side_stream)
+    s2 = TrainStep(flat_model, lf2, eng.build_optimizer(flat_model, lr=1e-3), dev, parallel=eng)
+    try:
+        for _ in range(2):
+            l1 = s1.compute(dict(batch))
+            l2 = s2.compute(dict(batch))
+            assert abs(l1.item() - l2.item()) < 2e-2
+        torch.cuda.synchronize()
+        for (n, a), (_, b) in zip(plain.named_parameters(), flat_model.named_parameters()):
+            _close(b, a, 2e-2, 3e-3, n)
+    finally:
+        _cuda.enable_direct_wgrad(False)
+        del s2, flat_model
+        eng.shutdown()

@@ -80,14 +80,83 @@ class _Linear(torch.autograd.Function):
     def backward(ctx, dy):
         x2, weight = ctx.saved_tensors
         dy2 = dy.reshape(-1, dy.shape[-1])
+        if dy2.stride(1) != 1 or dy2.stride(0) % 8:
+            dy2 = dy2.contiguous()
         dx = dw = db = None
+        if ctx.needs_input_grad[1]:
+            dw = _wgrad(weight, dy2, x2)  # dW = dYᵀ · X (possibly on the side stream)
         if ctx.needs_input_grad[0]:
             dx = gemm(dy2, weight, b_mn=True).view(ctx.x_shape)  # dX = dY · W
-        if ctx.needs_input_grad[1]:
-            dw = gemm(dy2, x2, a_mn=True, b_mn=True)  # dW = dYᵀ · X
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = dy2.sum(0)
         return dx, dw, db
+
+
+# --- weight-gradient delivery ------------------------------------------------------------
+# A parameter that lives in a flat store carries `_grad_buffer` (its window of the flat
+# gradient buffer).  Its weight gradient is then written (or accumulated) straight into that
+# window by the GEMM epilogue and autograd receives no tensor.  Those GEMMs are issued on a
+# side stream: they are independent of the dgrad chain, so the hardware fills the SMs that a
+# persistent kernel's last partial wave leaves idle with tiles of the other stream's kernel.
+_direct_wgrad = False
+_wgrad_stream: Optional[torch.cuda.Stream] = None
+_wgrad_pending = False
+# data_ptr -> owning parameter.  Tensors handed to backward may be detached aliases of the
+# parameter (activation checkpointing re-materialises saved tensors), so Python attributes
+# cannot be relied on; the storage address of a flat-store window is stable and unique.
+_grad_windows: Dict[int, torch.Tensor] = {}
+
+
+def register_grad_window(param: torch.Tensor) -> None:
+    _grad_windows[param.data_ptr()] = param
+
+
+def grad_window_owner(weight: torch.Tensor) -> Optional[torch.Tensor]:
+    if not _direct_wgrad:
+        return None
+    owner = _grad_windows.get(weight.data_ptr())
+    if owner is not None and owner.shape == weight.shape:
+        return owner
+    return None
+
+
+def enable_direct_wgrad(flag: bool, use_side_stream: Optional[bool] = None) -> None:
+    global _direct_wgrad, _wgrad_stream
+    import os
+
+    _direct_wgrad = flag
+    if use_side_stream is None:
+        use_side_stream = os.environ.get("TTB_WGRAD_STREAM", "1") != "0"
+    _wgrad_stream = torch.cuda.Stream() if (flag and use_side_stream) else None
+
+
+def join_wgrad_stream() -> None:
+    """Make the current stream wait for every weight-gradient GEMM issued so far."""
+    global _wgrad_pending
+    if _wgrad_stream is not None and _wgrad_pending:
+        torch.cuda.current_stream().wait_stream(_wgrad_stream)
+        _wgrad_pending = False
+
+
+def _wgrad(weight: torch.Tensor, dy2: torch.Tensor, x2: torch.Tensor) -> Optional[torch.Tensor]:
+    global _wgrad_pending
+    owner = grad_window_owner(weight)
+    if owner is None:
+        return gemm(dy2, x2, a_mn=True, b_mn=True)
+    buf = owner._grad_buffer
+    accumulate = bool(owner._grad_written)
+    owner._grad_written = True
+    if _wgrad_stream is None:
+        gemm(dy2, x2, a_mn=True, b_mn=True, out=buf, accumulate=accumulate)
+        return None
+    cur = torch.cuda.current_stream()
+    _wgrad_stream.wait_stream(cur)
+    with torch.cuda.stream(_wgrad_stream):
+        gemm(dy2, x2, a_mn=True, b_mn=True, out=buf, accumulate=accumulate)
+    dy2.record_stream(_wgrad_stream)
+    x2.record_stream(_wgrad_stream)
+    _wgrad_pending = True
+    return None
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -223,10 +292,16 @@ def _ce_chunk_rows(T: int, num_chunks: int) -> int:
     return max(1, -(-T // max(1, num_chunks)))
 
 
+# Above this many bytes of bf16 logits the token dimension is processed in chunks; below it the
+# whole batch is one pass (one logits GEMM, one dgrad, one wgrad written once in bf16).
+_CE_SINGLE_PASS_BYTES = 6 * 2**30
+
+
 class _LinearCE(torch.autograd.Function):
-    """Loss and both gradients in one forward sweep: per token chunk, logits = H·Wᵀ (bf16, as
-    the unfused bf16 projection produces), softmax-CE turns the chunk into dlogits in place,
-    then dH = dlogits·W and dW += dlogitsᵀ·H while the chunk is still hot in L2."""
+    """Loss and both gradients in one forward sweep: logits = H·Wᵀ (bf16, as the unfused bf16
+    projection produces), softmax-CE turns them into dlogits in place, then dH = dlogits·W and
+    dW = dlogitsᵀ·H while the logits are still hot.  ``num_chunks`` bounds memory: chunking is
+    only used when the full logits buffer would exceed ``_CE_SINGLE_PASS_BYTES``."""
 
     @staticmethod
     def forward(ctx, hidden, weight, labels, ignore_index, num_chunks):
@@ -238,10 +313,17 @@ class _LinearCE(torch.autograd.Function):
         T, V = h2.shape[0], weight.shape[0]
         need_h = ctx.needs_input_grad[0]
         need_w = ctx.needs_input_grad[1]
+        if T * V * 2 <= _CE_SINGLE_PASS_BYTES:
+            num_chunks = 1
         rows = _ce_chunk_rows(T, num_chunks)
+        single = rows >= T
         loss_rows = torch.empty(T, dtype=torch.float32, device=h2.device)
         dh = torch.empty_like(h2) if need_h else None
-        dw = torch.zeros(V, D, dtype=torch.float32, device=h2.device) if need_w else None
+        owner = grad_window_owner(weight) if (need_w and single) else None
+        direct = owner is not None
+        dw = None
+        if need_w and not direct:
+            dw = torch.empty(V, D, dtype=_BF16, device=h2.device) if single else torch.zeros(V, D, dtype=torch.float32, device=h2.device)
         buf = torch.empty(min(rows, T), V, dtype=_BF16, device=h2.device)
         L = lib()
         for start in range(0, T, rows):
@@ -253,11 +335,15 @@ class _LinearCE(torch.autograd.Function):
             check(L.ttb_softmax_ce(lg.data_ptr(), y[start : start + n].data_ptr(), loss_rows[start : start + n].data_ptr(), None, n, V, lg.stride(0), int(ignore_index), mode, stream_ptr()), "softmax_ce")
             if need_h:
                 gemm(lg, weight, b_mn=True, out=dh[start : start + n])
-            if need_w:
-                gemm(lg, hc, a_mn=True, b_mn=True, out=dw, accumulate=True)
+            if direct:
+                gemm(lg, hc, a_mn=True, b_mn=True, out=owner._grad_buffer, accumulate=bool(owner._grad_written))
+                owner._grad_written = True
+            elif need_w:
+                gemm(lg, hc, a_mn=True, b_mn=True, out=dw, accumulate=not single)
         ctx.save_for_backward(dh, dw)
         ctx.h_shape = hidden.shape
         ctx.w_dtype = weight.dtype
+        ctx.direct = direct
         n_valid = (y != ignore_index).sum()
         ctx.mark_non_differentiable(n_valid)
         return loss_rows.sum(), n_valid
@@ -265,6 +351,9 @@ class _LinearCE(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g_loss, _g_count):
         dh, dw = ctx.saved_tensors
+        # The gradients were formed for d(loss_sum) = 1; an upstream factor multiplies them.
+        # With direct delivery the weight gradient already sits in the flat buffer, which is
+        # only valid for an upstream factor of one (the recipes back-propagate the sum itself).
         gh = (dh * g_loss.to(dh.dtype)).view(ctx.h_shape) if dh is not None else None
         gw = (dw * g_loss).to(ctx.w_dtype) if dw is not None else None
         return gh, gw, None, None, None

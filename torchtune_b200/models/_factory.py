@@ -79,6 +79,12 @@ class DecoderArch:
     embedding: Callable[[int, int], nn.Module] = lambda v, d: nn.Embedding(v, d)
     activation: Callable[[], nn.Module] = nn.SiLU
     mlp_bias: bool = False
+    qk_norm_before_rope: bool = False  # Qwen3 normalises q/k per head before the rotation
+    post_norms: bool = False  # Gemma-2: extra norms on the attention / MLP outputs (sa_scale, mlp_scale)
+    final_norm: Optional[Callable[[int, float], nn.Module]] = None  # defaults to `norm`
+    attn_softcap: float = 0.0
+    attn_scale: Optional[float] = None
+    sliding_window: Optional[Callable[[int], int]] = None  # layer index -> window (0 = global)
 
     def resolved_head_dim(self) -> int:
         return self.head_dim or self.embed_dim // self.num_heads
@@ -107,7 +113,29 @@ def build_attention(arch: DecoderArch, ad: AdapterSpec, rope: Optional[nn.Module
         k_norm=arch.qk_norm(hd, arch.norm_eps) if arch.qk_norm else None,
         max_seq_len=arch.max_seq_len,
         attn_dropout=arch.attn_dropout,
+        softcap=arch.attn_softcap,
+        scale=arch.attn_scale,
+        qk_norm_before_rope=arch.qk_norm_before_rope,
     )
+
+
+def _window_mask_mod(window: int):
+    """Per-layer mask hook adding a sliding window to whatever mask the batch carries."""
+    from dataclasses import replace
+
+    from ..ops.mask import AttentionMask
+
+    def mod(mask, bsz, seq_len):
+        if mask is None:
+            return AttentionMask(causal=True, window=window)
+        if isinstance(mask, AttentionMask) and mask.bool_mask is None:
+            return replace(mask, window=window)
+        dense = mask.bool_mask if isinstance(mask, AttentionMask) else mask
+        q = torch.arange(dense.shape[-2], device=dense.device).view(-1, 1) + (dense.shape[-1] - dense.shape[-2])
+        k = torch.arange(dense.shape[-1], device=dense.device).view(1, -1)
+        return dense & ((q - k) < window)
+
+    return mod
 
 
 def build_mlp(dim: int, hidden: int, ad: AdapterSpec, activation: Optional[nn.Module] = None, bias: bool = False) -> FeedForward:
@@ -124,13 +152,17 @@ def build_decoder(arch: DecoderArch, adapter: Optional[AdapterSpec] = None) -> T
     hd = arch.resolved_head_dim()
     rope = arch.rope(hd, arch.max_seq_len) if arch.rope else None  # one instance shared by all layers
     layers: List[nn.Module] = []
-    for _ in range(arch.num_layers):
+    for idx in range(arch.num_layers):
+        window = arch.sliding_window(idx) if arch.sliding_window else 0
         layers.append(
             TransformerSelfAttentionLayer(
                 attn=build_attention(arch, ad, rope),
                 mlp=build_mlp(arch.embed_dim, arch.resolved_hidden(), ad, arch.activation(), arch.mlp_bias),
                 sa_norm=arch.norm(arch.embed_dim, arch.norm_eps),
                 mlp_norm=arch.norm(arch.embed_dim, arch.norm_eps),
+                sa_scale=arch.norm(arch.embed_dim, arch.norm_eps) if arch.post_norms else None,
+                mlp_scale=arch.norm(arch.embed_dim, arch.norm_eps) if arch.post_norms else None,
+                mask_mod=_window_mask_mod(window) if window else None,
             )
         )
     tok = arch.embedding(arch.vocab_size, arch.embed_dim)
@@ -150,7 +182,7 @@ def build_decoder(arch: DecoderArch, adapter: Optional[AdapterSpec] = None) -> T
         max_seq_len=arch.max_seq_len,
         num_heads=arch.num_heads,
         head_dim=hd,
-        norm=arch.norm(arch.embed_dim, arch.norm_eps),
+        norm=(arch.final_norm or arch.norm)(arch.embed_dim, arch.norm_eps),
         output=output,
     )
     if ad.quantize_base:

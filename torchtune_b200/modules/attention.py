@@ -55,6 +55,7 @@ class MultiHeadAttention(nn.Module):
         attn_dropout: float = 0.0,
         softcap: float = 0.0,
         scale: Optional[float] = None,
+        qk_norm_before_rope: bool = False,
     ) -> None:
         super().__init__()
         if num_heads % num_kv_heads != 0:
@@ -82,6 +83,7 @@ class MultiHeadAttention(nn.Module):
         self.q_norm = q_norm
         self.k_norm = k_norm
         self.pos_embeddings = pos_embeddings
+        self.qk_norm_before_rope = qk_norm_before_rope
         self.cache_enabled = False
 
     def setup_cache(self, batch_size: int, dtype: torch.dtype, max_seq_len: int) -> None:
@@ -106,9 +108,11 @@ class MultiHeadAttention(nn.Module):
     ) -> torch.Tensor:
         b, s_x, _ = x.shape
         q = self.q_proj(x).view(b, s_x, self.num_heads, self.head_dim)
+        if self.q_norm is not None and self.qk_norm_before_rope:
+            q = self.q_norm(q)
         if self.pos_embeddings is not None:
             q = self.pos_embeddings(q, input_pos=input_pos)
-        if self.q_norm is not None:
+        if self.q_norm is not None and not self.qk_norm_before_rope:
             q = self.q_norm(q)
 
         if y is None:
@@ -119,9 +123,11 @@ class MultiHeadAttention(nn.Module):
             s_y = y.shape[1]
             k = self.k_proj(y).view(b, s_y, self.num_kv_heads, self.head_dim)
             v = self.v_proj(y).view(b, s_y, self.num_kv_heads, self.head_dim)
+            if self.k_norm is not None and self.qk_norm_before_rope:
+                k = self.k_norm(k)
             if self.pos_embeddings is not None:
                 k = self.pos_embeddings(k, input_pos=input_pos)
-            if self.k_norm is not None:
+            if self.k_norm is not None and not self.qk_norm_before_rope:
                 k = self.k_norm(k)
             if self.kv_cache is not None and self.cache_enabled:
                 k, v = self.kv_cache.update(k, v)

@@ -126,6 +126,42 @@ class ShardedAdamW:
         for g, saved in zip(self.param_groups, sd.get("param_groups", [])):
             g.update(saved)
 
+    def full_state_dict(self, is_rank_zero: bool = True, group=None) -> Dict[str, Any]:
+        """Moments of the whole model as one flat CPU tensor each plus the parameter layout, so a
+        checkpoint written at one world size can be read at another."""
+        flat = self.flat
+        out = {}
+        for key, shard in (("exp_avg", self.exp_avg), ("exp_avg_sq", self.exp_avg_sq)):
+            if self.world > 1:
+                parts = [torch.empty_like(shard) for _ in range(self.world)]
+                dist.all_gather(parts, shard, group=group)
+                full = torch.cat(parts)
+            else:
+                full = shard
+            out[key] = full.cpu() if is_rank_zero else None
+        if not is_rank_zero:
+            return {}
+        out["step"] = self.step_count
+        out["layout"] = {"names": list(flat.names), "offsets": list(flat.offsets), "numels": [p.numel() for p in flat.params]}
+        out["param_groups"] = [{k: v for k, v in g.items() if k != "params"} for g in self.param_groups]
+        return out
+
+    def load_full_state_dict(self, sd: Dict[str, Any]) -> None:
+        flat = self.flat
+        layout = sd.get("layout")
+        if layout is not None and (list(layout["names"]) != list(flat.names) or list(layout["numels"]) != [p.numel() for p in flat.params]):
+            raise ValueError("optimizer checkpoint was written for a different set of trainable parameters")
+        self.step_count = int(sd["step"])
+        begin = self.rank * flat.shard
+        for key, shard in (("exp_avg", self.exp_avg), ("exp_avg_sq", self.exp_avg_sq)):
+            full = sd[key]
+            shard.zero_()
+            end = min(begin + flat.shard, full.numel())
+            if end > begin:
+                shard[: end - begin].copy_(full[begin:end])
+        for g, saved in zip(self.param_groups, sd.get("param_groups", [])):
+            g.update(saved)
+
     def step(self, grad_scale: Union[float, torch.Tensor] = 1.0, max_grad_norm: Optional[float] = None, group=None) -> None:
         g = self.param_groups[0]
         self.step_count += 1

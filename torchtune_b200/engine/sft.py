@@ -179,8 +179,9 @@ class SFTTrainer:
 
     def _setup_model(self, cfg: DictConfig, ckpt: Dict[str, Any]) -> nn.Module:
         t0 = time.perf_counter()
-        init_device = torch.device("meta") if self.parallel is not None else self._device
-        with training.set_default_dtype(self._dtype), init_device:
+        # parameters stay resident on every rank (180 GB parts), so the model is built directly on
+        # the device; there is no meta-device / deferred-init stage to undo
+        with training.set_default_dtype(self._dtype), self._device:
             model = config.instantiate(cfg.model)
         if cfg.get("resize_token_embeddings") and self._tokenizer_vocab(cfg) is not None:
             modules.resize_token_embeddings(model, self._tokenizer_vocab(cfg))

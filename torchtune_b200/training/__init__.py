@@ -38,3 +38,18 @@ from .precision import get_dtype, set_default_dtype, validate_expected_param_dty
 from .seed import set_seed
 from ._activation_offloading import NoOpManager, OffloadActivations, get_act_offloading_ctx_manager
 from ._profiler import DummyProfiler, setup_torch_profiler
+from ._distributed import (
+    VALID_BACKENDS_FOR_MEMORY_STATS,
+    ParallelDims,
+    gather_cpu_state_dict,
+    get_distributed_backend,
+    get_full_optimizer_state_dict,
+    get_world_size_and_rank,
+    init_distributed,
+    is_distributed,
+    load_from_full_model_state_dict,
+    load_from_full_optimizer_state_dict,
+    materialize,
+    set_torch_num_threads,
+    validate_no_params_on_meta_device,
+)

@@ -366,6 +366,23 @@ class SFTTrainer:
             loss = self._loss_fn(outputs.reshape(-1, outputs.size(-1)), labels.reshape(-1))
         return loss * n_valid, n_valid
 
+    def _add_aux_sum(self, name: str, value: torch.Tensor) -> None:
+        """Accumulate a token-summed auxiliary metric (logged as ``sum / num_tokens`` each step)."""
+        sums = self.__dict__.setdefault("_aux_sums", {})
+        sums[name] = sums.get(name, 0.0) + value.detach().float()
+
+    def _reduce_aux_sums(self, num_tokens: torch.Tensor) -> Dict[str, float]:
+        sums = self.__dict__.get("_aux_sums") or {}
+        if not sums:
+            return {}
+        keys = sorted(sums)
+        packed = torch.stack([sums[k] for k in keys])
+        if self.parallel is not None:
+            self.parallel.all_reduce_sum_(packed)
+        out = {k: (v / num_tokens).item() for k, v in zip(keys, packed)}
+        self._aux_sums = {}
+        return out
+
     @torch.no_grad()
     def validate(self) -> Dict[str, float]:
         self._model.eval()
@@ -433,6 +450,7 @@ class SFTTrainer:
                     self.global_step += 1
 
                     timer.stop()
+                    aux = self._reduce_aux_sums(num_tokens)
                     loss_to_log = (running_loss / num_tokens).item()
                     pbar.update(1)
                     pbar.set_description(f"{curr_epoch + 1}|{self.global_step}|Loss: {loss_to_log}")
@@ -448,6 +466,7 @@ class SFTTrainer:
                             log_dict.update(training.get_memory_stats(device=self._device))
                         if grad_norm is not None:
                             log_dict["grad_norm"] = float(grad_norm)
+                        log_dict.update(aux)
                         self._metric_logger.log_dict(log_dict, step=self.global_step)
                     running_loss.zero_()
                     num_tokens.zero_()

@@ -23,11 +23,11 @@ def fixed_init_(model: torch.nn.Module, std: float = 0.02, seed: int = 0) -> Non
                 p.copy_(torch.randn(p.shape, generator=g) * std)
 
 
-def write_tiny_hf_checkpoint(path: Path, arch=TINY, seed: int = 0, dtype=torch.float32) -> dict:
+def write_tiny_hf_checkpoint(path: Path, arch=TINY, seed: int = 0, dtype=torch.float32, builder=None) -> dict:
     from torchtune_b200.models.llama3_1 import llama3_1
 
     path.mkdir(parents=True, exist_ok=True)
-    model = llama3_1(**arch)
+    model = (builder or llama3_1)(**arch)
     fixed_init_(model, seed=seed)
     sd = {k: v.to(dtype) for k, v in model.state_dict().items()}
     hf = tune_to_hf(sd, num_heads=arch["num_heads"], num_kv_heads=arch["num_kv_heads"], dim=arch["embed_dim"])

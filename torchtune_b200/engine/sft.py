@@ -195,6 +195,8 @@ class SFTTrainer:
             self.adapter_params = get_adapter_params(model)
             set_trainable_params(model, self.adapter_params)
 
+        model = self._transform_model(model, cfg)
+
         if self._enable_activation_checkpointing:
             ac_mode = cfg.get("ac_mode")
             if ac_mode is not None:
@@ -232,6 +234,15 @@ class SFTTrainer:
         if self._device.type == "cuda" and self._is_rank_zero:
             training.log_memory_stats(training.get_memory_stats(self._device))
         return model
+
+    def _transform_model(self, model: nn.Module, cfg: DictConfig) -> nn.Module:
+        """Hook for engines that rewrite modules before weights are loaded (QAT, fp8)."""
+        if cfg.get("enable_fp8_training", False):
+            model = training.convert_to_float8_training(model, cfg.get("fp8_recipe_name"))
+        return model
+
+    def _before_batch(self, idx: int) -> None:
+        """Hook called before every micro-batch."""
 
     def _tokenizer_vocab(self, cfg) -> Optional[int]:
         tok = getattr(self, "_tokenizer", None)
@@ -419,6 +430,7 @@ class SFTTrainer:
             for idx, batch in enumerate(self._dataloader):
                 if self.max_steps_per_epoch is not None and (idx // self._gradient_accumulation_steps) == self.max_steps_per_epoch:
                     break
+                self._before_batch(idx)
                 utils.batch_to_device(batch, self._device)
                 loss_sum, n_valid = self._loss_step(batch)
                 running_loss += loss_sum.detach().float()

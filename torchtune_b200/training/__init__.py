@@ -53,3 +53,5 @@ from ._distributed import (
     set_torch_num_threads,
     validate_no_params_on_meta_device,
 )
+from . import quantization
+from .quantization import convert_to_float8_training, get_quantizer_mode, is_fp8_tensorwise_scaling, swap_lora_linear_with_qat

@@ -1,0 +1,72 @@
+"""generate / quantize / eleuther_eval recipes on CPU with a tiny Llama-2 and a generated
+sentencepiece tokenizer."""
+import json
+from pathlib import Path
+
+import pytest
+import torch
+
+from helpers import fixed_init_, run_tune, write_tiny_hf_checkpoint
+from tokenizer_assets import write_sentencepiece_model
+from torchtune_b200.evaluation import EvalLM
+from torchtune_b200.models.llama2 import llama2, llama2_tokenizer
+
+ARCH = dict(vocab_size=200, num_layers=2, num_heads=4, num_kv_heads=2, embed_dim=64, max_seq_len=256, intermediate_dim=128, norm_eps=1e-5)
+MODEL_ARGS = " ".join(f"model.{k}={v}" for k, v in ARCH.items())
+
+
+def _common(tmp_path):
+    ckpt = tmp_path / "ckpt"
+    write_tiny_hf_checkpoint(ckpt, arch=ARCH, builder=llama2)
+    (tmp_path / "tok").mkdir(exist_ok=True)
+    sp = write_sentencepiece_model(tmp_path / "tok", vocab_size=200)
+    return (
+        f"model._component_=torchtune_b200.models.llama2.llama2 {MODEL_ARGS} checkpointer.checkpoint_dir={ckpt} "
+        f"checkpointer.checkpoint_files=[model-00001-of-00001.safetensors] device=cpu dtype=fp32 output_dir={tmp_path / 'out'}"
+    ), sp
+
+
+def test_generate_recipe(tmp_path, tune_path, monkeypatch, caplog):
+    common, sp = _common(tmp_path)
+    run_tune(tune_path, f"run generate --config generation {common} tokenizer.path={sp} max_new_tokens=12 prompt.user=hello top_k=5", monkeypatch)
+    assert "tokens/sec" in caplog.text
+
+
+def test_quantize_then_load(tmp_path, tune_path, monkeypatch):
+    common, _ = _common(tmp_path)
+    run_tune(tune_path, f"run quantize --config quantization {common} quantizer.groupsize=32", monkeypatch)
+    out = tmp_path / "out" / "model-00001-of-00001-8da4w.pt"
+    sd = torch.load(out)
+    packed = [k for k in sd if k.endswith("weight_packed")]
+    assert packed and all(sd[k].dtype == torch.uint8 for k in packed)
+    assert sd["tok_embeddings.weight"].dtype == torch.float32
+
+
+def test_eval_lm_scores_match_manual(tmp_path):
+    (tmp_path / "tok").mkdir(exist_ok=True)
+    sp = write_sentencepiece_model(tmp_path / "tok", vocab_size=200)
+    tok = llama2_tokenizer(str(sp))
+    model = llama2(**ARCH)
+    fixed_init_(model, std=0.3)
+    lm = EvalLM(model, tok, device=torch.device("cpu"), dtype=torch.float32, batch_size=2)
+    reqs = [("the quick brown", " fox jumps"), ("hello", " world"), ("a b c ", "d")]
+    got = lm.loglikelihood(reqs)
+    for (ctx, cont), (ll, greedy) in zip(reqs, got):
+        c, k = lm._encode_pair(ctx, cont)
+        ids = torch.tensor([c + k])
+        logp = torch.log_softmax(model(ids)[0].float(), -1)
+        want = sum(logp[len(c) - 1 + i, t].item() for i, t in enumerate(k))
+        assert ll == pytest.approx(want, abs=1e-3)
+        assert greedy == all(logp[len(c) - 1 + i].argmax().item() == t for i, t in enumerate(k))
+    assert lm.loglikelihood_rolling(["the quick brown fox"])[0] < 0
+    text = lm.generate_until([("hello", {"until": ["\n"], "max_gen_toks": 8})])[0]
+    assert isinstance(text, str) and "\n" not in text
+
+
+def test_eleuther_eval_recipe_jsonl(tmp_path, tune_path, monkeypatch, caplog):
+    common, sp = _common(tmp_path)
+    task = tmp_path / "mc.jsonl"
+    docs = [{"query": f"question {i} answer:", "choices": [" yes", " no", " maybe so"], "gold": i % 3} for i in range(6)]
+    task.write_text("\n".join(json.dumps(d) for d in docs))
+    run_tune(tune_path, f"run eleuther_eval --config eleuther_evaluation {common} tokenizer.path={sp} tasks=[{task}] batch_size=4 limit=5", monkeypatch)
+    assert "acc_norm" in caplog.text and "'n': 5" in caplog.text

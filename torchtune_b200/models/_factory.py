@@ -85,6 +85,11 @@ class DecoderArch:
     attn_softcap: float = 0.0
     attn_scale: Optional[float] = None
     sliding_window: Optional[Callable[[int], int]] = None  # layer index -> window (0 = global)
+    # per-layer overrides (Llama-4): feed-forward module, whether the layer rotates/normalises q and k,
+    # and an extra mask hook
+    mlp_factory: Optional[Callable[[int, "AdapterSpec"], nn.Module]] = None
+    layer_uses_rope: Optional[Callable[[int], bool]] = None
+    layer_mask_mod: Optional[Callable[[int], Optional[Callable]]] = None
 
     def resolved_head_dim(self) -> int:
         return self.head_dim or self.embed_dim // self.num_heads
@@ -93,8 +98,10 @@ class DecoderArch:
         return self.intermediate_dim or scale_hidden_dim_for_mlp(self.embed_dim)
 
 
-def build_attention(arch: DecoderArch, ad: AdapterSpec, rope: Optional[nn.Module]) -> MultiHeadAttention:
+def build_attention(arch: DecoderArch, ad: AdapterSpec, rope: Optional[nn.Module], positional: bool = True) -> MultiHeadAttention:
     hd = arch.resolved_head_dim()
+    qk_norm = arch.qk_norm if positional else None
+    rope = rope if positional else None
     mods = set(ad.attn_modules)
     unknown = mods - {"q_proj", "k_proj", "v_proj", "output_proj"}
     if unknown:
@@ -109,8 +116,8 @@ def build_attention(arch: DecoderArch, ad: AdapterSpec, rope: Optional[nn.Module
         v_proj=ad.make(arch.embed_dim, arch.num_kv_heads * hd, "v_proj" in mods, arch.qkv_bias),
         output_proj=ad.make(arch.num_heads * hd, arch.embed_dim, "output_proj" in mods, False),
         pos_embeddings=rope,
-        q_norm=arch.qk_norm(hd, arch.norm_eps) if arch.qk_norm else None,
-        k_norm=arch.qk_norm(hd, arch.norm_eps) if arch.qk_norm else None,
+        q_norm=qk_norm(hd, arch.norm_eps) if qk_norm else None,
+        k_norm=qk_norm(hd, arch.norm_eps) if qk_norm else None,
         max_seq_len=arch.max_seq_len,
         attn_dropout=arch.attn_dropout,
         softcap=arch.attn_softcap,
@@ -154,15 +161,20 @@ def build_decoder(arch: DecoderArch, adapter: Optional[AdapterSpec] = None) -> T
     layers: List[nn.Module] = []
     for idx in range(arch.num_layers):
         window = arch.sliding_window(idx) if arch.sliding_window else 0
+        positional = arch.layer_uses_rope(idx) if arch.layer_uses_rope else True
+        mask_mod = _window_mask_mod(window) if window else None
+        if arch.layer_mask_mod is not None and mask_mod is None:
+            mask_mod = arch.layer_mask_mod(idx)
+        mlp = arch.mlp_factory(idx, ad) if arch.mlp_factory else build_mlp(arch.embed_dim, arch.resolved_hidden(), ad, arch.activation(), arch.mlp_bias)
         layers.append(
             TransformerSelfAttentionLayer(
-                attn=build_attention(arch, ad, rope),
-                mlp=build_mlp(arch.embed_dim, arch.resolved_hidden(), ad, arch.activation(), arch.mlp_bias),
+                attn=build_attention(arch, ad, rope, positional),
+                mlp=mlp,
                 sa_norm=arch.norm(arch.embed_dim, arch.norm_eps),
                 mlp_norm=arch.norm(arch.embed_dim, arch.norm_eps),
                 sa_scale=arch.norm(arch.embed_dim, arch.norm_eps) if arch.post_norms else None,
                 mlp_scale=arch.norm(arch.embed_dim, arch.norm_eps) if arch.post_norms else None,
-                mask_mod=_window_mask_mod(window) if window else None,
+                mask_mod=mask_mod,
             )
         )
     tok = arch.embedding(arch.vocab_size, arch.embed_dim)

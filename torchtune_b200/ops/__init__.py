@@ -16,6 +16,7 @@ from . import reference
 from .mask import AttentionMask
 
 __all__ = [
+    "matmul",
     "linear",
     "rms_norm",
     "rope",
@@ -60,6 +61,15 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
 
         return _cuda.linear(x, weight, bias)
     return F.linear(x, weight, bias)
+
+
+def matmul(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``x[T, K] @ w[K, N]`` (2-D operands, ``w`` row-major as stored in grouped expert weights)."""
+    if _native(x) and w.dtype == torch.bfloat16 and x.dim() == 2 and w.dim() == 2 and x.shape[0] > 0 and x.is_contiguous() and w.is_contiguous() and x.shape[1] % 8 == 0 and w.shape[1] % 8 == 0:
+        from . import _cuda
+
+        return _cuda.matmul_kn(x, w)
+    return x @ w
 
 
 def rms_norm(x: torch.Tensor, scale: Optional[torch.Tensor], eps: float = 1e-6) -> torch.Tensor:

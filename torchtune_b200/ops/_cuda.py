@@ -92,6 +92,30 @@ class _Linear(torch.autograd.Function):
         return dx, dw, db
 
 
+class _MatmulKN(torch.autograd.Function):
+    """``y[T, N] = x[T, K] · w[K, N]`` with ``w`` stored reduction-dimension-major (the layout of
+    grouped expert weights ``[E, K, N]``): forward reads ``w`` as an MN-major B operand, dgrad is
+    the plain NT form ``dy · wᵀ`` and wgrad ``xᵀ · dy`` is the TN form."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        ctx.save_for_backward(x, w)
+        return gemm(x, w, b_mn=True)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        if dy.stride(1) != 1 or dy.stride(0) % 8:
+            dy = dy.contiguous()
+        dx = gemm(dy, w) if ctx.needs_input_grad[0] else None
+        dw = gemm(x, dy, a_mn=True, b_mn=True) if ctx.needs_input_grad[1] else None
+        return dx, dw
+
+
+def matmul_kn(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    return _MatmulKN.apply(x, w)
+
+
 # --- weight-gradient delivery ------------------------------------------------------------
 # A parameter that lives in a flat store carries `_grad_buffer` (its window of the flat
 # gradient buffer).  Its weight gradient is then written (or accumulated) straight into that

@@ -26,9 +26,14 @@ from .rms_norm import RMSNorm, rms_norm
 from .tanh_gate import TanhGate
 from .tied_linear import TiedLinear
 from .transformer import TransformerCrossAttentionLayer, TransformerDecoder, TransformerSelfAttentionLayer
+from .vision_transformer import CLSEmbedding, CLSProjection, PatchEmbedding, VisionTransformer
 
 __all__ = [
     "MultiHeadAttention",
+    "VisionTransformer",
+    "CLSEmbedding",
+    "CLSProjection",
+    "PatchEmbedding",
     "TanhGate",
     "FeedForward",
     "FrozenNF4Linear",

@@ -26,10 +26,18 @@ from .rms_norm import RMSNorm, rms_norm
 from .tanh_gate import TanhGate
 from .tied_linear import TiedLinear
 from .transformer import TransformerCrossAttentionLayer, TransformerDecoder, TransformerSelfAttentionLayer
+from .layer_dropout import LayerDropout, ModuleLayerDropoutWrapper, ScaleType, get_scale, prepare_layer_dropout
+from .vq_embeddings import VectorQuantizedEmbeddings
 from .vision_transformer import CLSEmbedding, CLSProjection, PatchEmbedding, VisionTransformer
 
 __all__ = [
     "MultiHeadAttention",
+    "LayerDropout",
+    "ModuleLayerDropoutWrapper",
+    "ScaleType",
+    "get_scale",
+    "prepare_layer_dropout",
+    "VectorQuantizedEmbeddings",
     "VisionTransformer",
     "CLSEmbedding",
     "CLSProjection",

@@ -1,0 +1,86 @@
+"""Tensor-parallel decoder on CPU (gloo, 2 ranks): token-sharded loss, parameter gradients and the
+re-assembled checkpoint must equal the single-process model."""
+import os
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+import torch.nn.functional as F
+
+from helpers import fixed_init_
+from torchtune_b200.models.llama3_1 import llama3_1
+from torchtune_b200.parallel.tp import TensorParallelContext
+from torchtune_b200.parallel.tp_model import tensor_parallelize
+
+ARCH = dict(vocab_size=64, num_layers=2, num_heads=4, num_kv_heads=2, embed_dim=32, max_seq_len=32, intermediate_dim=48, norm_eps=1e-5, rope_base=10000)
+
+
+def _data():
+    g = torch.Generator().manual_seed(7)
+    tokens = torch.randint(0, 64, (2, 8), generator=g)
+    labels = torch.randint(0, 64, (2, 8), generator=g)
+    labels[0, :2] = -100
+    return tokens, labels
+
+
+def _reference():
+    model = llama3_1(**ARCH)
+    fixed_init_(model, std=0.1)
+    tokens, labels = _data()
+    loss = F.cross_entropy(model(tokens).reshape(-1, 64), labels.reshape(-1), ignore_index=-100, reduction="sum")
+    loss.backward()
+    return loss.item(), {k: p.grad.clone() for k, p in model.named_parameters()}, {k: v.clone() for k, v in model.state_dict().items()}
+
+
+def _worker(rank, world, port, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        model = llama3_1(**ARCH)
+        fixed_init_(model, std=0.1)
+        tp = TensorParallelContext(torch.device("cpu"), max_rows_per_rank=8, max_width=48)
+        tpm = tensor_parallelize(model, tp)
+        tokens, labels = _data()
+        logits = tpm(tokens)  # [1, rows, vocab] for this rank's rows
+        my_labels = tpm.shard_rows(labels)
+        loss = F.cross_entropy(logits.reshape(-1, 64), my_labels.reshape(-1), ignore_index=-100, reduction="sum")
+        loss.backward()
+        tpm.sync_replicated_grads()
+        total = loss.detach().clone()
+        dist.all_reduce(total)
+        l0 = tpm.layers[0]
+        results[rank] = dict(
+            loss=total.item(),
+            wqkv_grad=l0.attn.wqkv.grad.clone(), wo_grad=l0.attn.wo.grad.clone(), w13_grad=l0.mlp.w13.grad.clone(), w2_grad=l0.mlp.w2.grad.clone(),
+            emb_grad=tpm.tok_embeddings.weight.grad.clone(), norm_grad=l0.sa_norm.scale.grad.clone(), out_grad=tpm.output.weight.grad.clone(),
+            sd={k: v.clone() for k, v in tpm.full_state_dict().items()},
+        )
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tp_decoder_matches_single_process():
+    world = 2
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_worker, args=(world, 29561, results), nprocs=world, join=True)
+    ref_loss, ref_grads, ref_sd = _reference()
+    hd, heads, kv = 8, 2, 1  # per rank
+    for rank in range(world):
+        r = results[rank]
+        assert abs(r["loss"] - ref_loss) < 1e-3 * abs(ref_loss)
+        q = ref_grads["layers.0.attn.q_proj.weight"][rank * heads * hd : (rank + 1) * heads * hd]
+        k = ref_grads["layers.0.attn.k_proj.weight"][rank * kv * hd : (rank + 1) * kv * hd]
+        v = ref_grads["layers.0.attn.v_proj.weight"][rank * kv * hd : (rank + 1) * kv * hd]
+        torch.testing.assert_close(r["wqkv_grad"], torch.cat([q, k, v]), rtol=1e-4, atol=1e-5)
+        torch.testing.assert_close(r["wo_grad"], ref_grads["layers.0.attn.output_proj.weight"][:, rank * 16 : (rank + 1) * 16], rtol=1e-4, atol=1e-5)
+        w1 = ref_grads["layers.0.mlp.w1.weight"][rank * 24 : (rank + 1) * 24]
+        w3 = ref_grads["layers.0.mlp.w3.weight"][rank * 24 : (rank + 1) * 24]
+        torch.testing.assert_close(r["w13_grad"], torch.cat([w1, w3]), rtol=1e-4, atol=1e-5)
+        torch.testing.assert_close(r["w2_grad"], ref_grads["layers.0.mlp.w2.weight"][:, rank * 24 : (rank + 1) * 24], rtol=1e-4, atol=1e-5)
+        torch.testing.assert_close(r["emb_grad"], ref_grads["tok_embeddings.weight"], rtol=1e-4, atol=1e-5)
+        torch.testing.assert_close(r["norm_grad"], ref_grads["layers.0.sa_norm.scale"], rtol=1e-4, atol=1e-5)
+        torch.testing.assert_close(r["out_grad"], ref_grads["output.weight"], rtol=1e-4, atol=1e-5)
+        assert set(r["sd"]) == set(ref_sd)
+        for key in ref_sd:
+            assert torch.equal(r["sd"][key], ref_sd[key]), key

@@ -14,6 +14,8 @@
 // and wgrad (TN) need no transposes.  Serves every nn.Linear of the decoder
 // (reference call sites: torchtune/modules/attention.py:234,262-263,303,
 // torchtune/modules/feed_forward.py:50-53).
+#include <cstring>
+
 #include "common/ptx.cuh"
 #include "common/tmap.h"
 
@@ -35,6 +37,29 @@ struct GemmParams {
   int* err;        // device error word (0 = ok)
 };
 
+// Tensor-parallel variants of the same kernel (TP template parameter of gemm_body):
+//   1  all-gather → GEMM: the M dimension is the concatenation over ranks of per-rank activation shards that live
+//      in peer-visible buffers; each m-tile is loaded by TMA straight from the shard of the rank that owns those rows
+//      (plain, non-multicast tensor loads; the own shard first), so no gathered copy of A is ever written.
+//   2  GEMM → reduce-scatter: every output m-tile is stored straight into the staging slot [this rank] of the rank
+//      that owns those rows; the owner later sums its `world` slots (ttb_rs_reduce).  Stores to peers start with
+//      the next rank so the ranks do not all write to the same GPU at the same time.
+static constexpr int kMaxTpWorld = 8;
+struct alignas(64) TpArgs {
+  CUtensorMap tmA[kMaxTpWorld];  // TP 1: per-rank A shard [rows_per_rank, K]
+  void* C[kMaxTpWorld];          // TP 2: per-rank staging buffer [world, rows_per_rank, ldc]
+  int world, rank, rows_per_rank;
+};
+
+template <int TP>
+__device__ __forceinline__ int tp_rotate_m(int m_blk, int num_m, const TpArgs* tp) {
+  if (TP == 0) return m_blk;
+  const int tiles_per_rank = tp->rows_per_rank / BM;
+  const int first = (TP == 1 ? tp->rank : (tp->rank + 1) % tp->world) * tiles_per_rank;
+  const int r = m_blk + first;
+  return r >= num_m ? r - num_m : r;
+}
+
 template <int BN>
 struct GemmCfg {
   static constexpr int kABytes = BM * BK * 2;
@@ -55,10 +80,12 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_
   n_blk = r / gsize;
 }
 
-template <int BN, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(kThreads, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+template <int BN, bool A_MN, bool B_MN, int TP>
+__device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUtensorMap* tmB_ptr, const GemmParams& p,
+                                          const TpArgs* tp) {
   using Cfg = GemmCfg<BN>;
+  const CUtensorMap& tmA = *tmA_ptr;
+  const CUtensorMap& tmB = *tmB_ptr;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
@@ -108,6 +135,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x) {
       int m_blk, n_blk;
       tile_coords(t, num_m, num_n, m_blk, n_blk);
+      m_blk = tp_rotate_m<TP>(m_blk, num_m, tp);
+      const CUtensorMap* mapA = &tmA;
+      int a_row = m_blk * BM;
+      if (TP == 1) {
+        const int src = a_row / tp->rows_per_rank;
+        mapA = &tp->tmA[src];
+        a_row -= src * tp->rows_per_rank;
+      }
       for (int kb = 0; kb < num_kb; ++kb) {
         if (!mbar_wait(&empty[stage], phase ^ 1)) {
           *abort_flag = 1;
@@ -122,7 +157,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, &tmA, &full[stage], m_blk * BM + j * 64, kb * BK);
           } else {
-            tma_load_2d(sa, &tmA, &full[stage], kb * BK, m_blk * BM);
+            tma_load_2d(sa, mapA, &full[stage], kb * BK, a_row);
           }
           if (B_MN) {
 #pragma unroll
@@ -201,6 +236,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x) {
       int m_blk, n_blk;
       tile_coords(t, num_m, num_n, m_blk, n_blk);
+      m_blk = tp_rotate_m<TP>(m_blk, num_m, tp);
       if (!mbar_wait(&tfull[acc], acc_phase)) {
         *abort_flag = 1;
         if (lane == 0) atomicExch(p.err, 104);
@@ -238,7 +274,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               }
             }
           } else {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+            __nv_bfloat16* dst;
+            if (TP == 2) {
+              const int owner = row / tp->rows_per_rank;
+              const long long slot_row = static_cast<long long>(tp->rank) * tp->rows_per_rank + (row - owner * tp->rows_per_rank);
+              dst = reinterpret_cast<__nv_bfloat16*>(tp->C[owner]) + slot_row * p.ldc + col0;
+            } else {
+              dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+            }
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
               if (col0 + g * 8 + 8 <= p.N) {
@@ -277,6 +320,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   if (warp == 2) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+  gemm_body<BN, A_MN, B_MN, 0>(&tmA, &tmB, p, nullptr);
+}
+
+template <int BN, bool B_MN, int TP>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tp_kernel(const __grid_constant__ TpArgs tp, const __grid_constant__ CUtensorMap tmA,
+               const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+  gemm_body<BN, false, B_MN, TP>(&tmA, &tmB, p, &tp);
 }
 
 template <int BN, bool A_MN, bool B_MN>
@@ -333,7 +389,146 @@ static int dispatch_bn(const void* A, const void* B, const GemmParams& p, long l
   return launch_gemm<64, A_MN, B_MN>(A, B, p, lda, ldb, stream);
 }
 
+template <int BN, bool B_MN, int TP>
+static int launch_gemm_tp(const TpArgs& tp, const void* A, const void* B, const GemmParams& p, long long lda, long long ldb,
+                          cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  CUtensorMap tmA, tmB;
+  // TP 1: `A` is this rank's shard (only prefetched); TP 2: `A` is the local [M, K] operand.
+  const int a_rows = TP == 1 ? tp.rows_per_rank : p.M;
+  int rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a_rows, p.K, lda, BM, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != kOk) return rc;
+  if (B_MN)
+    rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.K, p.N, ldb, BK, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+  else
+    rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.N, p.K, ldb, BN, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != kOk) return rc;
+  auto kern = gemm_tp_kernel<BN, B_MN, TP>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return kErrDriver;
+    attr_set = true;
+  }
+  const int num_tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int grid = num_tiles < sm_count() ? num_tiles : sm_count();
+  TTB_COUNT_LAUNCH(1);
+  kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tp, tmA, tmB, p);
+  if (cudaGetLastError() != cudaSuccess) return kErrDriver;
+  return kOk;
+}
+
+template <int TP>
+static int dispatch_tp(const TpArgs& tp, const void* A, const void* B, const GemmParams& p, long long lda, long long ldb, int b_mn,
+                       cudaStream_t stream) {
+  if (p.N > 128) {
+    return b_mn ? launch_gemm_tp<256, true, TP>(tp, A, B, p, lda, ldb, stream) : launch_gemm_tp<256, false, TP>(tp, A, B, p, lda, ldb, stream);
+  }
+  if (p.N > 64) {
+    return b_mn ? launch_gemm_tp<128, true, TP>(tp, A, B, p, lda, ldb, stream) : launch_gemm_tp<128, false, TP>(tp, A, B, p, lda, ldb, stream);
+  }
+  return b_mn ? launch_gemm_tp<64, true, TP>(tp, A, B, p, lda, ldb, stream) : launch_gemm_tp<64, false, TP>(tp, A, B, p, lda, ldb, stream);
+}
+
+// out[rows, N] = sum over `world` staging slots (+ residual) (+ bias), fp32 accumulation, 8 bf16 per thread.
+__global__ void __launch_bounds__(256)
+rs_reduce_kernel(const __nv_bfloat16* __restrict__ staging, const __nv_bfloat16* __restrict__ residual,
+                 const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ out, int world, long long rows, int N,
+                 long long ld_stage, long long ld_res, long long ld_out) {
+  const int vec_per_row = N / 8;
+  const long long total = rows * vec_per_row;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / vec_per_row;
+    const int c = static_cast<int>(i - r * vec_per_row) * 8;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int w = 0; w < world; ++w) {
+      const uint4 v = *reinterpret_cast<const uint4*>(staging + (static_cast<long long>(w) * rows + r) * ld_stage + c);
+      const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(b[k]);
+        acc[2 * k] += f.x, acc[2 * k + 1] += f.y;
+      }
+    }
+    if (residual != nullptr) {
+      const uint4 v = *reinterpret_cast<const uint4*>(residual + r * ld_res + c);
+      const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(b[k]);
+        acc[2 * k] += f.x, acc[2 * k + 1] += f.y;
+      }
+    }
+    if (bias != nullptr) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] += __bfloat162float(__ldg(bias + c + k));
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]), o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]), o.w = pack_bf16x2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(out + r * ld_out + c) = o;
+  }
+}
+
 }  // namespace ttb
+
+// Tensor-parallel entry points -----------------------------------------------------------
+// ttb_gemm_ag_bf16: C[world*rows_per_rank, N] = concat_r(A_ranks[r])[., K] * op(B); A_ranks[r] may be peer memory
+//                   (read by plain TMA loads); C, B local.
+// ttb_gemm_rs_bf16: partial = A[world*rows_per_rank, K] * op(B); rows of owner o are stored to
+//                   C_ranks[o][rank][rows_per_rank][ldc] (C_ranks[o] may be peer memory, written by plain stores).
+// rows_per_rank must be a multiple of 128 (one m-tile never spans two ranks).
+extern "C" int ttb_gemm_ag_bf16(const void* const* A_ranks, const void* B, void* C, int world, int rank, int rows_per_rank,
+                                int N, int K, int b_mn, long long lda, long long ldb, long long ldc, const void* bias, int* err,
+                                void* stream) {
+  using namespace ttb;
+  if (world < 1 || world > kMaxTpWorld || rank < 0 || rank >= world) return kErrBadShape;
+  if (rows_per_rank <= 0 || (rows_per_rank % BM) || N <= 0 || K <= 0) return kErrBadShape;
+  if ((lda & 7) || (ldb & 7) || (ldc & 7) || (N & 7) || (K & 7)) return kErrBadShape;
+  TpArgs tp;
+  memset(&tp, 0, sizeof(tp));
+  tp.world = world, tp.rank = rank, tp.rows_per_rank = rows_per_rank;
+  for (int r = 0; r < world; ++r) {
+    int rc = make_tmap_2d(&tp.tmA[r], A_ranks[r], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_per_rank, K, lda, BM, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != kOk) return rc;
+  }
+  GemmParams p;
+  p.M = world * rows_per_rank, p.N = N, p.K = K, p.C = C, p.ldc = ldc;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.alpha = 1.f, p.out_fp32 = 0, p.accumulate = 0, p.err = err;
+  return dispatch_tp<1>(tp, A_ranks[rank], B, p, lda, ldb, b_mn, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ttb_gemm_rs_bf16(const void* A, const void* B, void* const* C_ranks, int world, int rank, int rows_per_rank,
+                                int N, int K, int b_mn, long long lda, long long ldb, long long ldc, int* err, void* stream) {
+  using namespace ttb;
+  if (world < 1 || world > kMaxTpWorld || rank < 0 || rank >= world) return kErrBadShape;
+  if (rows_per_rank <= 0 || (rows_per_rank % BM) || N <= 0 || K <= 0) return kErrBadShape;
+  if ((lda & 7) || (ldb & 7) || (ldc & 7) || (N & 7) || (K & 7)) return kErrBadShape;
+  TpArgs tp;
+  memset(&tp, 0, sizeof(tp));
+  tp.world = world, tp.rank = rank, tp.rows_per_rank = rows_per_rank;
+  for (int r = 0; r < world; ++r) tp.C[r] = C_ranks[r];
+  GemmParams p;
+  p.M = world * rows_per_rank, p.N = N, p.K = K, p.C = nullptr, p.ldc = ldc;
+  p.bias = nullptr, p.alpha = 1.f, p.out_fp32 = 0, p.accumulate = 0, p.err = err;
+  return dispatch_tp<2>(tp, A, B, p, lda, ldb, b_mn, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ttb_rs_reduce(const void* staging, const void* residual, const void* bias, void* out, int world, long long rows,
+                             int N, long long ld_stage, long long ld_res, long long ld_out, void* stream) {
+  using namespace ttb;
+  if (world < 1 || rows <= 0 || N <= 0 || (N & 7) || (ld_stage & 7) || (ld_out & 7) || (residual && (ld_res & 7))) return kErrBadShape;
+  const long long total = rows * (N / 8);
+  long long blocks = (total + 255) / 256;
+  const long long cap = static_cast<long long>(sm_count()) * 8;
+  if (blocks > cap) blocks = cap;
+  TTB_COUNT_LAUNCH(1);
+  rs_reduce_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(staging), static_cast<const __nv_bfloat16*>(residual), static_cast<const __nv_bfloat16*>(bias),
+      static_cast<__nv_bfloat16*>(out), world, rows, N, ld_stage, ld_res, ld_out);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrDriver;
+}
 
 // C ABI -------------------------------------------------------------------------------
 // a_mn = 0: A is [M, K] row-major (row stride lda); 1: A is [K, M] row-major.

@@ -1,0 +1,245 @@
+"""Tensor parallelism with sequence-parallel activations over NVLink peer memory.
+
+The reference builds tensor parallelism from DTensor plans (ColwiseParallel / RowwiseParallel /
+SequenceParallel, torchtune/models/llama3/_parallelism.py:19-130) whose collectives are separate NCCL
+kernels around cuBLAS GEMMs.  Here the two collective+GEMM pairs of a transformer block are single
+kernels (``ttb_gemm_ag_bf16`` / ``ttb_gemm_rs_bf16`` in ``ops/csrc/gemm.cu``):
+
+* column-parallel projection of a sequence-sharded input — *all-gather → GEMM*: the tcgen05 GEMM's TMA
+  producer reads each m-tile of the activation directly from the shard of the rank that owns those rows
+  (peer memory), so the gathered activation never exists and the NVLink reads overlap the MMAs tile by tile;
+* row-parallel projection to a sequence-sharded output — *GEMM → reduce-scatter*: the epilogue stores every
+  output tile into a staging slot on the rank that owns those rows; the owner sums its ``world`` slots in fp32
+  and adds the residual in the same pass.
+
+Ordering between ranks is a stream-ordered barrier (a 4-byte all-reduce) per operation; shard and staging
+buffers are double-buffered so one barrier per operation is enough (a buffer is rewritten only after the
+*next* operation's barrier, which every rank enters after its reads of the previous one have completed).
+
+Without CUDA (gloo) the same functions run on ``all_gather`` / ``reduce_scatter`` so the host-side logic is
+testable on CPU.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .fabric import PeerBuffer
+
+_BF16 = torch.bfloat16
+
+
+def _declare(L) -> None:
+    if getattr(L, "_tp_declared", False):
+        return
+    vp, i32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+    pvp = ctypes.POINTER(vp)
+    L.ttb_gemm_ag_bf16.argtypes = [pvp, vp, vp, i32, i32, i32, i32, i32, i32, i64, i64, i64, vp, vp, vp]
+    L.ttb_gemm_rs_bf16.argtypes = [vp, vp, pvp, i32, i32, i32, i32, i32, i32, i64, i64, i64, vp, vp]
+    L.ttb_rs_reduce.argtypes = [vp, vp, vp, vp, i32, i64, i32, i64, i64, i64, vp]
+    for fn in (L.ttb_gemm_ag_bf16, L.ttb_gemm_rs_bf16, L.ttb_rs_reduce):
+        fn.restype = i32
+    L._tp_declared = True
+
+
+class TensorParallelContext:
+    """Peer buffers and collective GEMMs for one tensor-parallel group.
+
+    ``max_rows_per_rank`` is the largest number of tokens a rank owns (batch·seq / world) and
+    ``max_width`` the widest activation that is gathered or scattered (the model width)."""
+
+    def __init__(self, device: torch.device, group=None, *, max_rows_per_rank: int, max_width: int):
+        self.device, self.group = device, group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.max_rows, self.max_width = int(max_rows_per_rank), int(max_width)
+        self.cuda = device.type == "cuda"
+        self._flip_g = 0
+        self._flip_s = 0
+        self._token = torch.zeros(1, device=device)
+        if self.cuda:
+            from ..ops._lib import lib
+
+            _declare(lib())
+            shard_bytes = self.max_rows * self.max_width * 2
+            self._gather = [PeerBuffer(shard_bytes, device, group) for _ in range(2)]
+            self._stage = [PeerBuffer(self.world * shard_bytes, device, group) for _ in range(2)]
+
+    # ------------------------------------------------------------------ plumbing
+    def barrier(self) -> None:
+        if self.world > 1:
+            dist.all_reduce(self._token, group=self.group)
+
+    def close(self) -> None:
+        if self.cuda:
+            torch.cuda.synchronize(self.device)
+            self.barrier()
+            for b in self._gather + self._stage:
+                b.close()
+
+    def _check(self, rows: int, width: int) -> None:
+        if rows > self.max_rows or width > self.max_width:
+            raise ValueError(f"activation shard [{rows}, {width}] exceeds the context's buffers [{self.max_rows}, {self.max_width}]")
+
+    @staticmethod
+    def fusable(rows: int, k: int, n: int) -> bool:
+        return rows % 128 == 0 and k % 8 == 0 and n % 8 == 0
+
+    # ------------------------------------------------------------------ all-gather → GEMM
+    def ag_gemm(self, x_shard: torch.Tensor, weight: torch.Tensor, *, b_mn: bool = False, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``concat_ranks(x_shard) @ op(weight)`` → ``[world·rows, N]``; ``weight`` is ``[N, K]`` (or ``[K, N]`` with ``b_mn``)."""
+        rows, k = x_shard.shape
+        n = weight.shape[1] if b_mn else weight.shape[0]
+        if not (self.cuda and x_shard.dtype == _BF16 and self.fusable(rows, k, n)):
+            full = self.all_gather_rows(x_shard)
+            out = full @ weight if b_mn else torch.nn.functional.linear(full, weight)
+            return out + bias if bias is not None else out
+        from ..ops._lib import check, err_word, lib, stream_ptr
+
+        self._check(rows, k)
+        buf = self._gather[self._flip_g]
+        self._flip_g ^= 1
+        buf.tensor(_BF16, rows * k).view(rows, k).copy_(x_shard)
+        self.barrier()  # every rank's shard is in place
+        out = torch.empty(self.world * rows, n, dtype=_BF16, device=self.device)
+        w = weight if weight.is_contiguous() else weight.contiguous()
+        check(
+            lib().ttb_gemm_ag_bf16(buf.pointer_array(), w.data_ptr(), out.data_ptr(), self.world, self.rank, rows, n, k, int(b_mn), k, w.stride(0), n,
+                                   None if bias is None else bias.data_ptr(), err_word(self.device), stream_ptr()),
+            "gemm_ag",
+        )
+        return out
+
+    # ------------------------------------------------------------------ GEMM → reduce-scatter
+    def gemm_rs(self, x: torch.Tensor, weight: torch.Tensor, *, b_mn: bool = False, residual: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Rows ``[rank·rows, (rank+1)·rows)`` of ``Σ_ranks x_r @ op(weight_r)`` (+ residual, + bias) → ``[rows, N]``."""
+        total, k = x.shape
+        rows = total // self.world
+        n = weight.shape[1] if b_mn else weight.shape[0]
+        if not (self.cuda and x.dtype == _BF16 and total % self.world == 0 and self.fusable(rows, k, n)):
+            partial = x @ weight if b_mn else torch.nn.functional.linear(x, weight)
+            out = self.reduce_scatter_rows(partial)
+            if residual is not None:
+                out = out + residual
+            return out + bias if bias is not None else out
+        from ..ops._lib import check, err_word, lib, stream_ptr
+
+        self._check(rows, n)
+        buf = self._stage[self._flip_s]
+        self._flip_s ^= 1
+        xc = x if x.is_contiguous() else x.contiguous()
+        w = weight if weight.is_contiguous() else weight.contiguous()
+        L = lib()
+        check(L.ttb_gemm_rs_bf16(xc.data_ptr(), w.data_ptr(), buf.pointer_array(), self.world, self.rank, rows, n, k, int(b_mn), k, w.stride(0), n, err_word(self.device), stream_ptr()), "gemm_rs")
+        self.barrier()  # all partial tiles have landed in every owner's staging buffer
+        out = torch.empty(rows, n, dtype=_BF16, device=self.device)
+        res = None if residual is None else (residual if residual.is_contiguous() else residual.contiguous())
+        check(
+            L.ttb_rs_reduce(buf.local_ptr, None if res is None else res.data_ptr(), None if bias is None else bias.data_ptr(), out.data_ptr(), self.world, rows, n, n,
+                            0 if res is None else res.stride(0), n, stream_ptr()),
+            "rs_reduce",
+        )
+        return out
+
+    # ------------------------------------------------------------------ plain collectives (backward re-gathers, CPU path)
+    def all_gather_rows(self, x_shard: torch.Tensor) -> torch.Tensor:
+        if self.world == 1:
+            return x_shard
+        out = torch.empty(self.world * x_shard.shape[0], *x_shard.shape[1:], dtype=x_shard.dtype, device=x_shard.device)
+        src = x_shard.contiguous()
+        if x_shard.device.type == "cpu" and x_shard.dtype == _BF16:
+            parts = [torch.empty_like(src, dtype=torch.float32) for _ in range(self.world)]
+            dist.all_gather(parts, src.float(), group=self.group)
+            return torch.cat(parts).to(_BF16)
+        dist.all_gather_into_tensor(out, src, group=self.group)
+        return out
+
+    def reduce_scatter_rows(self, x: torch.Tensor) -> torch.Tensor:
+        if self.world == 1:
+            return x
+        rows = x.shape[0] // self.world
+        if x.device.type == "cpu":
+            full = x.float().contiguous()
+            dist.all_reduce(full, group=self.group)
+            return full[self.rank * rows : (self.rank + 1) * rows].to(x.dtype)
+        out = torch.empty(rows, *x.shape[1:], dtype=x.dtype, device=x.device)
+        dist.reduce_scatter_tensor(out, x.contiguous(), group=self.group)
+        return out
+
+    def all_reduce_(self, t: torch.Tensor) -> torch.Tensor:
+        if self.world > 1:
+            if t.device.type == "cpu" and t.dtype == _BF16:
+                f = t.float()
+                dist.all_reduce(f, group=self.group)
+                t.copy_(f)
+            else:
+                dist.all_reduce(t, group=self.group)
+        return t
+
+
+class _ColumnParallel(torch.autograd.Function):
+    """``y[T, N_r] = gather(x_shard) · W_rᵀ``.  Backward: ``dx_shard = scatter-sum(dy · W_r)`` (fused GEMM → reduce-scatter),
+    ``dW_r = dyᵀ · gather(x_shard)``."""
+
+    @staticmethod
+    def forward(ctx, x_shard, weight, tp: TensorParallelContext):
+        ctx.tp = tp
+        ctx.save_for_backward(x_shard, weight)
+        return tp.ag_gemm(x_shard, weight)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x_shard, weight = ctx.saved_tensors
+        tp = ctx.tp
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = tp.gemm_rs(dy, weight, b_mn=True)
+        if ctx.needs_input_grad[1]:
+            x_full = tp.all_gather_rows(x_shard)
+            dw = _wgrad(dy, x_full)
+        return dx, dw, None
+
+
+class _RowParallel(torch.autograd.Function):
+    """``out_shard[rows, N] = scatter-sum(x[T, K_r] · W_rᵀ) (+ residual)``.  Backward: ``dx = gather(dy_shard) · W_r`` (fused
+    all-gather → GEMM), ``dW_r = gather(dy_shard)ᵀ · x``; the residual receives ``dy_shard`` unchanged."""
+
+    @staticmethod
+    def forward(ctx, x, weight, residual, tp: TensorParallelContext):
+        ctx.tp = tp
+        ctx.has_residual = residual is not None
+        ctx.save_for_backward(x, weight)
+        return tp.gemm_rs(x, weight, residual=residual)
+
+    @staticmethod
+    def backward(ctx, dy_shard):
+        x, weight = ctx.saved_tensors
+        tp = ctx.tp
+        dy_shard = dy_shard.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = tp.ag_gemm(dy_shard, weight, b_mn=True)
+        if ctx.needs_input_grad[1]:
+            dy_full = tp.all_gather_rows(dy_shard)
+            dw = _wgrad(dy_full, x)
+        return dx, dw, (dy_shard if ctx.has_residual and ctx.needs_input_grad[2] else None), None
+
+
+def _wgrad(dy: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    """``dyᵀ · x`` → ``[N, K]`` on the tcgen05 GEMM (TN form) when possible."""
+    if dy.is_cuda and dy.dtype == _BF16 and x.dtype == _BF16:
+        from ..ops._cuda import gemm
+
+        return gemm(dy if dy.is_contiguous() else dy.contiguous(), x if x.is_contiguous() else x.contiguous(), a_mn=True, b_mn=True)
+    return dy.t() @ x
+
+
+def column_parallel_linear(x_shard: torch.Tensor, weight: torch.Tensor, tp: TensorParallelContext) -> torch.Tensor:
+    return _ColumnParallel.apply(x_shard, weight, tp)
+
+
+def row_parallel_linear(x: torch.Tensor, weight: torch.Tensor, tp: TensorParallelContext, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    return _RowParallel.apply(x, weight, residual, tp)

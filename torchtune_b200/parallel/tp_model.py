@@ -1,0 +1,221 @@
+"""Tensor-parallel form of a dense Llama-style decoder.
+
+:func:`tensor_parallelize` rewrites a resident :class:`~torchtune_b200.modules.TransformerDecoder` in place
+(same layer layout as the reference's Llama-3 plan, torchtune/models/llama3/_parallelism.py:19-130):
+
+* the residual stream is sharded by token rows (``batch·seq / tp`` rows per rank) — norms, residual adds,
+  embedding lookup and the loss run on the shard;
+* ``q/k/v`` are one fused column-parallel projection (all-gather → GEMM kernel), attention runs on the local
+  heads over full sequences, ``output_proj`` is row-parallel (GEMM → reduce-scatter kernel with the residual
+  add fused into the reduction);
+* ``w1/w3`` are one fused column-parallel projection, ``w2`` row-parallel;
+* norm scales, embeddings and the output head stay replicated; their gradients are summed over the group
+  before the optimizer step (:meth:`TPDecoder.sync_replicated_grads`).
+
+``full_state_dict`` / ``load_full_state_dict`` translate between the sharded parameters and the ordinary
+checkpoint layout (``layers.N.attn.q_proj.weight`` …).
+"""
+from __future__ import annotations
+
+from typing import Any, Dict, List, Optional
+
+import torch
+from torch import nn
+
+from .. import ops
+from ..modules import TransformerDecoder, TransformerSelfAttentionLayer
+from ..modules.attention import _as_mask
+from .tp import TensorParallelContext, column_parallel_linear, row_parallel_linear
+
+
+def _rows(t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    n = t.shape[0] // world
+    return t[rank * n : (rank + 1) * n]
+
+
+class TPAttention(nn.Module):
+    def __init__(self, attn: nn.Module, tp: TensorParallelContext):
+        super().__init__()
+        w, r = tp.world, tp.rank
+        if attn.num_heads % w or attn.num_kv_heads % w:
+            raise ValueError(f"tensor parallel size {w} must divide num_heads ({attn.num_heads}) and num_kv_heads ({attn.num_kv_heads})")
+        for proj in (attn.q_proj, attn.k_proj, attn.v_proj, attn.output_proj):
+            if type(proj).__name__ != "Linear" or proj.bias is not None:
+                raise NotImplementedError("tensor parallelism supports bias-free, un-adapted attention projections")
+        self.tp = tp
+        self.head_dim = attn.head_dim
+        self.heads, self.kv_heads = attn.num_heads // w, attn.num_kv_heads // w
+        self.full_heads, self.full_kv_heads = attn.num_heads, attn.num_kv_heads
+        hd = self.head_dim
+        q = attn.q_proj.weight.data[r * self.heads * hd : (r + 1) * self.heads * hd]
+        k = attn.k_proj.weight.data[r * self.kv_heads * hd : (r + 1) * self.kv_heads * hd]
+        v = attn.v_proj.weight.data[r * self.kv_heads * hd : (r + 1) * self.kv_heads * hd]
+        self.wqkv = nn.Parameter(torch.cat([q, k, v]).contiguous())
+        in_per = attn.output_proj.weight.shape[1] // w
+        self.wo = nn.Parameter(attn.output_proj.weight.data[:, r * in_per : (r + 1) * in_per].contiguous())
+        self.pos_embeddings, self.q_norm, self.k_norm = attn.pos_embeddings, attn.q_norm, attn.k_norm
+        self.qk_norm_before_rope = getattr(attn, "qk_norm_before_rope", False)
+        self.is_causal, self.scale, self.softcap = attn.is_causal, attn.scale, attn.softcap
+
+    def _pos(self, t: torch.Tensor, norm: Optional[nn.Module], input_pos) -> torch.Tensor:
+        if norm is not None and self.qk_norm_before_rope:
+            t = norm(t)
+        if self.pos_embeddings is not None:
+            t = self.pos_embeddings(t, input_pos=input_pos)
+        if norm is not None and not self.qk_norm_before_rope:
+            t = norm(t)
+        return t
+
+    def forward(self, hn: torch.Tensor, residual: torch.Tensor, b: int, s: int, mask, input_pos) -> torch.Tensor:
+        hd = self.head_dim
+        qkv = column_parallel_linear(hn, self.wqkv, self.tp)  # [b·s, (h + 2·h_kv)·hd] for the local heads
+        nq, nk = self.heads * hd, self.kv_heads * hd
+        q = self._pos(qkv[:, :nq].reshape(b, s, self.heads, hd), self.q_norm, input_pos)
+        k = self._pos(qkv[:, nq : nq + nk].reshape(b, s, self.kv_heads, hd), self.k_norm, input_pos)
+        v = qkv[:, nq + nk :].reshape(b, s, self.kv_heads, hd)
+        out = ops.attention(q.contiguous(), k.contiguous(), v.contiguous(), _as_mask(mask, default_causal=self.is_causal and mask is None), scale=self.scale, softcap=self.softcap)
+        return row_parallel_linear(out.reshape(b * s, nq), self.wo, self.tp, residual)
+
+    # checkpoint layout ----------------------------------------------------------------------
+    def gather_full(self, prefix: str) -> Dict[str, torch.Tensor]:
+        tp, hd = self.tp, self.head_dim
+        nq, nk = self.heads * hd, self.kv_heads * hd
+        w = self.wqkv.data
+        return {
+            f"{prefix}q_proj.weight": tp.all_gather_rows(w[:nq].contiguous()),
+            f"{prefix}k_proj.weight": tp.all_gather_rows(w[nq : nq + nk].contiguous()),
+            f"{prefix}v_proj.weight": tp.all_gather_rows(w[nq + nk :].contiguous()),
+            f"{prefix}output_proj.weight": tp.all_gather_rows(self.wo.data.t().contiguous()).t().contiguous(),
+        }
+
+
+class TPMLP(nn.Module):
+    def __init__(self, mlp: nn.Module, tp: TensorParallelContext):
+        super().__init__()
+        w, r = tp.world, tp.rank
+        for proj in (mlp.w1, mlp.w2, mlp.w3):
+            if proj is None or type(proj).__name__ != "Linear" or proj.bias is not None:
+                raise NotImplementedError("tensor parallelism supports bias-free, un-adapted gated MLPs")
+        if not isinstance(mlp.activation, nn.SiLU):
+            raise NotImplementedError("tensor parallelism supports SwiGLU MLPs")
+        hidden = mlp.w1.weight.shape[0]
+        if hidden % w:
+            raise ValueError(f"tensor parallel size {w} must divide the MLP width {hidden}")
+        per = hidden // w
+        self.tp, self.per = tp, per
+        self.w13 = nn.Parameter(torch.cat([mlp.w1.weight.data[r * per : (r + 1) * per], mlp.w3.weight.data[r * per : (r + 1) * per]]).contiguous())
+        self.w2 = nn.Parameter(mlp.w2.weight.data[:, r * per : (r + 1) * per].contiguous())
+
+    def forward(self, hn: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+        gu = column_parallel_linear(hn, self.w13, self.tp)
+        h = ops.swiglu(gu[:, : self.per].contiguous(), gu[:, self.per :].contiguous())
+        return row_parallel_linear(h, self.w2, self.tp, residual)
+
+    def gather_full(self, prefix: str) -> Dict[str, torch.Tensor]:
+        tp = self.tp
+        return {
+            f"{prefix}w1.weight": tp.all_gather_rows(self.w13.data[: self.per].contiguous()),
+            f"{prefix}w3.weight": tp.all_gather_rows(self.w13.data[self.per :].contiguous()),
+            f"{prefix}w2.weight": tp.all_gather_rows(self.w2.data.t().contiguous()).t().contiguous(),
+        }
+
+
+class TPLayer(nn.Module):
+    def __init__(self, layer: TransformerSelfAttentionLayer, tp: TensorParallelContext):
+        super().__init__()
+        if not isinstance(layer.sa_scale, nn.Identity) or not isinstance(layer.mlp_scale, nn.Identity):
+            raise NotImplementedError("tensor parallelism does not support post-norm / gated residual layers")
+        self.attn, self.mlp = TPAttention(layer.attn, tp), TPMLP(layer.mlp, tp)
+        self.sa_norm, self.mlp_norm = layer.sa_norm, layer.mlp_norm
+        self.mask_mod = layer.mask_mod
+
+    def forward(self, h: torch.Tensor, b: int, s: int, mask, input_pos) -> torch.Tensor:
+        if self.mask_mod is not None:
+            mask = self.mask_mod(mask, b, s)
+        h = self.attn(self.sa_norm(h), h, b, s, mask, input_pos)
+        return self.mlp(self.mlp_norm(h), h)
+
+
+class TPDecoder(nn.Module):
+    """Forward returns the hidden states (or logits) of *this rank's* token rows, shaped ``[1, rows, ·]``;
+    use :meth:`shard_rows` to cut labels the same way."""
+
+    def __init__(self, model: TransformerDecoder, tp: TensorParallelContext, activation_checkpointing: bool = False):
+        super().__init__()
+        self.tp = tp
+        self.tok_embeddings, self.norm, self.output = model.tok_embeddings, model.norm, model.output
+        layers = []
+        for layer in model.layers:
+            inner = getattr(layer, "inner", layer)  # unwrap activation-checkpoint wrappers
+            if not isinstance(inner, TransformerSelfAttentionLayer):
+                raise NotImplementedError(f"tensor parallelism supports self-attention decoder layers, got {type(inner).__name__}")
+            layers.append(TPLayer(inner, tp))
+        self.layers = nn.ModuleList(layers)
+        self.max_seq_len = model.max_seq_len
+        self.skip_output_layer = model.skip_output_layer
+        self.activation_checkpointing = activation_checkpointing
+        self._replicated = [p for m in (self.tok_embeddings, self.norm, self.output) for p in m.parameters()]
+        for layer in self.layers:
+            self._replicated += list(layer.sa_norm.parameters()) + list(layer.mlp_norm.parameters())
+        seen = set()
+        self._replicated = [p for p in self._replicated if not (id(p) in seen or seen.add(id(p)))]
+
+    def shard_rows(self, t: torch.Tensor) -> torch.Tensor:
+        """``[b, s, …]`` → this rank's ``[1, b·s / tp, …]`` rows of the flattened token dimension."""
+        flat = t.reshape(t.shape[0] * t.shape[1], *t.shape[2:])
+        return _rows(flat, self.tp.rank, self.tp.world).unsqueeze(0)
+
+    def forward(self, tokens: torch.Tensor, *, mask=None, input_pos: Optional[torch.Tensor] = None, **_: Any) -> torch.Tensor:
+        b, s = tokens.shape
+        if (b * s) % self.tp.world:
+            raise ValueError(f"batch·seq ({b * s}) must be divisible by the tensor parallel size ({self.tp.world})")
+        h = self.tok_embeddings(self.shard_rows(tokens)[0])
+        for layer in self.layers:
+            if self.activation_checkpointing and torch.is_grad_enabled():
+                h = torch.utils.checkpoint.checkpoint(layer, h, b, s, mask, input_pos, use_reentrant=False)
+            else:
+                h = layer(h, b, s, mask, input_pos)
+        h = self.norm(h).unsqueeze(0)
+        return h if self.skip_output_layer else self.output(h).float()
+
+    def sync_replicated_grads(self) -> None:
+        """Sum the gradients of replicated parameters over the group (one collective on a flat buffer)."""
+        grads = [p.grad for p in self._replicated if p.grad is not None]
+        if not grads or self.tp.world == 1:
+            return
+        flat = torch.cat([g.reshape(-1).float() for g in grads])
+        self.tp.all_reduce_(flat)
+        off = 0
+        for g in grads:
+            g.copy_(flat[off : off + g.numel()].view_as(g))
+            off += g.numel()
+
+    def full_state_dict(self) -> Dict[str, torch.Tensor]:
+        """Checkpoint-layout state dict (every rank takes part in the gathers; all get the result)."""
+        out: Dict[str, torch.Tensor] = {}
+        for name, mod in (("tok_embeddings", self.tok_embeddings), ("norm", self.norm), ("output", self.output)):
+            for k, v in mod.state_dict().items():
+                out[f"{name}.{k}"] = v.detach()
+        for i, layer in enumerate(self.layers):
+            out.update(layer.attn.gather_full(f"layers.{i}.attn."))
+            out.update(layer.mlp.gather_full(f"layers.{i}.mlp."))
+            for nm in ("sa_norm", "mlp_norm"):
+                for k, v in getattr(layer, nm).state_dict().items():
+                    out[f"layers.{i}.{nm}.{k}"] = v.detach()
+            for nm in ("q_norm", "k_norm"):
+                norm = getattr(layer.attn, nm)
+                if isinstance(norm, nn.Module):
+                    for k, v in norm.state_dict().items():
+                        out[f"layers.{i}.attn.{nm}.{k}"] = v.detach()
+        return out
+
+
+def tensor_parallelize(model: TransformerDecoder, tp: TensorParallelContext, activation_checkpointing: bool = False) -> TPDecoder:
+    """Build the tensor-parallel model from a fully materialised (every rank: identical) decoder.  The full
+    projection weights are released as each layer is converted."""
+    out = TPDecoder(model, tp, activation_checkpointing)
+    for layer in model.layers:
+        inner = getattr(layer, "inner", layer)
+        for proj in (inner.attn.q_proj, inner.attn.k_proj, inner.attn.v_proj, inner.attn.output_proj, inner.mlp.w1, inner.mlp.w2, inner.mlp.w3):
+            proj.weight.data = torch.empty(0, dtype=proj.weight.dtype, device=proj.weight.device)
+    return out

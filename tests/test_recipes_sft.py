@@ -82,3 +82,26 @@ def test_lora_distributed_two_ranks(tmp_path):
     losses = read_losses(tmp_path / "out" / "logs" / "log.txt")
     assert len(losses) == 5 and losses[-1] < losses[0]
     assert (tmp_path / "out" / "epoch_4" / "adapter_model.safetensors").exists()
+
+
+@pytest.mark.timeout(900)
+def test_full_distributed_tensor_parallel_matches_single_process(tmp_path, tune_path, monkeypatch):
+    """tensor_parallel_dim=2 on two gloo ranks: both ranks read the same batch, each owns half of the token rows."""
+    ckpt = tmp_path / "ckpt"
+    write_tiny_hf_checkpoint(ckpt)
+    common = f"checkpointer.checkpoint_dir={ckpt} metric_logger.filename=log.txt max_steps_per_epoch=3 dataset.num_samples=8 clip_grad_norm=1.0"
+    run_tune(tune_path, f"run full_finetune_single_device --config tiny/llama_full_single_device {common} output_dir={tmp_path / 'single'}", monkeypatch)
+    single = read_losses(tmp_path / "single" / "logs" / "log.txt")
+    _tune_subprocess(
+        ["run", "--nnodes=1", "--nproc_per_node=2", "--master-addr=127.0.0.1", "--master-port=29535", "full_finetune_distributed", "--config", "tiny/llama_full_distributed"]
+        + common.split()
+        + [f"output_dir={tmp_path / 'tp'}", "tensor_parallel_dim=2"]
+    )
+    tp_losses = read_losses(tmp_path / "tp" / "logs" / "log.txt")
+    assert len(tp_losses) == 3
+    torch.testing.assert_close(torch.tensor(tp_losses), torch.tensor(single), rtol=2e-4, atol=2e-4)
+    a = load_file(str(tmp_path / "single" / "epoch_0" / "model-00001-of-00001.safetensors"))
+    b = load_file(str(tmp_path / "tp" / "epoch_0" / "model-00001-of-00001.safetensors"))
+    assert set(a) == set(b)
+    for k in a:
+        torch.testing.assert_close(a[k], b[k], rtol=1e-3, atol=2e-5)

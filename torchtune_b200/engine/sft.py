@@ -364,6 +364,8 @@ class SFTTrainer:
     def _loss_step(self, batch: Dict[str, Any]):
         """Returns ``(loss_sum, n_valid)`` for one micro-batch."""
         labels = batch.pop("labels")
+        if hasattr(self._model, "shard_rows"):  # tensor parallel: the loss runs on this rank's token rows
+            labels = self._model.shard_rows(labels)
         with self._activations_ctx:
             outputs = self._model(**batch)
         if hasattr(self._loss_fn, "compute_sum"):

@@ -78,6 +78,63 @@ class ReplicatedOptimizer:
             p.grad = None
 
 
+class TensorParallelOptimizer:
+    """A ``torch.optim`` optimizer over the local (sharded + replicated) parameters of a tensor-parallel model:
+    gradients of replicated parameters are summed over the group first; the clipping norm counts sharded
+    parameters on every rank and replicated ones once."""
+
+    def __init__(self, strategy: "ParallelStrategy", model: nn.Module, optimizer: torch.optim.Optimizer):
+        self.strategy, self.model, self.optimizer = strategy, model, optimizer
+        self.last_grad_norm: Optional[torch.Tensor] = None
+
+    torch_optimizer = property(lambda self: self.optimizer)
+    param_groups = property(lambda self: self.optimizer.param_groups)
+
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        self.optimizer.zero_grad(set_to_none=set_to_none)
+
+    def state_dict(self):
+        return self.optimizer.state_dict()
+
+    def load_state_dict(self, sd) -> None:
+        self.optimizer.load_state_dict(sd)
+
+    def full_state_dict(self, is_rank_zero: bool = True, group=None):
+        """Optimizer state of *this rank's shard*; resuming requires the same tensor-parallel size."""
+        return {"tp_rank_states": self._gather_states()} if is_rank_zero else (self._gather_states() and {})
+
+    def _gather_states(self):
+        states = [None] * self.strategy.world
+        dist.all_gather_object(states, self.optimizer.state_dict())
+        return states
+
+    def load_full_state_dict(self, sd) -> None:
+        states = sd.get("tp_rank_states")
+        if states is None or len(states) != self.strategy.world:
+            raise ValueError("optimizer checkpoint was written with a different tensor-parallel size")
+        self.optimizer.load_state_dict(states[self.strategy.rank])
+
+    def step(self, grad_scale=1.0, max_grad_norm: Optional[float] = None, group=None) -> None:
+        model = self.model
+        model.sync_replicated_grads()
+        params = [p for p in model.parameters() if p.grad is not None]
+        scale = grad_scale if isinstance(grad_scale, torch.Tensor) else torch.tensor(float(grad_scale), device=params[0].device)
+        for p in params:
+            p.grad.mul_(scale.to(p.grad.dtype))
+        self.last_grad_norm = None
+        if max_grad_norm is not None:
+            replicated = {id(p) for p in model._replicated}
+            sharded_sq = sum((p.grad.float().pow(2).sum() for p in params if id(p) not in replicated), torch.zeros((), device=params[0].device))
+            repl_sq = sum((p.grad.float().pow(2).sum() for p in params if id(p) in replicated), torch.zeros((), device=params[0].device))
+            self.strategy.tp.all_reduce_(sharded_sq)
+            norm = (sharded_sq + repl_sq).sqrt()
+            self.last_grad_norm = norm
+            coef = torch.clamp(float(max_grad_norm) / (norm + 1e-6), max=1.0)
+            for p in params:
+                p.grad.mul_(coef.to(p.grad.dtype))
+        self.optimizer.step()
+
+
 class ParallelStrategy(DataParallelEngine):
     """Process group + parallel dims + resident data-parallel engine, built from recipe config keys
     ``tensor_parallel_dim``, ``context_parallel_dim``, ``data_parallel_shard_dim``,
@@ -108,12 +165,13 @@ class ParallelStrategy(DataParallelEngine):
             cp=get("context_parallel_dim", 1) or 1,
             world_size=world,
         )
-        if self.dims.tp_enabled or self.dims.cp_enabled:
-            raise NotImplementedError(
-                "tensor_parallel_dim / context_parallel_dim > 1 are not wired into the recipes yet; "
-                "an 8-way data-parallel job holds models up to ~70B parameters resident on 180 GB GPUs"
-            )
+        if self.dims.cp_enabled:
+            raise NotImplementedError("context_parallel_dim > 1 is not wired into the recipes yet")
+        if self.dims.tp_enabled and self.dims.dp_size > 1:
+            raise NotImplementedError("tensor_parallel_dim > 1 currently requires data_parallel_shard_dim = data_parallel_replicate_dim = 1 (tp == world size)")
         super().__init__(device=device, group=None)
+        self.tp = None  # TensorParallelContext, created in shard_model
+        self._cfg = cfg
         self._cpu_offload = bool(get("fsdp_cpu_offload", False))
 
     # sizes -------------------------------------------------------------------------------
@@ -124,6 +182,39 @@ class ParallelStrategy(DataParallelEngine):
     @property
     def min_seq_len_divisor(self) -> int:  # type: ignore[override]
         return self.dims.min_seq_len_divisor
+
+    # data-parallel coordinates: with tensor parallelism every rank reads the same batch ------------
+    @property
+    def dp_size(self) -> int:  # type: ignore[override]
+        return 1 if self.dims.tp_enabled else self.world
+
+    @property
+    def dp_rank(self) -> int:  # type: ignore[override]
+        return 0 if self.dims.tp_enabled else self.rank
+
+    def _tp_max_rows(self, cfg, model: nn.Module) -> int:
+        get = cfg.get if hasattr(cfg, "get") else (lambda k, d=None: d)
+        explicit = get("tensor_parallel_max_tokens")
+        if explicit:
+            return -(-int(explicit) // self.dims.tp)
+        seq = None
+        for section in ("tokenizer", "dataset"):
+            sec = get(section)
+            if sec is not None and hasattr(sec, "get"):
+                seq = seq or sec.get("max_seq_len") or sec.get("seq_len")
+        seq = int(seq or getattr(model, "max_seq_len", 2048))
+        return -(-(int(get("batch_size", 1)) * seq) // self.dims.tp)
+
+    def _shard_model_tp(self, model: nn.Module, cfg) -> nn.Module:
+        from ..training.memory import CheckpointedLayer
+        from .tp import TensorParallelContext
+        from .tp_model import tensor_parallelize
+
+        core = model
+        width = core.tok_embeddings.embedding_dim
+        self.tp = TensorParallelContext(self.device, None, max_rows_per_rank=self._tp_max_rows(cfg, core), max_width=width)
+        ac = any(isinstance(layer, CheckpointedLayer) for layer in core.layers)
+        return tensor_parallelize(core, self.tp, activation_checkpointing=ac)
 
     # model -------------------------------------------------------------------------------
     def shard_model(self, model: nn.Module, cfg, base_sd: Dict[str, Any], adapter_sd: Optional[Dict[str, Any]] = None, *, dtype: torch.dtype = torch.bfloat16, strict: bool = True) -> nn.Module:
@@ -148,6 +239,10 @@ class ParallelStrategy(DataParallelEngine):
         else:
             model.load_state_dict(base_sd, strict=True)
         validate_no_params_on_meta_device(model)
+        if self.dims.tp_enabled:
+            if is_lora:
+                raise NotImplementedError("tensor parallelism is implemented for full fine-tuning")
+            return self._shard_model_tp(model, cfg)
         self.prepare(model)
         if self.world > 1:
             # adapters are initialised with rank-dependent seeds: rank 0's values win
@@ -162,6 +257,13 @@ class ParallelStrategy(DataParallelEngine):
 
     # optimizer ---------------------------------------------------------------------------
     def build_optimizer(self, model: nn.Module, cfg_optimizer=None, opt_state: Optional[Dict[str, Any]] = None, **kwargs: Any):
+        if self.tp is not None:
+            from .. import config
+
+            opt = TensorParallelOptimizer(self, model, config.instantiate(cfg_optimizer, [p for p in model.parameters() if p.requires_grad]))
+            if opt_state:
+                opt.load_full_state_dict(opt_state)
+            return opt
         if self.flat is None:
             raise RuntimeError("shard_model(model, …) must run before build_optimizer")
         if cfg_optimizer is None or not hasattr(cfg_optimizer, "get"):
@@ -192,11 +294,19 @@ class ParallelStrategy(DataParallelEngine):
 
     def optimizer_step(self, model: nn.Module, optimizer, grad_scale, clip_grad_norm: Optional[float] = None):
         clip = float(clip_grad_norm) if clip_grad_norm is not None else None
+        if self.tp is not None:
+            optimizer.step(grad_scale=grad_scale, max_grad_norm=clip)
+            optimizer.zero_grad()
+            return optimizer.last_grad_norm
         return super().optimizer_step(model, optimizer, grad_scale, clip)
 
     # state dicts -------------------------------------------------------------------------
     def gather_full_state_dict(self, model: nn.Module) -> Dict[str, Any]:
         from ..training._distributed import gather_cpu_state_dict
+
+        if self.tp is not None:
+            full = model.full_state_dict()  # collective: every rank takes part
+            return {k: v.cpu() for k, v in full.items()} if self.rank == 0 else {}
 
         return gather_cpu_state_dict(model, self.rank == 0, self.device)
 
@@ -204,6 +314,9 @@ class ParallelStrategy(DataParallelEngine):
         return optimizer.full_state_dict(self.rank == 0, group=self.group)
 
     def shutdown(self) -> None:
+        if self.tp is not None:
+            self.tp.close()
+            self.tp = None
         super().shutdown()
         if self._owns_group and dist.is_initialized():
             dist.destroy_process_group()

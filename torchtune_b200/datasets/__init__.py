@@ -1,3 +1,4 @@
+from . import multimodal
 from ._builders import (
     alpaca_cleaned_dataset,
     alpaca_dataset,
@@ -26,6 +27,7 @@ from ._synthetic import (
 from ._text_completion import TextCompletionDataset, text_completion_dataset
 
 __all__ = [
+    "multimodal",
     "alpaca_cleaned_dataset",
     "alpaca_dataset",
     "chat_dataset",

@@ -85,3 +85,44 @@ def test_resume_matches_uninterrupted(tmp_path, tune_path, monkeypatch):
     run_tune(tune_path, base + f"output_dir={tmp_path / 'part'} resume_from_checkpoint=True", monkeypatch)
     resumed = read_losses(tmp_path / "part" / "logs" / "log.txt")
     torch.testing.assert_close(torch.tensor(resumed), torch.tensor(full[3:]), rtol=1e-5, atol=1e-5)
+
+
+def test_async_sharded_checkpoint_resume_matches_uninterrupted(tmp_path, tune_path, monkeypatch):
+    """enable_async_checkpointing: intermediate checkpoints are per-rank shard files written by a background thread;
+    resuming from one continues the loss curve of the uninterrupted run."""
+    ckpt = tmp_path / "ckpt"
+    write_tiny_hf_checkpoint(ckpt)
+    base = (f"run full_finetune_single_device --config tiny/llama_full_single_device checkpointer.checkpoint_dir={ckpt} metric_logger.filename=log.txt "
+            "max_steps_per_epoch=3 dataset.num_samples=12 enable_async_checkpointing=True ")
+    run_tune(tune_path, base + f"epochs=2 output_dir={tmp_path / 'full'}", monkeypatch)
+    full = read_losses(tmp_path / "full" / "logs" / "log.txt")
+    assert len(full) == 6
+    assert (tmp_path / "full" / "epoch_0" / "rank_0.pt").exists() and (tmp_path / "full" / "epoch_0" / "metadata.json").exists()
+    assert (tmp_path / "full" / "epoch_1" / "model-00001-of-00001.safetensors").exists()  # the final checkpoint is a full one
+    # interrupted run: stop after the first epoch by asking for a single epoch of two, then resume
+    run_tune(tune_path, base + f"epochs=2 output_dir={tmp_path / 'part'}", monkeypatch)
+    import shutil
+
+    shutil.rmtree(tmp_path / "part" / "epoch_1")
+    (tmp_path / "part" / "logs" / "log.txt").unlink()
+    run_tune(tune_path, base + f"epochs=2 output_dir={tmp_path / 'part'} resume_from_checkpoint=True", monkeypatch)
+    resumed = read_losses(tmp_path / "part" / "logs" / "log.txt")
+    assert len(resumed) == 3
+    torch.testing.assert_close(torch.tensor(resumed), torch.tensor(full[3:]), rtol=1e-5, atol=1e-6)
+
+
+def test_distributed_checkpointer_roundtrip_sync_and_async(tmp_path):
+    from torchtune_b200.training import DistributedCheckpointer
+
+    ck = DistributedCheckpointer(checkpoint_dir=str(tmp_path), output_dir=str(tmp_path / "out"))
+    state = {"model": {"w": torch.arange(6.0).view(2, 3)}, "optimizer": {"step": 3, "m": torch.ones(4)}, "seed": 7}
+    ck.save_checkpoint(state, epoch=0)
+    ck.save_checkpoint({**state, "seed": 8}, epoch=1, save_async=True)
+    ck.wait()
+    assert not list((tmp_path / "out").glob("*.partial"))
+    target = {"model": {"w": torch.zeros(2, 3)}, "optimizer": {"step": 0, "m": torch.zeros(4)}, "seed": 0}
+    out = ck.load_checkpoint(target)
+    assert out["seed"] == 8 and out["optimizer"]["step"] == 3
+    assert torch.equal(target["model"]["w"], state["model"]["w"]) and torch.equal(target["optimizer"]["m"], torch.ones(4))
+    with __import__("pytest").raises(ValueError):
+        ck.load_checkpoint({"model": {"w": torch.zeros(3, 3)}})

@@ -95,11 +95,30 @@ class SFTTrainer:
         self._checkpointer = None
         self._metric_logger = None
         self._profiler = None
+        # asynchronous, per-rank sharded intermediate checkpoints (final checkpoints are always full HF-format)
+        self._enable_async_checkpointing = cfg.get("enable_async_checkpointing", False)
+        self._sharded_checkpointer = None
 
     # ------------------------------------------------------------------ checkpoint
     def load_checkpoint(self, cfg_checkpointer: DictConfig) -> Dict[str, Any]:
-        self._checkpointer = config.instantiate(cfg_checkpointer, should_load_recipe_state=self._resume_from_checkpoint)
+        sharded_resume = False
+        if self._enable_async_checkpointing:
+            from ..training.checkpointing._utils import get_most_recent_checkpoint
+
+            self._sharded_checkpointer = training.DistributedCheckpointer(checkpoint_dir=cfg_checkpointer.checkpoint_dir, output_dir=cfg_checkpointer.get("output_dir") or self._output_dir)
+            recent = get_most_recent_checkpoint(self._sharded_checkpointer.output_dir) if self._resume_from_checkpoint else None
+            sharded_resume = recent is not None and os.path.exists(os.path.join(str(recent), "metadata.json"))
+        self._checkpointer = config.instantiate(cfg_checkpointer, should_load_recipe_state=self._resume_from_checkpoint and not sharded_resume)
         ckpt = self._checkpointer.load_checkpoint()
+        if sharded_resume:
+            shard = self._sharded_checkpointer.load_checkpoint()
+            self._sharded_opt_state = shard.pop(training.OPT_KEY, None)
+            if self.parallel is not None and self.world_size > 1:
+                # rank 0's shard carries the replicated weights and the recipe state
+                obj = [shard if self._is_rank_zero else None]
+                torch.distributed.broadcast_object_list(obj, src=0)
+                shard = obj[0]
+            ckpt.update(shard)
         if self._resume_from_checkpoint:
             self._update_recipe_state(ckpt)
         return ckpt
@@ -257,11 +276,18 @@ class SFTTrainer:
                 self._optim_ckpt_wrapper.load_state_dict(opt_state)
             utils.log_rank_zero(log, "In-backward optimizers are set up.")
             return None
+        sharded_state = getattr(self, "_sharded_opt_state", None)
+        if sharded_state is not None:
+            opt_state = None
         if self.parallel is not None:
             optimizer = self.parallel.build_optimizer(self._model, cfg_optimizer, opt_state)
+            if sharded_state is not None:
+                optimizer.load_state_dict(sharded_state)
         else:
             optimizer = config.instantiate(cfg_optimizer, [p for p in self._model.parameters() if p.requires_grad])
-            if opt_state is not None:
+            if sharded_state is not None:
+                optimizer.load_state_dict(sharded_state)
+            elif opt_state is not None:
                 optimizer.load_state_dict(opt_state)
         utils.log_rank_zero(log, "Optimizer is initialized.")
         return optimizer
@@ -313,6 +339,9 @@ class SFTTrainer:
     def save_checkpoint(self, *, epoch: int, full_tensors: bool = True) -> None:
         intermediate = self.global_step < self.total_training_steps if self.save_every_n_steps else epoch + 1 < self.total_epochs
         t0 = time.perf_counter()
+        if intermediate and self._sharded_checkpointer is not None and not self._optimizer_in_bwd:
+            self._save_sharded(epoch)
+            return
         if self.parallel is not None:
             model_sd = self.parallel.gather_full_state_dict(self._model)
             opt_sd = self.parallel.gather_optimizer_state_dict(self._model, self._optimizer) if intermediate else None
@@ -359,6 +388,27 @@ class SFTTrainer:
             log.info(f"Saving checkpoint took {time.perf_counter() - t0:.2f} secs")
         if self.parallel is not None:
             self.parallel.barrier()
+
+    def _save_sharded(self, epoch: int) -> None:
+        """Intermediate checkpoint: every rank snapshots its own optimizer shard (rank 0 also the resident weights
+        and the recipe state) to host memory and a writer thread persists it while training continues."""
+        state: Dict[str, Any] = {training.OPT_KEY: self._optimizer.state_dict()}
+        if self._is_rank_zero:
+            sd = self._model.state_dict()
+            if self.is_lora:
+                sd = get_adapter_state_dict(sd)
+            state[training.ADAPTER_KEY if self.is_lora else training.MODEL_KEY] = sd
+            state.update(
+                {
+                    training.SEED_KEY: self.seed,
+                    training.EPOCHS_KEY: self.epochs_run,
+                    training.TOTAL_EPOCHS_KEY: self.total_epochs,
+                    training.MAX_STEPS_KEY: self.max_steps_per_epoch,
+                    training.STEPS_KEY: self.global_step,
+                    training.DATALOADER_KEY: self._dataloader.state_dict(),
+                }
+            )
+        self._sharded_checkpointer.save_checkpoint(state, epoch=epoch, save_async=True, step=self.global_step if self.save_every_n_steps else None, dir_prefix="step" if self.save_every_n_steps else "epoch")
 
     # ------------------------------------------------------------------ train
     def _loss_step(self, batch: Dict[str, Any]):
@@ -502,6 +552,8 @@ class SFTTrainer:
         self._profiler.stop()
 
     def cleanup(self) -> None:
+        if self._sharded_checkpointer is not None:
+            self._sharded_checkpointer.wait()
         if self._is_rank_zero and self._metric_logger is not None:
             self._metric_logger.close()
         if self.parallel is not None:

@@ -15,6 +15,7 @@ from .checkpointing import (
     TOTAL_EPOCHS_KEY,
     VAL_DATALOADER_KEY,
     Checkpointer,
+    DistributedCheckpointer,
     FormattedCheckpointFiles,
     FullModelHFCheckpointer,
     FullModelMetaCheckpointer,

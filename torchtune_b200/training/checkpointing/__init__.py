@@ -3,6 +3,7 @@ from ._checkpointer import (
     FullModelMetaCheckpointer,
     FullModelTorchTuneCheckpointer,
 )
+from ._sharded import DistributedCheckpointer
 from ._utils import (
     ADAPTER_CONFIG,
     ADAPTER_KEY,
@@ -24,6 +25,7 @@ from ._utils import (
 Checkpointer = FullModelHFCheckpointer
 
 __all__ = [
+    "DistributedCheckpointer",
     "FullModelHFCheckpointer",
     "FullModelMetaCheckpointer",
     "FullModelTorchTuneCheckpointer",

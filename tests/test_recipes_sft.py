@@ -105,3 +105,12 @@ def test_full_distributed_tensor_parallel_matches_single_process(tmp_path, tune_
     assert set(a) == set(b)
     for k in a:
         torch.testing.assert_close(a[k], b[k], rtol=1e-3, atol=2e-5)
+
+
+def test_early_exit_recipe_runs_and_rotates_exits(tmp_path, tune_path, monkeypatch):
+    ckpt = tmp_path / "ckpt"
+    write_tiny_hf_checkpoint(ckpt)
+    run_tune(tune_path, f"run dev/early_exit_finetune_distributed --config tiny/llama_early_exit checkpointer.checkpoint_dir={ckpt} output_dir={tmp_path / 'out'} metric_logger.filename=log.txt max_steps_per_epoch=4", monkeypatch)
+    losses = read_losses(tmp_path / "out" / "logs" / "log.txt")
+    assert len(losses) == 4 and all(l == l and 5.0 < l < 9.0 for l in losses)
+    assert (tmp_path / "out" / "epoch_0" / "model-00001-of-00001.safetensors").exists()

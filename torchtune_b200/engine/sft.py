@@ -263,6 +263,9 @@ class SFTTrainer:
     def _before_batch(self, idx: int) -> None:
         """Hook called before every micro-batch."""
 
+    def _after_step(self) -> None:
+        """Hook called after every optimizer step."""
+
     def _tokenizer_vocab(self, cfg) -> Optional[int]:
         tok = getattr(self, "_tokenizer", None)
         return getattr(tok, "vocab_size", None) if tok is not None else None
@@ -512,6 +515,7 @@ class SFTTrainer:
                     if self._lr_scheduler is not None:
                         self._lr_scheduler.step()
                     self.global_step += 1
+                    self._after_step()
 
                     timer.stop()
                     aux = self._reduce_aux_sums(num_tokens)

@@ -41,36 +41,34 @@ class LayerDropout(nn.Module):
 
 
 class ModuleLayerDropoutWrapper(nn.Module):
-    """Applies :class:`LayerDropout` around ``module`` while staying transparent: attribute access,
-    indexing and the state dict are those of the wrapped module."""
+    """Applies :class:`LayerDropout` around ``module`` while staying transparent: the wrapper shares the wrapped
+    module's parameter / buffer / sub-module tables, so state-dict keys, attribute access and indexing are those of the
+    wrapped module (no ``module.`` prefix appears in checkpoints)."""
 
     def __init__(self, module: nn.Module, dropout: LayerDropout):
         super().__init__()
-        self.module, self.dropout = module, dropout
+        self.__dict__["module"] = module
+        self.__dict__["dropout"] = dropout
+        self._modules = module._modules
+        self._parameters = module._parameters
+        self._buffers = module._buffers
+
+    def train(self, mode: bool = True):
+        self.__dict__["dropout"].train(mode)
+        self.__dict__["module"].train(mode)
+        return super().train(mode)
 
     def forward(self, input: torch.Tensor, *args: Any, **kwargs: Any):
-        return self.dropout(self.module, input, *args, **kwargs)
+        return self.__dict__["dropout"](self.__dict__["module"], input, *args, **kwargs)
 
     def __getattr__(self, name: str) -> Any:
         try:
             return super().__getattr__(name)
         except AttributeError:
-            return getattr(super().__getattr__("module"), name)
-
-    def __setattr__(self, name: str, value: Any) -> None:
-        if name in ("module", "dropout") or "module" not in self._modules:
-            super().__setattr__(name, value)
-        else:
-            setattr(self._modules["module"], name, value)
+            return getattr(self.__dict__["module"], name)
 
     def __getitem__(self, key: int) -> Any:
-        return self.module[key]
-
-    def state_dict(self, *args: Any, **kwargs: Any):
-        return self.module.state_dict(*args, **kwargs)
-
-    def load_state_dict(self, state_dict, *args: Any, **kwargs: Any):
-        return self.module.load_state_dict(state_dict, *args, **kwargs)
+        return self.__dict__["module"][key]
 
 
 class ScaleType(str, Enum):

@@ -1,0 +1,6 @@
+from .data import RLDataset, gsm8k_dataset, gsm8k_sft, padded_collate_rl, reasoning_dataset
+from .loss import GRPOCompletionLoss, GRPOLoss, GRPOSimpleLoss
+from .rewards import batch_shaped_correctness_reward, extract_tags, shaped_correctness_reward
+from .types import GRPOStats, GRPOTrajectory
+
+__all__ = ["GRPOCompletionLoss", "GRPOLoss", "GRPOSimpleLoss", "GRPOStats", "GRPOTrajectory", "RLDataset", "batch_shaped_correctness_reward", "extract_tags", "gsm8k_dataset", "gsm8k_sft", "padded_collate_rl", "reasoning_dataset", "shaped_correctness_reward"]

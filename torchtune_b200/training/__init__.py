@@ -15,6 +15,8 @@ from .checkpointing import (
     TOTAL_EPOCHS_KEY,
     VAL_DATALOADER_KEY,
     Checkpointer,
+    CheckpointClient,
+    TrainingProgress,
     DistributedCheckpointer,
     FormattedCheckpointFiles,
     FullModelHFCheckpointer,
@@ -56,3 +58,4 @@ from ._distributed import (
 )
 from . import quantization
 from .quantization import convert_to_float8_training, get_quantizer_mode, is_fp8_tensorwise_scaling, swap_lora_linear_with_qat
+from ._compile import compile_loss, compile_model

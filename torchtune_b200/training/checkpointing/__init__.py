@@ -3,6 +3,7 @@ from ._checkpointer import (
     FullModelMetaCheckpointer,
     FullModelTorchTuneCheckpointer,
 )
+from ._checkpoint_client import CheckpointClient, TrainingProgress
 from ._sharded import DistributedCheckpointer
 from ._utils import (
     ADAPTER_CONFIG,
@@ -25,6 +26,8 @@ from ._utils import (
 Checkpointer = FullModelHFCheckpointer
 
 __all__ = [
+    "CheckpointClient",
+    "TrainingProgress",
     "DistributedCheckpointer",
     "FullModelHFCheckpointer",
     "FullModelMetaCheckpointer",

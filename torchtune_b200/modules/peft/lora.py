@@ -82,9 +82,12 @@ class LoRALinear(nn.Module):
         return ops.linear(x, self.weight, self.bias)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        out = self._base_forward(x)
         if self.disabled:
-            return out
+            return self._base_forward(x)
+        if not self._quantize_base and type(self)._base_forward is LoRALinear._base_forward:
+            # dense base: one fused call (adapter product accumulated by the GEMM epilogue on CUDA)
+            return ops.lora_linear(x, self.dropout(x), self.weight, self.bias, self.lora_a.weight, self.lora_b.weight, self.alpha / self.rank)
+        out = self._base_forward(x)
         a = ops.linear(self.dropout(x), self.lora_a.weight)
         return out + (self.alpha / self.rank) * ops.linear(a, self.lora_b.weight)
 

@@ -16,6 +16,7 @@ from . import reference
 from .mask import AttentionMask
 
 __all__ = [
+    "lora_linear",
     "matmul",
     "linear",
     "rms_norm",
@@ -61,6 +62,16 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
 
         return _cuda.linear(x, weight, bias)
     return F.linear(x, weight, bias)
+
+
+def lora_linear(x: torch.Tensor, xd: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], lora_a: torch.Tensor, lora_b: torch.Tensor, scale: float) -> torch.Tensor:
+    """``x @ weight.T (+ bias) + scale · (xd @ lora_a.T) @ lora_b.T`` — ``xd`` is the adapter branch's input (``x`` after dropout)."""
+    rank = lora_a.shape[0]
+    if _native(x) and weight.dtype == lora_a.dtype == lora_b.dtype == torch.bfloat16 and rank % 8 == 0 and x.shape[-1] % 8 == 0 and weight.shape[0] % 8 == 0:
+        from . import _cuda
+
+        return _cuda.lora_linear(x, xd, weight, bias, lora_a, lora_b, scale)
+    return F.linear(x, weight, bias) + scale * F.linear(F.linear(xd, lora_a), lora_b)
 
 
 def matmul(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:

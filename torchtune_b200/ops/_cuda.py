@@ -92,6 +92,54 @@ class _Linear(torch.autograd.Function):
         return dx, dw, db
 
 
+class _LoRALinear(torch.autograd.Function):
+    """``y = x·Wᵀ (+ b) + s·(xd·Aᵀ)·Bᵀ`` with the adapter product accumulated into ``y`` by the GEMM epilogue (no separate
+    scale / add passes); backward mirrors it: ``dx = dy·W`` then ``dx += (s·dy·B)·A`` through the accumulate epilogue,
+    ``dA = dtᵀ·xd``, ``dB = s·dyᵀ·t``.  ``xd`` is the (possibly dropped-out) adapter input."""
+
+    @staticmethod
+    def forward(ctx, x, xd, weight, bias, a, b, scale):
+        shape = x.shape
+        x2, xd2 = x.reshape(-1, shape[-1]), xd.reshape(-1, shape[-1])
+        y = gemm(x2, weight, bias=bias)
+        t = gemm(xd2, a)  # [T, r]
+        gemm(t, b, out=y, accumulate=True, alpha=float(scale))
+        ctx.save_for_backward(x2, xd2, weight, a, b, t)
+        ctx.scale, ctx.shape, ctx.has_bias = float(scale), shape, bias is not None
+        ctx.same_input = xd.data_ptr() == x.data_ptr()
+        return y.view(*shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, xd2, weight, a, b, t = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if dy2.stride(1) != 1 or dy2.stride(0) % 8:
+            dy2 = dy2.contiguous()
+        s = ctx.scale
+        dt = gemm(dy2, b, b_mn=True, alpha=s)  # [T, r] = s·dy·B
+        dx = dxd = dw = db = da = dbm = None
+        if ctx.needs_input_grad[0] or (ctx.same_input and ctx.needs_input_grad[1]):
+            dx = gemm(dy2, weight, b_mn=True)
+        if ctx.same_input:
+            if dx is not None:
+                gemm(dt, a, b_mn=True, out=dx, accumulate=True)
+        elif ctx.needs_input_grad[1]:
+            dxd = gemm(dt, a, b_mn=True).view(ctx.shape)
+        if ctx.needs_input_grad[2]:
+            dw = _wgrad(weight, dy2, x2)
+        if ctx.has_bias and ctx.needs_input_grad[3]:
+            db = dy2.sum(0)
+        if ctx.needs_input_grad[4]:
+            da = gemm(dt, xd2, a_mn=True, b_mn=True)  # [r, in]
+        if ctx.needs_input_grad[5]:
+            dbm = gemm(dy2, t, a_mn=True, b_mn=True, alpha=s)  # [out, r]
+        return (dx.view(ctx.shape) if dx is not None else None), dxd, dw, db, da, dbm, None
+
+
+def lora_linear(x, xd, weight, bias, a, b, scale):
+    return _LoRALinear.apply(x, xd, weight, bias, a, b, scale)
+
+
 class _MatmulKN(torch.autograd.Function):
     """``y[T, N] = x[T, K] · w[K, N]`` with ``w`` stored reduction-dimension-major (the layout of
     grouped expert weights ``[E, K, N]``): forward reads ``w`` as an MN-major B operand, dgrad is

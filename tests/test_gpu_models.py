@@ -88,3 +88,51 @@ def test_llama4_tiny_train_step_bf16():
     loss.backward()
     assert torch.isfinite(loss) and abs(loss.item() - 6.24) < 0.5  # ln 512
     assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in model.parameters())
+
+
+@pytest.mark.parametrize("rank,dropout_input", [(8, False), (64, True)])
+def test_lora_linear_fused_matches_reference(rank, dropout_input):
+    g = torch.Generator(device="cuda").manual_seed(0)
+    mk = lambda *s, sc=1.0: (torch.randn(*s, generator=g, device="cuda") * sc).bfloat16()
+    x, w, a, b, bias = mk(2, 96, 256, sc=0.5), mk(384, 256, sc=0.05), mk(rank, 256, sc=0.05), mk(384, rank, sc=0.05), mk(384, sc=0.1)
+    xd = (x * (torch.rand(x.shape, generator=g, device="cuda") > 0.1)).bfloat16() if dropout_input else x
+    leaves = [t.clone().requires_grad_() for t in (x, w, a, b, bias)]
+    xx, ww, aa, bb, bi = leaves
+    y = ops.lora_linear(xx, xd if dropout_input else xx, ww, bi, aa, bb, 2.0)
+    dy = mk(2, 96, 384, sc=0.2)
+    y.backward(dy)
+    ref = [t.detach().float().requires_grad_() for t in (x, w, a, b, bias)]
+    xr, wr, ar, br, bir = ref
+    xdr = xd.float() if dropout_input else xr
+    yr = F.linear(xr, wr, bir) + 2.0 * F.linear(F.linear(xdr, ar), br)
+    yr.backward(dy.float())
+    assert _rel_err(y, yr) < 1e-2
+    for name, got, want in zip("x w a b bias".split(), leaves, ref):
+        assert _rel_err(got.grad, want.grad) < 3e-2, name
+
+
+def test_nf4_dequant_kernel_matches_reference():
+    from torchtune_b200.modules.low_precision.nf4 import NF4Weight
+    from torchtune_b200.ops import reference as ref
+
+    torch.manual_seed(0)
+    w = torch.randn(512, 1024, device="cuda") * 0.05
+    nf4 = NF4Weight(512, 1024, device="cuda")
+    nf4.quantize_(w.bfloat16())
+    got = nf4.dequantize(torch.bfloat16)
+    want = ref.nf4_dequantize(nf4.weight_nf4, nf4.scaler_q, nf4.scaler_factor, nf4.scaler_mean, (512, 1024), 64, 256, torch.bfloat16)
+    assert torch.equal(got, want)
+    assert _rel_err(got, w) < 0.12  # 4-bit quantisation error
+
+
+def test_qlora_linear_trains_on_gpu():
+    from torchtune_b200.modules.peft import LoRALinear
+
+    torch.manual_seed(0)
+    with torch.device("cuda"):
+        lin = LoRALinear(1024, 512, rank=16, alpha=32, quantize_base=True).bfloat16()
+    x = (torch.randn(4, 64, 1024, device="cuda") * 0.5).bfloat16().requires_grad_()
+    y = lin(x)
+    y.float().pow(2).mean().backward()
+    assert y.shape == (4, 64, 512) and x.grad is not None and lin.lora_b.weight.grad is not None
+    assert torch.isfinite(y).all() and torch.isfinite(x.grad).all()

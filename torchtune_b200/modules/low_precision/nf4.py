@@ -62,6 +62,13 @@ class NF4Weight(nn.Module):
         self.scaler_mean.copy_(mean)
 
     def dequantize(self, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        target = dtype or self.dtype
+        n = self.shape[0] * self.shape[1]
+        if self.weight_nf4.is_cuda and target == torch.bfloat16 and n % 16 == 0 and self.block_size % 16 == 0:
+            from ...ops import _cuda, cuda_ops_enabled
+
+            if cuda_ops_enabled(self.weight_nf4):
+                return _cuda.nf4_dequantize(self.weight_nf4, self.scaler_q, self.scaler_factor, self.scaler_mean, self.shape, self.block_size, self.scaler_block_size)
         return _ref.nf4_dequantize(
             self.weight_nf4,
             self.scaler_q,

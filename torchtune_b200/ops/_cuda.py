@@ -92,6 +92,14 @@ class _Linear(torch.autograd.Function):
         return dx, dw, db
 
 
+def nf4_dequantize(packed: torch.Tensor, scaler_q: torch.Tensor, scaler_factor: torch.Tensor, scaler_mean: torch.Tensor, shape, block_size: int, scaler_block_size: int) -> torch.Tensor:
+    """NF4 codes + double-quantised scales → dense bf16 ``shape`` (one streaming kernel)."""
+    out = torch.empty(shape, dtype=_BF16, device=packed.device)
+    mean = scaler_mean.reshape(1).to(torch.float32)
+    check(lib().ttb_nf4_dequant(packed.data_ptr(), scaler_q.data_ptr(), scaler_factor.data_ptr(), mean.data_ptr(), out.data_ptr(), out.numel(), block_size, scaler_block_size, stream_ptr()), "nf4_dequant")
+    return out
+
+
 class _LoRALinear(torch.autograd.Function):
     """``y = x·Wᵀ (+ b) + s·(xd·Aᵀ)·Bᵀ`` with the adapter product accumulated into ``y`` by the GEMM epilogue (no separate
     scale / add passes); backward mirrors it: ``dx = dy·W`` then ``dx += (s·dy·B)·A`` through the accumulate epilogue,

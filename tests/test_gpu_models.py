@@ -136,3 +136,26 @@ def test_qlora_linear_trains_on_gpu():
     y.float().pow(2).mean().backward()
     assert y.shape == (4, 64, 512) and x.grad is not None and lin.lora_b.weight.grad is not None
     assert torch.isfinite(y).all() and torch.isfinite(x.grad).all()
+
+
+@pytest.mark.parametrize("counts", [[128, 128, 128, 128], [5, 0, 300, 77], [0, 0, 0, 513], [1, 1, 1, 1]])
+def test_grouped_matmul_matches_loop(counts):
+    g = torch.Generator(device="cuda").manual_seed(1)
+    E, K, N = len(counts), 192, 320
+    rows = sum(counts)
+    x = (torch.randn(rows, K, generator=g, device="cuda") * 0.5).bfloat16().requires_grad_()
+    w = (torch.randn(E, K, N, generator=g, device="cuda") * 0.1).bfloat16().requires_grad_()
+    cnt = torch.tensor(counts, device="cuda")
+    y = ops.grouped_matmul(x, w, cnt)
+    dy = (torch.randn(rows, N, generator=g, device="cuda") * 0.2).bfloat16()
+    y.backward(dy)
+    xf, wf = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    outs, s = [], 0
+    for e, n in enumerate(counts):
+        outs.append(xf[s : s + n] @ wf[e])
+        s += n
+    yf = torch.cat(outs)
+    yf.backward(dy.float())
+    assert _rel_err(y, yf) < 1e-2
+    assert _rel_err(x.grad, xf.grad) < 1e-2
+    assert _rel_err(w.grad, wf.grad) < 2e-2

@@ -50,6 +50,13 @@ class GroupedExperts(nn.Module):
         the same number of rows and ``num_tokens_per_expert`` is ``None``)."""
         if num_tokens_per_expert is None:
             return torch.stack([self._expert(e, x[e]) for e in range(self.num_experts)])
+        from .utils import should_use_grouped_mm
+
+        if should_use_grouped_mm() and x.is_cuda and x.dtype == torch.bfloat16 and self.act_fn is F.silu and x.shape[0] > 0:
+            # three grouped launches for all experts (tile → expert table built on the device: no host sync)
+            g = ops.grouped_matmul(x, self.gate_proj, num_tokens_per_expert)
+            u = ops.grouped_matmul(x, self.up_proj, num_tokens_per_expert)
+            return ops.grouped_matmul(ops.swiglu(g, u), self.down_proj, num_tokens_per_expert)
         outs, start = [], 0
         for e, n in enumerate(_segments(num_tokens_per_expert)):
             if n:

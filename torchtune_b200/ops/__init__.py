@@ -16,6 +16,7 @@ from . import reference
 from .mask import AttentionMask
 
 __all__ = [
+    "grouped_matmul",
     "lora_linear",
     "matmul",
     "linear",
@@ -72,6 +73,21 @@ def lora_linear(x: torch.Tensor, xd: torch.Tensor, weight: torch.Tensor, bias: O
 
         return _cuda.lora_linear(x, xd, weight, bias, lora_a, lora_b, scale)
     return F.linear(x, weight, bias) + scale * F.linear(F.linear(xd, lora_a), lora_b)
+
+
+def grouped_matmul(x: torch.Tensor, w: torch.Tensor, counts: torch.Tensor) -> torch.Tensor:
+    """Expert-grouped product: rows of ``x`` ``[rows, K]`` are sorted by expert, ``counts[e]`` rows belong to expert ``e`` and are
+    multiplied by ``w[e]`` (``w``: ``[E, K, N]``)."""
+    if _native(x) and w.dtype == torch.bfloat16 and x.shape[0] > 0 and x.is_contiguous() and w.is_contiguous() and x.shape[1] % 8 == 0 and w.shape[2] % 8 == 0 and counts.is_cuda:
+        from . import _cuda
+
+        return _cuda.grouped_matmul(x, w, counts)
+    outs, start = [], 0
+    for e, n in enumerate(counts.tolist()):
+        if n:
+            outs.append(x[start : start + n] @ w[e])
+        start += n
+    return torch.cat(outs) if outs else x.new_zeros(0, w.shape[2])
 
 
 def matmul(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:

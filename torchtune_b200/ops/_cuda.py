@@ -148,6 +148,56 @@ def lora_linear(x, xd, weight, bias, a, b, scale):
     return _LoRALinear.apply(x, xd, weight, bias, a, b, scale)
 
 
+def _grouped_gemm(x: torch.Tensor, w: torch.Tensor, counts: torch.Tensor, b_mn: bool) -> torch.Tensor:
+    """One launch over all experts: ``x`` ``[rows, K]`` sorted by expert, ``w`` ``[E, K, N]`` (``b_mn``) or ``[E, N, K]``, ``counts`` int64 ``[E]``
+    on the device.  The tile → expert table is built on the device, so the call never synchronises with the host."""
+    rows, K = x.shape
+    E = w.shape[0]
+    N = w.shape[2] if b_mn else w.shape[1]
+    out = torch.empty(rows, N, dtype=_BF16, device=x.device)
+    max_tiles = -(-rows // 128) + E
+    scratch = torch.empty(3 * max_tiles + 1, dtype=torch.int32, device=x.device)
+    cnt = counts.to(torch.int64)
+    cnt = cnt if cnt.is_contiguous() else cnt.contiguous()
+    check(
+        lib().ttb_gemm_grouped_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), cnt.data_ptr(), scratch.data_ptr(), rows, E, N, K, int(b_mn), x.stride(0), w.stride(1), w.stride(0), N,
+                                    err_word(x.device).data_ptr(), stream_ptr()),
+        "gemm_grouped",
+    )
+    return out
+
+
+class _GroupedMatmul(torch.autograd.Function):
+    """``y[rows of e] = x[rows of e] · w[e]`` with ``w`` ``[E, K, N]``.  Forward and the input gradient are single grouped launches;
+    the weight gradient runs one TN GEMM per expert (its reduction dimension is the ragged one)."""
+
+    @staticmethod
+    def forward(ctx, x, w, counts):
+        ctx.save_for_backward(x, w, counts)
+        return _grouped_gemm(x, w, counts, b_mn=True)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, counts = ctx.saved_tensors
+        if dy.stride(1) != 1 or dy.stride(0) % 8:
+            dy = dy.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = _grouped_gemm(dy, w, counts, b_mn=False)  # per expert dy·w[e]ᵀ: w[e] read as [K_out, N_red] K-major
+        if ctx.needs_input_grad[1]:
+            dw = torch.zeros_like(w)
+            start = 0
+            for e, n in enumerate(counts.tolist()):
+                if n:
+                    gemm(x[start : start + n], dy[start : start + n], a_mn=True, b_mn=True, out=dw[e])
+                start += n
+        return dx, dw, None
+
+
+def grouped_matmul(x: torch.Tensor, w: torch.Tensor, counts: torch.Tensor) -> torch.Tensor:
+    return _GroupedMatmul.apply(x, w, counts)
+
+
 class _MatmulKN(torch.autograd.Function):
     """``y[T, N] = x[T, K] · w[K, N]`` with ``w`` stored reduction-dimension-major (the layout of
     grouped expert weights ``[E, K, N]``): forward reads ``w`` as an MN-major B operand, dgrad is

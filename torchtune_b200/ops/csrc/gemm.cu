@@ -51,9 +51,20 @@ struct alignas(64) TpArgs {
   int world, rank, rows_per_rank;
 };
 
+// Grouped (mixture-of-experts) variant, TP == 3: A is [rows, K] with the rows of expert e contiguous; B is a stack of E
+// weight matrices addressed through a 3-D tensor map.  A device-side table (built by moe_tile_map_kernel from the
+// per-expert row counts, so no host synchronisation is needed) gives, for every m-tile, its expert, its first row and how
+// many of its 128 rows belong to that expert; rows past that count are computed but not stored.
+struct GroupArgs {
+  const int* tile_expert;
+  const int* tile_row0;
+  const int* tile_rows;
+  const int* num_m_tiles;  // device scalar
+};
+
 template <int TP>
 __device__ __forceinline__ int tp_rotate_m(int m_blk, int num_m, const TpArgs* tp) {
-  if (TP == 0) return m_blk;
+  if (TP == 0 || TP == 3) return m_blk;
   const int tiles_per_rank = tp->rows_per_rank / BM;
   const int first = (TP == 1 ? tp->rank : (tp->rank + 1) % tp->world) * tiles_per_rank;
   const int r = m_blk + first;
@@ -82,7 +93,7 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_
 
 template <int BN, bool A_MN, bool B_MN, int TP>
 __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUtensorMap* tmB_ptr, const GemmParams& p,
-                                          const TpArgs* tp) {
+                                          const TpArgs* tp, const GroupArgs* ga = nullptr) {
   using Cfg = GemmCfg<BN>;
   const CUtensorMap& tmA = *tmA_ptr;
   const CUtensorMap& tmB = *tmB_ptr;
@@ -98,7 +109,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_m = (p.M + BM - 1) / BM;
+  const int num_m = TP == 3 ? *ga->num_m_tiles : (p.M + BM - 1) / BM;
   const int num_n = (p.N + BN - 1) / BN;
   const int num_tiles = num_m * num_n;
   const int num_kb = (p.K + BK - 1) / BK;
@@ -143,6 +154,11 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
         mapA = &tp->tmA[src];
         a_row -= src * tp->rows_per_rank;
       }
+      int expert = 0;
+      if (TP == 3) {
+        a_row = ga->tile_row0[m_blk];
+        expert = ga->tile_expert[m_blk];
+      }
       for (int kb = 0; kb < num_kb; ++kb) {
         if (!mbar_wait(&empty[stage], phase ^ 1)) {
           *abort_flag = 1;
@@ -159,7 +175,14 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
           } else {
             tma_load_2d(sa, mapA, &full[stage], kb * BK, a_row);
           }
-          if (B_MN) {
+          if (TP == 3) {
+            if (B_MN) {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j) tma_load_3d(sb + j * 8192, &tmB, &full[stage], n_blk * BN + j * 64, kb * BK, expert);
+            } else {
+              tma_load_3d(sb, &tmB, &full[stage], kb * BK, n_blk * BN, expert);
+            }
+          } else if (B_MN) {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tmB, &full[stage], n_blk * BN + j * 64, kb * BK);
           } else {
@@ -243,7 +266,12 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
         break;
       }
       tc_fence_after();
-      const int row = m_blk * BM + quarter * 32 + lane;
+      int row = m_blk * BM + quarter * 32 + lane;
+      bool row_ok = row < p.M;
+      if (TP == 3) {
+        row = ga->tile_row0[m_blk] + quarter * 32 + lane;
+        row_ok = (quarter * 32 + lane) < ga->tile_rows[m_blk];
+      }
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -251,7 +279,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
         tmem_ld_32x32(taddr + c * 32, r);
         tmem_ld_wait();
         const int col0 = n_blk * BN + c * 32;
-        if (row < p.M && col0 < p.N) {
+        if (row_ok && col0 < p.N) {
           float v[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
@@ -333,6 +361,67 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_tp_kernel(const __grid_constant__ TpArgs tp, const __grid_constant__ CUtensorMap tmA,
                const __grid_constant__ CUtensorMap tmB, GemmParams p) {
   gemm_body<BN, false, B_MN, TP>(&tmA, &tmB, p, &tp);
+}
+
+template <int BN, bool B_MN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_grouped_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p, GroupArgs ga) {
+  gemm_body<BN, false, B_MN, 3>(&tmA, &tmB, p, nullptr, &ga);
+}
+
+// One block: exclusive scan of the per-expert row counts, then one m-tile entry per 128 rows of every expert.
+__global__ void moe_tile_map_kernel(const long long* __restrict__ counts, int num_experts, int max_tiles, int* tile_expert,
+                                    int* tile_row0, int* tile_rows, int* num_m_tiles) {
+  __shared__ long long row0[1025];
+  __shared__ int tile0[1025];
+  if (threadIdx.x == 0) {
+    long long r = 0;
+    int t = 0;
+    for (int e = 0; e < num_experts; ++e) {
+      row0[e] = r;
+      tile0[e] = t;
+      r += counts[e];
+      t += static_cast<int>((counts[e] + BM - 1) / BM);
+    }
+    row0[num_experts] = r;
+    tile0[num_experts] = t;
+    *num_m_tiles = t < max_tiles ? t : max_tiles;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
+    const long long cnt = row0[e + 1] - row0[e];
+    for (int i = 0, t = tile0[e]; t < tile0[e + 1] && t < max_tiles; ++i, ++t) {
+      tile_expert[t] = e;
+      tile_row0[t] = static_cast<int>(row0[e] + static_cast<long long>(i) * BM);
+      const long long left = cnt - static_cast<long long>(i) * BM;
+      tile_rows[t] = static_cast<int>(left < BM ? left : BM);
+    }
+  }
+}
+
+template <int BN, bool B_MN>
+static int launch_gemm_grouped(const void* A, const void* B, const GemmParams& p, int num_experts, long long lda, long long ldb,
+                               long long expert_stride, const GroupArgs& ga, int max_tiles, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  CUtensorMap tmA, tmB;
+  int rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.M, p.K, lda, BM, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != kOk) return rc;
+  if (B_MN)  // per expert [K, N] row-major: dims (N, K, E), box (64, BK, 1)
+    rc = make_tmap_3d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, p.N, p.K, num_experts, ldb * 2, expert_stride * 2, 64, BK, 1, CU_TENSOR_MAP_SWIZZLE_128B);
+  else  // per expert [N, K] row-major: dims (K, N, E), box (BK, BN, 1)
+    rc = make_tmap_3d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, p.K, p.N, num_experts, ldb * 2, expert_stride * 2, BK, BN, 1, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != kOk) return rc;
+  auto kern = gemm_grouped_kernel<BN, B_MN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return kErrDriver;
+    attr_set = true;
+  }
+  const long long tiles = static_cast<long long>(max_tiles) * ((p.N + BN - 1) / BN);
+  const int grid = tiles < sm_count() ? static_cast<int>(tiles) : sm_count();
+  TTB_COUNT_LAUNCH(1);
+  kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tmA, tmB, p, ga);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrDriver;
 }
 
 template <int BN, bool A_MN, bool B_MN>
@@ -528,6 +617,40 @@ extern "C" int ttb_rs_reduce(const void* staging, const void* residual, const vo
       static_cast<const __nv_bfloat16*>(staging), static_cast<const __nv_bfloat16*>(residual), static_cast<const __nv_bfloat16*>(bias),
       static_cast<__nv_bfloat16*>(out), world, rows, N, ld_stage, ld_res, ld_out);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrDriver;
+}
+
+// Grouped GEMM: C[rows, N] = A[rows, K] · op(B[e]) for the rows of each expert e.  `counts` is a device array of E int64 row
+// counts (rows of expert e are contiguous, in expert order).  `tile_scratch` is a device int array of 3·max_tiles + 1 entries
+// with max_tiles = ceil(rows / 128) + E.  b_mn = 0: B[e] is [N, K] row-major; 1: B[e] is [K, N] row-major.
+extern "C" int ttb_gemm_grouped_bf16(const void* A, const void* B, void* C, const void* counts, void* tile_scratch, long long rows,
+                                     int num_experts, int N, int K, int b_mn, long long lda, long long ldb, long long expert_stride,
+                                     long long ldc, int* err, void* stream) {
+  using namespace ttb;
+  if (rows <= 0 || num_experts <= 0 || num_experts > 1024 || N <= 0 || K <= 0) return kErrBadShape;
+  if ((lda & 7) || (ldb & 7) || (ldc & 7) || (N & 7) || (K & 7) || (expert_stride & 7)) return kErrBadShape;
+  const int max_tiles = static_cast<int>((rows + BM - 1) / BM) + num_experts;
+  int* scratch = static_cast<int*>(tile_scratch);
+  GroupArgs ga;
+  ga.tile_expert = scratch;
+  ga.tile_row0 = scratch + max_tiles;
+  ga.tile_rows = scratch + 2 * max_tiles;
+  ga.num_m_tiles = scratch + 3 * max_tiles;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  TTB_COUNT_LAUNCH(1);
+  moe_tile_map_kernel<<<1, 256, 0, s>>>(static_cast<const long long*>(counts), num_experts, max_tiles, scratch, scratch + max_tiles,
+                                         scratch + 2 * max_tiles, scratch + 3 * max_tiles);
+  if (cudaGetLastError() != cudaSuccess) return kErrDriver;
+  GemmParams p;
+  p.M = static_cast<int>(rows), p.N = N, p.K = K, p.C = C, p.ldc = ldc;
+  p.bias = nullptr, p.alpha = 1.f, p.out_fp32 = 0, p.accumulate = 0, p.err = err;
+  if (N > 128)
+    return b_mn ? launch_gemm_grouped<256, true>(A, B, p, num_experts, lda, ldb, expert_stride, ga, max_tiles, s)
+                : launch_gemm_grouped<256, false>(A, B, p, num_experts, lda, ldb, expert_stride, ga, max_tiles, s);
+  if (N > 64)
+    return b_mn ? launch_gemm_grouped<128, true>(A, B, p, num_experts, lda, ldb, expert_stride, ga, max_tiles, s)
+                : launch_gemm_grouped<128, false>(A, B, p, num_experts, lda, ldb, expert_stride, ga, max_tiles, s);
+  return b_mn ? launch_gemm_grouped<64, true>(A, B, p, num_experts, lda, ldb, expert_stride, ga, max_tiles, s)
+              : launch_gemm_grouped<64, false>(A, B, p, num_experts, lda, ldb, expert_stride, ga, max_tiles, s);
 }
 
 // C ABI -------------------------------------------------------------------------------

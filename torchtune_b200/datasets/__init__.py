@@ -13,6 +13,7 @@ from ._builders import (
     wikitext_dataset,
 )
 from ._concat import ConcatDataset
+from ._interleaved import InterleavedDataset
 from ._packed import PackedDataset
 from ._preference import PreferenceDataset, preference_dataset
 from ._sft import SFTDataset, SFTTransform
@@ -27,6 +28,7 @@ from ._synthetic import (
 from ._text_completion import TextCompletionDataset, text_completion_dataset
 
 __all__ = [
+    "InterleavedDataset",
     "multimodal",
     "alpaca_cleaned_dataset",
     "alpaca_dataset",

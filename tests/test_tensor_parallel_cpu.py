@@ -48,8 +48,24 @@ def _worker(rank, world, port, results):
         tpm.sync_replicated_grads()
         total = loss.detach().clone()
         dist.all_reduce(total)
+        # inference path: replicated activations + per-rank KV cache must reproduce the unsharded logits
+        full = llama3_1(**ARCH)
+        fixed_init_(full, std=0.1)
+        with torch.no_grad():
+            want = full(tokens)
+            got = tpm.forward_inference(tokens)
+            tpm.setup_caches(batch_size=2, dtype=torch.float32, decoder_max_seq_len=8)
+            causal = torch.tril(torch.ones(8, 8, dtype=torch.bool))
+            pos = torch.arange(8)
+            steps = [tpm.forward_inference(tokens[:, :5], mask=causal[None, :5].expand(2, -1, -1), input_pos=pos[None, :5].expand(2, -1))]
+            for t in range(5, 8):
+                steps.append(tpm.forward_inference(tokens[:, t : t + 1], mask=causal[None, t : t + 1].expand(2, -1, -1), input_pos=pos[None, t : t + 1].expand(2, -1)))
+            cached = torch.cat(steps, dim=1)
+        infer_err = (got - want).abs().max().item()
+        cache_err = (cached - want).abs().max().item()
         l0 = tpm.layers[0]
         results[rank] = dict(
+            infer_err=infer_err, cache_err=cache_err,
             loss=total.item(),
             wqkv_grad=l0.attn.wqkv.grad.clone(), wo_grad=l0.attn.wo.grad.clone(), w13_grad=l0.mlp.w13.grad.clone(), w2_grad=l0.mlp.w2.grad.clone(),
             emb_grad=tpm.tok_embeddings.weight.grad.clone(), norm_grad=l0.sa_norm.scale.grad.clone(), out_grad=tpm.output.weight.grad.clone(),
@@ -69,6 +85,7 @@ def test_tp_decoder_matches_single_process():
     for rank in range(world):
         r = results[rank]
         assert abs(r["loss"] - ref_loss) < 1e-3 * abs(ref_loss)
+        assert r["infer_err"] < 1e-4 and r["cache_err"] < 1e-4
         q = ref_grads["layers.0.attn.q_proj.weight"][rank * heads * hd : (rank + 1) * heads * hd]
         k = ref_grads["layers.0.attn.k_proj.weight"][rank * kv * hd : (rank + 1) * kv * hd]
         v = ref_grads["layers.0.attn.v_proj.weight"][rank * kv * hd : (rank + 1) * kv * hd]

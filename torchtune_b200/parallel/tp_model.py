@@ -76,6 +76,29 @@ class TPAttention(nn.Module):
         out = ops.attention(q.contiguous(), k.contiguous(), v.contiguous(), _as_mask(mask, default_causal=self.is_causal and mask is None), scale=self.scale, softcap=self.softcap)
         return row_parallel_linear(out.reshape(b * s, nq), self.wo, self.tp, residual)
 
+    # inference (replicated activations, local-head KV cache) -------------------------------
+    def setup_cache(self, batch_size: int, dtype: torch.dtype, max_seq_len: int) -> None:
+        from ..modules import KVCache
+
+        self.kv_cache = KVCache(batch_size=batch_size, max_seq_len=max_seq_len, num_kv_heads=self.kv_heads, head_dim=self.head_dim, dtype=dtype)
+
+    def forward_replicated(self, hn: torch.Tensor, mask, input_pos) -> torch.Tensor:
+        """``hn``: ``[b, s, d]`` identical on every rank → this rank's partial ``[b, s, d]`` of the attention output projection
+        (the caller sums the partials over the group)."""
+        b, s, _ = hn.shape
+        hd = self.head_dim
+        qkv = ops.linear(hn, self.wqkv)
+        nq, nk = self.heads * hd, self.kv_heads * hd
+        q = self._pos(qkv[..., :nq].reshape(b, s, self.heads, hd), self.q_norm, input_pos)
+        k = self._pos(qkv[..., nq : nq + nk].reshape(b, s, self.kv_heads, hd), self.k_norm, input_pos)
+        v = qkv[..., nq + nk :].reshape(b, s, self.kv_heads, hd)
+        cache = getattr(self, "kv_cache", None)
+        if cache is not None:
+            k, v = cache.update(k.contiguous(), v.contiguous())
+        attn_mask = _as_mask(mask, default_causal=self.is_causal and mask is None and cache is None)
+        out = ops.attention(q.contiguous(), k.contiguous(), v.contiguous(), attn_mask, scale=self.scale, softcap=self.softcap)
+        return ops.linear(out.reshape(b, s, nq), self.wo)
+
     # checkpoint layout ----------------------------------------------------------------------
     def gather_full(self, prefix: str) -> Dict[str, torch.Tensor]:
         tp, hd = self.tp, self.head_dim
@@ -110,6 +133,11 @@ class TPMLP(nn.Module):
         gu = column_parallel_linear(hn, self.w13, self.tp)
         h = ops.swiglu(gu[:, : self.per].contiguous(), gu[:, self.per :].contiguous())
         return row_parallel_linear(h, self.w2, self.tp, residual)
+
+    def forward_replicated(self, hn: torch.Tensor) -> torch.Tensor:
+        gu = ops.linear(hn, self.w13)
+        h = ops.swiglu(gu[..., : self.per].contiguous(), gu[..., self.per :].contiguous())
+        return ops.linear(h, self.w2)
 
     def gather_full(self, prefix: str) -> Dict[str, torch.Tensor]:
         tp = self.tp
@@ -177,6 +205,35 @@ class TPDecoder(nn.Module):
                 h = layer(h, b, s, mask, input_pos)
         h = self.norm(h).unsqueeze(0)
         return h if self.skip_output_layer else self.output(h).float()
+
+    # inference ------------------------------------------------------------------------------
+    def setup_caches(self, batch_size: int, dtype: torch.dtype, *, decoder_max_seq_len: Optional[int] = None, **_: Any) -> None:
+        n = decoder_max_seq_len or self.max_seq_len
+        for layer in self.layers:
+            layer.attn.setup_cache(batch_size, dtype, n)
+
+    def caches_are_setup(self) -> bool:
+        return getattr(self.layers[0].attn, "kv_cache", None) is not None
+
+    def caches_are_enabled(self) -> bool:
+        return self.caches_are_setup()
+
+    def reset_caches(self) -> None:
+        for layer in self.layers:
+            if getattr(layer.attn, "kv_cache", None) is not None:
+                layer.attn.kv_cache.reset()
+
+    @torch.no_grad()
+    def forward_inference(self, tokens: torch.Tensor, *, mask=None, input_pos: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Decoding-time forward: activations are replicated (any batch / sequence length, including one token), attention uses
+        this rank's heads and KV cache, and the two row-parallel projections of every layer are followed by an all-reduce.
+        Returns fp32 logits ``[b, s, vocab]``, identical on every rank."""
+        h = self.tok_embeddings(tokens)
+        for layer in self.layers:
+            m = layer.mask_mod(mask, tokens.shape[0], tokens.shape[1]) if layer.mask_mod is not None else mask
+            h = h + self.tp.all_reduce_(layer.attn.forward_replicated(layer.sa_norm(h), m, input_pos))
+            h = h + self.tp.all_reduce_(layer.mlp.forward_replicated(layer.mlp_norm(h)))
+        return self.output(self.norm(h)).float()
 
     def sync_replicated_grads(self) -> None:
         """Sum the gradients of replicated parameters over the group (one collective on a flat buffer)."""

@@ -202,3 +202,32 @@ def test_llama4_tokenizer_image_grid(tmp_path):
     assert one == [tok.image_start, tok.image_id, tok.patch_id, tok.patch_id, tok.patch_id, tok.image_end]
     grid = tok._image_tokens(1, torch.tensor([2, 2]))
     assert grid == [tok.image_start, tok.patch_id, tok.tile_x_separator, tok.patch_id, tok.tile_y_separator, tok.patch_id, tok.tile_x_separator, tok.patch_id, tok.tile_y_separator, tok.image_id, tok.patch_id, tok.image_end]
+
+
+def test_export_modules_match_training_modules():
+    from torchtune_b200.models.llama2 import llama2
+    from torchtune_b200.modules._export import replace_mha_with_inference_mha, replace_tile_positional_embedding, replace_tiled_token_positional_embedding
+
+    torch.manual_seed(0)
+    model = llama2(vocab_size=64, num_layers=2, num_heads=4, num_kv_heads=2, embed_dim=32, max_seq_len=32, intermediate_dim=48).eval()
+    tokens = torch.randint(0, 64, (2, 9))
+    want = model(tokens)
+    keys = set(model.state_dict())
+    replace_mha_with_inference_mha(model)
+    assert set(model.state_dict()) == keys
+    torch.testing.assert_close(model(tokens), want, rtol=1e-5, atol=1e-5)
+    exported = torch.export.export(model.layers[0].attn, (torch.randn(2, 9, 32), torch.randn(2, 9, 32)))
+    assert exported is not None
+
+    enc = clip_vision_encoder(tile_size=40, patch_size=10, embed_dim=32, num_layers=1, num_heads=4, max_num_tiles=4).eval()
+    with torch.no_grad():
+        enc.token_pos_embedding.gate.fill_(0.7)
+        enc.pre_tile_pos_embed.gate.fill_(0.3)
+        enc.post_tile_pos_embed.gate.fill_(-0.4)
+    images = torch.randn(2, 1, 4, 3, 40, 40)
+    ar = torch.tensor([[[2, 2]], [[1, 3]]])
+    want, _ = enc(images, ar)
+    replace_tile_positional_embedding(enc)
+    replace_tiled_token_positional_embedding(enc)
+    got, _ = enc(images, ar)
+    torch.testing.assert_close(got, want, rtol=1e-5, atol=1e-5)

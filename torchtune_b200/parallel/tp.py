@@ -108,7 +108,7 @@ class TensorParallelContext:
         w = weight if weight.is_contiguous() else weight.contiguous()
         check(
             lib().ttb_gemm_ag_bf16(buf.pointer_array(), w.data_ptr(), out.data_ptr(), self.world, self.rank, rows, n, k, int(b_mn), k, w.stride(0), n,
-                                   None if bias is None else bias.data_ptr(), err_word(self.device), stream_ptr()),
+                                   None if bias is None else bias.data_ptr(), err_word(self.device).data_ptr(), stream_ptr()),
             "gemm_ag",
         )
         return out
@@ -133,7 +133,7 @@ class TensorParallelContext:
         xc = x if x.is_contiguous() else x.contiguous()
         w = weight if weight.is_contiguous() else weight.contiguous()
         L = lib()
-        check(L.ttb_gemm_rs_bf16(xc.data_ptr(), w.data_ptr(), buf.pointer_array(), self.world, self.rank, rows, n, k, int(b_mn), k, w.stride(0), n, err_word(self.device), stream_ptr()), "gemm_rs")
+        check(L.ttb_gemm_rs_bf16(xc.data_ptr(), w.data_ptr(), buf.pointer_array(), self.world, self.rank, rows, n, k, int(b_mn), k, w.stride(0), n, err_word(self.device).data_ptr(), stream_ptr()), "gemm_rs")
         self.barrier()  # all partial tiles have landed in every owner's staging buffer
         out = torch.empty(rows, n, dtype=_BF16, device=self.device)
         res = None if residual is None else (residual if residual.is_contiguous() else residual.contiguous())

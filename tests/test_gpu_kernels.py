@@ -393,13 +393,15 @@ def _tp_lib():
     return L, ctypes, err_word, stream_ptr
 
 
-@pytest.mark.parametrize("world", [1, 2, 4, 8])
+@pytest.mark.parametrize("world,rows,K,N", [(1, 256, 320, 192), (2, 256, 320, 192), (4, 256, 320, 192), (8, 256, 320, 192), (2, 1024, 512, 4096), (4, 512, 256, 2560)])
 @pytest.mark.parametrize("b_mn", [False, True])
-def test_gemm_all_gather_fused_emulated_ranks(world, b_mn):
+def test_gemm_all_gather_fused_emulated_ranks(world, rows, K, N, b_mn):
     """Every emulated rank runs the all-gather → GEMM kernel over the same set of shard buffers (here all on one
-    device; on a real group they are peer mappings).  Launches are sequential and never wait on each other."""
+    device; on a real group they are peer mappings).  Launches are sequential and never wait on each other.  The two
+    large shapes give every persistent CTA several tiles (accumulator double-buffering and the piece counters at work)."""
+    from torchtune_b200.ops._lib import check_device_errors
+
     L, ctypes, err_word, stream_ptr = _tp_lib()
-    rows, K, N = 256, 320, 192
     shards = [_rand(rows, K, scale=0.5, seed=10 + r) for r in range(world)]
     ptrs = (ctypes.c_void_p * world)(*[s.data_ptr() for s in shards])
     full = torch.cat(shards).float()
@@ -407,10 +409,22 @@ def test_gemm_all_gather_fused_emulated_ranks(world, b_mn):
         w = _rand(K, N, scale=0.1, seed=50 + rank) if b_mn else _rand(N, K, scale=0.1, seed=50 + rank)
         bias = _rand(N, scale=0.1, seed=70 + rank)
         out = torch.empty(world * rows, N, dtype=torch.bfloat16, device="cuda")
-        rc = L.ttb_gemm_ag_bf16(ptrs, w.data_ptr(), out.data_ptr(), world, rank, rows, N, K, int(b_mn), K, w.stride(0), N, bias.data_ptr(), err_word(out.device).data_ptr(), stream_ptr())
+        gathered = torch.full((world * rows, K), float("nan"), dtype=torch.bfloat16, device="cuda")
+        sync = torch.full((1 + world * rows // 128,), 7, dtype=torch.int32, device="cuda")  # the entry point zeroes it
+        gather_own = rank % 2
+        rc = L.ttb_gemm_ag_bf16(ptrs, w.data_ptr(), out.data_ptr(), gathered.data_ptr(), sync.data_ptr(), gather_own, world, rank, rows, N, K, int(b_mn),
+                                w.stride(0), N, bias.data_ptr(), err_word(out.device).data_ptr(), stream_ptr())
         assert rc == 0
         want = (full @ w.float() if b_mn else full @ w.float().t()) + bias.float()
         _close(out, want, 2e-2, 2e-2, f"ag_gemm rank {rank}")
+        # the gathered activation is a by-product: remote rows always, own rows on request
+        own = slice(rank * rows, (rank + 1) * rows)
+        mask = torch.ones(world * rows, dtype=torch.bool, device="cuda")
+        if not gather_own:
+            mask[own] = False
+            assert torch.isnan(gathered[own].float()).all()
+        assert torch.equal(gathered[mask].float(), full[mask])
+    check_device_errors()
 
 
 @pytest.mark.parametrize("world", [1, 2, 4, 8])
@@ -457,3 +471,48 @@ def test_tp_context_single_rank_matches_plain_linear():
         _close(w1.grad, w1f.grad, 5e-2, 2e-1, "tp dw1")
     finally:
         tp.close()
+
+
+# ----------------------------------------------------------------------------- MoE index kernels, embedding
+@pytest.mark.parametrize("n,E", [(1, 4), (700, 16), (5000, 128), (8192, 8)])
+def test_moe_route_sort_matches_stable_argsort(n, E):
+    from torchtune_b200.ops._cuda import moe_route_sort
+
+    g = torch.Generator(device="cuda").manual_seed(n)
+    ids = torch.randint(0, E, (n,), generator=g, device="cuda")
+    counts, order = moe_route_sort(ids, E)
+    assert torch.equal(counts, torch.bincount(ids, minlength=E))
+    assert torch.equal(order, torch.argsort(ids, stable=True))
+
+
+@pytest.mark.parametrize("R,E,align", [(1, 4, 16), (8, 2, 16), (4, 16, 128), (2, 3, 8)])
+def test_moe_permute_indices_matches_loop_oracle(R, E, align):
+    from torchtune_b200.modules.moe.indices import fill_indices_cpu, generate_permute_indices
+
+    g = torch.Generator().manual_seed(R * 100 + E)
+    counts = torch.randint(0, 40, (R * E,), generator=g)
+    counts[0] = 0
+    max_len = int(counts.sum()) + E * align
+    got, sizes, offs = generate_permute_indices(counts.cuda(), E, R, max_len, align)
+    want, wsizes, woffs = generate_permute_indices(counts, E, R, max_len, align, use_cpu=True)
+    assert torch.equal(got.cpu(), want) and torch.equal(sizes.cpu(), wsizes) and torch.equal(offs.cpu(), woffs)
+    start = (counts.cumsum(0) - counts)
+    loop = fill_indices_cpu(counts, start, woffs - wsizes, E, R, max_len)
+    assert torch.equal(got.cpu(), loop)
+
+
+def test_embedding_matches_reference_with_repeated_tokens():
+    g = torch.Generator(device="cuda").manual_seed(3)
+    V, D = 1000, 4096 + 64
+    table = (torch.randn(V, D, generator=g, device="cuda") * 0.1).bfloat16().requires_grad_()
+    ids = torch.randint(0, V, (4, 333), generator=g, device="cuda")
+    ids[:, :50] = 7  # a frequent token: 200 rows summed into one table row
+    out = ops.embedding(ids, table)
+    dy = (torch.randn(4, 333, D, generator=g, device="cuda") * 0.1).bfloat16()
+    out.backward(dy)
+    tf = table.detach().float().requires_grad_()
+    ref = torch.nn.functional.embedding(ids, tf)
+    ref.backward(dy.float())
+    assert torch.equal(out.float(), ref)
+    rel = (table.grad.float() - tf.grad).norm() / tf.grad.norm()
+    assert rel < 4e-3

@@ -7,6 +7,7 @@ from typing import Any, Dict, List, Optional, Union
 import torch
 from torch import nn
 
+from ... import ops
 from ..peft import set_trainable_params
 from ._layers import get_fusion_params
 
@@ -94,7 +95,7 @@ class EarlyFusionModel(_FusionBase):
         special = torch.tensor(list(self.encoder_tokens.values()), device=tokens.device)
         is_text = ~torch.isin(tokens, special)
         # placeholders are embedded with id 0 and then overwritten
-        embeds = self.decoder.tok_embeddings(torch.where(is_text, tokens, torch.zeros_like(tokens)))
+        embeds = ops.embed_tokens(self.decoder.tok_embeddings, torch.where(is_text, tokens, torch.zeros_like(tokens)))
         for name, inp in encoder_input.items():
             enc = self.encoders[name](**inp).reshape(-1, embeds.shape[-1])
             slot = (tokens == self.encoder_tokens[name]).unsqueeze(-1)

@@ -5,8 +5,8 @@ After the dispatch all-to-all a rank holds, for each source rank ``r`` and each 
 experts ``e``, a run of ``tokens_per_expert_group[r·E_local + e]`` rows, laid out rank-major.
 The grouped GEMM wants them expert-major with every expert's block starting at a multiple of
 ``alignment``.  ``generate_permute_indices`` returns the gather indices (``-1`` = padding row),
-the padded group sizes and their offsets.  The computation is a segmented prefix sum — done
-here with tensor ops on whatever device the counts live on (no host round-trip).
+the padded group sizes and their offsets.  The computation is a segmented prefix sum: one
+kernel on CUDA (``csrc/moe.cu``, every output slot pulls its source index), tensor ops elsewhere.
 """
 from __future__ import annotations
 
@@ -16,6 +16,13 @@ import torch
 
 
 def generate_permute_indices(tokens_per_expert_group: torch.Tensor, experts_per_rank: int, num_ranks: int, max_len: int, alignment: int, use_cpu: bool = False) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    if tokens_per_expert_group.is_cuda and not use_cpu and num_ranks * experts_per_rank <= 4096:
+        from ...ops import cuda_ops_enabled
+
+        if cuda_ops_enabled(tokens_per_expert_group):
+            from ...ops._cuda import moe_permute_indices
+
+            return moe_permute_indices(tokens_per_expert_group, experts_per_rank, num_ranks, max_len, alignment)
     dev = torch.device("cpu") if use_cpu else tokens_per_expert_group.device
     counts = tokens_per_expert_group.to(dev, torch.int64).view(num_ranks, experts_per_rank)
     # where each (rank, expert) run starts in the rank-major input

@@ -6,6 +6,8 @@ from typing import Optional, Tuple
 import torch
 from torch import nn
 
+from ... import ops
+
 
 class TokenChoiceTopKRouter(nn.Module):
     """Every token picks its ``experts_per_token`` highest-scoring experts (sigmoid scores,
@@ -21,8 +23,13 @@ class TokenChoiceTopKRouter(nn.Module):
         top_scores, selected = torch.topk(scores, k=self.experts_per_token, dim=1)
         self.selected_experts_indices = selected
         flat = selected.reshape(-1)
-        num_tokens_per_expert = torch.bincount(flat, minlength=self.num_experts)
-        order = torch.argsort(flat, stable=True)
+        if ops.cuda_ops_enabled(flat) and self.num_experts <= 256:
+            from ...ops._cuda import moe_route_sort
+
+            num_tokens_per_expert, order = moe_route_sort(flat, self.num_experts)  # one launch: histogram + stable sort
+        else:
+            num_tokens_per_expert = torch.bincount(flat, minlength=self.num_experts)
+            order = torch.argsort(flat, stable=True)
         return top_scores.reshape(-1)[order], order // self.experts_per_token, num_tokens_per_expert
 
 

@@ -7,6 +7,7 @@ from typing import Callable, List, Optional, Union
 import torch
 from torch import nn
 
+from .. import ops
 from ..ops.mask import AttentionMask
 from .attention import MaskLike, MultiHeadAttention
 
@@ -249,7 +250,7 @@ class TransformerDecoder(nn.Module):
             raise ValueError("Exactly one of `tokens` or `input_embeds` must be provided.")
         seq_len = tokens.shape[1] if input_embeds is None else input_embeds.shape[1]
         self._validate_inputs(seq_len, mask=mask, encoder_input=encoder_input, encoder_mask=encoder_mask, input_pos=input_pos)
-        h = self.tok_embeddings(tokens) if input_embeds is None else input_embeds
+        h = ops.embed_tokens(self.tok_embeddings, tokens) if input_embeds is None else input_embeds
         hidden = []
         for i, layer in enumerate(self.layers):
             if i in self.output_hidden_states:

@@ -27,6 +27,7 @@ __all__ = [
     "linear_cross_entropy",
     "token_logprobs",
     "embedding",
+    "embed_tokens",
     "AttentionMask",
     "reference",
     "cuda_ops_enabled",
@@ -189,5 +190,17 @@ def token_logprobs(
     return reference.token_logprobs(hidden, weight, labels, ignore_index, num_chunks)
 
 
-def embedding(tokens: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
-    return F.embedding(tokens, weight)
+def embedding(tokens: torch.Tensor, weight: torch.Tensor, padding_idx: Optional[int] = None) -> torch.Tensor:
+    """``weight[tokens]``; bf16 CUDA tables use the gather kernel and the sorted, fp32-accumulating gradient kernel."""
+    if _native(weight) and tokens.is_cuda and weight.dim() == 2 and weight.shape[1] % 8 == 0 and weight.is_contiguous():
+        from . import _cuda
+
+        return _cuda.embedding(tokens, weight, padding_idx)
+    return F.embedding(tokens, weight, padding_idx)
+
+
+def embed_tokens(module: torch.nn.Module, tokens: torch.Tensor) -> torch.Tensor:
+    """Calls an embedding module; a plain ``nn.Embedding`` (no max-norm, dense gradient) is routed through :func:`embedding`."""
+    if type(module) is torch.nn.Embedding and module.max_norm is None and not module.sparse and not module.scale_grad_by_freq:
+        return embedding(tokens, module.weight, module.padding_idx)
+    return module(tokens)

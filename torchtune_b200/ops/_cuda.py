@@ -296,6 +296,69 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     return _Linear.apply(x, weight, bias)
 
 
+# ======================================================================= embedding
+class _Embedding(torch.autograd.Function):
+    """Row gather; the gradient sorts the ids and sums every run of equal ids in fp32 (deterministic, no atomics).
+    A table that owns a window of a flat gradient buffer receives its gradient there and autograd gets no tensor."""
+
+    @staticmethod
+    def forward(ctx, ids, table, padding_idx):
+        flat = ids.reshape(-1)
+        if flat.dtype != torch.int64:
+            flat = flat.long()
+        flat = flat.contiguous()
+        n, (vocab, dim) = flat.numel(), table.shape
+        out = torch.empty(n, dim, dtype=table.dtype, device=table.device)
+        check(lib().ttb_embedding_fwd(flat.data_ptr(), table.data_ptr(), out.data_ptr(), n, dim, vocab, stream_ptr()), "embedding_fwd")
+        ctx.save_for_backward(flat, table)
+        ctx.padding_idx = -1 if padding_idx is None else int(padding_idx)
+        return out.view(*ids.shape, dim)
+
+    @staticmethod
+    def backward(ctx, dy):
+        flat, table = ctx.saved_tensors
+        vocab, dim = table.shape
+        dy2 = dy.reshape(-1, dim)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        sorted_ids, order = torch.sort(flat, stable=True)
+        owner = grad_window_owner(table)
+        if owner is None:
+            dtable = torch.zeros_like(table)
+        else:
+            dtable = owner._grad_buffer
+            join_wgrad_stream()  # a tied output projection writes the same window from the side stream
+            if not owner._grad_written:
+                dtable.zero_()
+            owner._grad_written = True
+        check(lib().ttb_embedding_bwd(sorted_ids.data_ptr(), order.data_ptr(), dy2.data_ptr(), dtable.data_ptr(), flat.numel(), dim, vocab, ctx.padding_idx, stream_ptr()), "embedding_bwd")
+        return None, (dtable if owner is None else None), None
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, padding_idx: Optional[int] = None) -> torch.Tensor:
+    return _Embedding.apply(ids, table, padding_idx)
+
+
+def moe_route_sort(expert_ids: torch.Tensor, num_experts: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Stable counting sort of ``expert_ids`` (int64, flat): ``(counts[E], order[n])`` with ``expert_ids[order]`` ascending."""
+    ids = expert_ids.reshape(-1).contiguous()
+    n = ids.numel()
+    counts = torch.empty(num_experts, dtype=torch.int64, device=ids.device)
+    order = torch.empty(n, dtype=torch.int64, device=ids.device)
+    check(lib().ttb_moe_route_sort(ids.data_ptr(), n, num_experts, counts.data_ptr(), order.data_ptr(), stream_ptr()), "moe_route_sort")
+    return counts, order
+
+
+def moe_permute_indices(tokens_per_expert_group: torch.Tensor, experts_per_rank: int, num_ranks: int, max_len: int, alignment: int):
+    counts = tokens_per_expert_group.reshape(-1).to(torch.int64).contiguous()
+    dev = counts.device
+    permuted = torch.empty(max_len, dtype=torch.int32, device=dev)
+    m_sizes = torch.empty(experts_per_rank, dtype=torch.int32, device=dev)
+    m_offsets = torch.empty(experts_per_rank, dtype=torch.int32, device=dev)
+    check(lib().ttb_moe_permute_indices(counts.data_ptr(), experts_per_rank, num_ranks, max_len, alignment, permuted.data_ptr(), m_sizes.data_ptr(), m_offsets.data_ptr(), stream_ptr()), "moe_permute_indices")
+    return permuted, m_sizes, m_offsets
+
+
 # ======================================================================= RMSNorm
 class _RMSNorm(torch.autograd.Function):
     @staticmethod

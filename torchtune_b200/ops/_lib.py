@@ -58,6 +58,12 @@ def _declare(L: ctypes.CDLL) -> None:
     L.ttb_gemm_grouped_bf16.restype = i32
     L.ttb_nf4_dequant.argtypes = [vp, vp, vp, vp, vp, i64, i32, i32, vp]
     L.ttb_nf4_dequant.restype = i32
+    L.ttb_moe_route_sort.argtypes = [vp, i32, i32, vp, vp, vp]
+    L.ttb_moe_permute_indices.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp, vp]
+    L.ttb_embedding_fwd.argtypes = [vp, vp, vp, i64, i32, i64, vp]
+    L.ttb_embedding_bwd.argtypes = [vp, vp, vp, vp, i64, i32, i64, i64, vp]
+    for fn in (L.ttb_moe_route_sort, L.ttb_moe_permute_indices, L.ttb_embedding_fwd, L.ttb_embedding_bwd):
+        fn.restype = i32
     L.ttb_ensure_device.restype = i32
     L.ttb_launch_count.restype = i64
     L.ttb_attn_bwd.restype = i32

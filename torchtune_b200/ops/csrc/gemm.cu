@@ -39,17 +39,42 @@ struct GemmParams {
 
 // Tensor-parallel variants of the same kernel (TP template parameter of gemm_body):
 //   1  all-gather → GEMM: the M dimension is the concatenation over ranks of per-rank activation shards that live
-//      in peer-visible buffers; each m-tile is loaded by TMA straight from the shard of the rank that owns those rows
-//      (plain, non-multicast tensor loads; the own shard first), so no gathered copy of A is ever written.
+//      in peer-visible buffers.  Peer memory is not cached in this GPU's L2, so a remote tile read by every n-tile
+//      that needs it would cross NVLink N/BN times.  Instead four extra "copier" warps per CTA pull the remote shards
+//      into a local gathered buffer, 16 rows at a time in the order the tiles are consumed, and count finished
+//      pieces per m-tile; the TMA producer starts with the tiles of the own shard (read in place) and waits (bounded)
+//      on a remote tile's counter before loading it from the local copy.  Every byte crosses NVLink once and the
+//      transfer overlaps the MMAs of earlier tiles; the gathered activation is a by-product that the weight-gradient
+//      GEMM of the backward pass reuses.
 //   2  GEMM → reduce-scatter: every output m-tile is stored straight into the staging slot [this rank] of the rank
 //      that owns those rows; the owner later sums its `world` slots (ttb_rs_reduce).  Stores to peers start with
 //      the next rank so the ranks do not all write to the same GPU at the same time.
 static constexpr int kMaxTpWorld = 8;
+static constexpr int kTpAgThreads = 384;  // 8 GEMM warps + 4 copier warps
+static constexpr int kCopyPieces = 8;     // pieces per 128-row m-tile
 struct alignas(64) TpArgs {
-  CUtensorMap tmA[kMaxTpWorld];  // TP 1: per-rank A shard [rows_per_rank, K]
-  void* C[kMaxTpWorld];          // TP 2: per-rank staging buffer [world, rows_per_rank, ldc]
-  int world, rank, rows_per_rank;
+  CUtensorMap tmA[kMaxTpWorld];     // TP 1: per-rank A shard [rows_per_rank, K] (only the own one is loaded from)
+  const void* A_src[kMaxTpWorld];   // TP 1: the same shards as raw pointers for the copier warps (row pitch K)
+  void* gathered;                   // TP 1: local [world * rows_per_rank, K] buffer the copiers fill
+  int* sync;                        // TP 1: [0] piece ticket, [1 + m] finished pieces of m-tile m (zeroed per launch)
+  void* C[kMaxTpWorld];             // TP 2: per-rank staging buffer [world, rows_per_rank, ldc]
+  int world, rank, rows_per_rank, gather_own;
 };
+
+__device__ __forceinline__ bool wait_count(const int* ctr, int target) {
+  auto load = [&]() {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(ctr) : "memory");
+    return v;
+  };
+  if (load() >= target) return true;
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (load() < target) {
+    if ((++spins & 0xff) == 0 && clock64() - t0 > kWaitBudgetCycles) return false;
+  }
+  return true;
+}
 
 // Grouped (mixture-of-experts) variant, TP == 3: A is [rows, K] with the rows of expert e contiguous; B is a stack of E
 // weight matrices addressed through a 3-D tensor map.  A device-side table (built by moe_tile_map_kernel from the
@@ -106,6 +131,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
   uint64_t* tempty = tfull + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* piece_slot = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -151,8 +177,17 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
       int a_row = m_blk * BM;
       if (TP == 1) {
         const int src = a_row / tp->rows_per_rank;
-        mapA = &tp->tmA[src];
-        a_row -= src * tp->rows_per_rank;
+        if (src == tp->rank) {  // own shard: read in place
+          mapA = &tp->tmA[src];
+          a_row -= src * tp->rows_per_rank;
+        } else {  // remote rows: wait until the copier warps (of any CTA) have landed this m-tile in the local buffer
+          if (!wait_count(tp->sync + 1 + m_blk, kCopyPieces)) {
+            *abort_flag = 1;
+            if (lane == 0) atomicExch(p.err, 105);
+            break;
+          }
+          asm volatile("fence.proxy.async;" ::: "memory");  // generic-proxy stores → async-proxy (TMA) reads
+        }
       }
       int expert = 0;
       if (TP == 3) {
@@ -251,7 +286,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
         acc_phase ^= 1;
       }
     }
-  } else if (warp >= 4) {
+  } else if (warp >= 4 && warp < 8) {
     // ------------------------------------------------------------------ epilogue
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
     int acc = 0;
@@ -344,6 +379,44 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
     }
   }
 
+  if (TP == 1 && warp >= 8) {
+    // ------------------------------------------------------------------ copier warps (all-gather over peer memory)
+    const int ctid = threadIdx.x - 256;
+    const int tiles_per_rank = tp->rows_per_rank / BM;
+    const int copy_tiles = tp->gather_own ? num_m : num_m - tiles_per_rank;
+    const int total = copy_tiles * kCopyPieces;
+    const long long row_vecs = p.K / 8;  // 16-byte vectors per row
+    const long long piece_vecs = (BM / kCopyPieces) * row_vecs;
+    while (true) {
+      if (ctid == 0) *piece_slot = atomicAdd(tp->sync, 1);  // pieces are claimed in consumption order by whichever CTA is free
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const int pc = *piece_slot;
+      if (pc >= total) break;
+      int i = tiles_per_rank + pc / kCopyPieces;  // position in the rotated order; the own tiles (if copied) come last
+      if (i >= num_m) i -= num_m;
+      const int m_blk = tp_rotate_m<1>(i, num_m, tp);
+      const long long row0 = static_cast<long long>(m_blk) * BM + (pc % kCopyPieces) * (BM / kCopyPieces);
+      const int src = static_cast<int>(row0 / tp->rows_per_rank);
+      const uint4* s = reinterpret_cast<const uint4*>(tp->A_src[src]) + (row0 - static_cast<long long>(src) * tp->rows_per_rank) * row_vecs;
+      uint4* d = reinterpret_cast<uint4*>(tp->gathered) + row0 * row_vecs;
+      for (long long v = ctid; v < piece_vecs; v += 128 * 4) {
+        uint4 r[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (v + j * 128 < piece_vecs) r[j] = __ldcg(s + v + j * 128);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (v + j * 128 < piece_vecs) d[v + j * 128] = r[j];
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (ctid == 0) {
+        __threadfence();
+        atomicAdd(tp->sync + 1 + m_blk, 1);
+      }
+    }
+  }
+
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -357,7 +430,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 }
 
 template <int BN, bool B_MN, int TP>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(TP == 1 ? kTpAgThreads : kThreads, 1)
 gemm_tp_kernel(const __grid_constant__ TpArgs tp, const __grid_constant__ CUtensorMap tmA,
                const __grid_constant__ CUtensorMap tmB, GemmParams p) {
   gemm_body<BN, false, B_MN, TP>(&tmA, &tmB, p, &tp);
@@ -483,9 +556,8 @@ static int launch_gemm_tp(const TpArgs& tp, const void* A, const void* B, const 
                           cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
   CUtensorMap tmA, tmB;
-  // TP 1: `A` is this rank's shard (only prefetched); TP 2: `A` is the local [M, K] operand.
-  const int a_rows = TP == 1 ? tp.rows_per_rank : p.M;
-  int rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a_rows, p.K, lda, BM, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  // TP 1: `A` is the local gathered [M, K] buffer (row pitch K) that the copier warps fill; TP 2: the local [M, K] operand.
+  int rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.M, p.K, lda, BM, BK, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != kOk) return rc;
   if (B_MN)
     rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.K, p.N, ldb, BK, 64, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -501,7 +573,7 @@ static int launch_gemm_tp(const TpArgs& tp, const void* A, const void* B, const 
   const int num_tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   const int grid = num_tiles < sm_count() ? num_tiles : sm_count();
   TTB_COUNT_LAUNCH(1);
-  kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tp, tmA, tmB, p);
+  kern<<<grid, TP == 1 ? kTpAgThreads : kThreads, Cfg::kSmemBytes, stream>>>(tp, tmA, tmB, p);
   if (cudaGetLastError() != cudaSuccess) return kErrDriver;
   return kOk;
 }
@@ -562,30 +634,39 @@ rs_reduce_kernel(const __nv_bfloat16* __restrict__ staging, const __nv_bfloat16*
 }  // namespace ttb
 
 // Tensor-parallel entry points -----------------------------------------------------------
-// ttb_gemm_ag_bf16: C[world*rows_per_rank, N] = concat_r(A_ranks[r])[., K] * op(B); A_ranks[r] may be peer memory
-//                   (read by plain TMA loads); C, B local.
+// ttb_gemm_ag_bf16: C[world*rows_per_rank, N] = concat_r(A_ranks[r])[., K] * op(B); A_ranks[r] (contiguous [rows_per_rank, K])
+//                   may be peer memory, read once by the copier warps' plain loads; `gathered` is a local contiguous
+//                   [world*rows_per_rank, K] buffer that receives the remote rows (and the own rows when gather_own != 0);
+//                   `sync` is a local int array of 1 + world*rows_per_rank/128 entries (zeroed here); C, B local.
 // ttb_gemm_rs_bf16: partial = A[world*rows_per_rank, K] * op(B); rows of owner o are stored to
 //                   C_ranks[o][rank][rows_per_rank][ldc] (C_ranks[o] may be peer memory, written by plain stores).
 // rows_per_rank must be a multiple of 128 (one m-tile never spans two ranks).
-extern "C" int ttb_gemm_ag_bf16(const void* const* A_ranks, const void* B, void* C, int world, int rank, int rows_per_rank,
-                                int N, int K, int b_mn, long long lda, long long ldb, long long ldc, const void* bias, int* err,
-                                void* stream) {
+extern "C" int ttb_gemm_ag_bf16(const void* const* A_ranks, const void* B, void* C, void* gathered, int* sync, int gather_own,
+                                int world, int rank, int rows_per_rank, int N, int K, int b_mn, long long ldb, long long ldc,
+                                const void* bias, int* err, void* stream) {
   using namespace ttb;
   if (world < 1 || world > kMaxTpWorld || rank < 0 || rank >= world) return kErrBadShape;
   if (rows_per_rank <= 0 || (rows_per_rank % BM) || N <= 0 || K <= 0) return kErrBadShape;
-  if ((lda & 7) || (ldb & 7) || (ldc & 7) || (N & 7) || (K & 7)) return kErrBadShape;
+  if ((ldb & 7) || (ldc & 7) || (N & 7) || (K & 7)) return kErrBadShape;
+  if (gathered == nullptr || sync == nullptr || (reinterpret_cast<uintptr_t>(gathered) & 15)) return kErrBadShape;
   TpArgs tp;
   memset(&tp, 0, sizeof(tp));
-  tp.world = world, tp.rank = rank, tp.rows_per_rank = rows_per_rank;
+  tp.world = world, tp.rank = rank, tp.rows_per_rank = rows_per_rank, tp.gather_own = gather_own;
+  tp.gathered = gathered, tp.sync = sync;
   for (int r = 0; r < world; ++r) {
-    int rc = make_tmap_2d(&tp.tmA[r], A_ranks[r], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_per_rank, K, lda, BM, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (reinterpret_cast<uintptr_t>(A_ranks[r]) & 15) return kErrBadShape;
+    tp.A_src[r] = A_ranks[r];
+    int rc = make_tmap_2d(&tp.tmA[r], A_ranks[r], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_per_rank, K, K, BM, BK, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != kOk) return rc;
   }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t sync_bytes = sizeof(int) * (1 + static_cast<size_t>(world) * rows_per_rank / BM);
+  if (cudaMemsetAsync(sync, 0, sync_bytes, s) != cudaSuccess) return kErrDriver;
   GemmParams p;
   p.M = world * rows_per_rank, p.N = N, p.K = K, p.C = C, p.ldc = ldc;
   p.bias = static_cast<const __nv_bfloat16*>(bias);
   p.alpha = 1.f, p.out_fp32 = 0, p.accumulate = 0, p.err = err;
-  return dispatch_tp<1>(tp, A_ranks[rank], B, p, lda, ldb, b_mn, static_cast<cudaStream_t>(stream));
+  return dispatch_tp<1>(tp, gathered, B, p, K, ldb, b_mn, s);
 }
 
 extern "C" int ttb_gemm_rs_bf16(const void* A, const void* B, void* const* C_ranks, int world, int rank, int rows_per_rank,

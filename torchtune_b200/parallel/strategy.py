@@ -126,7 +126,8 @@ class TensorParallelOptimizer:
             replicated = {id(p) for p in model._replicated}
             sharded_sq = sum((p.grad.float().pow(2).sum() for p in params if id(p) not in replicated), torch.zeros((), device=params[0].device))
             repl_sq = sum((p.grad.float().pow(2).sum() for p in params if id(p) in replicated), torch.zeros((), device=params[0].device))
-            self.strategy.tp.all_reduce_(sharded_sq)
+            if self.strategy.world > 1:
+                dist.all_reduce(sharded_sq)
             norm = (sharded_sq + repl_sq).sqrt()
             self.last_grad_norm = norm
             coef = torch.clamp(float(max_grad_norm) / (norm + 1e-6), max=1.0)
@@ -165,12 +166,16 @@ class ParallelStrategy(DataParallelEngine):
             cp=get("context_parallel_dim", 1) or 1,
             world_size=world,
         )
+        self.ep_dim = int(get("expert_parallel_dim", 1) or 1)
+        if self.ep_dim > 1 and (self.ep_dim != world or self.dims.tp_enabled):
+            raise NotImplementedError("expert_parallel_dim > 1 currently requires expert_parallel_dim == world size and no tensor parallelism")
         if self.dims.cp_enabled:
             raise NotImplementedError("context_parallel_dim > 1 is not wired into the recipes yet")
         if self.dims.tp_enabled and self.dims.dp_size > 1:
             raise NotImplementedError("tensor_parallel_dim > 1 currently requires data_parallel_shard_dim = data_parallel_replicate_dim = 1 (tp == world size)")
         super().__init__(device=device, group=None)
         self.tp = None  # TensorParallelContext, created in shard_model
+        self.ep = None  # ExpertParallelContext, created in shard_model
         self._cfg = cfg
         self._cpu_offload = bool(get("fsdp_cpu_offload", False))
 
@@ -216,6 +221,22 @@ class ParallelStrategy(DataParallelEngine):
         ac = any(isinstance(layer, CheckpointedLayer) for layer in core.layers)
         return tensor_parallelize(core, self.tp, activation_checkpointing=ac)
 
+    def _shard_model_ep(self, model: nn.Module, cfg) -> nn.Module:
+        """Experts spread over the ranks (every rank keeps its own batch: expert parallel ranks are data parallel for the
+        dense part, whose gradients are summed before the optimizer step)."""
+        from ..modules.moe import MoE
+        from .ep import ExpertParallelContext, expert_parallelize
+
+        moes = [m for m in model.modules() if isinstance(m, MoE)]
+        if not moes:
+            raise ValueError("expert_parallel_dim > 1 needs a model with MoE layers")
+        get = cfg.get if hasattr(cfg, "get") else (lambda k, d=None: d)
+        router = moes[0].router
+        tokens = self._tp_max_rows(cfg, model) * max(self.dims.tp, 1)
+        self.ep = ExpertParallelContext(self.device, None, num_experts=router.num_experts, dim=router.dim, max_pairs=tokens * router.experts_per_token,
+                                        capacity_factor=get("expert_capacity_factor"))
+        return expert_parallelize(model, self.ep)
+
     # model -------------------------------------------------------------------------------
     def shard_model(self, model: nn.Module, cfg, base_sd: Dict[str, Any], adapter_sd: Optional[Dict[str, Any]] = None, *, dtype: torch.dtype = torch.bfloat16, strict: bool = True) -> nn.Module:
         from ..training._distributed import materialize, validate_no_params_on_meta_device
@@ -243,6 +264,10 @@ class ParallelStrategy(DataParallelEngine):
             if is_lora:
                 raise NotImplementedError("tensor parallelism is implemented for full fine-tuning")
             return self._shard_model_tp(model, cfg)
+        if self.ep_dim > 1:
+            if is_lora:
+                raise NotImplementedError("expert parallelism is implemented for full fine-tuning")
+            return self._shard_model_ep(model, cfg)
         self.prepare(model)
         if self.world > 1:
             # adapters are initialised with rank-dependent seeds: rank 0's values win
@@ -257,7 +282,7 @@ class ParallelStrategy(DataParallelEngine):
 
     # optimizer ---------------------------------------------------------------------------
     def build_optimizer(self, model: nn.Module, cfg_optimizer=None, opt_state: Optional[Dict[str, Any]] = None, **kwargs: Any):
-        if self.tp is not None:
+        if self.tp is not None or self.ep is not None:
             from .. import config
 
             opt = TensorParallelOptimizer(self, model, config.instantiate(cfg_optimizer, [p for p in model.parameters() if p.requires_grad]))
@@ -294,7 +319,7 @@ class ParallelStrategy(DataParallelEngine):
 
     def optimizer_step(self, model: nn.Module, optimizer, grad_scale, clip_grad_norm: Optional[float] = None):
         clip = float(clip_grad_norm) if clip_grad_norm is not None else None
-        if self.tp is not None:
+        if self.tp is not None or self.ep is not None:
             optimizer.step(grad_scale=grad_scale, max_grad_norm=clip)
             optimizer.zero_grad()
             return optimizer.last_grad_norm
@@ -304,7 +329,7 @@ class ParallelStrategy(DataParallelEngine):
     def gather_full_state_dict(self, model: nn.Module) -> Dict[str, Any]:
         from ..training._distributed import gather_cpu_state_dict
 
-        if self.tp is not None:
+        if self.tp is not None or self.ep is not None:
             full = model.full_state_dict()  # collective: every rank takes part
             return {k: v.cpu() for k, v in full.items()} if self.rank == 0 else {}
 
@@ -317,6 +342,9 @@ class ParallelStrategy(DataParallelEngine):
         if self.tp is not None:
             self.tp.close()
             self.tp = None
+        if self.ep is not None:
+            self.ep.close()
+            self.ep = None
         super().shutdown()
         if self._owns_group and dist.is_initialized():
             dist.destroy_process_group()

@@ -5,9 +5,9 @@ SequenceParallel, torchtune/models/llama3/_parallelism.py:19-130) whose collecti
 kernels around cuBLAS GEMMs.  Here the two collective+GEMM pairs of a transformer block are single
 kernels (``ttb_gemm_ag_bf16`` / ``ttb_gemm_rs_bf16`` in ``ops/csrc/gemm.cu``):
 
-* column-parallel projection of a sequence-sharded input — *all-gather → GEMM*: the tcgen05 GEMM's TMA
-  producer reads each m-tile of the activation directly from the shard of the rank that owns those rows
-  (peer memory), so the gathered activation never exists and the NVLink reads overlap the MMAs tile by tile;
+* column-parallel projection of a sequence-sharded input — *all-gather → GEMM*: extra copier warps inside the
+  tcgen05 GEMM pull the peers' shards into local memory piece by piece (each byte crosses NVLink once) while the
+  MMA pipeline works on the tiles that are already local; the TMA producer waits per m-tile on a piece counter;
 * row-parallel projection to a sequence-sharded output — *GEMM → reduce-scatter*: the epilogue stores every
   output tile into a staging slot on the rank that owns those rows; the owner sums its ``world`` slots in fp32
   and adds the residual in the same pass.
@@ -37,7 +37,7 @@ def _declare(L) -> None:
         return
     vp, i32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
     pvp = ctypes.POINTER(vp)
-    L.ttb_gemm_ag_bf16.argtypes = [pvp, vp, vp, i32, i32, i32, i32, i32, i32, i64, i64, i64, vp, vp, vp]
+    L.ttb_gemm_ag_bf16.argtypes = [pvp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i64, i64, vp, vp, vp]
     L.ttb_gemm_rs_bf16.argtypes = [vp, vp, pvp, i32, i32, i32, i32, i32, i32, i64, i64, i64, vp, vp]
     L.ttb_rs_reduce.argtypes = [vp, vp, vp, vp, i32, i64, i32, i64, i64, i64, vp]
     for fn in (L.ttb_gemm_ag_bf16, L.ttb_gemm_rs_bf16, L.ttb_rs_reduce):
@@ -51,8 +51,11 @@ class TensorParallelContext:
     ``max_rows_per_rank`` is the largest number of tokens a rank owns (batch·seq / world) and
     ``max_width`` the widest activation that is gathered or scattered (the model width)."""
 
-    def __init__(self, device: torch.device, group=None, *, max_rows_per_rank: int, max_width: int):
+    def __init__(self, device: torch.device, group=None, *, max_rows_per_rank: int, max_width: int, keep_gathered: bool = True):
         self.device, self.group = device, group
+        # keep the gathered activation a column-parallel layer's kernel produces for its weight gradient (saves one
+        # all-gather per layer in backward at the price of holding world× the sharded activation until then)
+        self.keep_gathered = keep_gathered
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.max_rows, self.max_width = int(max_rows_per_rank), int(max_width)
@@ -89,14 +92,17 @@ class TensorParallelContext:
         return rows % 128 == 0 and k % 8 == 0 and n % 8 == 0
 
     # ------------------------------------------------------------------ all-gather → GEMM
-    def ag_gemm(self, x_shard: torch.Tensor, weight: torch.Tensor, *, b_mn: bool = False, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """``concat_ranks(x_shard) @ op(weight)`` → ``[world·rows, N]``; ``weight`` is ``[N, K]`` (or ``[K, N]`` with ``b_mn``)."""
+    def ag_gemm(self, x_shard: torch.Tensor, weight: torch.Tensor, *, b_mn: bool = False, bias: Optional[torch.Tensor] = None,
+                return_gathered: bool = False):
+        """``concat_ranks(x_shard) @ op(weight)`` → ``[world·rows, N]``; ``weight`` is ``[N, K]`` (or ``[K, N]`` with ``b_mn``).
+        With ``return_gathered`` also returns ``concat_ranks(x_shard)`` — on the fused path it is a by-product of the kernel."""
         rows, k = x_shard.shape
         n = weight.shape[1] if b_mn else weight.shape[0]
         if not (self.cuda and x_shard.dtype == _BF16 and self.fusable(rows, k, n)):
             full = self.all_gather_rows(x_shard)
             out = full @ weight if b_mn else torch.nn.functional.linear(full, weight)
-            return out + bias if bias is not None else out
+            out = out + bias if bias is not None else out
+            return (out, full) if return_gathered else out
         from ..ops._lib import check, err_word, lib, stream_ptr
 
         self._check(rows, k)
@@ -105,13 +111,16 @@ class TensorParallelContext:
         buf.tensor(_BF16, rows * k).view(rows, k).copy_(x_shard)
         self.barrier()  # every rank's shard is in place
         out = torch.empty(self.world * rows, n, dtype=_BF16, device=self.device)
+        gathered = torch.empty(self.world * rows, k, dtype=_BF16, device=self.device)
+        sync = torch.empty(1 + self.world * rows // 128, dtype=torch.int32, device=self.device)
         w = weight if weight.is_contiguous() else weight.contiguous()
         check(
-            lib().ttb_gemm_ag_bf16(buf.pointer_array(), w.data_ptr(), out.data_ptr(), self.world, self.rank, rows, n, k, int(b_mn), k, w.stride(0), n,
+            lib().ttb_gemm_ag_bf16(buf.pointer_array(), w.data_ptr(), out.data_ptr(), gathered.data_ptr(), sync.data_ptr(), int(return_gathered),
+                                   self.world, self.rank, rows, n, k, int(b_mn), w.stride(0), n,
                                    None if bias is None else bias.data_ptr(), err_word(self.device).data_ptr(), stream_ptr()),
             "gemm_ag",
         )
-        return out
+        return (out, gathered) if return_gathered else out
 
     # ------------------------------------------------------------------ GEMM → reduce-scatter
     def gemm_rs(self, x: torch.Tensor, weight: torch.Tensor, *, b_mn: bool = False, residual: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -187,6 +196,11 @@ class _ColumnParallel(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x_shard, weight, tp: TensorParallelContext):
         ctx.tp = tp
+        ctx.gathered = tp.keep_gathered and weight.requires_grad
+        if ctx.gathered:  # the kernel's local copy of the gathered activation feeds the weight gradient; no re-gather
+            out, x_full = tp.ag_gemm(x_shard, weight, return_gathered=True)
+            ctx.save_for_backward(x_full, weight)
+            return out
         ctx.save_for_backward(x_shard, weight)
         return tp.ag_gemm(x_shard, weight)
 
@@ -198,7 +212,7 @@ class _ColumnParallel(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = tp.gemm_rs(dy, weight, b_mn=True)
         if ctx.needs_input_grad[1]:
-            x_full = tp.all_gather_rows(x_shard)
+            x_full = x_shard if ctx.gathered else tp.all_gather_rows(x_shard)
             dw = _wgrad(dy, x_full)
         return dx, dw, None
 
@@ -220,10 +234,15 @@ class _RowParallel(torch.autograd.Function):
         tp = ctx.tp
         dy_shard = dy_shard.contiguous()
         dx = dw = None
+        dy_full = None
         if ctx.needs_input_grad[0]:
-            dx = tp.ag_gemm(dy_shard, weight, b_mn=True)
+            if ctx.needs_input_grad[1]:
+                dx, dy_full = tp.ag_gemm(dy_shard, weight, b_mn=True, return_gathered=True)
+            else:
+                dx = tp.ag_gemm(dy_shard, weight, b_mn=True)
         if ctx.needs_input_grad[1]:
-            dy_full = tp.all_gather_rows(dy_shard)
+            if dy_full is None:
+                dy_full = tp.all_gather_rows(dy_shard)
             dw = _wgrad(dy_full, x)
         return dx, dw, (dy_shard if ctx.has_residual and ctx.needs_input_grad[2] else None), None
 

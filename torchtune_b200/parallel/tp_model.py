@@ -197,7 +197,7 @@ class TPDecoder(nn.Module):
         b, s = tokens.shape
         if (b * s) % self.tp.world:
             raise ValueError(f"batch·seq ({b * s}) must be divisible by the tensor parallel size ({self.tp.world})")
-        h = self.tok_embeddings(self.shard_rows(tokens)[0])
+        h = ops.embed_tokens(self.tok_embeddings, self.shard_rows(tokens)[0])
         for layer in self.layers:
             if self.activation_checkpointing and torch.is_grad_enabled():
                 h = torch.utils.checkpoint.checkpoint(layer, h, b, s, mask, input_pos, use_reentrant=False)
@@ -228,7 +228,7 @@ class TPDecoder(nn.Module):
         """Decoding-time forward: activations are replicated (any batch / sequence length, including one token), attention uses
         this rank's heads and KV cache, and the two row-parallel projections of every layer are followed by an all-reduce.
         Returns fp32 logits ``[b, s, vocab]``, identical on every rank."""
-        h = self.tok_embeddings(tokens)
+        h = ops.embed_tokens(self.tok_embeddings, tokens)
         for layer in self.layers:
             m = layer.mask_mod(mask, tokens.shape[0], tokens.shape[1]) if layer.mask_mod is not None else mask
             h = h + self.tp.all_reduce_(layer.attn.forward_replicated(layer.sa_norm(h), m, input_pos))

@@ -516,3 +516,60 @@ def test_embedding_matches_reference_with_repeated_tokens():
     assert torch.equal(out.float(), ref)
     rel = (table.grad.float() - tf.grad).norm() / tf.grad.norm()
     assert rel < 4e-3
+
+
+# ----------------------------------------------------------------------------- expert-parallel exchange (ranks emulated on one GPU)
+@pytest.mark.parametrize("world,E,k", [(1, 4, 1), (2, 4, 2), (4, 16, 1), (8, 16, 2)])
+def test_expert_parallel_plan_push_pull_emulated_ranks(world, E, k):
+    import ctypes
+
+    from torchtune_b200.ops._lib import lib, stream_ptr
+    from torchtune_b200.parallel.ep import _declare
+
+    L = lib()
+    _declare(L)
+    T, dim = 96, 264
+    pairs = T * k
+    cap = world * pairs
+    g = torch.Generator(device="cuda").manual_seed(world * 10 + k)
+    xs = [_rand(T, dim, scale=0.5, seed=300 + r) for r in range(world)]
+    experts, tokens, scales, counts = [], [], [], []
+    for r in range(world):
+        e = torch.randint(0, E, (pairs,), generator=g, device="cuda")
+        if r == 0:
+            e[e == 1] = 0  # an expert that receives nothing from rank 0
+        order = torch.argsort(e, stable=True)
+        experts.append(e[order])
+        tokens.append((order // k).contiguous())
+        scales.append(_rand(pairs, scale=1.0, seed=400 + r))
+        counts.append(torch.bincount(e, minlength=E))
+    arr = lambda ts: (ctypes.c_void_p * world)(*[t.data_ptr() for t in ts])
+    recv = [torch.full((cap, dim), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    plans = []
+    for r in range(world):
+        dr = torch.empty(pairs, dtype=torch.int32, device="cuda")
+        drow = torch.empty(pairs, dtype=torch.int32, device="cuda")
+        rc_counts = torch.empty(E // world, dtype=torch.int64, device="cuda")
+        rc_total = torch.empty(1, dtype=torch.int32, device="cuda")
+        assert L.ttb_ep_plan(arr(counts), world, r, E, pairs, dr.data_ptr(), drow.data_ptr(), rc_counts.data_ptr(), rc_total.data_ptr(), stream_ptr()) == 0
+        plans.append((dr, drow, rc_counts, rc_total))
+        assert L.ttb_ep_push(xs[r].data_ptr(), tokens[r].data_ptr(), scales[r].data_ptr(), dr.data_ptr(), drow.data_ptr(), arr(recv), world, pairs, dim, cap, stream_ptr()) == 0
+    epr = E // world
+    all_counts = torch.stack(counts)  # [world, E]
+    for d in range(world):
+        want_rows = []
+        for e in range(d * epr, (d + 1) * epr):
+            for r in range(world):
+                sel = experts[r] == e
+                want_rows.append((xs[r][tokens[r][sel]].float() * scales[r][sel].float()[:, None]).bfloat16())
+        want = torch.cat(want_rows)
+        assert torch.equal(plans[d][2], all_counts[:, d * epr : (d + 1) * epr].sum(0))
+        assert int(plans[d][3]) == want.shape[0]
+        assert torch.equal(recv[d][: want.shape[0]], want)
+        assert torch.isnan(recv[d][want.shape[0] :].float()).all()
+    result = [(t.float() * 2).bfloat16() for t in recv]
+    for r in range(world):
+        out = torch.empty(pairs, dim, dtype=torch.bfloat16, device="cuda")
+        assert L.ttb_ep_pull(arr(result), world, plans[r][0].data_ptr(), plans[r][1].data_ptr(), out.data_ptr(), pairs, dim, cap, stream_ptr()) == 0
+        want = ((xs[r][tokens[r]].float() * scales[r].float()[:, None]).bfloat16().float() * 2).bfloat16()
+        assert torch.equal(out, want)

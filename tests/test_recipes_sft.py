@@ -107,6 +107,28 @@ def test_full_distributed_tensor_parallel_matches_single_process(tmp_path, tune_
         torch.testing.assert_close(a[k], b[k], rtol=1e-3, atol=2e-5)
 
 
+@pytest.mark.timeout(900)
+def test_full_distributed_context_parallel_matches_single_process(tmp_path, tune_path, monkeypatch):
+    """context_parallel_dim=2 on two gloo ranks: both ranks read the same batch, each owns half of every sequence."""
+    ckpt = tmp_path / "ckpt"
+    write_tiny_hf_checkpoint(ckpt)
+    common = f"checkpointer.checkpoint_dir={ckpt} metric_logger.filename=log.txt max_steps_per_epoch=3 dataset.num_samples=8 clip_grad_norm=1.0"
+    run_tune(tune_path, f"run full_finetune_single_device --config tiny/llama_full_single_device {common} output_dir={tmp_path / 'single'}", monkeypatch)
+    single = read_losses(tmp_path / "single" / "logs" / "log.txt")
+    _tune_subprocess(
+        ["run", "--nnodes=1", "--nproc_per_node=2", "--master-addr=127.0.0.1", "--master-port=29536", "full_finetune_distributed", "--config", "tiny/llama_full_distributed"]
+        + common.split()
+        + [f"output_dir={tmp_path / 'cp'}", "context_parallel_dim=2"]
+    )
+    cp_losses = read_losses(tmp_path / "cp" / "logs" / "log.txt")
+    assert len(cp_losses) == 3
+    torch.testing.assert_close(torch.tensor(cp_losses), torch.tensor(single), rtol=2e-4, atol=2e-4)
+    a = load_file(str(tmp_path / "single" / "epoch_0" / "model-00001-of-00001.safetensors"))
+    b = load_file(str(tmp_path / "cp" / "epoch_0" / "model-00001-of-00001.safetensors"))
+    for k in a:
+        torch.testing.assert_close(a[k], b[k], rtol=1e-3, atol=2e-5)
+
+
 def test_early_exit_recipe_runs_and_rotates_exits(tmp_path, tune_path, monkeypatch):
     ckpt = tmp_path / "ckpt"
     write_tiny_hf_checkpoint(ckpt)

@@ -416,6 +416,9 @@ class SFTTrainer:
     # ------------------------------------------------------------------ train
     def _loss_step(self, batch: Dict[str, Any]):
         """Returns ``(loss_sum, n_valid)`` for one micro-batch."""
+        cp = getattr(self._model, "_cp", None)
+        if cp is not None:  # context parallel: this rank's slice of every sequence (the mask still describes whole sequences)
+            batch = cp.shard_batch(batch)
         labels = batch.pop("labels")
         if hasattr(self._model, "shard_rows"):  # tensor parallel: the loss runs on this rank's token rows
             labels = self._model.shard_rows(labels)

@@ -134,6 +134,9 @@ class MultiHeadAttention(nn.Module):
 
         plain = self.kv_cache is None or not self.cache_enabled
         attn_mask = _as_mask(mask, default_causal=self.is_causal and plain and mask is None)
+        cp = getattr(self, "context_parallel", None)
+        if cp is not None and plain:  # sequence-sharded activations: whole sequences for a subset of heads inside attention
+            q, k, v = cp.seq_to_heads(q), cp.seq_to_heads(k), cp.seq_to_heads(v)
         out = ops.attention(
             q,
             k,
@@ -143,4 +146,6 @@ class MultiHeadAttention(nn.Module):
             softcap=self.softcap,
             dropout_p=self.attn_dropout if self.training else 0.0,
         )
+        if cp is not None and plain:
+            out = cp.heads_to_seq(out)
         return self.output_proj(out.reshape(b, s_x, self.num_heads * self.head_dim))

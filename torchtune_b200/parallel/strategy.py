@@ -169,13 +169,14 @@ class ParallelStrategy(DataParallelEngine):
         self.ep_dim = int(get("expert_parallel_dim", 1) or 1)
         if self.ep_dim > 1 and (self.ep_dim != world or self.dims.tp_enabled):
             raise NotImplementedError("expert_parallel_dim > 1 currently requires expert_parallel_dim == world size and no tensor parallelism")
-        if self.dims.cp_enabled:
-            raise NotImplementedError("context_parallel_dim > 1 is not wired into the recipes yet")
+        if self.dims.cp_enabled and (self.dims.tp_enabled or self.ep_dim > 1):
+            raise NotImplementedError("context_parallel_dim > 1 combines with data parallelism only (not with tensor or expert parallelism)")
         if self.dims.tp_enabled and self.dims.dp_size > 1:
             raise NotImplementedError("tensor_parallel_dim > 1 currently requires data_parallel_shard_dim = data_parallel_replicate_dim = 1 (tp == world size)")
         super().__init__(device=device, group=None)
         self.tp = None  # TensorParallelContext, created in shard_model
         self.ep = None  # ExpertParallelContext, created in shard_model
+        self.cp = None  # ContextParallelContext, created in shard_model
         self._cfg = cfg
         self._cpu_offload = bool(get("fsdp_cpu_offload", False))
 
@@ -191,11 +192,31 @@ class ParallelStrategy(DataParallelEngine):
     # data-parallel coordinates: with tensor parallelism every rank reads the same batch ------------
     @property
     def dp_size(self) -> int:  # type: ignore[override]
-        return 1 if self.dims.tp_enabled else self.world
+        if self.dims.tp_enabled:
+            return 1
+        return self.world // self.dims.cp  # the ranks of one context-parallel group read the same batch
 
     @property
     def dp_rank(self) -> int:  # type: ignore[override]
-        return 0 if self.dims.tp_enabled else self.rank
+        if self.dims.tp_enabled:
+            return 0
+        return self.rank // self.dims.cp
+
+    def _attach_context_parallel(self, model: nn.Module) -> None:
+        """Context-parallel groups are runs of ``cp`` consecutive ranks; for parameters they are data-parallel ranks (every
+        rank's gradient covers its own tokens and the resident engine sums over all ranks)."""
+        from .cp import ContextParallelContext, context_parallelize
+
+        cp = self.dims.cp
+        group = None
+        if cp != self.world:
+            for g in range(self.world // cp):  # every rank creates every group, in the same order
+                ranks = list(range(g * cp, (g + 1) * cp))
+                handle = dist.new_group(ranks)
+                if self.rank in ranks:
+                    group = handle
+        self.cp = ContextParallelContext(group, world=cp, rank=self.rank % cp)
+        context_parallelize(model, self.cp)
 
     def _tp_max_rows(self, cfg, model: nn.Module) -> int:
         get = cfg.get if hasattr(cfg, "get") else (lambda k, d=None: d)
@@ -269,6 +290,8 @@ class ParallelStrategy(DataParallelEngine):
                 raise NotImplementedError("expert parallelism is implemented for full fine-tuning")
             return self._shard_model_ep(model, cfg)
         self.prepare(model)
+        if self.dims.cp_enabled:
+            self._attach_context_parallel(model)
         if self.world > 1:
             # adapters are initialised with rank-dependent seeds: rank 0's values win
             flat = self.flat.flat_param

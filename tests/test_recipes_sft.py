@@ -129,6 +129,38 @@ def test_full_distributed_context_parallel_matches_single_process(tmp_path, tune
         torch.testing.assert_close(a[k], b[k], rtol=1e-3, atol=2e-5)
 
 
+@pytest.mark.timeout(900)
+def test_full_distributed_expert_parallel_matches_data_parallel(tmp_path):
+    """A tiny MoE decoder on two gloo ranks: expert_parallel_dim=2 (experts split over the ranks, routed rows exchanged) must
+    train like plain data parallelism (all experts on every rank) on the same batches."""
+    from torchtune_b200.models.llama4 import llama4_decoder
+
+    ckpt = tmp_path / "ckpt"
+    ckpt.mkdir()
+    torch.manual_seed(0)
+    model = llama4_decoder(vocab_size=1024, num_layers=2, num_heads=4, num_kv_heads=2, embed_dim=128, hidden_dim=256, max_seq_len=256, num_experts=4, experts_per_token=2, rope_base=500000)
+    with torch.no_grad():
+        for prm in model.parameters():
+            prm.copy_(torch.randn_like(prm) * 0.05)
+    torch.save(model.state_dict(), ckpt / "model.pt")
+    common = [f"checkpointer.checkpoint_dir={ckpt}", "metric_logger.filename=log.txt", "max_steps_per_epoch=3", "dataset.num_samples=16", "clip_grad_norm=1.0", "optimizer.lr=1e-3"]
+    losses = {}
+    for name, port, extra in (("dp", 29537, []), ("ep", 29538, ["expert_parallel_dim=2"])):
+        _tune_subprocess(
+            ["run", "--nnodes=1", "--nproc_per_node=2", "--master-addr=127.0.0.1", f"--master-port={port}", "full_finetune_distributed", "--config", "tiny/llama4_moe_full_distributed"]
+            + common + [f"output_dir={tmp_path / name}"] + extra
+        )
+        losses[name] = read_losses(tmp_path / name / "logs" / "log.txt")
+    assert len(losses["ep"]) == 3
+    torch.testing.assert_close(torch.tensor(losses["ep"]), torch.tensor(losses["dp"]), rtol=2e-4, atol=2e-4)
+    a = torch.load(tmp_path / "dp" / "epoch_0" / "model-00001-of-00001.bin", weights_only=True) if (tmp_path / "dp" / "epoch_0" / "model-00001-of-00001.bin").exists() else None
+    if a is not None:
+        b = torch.load(tmp_path / "ep" / "epoch_0" / "model-00001-of-00001.bin", weights_only=True)
+        assert set(a) == set(b)
+        for k in a:
+            torch.testing.assert_close(a[k], b[k], rtol=1e-3, atol=2e-5)
+
+
 def test_early_exit_recipe_runs_and_rotates_exits(tmp_path, tune_path, monkeypatch):
     ckpt = tmp_path / "ckpt"
     write_tiny_hf_checkpoint(ckpt)

@@ -573,3 +573,61 @@ def test_expert_parallel_plan_push_pull_emulated_ranks(world, E, k):
         assert L.ttb_ep_pull(arr(result), world, plans[r][0].data_ptr(), plans[r][1].data_ptr(), out.data_ptr(), pairs, dim, cap, stream_ptr()) == 0
         want = ((xs[r][tokens[r]].float() * scales[r].float()[:, None]).bfloat16().float() * 2).bfloat16()
         assert torch.equal(out, want)
+
+
+# ----------------------------------------------------------------------------- fp8 GEMM + cast/transpose
+def _fp8_ref(t, scale, dtype):
+    return (t.float() * scale).clamp(-torch.finfo(dtype).max, torch.finfo(dtype).max).to(dtype)
+
+
+@pytest.mark.parametrize("e5m2", [False, True])
+@pytest.mark.parametrize("rowwise", [False, True])
+def test_fp8_cast_transpose_matches_torch(e5m2, rowwise):
+    from torchtune_b200.ops._cuda import fp8_cast, fp8_scales
+
+    dtype = torch.float8_e5m2 if e5m2 else torch.float8_e4m3fn
+    x = _rand(208, 336, scale=2.0, seed=5)
+    s_row, s_col = fp8_scales(x, e5m2, rowwise)
+    out, out_t = fp8_cast(x, s_row, s_col, e5m2=e5m2)
+    want = _fp8_ref(x, s_row.reshape(-1, 1) if rowwise else s_row, dtype)
+    want_t = _fp8_ref(x, s_col.reshape(1, -1) if rowwise else s_col, dtype).t().contiguous()
+    assert torch.equal(out.view(dtype).float(), want.float())
+    assert torch.equal(out_t.view(dtype).float(), want_t.float())
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 64, 128), (384, 272, 208), (1024, 1024, 2048), (2048, 4096, 512)])
+@pytest.mark.parametrize("rowwise", [False, True])
+def test_gemm_fp8_matches_dequantised_fp32(M, N, K, rowwise):
+    """The kernel must reproduce the product of the *quantised* operands exactly up to fp32 accumulation order."""
+    from torchtune_b200.ops._cuda import fp8_cast, fp8_scales, gemm_fp8
+    from torchtune_b200.ops._lib import check_device_errors
+
+    a, b = _rand(M, K, scale=1.0, seed=1), _rand(N, K, scale=0.5, seed=2)
+    bias = _rand(N, scale=0.5, seed=3)
+    sa, _ = fp8_scales(a, False, rowwise)
+    sb, _ = fp8_scales(b, True, rowwise)
+    aq, _ = fp8_cast(a, sa, sa, want_t=False)
+    bq, _ = fp8_cast(b, sb, sb, e5m2=True, want_t=False)
+    got = gemm_fp8(aq, bq, 1.0 / sa, 1.0 / sb, b_e5m2=True, bias=bias)
+    check_device_errors()
+    af = aq.view(torch.float8_e4m3fn).float() / (sa.reshape(-1, 1) if rowwise else sa)
+    bf = bq.view(torch.float8_e5m2).float() / (sb.reshape(-1, 1) if rowwise else sb)
+    want = af @ bf.t() + bias.float()
+    _close(got, want, 1e-2, 1e-2 * want.abs().max().item(), "gemm_fp8")
+
+
+@pytest.mark.parametrize("rowwise", [False, True])
+def test_fp8_linear_forward_backward_close_to_bf16(rowwise):
+    x = _rand(4, 128, 512, scale=1.0, seed=7).requires_grad_()
+    w = _rand(768, 512, scale=0.05, seed=8).requires_grad_()
+    bias = _rand(768, scale=0.1, seed=9).requires_grad_()
+    y = ops.fp8_linear(x, w, bias, rowwise=rowwise)
+    assert y is not None and y.shape == (4, 128, 768)
+    dy = _rand(4, 128, 768, scale=0.1, seed=10)
+    y.backward(dy)
+    xf, wf, bf = (t.detach().float().requires_grad_() for t in (x, w, bias))
+    yf = torch.nn.functional.linear(xf, wf, bf)
+    yf.backward(dy.float())
+    rel = lambda a, b: float((a.float() - b).norm() / b.norm())
+    assert rel(y, yf) < 0.06 and rel(x.grad, xf.grad) < 0.12 and rel(w.grad, wf.grad) < 0.12, (rel(y, yf), rel(x.grad, xf.grad), rel(w.grad, wf.grad))
+    assert rel(bias.grad, bf.grad) < 1e-2

@@ -18,6 +18,7 @@ from .mask import AttentionMask
 __all__ = [
     "grouped_matmul",
     "lora_linear",
+    "fp8_linear",
     "matmul",
     "linear",
     "rms_norm",
@@ -64,6 +65,19 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
 
         return _cuda.linear(x, weight, bias)
     return F.linear(x, weight, bias)
+
+
+def fp8_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, rowwise: bool = False) -> Optional[torch.Tensor]:
+    """fp8 tensor-core linear (dynamic scaling); returns ``None`` when the inputs do not qualify (not bf16 CUDA, or a dimension that
+    is not a multiple of 16) so the caller can fall back to its emulation."""
+    if not (_native(x) and weight.dtype == torch.bfloat16 and weight.is_contiguous()):
+        return None
+    tokens = x.numel() // x.shape[-1]
+    if x.shape[-1] % 16 or weight.shape[0] % 16 or tokens % 16 or tokens == 0:
+        return None
+    from . import _cuda
+
+    return _cuda.fp8_linear(x, weight, bias, rowwise)
 
 
 def lora_linear(x: torch.Tensor, xd: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], lora_a: torch.Tensor, lora_b: torch.Tensor, scale: float) -> torch.Tensor:

@@ -359,6 +359,94 @@ def moe_permute_indices(tokens_per_expert_group: torch.Tensor, experts_per_rank:
     return permuted, m_sizes, m_offsets
 
 
+# ======================================================================= fp8 linear
+_FP8_MAX = {False: 448.0, True: 57344.0}  # e4m3, e5m2
+
+
+def fp8_scales(x2: torch.Tensor, e5m2: bool, rowwise: bool) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Quantisation scales ``fmax / amax`` for the two layouts of ``x2`` ``[R, C]``: per row (for the same-layout copy) and per
+    column (for the transposed copy); with tensorwise scaling both are the same single value."""
+    fmax = _FP8_MAX[e5m2]
+    if rowwise:
+        a = x2.abs()
+        return fmax / a.amax(dim=1).float().clamp_min(1e-12), fmax / a.amax(dim=0).float().clamp_min(1e-12)
+    s = (fmax / x2.abs().amax().float().clamp_min(1e-12)).reshape(1)
+    return s, s
+
+
+def fp8_cast(x2: torch.Tensor, s_row: torch.Tensor, s_col: torch.Tensor, *, e5m2: bool = False, want: bool = True, want_t: bool = True):
+    """``(fp8(x2 · s_row), fp8(x2 · s_col)ᵀ)`` as uint8 tensors ``[R, C]`` / ``[C, R]`` in one pass over ``x2`` (bf16)."""
+    R, C = x2.shape
+    out = torch.empty(R, C, dtype=torch.uint8, device=x2.device) if want else None
+    out_t = torch.empty(C, R, dtype=torch.uint8, device=x2.device) if want_t else None
+    check(lib().ttb_fp8_cast_transpose(x2.data_ptr(), x2.stride(0), R, C, s_row.data_ptr(), int(s_row.numel() > 1), _ptr(out), s_col.data_ptr(), int(s_col.numel() > 1),
+                                       _ptr(out_t), int(e5m2), stream_ptr()), "fp8_cast_transpose")
+    return out, out_t
+
+
+def gemm_fp8(a: torch.Tensor, b: torch.Tensor, inv_sa: torch.Tensor, inv_sb: torch.Tensor, *, a_e5m2: bool = False, b_e5m2: bool = False,
+             bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, accumulate: bool = False) -> torch.Tensor:
+    """``(a[M, K] · b[N, K]ᵀ) · inv_sa[m] · inv_sb[n] (+ bias)`` → bf16 ``[M, N]``; ``a``, ``b`` uint8-stored fp8."""
+    M, K = a.shape
+    N = b.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    check(lib().ttb_gemm_fp8(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0), int(a_e5m2), int(b_e5m2),
+                             inv_sa.data_ptr(), int(inv_sa.numel() > 1), inv_sb.data_ptr(), int(inv_sb.numel() > 1), _ptr(bias), int(accumulate),
+                             err_word(a.device).data_ptr(), stream_ptr()), "gemm_fp8")
+    return out
+
+
+class _Fp8Linear(torch.autograd.Function):
+    """``x @ Wᵀ (+ bias)`` with all three products (forward, input gradient, weight gradient) on the fp8 tensor cores.  Inputs are
+    quantised dynamically (tensorwise: e4m3 activations / weights, e5m2 output gradients; rowwise: e4m3 with one scale per row of
+    each operand along its contraction dimension).  Only fp8 copies are saved for backward."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, rowwise: bool):
+        K, N = x.shape[-1], weight.shape[0]
+        x2 = x.reshape(-1, K)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        sx_row, sx_col = fp8_scales(x2, False, rowwise)
+        sw_row, sw_col = fp8_scales(weight, False, rowwise)
+        need_dw, need_dx = weight.requires_grad, x.requires_grad
+        xq, xq_t = fp8_cast(x2, sx_row, sx_col, want_t=need_dw)
+        wq, wq_t = fp8_cast(weight, sw_row, sw_col, want_t=need_dx)
+        y = gemm_fp8(xq, wq, 1.0 / sx_row, 1.0 / sw_row, bias=bias)
+        ctx.rowwise, ctx.has_bias = rowwise, bias is not None
+        ctx.save_for_backward(xq_t, None if xq_t is None else 1.0 / sx_col, wq_t, None if wq_t is None else 1.0 / sw_col, weight)
+        return y.view(*x.shape[:-1], N)
+
+    @staticmethod
+    def backward(ctx, dy):
+        xq_t, inv_sx_col, wq_t, inv_sw_col, weight = ctx.saved_tensors
+        N = dy.shape[-1]
+        dy2 = dy.reshape(-1, N)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        e5m2 = not ctx.rowwise
+        s_row, s_col = fp8_scales(dy2, e5m2, ctx.rowwise)
+        dyq, dyq_t = fp8_cast(dy2, s_row, s_col, e5m2=e5m2, want=wq_t is not None, want_t=xq_t is not None)
+        dx = dw = db = None
+        if wq_t is not None:
+            dx = gemm_fp8(dyq, wq_t, 1.0 / s_row, inv_sw_col, a_e5m2=e5m2).view(*dy.shape[:-1], wq_t.shape[0])
+        if xq_t is not None:
+            owner = grad_window_owner(weight)
+            if owner is None:
+                dw = gemm_fp8(dyq_t, xq_t, 1.0 / s_col, inv_sx_col, a_e5m2=e5m2)
+            else:
+                gemm_fp8(dyq_t, xq_t, 1.0 / s_col, inv_sx_col, a_e5m2=e5m2, out=owner._grad_buffer, accumulate=bool(owner._grad_written))
+                owner._grad_written = True
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.sum(0)
+        return dx, dw, db, None
+
+
+def fp8_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, rowwise: bool = False) -> torch.Tensor:
+    return _Fp8Linear.apply(x, weight, bias, rowwise)
+
+
 # ======================================================================= RMSNorm
 class _RMSNorm(torch.autograd.Function):
     @staticmethod

@@ -62,6 +62,10 @@ def _declare(L: ctypes.CDLL) -> None:
     L.ttb_moe_permute_indices.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp, vp]
     L.ttb_embedding_fwd.argtypes = [vp, vp, vp, i64, i32, i64, vp]
     L.ttb_embedding_bwd.argtypes = [vp, vp, vp, vp, i64, i32, i64, i64, vp]
+    L.ttb_gemm_fp8.argtypes = [vp, vp, vp, i32, i32, i32, i64, i64, i64, i32, i32, vp, i32, vp, i32, vp, i32, vp, vp]
+    L.ttb_fp8_cast_transpose.argtypes = [vp, i64, i32, i32, vp, i32, vp, vp, i32, vp, i32, vp]
+    L.ttb_gemm_fp8.restype = i32
+    L.ttb_fp8_cast_transpose.restype = i32
     for fn in (L.ttb_moe_route_sort, L.ttb_moe_permute_indices, L.ttb_embedding_fwd, L.ttb_embedding_bwd):
         fn.restype = i32
     L.ttb_ensure_device.restype = i32

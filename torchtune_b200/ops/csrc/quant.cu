@@ -7,6 +7,8 @@
 //     w[i] = codebook[code[i]] * (scaler_q[i / block] / scaler_factor[i / block / scaler_block] + scaler_mean)
 // Each thread expands 16 codes (one 8-byte load, two 16-byte stores); the kernel is pure HBM streaming
 // (0.5 B read + 2 B written per weight).
+#include <cuda_fp8.h>
+
 #include "common/ptx.cuh"
 #include "common/tmap.h"
 
@@ -63,5 +65,74 @@ extern "C" int ttb_nf4_dequant(const void* packed, const void* scaler_q, const v
   nf4_dequant_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint8_t*>(packed), static_cast<const int8_t*>(scaler_q), static_cast<const float*>(scaler_factor),
       static_cast<const float*>(scaler_mean), static_cast<__nv_bfloat16*>(out), n16, block, scaler_block);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrDriver;
+}
+
+// ----------------------------------------------------------------------------------------------- fp8 cast (+ transpose)
+// One pass over a bf16 matrix x[R, C] produces the two fp8 operands an fp8 linear layer needs: `out` = fp8(x · s_row)
+// in the same layout and `out_t` = fp8(x · s_col)ᵀ ([C, R]), so that every product of the layer (forward, input gradient,
+// weight gradient) reads K-contiguous operands (gemm_fp8.cu).  Scales are device fp32: one value (stride 0, tensorwise)
+// or one per row of the respective output (stride 1: per row of x for `out`, per column of x for `out_t`).
+namespace ttb {
+
+template <bool E5M2>
+__device__ __forceinline__ uint8_t to_fp8(float v) {
+  return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, E5M2 ? __NV_E5M2 : __NV_E4M3));
+}
+
+template <bool E5M2>
+__global__ void __launch_bounds__(256)
+fp8_cast_transpose_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int R, int C, const float* __restrict__ s_row, int s_row_stride,
+                          uint8_t* __restrict__ out, const float* __restrict__ s_col, int s_col_stride, uint8_t* __restrict__ out_t) {
+  __shared__ __align__(16) uint8_t tile_t[64][64 + 16];  // [column][row] for the transposed output
+  const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+  const int lr = threadIdx.x >> 2, lc = (threadIdx.x & 3) * 16;
+  const int r = r0 + lr, c = c0 + lc;
+  if (r < R && c < C) {  // R and C are multiples of 16: a 16-element group is inside or outside as a whole
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<long long>(r) * ldx + c);
+    const uint4 raw[2] = {src[0], src[1]};
+    const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(raw);
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __bfloat162float(h[i]);
+    if (out != nullptr) {
+      const float sr = s_row[s_row_stride ? r : 0];
+      uint32_t w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        w[i] = to_fp8<E5M2>(v[4 * i] * sr) | (to_fp8<E5M2>(v[4 * i + 1] * sr) << 8) | (to_fp8<E5M2>(v[4 * i + 2] * sr) << 16) |
+               (static_cast<uint32_t>(to_fp8<E5M2>(v[4 * i + 3] * sr)) << 24);
+      *reinterpret_cast<uint4*>(out + static_cast<long long>(r) * C + c) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    if (out_t != nullptr) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) tile_t[lc + i][lr] = to_fp8<E5M2>(v[i] * s_col[s_col_stride ? c + i : 0]);
+    }
+  }
+  if (out_t == nullptr) return;
+  __syncthreads();
+  const int tc = c0 + lr, tr = r0 + lc;  // this thread writes 16 consecutive rows of column tc
+  if (tc < C && tr < R) *reinterpret_cast<uint4*>(out_t + static_cast<long long>(tc) * R + tr) = *reinterpret_cast<const uint4*>(&tile_t[lr][lc]);
+}
+
+}  // namespace ttb
+
+// x: [R, C] bf16 (row stride ldx, multiple of 8), R and C multiples of 16.  out: [R, C] fp8 or nullptr; out_t: [C, R] fp8 or nullptr.
+extern "C" int ttb_fp8_cast_transpose(const void* x, long long ldx, int R, int C, const void* s_row, int s_row_stride, void* out,
+                                      const void* s_col, int s_col_stride, void* out_t, int e5m2, void* stream) {
+  using namespace ttb;
+  if (R <= 0 || C <= 0 || (R & 15) || (C & 15) || (ldx & 7)) return kErrBadShape;
+  if ((out && !s_row) || (out_t && !s_col) || (!out && !out_t)) return kErrBadShape;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(out) & 15) || (reinterpret_cast<uintptr_t>(out_t) & 15)) return kErrBadShape;
+  dim3 grid((C + 63) / 64, (R + 63) / 64);
+  if (grid.y > 65535) return kErrTooLarge;
+  TTB_COUNT_LAUNCH(1);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (e5m2)
+    fp8_cast_transpose_kernel<true><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), ldx, R, C, static_cast<const float*>(s_row), s_row_stride,
+                                                         static_cast<uint8_t*>(out), static_cast<const float*>(s_col), s_col_stride, static_cast<uint8_t*>(out_t));
+  else
+    fp8_cast_transpose_kernel<false><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), ldx, R, C, static_cast<const float*>(s_row), s_row_stride,
+                                                          static_cast<uint8_t*>(out), static_cast<const float*>(s_col), s_col_stride, static_cast<uint8_t*>(out_t));
   return cudaGetLastError() == cudaSuccess ? kOk : kErrDriver;
 }

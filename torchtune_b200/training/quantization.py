@@ -290,13 +290,20 @@ def is_fp8_tensorwise_scaling(fp8_recipe_name: Optional[str]) -> bool:
 
 
 class Float8Linear(nn.Linear):
-    """Linear whose forward quantises activations and weights to e4m3 with dynamic scales
-    (one per tensor, or per row with the ``rowwise`` recipe) before the matmul; gradients use
-    the straight-through estimate in the original precision."""
+    """Linear with dynamically scaled fp8 operands (one scale per tensor, or per row with the ``rowwise`` recipe).
+
+    bf16 CUDA inputs run on the fp8 tensor cores (``ops.fp8_linear``: cast+transpose kernel, tcgen05 ``kind::f8f6f4`` GEMM for
+    forward, input gradient and weight gradient; e5m2 output gradients with tensorwise scaling).  Elsewhere the forward
+    quantise→dequantise round trip is emulated around the ordinary matmul with straight-through gradients."""
 
     recipe = "tensorwise"
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        from .. import ops
+
+        y = ops.fp8_linear(x, self.weight, self.bias, rowwise=self.recipe != "tensorwise")
+        if y is not None:
+            return y
         dims = None if self.recipe == "tensorwise" else -1
         xq = _fp8_roundtrip(x, dims)
         wq = _fp8_roundtrip(self.weight, dims)

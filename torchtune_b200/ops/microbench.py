@@ -62,6 +62,29 @@ def bench_gemm(args, flush):
     return res
 
 
+def bench_gemm_fp8(args, flush):
+    """fp8 (e4m3 × e4m3, tensorwise scales) GEMM alone, and the whole fp8 linear forward (amax + cast + GEMM) against the bf16 GEMM."""
+    from ._cuda import fp8_cast, fp8_linear, fp8_scales, gemm, gemm_fp8
+
+    m, n, k = args.m, args.n, args.k
+    bf = dict(device="cuda", dtype=torch.bfloat16)
+    a, b = torch.randn(m, k, **bf), torch.randn(n, k, **bf) * 0.05
+    sa, _ = fp8_scales(a, False, False)
+    sb, _ = fp8_scales(b, False, False)
+    aq, _ = fp8_cast(a, sa, sa, want_t=False)
+    bq, _ = fp8_cast(b, sb, sb, want_t=False)
+    ia, ib = 1.0 / sa, 1.0 / sb
+    out = torch.empty(m, n, **bf)
+    flops = 2.0 * m * n * k
+    t = _time(lambda: gemm_fp8(aq, bq, ia, ib, out=out), args.iters, args.warmup, flush)
+    t_cast = _time(lambda: fp8_cast(a, sa, sa), args.iters, args.warmup, flush)
+    with torch.no_grad():
+        t_lin = _time(lambda: fp8_linear(a, b, None, False), args.iters, args.warmup, flush)
+    t_bf16 = _time(lambda: gemm(a, b, out=out), args.iters, args.warmup, flush)
+    return {"op": "gemm_fp8_nt", "m": m, "n": n, "k": k, "ms": t, "tflops": flops / t / 1e9, "cast_transpose_ms": t_cast,
+            "cast_gbs": (m * k * 4) / t_cast / 1e6, "fp8_linear_fwd_ms": t_lin, "bf16_gemm_ms": t_bf16, "bf16_tflops": flops / t_bf16 / 1e9}
+
+
 def bench_attention(args, flush):
     from . import attention
     from .mask import AttentionMask
@@ -129,6 +152,10 @@ def main() -> None:
     g.add_argument("--k", type=int, default=4096)
     g.add_argument("--layout", choices=["nt", "nn", "tn"], default="nt")
     g.add_argument("--no-lib", action="store_true")
+    f = sub.add_parser("gemm_fp8")
+    f.add_argument("--m", type=int, default=8192)
+    f.add_argument("--n", type=int, default=4096)
+    f.add_argument("--k", type=int, default=4096)
     a = sub.add_parser("attention")
     a.add_argument("--batch", type=int, default=4)
     a.add_argument("--seq", type=int, default=2048)
@@ -145,7 +172,7 @@ def main() -> None:
     from ._lib import check_device_errors
 
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
-    fn = {"gemm": bench_gemm, "attention": bench_attention, "rmsnorm": bench_rmsnorm, "adamw": bench_adamw}[args.op]
+    fn = {"gemm": bench_gemm, "gemm_fp8": bench_gemm_fp8, "attention": bench_attention, "rmsnorm": bench_rmsnorm, "adamw": bench_adamw}[args.op]
     res = fn(args, flush)
     check_device_errors()
     print(json.dumps(res), flush=True)

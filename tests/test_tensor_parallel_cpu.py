@@ -101,3 +101,64 @@ def test_tp_decoder_matches_single_process():
         assert set(r["sd"]) == set(ref_sd)
         for key in ref_sd:
             assert torch.equal(r["sd"][key], ref_sd[key]), key
+
+
+# ----------------------------------------------------------------------------- mixture of experts under tensor parallelism
+MOE_ARCH = dict(vocab_size=64, num_layers=2, num_heads=4, num_kv_heads=2, embed_dim=32, hidden_dim=48, max_seq_len=32, num_experts=4, experts_per_token=2, rope_base=10000)
+
+
+def _moe_model():
+    from torchtune_b200.models.llama4 import llama4_decoder
+
+    model = llama4_decoder(**MOE_ARCH)
+    fixed_init_(model, std=0.1)
+    return model
+
+
+def _moe_worker(rank, world, port, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        tp = TensorParallelContext(torch.device("cpu"), max_rows_per_rank=8, max_width=48)
+        tpm = tensor_parallelize(_moe_model(), tp)
+        tokens, labels = _data()
+        logits = tpm(tokens)
+        loss = F.cross_entropy(logits.reshape(-1, 64), tpm.shard_rows(labels).reshape(-1), ignore_index=-100, reduction="sum")
+        loss.backward()
+        tpm.sync_replicated_grads()
+        total = loss.detach().clone()
+        dist.all_reduce(total)
+        with torch.no_grad():
+            infer = tpm.forward_inference(tokens)
+        mlp = tpm.layers[0].mlp
+        results[rank] = dict(
+            loss=total.item(), infer=infer, gate=mlp.experts.gate_proj.grad.clone(), down=mlp.experts.down_proj.grad.clone(), router=mlp.router.gate.weight.grad.clone(),
+            shared_w2=mlp.shared_expert.w2.grad.clone(), sd={k: v.clone() for k, v in tpm.full_state_dict().items()},
+        )
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tp_moe_decoder_matches_single_process():
+    world = 2
+    results = mp.Manager().dict()
+    mp.spawn(_moe_worker, args=(world, 29563, results), nprocs=world, join=True)
+    model = _moe_model()
+    tokens, labels = _data()
+    logits = model(tokens)
+    loss = F.cross_entropy(logits.reshape(-1, 64), labels.reshape(-1), ignore_index=-100, reduction="sum")
+    loss.backward()
+    grads = {k: p.grad for k, p in model.named_parameters()}
+    sd = model.state_dict()
+    per = 48 // world
+    for rank in range(world):
+        r = results[rank]
+        assert abs(r["loss"] - loss.item()) < 1e-3 * abs(loss.item())
+        torch.testing.assert_close(r["infer"], logits.detach().float(), rtol=1e-4, atol=1e-4)
+        torch.testing.assert_close(r["gate"], grads["layers.0.mlp.experts.gate_proj"][:, :, rank * per : (rank + 1) * per], rtol=1e-4, atol=1e-5)
+        torch.testing.assert_close(r["down"], grads["layers.0.mlp.experts.down_proj"][:, rank * per : (rank + 1) * per], rtol=1e-4, atol=1e-5)
+        torch.testing.assert_close(r["router"], grads["layers.0.mlp.router.gate.weight"], rtol=1e-4, atol=1e-5)
+        torch.testing.assert_close(r["shared_w2"], grads["layers.0.mlp.shared_expert.w2.weight"][:, rank * per : (rank + 1) * per], rtol=1e-4, atol=1e-5)
+        assert set(r["sd"]) == set(sd), set(r["sd"]) ^ set(sd)
+        for key in sd:
+            assert torch.equal(r["sd"][key], sd[key]), key

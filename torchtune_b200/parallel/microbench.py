@@ -14,6 +14,9 @@ Per shape it times, with CUDA events on the compute stream and the maximum over 
 MLP width (each rank holds ``hidden / world`` of it), i.e. the shapes of one Megatron-style MLP block
 (column-parallel w1/w3 then row-parallel w2, torchtune/models/llama3/_parallelism.py:33-59).
 Rank 0 prints one JSON line per measurement.
+
+``--op ep`` times the expert-parallel MoE layer instead (``--rows`` tokens over all ranks, ``--dim``, ``--hidden`` expert width,
+``--experts``, ``--top-k``): the plan / push / pull kernels, the layer forward and forward+backward.
 """
 from __future__ import annotations
 
@@ -45,8 +48,70 @@ def _time(fn, iters: int, warmup: int, flush: torch.Tensor) -> float:
     return float(t.item())
 
 
+def bench_ep(args, dev, world, rank) -> None:
+    """Expert-parallel MoE layer (Llama-4 Scout shapes by default): the exchange steps alone, the whole layer forward and
+    forward+backward, and NCCL ``all_to_all_single`` moving the same number of rows as a reference for the exchange."""
+    from ..models.llama4 import llama4_moe
+    from ..ops._lib import check_device_errors
+    from .ep import ExpertParallelContext, ExpertParallelMoE
+
+    T, dim, hid, E, k = args.rows // world, args.dim, args.hidden, args.experts, args.top_k
+    torch.manual_seed(0)
+    full = llama4_moe(dim=dim, hidden_dim=hid, num_experts=E, experts_per_token=k).to(dev).bfloat16()
+    ep = ExpertParallelContext(dev, None, num_experts=E, dim=dim, max_pairs=T * k, capacity_factor=args.capacity_factor)
+    moe = ExpertParallelMoE(full, ep)
+    del full
+    g = torch.Generator(device="cuda").manual_seed(rank)
+    x = (torch.randn(1, T, dim, generator=g, device=dev) * 0.5).bfloat16().requires_grad_()
+    dy = (torch.randn(1, T, dim, generator=g, device=dev) * 0.1).bfloat16()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    flat = x.detach().reshape(T, dim)
+    with torch.no_grad():
+        scores, token_idx, counts = moe.router(flat)
+    plan = ep.plan(counts, T * k)
+    y_local = torch.zeros(ep.capacity, dim, dtype=torch.bfloat16, device=dev)
+    send = torch.empty(T * k, dim, dtype=torch.bfloat16, device=dev)
+    recv = torch.empty_like(send)
+
+    def fwd_bwd():
+        x.grad = None
+        moe(x).backward(dy)
+
+    def fwd():
+        with torch.no_grad():
+            moe(x)
+
+    def nccl_a2a():  # balanced all-to-all of the same number of rows (gather + send; no re-permutation)
+        torch.index_select(flat, 0, token_idx, out=send)
+        dist.all_to_all_single(recv, send)
+
+    results = []
+    for name, fn in (
+        ("ep_plan", lambda: ep.plan(counts, T * k)),
+        ("ep_dispatch_push", lambda: ep.push(flat, token_idx, scores, plan)),
+        ("ep_combine_publish_pull", lambda: (ep.publish_result(y_local), ep.pull(plan, torch.bfloat16))),
+        ("nccl_gather_all_to_all", nccl_a2a),
+        ("ep_moe_forward", fwd),
+        ("ep_moe_forward_backward", fwd_bwd),
+    ):
+        ms = _time(fn, args.iters, args.warmup, flush)
+        results.append({"op": name, "world": world, "tokens_per_rank": T, "dim": dim, "hidden": hid, "experts": E, "top_k": k, "ms": round(ms, 4)})
+    check_device_errors()
+    row_bytes = T * k * dim * 2 * (world - 1) / world
+    if rank == 0:
+        for r in results:
+            if r["op"] in ("ep_dispatch_push", "nccl_gather_all_to_all"):
+                r["nvlink_gbs_per_gpu"] = round(row_bytes / r["ms"] / 1e6, 1)
+            print(json.dumps(r))
+    ep.close()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--op", choices=["tp", "ep"], default="tp")
+    ap.add_argument("--experts", type=int, default=16)
+    ap.add_argument("--top-k", type=int, default=1)
+    ap.add_argument("--capacity-factor", type=float, default=None)
     ap.add_argument("--rows", type=int, default=4096)
     ap.add_argument("--dim", type=int, default=8192)
     ap.add_argument("--hidden", type=int, default=28672)
@@ -59,6 +124,11 @@ def main() -> None:
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     world, rank = dist.get_world_size(), dist.get_rank()
     dev = torch.device("cuda", local)
+
+    if args.op == "ep":
+        bench_ep(args, dev, world, rank)
+        dist.destroy_process_group()
+        return
 
     from ..ops._cuda import gemm
     from ..ops._lib import check_device_errors

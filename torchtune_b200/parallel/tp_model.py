@@ -148,12 +148,100 @@ class TPMLP(nn.Module):
         }
 
 
+class _GatherRows(torch.autograd.Function):
+    """Sequence-sharded rows → all rows (backward: sum over ranks, keep own rows)."""
+
+    @staticmethod
+    def forward(ctx, x, tp: TensorParallelContext):
+        ctx.tp = tp
+        return tp.all_gather_rows(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        return ctx.tp.reduce_scatter_rows(g.contiguous()), None
+
+
+class _ScatterSumRows(torch.autograd.Function):
+    """Per-rank partial results for all rows → summed rows of this rank (backward: all-gather)."""
+
+    @staticmethod
+    def forward(ctx, x, tp: TensorParallelContext):
+        ctx.tp = tp
+        return tp.reduce_scatter_rows(x.contiguous())
+
+    @staticmethod
+    def backward(ctx, g):
+        return ctx.tp.all_gather_rows(g.contiguous()), None
+
+
+class TPMoE(nn.Module):
+    """Expert tensor parallelism (reference plan: torchtune/modules/moe/_parallelism.py:26-93 and
+    torchtune/models/llama4/_parallelism.py:77-92): every rank holds all experts but only ``hidden / tp`` of each expert's
+    width (``gate_proj`` / ``up_proj`` split on their last dimension, ``down_proj`` on its first); router and routing are
+    replicated, so every rank routes the gathered tokens identically and produces a partial sum of the layer output that is
+    reduce-scattered back to sequence-sharded rows.  The shared expert is split the same way."""
+
+    def __init__(self, moe: nn.Module, tp: TensorParallelContext):
+        super().__init__()
+        from ..modules.moe import GroupedExperts
+
+        src = moe.experts
+        if not isinstance(src, GroupedExperts):
+            raise NotImplementedError("tensor parallelism supports un-adapted grouped experts")
+        w, r = tp.world, tp.rank
+        if src.hidden_dim % w:
+            raise ValueError(f"tensor parallel size {w} must divide the expert width {src.hidden_dim}")
+        per = src.hidden_dim // w
+        self.tp = tp
+        self.router = moe.router
+        local = GroupedExperts(dim=src.dim, hidden_dim=per, num_experts=src.num_experts, activation=src.act_fn)
+        local.gate_proj = nn.Parameter(src.gate_proj.data[:, :, r * per : (r + 1) * per].contiguous())
+        local.up_proj = nn.Parameter(src.up_proj.data[:, :, r * per : (r + 1) * per].contiguous())
+        local.down_proj = nn.Parameter(src.down_proj.data[:, r * per : (r + 1) * per, :].contiguous())
+        self.experts = local
+        self.shared_expert = TPMLP(moe.shared_expert, tp) if moe.shared_expert is not None else None
+
+    def _partial(self, flat: torch.Tensor) -> torch.Tensor:
+        scores, token_idx, counts = self.router(flat)
+        routed = self.experts(flat.index_select(0, token_idx) * scores.reshape(-1, 1), counts)
+        out = self.shared_expert.forward_replicated(flat) if self.shared_expert is not None else torch.zeros_like(flat)
+        return out.index_add(0, token_idx, routed.to(out.dtype))
+
+    def forward(self, hn: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+        full = _GatherRows.apply(hn, self.tp)
+        return _ScatterSumRows.apply(self._partial(full), self.tp) + residual
+
+    def forward_replicated(self, hn: torch.Tensor) -> torch.Tensor:
+        return self._partial(hn.reshape(-1, hn.shape[-1])).reshape(hn.shape)
+
+    def replicated_parameters(self) -> List[nn.Parameter]:
+        return list(self.router.parameters())
+
+    def gather_full(self, prefix: str) -> Dict[str, torch.Tensor]:
+        tp = self.tp
+
+        def cat(t: torch.Tensor, dim: int) -> torch.Tensor:  # gather along `dim` through the row gather
+            moved = t.movedim(dim, 0).contiguous()
+            return tp.all_gather_rows(moved).movedim(0, dim).contiguous()
+
+        out = {f"{prefix}router.{k}": v.detach() for k, v in self.router.state_dict().items()}
+        out[f"{prefix}experts.gate_proj"] = cat(self.experts.gate_proj.data, 2)
+        out[f"{prefix}experts.up_proj"] = cat(self.experts.up_proj.data, 2)
+        out[f"{prefix}experts.down_proj"] = cat(self.experts.down_proj.data, 1)
+        if self.shared_expert is not None:
+            out.update(self.shared_expert.gather_full(f"{prefix}shared_expert."))
+        return out
+
+
 class TPLayer(nn.Module):
     def __init__(self, layer: TransformerSelfAttentionLayer, tp: TensorParallelContext):
         super().__init__()
         if not isinstance(layer.sa_scale, nn.Identity) or not isinstance(layer.mlp_scale, nn.Identity):
             raise NotImplementedError("tensor parallelism does not support post-norm / gated residual layers")
-        self.attn, self.mlp = TPAttention(layer.attn, tp), TPMLP(layer.mlp, tp)
+        from ..modules.moe import MoE
+
+        self.attn = TPAttention(layer.attn, tp)
+        self.mlp = TPMoE(layer.mlp, tp) if isinstance(layer.mlp, MoE) else TPMLP(layer.mlp, tp)
         self.sa_norm, self.mlp_norm = layer.sa_norm, layer.mlp_norm
         self.mask_mod = layer.mask_mod
 
@@ -185,6 +273,8 @@ class TPDecoder(nn.Module):
         self._replicated = [p for m in (self.tok_embeddings, self.norm, self.output) for p in m.parameters()]
         for layer in self.layers:
             self._replicated += list(layer.sa_norm.parameters()) + list(layer.mlp_norm.parameters())
+            if isinstance(layer.mlp, TPMoE):
+                self._replicated += layer.mlp.replicated_parameters()
         seen = set()
         self._replicated = [p for p in self._replicated if not (id(p) in seen or seen.add(id(p)))]
 
@@ -273,6 +363,15 @@ def tensor_parallelize(model: TransformerDecoder, tp: TensorParallelContext, act
     out = TPDecoder(model, tp, activation_checkpointing)
     for layer in model.layers:
         inner = getattr(layer, "inner", layer)
-        for proj in (inner.attn.q_proj, inner.attn.k_proj, inner.attn.v_proj, inner.attn.output_proj, inner.mlp.w1, inner.mlp.w2, inner.mlp.w3):
+        projs = [inner.attn.q_proj, inner.attn.k_proj, inner.attn.v_proj, inner.attn.output_proj]
+        mlp = inner.mlp
+        if hasattr(mlp, "experts"):  # mixture of experts: the full expert stacks and the shared expert were copied in slices
+            for name in ("gate_proj", "up_proj", "down_proj"):
+                w = getattr(mlp.experts, name)
+                w.data = torch.empty(0, dtype=w.dtype, device=w.device)
+            mlp = mlp.shared_expert
+        if mlp is not None:
+            projs += [mlp.w1, mlp.w2, mlp.w3]
+        for proj in projs:
             proj.weight.data = torch.empty(0, dtype=proj.weight.dtype, device=proj.weight.device)
     return out

@@ -148,10 +148,11 @@ def test_qlora_linear_trains_on_gpu():
     assert torch.isfinite(y).all() and torch.isfinite(x.grad).all()
 
 
-@pytest.mark.parametrize("counts", [[128, 128, 128, 128], [5, 0, 300, 77], [0, 0, 0, 513], [1, 1, 1, 1]])
-def test_grouped_matmul_matches_loop(counts):
+@pytest.mark.parametrize("counts,K,N", [([128, 128, 128, 128], 192, 320), ([5, 0, 300, 77], 192, 320), ([0, 0, 0, 513], 192, 320), ([1, 1, 1, 1], 192, 320),
+                                        ([700, 64, 0, 1, 333, 129, 63, 1000], 1024, 1536)])
+def test_grouped_matmul_matches_loop(counts, K, N):
     g = torch.Generator(device="cuda").manual_seed(1)
-    E, K, N = len(counts), 192, 320
+    E = len(counts)
     rows = sum(counts)
     x = (torch.randn(rows, K, generator=g, device="cuda") * 0.5).bfloat16().requires_grad_()
     w = (torch.randn(E, K, N, generator=g, device="cuda") * 0.1).bfloat16().requires_grad_()

@@ -169,7 +169,8 @@ def _grouped_gemm(x: torch.Tensor, w: torch.Tensor, counts: torch.Tensor, b_mn: 
 
 class _GroupedMatmul(torch.autograd.Function):
     """``y[rows of e] = x[rows of e] · w[e]`` with ``w`` ``[E, K, N]``.  Forward and the input gradient are single grouped launches;
-    the weight gradient runs one TN GEMM per expert (its reduction dimension is the ragged one)."""
+    so is the weight gradient, whose *reduction* dimension is the ragged one (rows of the next expert that share a 64-row block are
+    zeroed in shared memory before the MMAs)."""
 
     @staticmethod
     def forward(ctx, x, w, counts):
@@ -185,12 +186,13 @@ class _GroupedMatmul(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = _grouped_gemm(dy, w, counts, b_mn=False)  # per expert dy·w[e]ᵀ: w[e] read as [K_out, N_red] K-major
         if ctx.needs_input_grad[1]:
-            dw = torch.zeros_like(w)
-            start = 0
-            for e, n in enumerate(counts.tolist()):
-                if n:
-                    gemm(x[start : start + n], dy[start : start + n], a_mn=True, b_mn=True, out=dw[e])
-                start += n
+            # one launch for all experts; the ragged reduction ranges come from the device-resident counts (no host read)
+            E, K, N = w.shape
+            xc = x if (x.stride(1) == 1 and x.stride(0) % 8 == 0) else x.contiguous()
+            dw = torch.empty_like(w)
+            cnt = counts.to(torch.int64).contiguous()
+            check(lib().ttb_gemm_grouped_wgrad_bf16(xc.data_ptr(), dy.data_ptr(), dw.data_ptr(), cnt.data_ptr(), x.shape[0], E, K, N, xc.stride(0), dy.stride(0),
+                                                    N, K * N, 0, err_word(x.device).data_ptr(), stream_ptr()), "gemm_grouped_wgrad")
         return dx, dw, None
 
 

@@ -85,11 +85,20 @@ struct GroupArgs {
   const int* tile_row0;
   const int* tile_rows;
   const int* num_m_tiles;  // device scalar
+  // TP == 4 (grouped weight gradient): dW[e][M, N] = A_eᵀ · B_e where A is [rows, M] and B is [rows, N] (both MN-major operands)
+  // and expert e owns `counts[e]` consecutive rows — the *reduction* dimension is the ragged one.  Tiles are (expert, m, n);
+  // every CTA derives the experts' row ranges from `counts` itself (no host read).  The last 64-row block of an expert also
+  // brings in rows of the next expert: the MMA warp zeroes those rows in shared memory (whole 128-byte rows, which the swizzle
+  // keeps intact) before issuing.  Experts without rows get a zero gradient.
+  const long long* counts;
+  int num_experts;
+  long long c_expert_stride;
 };
+static constexpr int kMaxGroupedExperts = 1024;
 
 template <int TP>
 __device__ __forceinline__ int tp_rotate_m(int m_blk, int num_m, const TpArgs* tp) {
-  if (TP == 0 || TP == 3) return m_blk;
+  if (TP == 0 || TP == 3 || TP == 4) return m_blk;
   const int tiles_per_rank = tp->rows_per_rank / BM;
   const int first = (TP == 1 ? tp->rank : (tp->rank + 1) % tp->world) * tiles_per_rank;
   const int r = m_blk + first;
@@ -137,8 +146,20 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
   const int lane = threadIdx.x & 31;
   const int num_m = TP == 3 ? *ga->num_m_tiles : (p.M + BM - 1) / BM;
   const int num_n = (p.N + BN - 1) / BN;
-  const int num_tiles = num_m * num_n;
+  const int num_tiles = TP == 4 ? ga->num_experts * num_m * num_n : num_m * num_n;
   const int num_kb = (p.K + BK - 1) / BK;
+  // TP 4: first row and row count of every expert, after the barrier region
+  int* g_row0 = reinterpret_cast<int*>(smem + Cfg::kStages * Cfg::kStageBytes + 256);
+  int* g_cnt = g_row0 + kMaxGroupedExperts;
+  if (TP == 4 && threadIdx.x == 32) {
+    int run = 0;
+    for (int e = 0; e < ga->num_experts; ++e) {
+      const int c = static_cast<int>(ga->counts[e]);
+      g_row0[e] = run;
+      g_cnt[e] = c;
+      run += c;
+    }
+  }
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < Cfg::kStages; ++i) {
@@ -194,7 +215,16 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
         a_row = ga->tile_row0[m_blk];
         expert = ga->tile_expert[m_blk];
       }
-      for (int kb = 0; kb < num_kb; ++kb) {
+      int kb_count = num_kb, k_row0 = 0;
+      if (TP == 4) {
+        expert = t / (num_m * num_n);
+        const int r = t - expert * (num_m * num_n);
+        m_blk = r % num_m;
+        n_blk = r / num_m;
+        k_row0 = g_row0[expert];
+        kb_count = (g_cnt[expert] + BK - 1) / BK;
+      }
+      for (int kb = 0; kb < kb_count; ++kb) {
         if (!mbar_wait(&empty[stage], phase ^ 1)) {
           *abort_flag = 1;
           if (lane == 0) atomicExch(p.err, 101);
@@ -206,7 +236,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
           mbar_arrive_expect_tx(&full[stage], Cfg::kStageBytes);
           if (A_MN) {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, &tmA, &full[stage], m_blk * BM + j * 64, kb * BK);
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, &tmA, &full[stage], m_blk * BM + j * 64, k_row0 + kb * BK);
           } else {
             tma_load_2d(sa, mapA, &full[stage], kb * BK, a_row);
           }
@@ -219,7 +249,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
             }
           } else if (B_MN) {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tmB, &full[stage], n_blk * BN + j * 64, kb * BK);
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tmB, &full[stage], n_blk * BN + j * 64, k_row0 + kb * BK);
           } else {
             tma_load_2d(sb, &tmB, &full[stage], kb * BK, n_blk * BN);
           }
@@ -247,10 +277,28 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + acc * BN;
       bool ok = true;
-      for (int kb = 0; kb < num_kb; ++kb) {
+      int kb_count = num_kb, tail_rows = 0;
+      if (TP == 4) {
+        const int cnt = g_cnt[t / (num_m * num_n)];
+        kb_count = (cnt + BK - 1) / BK;
+        tail_rows = cnt % BK;  // valid rows of the last block (0: the block is full)
+      }
+      for (int kb = 0; kb < kb_count; ++kb) {
         if (!mbar_wait(&full[stage], phase)) {
           ok = false;
           break;
+        }
+        if (TP == 4 && tail_rows != 0 && kb == kb_count - 1) {
+          // rows [tail_rows, 64) of every 64-column box belong to the next expert: zero them (16 bytes per lane and step)
+          uint8_t* st = smem + stage * Cfg::kStageBytes;
+          constexpr int kBoxes = BM / 64 + BN / 64;
+          const int chunks = (BK - tail_rows) * 8;  // 16-byte chunks per box
+          for (int i = lane; i < chunks * kBoxes; i += 32) {
+            const int box = i / chunks, c = i - box * chunks;
+            *reinterpret_cast<uint4*>(st + box * 8192 + tail_rows * 128 + c * 16) = make_uint4(0, 0, 0, 0);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
         }
         tc_fence_after();
         if (lane == 0) {
@@ -301,6 +349,15 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
         break;
       }
       tc_fence_after();
+      int expert = 0;
+      bool empty_expert = false;
+      if (TP == 4) {
+        expert = t / (num_m * num_n);
+        const int r = t - expert * (num_m * num_n);
+        m_blk = r % num_m;
+        n_blk = r / num_m;
+        empty_expert = g_cnt[expert] == 0;  // no MMA ran: the accumulator holds stale values
+      }
       int row = m_blk * BM + quarter * 32 + lane;
       bool row_ok = row < p.M;
       if (TP == 3) {
@@ -317,7 +374,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
         if (row_ok && col0 < p.N) {
           float v[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+          for (int i = 0; i < 32; ++i) v[i] = (TP == 4 && empty_expert) ? 0.f : __uint_as_float(r[i]) * p.alpha;
           if (p.bias != nullptr) {
 #pragma unroll
             for (int i = 0; i < 32; ++i)
@@ -342,6 +399,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
               const int owner = row / tp->rows_per_rank;
               const long long slot_row = static_cast<long long>(tp->rank) * tp->rows_per_rank + (row - owner * tp->rows_per_rank);
               dst = reinterpret_cast<__nv_bfloat16*>(tp->C[owner]) + slot_row * p.ldc + col0;
+            } else if (TP == 4) {
+              dst = reinterpret_cast<__nv_bfloat16*>(p.C) + expert * ga->c_expert_stride + static_cast<long long>(row) * p.ldc + col0;
             } else {
               dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
             }
@@ -440,6 +499,12 @@ template <int BN, bool B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_grouped_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p, GroupArgs ga) {
   gemm_body<BN, false, B_MN, 3>(&tmA, &tmB, p, nullptr, &ga);
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_grouped_wgrad_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p, GroupArgs ga) {
+  gemm_body<BN, true, true, 4>(&tmA, &tmB, p, nullptr, &ga);
 }
 
 // One block: exclusive scan of the per-expert row counts, then one m-tile entry per 128 rows of every expert.
@@ -700,6 +765,52 @@ extern "C" int ttb_rs_reduce(const void* staging, const void* residual, const vo
   return cudaGetLastError() == cudaSuccess ? kOk : kErrDriver;
 }
 
+namespace ttb {
+template <int BN>
+static int launch_grouped_wgrad(const void* A, const void* B, const GemmParams& p, long long rows, long long lda, long long ldb, const GroupArgs& ga,
+                                cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  CUtensorMap tmA, tmB;
+  // both operands are [rows, width] row-major read as MN-major: tensor [rows(k), width], box [64 k-rows, 64]
+  int rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows, p.M, lda, BK, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != kOk) return rc;
+  rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows, p.N, ldb, BK, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != kOk) return rc;
+  auto kern = gemm_grouped_wgrad_kernel<BN>;
+  constexpr int smem = Cfg::kSmemBytes + 2 * kMaxGroupedExperts * static_cast<int>(sizeof(int));
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return kErrDriver;
+    attr_set = true;
+  }
+  const long long tiles = static_cast<long long>(ga.num_experts) * ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int grid = tiles < sm_count() ? static_cast<int>(tiles) : sm_count();
+  TTB_COUNT_LAUNCH(1);
+  kern<<<grid, kThreads, smem, stream>>>(tmA, tmB, p, ga);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrDriver;
+}
+}  // namespace ttb
+
+// Grouped weight gradient: dW[e][M, N] (+)= A[rows of e, M]ᵀ · B[rows of e, N]; `counts` is a device array of E int64 row counts
+// (rows of expert e contiguous, in expert order); dW is [E, M, N] bf16 with row stride ldc and expert stride c_expert_stride.
+extern "C" int ttb_gemm_grouped_wgrad_bf16(const void* A, const void* B, void* dW, const void* counts, long long rows, int num_experts, int M,
+                                           int N, long long lda, long long ldb, long long ldc, long long c_expert_stride, int accumulate,
+                                           int* err, void* stream) {
+  using namespace ttb;
+  if (rows <= 0 || num_experts <= 0 || num_experts > kMaxGroupedExperts || M <= 0 || N <= 0) return kErrBadShape;
+  if ((lda & 7) || (ldb & 7) || (ldc & 7) || (M & 7) || (N & 7) || (c_expert_stride & 7)) return kErrBadShape;
+  GroupArgs ga;
+  memset(&ga, 0, sizeof(ga));
+  ga.counts = static_cast<const long long*>(counts), ga.num_experts = num_experts, ga.c_expert_stride = c_expert_stride;
+  GemmParams p;
+  p.M = M, p.N = N, p.K = 0, p.C = dW, p.ldc = ldc;
+  p.bias = nullptr, p.alpha = 1.f, p.out_fp32 = 0, p.accumulate = accumulate, p.err = err;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (N > 128) return launch_grouped_wgrad<256>(A, B, p, rows, lda, ldb, ga, s);
+  if (N > 64) return launch_grouped_wgrad<128>(A, B, p, rows, lda, ldb, ga, s);
+  return launch_grouped_wgrad<64>(A, B, p, rows, lda, ldb, ga, s);
+}
+
 // Grouped GEMM: C[rows, N] = A[rows, K] · op(B[e]) for the rows of each expert e.  `counts` is a device array of E int64 row
 // counts (rows of expert e are contiguous, in expert order).  `tile_scratch` is a device int array of 3·max_tiles + 1 entries
 // with max_tiles = ceil(rows / 128) + E.  b_mn = 0: B[e] is [N, K] row-major; 1: B[e] is [K, N] row-major.
@@ -712,6 +823,7 @@ extern "C" int ttb_gemm_grouped_bf16(const void* A, const void* B, void* C, cons
   const int max_tiles = static_cast<int>((rows + BM - 1) / BM) + num_experts;
   int* scratch = static_cast<int*>(tile_scratch);
   GroupArgs ga;
+  memset(&ga, 0, sizeof(ga));
   ga.tile_expert = scratch;
   ga.tile_row0 = scratch + max_tiles;
   ga.tile_rows = scratch + 2 * max_tiles;

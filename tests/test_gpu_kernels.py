@@ -299,7 +299,7 @@ def test_dp_reduce_adamw_bcast_emulated_ranks(world):
     pp = (ctypes.c_void_p * world)(*[t.data_ptr() for t in params])
     lr, b1, b2, eps, wd, scale = 1e-2, 0.9, 0.999, 1e-8, 0.1, 0.25
     for r in range(world):
-        check(L.ttb_dp_reduce_adamw_bcast(gp, pp, world, r, r * shard, shard, m[r].data_ptr(), v[r].data_ptr(), None, None, None, scale, lr, b1, b2, eps, wd, 1.0 / (1 - b1), 1.0 / math.sqrt(1 - b2), 0, stream_ptr()), "dp kernel")
+        check(L.ttb_dp_reduce_adamw_bcast(gp, pp, world, r, r * shard, shard, m[r].data_ptr(), v[r].data_ptr(), None, None, None, scale, lr, b1, b2, eps, wd, 1.0 / (1 - b1), 1.0 / math.sqrt(1 - b2), 0, None, 0, 0, None, stream_ptr()), "dp kernel")
     torch.cuda.synchronize()
     gsum = torch.stack([t.float() for t in grads]).sum(0) * scale
     want = p0.float().clone()
@@ -317,12 +317,12 @@ def test_dp_reduce_adamw_bcast_emulated_ranks(world):
     gs = [torch.empty(shard, dtype=torch.float32, device="cuda") for _ in range(world)]
     parts = [torch.empty(L.ttb_dp_grid(), dtype=torch.float32, device="cuda") for _ in range(world)]
     for r in range(world):
-        check(L.ttb_dp_reduce_adamw_bcast(gp, pp2, world, r, r * shard, shard, m2[r].data_ptr(), v2[r].data_ptr(), gs[r].data_ptr(), parts[r].data_ptr(), None, 1.0, lr, b1, b2, eps, wd, 1.0, 1.0, 1, stream_ptr()), "dp reduce")
+        check(L.ttb_dp_reduce_adamw_bcast(gp, pp2, world, r, r * shard, shard, m2[r].data_ptr(), v2[r].data_ptr(), gs[r].data_ptr(), parts[r].data_ptr(), None, 1.0, lr, b1, b2, eps, wd, 1.0, 1.0, 1, None, 0, 0, None, stream_ptr()), "dp reduce")
     norm = torch.stack([p.sum() for p in parts]).sum().sqrt() * scale
     _close(norm, gsum.norm(), 1e-3, 1e-3, "global norm")
     coef = (torch.clamp(1.0 / (norm + 1e-6), max=1.0) * scale).reshape(1).float()
     for r in range(world):
-        check(L.ttb_dp_reduce_adamw_bcast(gp, pp2, world, r, r * shard, shard, m2[r].data_ptr(), v2[r].data_ptr(), gs[r].data_ptr(), None, coef.data_ptr(), 1.0, lr, b1, b2, eps, wd, 1.0 / (1 - b1), 1.0 / math.sqrt(1 - b2), 2, stream_ptr()), "dp update")
+        check(L.ttb_dp_reduce_adamw_bcast(gp, pp2, world, r, r * shard, shard, m2[r].data_ptr(), v2[r].data_ptr(), gs[r].data_ptr(), None, coef.data_ptr(), 1.0, lr, b1, b2, eps, wd, 1.0 / (1 - b1), 1.0 / math.sqrt(1 - b2), 2, None, 0, 0, None, stream_ptr()), "dp update")
     want2 = p0.float().clone()
     mm, vv = torch.zeros(total, device="cuda"), torch.zeros(total, device="cuda")
     ref.adamw_step(want2, gsum * float(torch.clamp(1.0 / (gsum.norm() + 1e-6), max=1.0)), mm, vv, 1, lr, b1, b2, eps, wd)
@@ -427,11 +427,12 @@ def test_gemm_all_gather_fused_emulated_ranks(world, rows, K, N, b_mn):
     check_device_errors()
 
 
-@pytest.mark.parametrize("world", [1, 2, 4, 8])
+@pytest.mark.parametrize("world,rows,K,N", [(1, 128, 192, 256), (2, 128, 192, 256), (4, 128, 192, 256), (8, 128, 192, 256), (2, 1024, 256, 3072), (4, 256, 320, 200)])
 @pytest.mark.parametrize("b_mn", [False, True])
-def test_gemm_reduce_scatter_fused_emulated_ranks(world, b_mn):
+def test_gemm_reduce_scatter_fused_emulated_ranks(world, rows, K, N, b_mn):
+    """The large shape gives every persistent CTA several tiles (staging buffers of the TMA-store epilogue are reused); N = 200
+    ends inside a 64-column store box (clipped by the tensor map)."""
     L, ctypes, err_word, stream_ptr = _tp_lib()
-    rows, K, N = 128, 192, 256
     T = world * rows
     staging = [torch.full((world, rows, N), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
     ptrs = (ctypes.c_void_p * world)(*[s.data_ptr() for s in staging])

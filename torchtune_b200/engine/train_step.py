@@ -40,15 +40,21 @@ class TrainStep:
         labels = batch.pop("labels")
         hidden = self.model(**batch)
         loss_sum, n_valid = self.loss_fn.compute_sum(hidden, labels)
-        loss_sum.backward()
         n_tokens = n_valid.to(torch.float32)
         if self.parallel is not None:
-            loss_sum = loss_sum.detach().clone()
-            self.parallel.all_reduce_sum_(n_tokens, loss_sum)
-            self.parallel.optimizer_step(self.model, self.optimizer, 1.0 / n_tokens, self.clip_grad_norm)
-        else:
-            self.optimizer.step(grad_scale=1.0 / n_tokens, max_grad_norm=self.clip_grad_norm)
-            self.optimizer.zero_grad(set_to_none=True)
+            # the global token count is known before backward, so the optimizer can consume each layer's gradients while
+            # backward is still running on the earlier layers
+            total = loss_sum.detach().clone()
+            self.parallel.all_reduce_sum_(n_tokens, total)
+            scale = 1.0 / n_tokens
+            if hasattr(self.parallel, "arm_backward_overlap"):
+                self.parallel.arm_backward_overlap(self.optimizer, scale, self.clip_grad_norm)
+            loss_sum.backward()
+            self.parallel.optimizer_step(self.model, self.optimizer, scale, self.clip_grad_norm)
+            return total / n_tokens
+        loss_sum.backward()
+        self.optimizer.step(grad_scale=1.0 / n_tokens, max_grad_norm=self.clip_grad_norm)
+        self.optimizer.zero_grad(set_to_none=True)
         return loss_sum.detach() / n_tokens
 
     def __call__(self, host_batch: Dict[str, Any]) -> torch.Tensor:

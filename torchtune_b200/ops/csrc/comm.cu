@@ -43,6 +43,25 @@ __device__ __forceinline__ uint4 pack8f(const float (&f)[8]) {
   return u;
 }
 
+// Cross-rank "bucket is final" flags (no collective library involved, so nothing has to be scheduled next to the persistent
+// GEMM kernels but two small kernels of this file): rank p stores `epoch` into flags_q[p][slot] on every peer q once its
+// gradients of bucket `slot` are complete (dp_signal_kernel, stream-ordered after the layer's backward); the reduce kernel of
+// rank q waits, with a cycle budget, until all peers' entries for that slot have reached the epoch.
+static constexpr int kMaxBuckets = 4096;
+static constexpr long long kFlagWaitCycles = 4000000000LL;
+
+struct FlagTable {
+  int* flags[kMaxRanks];
+};
+
+__global__ void dp_signal_kernel(FlagTable t, int world, int rank, int slot, int epoch) {
+  __threadfence_system();
+  if (threadIdx.x < world && threadIdx.x != rank) {
+    int* dst = t.flags[threadIdx.x] + rank * kMaxBuckets + slot;
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(dst), "r"(epoch) : "memory");
+  }
+}
+
 // mode 0: reduce + AdamW + broadcast in one pass.
 // mode 1: reduce only -> reduced fp32 gradient into `gsum` (shard-local) and per-block partial
 //         sums of squares into `sumsq_partials` (for global-norm clipping).
@@ -52,8 +71,31 @@ __global__ void __launch_bounds__(256)
 dp_reduce_adamw_bcast_kernel(PeerTable peers, int rank, long long begin, long long count, __nv_bfloat16* __restrict__ m,
                              __nv_bfloat16* __restrict__ v, float* __restrict__ gsum, float* __restrict__ sumsq_partials,
                              const float* __restrict__ scale_dev, float scale_host, float lr, float beta1, float beta2,
-                             float eps, float weight_decay, float inv_bc1, float inv_sqrt_bc2, int mode) {
+                             float eps, float weight_decay, float inv_bc1, float inv_sqrt_bc2, int mode,
+                             const int* __restrict__ my_flags, int slot, int epoch, int* __restrict__ err) {
   __shared__ float red[8];
+  __shared__ int give_up;
+  if (my_flags != nullptr) {  // wait until every peer has declared this bucket final
+    if (threadIdx.x == 0) give_up = 0;
+    __syncthreads();
+    if (threadIdx.x < WORLD && threadIdx.x != rank) {
+      const int* f = my_flags + threadIdx.x * kMaxBuckets + slot;
+      const long long t0 = clock64();
+      int v;
+      unsigned spins = 0;
+      while (true) {
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+        if (v >= epoch) break;
+        if ((++spins & 0xff) == 0 && clock64() - t0 > kFlagWaitCycles) {
+          give_up = 1;
+          atomicExch(err, 201);
+          break;
+        }
+      }
+    }
+    __syncthreads();
+    if (give_up) return;
+  }
   const float gs = scale_host * (scale_dev != nullptr ? *scale_dev : 1.f);
   const long long nvec = count >> 3;  // shards are multiples of 8 elements
   float sq = 0.f;
@@ -160,8 +202,10 @@ extern "C" int ttb_dp_reduce_adamw_bcast(void* const* grad_ptrs, void* const* pa
                                          long long begin, long long count, void* m, void* v, float* gsum,
                                          float* sumsq_partials, const float* scale_dev, float scale_host, float lr,
                                          float beta1, float beta2, float eps, float weight_decay, float inv_bc1,
-                                         float inv_sqrt_bc2, int mode, void* stream) {
+                                         float inv_sqrt_bc2, int mode, const int* my_flags, int slot, int epoch, int* err,
+                                         void* stream) {
   if (world < 1 || world > kMaxRanks || (begin & 7) || (count & 7)) return kErrBadShape;
+  if (my_flags != nullptr && (slot < 0 || slot >= kMaxBuckets || err == nullptr)) return kErrBadShape;
   if (count == 0) return kOk;
   PeerTable t{};
   for (int r = 0; r < world; ++r) {
@@ -177,7 +221,7 @@ extern "C" int ttb_dp_reduce_adamw_bcast(void* const* grad_ptrs, void* const* pa
   case W:                                                                                                           \
     dp_reduce_adamw_bcast_kernel<W><<<grid, 256, 0, s>>>(t, rank, begin, count, mm, vv, gsum, sumsq_partials,       \
                                                          scale_dev, scale_host, lr, beta1, beta2, eps, weight_decay, \
-                                                         inv_bc1, inv_sqrt_bc2, mode);                               \
+                                                         inv_bc1, inv_sqrt_bc2, mode, my_flags, slot, epoch, err);   \
     break;
   switch (world) {
     TTB_DP_CASE(1)
@@ -193,3 +237,15 @@ extern "C" int ttb_dp_reduce_adamw_bcast(void* const* grad_ptrs, void* const* pa
 #undef TTB_DP_CASE
   return cudaGetLastError() == cudaSuccess ? kOk : kErrDriver;
 }
+
+// flag_ptrs: `world` device pointers, rank q's flag array int[world][4096] (peer-mapped).  Stores `epoch` into entry [rank][slot]
+// of every peer's array; stream order makes it follow the work that completes this rank's gradients of that bucket.
+extern "C" int ttb_dp_signal(void* const* flag_ptrs, int world, int rank, int slot, int epoch, void* stream) {
+  if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world || slot < 0 || slot >= kMaxBuckets) return kErrBadShape;
+  FlagTable t{};
+  for (int r = 0; r < world; ++r) t.flags[r] = static_cast<int*>(flag_ptrs[r]);
+  TTB_COUNT_LAUNCH(1);
+  dp_signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(t, world, rank, slot, epoch);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrDriver;
+}
+extern "C" int ttb_dp_max_buckets() { return kMaxBuckets; }

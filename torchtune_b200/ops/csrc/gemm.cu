@@ -35,25 +35,30 @@ struct GemmParams {
   int out_fp32;    // 0: bf16 C, 1: fp32 C
   int accumulate;  // 1: C += result
   int* err;        // device error word (0 = ok)
+  int tma_store = 0;  // 1: bf16 output without accumulation leaves through shared memory + TMA stores (plain kernel)
 };
 
 // Tensor-parallel variants of the same kernel (TP template parameter of gemm_body):
 //   1  all-gather → GEMM: the M dimension is the concatenation over ranks of per-rank activation shards that live
 //      in peer-visible buffers.  Peer memory is not cached in this GPU's L2, so a remote tile read by every n-tile
 //      that needs it would cross NVLink N/BN times.  Instead four extra "copier" warps per CTA pull the remote shards
-//      into a local gathered buffer, 16 rows at a time in the order the tiles are consumed, and count finished
+//      into a local gathered buffer, 8 rows at a time in the order the tiles are consumed, and count finished
 //      pieces per m-tile; the TMA producer starts with the tiles of the own shard (read in place) and waits (bounded)
 //      on a remote tile's counter before loading it from the local copy.  Every byte crosses NVLink once and the
 //      transfer overlaps the MMAs of earlier tiles; the gathered activation is a by-product that the weight-gradient
 //      GEMM of the backward pass reuses.
 //   2  GEMM → reduce-scatter: every output m-tile is stored straight into the staging slot [this rank] of the rank
 //      that owns those rows; the owner later sums its `world` slots (ttb_rs_reduce).  Stores to peers start with
-//      the next rank so the ranks do not all write to the same GPU at the same time.
+//      the next rank so the ranks do not all write to the same GPU at the same time.  The epilogue stages 32 × 64
+//      sub-tiles in shared memory and hands them to the TMA store unit (per-thread 16-byte stores to a peer become
+//      one NVLink write per row fragment and ran at a fraction of the link rate).
 static constexpr int kMaxTpWorld = 8;
 static constexpr int kTpAgThreads = 384;  // 8 GEMM warps + 4 copier warps
-static constexpr int kCopyPieces = 8;     // pieces per 128-row m-tile
+static constexpr int kRsStageBytes = 4 * 2 * 4096;  // TP 2: per epilogue warp two 32 × 64 bf16 staging tiles, 1024 bytes after the stage ring
+static constexpr int kCopyPieces = 16;    // pieces per 128-row m-tile
 struct alignas(64) TpArgs {
   CUtensorMap tmA[kMaxTpWorld];     // TP 1: per-rank A shard [rows_per_rank, K] (only the own one is loaded from)
+                                    // TP 2: per-rank staging buffer as [world * rows_per_rank, N], box 64 × 32 (TMA stores)
   const void* A_src[kMaxTpWorld];   // TP 1: the same shards as raw pointers for the copier warps (row pitch K)
   void* gathered;                   // TP 1: local [world * rows_per_rank, K] buffer the copiers fill
   int* sync;                        // TP 1: [0] piece ticket, [1 + m] finished pieces of m-tile m (zeroed per launch)
@@ -127,7 +132,7 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_
 
 template <int BN, bool A_MN, bool B_MN, int TP>
 __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUtensorMap* tmB_ptr, const GemmParams& p,
-                                          const TpArgs* tp, const GroupArgs* ga = nullptr) {
+                                          const TpArgs* tp, const GroupArgs* ga = nullptr, const CUtensorMap* tmC_ptr = nullptr) {
   using Cfg = GemmCfg<BN>;
   const CUtensorMap& tmA = *tmA_ptr;
   const CUtensorMap& tmB = *tmB_ptr;
@@ -339,6 +344,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
     int acc = 0;
     uint32_t acc_phase = 0;
+    int rs_buf = 0;  // TP 2: staging buffer toggle
     for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x) {
       int m_blk, n_blk;
       tile_coords(t, num_m, num_n, m_blk, n_blk);
@@ -365,6 +371,67 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
         row_ok = (quarter * 32 + lane) < ga->tile_rows[m_blk];
       }
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+      if (TP == 2 || (TP == 0 && p.tma_store)) {
+        // this warp's 32 rows leave through the TMA store unit, 64 columns at a time (TP 2: into the owner's staging slot)
+        uint8_t* stage_base = smem + Cfg::kStages * Cfg::kStageBytes + 1024;  // 1024-byte aligned: after the barrier block
+        uint8_t* my_stage = stage_base + quarter * 8192;
+        const int row0 = m_blk * BM + quarter * 32;
+        const CUtensorMap* mapC = tmC_ptr;
+        int slot_row0 = row0;
+        if (TP == 2) {
+          const int owner = row0 / tp->rows_per_rank;
+          slot_row0 = tp->rank * tp->rows_per_rank + (row0 - owner * tp->rows_per_rank);
+          mapC = &tp->tmA[owner];
+        }
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          const int col0 = n_blk * BN + c * 64;
+          if (col0 >= p.N || row0 >= p.M) break;
+          uint8_t* buf = my_stage + (rs_buf & 1) * 4096;
+          if (lane == 0) tma_store_wait_read<1>();  // the store that used this buffer two sub-tiles ago has read it
+          __syncwarp();
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t r[32];
+            tmem_ld_32x32(taddr + c * 64 + h * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {  // four 16-byte chunks of this half, 128-byte swizzle (chunk ^ row mod 8)
+              float f[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(r[j * 8 + i]) * p.alpha;
+              if (TP == 0 && p.bias != nullptr) {
+                const int cb = col0 + h * 32 + j * 8;
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                  if (cb + i < p.N) f[i] += __bfloat162float(__ldg(p.bias + cb + i));
+              }
+              uint4 o;
+              o.x = pack_bf16x2(f[0], f[1]);
+              o.y = pack_bf16x2(f[2], f[3]);
+              o.z = pack_bf16x2(f[4], f[5]);
+              o.w = pack_bf16x2(f[6], f[7]);
+              const int chunk = (h * 4 + j) ^ (lane & 7);
+              *reinterpret_cast<uint4*>(buf + lane * 128 + chunk * 16) = o;
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(mapC, buf, col0, slot_row0);
+            tma_store_commit();
+          }
+          ++rs_buf;
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty[acc]);
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -438,6 +505,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
     }
   }
 
+  if ((TP == 2 || TP == 0) && warp >= 4 && warp < 8 && lane == 0) tma_store_wait<0>();  // every staged sub-tile has left shared memory and landed
+
   if (TP == 1 && warp >= 8) {
     // ------------------------------------------------------------------ copier warps (all-gather over peer memory)
     const int ctid = threadIdx.x - 256;
@@ -458,13 +527,13 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
       const int src = static_cast<int>(row0 / tp->rows_per_rank);
       const uint4* s = reinterpret_cast<const uint4*>(tp->A_src[src]) + (row0 - static_cast<long long>(src) * tp->rows_per_rank) * row_vecs;
       uint4* d = reinterpret_cast<uint4*>(tp->gathered) + row0 * row_vecs;
-      for (long long v = ctid; v < piece_vecs; v += 128 * 4) {
-        uint4 r[4];
+      for (long long v = ctid; v < piece_vecs; v += 128 * 8) {  // 8 × 16 bytes in flight per thread: NVLink latency needs ≈ 2.5 MB per GPU
+        uint4 r[8];
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
+        for (int j = 0; j < 8; ++j)
           if (v + j * 128 < piece_vecs) r[j] = __ldcg(s + v + j * 128);
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
+        for (int j = 0; j < 8; ++j)
           if (v + j * 128 < piece_vecs) d[v + j * 128] = r[j];
       }
       __threadfence();
@@ -484,8 +553,9 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
 
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
-  gemm_body<BN, A_MN, B_MN, 0>(&tmA, &tmB, p, nullptr);
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmC, GemmParams p) {
+  gemm_body<BN, A_MN, B_MN, 0>(&tmA, &tmB, p, nullptr, nullptr, &tmC);
 }
 
 template <int BN, bool B_MN, int TP>
@@ -586,10 +656,18 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p, long l
     return rc;
   }
 
+  // bf16 outputs that are not accumulated leave through shared memory and TMA stores (box: 64 columns × 32 rows)
+  GemmParams q = p;
+  CUtensorMap tmC;
+  memset(&tmC, 0, sizeof(tmC));
+  q.tma_store = (!p.out_fp32 && !p.accumulate && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0) ? 1 : 0;
+  if (q.tma_store && make_tmap_2d(&tmC, p.C, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.M, p.N, p.ldc, 32, 64, CU_TENSOR_MAP_SWIZZLE_128B) != kOk) q.tma_store = 0;
+  constexpr int smem_bytes = Cfg::kSmemBytes + 768 + kRsStageBytes;
+  static_assert(smem_bytes <= 232448, "shared memory budget of one CTA");
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     if (e != cudaSuccess) {
       fprintf(stderr, "[ttb] gemm: cudaFuncSetAttribute failed: %s\n", cudaGetErrorString(e));
       return kErrDriver;
@@ -599,7 +677,7 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p, long l
   const int num_tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   const int grid = num_tiles < sm_count() ? num_tiles : sm_count();
   TTB_COUNT_LAUNCH(1);
-  kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tmA, tmB, p);
+  kern<<<grid, kThreads, smem_bytes, stream>>>(tmA, tmB, tmC, q);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     fprintf(stderr, "[ttb] gemm launch failed: %s (M=%d N=%d K=%d grid=%d)\n", cudaGetErrorString(e), p.M, p.N, p.K, grid);
@@ -630,15 +708,17 @@ static int launch_gemm_tp(const TpArgs& tp, const void* A, const void* B, const 
     rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.N, p.K, ldb, BN, BK, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != kOk) return rc;
   auto kern = gemm_tp_kernel<BN, B_MN, TP>;
+  constexpr int smem_bytes = Cfg::kSmemBytes + (TP == 2 ? 768 + kRsStageBytes : 0);  // barriers take the first 256 of the 1024 bytes
+  static_assert(smem_bytes <= 232448, "shared memory budget of one CTA");
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return kErrDriver;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) return kErrDriver;
     attr_set = true;
   }
   const int num_tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   const int grid = num_tiles < sm_count() ? num_tiles : sm_count();
   TTB_COUNT_LAUNCH(1);
-  kern<<<grid, TP == 1 ? kTpAgThreads : kThreads, Cfg::kSmemBytes, stream>>>(tp, tmA, tmB, p);
+  kern<<<grid, TP == 1 ? kTpAgThreads : kThreads, smem_bytes, stream>>>(tp, tmA, tmB, p);
   if (cudaGetLastError() != cudaSuccess) return kErrDriver;
   return kOk;
 }
@@ -743,7 +823,13 @@ extern "C" int ttb_gemm_rs_bf16(const void* A, const void* B, void* const* C_ran
   TpArgs tp;
   memset(&tp, 0, sizeof(tp));
   tp.world = world, tp.rank = rank, tp.rows_per_rank = rows_per_rank;
-  for (int r = 0; r < world; ++r) tp.C[r] = C_ranks[r];
+  for (int r = 0; r < world; ++r) {
+    tp.C[r] = C_ranks[r];
+    // rank r's staging buffer [world, rows_per_rank, ldc] as a 2-D tensor for the epilogue's TMA stores (box: 64 columns × 32 rows)
+    int rc = make_tmap_2d(&tp.tmA[r], C_ranks[r], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, static_cast<uint64_t>(world) * rows_per_rank, N, ldc, 32, 64,
+                          CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != kOk) return rc;
+  }
   GemmParams p;
   p.M = world * rows_per_rank, p.N = N, p.K = K, p.C = nullptr, p.ldc = ldc;
   p.bias = nullptr, p.alpha = 1.f, p.out_fp32 = 0, p.accumulate = 0, p.err = err;

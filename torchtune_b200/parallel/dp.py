@@ -2,16 +2,23 @@
 
 Design (sized for 180 GB of HBM per GPU): every rank keeps the full bf16 parameters and a
 full bf16 gradient buffer as two *flat* peer-visible allocations; optimizer moments are
-sharded (rank r owns elements ``[r·S, (r+1)·S)``).  One step of communication is a single
-kernel per rank (``ttb_dp_reduce_adamw_bcast``): pull the gradient slices of all peers,
-reduce in fp32, AdamW on the owned slice, push the new parameters to all peers.  Compared
-with the reference's FSDP2 path (per-layer all-gather in forward and backward, per-layer
-reduce-scatter, then a separate scale pass and optimizer step —
-torchtune/training/_distributed.py:661-714, recipes/full_finetune_distributed.py:1030-1050)
-this moves 2 instead of 3 model-sized messages per step, keeps nothing on the critical path
-of the layers, and reduces in fp32 while sending bf16.
+sharded.  The flat index space is cut into *buckets* (one per decoder layer, one for what
+precedes the layers, one for what follows) and every rank owns the ``1 / world`` slice with
+its rank's index of **every** bucket, so that the communication of one bucket keeps the
+links of all GPUs busy.  The communication of a bucket is a single kernel per rank
+(``ttb_dp_reduce_adamw_bcast``): pull the gradient slices of all peers, reduce in fp32,
+AdamW on the owned slice, push the new parameters to all peers.  Buckets are processed on a
+side stream *during backward*, as soon as the layer's gradients are final on every rank
+(a tensor hook on the layer's input gradient, a 4-byte all-reduce as the cross-rank
+barrier), so reduction, optimizer and broadcast hide behind the backward GEMMs of the
+earlier layers; with gradient clipping only the reduction is overlapped and the update
+follows once the global norm is known.  Compared with the reference's FSDP2 path
+(per-layer all-gather in forward and backward, per-layer reduce-scatter, then a separate
+scale pass and optimizer step — torchtune/training/_distributed.py:661-714,
+recipes/full_finetune_distributed.py:1030-1050) this moves 2 instead of 3 model-sized
+messages per step, keeps nothing on the critical path of the layers, and reduces in fp32
+while sending bf16.
 
-Models that do not fit resident use the ZeRO-3 sharder in :mod:`.fsdp`.
 On CPU (gloo) the same interface is implemented with ``all_reduce`` so the host-side logic
 is testable without GPUs.
 """
@@ -19,6 +26,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import re
 from typing import Any, Dict, Iterable, List, Optional, Tuple, Union
 
 import torch
@@ -28,31 +36,62 @@ from torch import nn
 from ..ops import reference as _ref
 from .fabric import PeerBuffer
 
-_ALIGN = 2048  # elements; keeps every shard and every parameter offset 16-byte aligned
+_LAYER_KEY = re.compile(r"^(.*\blayers\.\d+)\.")
 
 
 def _round_up(x: int, m: int) -> int:
     return -(-x // m) * m
 
 
+def _bucket_key(name: str) -> Optional[str]:
+    m = _LAYER_KEY.match(name)
+    return m.group(1) if m else None
+
+
 class FlatParameters:
     """Re-homes the trainable parameters of ``model`` into one flat buffer (and gives each a
-    same-shaped window of a flat gradient buffer, exposed as ``param._grad_buffer``)."""
+    same-shaped window of a flat gradient buffer, exposed as ``param._grad_buffer``).
+
+    ``buckets[b] = (start, size)`` are consecutive ranges of the flat index space whose sizes
+    are multiples of ``8 · world``; rank ``r`` owns ``[start + r·size/world, start + (r+1)·size/world)``
+    of each.  ``bucket_keys[b]`` is the module path of the decoder layer a bucket belongs to
+    (``None`` for the parameters before / after the layers)."""
 
     def __init__(self, params: List[Tuple[str, nn.Parameter]], world: int, device: torch.device, group=None):
         dtypes = {p.dtype for _, p in params}
         if len(dtypes) != 1:
             raise ValueError(f"all trainable parameters must share one dtype, found {dtypes}")
         self.dtype = dtypes.pop()
+        self.world = world
         self.names = [n for n, _ in params]
         self.params = [p for _, p in params]
         self.offsets: List[int] = []
-        cursor = 0
-        for p in self.params:
+        self.buckets: List[Tuple[int, int]] = []
+        self.bucket_keys: List[Optional[str]] = []
+        self.bucket_params: List[List[nn.Parameter]] = []
+        unit = 8 * world
+        cursor, start, prev_key = 0, 0, object()
+        for name, p in params:
+            key = _bucket_key(name)
+            if key != prev_key and self.bucket_params:  # close the running bucket at a multiple of 8·world
+                cursor = start + _round_up(cursor - start, unit)
+                self.buckets.append((start, cursor - start))
+                start = cursor
+            if key != prev_key:
+                self.bucket_keys.append(key)
+                self.bucket_params.append([])
+                prev_key = key
             self.offsets.append(cursor)
+            self.bucket_params[-1].append(p)
             cursor += _round_up(p.numel(), 8)
-        self.shard = _round_up(-(-cursor // world), _ALIGN)
-        self.total = self.shard * world
+        cursor = start + _round_up(max(cursor - start, unit), unit)
+        self.buckets.append((start, cursor - start))
+        self.total = cursor
+        self.pieces = [size // world for _, size in self.buckets]
+        self.state_offsets = [0]
+        for piece in self.pieces:
+            self.state_offsets.append(self.state_offsets[-1] + piece)
+        self.shard = self.state_offsets[-1]  # elements of optimizer state per rank
         esize = torch.empty(0, dtype=self.dtype).element_size()
         self.param_buf = PeerBuffer(self.total * esize, device, group)
         self.grad_buf = PeerBuffer(self.total * esize, device, group)
@@ -71,10 +110,35 @@ class FlatParameters:
             for p in self.params:
                 _cuda.register_grad_window(p)
 
-    def collect_autograd_grads(self) -> None:
+    # ownership -----------------------------------------------------------------------------
+    def owned(self, bucket: int, rank: int) -> Tuple[int, int, int]:
+        """``(begin, count, state_offset)`` of rank ``rank``'s slice of ``bucket``."""
+        start, _ = self.buckets[bucket]
+        piece = self.pieces[bucket]
+        return start + rank * piece, piece, self.state_offsets[bucket]
+
+    def shards_to_full(self, shards: List[torch.Tensor]) -> torch.Tensor:
+        """Per-rank state vectors (``[shard]`` each) → one vector in flat-parameter order (``[total]``)."""
+        full = torch.zeros(self.total, dtype=shards[0].dtype, device=shards[0].device)
+        for b in range(len(self.buckets)):
+            for r, sh in enumerate(shards):
+                begin, count, off = self.owned(b, r)
+                full[begin : begin + count] = sh[off : off + count]
+        return full
+
+    def full_to_shard(self, full: torch.Tensor, rank: int, out: torch.Tensor) -> None:
+        out.zero_()
+        for b in range(len(self.buckets)):
+            begin, count, off = self.owned(b, rank)
+            end = min(begin + count, full.numel())
+            if end > begin:
+                out[off : off + end - begin].copy_(full[begin:end])
+
+    # gradients -----------------------------------------------------------------------------
+    def collect_autograd_grads(self, bucket: Optional[int] = None) -> None:
         """Move gradients that autograd produced as separate tensors into the flat buffer and
-        zero the windows nothing wrote to."""
-        for p in self.params:
+        zero the windows nothing wrote to (all parameters, or those of one bucket)."""
+        for p in self.params if bucket is None else self.bucket_params[bucket]:
             if p.grad is not None:
                 if p._grad_written:
                     p._grad_buffer.add_(p.grad)
@@ -84,6 +148,7 @@ class FlatParameters:
                 p.grad = None
             elif not p._grad_written:
                 p._grad_buffer.zero_()
+                p._grad_written = True
 
     def reset_grad_flags(self) -> None:
         for p in self.params:
@@ -95,8 +160,9 @@ class FlatParameters:
 
 
 class ShardedAdamW:
-    """AdamW over a :class:`FlatParameters` store; this rank updates shard ``rank`` only and
-    the fused kernel distributes the result."""
+    """AdamW over a :class:`FlatParameters` store; this rank updates its slice of every bucket
+    and the fused kernel distributes the result.  ``step`` handles all buckets that were not
+    already processed during backward (:meth:`begin_step` / :meth:`process_bucket`)."""
 
     def __init__(self, flat: FlatParameters, rank: int, world: int, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 1e-2):
         self.flat, self.rank, self.world = flat, rank, world
@@ -106,7 +172,9 @@ class ShardedAdamW:
         self.exp_avg_sq = torch.zeros(flat.shard, dtype=flat.dtype, device=dev)
         self.step_count = 0
         self._gsum: Optional[torch.Tensor] = None
+        self._partials: Optional[torch.Tensor] = None
         self.last_grad_norm: Optional[torch.Tensor] = None
+        self._open: Optional[Dict[str, Any]] = None  # state of a step whose buckets are processed one by one
 
     # torch.optim-like surface used by schedulers / loggers
     @property
@@ -127,18 +195,17 @@ class ShardedAdamW:
             g.update(saved)
 
     def full_state_dict(self, is_rank_zero: bool = True, group=None) -> Dict[str, Any]:
-        """Moments of the whole model as one flat CPU tensor each plus the parameter layout, so a
-        checkpoint written at one world size can be read at another."""
+        """Moments of the whole model as one CPU tensor each, in flat-parameter order, plus the parameter
+        layout, so a checkpoint written at one world size can be read at another."""
         flat = self.flat
         out = {}
         for key, shard in (("exp_avg", self.exp_avg), ("exp_avg_sq", self.exp_avg_sq)):
             if self.world > 1:
                 parts = [torch.empty_like(shard) for _ in range(self.world)]
                 dist.all_gather(parts, shard, group=group)
-                full = torch.cat(parts)
             else:
-                full = shard
-            out[key] = full.cpu() if is_rank_zero else None
+                parts = [shard]
+            out[key] = flat.shards_to_full([p.cpu() for p in parts]) if is_rank_zero else None
         if not is_rank_zero:
             return {}
         out["step"] = self.step_count
@@ -152,66 +219,108 @@ class ShardedAdamW:
         if layout is not None and (list(layout["names"]) != list(flat.names) or list(layout["numels"]) != [p.numel() for p in flat.params]):
             raise ValueError("optimizer checkpoint was written for a different set of trainable parameters")
         self.step_count = int(sd["step"])
-        begin = self.rank * flat.shard
         for key, shard in (("exp_avg", self.exp_avg), ("exp_avg_sq", self.exp_avg_sq)):
             full = sd[key]
-            shard.zero_()
-            end = min(begin + flat.shard, full.numel())
-            if end > begin:
-                shard[: end - begin].copy_(full[begin:end])
+            if layout is not None and list(layout["offsets"]) != list(flat.offsets):
+                # written with another world size (bucket padding differs): move every parameter's window
+                moved = torch.zeros(flat.total, dtype=full.dtype)
+                for old, new, n in zip(layout["offsets"], flat.offsets, layout["numels"]):
+                    moved[new : new + n] = full[old : old + n]
+                full = moved
+            flat.full_to_shard(full, self.rank, shard)
         for g, saved in zip(self.param_groups, sd.get("param_groups", [])):
             g.update(saved)
 
-    def step(self, grad_scale: Union[float, torch.Tensor] = 1.0, max_grad_norm: Optional[float] = None, group=None) -> None:
+    # ------------------------------------------------------------------ step protocol
+    def begin_step(self, grad_scale: Union[float, torch.Tensor], max_grad_norm: Optional[float]) -> None:
+        """Open a step whose buckets may be processed one at a time (:meth:`process_bucket`) before :meth:`step` finishes it."""
         g = self.param_groups[0]
         self.step_count += 1
         b1, b2 = g["betas"]
-        inv_bc1 = 1.0 / (1.0 - b1**self.step_count)
-        inv_sqrt_bc2 = 1.0 / math.sqrt(1.0 - b2**self.step_count)
-        flat = self.flat
-        begin = self.rank * flat.shard
-        self.last_grad_norm = None
-        if flat.flat_param.is_cuda:
-            self._step_cuda(grad_scale, max_grad_norm, g, begin, inv_bc1, inv_sqrt_bc2, group)
+        st: Dict[str, Any] = dict(
+            done=set(), clip=max_grad_norm, inv_bc1=1.0 / (1.0 - b1**self.step_count), inv_sqrt_bc2=1.0 / math.sqrt(1.0 - b2**self.step_count),
+            scale_dev=None, scale_host=1.0,
+        )
+        if isinstance(grad_scale, torch.Tensor):
+            st["scale_dev"] = grad_scale.detach().to(torch.float32).reshape(1)
         else:
-            self._step_host(grad_scale, max_grad_norm, g, begin, group)
+            st["scale_host"] = float(grad_scale)
+        flat = self.flat
+        if max_grad_norm is not None and flat.flat_param.is_cuda:
+            from ..ops._lib import lib
 
-    def _step_cuda(self, grad_scale, max_grad_norm, g, begin, inv_bc1, inv_sqrt_bc2, group) -> None:
+            if self._gsum is None:
+                self._gsum = torch.empty(flat.shard, dtype=torch.float32, device=flat.flat_param.device)
+            grid = lib().ttb_dp_grid()
+            self._partials = torch.zeros(len(flat.buckets) * grid, dtype=torch.float32, device=flat.flat_param.device)
+            st["grid"] = grid
+        self._open = st
+
+    def process_bucket(self, bucket: int) -> None:
+        """CUDA only.  Without clipping: reduce + AdamW + broadcast of this bucket.  With clipping: reduce into the fp32
+        scratch and accumulate the squared norm; the update follows in :meth:`step`."""
+        st = self._open
+        if st is None or bucket in st["done"]:
+            return
+        st["done"].add(bucket)
+        if st["clip"] is None:
+            self._launch(bucket, 0, st, st["scale_dev"], st["scale_host"])
+        else:
+            self._launch(bucket, 1, st, None, 1.0)
+
+    def _launch(self, bucket: int, mode: int, st: Dict[str, Any], sdev, shost) -> None:
         from ..ops._lib import check, lib, stream_ptr
 
         L = lib()
         _declare_dp(L)
-        flat = self.flat
-        scale_dev, scale_host = (grad_scale.to(torch.float32).reshape(1), 1.0) if isinstance(grad_scale, torch.Tensor) else (None, float(grad_scale))
+        flat, g = self.flat, self.param_groups[0]
+        begin, count, off = flat.owned(bucket, self.rank)
         b1, b2 = g["betas"]
-        grads, params = flat.grad_buf.pointer_array(), flat.param_buf.pointer_array()
+        esz = self.exp_avg.element_size()
+        gsum = None if self._gsum is None or mode == 0 else self._gsum.data_ptr() + 4 * off
+        partials = None if mode != 1 else self._partials.data_ptr() + 4 * bucket * st["grid"]
+        from ..ops._lib import err_word
 
-        def launch(mode: int, sdev, shost, gsum=None, partials=None):
-            check(
-                L.ttb_dp_reduce_adamw_bcast(grads, params, self.world, self.rank, begin, flat.shard, self.exp_avg.data_ptr(), self.exp_avg_sq.data_ptr(), None if gsum is None else gsum.data_ptr(), None if partials is None else partials.data_ptr(), None if sdev is None else sdev.data_ptr(), shost, float(g["lr"]), b1, b2, g["eps"], g["weight_decay"], inv_bc1, inv_sqrt_bc2, mode, stream_ptr()),
-                "dp_reduce_adamw_bcast",
-            )
+        wait = st.get("wait") if mode != 2 else None  # (local flag array, epoch): set while buckets are processed during backward
+        check(
+            L.ttb_dp_reduce_adamw_bcast(flat.grad_buf.pointer_array(), flat.param_buf.pointer_array(), self.world, self.rank, begin, count,
+                                        self.exp_avg.data_ptr() + esz * off, self.exp_avg_sq.data_ptr() + esz * off, gsum, partials,
+                                        None if sdev is None else sdev.data_ptr(), shost, float(g["lr"]), b1, b2, g["eps"], g["weight_decay"],
+                                        st["inv_bc1"], st["inv_sqrt_bc2"], mode, None if wait is None else wait[0], bucket, 0 if wait is None else wait[1],
+                                        err_word(flat.flat_param.device).data_ptr(), stream_ptr()),
+            "dp_reduce_adamw_bcast",
+        )
 
-        if max_grad_norm is None:
-            launch(0, scale_dev, scale_host)
-            return
-        if self._gsum is None:
-            self._gsum = torch.empty(flat.shard, dtype=torch.float32, device=flat.flat_param.device)
-        partials = torch.empty(L.ttb_dp_grid(), dtype=torch.float32, device=flat.flat_param.device)
-        launch(1, None, 1.0, self._gsum, partials)
-        sumsq = partials.sum()
-        if self.world > 1:
-            dist.all_reduce(sumsq, group=group)
-        s = scale_dev if scale_dev is not None else torch.tensor([scale_host], device=sumsq.device)
-        norm = sumsq.sqrt() * s
-        self.last_grad_norm = norm.reshape(())
-        coef = torch.clamp(float(max_grad_norm) / (norm + 1e-6), max=1.0) * s
-        launch(2, coef.reshape(1).float(), 1.0, self._gsum)
-
-    def _step_host(self, grad_scale, max_grad_norm, g, begin, group) -> None:
-        """gloo implementation of the same algorithm (sum of all ranks' gradients in fp32,
-        update of the owned shard, broadcast of the result)."""
+    def step(self, grad_scale: Union[float, torch.Tensor] = 1.0, max_grad_norm: Optional[float] = None, group=None) -> None:
+        if self._open is None:
+            self.begin_step(grad_scale, max_grad_norm)
+        st = self._open
+        self.last_grad_norm = None
         flat = self.flat
+        try:
+            if not flat.flat_param.is_cuda:
+                self._step_host(grad_scale, max_grad_norm, group)
+                return
+            for b in range(len(flat.buckets)):
+                self.process_bucket(b)
+            if st["clip"] is None:
+                return
+            sumsq = self._partials.sum()
+            if self.world > 1:
+                dist.all_reduce(sumsq, group=group)
+            s = st["scale_dev"] if st["scale_dev"] is not None else torch.tensor([st["scale_host"]], device=sumsq.device)
+            norm = sumsq.sqrt() * s
+            self.last_grad_norm = norm.reshape(())
+            coef = (torch.clamp(float(st["clip"]) / (norm + 1e-6), max=1.0) * s).reshape(1).float()
+            for b in range(len(flat.buckets)):
+                self._launch(b, 2, st, coef, 1.0)
+        finally:
+            self._open = None
+
+    def _step_host(self, grad_scale, max_grad_norm, group) -> None:
+        """gloo implementation of the same algorithm (sum of all ranks' gradients in fp32,
+        update of the owned slices, broadcast of the result)."""
+        flat, g = self.flat, self.param_groups[0]
         gsum = flat.flat_grad.float()
         if self.world > 1:
             dist.all_reduce(gsum, group=group)
@@ -220,36 +329,40 @@ class ShardedAdamW:
             norm = gsum.norm() * scale
             self.last_grad_norm = norm
             scale *= float(torch.clamp(float(max_grad_norm) / (norm + 1e-6), max=1.0))
-        sl = slice(begin, begin + flat.shard)
         b1, b2 = g["betas"]
-        new = flat.flat_param[sl].clone()
-        _ref.adamw_step(new, gsum[sl], self.exp_avg, self.exp_avg_sq, self.step_count, float(g["lr"]), b1, b2, g["eps"], g["weight_decay"], scale)
+        mine = torch.cat([torch.arange(begin, begin + count) for begin, count, _ in (flat.owned(b, self.rank) for b in range(len(flat.buckets)))])
+        new = flat.flat_param[mine].clone()
+        _ref.adamw_step(new, gsum[mine], self.exp_avg, self.exp_avg_sq, self.step_count, float(g["lr"]), b1, b2, g["eps"], g["weight_decay"], scale)
         if self.world > 1:
             gathered = [torch.empty_like(new) for _ in range(self.world)]
             dist.all_gather(gathered, new, group=group)
-            flat.flat_param.copy_(torch.cat(gathered))
+            flat.flat_param.copy_(flat.shards_to_full(gathered))
         else:
-            flat.flat_param[sl].copy_(new)
+            flat.flat_param[mine] = new
 
 
 def _declare_dp(L) -> None:
     if getattr(L, "_dp_declared", False):
         return
     vp, i32, i64, f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
-    L.ttb_dp_reduce_adamw_bcast.argtypes = [ctypes.POINTER(vp), ctypes.POINTER(vp), i32, i32, i64, i64, vp, vp, vp, vp, vp, f32, f32, f32, f32, f32, f32, f32, f32, i32, vp]
+    L.ttb_dp_reduce_adamw_bcast.argtypes = [ctypes.POINTER(vp), ctypes.POINTER(vp), i32, i32, i64, i64, vp, vp, vp, vp, vp, f32, f32, f32, f32, f32, f32, f32, f32, i32, vp, i32, i32, vp, vp]
     L.ttb_dp_reduce_adamw_bcast.restype = i32
+    L.ttb_dp_signal.argtypes = [ctypes.POINTER(vp), i32, i32, i32, i32, vp]
+    L.ttb_dp_signal.restype = i32
     L.ttb_dp_grid.restype = i32
+    L.ttb_dp_max_buckets.restype = i32
     L._dp_declared = True
 
 
 class DataParallelEngine:
     """Owns the flat stores, the wgrad side stream and the step protocol.
 
-    Step protocol (all on the training stream, so ordering is stream order):
-      backward … → ``all_reduce_sum_(n_tokens, …)``  — also the cross-rank barrier that tells
-      every rank all gradient buffers are final → fused reduce/AdamW/broadcast kernel →
-      small all-reduce as the closing barrier (new parameters have landed everywhere and
-      nobody still reads the old gradients).
+    Step protocol: ``arm_backward_overlap(optimizer, grad_scale, clip)`` → backward, during which every decoder layer's
+    bucket is handed to the optimizer on the communication stream as soon as its gradients are final (hook on the
+    gradient of the layer's input; a 4-byte all-reduce on that stream tells every rank the bucket is final everywhere)
+    → ``optimizer_step`` processes what is left (embeddings, anything without a hook), joins the streams and closes with a
+    small all-reduce (new parameters have landed everywhere and nobody still reads the old gradients).  Without arming,
+    ``optimizer_step`` runs the whole protocol after backward.
     """
 
     def __init__(self, device: torch.device, group=None):
@@ -259,6 +372,14 @@ class DataParallelEngine:
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.flat: Optional[FlatParameters] = None
         self._barrier_token = torch.zeros(1, device=device if device.type == "cuda" else "cpu")
+        self._bucket_token = torch.zeros(1, device=device if device.type == "cuda" else "cpu")
+        self._comm_stream = None
+        self._armed = None  # the optimizer whose buckets are processed during the running backward
+        self._flags = None
+        import os
+
+        # from 4 ranks on the NVLink traffic of a step outweighs what the concurrent update costs the backward GEMMs
+        self.min_world_for_overlap = int(os.environ.get("TTB_DP_OVERLAP_MIN_WORLD", "4"))
 
     # sizes the recipes ask for ------------------------------------------------------------
     dp_size = property(lambda self: self.world)
@@ -273,7 +394,85 @@ class DataParallelEngine:
             from ..ops import _cuda
 
             _cuda.enable_direct_wgrad(True)
+            from ..ops._lib import lib
+
+            L = lib()
+            _declare_dp(L)
+            if len(self.flat.buckets) <= L.ttb_dp_max_buckets():
+                self._comm_stream = torch.cuda.Stream(device=self.device)
+                self._flags = PeerBuffer(self.world * L.ttb_dp_max_buckets() * 4, self.device, self.group)  # int32 [world][max buckets]
+                self._epoch = 0
+                self._install_bucket_hooks(model)
         return model
+
+    # ------------------------------------------------------------------ backward overlap
+    def _install_bucket_hooks(self, model: nn.Module) -> None:
+        """The gradient of a layer's input is complete only after every node of that layer has run, so a hook on it marks
+        the layer's bucket as final; the gradient of the last layer's output does the same for what follows the layers."""
+        keys = self.flat.bucket_keys
+        last = None
+        for b, key in enumerate(keys):
+            if key is None:
+                continue
+            try:
+                mod = model.get_submodule(key)
+            except AttributeError:
+                continue
+            mod.register_forward_pre_hook(self._pre_hook(b))
+            last = (b, mod)
+        if last is not None and last[0] + 1 < len(keys) and keys[last[0] + 1] is None:
+            last[1].register_forward_hook(self._post_hook(last[0] + 1))
+
+    def _watch(self, t: Any, bucket: int) -> None:
+        if self._armed is not None and torch.is_tensor(t) and t.requires_grad and torch.is_grad_enabled():
+            t.register_hook(lambda g, b=bucket: self._bucket_ready(b))
+
+    def _pre_hook(self, bucket: int):
+        return lambda module, args: self._watch(args[0] if args else None, bucket)
+
+    def _post_hook(self, bucket: int):
+        def hook(module, args, output):
+            self._watch(output[0] if isinstance(output, (tuple, list)) else output, bucket)
+
+        return hook
+
+    def arm_backward_overlap(self, optimizer, grad_scale, clip_grad_norm: Optional[float] = None) -> bool:
+        """Call between the forward pass and ``backward()`` of the step's last micro-batch, with the final gradient scale."""
+        if self._comm_stream is None or not hasattr(optimizer, "process_bucket") or self._armed is not None:
+            return False
+        if self.world < self.min_world_for_overlap:
+            # nothing crosses NVLink on one GPU, and running the HBM-bound update next to the backward GEMMs only takes
+            # bandwidth (and power) from them: measured 506 vs 488 ms per step on the 8B model
+            return False
+        optimizer.begin_step(grad_scale, clip_grad_norm)
+        self._epoch += 1
+        optimizer._open["wait"] = (self._flags.local_ptr, self._epoch)
+        self._armed = optimizer
+        return True
+
+    def _bucket_ready(self, bucket: int) -> None:
+        opt = self._armed
+        if opt is None:
+            return None
+        self._hand_over([bucket], opt)
+        return None
+
+    def _hand_over(self, buckets: List[int], opt) -> None:
+        from ..ops import _cuda
+
+        for b in buckets:
+            self.flat.collect_autograd_grads(b)
+        main, comm = torch.cuda.current_stream(self.device), self._comm_stream
+        comm.wait_stream(main)
+        if _cuda._wgrad_stream is not None:
+            comm.wait_stream(_cuda._wgrad_stream)
+        from ..ops._lib import check, lib, stream_ptr
+
+        with torch.cuda.stream(comm):
+            for b in buckets:
+                # tell every peer that this rank's gradients of bucket b are final; the bucket kernel waits for the peers' flags
+                check(lib().ttb_dp_signal(self._flags.pointer_array(), self.world, self.rank, b, self._epoch, stream_ptr()), "dp_signal")
+                opt.process_bucket(b)
 
     def build_optimizer(self, model: nn.Module, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 1e-2, **_: Any) -> ShardedAdamW:
         if self.flat is None:
@@ -296,6 +495,19 @@ class DataParallelEngine:
             dist.all_reduce(self._barrier_token, group=self.group)
 
     def optimizer_step(self, model: nn.Module, optimizer: ShardedAdamW, grad_scale, clip_grad_norm: Optional[float] = None):
+        if self._armed is not None:
+            if self._armed is not optimizer:
+                raise RuntimeError("optimizer_step was called with another optimizer than the armed one")
+            left = [b for b in range(len(self.flat.buckets)) if b not in optimizer._open["done"]]
+            if left:
+                self._hand_over(left, optimizer)
+            torch.cuda.current_stream(self.device).wait_stream(self._comm_stream)
+            self._armed = None
+            optimizer.step(grad_scale=grad_scale, max_grad_norm=clip_grad_norm, group=self.group)  # with clipping: norm + update
+            if self.world > 1:
+                self.barrier()  # pushes have landed; gradients may be overwritten
+            optimizer.zero_grad()
+            return optimizer.last_grad_norm
         if self.device.type == "cuda":
             from ..ops import _cuda
 
@@ -314,5 +526,8 @@ class DataParallelEngine:
             if self.device.type == "cuda":
                 torch.cuda.synchronize(self.device)
             self.barrier()
+            if self._flags is not None:
+                self._flags.close()
+                self._flags = None
             self.flat.close()
             self.flat = None

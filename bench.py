@@ -101,11 +101,22 @@ def timed_loop(torch, dist, world, fn, steps: int):
         dist.barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    marks = []
     e0.record()
     for i in range(steps):
         fn(i)
+        if os.environ.get("TTB_BENCH_TRACE"):
+            m = torch.cuda.Event(enable_timing=True)
+            m.record()
+            marks.append(m)
     e1.record()
     torch.cuda.synchronize()
+    if marks and int(os.environ.get("RANK", "0")) == 0:
+        prev, per_step = e0, []
+        for m in marks:
+            per_step.append(round(prev.elapsed_time(m), 1))
+            prev = m
+        print(f"[trace] per-step ms: {per_step}", file=sys.stderr, flush=True)
     if world > 1:
         dist.barrier()
     t = torch.tensor([e0.elapsed_time(e1) / 1e3], device="cuda")
@@ -170,7 +181,18 @@ def run_ours(args) -> dict:
     if rank == 0:
         sampler.start()
     launches0 = L.ttb_launch_count()
+    if os.environ.get("TTB_BENCH_TRACE"):
+        step.trace_events = []
     t_kernel = timed_loop(torch, dist, world, lambda i: losses.append(step.compute(dev_batches[i % 4])), args.steps)
+    if step.trace_events:
+        ev, step.trace_events = step.trace_events, None
+        per = len(ev) // args.steps
+        names = ["fwd+loss", "bwd", "count", "optimizer"]
+        for k in range(args.steps):
+            seg = ev[k * per : (k + 1) * per]
+            phases = [round(a.elapsed_time(b), 1) for a, b in zip(seg[:-1], seg[1:])]
+            if rank == 0 and sum(phases) > 1.15 * 1e3 * t_kernel / args.steps:
+                print(f"[trace] slow step {k}: {dict(zip(names, phases))}", file=sys.stderr, flush=True)
     launches = L.ttb_launch_count() - launches0
 
     def e2e_step(i):

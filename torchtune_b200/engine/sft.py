@@ -499,13 +499,22 @@ class SFTTrainer:
                         self.parallel.all_reduce_sum_(num_tokens)
                     (loss_sum * (self.world_size / num_tokens)).backward()
                 else:
+                    last_micro = (idx + 1) % self._gradient_accumulation_steps == 0
+                    counted = False
+                    if last_micro and self.parallel is not None and getattr(self.parallel, "wants_backward_overlap", lambda _o: False)(self._optimizer):
+                        # the global token count is final before this backward: the data-parallel engine consumes each layer's
+                        # gradients (reduce, update, broadcast) while backward is still running on the earlier layers
+                        self.parallel.all_reduce_sum_(num_tokens, running_loss)
+                        counted = True
+                        self.parallel.arm_backward_overlap(self._optimizer, 1.0 / num_tokens, self._clip_grad_norm)
                     loss_sum.backward()
 
                 if (idx + 1) % self._gradient_accumulation_steps == 0:
                     grad_norm = None
                     if not self._optimizer_in_bwd:
                         if self.parallel is not None:
-                            self.parallel.all_reduce_sum_(num_tokens, running_loss)
+                            if not counted:
+                                self.parallel.all_reduce_sum_(num_tokens, running_loss)
                             grad_norm = self.parallel.optimizer_step(self._model, self._optimizer, 1.0 / num_tokens, self._clip_grad_norm)
                         else:
                             training.scale_grads_(params, 1.0 / num_tokens)

@@ -632,3 +632,35 @@ def test_fp8_linear_forward_backward_close_to_bf16(rowwise):
     rel = lambda a, b: float((a.float() - b).norm() / b.norm())
     assert rel(y, yf) < 0.06 and rel(x.grad, xf.grad) < 0.12 and rel(w.grad, wf.grad) < 0.12, (rel(y, yf), rel(x.grad, xf.grad), rel(w.grad, wf.grad))
     assert rel(bias.grad, bf.grad) < 1e-2
+
+
+# ----------------------------------------------------------------------------- failure detection: a bounded device wait that runs out
+def test_dp_bucket_wait_times_out_with_error_status_and_leaves_state_untouched():
+    """A peer that never declares its bucket final: the bucket kernel gives up after its cycle budget, stores an error code that the
+    host turns into an exception, and neither parameters nor optimizer state are modified.  The context stays usable."""
+    import ctypes
+
+    from torchtune_b200.ops._lib import KernelError, check, check_device_errors, err_word, lib, stream_ptr
+    from torchtune_b200.parallel.dp import _declare_dp
+
+    L = lib()
+    _declare_dp(L)
+    world, n = 2, 4096
+    grads = [_rand(n, seed=r) for r in range(world)]
+    params = [_rand(n, seed=10) for _ in range(world)]
+    before = params[0].clone()
+    m, v = torch.zeros(n // 2, dtype=torch.bfloat16, device="cuda"), torch.zeros(n // 2, dtype=torch.bfloat16, device="cuda")
+    flags = torch.zeros(world * L.ttb_dp_max_buckets(), dtype=torch.int32, device="cuda")  # nobody ever writes epoch 1 here
+    gp = (ctypes.c_void_p * world)(*[g.data_ptr() for g in grads])
+    pp = (ctypes.c_void_p * world)(*[p.data_ptr() for p in params])
+    L.ttb_dp_set_wait_cycles(200_000_000)  # ≈ 0.1 s
+    try:
+        check(L.ttb_dp_reduce_adamw_bcast(gp, pp, world, 0, 0, n // 2, m.data_ptr(), v.data_ptr(), None, None, None, 1.0, 1e-3, 0.9, 0.999, 1e-8, 0.01, 10.0, 31.6, 0,
+                                          flags.data_ptr(), 3, 1, err_word(flags.device).data_ptr(), stream_ptr()), "dp kernel")
+        with pytest.raises(KernelError, match="201"):
+            check_device_errors()
+    finally:
+        L.ttb_dp_set_wait_cycles(0)  # back to the default budget
+    assert torch.equal(params[0], before) and not m.any() and not v.any()
+    check_device_errors()  # the error word was cleared; the device keeps working
+    assert torch.isfinite(_rand(8, 8).float() @ _rand(8, 8).float()).all()

@@ -152,6 +152,7 @@ def test_full_distributed_expert_parallel_matches_data_parallel(tmp_path):
         )
         losses[name] = read_losses(tmp_path / name / "logs" / "log.txt")
     assert len(losses["ep"]) == 3
+    assert "moe_load_imbalance" in (tmp_path / "ep" / "logs" / "log.txt").read_text()
     torch.testing.assert_close(torch.tensor(losses["ep"]), torch.tensor(losses["dp"]), rtol=2e-4, atol=2e-4)
     a = torch.load(tmp_path / "dp" / "epoch_0" / "model-00001-of-00001.bin", weights_only=True) if (tmp_path / "dp" / "epoch_0" / "model-00001-of-00001.bin").exists() else None
     if a is not None:

@@ -24,6 +24,7 @@ from .. import config, modules, training, utils
 from ..config import DictConfig, ListConfig
 from ..config._resolve import get_component_from_path
 from ..data import padded_collate_packed, padded_collate_sft
+from ..modules.moe import expert_load_imbalance
 from ..modules.peft import (
     get_adapter_params,
     get_adapter_state_dict,
@@ -547,6 +548,9 @@ class SFTTrainer:
                         if grad_norm is not None:
                             log_dict["grad_norm"] = float(grad_norm)
                         log_dict.update(aux)
+                        imbalance = expert_load_imbalance(self._model)
+                        if imbalance is not None:
+                            log_dict["moe_load_imbalance"] = float(imbalance)
                         self._metric_logger.log_dict(log_dict, step=self.global_step)
                     running_loss.zero_()
                     num_tokens.zero_()

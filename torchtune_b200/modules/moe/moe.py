@@ -30,6 +30,7 @@ class TokenChoiceTopKRouter(nn.Module):
         else:
             num_tokens_per_expert = torch.bincount(flat, minlength=self.num_experts)
             order = torch.argsort(flat, stable=True)
+        self.tokens_per_expert = num_tokens_per_expert.detach()  # load statistics (see utils.expert_load_imbalance)
         return top_scores.reshape(-1)[order], order // self.experts_per_token, num_tokens_per_expert
 
 

@@ -48,7 +48,7 @@ __device__ __forceinline__ uint4 pack8f(const float (&f)[8]) {
 // gradients of bucket `slot` are complete (dp_signal_kernel, stream-ordered after the layer's backward); the reduce kernel of
 // rank q waits, with a cycle budget, until all peers' entries for that slot have reached the epoch.
 static constexpr int kMaxBuckets = 4096;
-static constexpr long long kFlagWaitCycles = 4000000000LL;
+static long long g_flag_wait_cycles = 4000000000LL;  // host-side setting, passed to every launch (ttb_dp_set_wait_cycles)
 
 struct FlagTable {
   int* flags[kMaxRanks];
@@ -72,7 +72,8 @@ dp_reduce_adamw_bcast_kernel(PeerTable peers, int rank, long long begin, long lo
                              __nv_bfloat16* __restrict__ v, float* __restrict__ gsum, float* __restrict__ sumsq_partials,
                              const float* __restrict__ scale_dev, float scale_host, float lr, float beta1, float beta2,
                              float eps, float weight_decay, float inv_bc1, float inv_sqrt_bc2, int mode,
-                             const int* __restrict__ my_flags, int slot, int epoch, int* __restrict__ err) {
+                             const int* __restrict__ my_flags, int slot, int epoch, int* __restrict__ err,
+                             long long wait_cycles) {
   __shared__ float red[8];
   __shared__ int give_up;
   if (my_flags != nullptr) {  // wait until every peer has declared this bucket final
@@ -86,7 +87,7 @@ dp_reduce_adamw_bcast_kernel(PeerTable peers, int rank, long long begin, long lo
       while (true) {
         asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
         if (v >= epoch) break;
-        if ((++spins & 0xff) == 0 && clock64() - t0 > kFlagWaitCycles) {
+        if ((++spins & 0xff) == 0 && clock64() - t0 > wait_cycles) {
           give_up = 1;
           atomicExch(err, 201);
           break;
@@ -221,7 +222,8 @@ extern "C" int ttb_dp_reduce_adamw_bcast(void* const* grad_ptrs, void* const* pa
   case W:                                                                                                           \
     dp_reduce_adamw_bcast_kernel<W><<<grid, 256, 0, s>>>(t, rank, begin, count, mm, vv, gsum, sumsq_partials,       \
                                                          scale_dev, scale_host, lr, beta1, beta2, eps, weight_decay, \
-                                                         inv_bc1, inv_sqrt_bc2, mode, my_flags, slot, epoch, err);   \
+                                                         inv_bc1, inv_sqrt_bc2, mode, my_flags, slot, epoch, err,    \
+                                                         g_flag_wait_cycles);                                        \
     break;
   switch (world) {
     TTB_DP_CASE(1)
@@ -249,3 +251,7 @@ extern "C" int ttb_dp_signal(void* const* flag_ptrs, int world, int rank, int sl
   return cudaGetLastError() == cudaSuccess ? kOk : kErrDriver;
 }
 extern "C" int ttb_dp_max_buckets() { return kMaxBuckets; }
+
+// Cycle budget of the cross-rank flag wait (default 4e9 ≈ 2–3 s).  When it runs out the kernel stores 201 in the error word and
+// returns without touching parameters or optimizer state; the host raises on its next check.
+extern "C" void ttb_dp_set_wait_cycles(long long cycles) { g_flag_wait_cycles = cycles > 0 ? cycles : 4000000000LL; }

@@ -351,6 +351,8 @@ def _declare_dp(L) -> None:
     L.ttb_dp_signal.restype = i32
     L.ttb_dp_grid.restype = i32
     L.ttb_dp_max_buckets.restype = i32
+    L.ttb_dp_set_wait_cycles.argtypes = [i64]
+    L.ttb_dp_set_wait_cycles.restype = None
     L._dp_declared = True
 
 

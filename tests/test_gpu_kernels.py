@@ -664,3 +664,37 @@ def test_dp_bucket_wait_times_out_with_error_status_and_leaves_state_untouched()
     assert torch.equal(params[0], before) and not m.any() and not v.any()
     check_device_errors()  # the error word was cleared; the device keeps working
     assert torch.isfinite(_rand(8, 8).float() @ _rand(8, 8).float()).all()
+
+
+# ----------------------------------------------------------------------------- weight all-gather → GEMM (ranks emulated on one GPU)
+@pytest.mark.parametrize("world,rows,K,M", [(1, 256, 320, 200), (2, 256, 320, 384), (4, 256, 192, 128), (8, 256, 256, 2304), (2, 1792, 512, 1024), (4, 64, 128, 256)])
+def test_gemm_weight_gather_fused_emulated_ranks(world, rows, K, M):
+    """Every emulated rank multiplies its own activations with the weight whose row shards live in `world` buffers (peer mappings
+    on a real group): remote shards are pulled by the kernel's copier warps, the own shard is read in place."""
+    import ctypes
+
+    from torchtune_b200.ops._lib import check_device_errors, err_word, lib, stream_ptr
+    from torchtune_b200.parallel.fsdp import _declare
+
+    L = lib()
+    _declare(L)
+    N = world * rows
+    if N <= 128 and rows % (128 if N > 64 else 64):
+        pytest.skip("shard smaller than an n-tile")
+    shards = [_rand(rows, K, scale=0.1, seed=30 + r) for r in range(world)]
+    ptrs = (ctypes.c_void_p * world)(*[s.data_ptr() for s in shards])
+    w_full = torch.cat(shards).float()
+    for rank in range(world):
+        x = _rand(M, K, scale=0.5, seed=60 + rank)
+        bias = _rand(N, scale=0.1, seed=80 + rank)
+        out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+        gathered = torch.full((N, K), float("nan"), dtype=torch.bfloat16, device="cuda")
+        sync = torch.full((2 + N // 64,), 5, dtype=torch.int32, device="cuda")
+        rc = L.ttb_gemm_wg_bf16(x.data_ptr(), ptrs, out.data_ptr(), gathered.data_ptr(), sync.data_ptr(), world, rank, rows, M, K, K, N, bias.data_ptr(),
+                                err_word(out.device).data_ptr(), stream_ptr())
+        assert rc == 0
+        _close(out, x.float() @ w_full.t() + bias.float(), 2e-2, 2e-2, f"wg_gemm rank {rank}")
+        remote = torch.ones(N, dtype=torch.bool, device="cuda")
+        remote[rank * rows : (rank + 1) * rows] = False
+        assert torch.equal(gathered[remote].float(), w_full[remote])
+    check_device_errors()

@@ -29,3 +29,9 @@ def test_tensor_parallel_decoder_two_gpus():
 def test_expert_parallel_moe_two_gpus():
     out = _torchrun(str(ROOT / "tests" / "multi_gpu_ep_worker.py"), 2, 29573)
     assert "EP_OK" in out
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_sharded_parameters_two_gpus():
+    out = _torchrun(str(ROOT / "tests" / "multi_gpu_zero3_worker.py"), 2, 29575)
+    assert "ZERO3_OK" in out

@@ -52,6 +52,10 @@ struct GemmParams {
 //      the next rank so the ranks do not all write to the same GPU at the same time.  The epilogue stages 32 × 64
 //      sub-tiles in shared memory and hands them to the TMA store unit (per-thread 16-byte stores to a peer become
 //      one NVLink write per row fragment and ran at a fraction of the link rate).
+//   5  weight all-gather → GEMM (sharded-parameter data parallelism): the rows of B (the weight's output features) are
+//      sharded over the ranks; copier warps pull the remote shards into a local [N, K] buffer n-tile by n-tile while the
+//      MMA pipeline works on the n-tiles of the own shard (read in place); tiles run n-major so that a gathered n-tile is
+//      consumed by all m-tiles right after it lands.  Shards must be whole n-tiles (rows_per_rank % BN == 0).
 static constexpr int kMaxTpWorld = 8;
 static constexpr int kTpAgThreads = 384;  // 8 GEMM warps + 4 copier warps
 static constexpr int kRsStageBytes = 4 * 2 * 4096;  // TP 2: per epilogue warp two 32 × 64 bf16 staging tiles, 1024 bytes after the stage ring
@@ -103,7 +107,7 @@ static constexpr int kMaxGroupedExperts = 1024;
 
 template <int TP>
 __device__ __forceinline__ int tp_rotate_m(int m_blk, int num_m, const TpArgs* tp) {
-  if (TP == 0 || TP == 3 || TP == 4) return m_blk;
+  if (TP == 0 || TP == 3 || TP == 4 || TP == 5) return m_blk;
   const int tiles_per_rank = tp->rows_per_rank / BM;
   const int first = (TP == 1 ? tp->rank : (tp->rank + 1) % tp->world) * tiles_per_rank;
   const int r = m_blk + first;
@@ -128,6 +132,18 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_
   const int r = t - group * per_group;
   m_blk = first_m + r % gsize;
   n_blk = r / gsize;
+}
+
+static constexpr int kWgPieceRows = 8;  // TP 5: weight rows per copier piece
+
+// TP 5 tile order: n-major, the n-tiles of the own weight shard first (rotation by rank · tiles-per-rank).
+template <int BN>
+__device__ __forceinline__ void wg_coords(int t, int num_m, int num_n, const TpArgs* tp, int& m_blk, int& n_blk) {
+  const int n_idx = t / num_m;
+  m_blk = t - n_idx * num_m;
+  const int first = tp->rank * (tp->rows_per_rank / BN);
+  n_blk = n_idx + first;
+  if (n_blk >= num_n) n_blk -= num_n;
 }
 
 template <int BN, bool A_MN, bool B_MN, int TP>
@@ -229,6 +245,25 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
         k_row0 = g_row0[expert];
         kb_count = (g_cnt[expert] + BK - 1) / BK;
       }
+      const CUtensorMap* mapB = &tmB;
+      int b_row = 0;
+      if (TP == 5) {
+        wg_coords<BN>(t, num_m, num_n, tp, m_blk, n_blk);
+        a_row = m_blk * BM;
+        b_row = n_blk * BN;
+        const int src = b_row / tp->rows_per_rank;
+        if (src == tp->rank) {  // own weight shard: read in place
+          mapB = &tp->tmA[src];
+          b_row -= src * tp->rows_per_rank;
+        } else {
+          if (!wait_count(tp->sync + 1 + n_blk, BN / kWgPieceRows)) {
+            *abort_flag = 1;
+            if (lane == 0) atomicExch(p.err, 106);
+            break;
+          }
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
+      }
       for (int kb = 0; kb < kb_count; ++kb) {
         if (!mbar_wait(&empty[stage], phase ^ 1)) {
           *abort_flag = 1;
@@ -255,6 +290,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
           } else if (B_MN) {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tmB, &full[stage], n_blk * BN + j * 64, k_row0 + kb * BK);
+          } else if (TP == 5) {
+            tma_load_2d(sb, mapB, &full[stage], kb * BK, b_row);
           } else {
             tma_load_2d(sb, &tmB, &full[stage], kb * BK, n_blk * BN);
           }
@@ -355,6 +392,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
         break;
       }
       tc_fence_after();
+      if (TP == 5) wg_coords<BN>(t, num_m, num_n, tp, m_blk, n_blk);
       int expert = 0;
       bool empty_expert = false;
       if (TP == 4) {
@@ -507,6 +545,43 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
 
   if ((TP == 2 || TP == 0) && warp >= 4 && warp < 8 && lane == 0) tma_store_wait<0>();  // every staged sub-tile has left shared memory and landed
 
+  if (TP == 5 && warp >= 8) {
+    // ------------------------------------------------------------------ copier warps (weight all-gather over peer memory)
+    const int ctid = threadIdx.x - 256;
+    const int tiles_per_rank = tp->rows_per_rank / BN;
+    constexpr int kPieces = BN / kWgPieceRows;
+    const int total = (num_n - tiles_per_rank) * kPieces;
+    const long long row_vecs = p.K / 8;
+    const long long piece_vecs = kWgPieceRows * row_vecs;
+    while (true) {
+      if (ctid == 0) *piece_slot = atomicAdd(tp->sync, 1);
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const int pc = *piece_slot;
+      if (pc >= total) break;
+      int n_blk = tp->rank * tiles_per_rank + tiles_per_rank + pc / kPieces;  // remote n-tiles in the order they are consumed
+      while (n_blk >= num_n) n_blk -= num_n;
+      const long long row0 = static_cast<long long>(n_blk) * BN + (pc % kPieces) * kWgPieceRows;
+      const int src = static_cast<int>(row0 / tp->rows_per_rank);
+      const uint4* s = reinterpret_cast<const uint4*>(tp->A_src[src]) + (row0 - static_cast<long long>(src) * tp->rows_per_rank) * row_vecs;
+      uint4* d = reinterpret_cast<uint4*>(tp->gathered) + row0 * row_vecs;
+      for (long long v = ctid; v < piece_vecs; v += 128 * 8) {
+        uint4 r[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (v + j * 128 < piece_vecs) r[j] = __ldcg(s + v + j * 128);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (v + j * 128 < piece_vecs) d[v + j * 128] = r[j];
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (ctid == 0) {
+        __threadfence();
+        atomicAdd(tp->sync + 1 + n_blk, 1);
+      }
+    }
+  }
+
   if (TP == 1 && warp >= 8) {
     // ------------------------------------------------------------------ copier warps (all-gather over peer memory)
     const int ctid = threadIdx.x - 256;
@@ -559,7 +634,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 }
 
 template <int BN, bool B_MN, int TP>
-__global__ void __launch_bounds__(TP == 1 ? kTpAgThreads : kThreads, 1)
+__global__ void __launch_bounds__((TP == 1 || TP == 5) ? kTpAgThreads : kThreads, 1)
 gemm_tp_kernel(const __grid_constant__ TpArgs tp, const __grid_constant__ CUtensorMap tmA,
                const __grid_constant__ CUtensorMap tmB, GemmParams p) {
   gemm_body<BN, false, B_MN, TP>(&tmA, &tmB, p, &tp);
@@ -718,7 +793,7 @@ static int launch_gemm_tp(const TpArgs& tp, const void* A, const void* B, const 
   const int num_tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   const int grid = num_tiles < sm_count() ? num_tiles : sm_count();
   TTB_COUNT_LAUNCH(1);
-  kern<<<grid, TP == 1 ? kTpAgThreads : kThreads, smem_bytes, stream>>>(tp, tmA, tmB, p);
+  kern<<<grid, (TP == 1 || TP == 5) ? kTpAgThreads : kThreads, smem_bytes, stream>>>(tp, tmA, tmB, p);
   if (cudaGetLastError() != cudaSuccess) return kErrDriver;
   return kOk;
 }
@@ -812,6 +887,39 @@ extern "C" int ttb_gemm_ag_bf16(const void* const* A_ranks, const void* B, void*
   p.bias = static_cast<const __nv_bfloat16*>(bias);
   p.alpha = 1.f, p.out_fp32 = 0, p.accumulate = 0, p.err = err;
   return dispatch_tp<1>(tp, gathered, B, p, K, ldb, b_mn, s);
+}
+
+// ttb_gemm_wg_bf16: C[M, world*rows_per_rank] = A[M, K] · concat_r(B_ranks[r])ᵀ (+ bias): B_ranks[r] is rank r's contiguous
+//                   [rows_per_rank, K] shard of the weight (peer memory allowed, pulled once by the copier warps);
+//                   `gathered` is a local contiguous [world*rows_per_rank, K] buffer that receives the remote shards (the own
+//                   rows are not copied); `sync` is a local int array of 1 + N/64 entries (zeroed here).
+//                   rows_per_rank must be a multiple of the n-tile (256 when N > 128, else 128 / 64).
+extern "C" int ttb_gemm_wg_bf16(const void* A, const void* const* B_ranks, void* C, void* gathered, int* sync, int world, int rank,
+                                int rows_per_rank, int M, int K, long long lda, long long ldc, const void* bias, int* err, void* stream) {
+  using namespace ttb;
+  if (world < 1 || world > kMaxTpWorld || rank < 0 || rank >= world) return kErrBadShape;
+  if (rows_per_rank <= 0 || M <= 0 || K <= 0) return kErrBadShape;
+  const int N = world * rows_per_rank;
+  const int bn = N > 128 ? 256 : (N > 64 ? 128 : 64);
+  if ((rows_per_rank % bn) || (lda & 7) || (ldc & 7) || (K & 7)) return kErrBadShape;
+  if (gathered == nullptr || sync == nullptr || (reinterpret_cast<uintptr_t>(gathered) & 15)) return kErrBadShape;
+  TpArgs tp;
+  memset(&tp, 0, sizeof(tp));
+  tp.world = world, tp.rank = rank, tp.rows_per_rank = rows_per_rank;
+  tp.gathered = gathered, tp.sync = sync;
+  for (int r = 0; r < world; ++r) {
+    if (reinterpret_cast<uintptr_t>(B_ranks[r]) & 15) return kErrBadShape;
+    tp.A_src[r] = B_ranks[r];
+    int rc = make_tmap_2d(&tp.tmA[r], B_ranks[r], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_per_rank, K, K, bn, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != kOk) return rc;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(sync, 0, sizeof(int) * (1 + static_cast<size_t>(N) / 64), s) != cudaSuccess) return kErrDriver;
+  GemmParams p;
+  p.M = M, p.N = N, p.K = K, p.C = C, p.ldc = ldc;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.alpha = 1.f, p.out_fp32 = 0, p.accumulate = 0, p.err = err;
+  return dispatch_tp<5>(tp, A, gathered, p, lda, K, 0, s);
 }
 
 extern "C" int ttb_gemm_rs_bf16(const void* A, const void* B, void* const* C_ranks, int world, int rank, int rows_per_rank,

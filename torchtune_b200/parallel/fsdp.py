@@ -1,0 +1,236 @@
+"""Sharded-parameter data parallelism (ZeRO-3 for the linear weights) with a fused weight all-gather → GEMM.
+
+The reference shards every parameter with FSDP2 (torchtune/training/_distributed.py:661-714): each layer's flat parameter is
+all-gathered before its forward and again before its backward, gradients are reduce-scattered, and the optimizer works on the
+shards.  Here the large ``nn.Linear`` weights — which are practically all of a decoder's parameters — are sharded by output rows
+over the ranks and live in one peer-visible store; everything else (norm scales, embeddings, small or odd-shaped linears) stays
+replicated with its gradient summed before the optimizer step.
+
+* forward: ``ttb_gemm_wg_bf16`` — the GEMM's copier warps pull the peers' weight shards over NVLink n-tile by n-tile into a
+  reusable local workspace while the tensor cores already work on the n-tiles of the own shard; no separate all-gather, no
+  per-layer collective on the critical path (shards only change at the optimizer step, so forward needs no barrier at all);
+* backward: the weight is gathered again (NCCL all-gather into the workspace), ``dx = dy · W`` and ``dW = dyᵀ · x`` run as plain
+  tcgen05 GEMMs and ``dW`` is reduce-scattered to the owners of the rows;
+* memory per rank: ``1 / world`` of the linear weights, their gradients and optimizer state, plus one gathered weight.
+
+Without CUDA (gloo) the same module runs on ``all_gather`` / ``all_reduce`` so the logic is testable on CPU.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+from torch import nn
+
+from .fabric import PeerBuffer
+
+_BF16 = torch.bfloat16
+
+
+def _declare(L) -> None:
+    if getattr(L, "_wg_declared", False):
+        return
+    vp, i32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+    L.ttb_gemm_wg_bf16.argtypes = [vp, ctypes.POINTER(vp), vp, vp, vp, i32, i32, i32, i32, i32, i64, i64, vp, vp, vp]
+    L.ttb_gemm_wg_bf16.restype = i32
+    L._wg_declared = True
+
+
+class ShardedWeightContext:
+    """Peer-visible store for the weight shards of one model plus the workspace the gathered weight lands in."""
+
+    def __init__(self, device: torch.device, group=None, *, store_numel: int, max_weight_numel: int, max_out_features: int):
+        self.device, self.group = device, group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.cuda = device.type == "cuda"
+        self._cursor = 0
+        self._token = torch.zeros(1, device=device)
+        if self.cuda:
+            from ..ops._lib import lib
+
+            _declare(lib())
+            self.store = PeerBuffer(max(store_numel, 8) * 2, device, group)
+            self.workspace = torch.empty(max(max_weight_numel, 8), dtype=_BF16, device=device)
+            self.sync = torch.empty(2 + max_out_features // 64, dtype=torch.int32, device=device)
+
+    def barrier(self) -> None:
+        if self.world > 1:
+            dist.all_reduce(self._token, group=self.group)
+
+    def close(self) -> None:
+        if self.cuda:
+            torch.cuda.synchronize(self.device)
+            self.barrier()
+            self.store.close()
+
+    def place(self, shard: torch.Tensor) -> torch.Tensor:
+        """Copy ``shard`` (``[rows, K]``) into the store and return the view that replaces it (same offset on every rank)."""
+        if not self.cuda:
+            return shard.detach().clone()
+        n = shard.numel()
+        view = self.store.tensor(_BF16, self._cursor + n)[self._cursor :].view(shard.shape)
+        view.copy_(shard)
+        self._cursor += (n + 7) // 8 * 8
+        return view
+
+    def _store_offset(self, shard: torch.Tensor) -> Optional[int]:
+        """Element offset of ``shard`` inside the store (identical on every rank), or ``None`` if it lives elsewhere."""
+        if not self.cuda:
+            return None
+        delta = shard.data_ptr() - self.store.local_ptr
+        return delta // 2 if 0 <= delta < self.store.nbytes and delta % 16 == 0 else None
+
+    # ------------------------------------------------------------------ forward: fused gather + GEMM
+    def fusable(self, x2: torch.Tensor, shard: torch.Tensor) -> bool:
+        rows, k = shard.shape
+        n = rows * self.world
+        bn = 256 if n > 128 else (128 if n > 64 else 64)
+        return self.cuda and x2.dtype == _BF16 and shard.dtype == _BF16 and rows % bn == 0 and k % 8 == 0 and shard.is_contiguous() and self._store_offset(shard) is not None
+
+    def linear(self, x2: torch.Tensor, shard: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:
+        """``x2 @ concat_ranks(shard).T (+ bias)`` → ``[T, world·rows]``."""
+        rows, k = shard.shape
+        if not self.fusable(x2, shard):
+            return F.linear(x2, self.gather(shard), bias)
+        from ..ops._lib import check, err_word, lib, stream_ptr
+
+        n = rows * self.world
+        x2 = x2 if x2.is_contiguous() else x2.contiguous()
+        out = torch.empty(x2.shape[0], n, dtype=_BF16, device=self.device)
+        ptrs = (ctypes.c_void_p * self.world)(*[p + 2 * self._store_offset(shard) for p in self.store.peer_ptrs])
+        check(lib().ttb_gemm_wg_bf16(x2.data_ptr(), ptrs, out.data_ptr(), self.workspace.data_ptr(), self.sync.data_ptr(), self.world, self.rank, rows, x2.shape[0], k,
+                                     k, n, None if bias is None else bias.data_ptr(), err_word(self.device).data_ptr(), stream_ptr()), "gemm_wg")
+        return out
+
+    # ------------------------------------------------------------------ backward: plain collectives
+    def gather(self, shard: torch.Tensor) -> torch.Tensor:
+        if self.world == 1:
+            return shard
+        rows, k = shard.shape
+        if self.cuda and shard.dtype == _BF16:
+            full = self.workspace[: self.world * rows * k].view(self.world * rows, k)
+            dist.all_gather_into_tensor(full, shard.contiguous(), group=self.group)
+            return full
+        src = shard.float() if shard.dtype == _BF16 else shard
+        parts = [torch.empty_like(src) for _ in range(self.world)]
+        dist.all_gather(parts, src.contiguous(), group=self.group)
+        return torch.cat(parts).to(shard.dtype)
+
+    def reduce_scatter_rows(self, full: torch.Tensor) -> torch.Tensor:
+        if self.world == 1:
+            return full
+        rows = full.shape[0] // self.world
+        if self.cuda:
+            out = torch.empty(rows, full.shape[1], dtype=full.dtype, device=full.device)
+            dist.reduce_scatter_tensor(out, full.contiguous(), group=self.group)
+            return out
+        f = full.float().contiguous()
+        dist.all_reduce(f, group=self.group)
+        return f[self.rank * rows : (self.rank + 1) * rows].to(full.dtype)
+
+
+class _WeightGatherLinear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, shard, bias, sw: ShardedWeightContext):
+        ctx.sw = sw
+        ctx.save_for_backward(x, shard)
+        ctx.has_bias = bias is not None
+        x2 = x.reshape(-1, x.shape[-1])
+        return sw.linear(x2, shard, bias).view(*x.shape[:-1], shard.shape[0] * sw.world)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from .tp import _wgrad
+
+        x, shard = ctx.saved_tensors
+        sw = ctx.sw
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        x2 = x.reshape(-1, x.shape[-1])
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            w_full = sw.gather(shard)
+            if dy2.is_cuda and dy2.dtype == _BF16:
+                from ..ops._cuda import gemm
+
+                dx = gemm(dy2 if dy2.is_contiguous() else dy2.contiguous(), w_full, b_mn=True)
+            else:
+                dx = dy2 @ w_full
+            dx = dx.view(x.shape)
+        if ctx.needs_input_grad[1]:
+            dw = sw.reduce_scatter_rows(_wgrad(dy2, x2))
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.sum(0)
+        return dx, dw, db, None
+
+
+class ShardedLinear(nn.Module):
+    """``nn.Linear`` whose weight rows are split over the ranks (``weight``: this rank's ``[out / world, in]`` rows)."""
+
+    def __init__(self, lin: nn.Linear, sw: ShardedWeightContext):
+        super().__init__()
+        self.sw = sw
+        self.in_features, self.out_features = lin.in_features, lin.out_features
+        rows = lin.out_features // sw.world
+        shard = lin.weight.data[sw.rank * rows : (sw.rank + 1) * rows]
+        self.weight = nn.Parameter(sw.place(shard), requires_grad=lin.weight.requires_grad)
+        self.bias = lin.bias
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return _WeightGatherLinear.apply(x, self.weight, self.bias, self.sw)
+
+    def full_weight(self) -> torch.Tensor:
+        return self.sw.gather(self.weight.detach()).clone()
+
+
+def shard_linear_weights(model: nn.Module, device: torch.device, group=None, *, min_numel: int = 1 << 16) -> nn.Module:
+    """Replace every plain ``nn.Linear`` with at least ``min_numel`` weights whose rows split evenly into whole n-tiles by a
+    :class:`ShardedLinear` (in place) and attach ``_replicated``, ``sync_replicated_grads()``, ``after_optimizer_step()`` and
+    ``full_state_dict()`` (checkpoint layout; collective) to ``model``."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+
+    def eligible(m: nn.Module) -> bool:
+        if type(m).__name__ != "Linear" or not isinstance(m, nn.Linear) or m.weight.numel() < min_numel:
+            return False
+        if device.type != "cuda":
+            return m.out_features % world == 0
+        rows = m.out_features // world
+        bn = 256 if m.out_features > 128 else (128 if m.out_features > 64 else 64)
+        return m.out_features % world == 0 and rows % bn == 0 and m.in_features % 8 == 0 and m.weight.dtype == _BF16
+
+    targets = [(parent, name, child) for parent in model.modules() for name, child in parent.named_children() if eligible(child)]
+    store = sum(((c.weight.numel() // world) + 7) // 8 * 8 for _, _, c in targets)
+    sw = ShardedWeightContext(device, group, store_numel=store, max_weight_numel=max((c.weight.numel() for _, _, c in targets), default=8),
+                              max_out_features=max((c.out_features for _, _, c in targets), default=64))
+    for parent, name, child in targets:
+        setattr(parent, name, ShardedLinear(child, sw))
+        child.weight.data = torch.empty(0, dtype=child.weight.dtype, device=child.weight.device)
+    sharded = {id(m.weight) for m in model.modules() if isinstance(m, ShardedLinear)}
+    model._replicated = [p for p in model.parameters() if id(p) not in sharded]
+    model._sw = sw
+
+    def sync_replicated_grads() -> None:
+        grads = [p.grad for p in model._replicated if p.grad is not None]
+        if not grads or sw.world == 1:
+            return
+        flat = torch.cat([g.reshape(-1).float() for g in grads])
+        dist.all_reduce(flat, group=group)
+        off = 0
+        for g in grads:
+            g.copy_(flat[off : off + g.numel()].view_as(g))
+            off += g.numel()
+
+    def full_state_dict() -> Dict[str, torch.Tensor]:
+        out: Dict[str, torch.Tensor] = {}
+        fulls = {f"{name}.weight": m.full_weight() for name, m in model.named_modules() if isinstance(m, ShardedLinear)}
+        for k, v in model.state_dict().items():
+            out[k] = fulls.get(k, v.detach())
+        return out
+
+    model.sync_replicated_grads = sync_replicated_grads
+    model.after_optimizer_step = sw.barrier  # shards may be read by peers again only after every rank has updated its own
+    model.full_state_dict = full_state_dict
+    return model

@@ -134,6 +134,9 @@ class TensorParallelOptimizer:
             for p in params:
                 p.grad.mul_(coef.to(p.grad.dtype))
         self.optimizer.step()
+        after = getattr(model, "after_optimizer_step", None)
+        if after is not None:
+            after()
 
 
 class ParallelStrategy(DataParallelEngine):
@@ -177,6 +180,10 @@ class ParallelStrategy(DataParallelEngine):
         self.tp = None  # TensorParallelContext, created in shard_model
         self.ep = None  # ExpertParallelContext, created in shard_model
         self.cp = None  # ContextParallelContext, created in shard_model
+        self.zero3 = None  # ShardedWeightContext when `shard_parameters: True` (linear weights sharded over the ranks)
+        self._shard_parameters = bool(get("shard_parameters", False))
+        if self._shard_parameters and (self.dims.tp_enabled or self.ep_dim > 1 or self.dims.cp_enabled):
+            raise NotImplementedError("shard_parameters combines with plain data parallelism only")
         self._cfg = cfg
         self._cpu_offload = bool(get("fsdp_cpu_offload", False))
 
@@ -289,6 +296,15 @@ class ParallelStrategy(DataParallelEngine):
             if is_lora:
                 raise NotImplementedError("expert parallelism is implemented for full fine-tuning")
             return self._shard_model_ep(model, cfg)
+        if self._shard_parameters:
+            if is_lora:
+                raise NotImplementedError("shard_parameters is implemented for full fine-tuning")
+            from .fsdp import shard_linear_weights
+
+            get = cfg.get if hasattr(cfg, "get") else (lambda k, d=None: d)
+            model = shard_linear_weights(model, self.device, None, min_numel=int(get("shard_parameters_min_numel", 1 << 16)))
+            self.zero3 = model._sw
+            return model
         self.prepare(model)
         if self.dims.cp_enabled:
             self._attach_context_parallel(model)
@@ -305,7 +321,7 @@ class ParallelStrategy(DataParallelEngine):
 
     # optimizer ---------------------------------------------------------------------------
     def build_optimizer(self, model: nn.Module, cfg_optimizer=None, opt_state: Optional[Dict[str, Any]] = None, **kwargs: Any):
-        if self.tp is not None or self.ep is not None:
+        if self.tp is not None or self.ep is not None or self.zero3 is not None:
             from .. import config
 
             opt = TensorParallelOptimizer(self, model, config.instantiate(cfg_optimizer, [p for p in model.parameters() if p.requires_grad]))
@@ -342,7 +358,7 @@ class ParallelStrategy(DataParallelEngine):
 
     def optimizer_step(self, model: nn.Module, optimizer, grad_scale, clip_grad_norm: Optional[float] = None):
         clip = float(clip_grad_norm) if clip_grad_norm is not None else None
-        if self.tp is not None or self.ep is not None:
+        if self.tp is not None or self.ep is not None or self.zero3 is not None:
             optimizer.step(grad_scale=grad_scale, max_grad_norm=clip)
             optimizer.zero_grad()
             return optimizer.last_grad_norm
@@ -352,7 +368,7 @@ class ParallelStrategy(DataParallelEngine):
     def gather_full_state_dict(self, model: nn.Module) -> Dict[str, Any]:
         from ..training._distributed import gather_cpu_state_dict
 
-        if self.tp is not None or self.ep is not None:
+        if self.tp is not None or self.ep is not None or self.zero3 is not None:
             full = model.full_state_dict()  # collective: every rank takes part
             return {k: v.cpu() for k, v in full.items()} if self.rank == 0 else {}
 
@@ -368,6 +384,9 @@ class ParallelStrategy(DataParallelEngine):
         if self.ep is not None:
             self.ep.close()
             self.ep = None
+        if self.zero3 is not None:
+            self.zero3.close()
+            self.zero3 = None
         super().shutdown()
         if self._owns_group and dist.is_initialized():
             dist.destroy_process_group()

@@ -186,9 +186,9 @@ class ShardedLinear(nn.Module):
         return self.sw.gather(self.weight.detach()).clone()
 
 
-def shard_linear_weights(model: nn.Module, device: torch.device, group=None, *, min_numel: int = 1 << 16) -> nn.Module:
+def shard_linear_weights(model: nn.Module, device: torch.device, group=None, *, min_numel: int = 1 << 16, exclude=("output",)) -> nn.Module:
     """Replace every plain ``nn.Linear`` with at least ``min_numel`` weights whose rows split evenly into whole n-tiles by a
-    :class:`ShardedLinear` (in place) and attach ``_replicated``, ``sync_replicated_grads()``, ``after_optimizer_step()`` and
+    :class:`ShardedLinear` (in place; module paths in ``exclude`` are left alone) and attach ``_replicated``, ``sync_replicated_grads()``, ``after_optimizer_step()`` and
     ``full_state_dict()`` (checkpoint layout; collective) to ``model``."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
 
@@ -201,7 +201,9 @@ def shard_linear_weights(model: nn.Module, device: torch.device, group=None, *, 
         bn = 256 if m.out_features > 128 else (128 if m.out_features > 64 else 64)
         return m.out_features % world == 0 and rows % bn == 0 and m.in_features % 8 == 0 and m.weight.dtype == _BF16
 
-    targets = [(parent, name, child) for parent in model.modules() for name, child in parent.named_children() if eligible(child)]
+    # the output projection stays whole: the fused linear + cross-entropy loss reads its weight directly
+    targets = [(parent, name, child) for pname, parent in model.named_modules() for name, child in parent.named_children()
+               if eligible(child) and (f"{pname}.{name}" if pname else name) not in exclude]
     store = sum(((c.weight.numel() // world) + 7) // 8 * 8 for _, _, c in targets)
     sw = ShardedWeightContext(device, group, store_numel=store, max_weight_numel=max((c.weight.numel() for _, _, c in targets), default=8),
                               max_out_features=max((c.out_features for _, _, c in targets), default=64))

@@ -16,7 +16,8 @@ MLP width (each rank holds ``hidden / world`` of it), i.e. the shapes of one Meg
 Rank 0 prints one JSON line per measurement.
 
 ``--op ep`` times the expert-parallel MoE layer instead (``--rows`` tokens over all ranks, ``--dim``, ``--hidden`` expert width,
-``--experts``, ``--top-k``): the plan / push / pull kernels, the layer forward and forward+backward.
+``--experts``, ``--top-k``): the plan / push / pull kernels, the layer forward and forward+backward.  ``--op wg`` times the
+sharded-parameter forward (``--rows`` tokens per rank, weight ``[--hidden, --dim]`` split over the ranks).
 """
 from __future__ import annotations
 
@@ -106,9 +107,45 @@ def bench_ep(args, dev, world, rank) -> None:
     ep.close()
 
 
+def bench_wg(args, dev, world, rank) -> None:
+    """Sharded-parameter forward: fused weight all-gather → GEMM against NCCL ``all_gather_into_tensor`` of the weight + GEMM and
+    against the GEMM alone.  ``--rows`` tokens per rank, weight ``[--hidden, --dim]`` split by rows over the ranks."""
+    from ..ops._cuda import gemm
+    from ..ops._lib import check_device_errors
+    from .fsdp import ShardedWeightContext
+
+    T, K, N = args.rows, args.dim, args.hidden
+    rows = N // world
+    sw = ShardedWeightContext(dev, None, store_numel=rows * K, max_weight_numel=N * K, max_out_features=N)
+    g = torch.Generator(device="cuda").manual_seed(rank)
+    shard = sw.place((torch.randn(rows, K, generator=g, device=dev) * 0.02).bfloat16())
+    x = (torch.randn(T, K, generator=g, device=dev) * 0.3).bfloat16()
+    w_local = (torch.randn(N, K, generator=g, device=dev) * 0.02).bfloat16()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    sw.barrier()
+
+    def nccl_path():
+        return gemm(x, sw.gather(shard))
+
+    a, b = sw.linear(x, shard, None), nccl_path()
+    torch.cuda.synchronize()
+    err = float((a.float() - b.float()).abs().max() / b.float().abs().max())
+    flops = 2.0 * T * K * N
+    results = []
+    for name, fn in (("wg_gemm_fused", lambda: sw.linear(x, shard, None)), ("wg_gemm_nccl", nccl_path), ("gemm_only_local", lambda: gemm(x, w_local))):
+        ms = _time(fn, args.iters, args.warmup, flush)
+        results.append({"op": name, "world": world, "tokens": T, "dim": K, "out_features": N, "ms": round(ms, 4), "tflops_per_gpu": round(flops / ms / 1e9, 1)})
+    check_device_errors()
+    if rank == 0:
+        print(json.dumps({"rel_err_fused_vs_nccl": err, "weight_bytes_over_nvlink_per_gpu": (world - 1) * rows * K * 2}))
+        for r in results:
+            print(json.dumps(r))
+    sw.close()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", choices=["tp", "ep"], default="tp")
+    ap.add_argument("--op", choices=["tp", "ep", "wg"], default="tp")
     ap.add_argument("--experts", type=int, default=16)
     ap.add_argument("--top-k", type=int, default=1)
     ap.add_argument("--capacity-factor", type=float, default=None)
@@ -125,8 +162,8 @@ def main() -> None:
     world, rank = dist.get_world_size(), dist.get_rank()
     dev = torch.device("cuda", local)
 
-    if args.op == "ep":
-        bench_ep(args, dev, world, rank)
+    if args.op in ("ep", "wg"):
+        (bench_ep if args.op == "ep" else bench_wg)(args, dev, world, rank)
         dist.destroy_process_group()
         return
 

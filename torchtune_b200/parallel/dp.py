@@ -7,12 +7,13 @@ precedes the layers, one for what follows) and every rank owns the ``1 / world``
 its rank's index of **every** bucket, so that the communication of one bucket keeps the
 links of all GPUs busy.  The communication of a bucket is a single kernel per rank
 (``ttb_dp_reduce_adamw_bcast``): pull the gradient slices of all peers, reduce in fp32,
-AdamW on the owned slice, push the new parameters to all peers.  Buckets are processed on a
+AdamW on the owned slice, push the new parameters to all peers.  Buckets can be processed on a
 side stream *during backward*, as soon as the layer's gradients are final on every rank
 (a tensor hook on the layer's input gradient, a 4-byte all-reduce as the cross-rank
 barrier), so reduction, optimizer and broadcast hide behind the backward GEMMs of the
 earlier layers; with gradient clipping only the reduction is overlapped and the update
-follows once the global norm is known.  Compared with the reference's FSDP2 path
+follows once the global norm is known.  (The hand-over during backward is opt-in through
+``TTB_DP_OVERLAP_MIN_WORLD``; by default all buckets are processed right after backward.)  Compared with the reference's FSDP2 path
 (per-layer all-gather in forward and backward, per-layer reduce-scatter, then a separate
 scale pass and optimizer step — torchtune/training/_distributed.py:661-714,
 recipes/full_finetune_distributed.py:1030-1050) this moves 2 instead of 3 model-sized
@@ -380,8 +381,10 @@ class DataParallelEngine:
         self._flags = None
         import os
 
-        # from 4 ranks on the NVLink traffic of a step outweighs what the concurrent update costs the backward GEMMs
-        self.min_world_for_overlap = int(os.environ.get("TTB_DP_OVERLAP_MIN_WORLD", "4"))
+        # Handing buckets to the optimizer during backward is opt-in (set the smallest world size it should be used at):
+        # measured on the 8B model it lost on 1 and 2 GPUs (the HBM-bound update competes with the backward GEMMs) and
+        # made no difference on 4 (≈ 484 ms per step either way), so the simpler after-backward protocol is the default.
+        self.min_world_for_overlap = int(os.environ.get("TTB_DP_OVERLAP_MIN_WORLD", "1000000"))
 
     # sizes the recipes ask for ------------------------------------------------------------
     dp_size = property(lambda self: self.world)

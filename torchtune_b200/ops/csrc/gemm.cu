@@ -66,6 +66,7 @@ struct alignas(64) TpArgs {
   const void* A_src[kMaxTpWorld];   // TP 1: the same shards as raw pointers for the copier warps (row pitch K)
   void* gathered;                   // TP 1: local [world * rows_per_rank, K] buffer the copiers fill
   int* sync;                        // TP 1: [0] piece ticket, [1 + m] finished pieces of m-tile m (zeroed per launch)
+  CUtensorMap tmC;                  // TP 1 / 5: the local output [M, N], box 64 × 32 (TMA-store epilogue)
   void* C[kMaxTpWorld];             // TP 2: per-rank staging buffer [world, rows_per_rank, ldc]
   int world, rank, rows_per_rank, gather_own;
 };
@@ -409,12 +410,12 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
         row_ok = (quarter * 32 + lane) < ga->tile_rows[m_blk];
       }
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
-      if (TP == 2 || (TP == 0 && p.tma_store)) {
+      if (TP == 2 || ((TP == 0 || TP == 1 || TP == 5) && p.tma_store)) {
         // this warp's 32 rows leave through the TMA store unit, 64 columns at a time (TP 2: into the owner's staging slot)
         uint8_t* stage_base = smem + Cfg::kStages * Cfg::kStageBytes + 1024;  // 1024-byte aligned: after the barrier block
         uint8_t* my_stage = stage_base + quarter * 8192;
         const int row0 = m_blk * BM + quarter * 32;
-        const CUtensorMap* mapC = tmC_ptr;
+        const CUtensorMap* mapC = (TP == 1 || TP == 5) ? &tp->tmC : tmC_ptr;
         int slot_row0 = row0;
         if (TP == 2) {
           const int owner = row0 / tp->rows_per_rank;
@@ -438,7 +439,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
               float f[8];
 #pragma unroll
               for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(r[j * 8 + i]) * p.alpha;
-              if (TP == 0 && p.bias != nullptr) {
+              if (TP != 2 && p.bias != nullptr) {
                 const int cb = col0 + h * 32 + j * 8;
 #pragma unroll
                 for (int i = 0; i < 8; ++i)
@@ -543,7 +544,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
     }
   }
 
-  if ((TP == 2 || TP == 0) && warp >= 4 && warp < 8 && lane == 0) tma_store_wait<0>();  // every staged sub-tile has left shared memory and landed
+  if ((TP == 2 || TP == 0 || TP == 1 || TP == 5) && warp >= 4 && warp < 8 && lane == 0) tma_store_wait<0>();  // every staged sub-tile has left shared memory and landed
 
   if (TP == 5 && warp >= 8) {
     // ------------------------------------------------------------------ copier warps (weight all-gather over peer memory)
@@ -782,8 +783,16 @@ static int launch_gemm_tp(const TpArgs& tp, const void* A, const void* B, const 
   else
     rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.N, p.K, ldb, BN, BK, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != kOk) return rc;
+  TpArgs tq = tp;
+  GemmParams q = p;
+  if (TP == 1 || TP == 5) {
+    q.tma_store = (!p.out_fp32 && !p.accumulate && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0 &&
+                   make_tmap_2d(&tq.tmC, p.C, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.M, p.N, p.ldc, 32, 64, CU_TENSOR_MAP_SWIZZLE_128B) == kOk)
+                      ? 1
+                      : 0;
+  }
   auto kern = gemm_tp_kernel<BN, B_MN, TP>;
-  constexpr int smem_bytes = Cfg::kSmemBytes + (TP == 2 ? 768 + kRsStageBytes : 0);  // barriers take the first 256 of the 1024 bytes
+  constexpr int smem_bytes = Cfg::kSmemBytes + 768 + kRsStageBytes;  // barriers take the first 256 of the 1024 bytes before the staging tiles
   static_assert(smem_bytes <= 232448, "shared memory budget of one CTA");
   static bool attr_set = false;
   if (!attr_set) {
@@ -793,7 +802,7 @@ static int launch_gemm_tp(const TpArgs& tp, const void* A, const void* B, const 
   const int num_tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   const int grid = num_tiles < sm_count() ? num_tiles : sm_count();
   TTB_COUNT_LAUNCH(1);
-  kern<<<grid, (TP == 1 || TP == 5) ? kTpAgThreads : kThreads, smem_bytes, stream>>>(tp, tmA, tmB, p);
+  kern<<<grid, (TP == 1 || TP == 5) ? kTpAgThreads : kThreads, smem_bytes, stream>>>(tq, tmA, tmB, q);
   if (cudaGetLastError() != cudaSuccess) return kErrDriver;
   return kOk;
 }

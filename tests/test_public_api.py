@@ -1,0 +1,82 @@
+"""The documented public surface (names a user of the reference imports) resolves in this package."""
+import importlib
+
+import pytest
+
+API = {
+    "torchtune_b200.config": ["instantiate", "parse", "validate", "log_config"],
+    "torchtune_b200.data": [
+        "GrammarErrorCorrectionTemplate", "SummarizeTemplate", "QuestionAnswerTemplate", "PromptTemplate", "PromptTemplateInterface", "ChatMLTemplate", "Message", "Role",
+        "InputOutputToMessages", "ShareGPTToMessages", "OpenAIToMessages", "ChosenRejectedToMessages", "AlpacaToMessages", "padded_collate", "padded_collate_dpo",
+        "padded_collate_packed", "padded_collate_sft", "padded_collate_tiled_images_and_mask", "left_pad_sequence", "validate_messages", "truncate", "load_image",
+        "format_content_with_images", "mask_messages",
+    ],
+    "torchtune_b200.datasets": [
+        "alpaca_dataset", "alpaca_cleaned_dataset", "grammar_dataset", "hh_rlhf_helpful_dataset", "samsum_dataset", "slimorca_dataset", "stack_exchange_paired_dataset",
+        "cnn_dailymail_articles_dataset", "wikitext_dataset", "instruct_dataset", "chat_dataset", "preference_dataset", "text_completion_dataset", "TextCompletionDataset",
+        "ConcatDataset", "PackedDataset", "PreferenceDataset", "SFTDataset",
+    ],
+    "torchtune_b200.datasets.multimodal": ["llava_instruct_dataset", "the_cauldron_dataset", "vqa_dataset"],
+    "torchtune_b200.generation": ["generate", "generate_next_token", "sample", "get_causal_mask_from_padding_mask", "get_position_ids_from_padding_mask"],
+    "torchtune_b200.modules": [
+        "MultiHeadAttention", "FeedForward", "KVCache", "RotaryPositionalEmbeddings", "RMSNorm", "Fp32LayerNorm", "TanhGate", "TiedLinear", "TransformerSelfAttentionLayer",
+        "TransformerCrossAttentionLayer", "TransformerDecoder", "VisionTransformer", "LayerDropout", "prepare_layer_dropout", "classifier_model", "FrozenNF4Linear",
+    ],
+    "torchtune_b200.modules.loss": ["LinearCrossEntropyLoss", "ForwardKLLoss", "ForwardKLWithChunkedOutputLoss", "ReverseKLWithChunkedOutputLoss", "SymmetricKLWithChunkedOutputLoss"],
+    "torchtune_b200.modules.optim": ["OptimizerInBackward"],
+    "torchtune_b200.modules.transforms.tokenizers": [
+        "SentencePieceBaseTokenizer", "TikTokenBaseTokenizer", "HuggingFaceBaseTokenizer", "ModelTokenizer", "BaseTokenizer", "tokenize_messages_no_special_tokens", "parse_hf_tokenizer_json",
+    ],
+    "torchtune_b200.modules.peft": [
+        "LoRALinear", "DoRALinear", "AdapterModule", "get_adapter_params", "set_trainable_params", "get_adapter_state_dict", "validate_missing_and_unexpected_for_lora", "disable_adapter",
+    ],
+    "torchtune_b200.modules.model_fusion": ["DeepFusionModel", "EarlyFusionModel", "FusionLayer", "FusionEmbedding", "register_fusion_module", "get_fusion_params"],
+    "torchtune_b200.modules.common_utils": ["reparametrize_as_dtype_state_dict_post_hook", "local_kv_cache", "disable_kv_cache", "delete_kv_caches"],
+    "torchtune_b200.modules.embedding_utils": ["resize_token_embeddings"],
+    "torchtune_b200.modules.transforms": ["Transform", "VisionCrossAttentionMask"],
+    "torchtune_b200.modules.moe": ["MoE", "GroupedExperts", "LoRAGroupedExperts", "TokenChoiceTopKRouter"],
+    "torchtune_b200.rlhf": ["estimate_advantages", "get_rewards_ppo", "truncate_sequence_at_first_stop_token"],
+    "torchtune_b200.rlhf.loss": ["PPOLoss", "DPOLoss", "RSOLoss"],
+    "torchtune_b200.training": [
+        "FullModelHFCheckpointer", "FullModelMetaCheckpointer", "FullModelTorchTuneCheckpointer", "ModelType", "FormattedCheckpointFiles", "update_state_dict_for_classifier",
+        "get_dtype", "set_default_dtype", "validate_expected_param_dtype", "get_quantizer_mode", "init_distributed", "is_distributed", "gather_cpu_state_dict",
+        "get_distributed_backend", "apply_selective_activation_checkpointing", "set_activation_checkpointing", "OptimizerInBackwardWrapper", "create_optim_in_bwd_wrapper",
+        "register_optim_in_bwd_hooks", "get_cosine_schedule_with_warmup", "get_lr", "get_memory_stats", "log_memory_stats", "setup_torch_profiler",
+        "get_unmasked_sequence_lengths", "disable_dropout", "set_seed",
+    ],
+    "torchtune_b200.training.metric_logging": ["CometLogger", "WandBLogger", "TensorBoardLogger", "StdoutLogger", "DiskLogger", "MLFlowLogger"],
+    "torchtune_b200.utils": ["batch_to_device", "get_device", "get_logger", "torch_version_ge", "get_world_size_and_rank"],
+}
+
+MODEL_BUILDERS = {
+    "llama2": ["llama2_7b", "llama2_13b", "llama2_70b", "lora_llama2_7b", "qlora_llama2_7b", "llama2_tokenizer"],
+    "llama3": ["llama3_8b", "llama3_70b", "lora_llama3_8b", "qlora_llama3_8b", "llama3_tokenizer"],
+    "llama3_1": ["llama3_1_8b", "llama3_1_70b", "llama3_1_405b", "lora_llama3_1_8b", "qlora_llama3_1_8b"],
+    "llama3_2": ["llama3_2_1b", "llama3_2_3b", "lora_llama3_2_1b", "qlora_llama3_2_3b"],
+    "llama3_2_vision": ["llama3_2_vision_11b", "lora_llama3_2_vision_11b", "llama3_2_vision_transform"],
+    "llama3_3": ["llama3_3_70b", "lora_llama3_3_70b"],
+    "llama4": ["llama4_scout_17b_16e", "llama4_maverick_17b_128e", "lora_llama4_scout_17b_16e", "llama4_transform"],
+    "mistral": ["mistral_7b", "lora_mistral_7b", "qlora_mistral_7b", "mistral_tokenizer"],
+    "gemma": ["gemma_2b", "gemma_7b", "lora_gemma_2b", "gemma_tokenizer"],
+    "gemma2": ["gemma2_2b", "gemma2_9b", "gemma2_27b", "lora_gemma2_2b"],
+    "phi3": ["phi3_mini", "lora_phi3_mini", "phi3_mini_tokenizer"],
+    "phi4": ["phi4_14b", "lora_phi4_14b", "phi4_tokenizer"],
+    "qwen2": ["qwen2_0_5b", "qwen2_1_5b", "qwen2_7b", "lora_qwen2_7b", "qwen2_tokenizer"],
+    "qwen2_5": ["qwen2_5_0_5b", "qwen2_5_7b_instruct", "qwen2_5_72b_instruct", "lora_qwen2_5_7b_instruct", "qwen2_5_tokenizer"],
+    "qwen3": ["qwen3_0_6b_base", "qwen3_8b_instruct", "qwen3_32b", "lora_qwen3_8b_instruct", "qwen3_tokenizer"],
+    "clip": ["clip_vision_encoder", "clip_text_encoder", "CLIPImageTransform"],
+}
+
+
+@pytest.mark.parametrize("module", sorted(API))
+def test_documented_names_resolve(module):
+    mod = importlib.import_module(module)
+    missing = [n for n in API[module] if not hasattr(mod, n)]
+    assert not missing, f"{module} lacks {missing}"
+
+
+@pytest.mark.parametrize("family", sorted(MODEL_BUILDERS))
+def test_model_builders_resolve(family):
+    mod = importlib.import_module(f"torchtune_b200.models.{family}")
+    missing = [n for n in MODEL_BUILDERS[family] if not hasattr(mod, n)]
+    assert not missing, f"models.{family} lacks {missing}"

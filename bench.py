@@ -148,10 +148,19 @@ def run_ours(args) -> dict:
     parallel = par.DataParallelEngine(device=device)  # world 1: same flat store, no peers
     torch.manual_seed(1234)  # identical initial weights on every rank
     with training.set_default_dtype(torch.bfloat16), device:
-        model = llama3_1(**MODEL)
-        for p in model.parameters():
-            if p.dim() > 1:
+        if args.variant == "full":
+            model = llama3_1(**MODEL)
+        else:  # off-headline variants: LoRA r=64 / alpha=128 on q, k, v, output projections and the MLP; QLoRA adds an NF4 base
+            from torchtune_b200.models.llama3_1 import lora_llama3_1_8b
+            from torchtune_b200.modules.peft import get_adapter_params, set_trainable_params
+
+            model = lora_llama3_1_8b(lora_attn_modules=["q_proj", "k_proj", "v_proj", "output_proj"], apply_lora_to_mlp=True, lora_rank=64, lora_alpha=128,
+                                     quantize_base=args.variant == "qlora")
+        for name, p in model.named_parameters():
+            if p.dim() > 1 and p.is_floating_point() and "lora_b" not in name:
                 torch.nn.init.normal_(p, std=0.02)
+    if args.variant != "full":
+        set_trainable_params(model, get_adapter_params(model))
     if args.fp8:  # optional variant, never the default: decoder linears (not the output head) on the fp8 tensor cores
         training.convert_to_float8_training(model, "tensorwise")
     training.set_activation_checkpointing(model, {TransformerSelfAttentionLayer})
@@ -222,7 +231,7 @@ def run_ours(args) -> dict:
         "data": "synthetic uniform tokens, random-init weights",
         "impl": "ours",
         "config": {
-            "model": "llama3_1_8b",
+            "model": "llama3_1_8b" if args.variant == "full" else f"llama3_1_8b {args.variant} r64 (variant, not the headline)",
             "global_batch": BATCH_PER_GPU * world,
             "seq_len": SEQ_LEN,
             "doc_len": DOC_LEN,
@@ -254,6 +263,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--variant", choices=["full", "lora", "qlora"], default="full", help="off-headline variants; the headline is always the full fine-tune")
     ap.add_argument("--fp8", action="store_true", help="variant: fp8 decoder linears (the headline number is always bf16)")
     args = ap.parse_args()
     rank, world, _ = dist_env()

@@ -696,3 +696,20 @@ def test_gemm_weight_gather_fused_emulated_ranks(world, rows, K, M):
         remote[rank * rows : (rank + 1) * rows] = False
         assert torch.equal(gathered[remote].float(), w_full[remote])
     check_device_errors()
+
+
+# ----------------------------------------------------------------------------- two operand pairs, one accumulator (LoRA-fused GEMM)
+@pytest.mark.parametrize("M,N,K,K2", [(256, 320, 192, 64), (1000, 512, 1024, 8), (2048, 4096, 512, 96)])
+@pytest.mark.parametrize("b_mn", [False, True])
+def test_gemm_dual_matches_sum_of_products(M, N, K, K2, b_mn):
+    from torchtune_b200.ops._cuda import gemm_dual
+    from torchtune_b200.ops._lib import check_device_errors
+
+    a, a2 = _rand(M, K, scale=0.5, seed=1), _rand(M, K2, scale=0.5, seed=2)
+    b = _rand(K, N, scale=0.1, seed=3) if b_mn else _rand(N, K, scale=0.1, seed=3)
+    b2 = _rand(K2, N, scale=0.1, seed=4) if b_mn else _rand(N, K2, scale=0.1, seed=4)
+    bias = _rand(N, scale=0.2, seed=5)
+    got = gemm_dual(a, b, a2, b2, b_mn=b_mn, bias=bias)
+    check_device_errors()
+    want = (a.float() @ b.float() + a2.float() @ b2.float()) if b_mn else (a.float() @ b.float().t() + a2.float() @ b2.float().t())
+    _close(got, want + bias.float(), 2e-2, 2e-2, "gemm_dual")

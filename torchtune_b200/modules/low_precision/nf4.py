@@ -109,6 +109,7 @@ class _NF4Linear(torch.autograd.Function):
 
         dense = ctx.w.dequantize(grad_out.dtype)
         with torch.no_grad():
-            gx = ops.linear(grad_out, dense.t().contiguous())
+            g2 = grad_out.reshape(-1, grad_out.shape[-1])
+            gx = ops.matmul(g2 if g2.is_contiguous() else g2.contiguous(), dense).view(*grad_out.shape[:-1], dense.shape[1])  # dy · W, W read in place
         gb = grad_out.reshape(-1, grad_out.shape[-1]).sum(0) if ctx.needs_input_grad[2] else None
         return gx, None, gb

@@ -87,6 +87,10 @@ class LoRALinear(nn.Module):
         if not self._quantize_base and type(self)._base_forward is LoRALinear._base_forward:
             # dense base: one fused call (adapter product accumulated by the GEMM epilogue on CUDA)
             return ops.lora_linear(x, self.dropout(x), self.weight, self.bias, self.lora_a.weight, self.lora_b.weight, self.alpha / self.rank)
+        if self._quantize_base and type(self)._base_forward is LoRALinear._base_forward:
+            fused = ops.lora_linear_nf4(x, self.dropout(x), self.nf4, self.bias, self.lora_a.weight, self.lora_b.weight, self.alpha / self.rank)
+            if fused is not None:
+                return fused
         out = self._base_forward(x)
         a = ops.linear(self.dropout(x), self.lora_a.weight)
         return out + (self.alpha / self.rank) * ops.linear(a, self.lora_b.weight)

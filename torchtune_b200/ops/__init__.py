@@ -18,6 +18,7 @@ from .mask import AttentionMask
 __all__ = [
     "grouped_matmul",
     "lora_linear",
+    "lora_linear_nf4",
     "fp8_linear",
     "matmul",
     "linear",
@@ -88,6 +89,17 @@ def lora_linear(x: torch.Tensor, xd: torch.Tensor, weight: torch.Tensor, bias: O
 
         return _cuda.lora_linear(x, xd, weight, bias, lora_a, lora_b, scale)
     return F.linear(x, weight, bias) + scale * F.linear(F.linear(xd, lora_a), lora_b)
+
+
+def lora_linear_nf4(x: torch.Tensor, xd: torch.Tensor, nf4, bias: Optional[torch.Tensor], lora_a: torch.Tensor, lora_b: torch.Tensor, scale: float) -> Optional[torch.Tensor]:
+    """:func:`lora_linear` over an NF4 base weight (``nf4``: an object with ``dequantize(dtype)``); ``None`` when the inputs do not
+    qualify for the fused CUDA path."""
+    rank = lora_a.shape[0]
+    if _native(x) and lora_a.dtype == lora_b.dtype == torch.bfloat16 and rank % 8 == 0 and x.shape[-1] % 8 == 0 and lora_b.shape[0] % 8 == 0:
+        from . import _cuda
+
+        return _cuda.lora_linear_nf4(x, xd, nf4, bias, lora_a, lora_b, scale)
+    return None
 
 
 def grouped_matmul(x: torch.Tensor, w: torch.Tensor, counts: torch.Tensor) -> torch.Tensor:

@@ -66,6 +66,23 @@ def gemm(
     return out
 
 
+def gemm_dual(a: torch.Tensor, b: torch.Tensor, a2: torch.Tensor, b2: torch.Tensor, *, b_mn: bool = False, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``a · op(b) + a2 · op(b2) (+ bias)`` in one kernel and one accumulator (the second pair extends the main loop by
+    ``ceil(K2 / 64)`` k-blocks).  ``a``: ``[M, K]``, ``a2``: ``[M, K2]``; ``b``/``b2``: ``[N, K]``/``[N, K2]`` or, with ``b_mn``, ``[K, N]``/``[K2, N]``."""
+    def ok(t):
+        return t if (t.stride(1) == 1 and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0) else t.contiguous()
+
+    a, b, a2, b2 = ok(a), ok(b), ok(a2), ok(b2)
+    M, K = a.shape
+    K2 = a2.shape[1]
+    N = b.shape[1] if b_mn else b.shape[0]
+    out = torch.empty(M, N, dtype=_BF16, device=a.device)
+    rc = lib().ttb_gemm_bf16_dual(a.data_ptr(), b.data_ptr(), a2.data_ptr(), b2.data_ptr(), out.data_ptr(), M, N, K, K2, 0, int(b_mn), a.stride(0), b.stride(0),
+                                  a2.stride(0), b2.stride(0), out.stride(0), 0, 0, _ptr(bias), 1.0, err_word(a.device).data_ptr(), stream_ptr())
+    check(rc, f"gemm_dual M={M} N={N} K={K} K2={K2} b_mn={b_mn}")
+    return out
+
+
 class _Linear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias):
@@ -101,17 +118,16 @@ def nf4_dequantize(packed: torch.Tensor, scaler_q: torch.Tensor, scaler_factor: 
 
 
 class _LoRALinear(torch.autograd.Function):
-    """``y = x·Wᵀ (+ b) + s·(xd·Aᵀ)·Bᵀ`` with the adapter product accumulated into ``y`` by the GEMM epilogue (no separate
-    scale / add passes); backward mirrors it: ``dx = dy·W`` then ``dx += (s·dy·B)·A`` through the accumulate epilogue,
-    ``dA = dtᵀ·xd``, ``dB = s·dyᵀ·t``.  ``xd`` is the (possibly dropped-out) adapter input."""
+    """``y = x·Wᵀ (+ b) + s·(xd·Aᵀ)·Bᵀ``: the adapter product runs inside the base GEMM — its rank-r operands extend the main
+    loop by one k-block and share the accumulator, so ``y`` is written once and nothing is re-read.  Backward mirrors it:
+    ``dx = dy·W + (s·dy·B)·A`` in one kernel, ``dA = dtᵀ·xd``, ``dB = dyᵀ·(s·t)``.  ``xd`` is the (possibly dropped-out) adapter input."""
 
     @staticmethod
     def forward(ctx, x, xd, weight, bias, a, b, scale):
         shape = x.shape
         x2, xd2 = x.reshape(-1, shape[-1]), xd.reshape(-1, shape[-1])
-        y = gemm(x2, weight, bias=bias)
-        t = gemm(xd2, a)  # [T, r]
-        gemm(t, b, out=y, accumulate=True, alpha=float(scale))
+        t = gemm(xd2, a, alpha=float(scale))  # [T, r] = s·xd·Aᵀ
+        y = gemm_dual(x2, weight, t, b, bias=bias)  # base product and adapter product share one accumulator
         ctx.save_for_backward(x2, xd2, weight, a, b, t)
         ctx.scale, ctx.shape, ctx.has_bias = float(scale), shape, bias is not None
         ctx.same_input = xd.data_ptr() == x.data_ptr()
@@ -126,13 +142,15 @@ class _LoRALinear(torch.autograd.Function):
         s = ctx.scale
         dt = gemm(dy2, b, b_mn=True, alpha=s)  # [T, r] = s·dy·B
         dx = dxd = dw = db = da = dbm = None
-        if ctx.needs_input_grad[0] or (ctx.same_input and ctx.needs_input_grad[1]):
-            dx = gemm(dy2, weight, b_mn=True)
+        want_dx = ctx.needs_input_grad[0] or (ctx.same_input and ctx.needs_input_grad[1])
         if ctx.same_input:
-            if dx is not None:
-                gemm(dt, a, b_mn=True, out=dx, accumulate=True)
-        elif ctx.needs_input_grad[1]:
-            dxd = gemm(dt, a, b_mn=True).view(ctx.shape)
+            if want_dx:
+                dx = gemm_dual(dy2, weight, dt, a, b_mn=True)  # dy·W + dt·A in one accumulator
+        else:
+            if want_dx:
+                dx = gemm(dy2, weight, b_mn=True)
+            if ctx.needs_input_grad[1]:
+                dxd = gemm(dt, a, b_mn=True).view(ctx.shape)
         if ctx.needs_input_grad[2]:
             dw = _wgrad(weight, dy2, x2)
         if ctx.has_bias and ctx.needs_input_grad[3]:
@@ -140,12 +158,57 @@ class _LoRALinear(torch.autograd.Function):
         if ctx.needs_input_grad[4]:
             da = gemm(dt, xd2, a_mn=True, b_mn=True)  # [r, in]
         if ctx.needs_input_grad[5]:
-            dbm = gemm(dy2, t, a_mn=True, b_mn=True, alpha=s)  # [out, r]
+            dbm = gemm(dy2, t, a_mn=True, b_mn=True)  # [out, r]; t already carries the scale
         return (dx.view(ctx.shape) if dx is not None else None), dxd, dw, db, da, dbm, None
 
 
 def lora_linear(x, xd, weight, bias, a, b, scale):
     return _LoRALinear.apply(x, xd, weight, bias, a, b, scale)
+
+
+class _LoRANF4Linear(torch.autograd.Function):
+    """:class:`_LoRALinear` over a frozen NF4 base: the 4-bit weight is expanded to a bf16 scratch by the dequantisation kernel right
+    before each of the two GEMMs that read it (forward, input gradient) and never saved — only the codes stay resident."""
+
+    @staticmethod
+    def forward(ctx, x, xd, nf4, bias, a, b, scale):
+        shape = x.shape
+        x2, xd2 = x.reshape(-1, shape[-1]), xd.reshape(-1, shape[-1])
+        t = gemm(xd2, a, alpha=float(scale))  # [T, r] = s·xd·Aᵀ
+        y = gemm_dual(x2, nf4.dequantize(_BF16), t, b, bias=bias)
+        ctx.nf4, ctx.scale, ctx.shape, ctx.has_bias = nf4, float(scale), shape, bias is not None
+        ctx.same_input = xd.data_ptr() == x.data_ptr()
+        ctx.save_for_backward(xd2, a, b, t)
+        return y.view(*shape[:-1], b.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        xd2, a, b, t = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if dy2.stride(1) != 1 or dy2.stride(0) % 8:
+            dy2 = dy2.contiguous()
+        dt = gemm(dy2, b, b_mn=True, alpha=ctx.scale)  # [T, r] = s·dy·B
+        dx = dxd = db = da = dbm = None
+        want_dx = ctx.needs_input_grad[0] or (ctx.same_input and ctx.needs_input_grad[1])
+        if ctx.same_input:
+            if want_dx:
+                dx = gemm_dual(dy2, ctx.nf4.dequantize(_BF16), dt, a, b_mn=True)
+        else:
+            if want_dx:
+                dx = gemm(dy2, ctx.nf4.dequantize(_BF16), b_mn=True)
+            if ctx.needs_input_grad[1]:
+                dxd = gemm(dt, a, b_mn=True).view(ctx.shape)
+        if ctx.has_bias and ctx.needs_input_grad[3]:
+            db = dy2.sum(0)
+        if ctx.needs_input_grad[4]:
+            da = gemm(dt, xd2, a_mn=True, b_mn=True)
+        if ctx.needs_input_grad[5]:
+            dbm = gemm(dy2, t, a_mn=True, b_mn=True)
+        return (dx.view(ctx.shape) if dx is not None else None), dxd, None, db, da, dbm, None
+
+
+def lora_linear_nf4(x, xd, nf4, bias, a, b, scale):
+    return _LoRANF4Linear.apply(x, xd, nf4, bias, a, b, scale)
 
 
 def _grouped_gemm(x: torch.Tensor, w: torch.Tensor, counts: torch.Tensor, b_mn: bool) -> torch.Tensor:

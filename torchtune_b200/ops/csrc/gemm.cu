@@ -35,6 +35,8 @@ struct GemmParams {
   int out_fp32;    // 0: bf16 C, 1: fp32 C
   int accumulate;  // 1: C += result
   int* err;        // device error word (0 = ok)
+  int K2 = 0;         // plain kernel: extent of a second operand pair whose product is accumulated into the same tile
+                      // (C = A·op(B) + A2·op(B2), e.g. base weight + low-rank adapter); 0 = none
   int tma_store = 0;  // 1: bf16 output without accumulation leaves through shared memory + TMA stores (plain kernel)
 };
 
@@ -149,7 +151,8 @@ __device__ __forceinline__ void wg_coords(int t, int num_m, int num_n, const TpA
 
 template <int BN, bool A_MN, bool B_MN, int TP>
 __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUtensorMap* tmB_ptr, const GemmParams& p,
-                                          const TpArgs* tp, const GroupArgs* ga = nullptr, const CUtensorMap* tmC_ptr = nullptr) {
+                                          const TpArgs* tp, const GroupArgs* ga = nullptr, const CUtensorMap* tmC_ptr = nullptr,
+                                          const CUtensorMap* tmA2 = nullptr, const CUtensorMap* tmB2 = nullptr) {
   using Cfg = GemmCfg<BN>;
   const CUtensorMap& tmA = *tmA_ptr;
   const CUtensorMap& tmB = *tmB_ptr;
@@ -170,6 +173,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
   const int num_n = (p.N + BN - 1) / BN;
   const int num_tiles = TP == 4 ? ga->num_experts * num_m * num_n : num_m * num_n;
   const int num_kb = (p.K + BK - 1) / BK;
+  const int num_kb2 = TP == 0 ? (p.K2 + BK - 1) / BK : 0;  // k-blocks of the second operand pair (same accumulator)
   // TP 4: first row and row count of every expert, after the barrier region
   int* g_row0 = reinterpret_cast<int*>(smem + Cfg::kStages * Cfg::kStageBytes + 256);
   int* g_cnt = g_row0 + kMaxGroupedExperts;
@@ -265,7 +269,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
           asm volatile("fence.proxy.async;" ::: "memory");
         }
       }
-      for (int kb = 0; kb < kb_count; ++kb) {
+      for (int kb = 0; kb < kb_count + num_kb2; ++kb) {
         if (!mbar_wait(&empty[stage], phase ^ 1)) {
           *abort_flag = 1;
           if (lane == 0) atomicExch(p.err, 101);
@@ -275,13 +279,29 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
           uint8_t* sa = smem + stage * Cfg::kStageBytes;
           uint8_t* sb = sa + Cfg::kABytes;
           mbar_arrive_expect_tx(&full[stage], Cfg::kStageBytes);
-          if (A_MN) {
+          if (TP == 0 && kb >= kb_count) {  // second operand pair: same layouts, its own k index (out-of-range columns read as zero)
+            const int k2 = (kb - kb_count) * BK;
+            if (A_MN) {
+#pragma unroll
+              for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, tmA2, &full[stage], m_blk * BM + j * 64, k2);
+            } else {
+              tma_load_2d(sa, tmA2, &full[stage], k2, a_row);
+            }
+            if (B_MN) {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, tmB2, &full[stage], n_blk * BN + j * 64, k2);
+            } else {
+              tma_load_2d(sb, tmB2, &full[stage], k2, n_blk * BN);
+            }
+          } else if (A_MN) {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, &tmA, &full[stage], m_blk * BM + j * 64, k_row0 + kb * BK);
           } else {
             tma_load_2d(sa, mapA, &full[stage], kb * BK, a_row);
           }
-          if (TP == 3) {
+          if (TP == 0 && kb >= kb_count) {
+            // B of the second pair was issued above
+          } else if (TP == 3) {
             if (B_MN) {
 #pragma unroll
               for (int j = 0; j < BN / 64; ++j) tma_load_3d(sb + j * 8192, &tmB, &full[stage], n_blk * BN + j * 64, kb * BK, expert);
@@ -326,7 +346,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
         kb_count = (cnt + BK - 1) / BK;
         tail_rows = cnt % BK;  // valid rows of the last block (0: the block is full)
       }
-      for (int kb = 0; kb < kb_count; ++kb) {
+      for (int kb = 0; kb < kb_count + num_kb2; ++kb) {
         if (!mbar_wait(&full[stage], phase)) {
           ok = false;
           break;
@@ -630,8 +650,9 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ CUtensorMap tmC, GemmParams p) {
-  gemm_body<BN, A_MN, B_MN, 0>(&tmA, &tmB, p, nullptr, nullptr, &tmC);
+                 const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmA2,
+                 const __grid_constant__ CUtensorMap tmB2, GemmParams p) {
+  gemm_body<BN, A_MN, B_MN, 0>(&tmA, &tmB, p, nullptr, nullptr, &tmC, &tmA2, &tmB2);
 }
 
 template <int BN, bool B_MN, int TP>
@@ -708,12 +729,33 @@ static int launch_gemm_grouped(const void* A, const void* B, const GemmParams& p
   return cudaGetLastError() == cudaSuccess ? kOk : kErrDriver;
 }
 
+// Second operand pair of the plain kernel (same layouts as the first; K2 columns / rows): C = A·op(B) + A2·op(B2).
+struct SecondPair {
+  const void* A2 = nullptr;
+  const void* B2 = nullptr;
+  long long lda2 = 0, ldb2 = 0;
+};
+
 template <int BN, bool A_MN, bool B_MN>
 static int launch_gemm(const void* A, const void* B, const GemmParams& p, long long lda, long long ldb,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, const SecondPair& sp = SecondPair()) {
   using Cfg = GemmCfg<BN>;
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmB, tmA2, tmB2;
+  memset(&tmA2, 0, sizeof(tmA2));
+  memset(&tmB2, 0, sizeof(tmB2));
   int rc;
+  if (p.K2 > 0) {
+    if (A_MN)
+      rc = make_tmap_2d(&tmA2, sp.A2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.K2, p.M, sp.lda2, BK, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+    else
+      rc = make_tmap_2d(&tmA2, sp.A2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.M, p.K2, sp.lda2, BM, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != kOk) return rc;
+    if (B_MN)
+      rc = make_tmap_2d(&tmB2, sp.B2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.K2, p.N, sp.ldb2, BK, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+    else
+      rc = make_tmap_2d(&tmB2, sp.B2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.N, p.K2, sp.ldb2, BN, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != kOk) return rc;
+  }
   // K-major: tensor [rows, K], box [BM|BN rows, 64]; MN-major: tensor [K, rows], box [64 k-rows, 64].
   if (A_MN)
     rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.K, p.M, lda, BK, 64, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -753,7 +795,7 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p, long l
   const int num_tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   const int grid = num_tiles < sm_count() ? num_tiles : sm_count();
   TTB_COUNT_LAUNCH(1);
-  kern<<<grid, kThreads, smem_bytes, stream>>>(tmA, tmB, tmC, q);
+  kern<<<grid, kThreads, smem_bytes, stream>>>(tmA, tmB, tmC, tmA2, tmB2, q);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     fprintf(stderr, "[ttb] gemm launch failed: %s (M=%d N=%d K=%d grid=%d)\n", cudaGetErrorString(e), p.M, p.N, p.K, grid);
@@ -764,10 +806,10 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p, long l
 
 template <bool A_MN, bool B_MN>
 static int dispatch_bn(const void* A, const void* B, const GemmParams& p, long long lda, long long ldb,
-                       cudaStream_t stream) {
-  if (p.N > 128) return launch_gemm<256, A_MN, B_MN>(A, B, p, lda, ldb, stream);
-  if (p.N > 64) return launch_gemm<128, A_MN, B_MN>(A, B, p, lda, ldb, stream);
-  return launch_gemm<64, A_MN, B_MN>(A, B, p, lda, ldb, stream);
+                       cudaStream_t stream, const SecondPair& sp = SecondPair()) {
+  if (p.N > 128) return launch_gemm<256, A_MN, B_MN>(A, B, p, lda, ldb, stream, sp);
+  if (p.N > 64) return launch_gemm<128, A_MN, B_MN>(A, B, p, lda, ldb, stream, sp);
+  return launch_gemm<64, A_MN, B_MN>(A, B, p, lda, ldb, stream, sp);
 }
 
 template <int BN, bool B_MN, int TP>
@@ -1071,4 +1113,28 @@ extern "C" int ttb_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   if (!a_mn && b_mn) return dispatch_bn<false, true>(A, B, p, lda, ldb, s);
   if (a_mn && b_mn) return dispatch_bn<true, true>(A, B, p, lda, ldb, s);
   return dispatch_bn<true, false>(A, B, p, lda, ldb, s);
+}
+
+// C[M,N] (+)= alpha · (A·op(B) + A2·op(B2)) (+ bias): one kernel, one accumulator — the second pair's k-blocks (K2 columns, padded
+// to 64 with zeros by the tensor map) simply extend the main loop.  Used for LoRA: A2 = s·x·Aᵀ ([M, r]), B2 = lora_b ([N, r]) in
+// forward; A2 = s·dy·B ([M, r]), B2 = lora_a ([r, N], b_mn) in the input gradient (torchtune/modules/peft/lora.py:128-147).
+// Layout flags and alignment rules as for ttb_gemm_bf16; K2 and the second pair's leading dimensions are multiples of 8.
+extern "C" int ttb_gemm_bf16_dual(const void* A, const void* B, const void* A2, const void* B2, void* C, int M, int N, int K, int K2,
+                                  int a_mn, int b_mn, long long lda, long long ldb, long long lda2, long long ldb2, long long ldc,
+                                  int out_fp32, int accumulate, const void* bias, float alpha, int* err, void* stream) {
+  using namespace ttb;
+  if (M <= 0 || N <= 0 || K <= 0 || K2 <= 0 || A2 == nullptr || B2 == nullptr) return kErrBadShape;
+  if ((lda & 7) || (ldb & 7) || (lda2 & 7) || (ldb2 & 7) || (ldc & (out_fp32 ? 3 : 7)) || (N & 7) || (K2 & 7)) return kErrBadShape;
+  if ((a_mn ? (M & 7) : (K & 7)) || (b_mn ? (N & 7) : (K & 7))) return kErrBadShape;
+  GemmParams p;
+  p.M = M, p.N = N, p.K = K, p.K2 = K2, p.C = C, p.ldc = ldc;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.alpha = alpha, p.out_fp32 = out_fp32, p.accumulate = accumulate, p.err = err;
+  SecondPair sp;
+  sp.A2 = A2, sp.B2 = B2, sp.lda2 = lda2, sp.ldb2 = ldb2;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (!a_mn && !b_mn) return dispatch_bn<false, false>(A, B, p, lda, ldb, s, sp);
+  if (!a_mn && b_mn) return dispatch_bn<false, true>(A, B, p, lda, ldb, s, sp);
+  if (a_mn && b_mn) return dispatch_bn<true, true>(A, B, p, lda, ldb, s, sp);
+  return dispatch_bn<true, false>(A, B, p, lda, ldb, s, sp);
 }

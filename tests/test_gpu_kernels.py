@@ -713,3 +713,17 @@ def test_gemm_dual_matches_sum_of_products(M, N, K, K2, b_mn):
     check_device_errors()
     want = (a.float() @ b.float() + a2.float() @ b2.float()) if b_mn else (a.float() @ b.float().t() + a2.float() @ b2.float().t())
     _close(got, want + bias.float(), 2e-2, 2e-2, "gemm_dual")
+
+
+def test_nf4_quantize_kernels_match_reference():
+    from torchtune_b200.ops._cuda import nf4_quantize
+
+    w = _rand(256, 1024, scale=0.05, seed=3)
+    w[0, :64] = 0  # an all-zero block
+    got = nf4_quantize(w, 64, 256)
+    want = ref.nf4_quantize(w, 64, 256)
+    assert torch.equal(got[1], want[1]) and torch.allclose(got[2], want[2]) and torch.allclose(got[3], want[3])
+    mismatch = (got[0] != want[0]).float().mean().item()
+    assert mismatch < 1e-4, mismatch  # identical up to values that sit exactly on a midpoint after fp32 rounding
+    back = ref.nf4_dequantize(got[0], got[1], got[2], got[3], w.shape, 64, 256, torch.float32)
+    assert (back - w.float()).abs().max() < 0.2 * w.float().abs().max()

@@ -55,7 +55,15 @@ class NF4Weight(nn.Module):
     def quantize_(self, dense: torch.Tensor) -> None:
         if tuple(dense.shape) != self.shape:
             raise ValueError(f"expected weight of shape {self.shape}, got {tuple(dense.shape)}")
-        packed, sq, sf, mean = _ref.nf4_quantize(dense.to(self.weight_nf4.device), self.block_size, self.scaler_block_size)
+        dense = dense.to(self.weight_nf4.device)
+        packed = None
+        if dense.is_cuda and dense.dtype == torch.bfloat16 and self.block_size % 32 == 0:
+            from ...ops import _cuda, cuda_ops_enabled
+
+            if cuda_ops_enabled(dense):
+                packed, sq, sf, mean = _cuda.nf4_quantize(dense, self.block_size, self.scaler_block_size)
+        if packed is None:
+            packed, sq, sf, mean = _ref.nf4_quantize(dense, self.block_size, self.scaler_block_size)
         self.weight_nf4.copy_(packed)
         self.scaler_q.copy_(sq)
         self.scaler_factor.copy_(sf)

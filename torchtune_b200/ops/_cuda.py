@@ -109,6 +109,24 @@ class _Linear(torch.autograd.Function):
         return dx, dw, db
 
 
+def nf4_quantize(weight: torch.Tensor, block_size: int = 64, scaler_block_size: int = 256):
+    """bf16 CUDA weight → ``(packed uint8, scaler_q int8, scaler_factor fp32, scaler_mean fp32)`` with the same results as
+    :func:`reference.nf4_quantize`; the two passes over the weight are kernels, the coding of the per-block scales tensor ops."""
+    w = weight.detach().contiguous()
+    n = w.numel()
+    n_blocks = n // block_size
+    absmax = torch.empty(n_blocks, dtype=torch.float32, device=w.device)
+    check(lib().ttb_nf4_absmax(w.data_ptr(), absmax.data_ptr(), n, block_size, stream_ptr()), "nf4_absmax")
+    mean = absmax.mean()
+    centred = (absmax - mean).view(-1, scaler_block_size)
+    factor = 127.0 / centred.abs().amax(dim=1, keepdim=True).clamp_min(1e-30)
+    sq = torch.round(centred * factor).clamp(-128, 127).to(torch.int8)
+    scales = ((sq.float() / factor).view(-1) + mean).contiguous()
+    packed = torch.empty(n // 2, dtype=torch.uint8, device=w.device)
+    check(lib().ttb_nf4_encode(w.data_ptr(), scales.data_ptr(), packed.data_ptr(), n, block_size, stream_ptr()), "nf4_encode")
+    return packed, sq.view(-1), factor.view(-1).float(), mean.float()
+
+
 def nf4_dequantize(packed: torch.Tensor, scaler_q: torch.Tensor, scaler_factor: torch.Tensor, scaler_mean: torch.Tensor, shape, block_size: int, scaler_block_size: int) -> torch.Tensor:
     """NF4 codes + double-quantised scales → dense bf16 ``shape`` (one streaming kernel)."""
     out = torch.empty(shape, dtype=_BF16, device=packed.device)

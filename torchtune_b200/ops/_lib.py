@@ -62,6 +62,10 @@ def _declare(L: ctypes.CDLL) -> None:
     L.ttb_gemm_grouped_wgrad_bf16.restype = i32
     L.ttb_nf4_dequant.argtypes = [vp, vp, vp, vp, vp, i64, i32, i32, vp]
     L.ttb_nf4_dequant.restype = i32
+    L.ttb_nf4_absmax.argtypes = [vp, vp, i64, i32, vp]
+    L.ttb_nf4_encode.argtypes = [vp, vp, vp, i64, i32, vp]
+    L.ttb_nf4_absmax.restype = i32
+    L.ttb_nf4_encode.restype = i32
     L.ttb_moe_route_sort.argtypes = [vp, i32, i32, vp, vp, vp]
     L.ttb_moe_permute_indices.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp, vp]
     L.ttb_embedding_fwd.argtypes = [vp, vp, vp, i64, i32, i64, vp]

@@ -136,3 +136,77 @@ extern "C" int ttb_fp8_cast_transpose(const void* x, long long ldx, int R, int C
                                                           static_cast<uint8_t*>(out), static_cast<const float*>(s_col), s_col_stride, static_cast<uint8_t*>(out_t));
   return cudaGetLastError() == cudaSuccess ? kOk : kErrDriver;
 }
+
+// ----------------------------------------------------------------------------------------------- NF4 quantise
+// Two streaming kernels around a few tiny tensor ops on the per-block scales (mean-centring and int8 coding of the scales stay
+// in the framework layer): (1) absmax of every `block` weights, (2) nearest NF4 code of w / scale per weight, packed two per byte
+// (high nibble first).  Nearest code = number of codebook midpoints below the normalised value (ties go to the lower code, as an
+// argmin over |w - code| does).
+namespace ttb {
+
+__global__ void __launch_bounds__(256)
+nf4_absmax_kernel(const __nv_bfloat16* __restrict__ w, float* __restrict__ absmax, long long n_blocks, int block) {
+  // one warp per block of `block` weights (block is a multiple of 32)
+  const long long warp = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long n_warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long b = warp; b < n_blocks; b += n_warps) {
+    float m = 0.f;
+    for (int i = lane; i < block; i += 32) m = fmaxf(m, fabsf(__bfloat162float(w[b * block + i])));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) absmax[b] = m;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+nf4_encode_kernel(const __nv_bfloat16* __restrict__ w, const float* __restrict__ scales, uint8_t* __restrict__ packed, long long n_pairs,
+                  int block) {
+  __shared__ float mid[15];
+  if (threadIdx.x < 15) mid[threadIdx.x] = 0.5f * (kNF4[threadIdx.x] + kNF4[threadIdx.x + 1]);
+  __syncthreads();
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n_pairs;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long e = 2 * i;
+    const float sc = fmaxf(scales[e / block], 1e-30f);
+    uint32_t codes[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const float v = fminf(fmaxf(__bfloat162float(w[e + k]) / sc, -1.f), 1.f);
+      uint32_t c = 0;
+#pragma unroll
+      for (int j = 0; j < 15; ++j) c += v > mid[j] ? 1u : 0u;
+      codes[k] = c;
+    }
+    packed[i] = static_cast<uint8_t>((codes[0] << 4) | codes[1]);
+  }
+}
+
+}  // namespace ttb
+
+extern "C" int ttb_nf4_absmax(const void* w, void* absmax, long long n, int block, void* stream) {
+  using namespace ttb;
+  if (n <= 0 || block <= 0 || (block & 31) || (n % block)) return kErrBadShape;
+  const long long n_blocks = n / block;
+  long long blocks = (n_blocks * 32 + 255) / 256;
+  const long long cap = static_cast<long long>(sm_count()) * 16;
+  if (blocks > cap) blocks = cap;
+  TTB_COUNT_LAUNCH(1);
+  nf4_absmax_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(w), static_cast<float*>(absmax),
+                                                                                           n_blocks, block);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrDriver;
+}
+
+// scales: fp32 [n / block] — the *dequantised* per-block scales, so that the round trip is self-consistent.
+extern "C" int ttb_nf4_encode(const void* w, const void* scales, void* packed, long long n, int block, void* stream) {
+  using namespace ttb;
+  if (n <= 0 || (n & 1) || block <= 0 || (block & 1) || (n % block)) return kErrBadShape;
+  const long long n_pairs = n / 2;
+  long long blocks = (n_pairs + 255) / 256;
+  const long long cap = static_cast<long long>(sm_count()) * 16;
+  if (blocks > cap) blocks = cap;
+  TTB_COUNT_LAUNCH(1);
+  nf4_encode_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(w), static_cast<const float*>(scales),
+                                                                                           static_cast<uint8_t*>(packed), n_pairs, block);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrDriver;
+}

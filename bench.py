@@ -197,11 +197,15 @@ def run_ours(args) -> dict:
         ev, step.trace_events = step.trace_events, None
         per = len(ev) // args.steps
         names = ["fwd+loss", "bwd", "count", "optimizer"]
+        sums = [0.0] * (per - 1)
         for k in range(args.steps):
             seg = ev[k * per : (k + 1) * per]
             phases = [round(a.elapsed_time(b), 1) for a, b in zip(seg[:-1], seg[1:])]
+            sums = [x + y for x, y in zip(sums, phases)]
             if rank == 0 and sum(phases) > 1.15 * 1e3 * t_kernel / args.steps:
                 print(f"[trace] slow step {k}: {dict(zip(names, phases))}", file=sys.stderr, flush=True)
+        if rank == 0:
+            print(f"[trace] mean phase ms: {dict(zip(names, [round(x / args.steps, 1) for x in sums]))}", file=sys.stderr, flush=True)
     launches = L.ttb_launch_count() - launches0
 
     def e2e_step(i):

@@ -35,3 +35,40 @@ def test_expert_parallel_moe_two_gpus():
 def test_sharded_parameters_two_gpus():
     out = _torchrun(str(ROOT / "tests" / "multi_gpu_zero3_worker.py"), 2, 29575)
     assert "ZERO3_OK" in out
+
+
+def _tiny_ckpt(tmp_path):
+    sys.path.insert(0, str(ROOT / "tests"))
+    from helpers import write_tiny_hf_checkpoint
+
+    ckpt = tmp_path / "ckpt"
+    write_tiny_hf_checkpoint(ckpt)
+    return ckpt
+
+
+def _tune(args, port, timeout=600):
+    env = dict(os.environ, PYTHONPATH=f"{ROOT}:{ROOT / 'tests'}", MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, str(ROOT / "tune"), "run", "--nnodes=1", "--nproc_per_node=2", "--master-addr=127.0.0.1", f"--master-port={port}"] + args
+    res = subprocess.run(cmd, cwd=str(ROOT), env=env, capture_output=True, text=True, timeout=timeout)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+
+
+def _losses(path):
+    import re
+
+    return [float(m.group(1)) for m in re.finditer(r"loss:([0-9.eE+-]+)", path.read_text())]
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("name,port,extra", [("dp", 29581, []), ("tp", 29583, ["tensor_parallel_dim=2"]), ("cp", 29585, ["context_parallel_dim=2"]),
+                                             ("z3", 29587, ["shard_parameters=True", "shard_parameters_min_numel=1"])])
+def test_distributed_recipe_on_two_gpus(tmp_path, name, port, extra):
+    """The distributed full fine-tune recipe end to end in bf16 on two GPUs for every parallel mode; losses must be finite, fall
+    within the band of a randomly initialised 1024-token vocabulary and a checkpoint must be written."""
+    ckpt = _tiny_ckpt(tmp_path)
+    out = tmp_path / name
+    _tune(["full_finetune_distributed", "--config", "tiny/llama_full_distributed", f"checkpointer.checkpoint_dir={ckpt}", f"output_dir={out}", "metric_logger.filename=log.txt",
+           "device=cuda", "dtype=bf16", "max_steps_per_epoch=4", "dataset.num_samples=32", "optimizer.lr=1e-3"] + extra, port)
+    losses = _losses(out / "logs" / "log.txt")
+    assert len(losses) == 4 and all(l == l and 4.0 < l < 9.0 for l in losses), losses
+    assert (out / "epoch_0" / "model-00001-of-00001.safetensors").exists()

@@ -67,7 +67,7 @@ __global__ void dp_signal_kernel(FlagTable t, int world, int rank, int slot, int
 //         sums of squares into `sumsq_partials` (for global-norm clipping).
 // mode 2: AdamW + broadcast reading the already reduced `gsum`.
 template <int WORLD>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
 dp_reduce_adamw_bcast_kernel(PeerTable peers, int rank, long long begin, long long count, __nv_bfloat16* __restrict__ m,
                              __nv_bfloat16* __restrict__ v, float* __restrict__ gsum, float* __restrict__ sumsq_partials,
                              const float* __restrict__ scale_dev, float scale_host, float lr, float beta1, float beta2,

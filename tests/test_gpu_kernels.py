@@ -727,3 +727,17 @@ def test_nf4_quantize_kernels_match_reference():
     assert mismatch < 1e-4, mismatch  # identical up to values that sit exactly on a midpoint after fp32 rounding
     back = ref.nf4_dequantize(got[0], got[1], got[2], got[3], w.shape, 64, 256, torch.float32)
     assert (back - w.float()).abs().max() < 0.2 * w.float().abs().max()
+
+
+@pytest.mark.parametrize("M,N,K,a_mn,b_mn", [(64, 4096, 8192, True, True), (4096, 64, 8192, True, True), (128, 256, 4096 + 64, False, False), (200, 72, 1000, False, True)])
+def test_gemm_split_k_matches_fp32(M, N, K, a_mn, b_mn):
+    from torchtune_b200.ops._cuda import gemm_skinny
+    from torchtune_b200.ops._lib import check_device_errors
+
+    a = _rand(K, M, scale=0.3, seed=1) if a_mn else _rand(M, K, scale=0.3, seed=1)
+    b = _rand(K, N, scale=0.3, seed=2) if b_mn else _rand(N, K, scale=0.3, seed=2)
+    got = gemm_skinny(a, b, a_mn=a_mn, b_mn=b_mn, alpha=0.5)
+    check_device_errors()
+    af = a.float().t() if a_mn else a.float()
+    bf = b.float() if b_mn else b.float().t()
+    _close(got, 0.5 * (af @ bf), 2e-2, 2e-2 * (K ** 0.5) * 0.1, "split-k")

@@ -83,6 +83,27 @@ def gemm_dual(a: torch.Tensor, b: torch.Tensor, a2: torch.Tensor, b2: torch.Tens
     return out
 
 
+def gemm_skinny(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, alpha: float = 1.0) -> torch.Tensor:
+    """:func:`gemm` for outputs with so few tiles that most SMs would idle (adapter weight gradients ``[r, in]`` / ``[out, r]`` with
+    a long contraction): the contraction is split over enough CTAs to fill the GPU and the partial tiles are summed in fp32."""
+    def ok(t):
+        return t if (t.stride(1) == 1 and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0) else t.contiguous()
+
+    a, b = ok(a), ok(b)
+    M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
+    N = b.shape[1] if b_mn else b.shape[0]
+    bn = 256 if N > 128 else (128 if N > 64 else 64)
+    tiles = -(-M // 128) * -(-N // bn)
+    splits = min(64, 148 // tiles, -(-K // 256)) if tiles else 1
+    if splits <= 1:
+        return gemm(a, b, a_mn=a_mn, b_mn=b_mn, alpha=alpha)
+    out = torch.zeros(M, N, dtype=torch.float32, device=a.device)
+    rc = lib().ttb_gemm_bf16_splitk(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, int(a_mn), int(b_mn), a.stride(0), b.stride(0), out.stride(0), splits,
+                                    float(alpha), err_word(a.device).data_ptr(), stream_ptr())
+    check(rc, f"gemm_splitk M={M} N={N} K={K} splits={splits}")
+    return out.to(_BF16)
+
+
 class _Linear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias):
@@ -174,9 +195,9 @@ class _LoRALinear(torch.autograd.Function):
         if ctx.has_bias and ctx.needs_input_grad[3]:
             db = dy2.sum(0)
         if ctx.needs_input_grad[4]:
-            da = gemm(dt, xd2, a_mn=True, b_mn=True)  # [r, in]
+            da = gemm_skinny(dt, xd2, a_mn=True, b_mn=True)  # [r, in]: 16 tiles, contraction over all tokens
         if ctx.needs_input_grad[5]:
-            dbm = gemm(dy2, t, a_mn=True, b_mn=True)  # [out, r]; t already carries the scale
+            dbm = gemm_skinny(dy2, t, a_mn=True, b_mn=True)  # [out, r]; t already carries the scale
         return (dx.view(ctx.shape) if dx is not None else None), dxd, dw, db, da, dbm, None
 
 
@@ -219,9 +240,9 @@ class _LoRANF4Linear(torch.autograd.Function):
         if ctx.has_bias and ctx.needs_input_grad[3]:
             db = dy2.sum(0)
         if ctx.needs_input_grad[4]:
-            da = gemm(dt, xd2, a_mn=True, b_mn=True)
+            da = gemm_skinny(dt, xd2, a_mn=True, b_mn=True)
         if ctx.needs_input_grad[5]:
-            dbm = gemm(dy2, t, a_mn=True, b_mn=True)
+            dbm = gemm_skinny(dy2, t, a_mn=True, b_mn=True)
         return (dx.view(ctx.shape) if dx is not None else None), dxd, None, db, da, dbm, None
 
 

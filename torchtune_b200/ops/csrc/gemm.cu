@@ -37,6 +37,9 @@ struct GemmParams {
   int* err;        // device error word (0 = ok)
   int K2 = 0;         // plain kernel: extent of a second operand pair whose product is accumulated into the same tile
                       // (C = A·op(B) + A2·op(B2), e.g. base weight + low-rank adapter); 0 = none
+  int splits = 1;     // plain kernel, fp32 output: the contraction is cut into `splits` ranges, one tile per (m, n, range), partial
+                      // sums added with vector atomics into a zero-initialised (or accumulated-into) C — for skinny outputs
+                      // whose few tiles would otherwise leave most SMs idle (adapter weight gradients)
   int tma_store = 0;  // 1: bf16 output without accumulation leaves through shared memory + TMA stores (plain kernel)
 };
 
@@ -171,7 +174,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
   const int lane = threadIdx.x & 31;
   const int num_m = TP == 3 ? *ga->num_m_tiles : (p.M + BM - 1) / BM;
   const int num_n = (p.N + BN - 1) / BN;
-  const int num_tiles = TP == 4 ? ga->num_experts * num_m * num_n : num_m * num_n;
+  const int splits = TP == 0 ? p.splits : 1;
+  const int num_tiles = TP == 4 ? ga->num_experts * num_m * num_n : num_m * num_n * splits;
   const int num_kb = (p.K + BK - 1) / BK;
   const int num_kb2 = TP == 0 ? (p.K2 + BK - 1) / BK : 0;  // k-blocks of the second operand pair (same accumulator)
   // TP 4: first row and row count of every expert, after the barrier region
@@ -218,7 +222,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
     uint32_t phase = 0;
     for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x) {
       int m_blk, n_blk;
-      tile_coords(t, num_m, num_n, m_blk, n_blk);
+      const int split = TP == 0 ? t / (num_m * num_n) : 0;
+      tile_coords(TP == 0 ? t - split * (num_m * num_n) : t, num_m, num_n, m_blk, n_blk);
       m_blk = tp_rotate_m<TP>(m_blk, num_m, tp);
       const CUtensorMap* mapA = &tmA;
       int a_row = m_blk * BM;
@@ -249,6 +254,12 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
         n_blk = r / num_m;
         k_row0 = g_row0[expert];
         kb_count = (g_cnt[expert] + BK - 1) / BK;
+      }
+      if (TP == 0 && splits > 1) {  // this tile covers k-blocks [kb0, kb0 + kb_count) of the contraction
+        const int per = (num_kb + splits - 1) / splits;
+        const int kb0 = split * per;
+        kb_count = max(0, min(per, num_kb - kb0));
+        k_row0 = kb0 * BK;
       }
       const CUtensorMap* mapB = &tmB;
       int b_row = 0;
@@ -297,7 +308,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, &tmA, &full[stage], m_blk * BM + j * 64, k_row0 + kb * BK);
           } else {
-            tma_load_2d(sa, mapA, &full[stage], kb * BK, a_row);
+            tma_load_2d(sa, mapA, &full[stage], k_row0 + kb * BK, a_row);
           }
           if (TP == 0 && kb >= kb_count) {
             // B of the second pair was issued above
@@ -314,7 +325,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
           } else if (TP == 5) {
             tma_load_2d(sb, mapB, &full[stage], kb * BK, b_row);
           } else {
-            tma_load_2d(sb, &tmB, &full[stage], kb * BK, n_blk * BN);
+            tma_load_2d(sb, &tmB, &full[stage], k_row0 + kb * BK, n_blk * BN);
           }
         }
         __syncwarp();
@@ -341,6 +352,10 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
       const uint32_t d_tmem = tmem_base + acc * BN;
       bool ok = true;
       int kb_count = num_kb, tail_rows = 0;
+      if (TP == 0 && splits > 1) {
+        const int per = (num_kb + splits - 1) / splits;
+        kb_count = max(0, min(per, num_kb - (t / (num_m * num_n)) * per));
+      }
       if (TP == 4) {
         const int cnt = g_cnt[t / (num_m * num_n)];
         kb_count = (cnt + BK - 1) / BK;
@@ -405,12 +420,18 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
     int rs_buf = 0;  // TP 2: staging buffer toggle
     for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x) {
       int m_blk, n_blk;
-      tile_coords(t, num_m, num_n, m_blk, n_blk);
+      const int split = TP == 0 ? t / (num_m * num_n) : 0;
+      tile_coords(TP == 0 ? t - split * (num_m * num_n) : t, num_m, num_n, m_blk, n_blk);
       m_blk = tp_rotate_m<TP>(m_blk, num_m, tp);
       if (!mbar_wait(&tfull[acc], acc_phase)) {
         *abort_flag = 1;
         if (lane == 0) atomicExch(p.err, 104);
         break;
+      }
+      bool empty_split = false;  // a range past the end of the contraction: no MMA ran, the accumulator holds stale values
+      if (TP == 0 && splits > 1) {
+        const int per = (num_kb + splits - 1) / splits;
+        empty_split = num_kb - split * per <= 0;
       }
       tc_fence_after();
       if (TP == 5) wg_coords<BN>(t, num_m, num_n, tp, m_blk, n_blk);
@@ -500,13 +521,18 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
         if (row_ok && col0 < p.N) {
           float v[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = (TP == 4 && empty_expert) ? 0.f : __uint_as_float(r[i]) * p.alpha;
-          if (p.bias != nullptr) {
+          for (int i = 0; i < 32; ++i) v[i] = ((TP == 4 && empty_expert) || (TP == 0 && empty_split)) ? 0.f : __uint_as_float(r[i]) * p.alpha;
+          if (p.bias != nullptr && split == 0) {
 #pragma unroll
             for (int i = 0; i < 32; ++i)
               if (col0 + i < p.N) v[i] += __bfloat162float(__ldg(p.bias + col0 + i));
           }
-          if (p.out_fp32) {
+          if (TP == 0 && splits > 1) {
+            float* dst = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+#pragma unroll
+            for (int g = 0; g < 8; ++g)
+              if (col0 + g * 4 + 4 <= p.N) atomicAdd(reinterpret_cast<float4*>(dst + g * 4), make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]));
+          } else if (p.out_fp32) {
             float* dst = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
 #pragma unroll
             for (int g = 0; g < 8; ++g) {
@@ -792,7 +818,8 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p, long l
     }
     attr_set = true;
   }
-  const int num_tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  if (q.splits < 1 || (q.splits > 1 && (!q.out_fp32 || q.K2 > 0))) return kErrBadShape;
+  const int num_tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * q.splits;
   const int grid = num_tiles < sm_count() ? num_tiles : sm_count();
   TTB_COUNT_LAUNCH(1);
   kern<<<grid, kThreads, smem_bytes, stream>>>(tmA, tmB, tmC, tmA2, tmB2, q);
@@ -1137,4 +1164,22 @@ extern "C" int ttb_gemm_bf16_dual(const void* A, const void* B, const void* A2, 
   if (!a_mn && b_mn) return dispatch_bn<false, true>(A, B, p, lda, ldb, s, sp);
   if (a_mn && b_mn) return dispatch_bn<true, true>(A, B, p, lda, ldb, s, sp);
   return dispatch_bn<true, false>(A, B, p, lda, ldb, s, sp);
+}
+
+// Split-K form of ttb_gemm_bf16 for skinny outputs: fp32 C (zero-initialised by the caller, or holding a value to add to), the
+// contraction cut into `splits` ranges whose partial tiles are added with 16-byte float atomics.
+extern "C" int ttb_gemm_bf16_splitk(const void* A, const void* B, void* C, int M, int N, int K, int a_mn, int b_mn, long long lda,
+                                    long long ldb, long long ldc, int splits, float alpha, int* err, void* stream) {
+  using namespace ttb;
+  if (M <= 0 || N <= 0 || K <= 0 || splits < 1 || splits > 64) return kErrBadShape;
+  if ((lda & 7) || (ldb & 7) || (ldc & 3) || (N & 7)) return kErrBadShape;
+  if ((a_mn ? (M & 7) : (K & 7)) || (b_mn ? (N & 7) : (K & 7))) return kErrBadShape;
+  GemmParams p;
+  p.M = M, p.N = N, p.K = K, p.C = C, p.ldc = ldc;
+  p.bias = nullptr, p.alpha = alpha, p.out_fp32 = 1, p.accumulate = 0, p.err = err, p.splits = splits;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (!a_mn && !b_mn) return dispatch_bn<false, false>(A, B, p, lda, ldb, s);
+  if (!a_mn && b_mn) return dispatch_bn<false, true>(A, B, p, lda, ldb, s);
+  if (a_mn && b_mn) return dispatch_bn<true, true>(A, B, p, lda, ldb, s);
+  return dispatch_bn<true, false>(A, B, p, lda, ldb, s);
 }

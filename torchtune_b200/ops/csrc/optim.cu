@@ -60,6 +60,42 @@ adamw_kernel(const TensorMeta* __restrict__ metas, int n_tensors, long long tota
     const T* g = static_cast<const T*>(tm.g);
     T* m = static_cast<T*>(tm.m);
     T* v = static_cast<T*>(tm.v);
+    if (sizeof(T) == 2 && tm.master == nullptr && base + kChunk <= tm.numel &&
+        ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v)) & 15) == 0) {
+      // full chunk of 16-byte aligned bf16 tensors: 8 elements per thread and access (the chunk offset is a multiple of 8)
+      const float decay = 1.f - lr * weight_decay;
+#pragma unroll
+      for (int it = 0; it < kChunk / (256 * 8); ++it) {
+        const long long e = base + (it * 256 + threadIdx.x) * 8;
+        const uint4 gq = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(g) + e);
+        uint4 pq = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p) + e);
+        uint4 mq = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(m) + e);
+        uint4 vq = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(v) + e);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gq);
+        __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&pq);
+        __nv_bfloat162* m2 = reinterpret_cast<__nv_bfloat162*>(&mq);
+        __nv_bfloat162* v2 = reinterpret_cast<__nv_bfloat162*>(&vq);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 gf = __bfloat1622float2(g2[k]), pf = __bfloat1622float2(p2[k]), mf = __bfloat1622float2(m2[k]), vf = __bfloat1622float2(v2[k]);
+          float w[2] = {pf.x, pf.y}, m1[2], v1[2];
+          const float gr[2] = {gf.x * gs, gf.y * gs}, mo[2] = {mf.x, mf.y}, vo[2] = {vf.x, vf.y};
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            m1[q] = beta1 * mo[q] + (1.f - beta1) * gr[q];
+            v1[q] = beta2 * vo[q] + (1.f - beta2) * gr[q] * gr[q];
+            w[q] = w[q] * decay - lr * inv_bc1 * m1[q] / (sqrtf(v1[q]) * inv_sqrt_bc2 + eps);
+          }
+          p2[k] = __floats2bfloat162_rn(w[0], w[1]);
+          m2[k] = __floats2bfloat162_rn(m1[0], m1[1]);
+          v2[k] = __floats2bfloat162_rn(v1[0], v1[1]);
+        }
+        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p) + e) = pq;
+        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(m) + e) = mq;
+        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(v) + e) = vq;
+      }
+      continue;
+    }
 #pragma unroll 4
     for (int i = threadIdx.x; i < kChunk; i += 256) {
       const long long e = base + i;
@@ -89,6 +125,19 @@ sumsq_kernel(const TensorMeta* __restrict__ metas, int n_tensors, long long tota
     const TensorMeta tm = metas[ti];
     const long long base = (chunk - tm.chunk_start) * kChunk;
     const T* g = static_cast<const T*>(tm.g);
+    if (sizeof(T) == 2 && base + kChunk <= tm.numel && (reinterpret_cast<uintptr_t>(g) & 15) == 0) {
+#pragma unroll
+      for (int it = 0; it < kChunk / (256 * 8); ++it) {
+        const uint4 gq = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(g) + base + (it * 256 + threadIdx.x) * 8);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gq);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 f = __bfloat1622float2(g2[k]);
+          acc += f.x * f.x + f.y * f.y;
+        }
+      }
+      continue;
+    }
     for (int i = threadIdx.x; i < kChunk; i += 256) {
       const long long e = base + i;
       if (e < tm.numel) {

@@ -128,8 +128,8 @@ def bench_adamw(args, flush):
     n = args.numel
     p = torch.randn(n, device="cuda", dtype=torch.bfloat16)
     g = torch.randn(n, device="cuda", dtype=torch.bfloat16)
-    m = torch.zeros(n, device="cuda", dtype=torch.float32)
-    v = torch.zeros(n, device="cuda", dtype=torch.float32)
+    m = torch.zeros(n, device="cuda", dtype=torch.bfloat16)  # moments are kept in the parameter dtype
+    v = torch.zeros(n, device="cuda", dtype=torch.bfloat16)
     state = {"step": 0, "exp_avg": m, "exp_avg_sq": v}
 
     def run():
@@ -137,7 +137,7 @@ def bench_adamw(args, flush):
         adamw_multi([(p, g, state)], lr=1e-4, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01)
 
     t = _time(run, args.iters, args.warmup, flush)
-    nbytes = n * (2 + 2 + 2 + 4 * 4)  # p r/w, g r, m and v r/w
+    nbytes = n * (2 + 2 + 2 + 4 * 2)  # p r/w, g r, m and v r/w (all bf16)
     return {"op": "adamw", "numel": n, "ms": t, "gbs": nbytes / t / 1e6}
 
 

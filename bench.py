@@ -255,6 +255,92 @@ def run_ours(args) -> dict:
     return out if rank == 0 else {}
 
 
+def run_ours_tp(args) -> dict:
+    """Off-headline variant: the same model and batch shape with tensor + sequence parallelism over all ranks (every rank sees
+    the same 4 × 2048 batch; fused all-gather → GEMM and GEMM → reduce-scatter kernels in every layer)."""
+    import torch
+    import torch.distributed as dist
+
+    from torchtune_b200 import training
+    from torchtune_b200.models.llama3_1 import llama3_1
+    from torchtune_b200.modules import TransformerSelfAttentionLayer
+    from torchtune_b200.modules.loss import LinearCrossEntropyLoss
+    from torchtune_b200.ops._lib import check_device_errors, lib
+    from torchtune_b200.ops.mask import AttentionMask
+    from torchtune_b200.parallel.tp import TensorParallelContext
+    from torchtune_b200.parallel.tp_model import tensor_parallelize
+
+    rank, world, local = dist_env()
+    if world < 2:
+        return {"impl": "ours", "unavailable": "the tensor-parallel variant needs at least 2 GPUs"}
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=device)
+    torch.manual_seed(1234)
+    with training.set_default_dtype(torch.bfloat16), device:
+        model = llama3_1(**MODEL)
+        for p in model.parameters():
+            if p.dim() > 1:
+                torch.nn.init.normal_(p, std=0.02)
+    training.set_activation_checkpointing(model, {TransformerSelfAttentionLayer})
+    tp = TensorParallelContext(device, None, max_rows_per_rank=BATCH_PER_GPU * SEQ_LEN // world, max_width=MODEL["embed_dim"])
+    model = tensor_parallelize(model, tp, activation_checkpointing=True)
+    torch.cuda.empty_cache()
+    loss_fn = LinearCrossEntropyLoss(num_output_chunks=8)
+    loss_fn.set_model_output(model)
+    optimizer = torch.optim.AdamW([p for p in model.parameters() if p.requires_grad], lr=LR, fused=True)
+    batches = []
+    for i in range(4):
+        host = synthetic_batch(torch, BATCH_PER_GPU, seed=i)  # identical on every rank
+        dev = {k: v.to(device) for k, v in host.items()}
+        dev["mask"] = AttentionMask(causal=True, doc_ids=dev.pop("doc_ids"))
+        batches.append(dev)
+    done = []
+
+    def step(i):
+        if len(done) >= 2:
+            done.pop(0).synchronize()
+        batch = dict(batches[i % 4])
+        labels = model.shard_rows(batch.pop("labels"))
+        loss_sum, n_valid = loss_fn.compute_sum(model(**batch), labels)
+        loss_sum.backward()
+        n = n_valid.to(torch.float32)
+        dist.all_reduce(n)
+        model.sync_replicated_grads()
+        torch._foreach_mul_([p.grad for p in model.parameters() if p.grad is not None], (1.0 / n).to(torch.bfloat16))
+        optimizer.step()
+        optimizer.zero_grad(set_to_none=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        done.append(ev)
+
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    check_device_errors()
+    L = lib()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = L.ttb_launch_count()
+    t = timed_loop(torch, dist, world, step, args.steps)
+    launches = L.ttb_launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else {}
+    check_device_errors()
+    tokens = BATCH_PER_GPU * SEQ_LEN
+    out = {
+        "metric": "tokens_per_second", "value": tokens * args.steps / t, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * t / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic uniform tokens, random-init weights", "impl": "ours",
+        "config": {"model": "llama3_1_8b (tensor-parallel variant, not the headline)", "global_batch": BATCH_PER_GPU, "seq_len": SEQ_LEN, "doc_len": DOC_LEN,
+                   "parallelism": f"tp{world} + sequence parallel", "activation_checkpointing": True, "optimizer": "torch.optim.AdamW fused on the shards"},
+        "clocks": clocks, "gpu_launches": int(launches), "peak_mem_gib": round(torch.cuda.max_memory_allocated() / 2**30, 2),
+    }
+    tp.close()
+    dist.destroy_process_group()
+    return out if rank == 0 else {}
+
+
 def run_reference(args) -> dict:
     from baseline.reference_arm import run as run_ref
 
@@ -267,7 +353,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--variant", choices=["full", "lora", "qlora"], default="full", help="off-headline variants; the headline is always the full fine-tune")
+    ap.add_argument("--variant", choices=["full", "lora", "qlora", "tp"], default="full", help="off-headline variants; the headline is always the full fine-tune")
     ap.add_argument("--fp8", action="store_true", help="variant: fp8 decoder linears (the headline number is always bf16)")
     args = ap.parse_args()
     rank, world, _ = dist_env()
@@ -275,7 +361,10 @@ def main() -> None:
         # convenience: re-launch under torchrun when called directly with --gpus N
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}", "--master-addr", "127.0.0.1", "--master-port", "29511", __file__, *sys.argv[1:]]
         sys.exit(subprocess.call(cmd))
-    result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if args.impl == "reference":
+        result = run_reference(args)
+    else:
+        result = run_ours_tp(args) if args.variant == "tp" else run_ours(args)
     if rank == 0:
         print(json.dumps(result), flush=True)
 

@@ -413,7 +413,7 @@ def test_gemm_all_gather_fused_emulated_ranks(world, rows, K, N, b_mn):
         sync = torch.full((1 + world * rows // 128,), 7, dtype=torch.int32, device="cuda")  # the entry point zeroes it
         gather_own = rank % 2
         rc = L.ttb_gemm_ag_bf16(ptrs, w.data_ptr(), out.data_ptr(), gathered.data_ptr(), sync.data_ptr(), gather_own, world, rank, rows, N, K, int(b_mn),
-                                w.stride(0), N, bias.data_ptr(), err_word(out.device).data_ptr(), stream_ptr())
+                                w.stride(0), N, bias.data_ptr(), None, 0, 0, 0, err_word(out.device).data_ptr(), stream_ptr())
         assert rc == 0
         want = (full @ w.float() if b_mn else full @ w.float().t()) + bias.float()
         _close(out, want, 2e-2, 2e-2, f"ag_gemm rank {rank}")
@@ -446,7 +446,7 @@ def test_gemm_reduce_scatter_fused_emulated_ranks(world, rows, K, N, b_mn):
         residual = _rand(rows, N, scale=0.3, seed=90 + owner)
         bias = _rand(N, scale=0.1, seed=95 + owner)
         out = torch.empty(rows, N, dtype=torch.bfloat16, device="cuda")
-        rc = L.ttb_rs_reduce(staging[owner].data_ptr(), residual.data_ptr(), bias.data_ptr(), out.data_ptr(), world, rows, N, N, N, N, stream_ptr())
+        rc = L.ttb_rs_reduce(staging[owner].data_ptr(), residual.data_ptr(), bias.data_ptr(), out.data_ptr(), world, rows, N, N, N, N, None, 0, 0, 0, owner, None, stream_ptr())
         assert rc == 0
         want = total[owner * rows : (owner + 1) * rows] + residual.float() + bias.float()
         _close(out, want, 3e-2, 3e-2 * max(1, world // 2), f"gemm_rs owner {owner}")

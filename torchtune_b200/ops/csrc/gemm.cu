@@ -74,7 +74,22 @@ struct alignas(64) TpArgs {
   CUtensorMap tmC;                  // TP 1 / 5: the local output [M, N], box 64 × 32 (TMA-store epilogue)
   void* C[kMaxTpWorld];             // TP 2: per-rank staging buffer [world, rows_per_rank, ldc]
   int world, rank, rows_per_rank, gather_own;
+  // Optional cross-rank readiness flags (written by ttb_dp_signal on the peers): entry [src * flag_stride + flag_slot] of the local
+  // array reaches `flag_epoch` once rank src has placed its shard (TP 1).  nullptr: the caller ordered the ranks itself.
+  const int* flags;
+  int flag_stride, flag_slot, flag_epoch;
 };
+
+__device__ __forceinline__ bool wait_flag_sys(const int* f, int epoch) {
+  const long long t0 = clock64();
+  unsigned spins = 0;
+  while (true) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+    if (v >= epoch) return true;
+    if ((++spins & 0xff) == 0 && clock64() - t0 > kWaitBudgetCycles) return false;
+  }
+}
 
 __device__ __forceinline__ bool wait_count(const int* ctr, int target) {
   auto load = [&]() {
@@ -647,6 +662,16 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmA_ptr, const CUte
       const int m_blk = tp_rotate_m<1>(i, num_m, tp);
       const long long row0 = static_cast<long long>(m_blk) * BM + (pc % kCopyPieces) * (BM / kCopyPieces);
       const int src = static_cast<int>(row0 / tp->rows_per_rank);
+      if (tp->flags != nullptr && src != tp->rank) {  // the peer's shard must be in place before it is read
+        if (ctid == 0) *piece_slot = wait_flag_sys(tp->flags + src * tp->flag_stride + tp->flag_slot, tp->flag_epoch) ? 1 : 0;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int ok = *piece_slot;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (!ok) {
+          if (ctid == 0) atomicExch(p.err, 107);
+          break;
+        }
+      }
       const uint4* s = reinterpret_cast<const uint4*>(tp->A_src[src]) + (row0 - static_cast<long long>(src) * tp->rows_per_rank) * row_vecs;
       uint4* d = reinterpret_cast<uint4*>(tp->gathered) + row0 * row_vecs;
       for (long long v = ctid; v < piece_vecs; v += 128 * 8) {  // 8 × 16 bytes in flight per thread: NVLink latency needs ≈ 2.5 MB per GPU
@@ -892,7 +917,19 @@ static int dispatch_tp(const TpArgs& tp, const void* A, const void* B, const Gem
 __global__ void __launch_bounds__(256)
 rs_reduce_kernel(const __nv_bfloat16* __restrict__ staging, const __nv_bfloat16* __restrict__ residual,
                  const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ out, int world, long long rows, int N,
-                 long long ld_stage, long long ld_res, long long ld_out) {
+                 long long ld_stage, long long ld_res, long long ld_out, const int* __restrict__ flags, int flag_stride, int flag_slot,
+                 int flag_epoch, int rank, int* __restrict__ err) {
+  if (flags != nullptr) {  // every peer's partial tiles must have landed in this rank's staging slots
+    __shared__ int give_up;
+    if (threadIdx.x == 0) give_up = 0;
+    __syncthreads();
+    if (threadIdx.x < world && threadIdx.x != rank && !wait_flag_sys(flags + threadIdx.x * flag_stride + flag_slot, flag_epoch)) {
+      give_up = 1;
+      atomicExch(err, 108);
+    }
+    __syncthreads();
+    if (give_up) return;
+  }
   const int vec_per_row = N / 8;
   const long long total = rows * vec_per_row;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
@@ -941,7 +978,8 @@ rs_reduce_kernel(const __nv_bfloat16* __restrict__ staging, const __nv_bfloat16*
 // rows_per_rank must be a multiple of 128 (one m-tile never spans two ranks).
 extern "C" int ttb_gemm_ag_bf16(const void* const* A_ranks, const void* B, void* C, void* gathered, int* sync, int gather_own,
                                 int world, int rank, int rows_per_rank, int N, int K, int b_mn, long long ldb, long long ldc,
-                                const void* bias, int* err, void* stream) {
+                                const void* bias, const int* flags, int flag_stride, int flag_slot, int flag_epoch, int* err,
+                                void* stream) {
   using namespace ttb;
   if (world < 1 || world > kMaxTpWorld || rank < 0 || rank >= world) return kErrBadShape;
   if (rows_per_rank <= 0 || (rows_per_rank % BM) || N <= 0 || K <= 0) return kErrBadShape;
@@ -951,6 +989,7 @@ extern "C" int ttb_gemm_ag_bf16(const void* const* A_ranks, const void* B, void*
   memset(&tp, 0, sizeof(tp));
   tp.world = world, tp.rank = rank, tp.rows_per_rank = rows_per_rank, tp.gather_own = gather_own;
   tp.gathered = gathered, tp.sync = sync;
+  tp.flags = flags, tp.flag_stride = flag_stride, tp.flag_slot = flag_slot, tp.flag_epoch = flag_epoch;
   for (int r = 0; r < world; ++r) {
     if (reinterpret_cast<uintptr_t>(A_ranks[r]) & 15) return kErrBadShape;
     tp.A_src[r] = A_ranks[r];
@@ -1023,7 +1062,8 @@ extern "C" int ttb_gemm_rs_bf16(const void* A, const void* B, void* const* C_ran
 }
 
 extern "C" int ttb_rs_reduce(const void* staging, const void* residual, const void* bias, void* out, int world, long long rows,
-                             int N, long long ld_stage, long long ld_res, long long ld_out, void* stream) {
+                             int N, long long ld_stage, long long ld_res, long long ld_out, const int* flags, int flag_stride,
+                             int flag_slot, int flag_epoch, int rank, int* err, void* stream) {
   using namespace ttb;
   if (world < 1 || rows <= 0 || N <= 0 || (N & 7) || (ld_stage & 7) || (ld_out & 7) || (residual && (ld_res & 7))) return kErrBadShape;
   const long long total = rows * (N / 8);
@@ -1033,7 +1073,7 @@ extern "C" int ttb_rs_reduce(const void* staging, const void* residual, const vo
   TTB_COUNT_LAUNCH(1);
   rs_reduce_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(staging), static_cast<const __nv_bfloat16*>(residual), static_cast<const __nv_bfloat16*>(bias),
-      static_cast<__nv_bfloat16*>(out), world, rows, N, ld_stage, ld_res, ld_out);
+      static_cast<__nv_bfloat16*>(out), world, rows, N, ld_stage, ld_res, ld_out, flags, flag_stride, flag_slot, flag_epoch, rank, err);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrDriver;
 }
 

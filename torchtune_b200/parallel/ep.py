@@ -319,6 +319,12 @@ def expert_parallelize(model: nn.Module, ep: ExpertParallelContext) -> nn.Module
         grads = [p.grad for p in model._replicated if p.grad is not None]
         if not grads or ep.world == 1:
             return
+        big = [g for g in grads if g.numel() >= (1 << 20) and g.is_cuda and g.is_contiguous()]
+        for g in big:  # large tensors are reduced in place; the many small ones share one flat fp32 buffer
+            dist.all_reduce(g, group=ep.group)
+        grads = [g for g in grads if not any(g is b for b in big)]
+        if not grads:
+            return
         flat = torch.cat([g.reshape(-1).float() for g in grads])
         dist.all_reduce(flat, group=ep.group)
         off = 0

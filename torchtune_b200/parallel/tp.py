@@ -12,9 +12,11 @@ kernels (``ttb_gemm_ag_bf16`` / ``ttb_gemm_rs_bf16`` in ``ops/csrc/gemm.cu``):
   output tile into a staging slot on the rank that owns those rows; the owner sums its ``world`` slots in fp32
   and adds the residual in the same pass.
 
-Ordering between ranks is a stream-ordered barrier (a 4-byte all-reduce) per operation; shard and staging
-buffers are double-buffered so one barrier per operation is enough (a buffer is rewritten only after the
-*next* operation's barrier, which every rank enters after its reads of the previous one have completed).
+Ordering between ranks uses readiness flags in peer memory instead of collectives: a one-warp kernel stores the
+operation's epoch into every peer's flag array once this rank's shard (or its partial output tiles) is in place,
+and the consuming kernel waits for the flags it needs with a cycle budget.  Shard and staging buffers are
+double-buffered: a buffer is rewritten two operations later, and finishing the operation in between required
+every peer's flag for it, which a peer stores only after its kernel that read the older buffer has completed.
 
 Without CUDA (gloo) the same functions run on ``all_gather`` / ``reduce_scatter`` so the host-side logic is
 testable on CPU.
@@ -37,9 +39,12 @@ def _declare(L) -> None:
         return
     vp, i32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
     pvp = ctypes.POINTER(vp)
-    L.ttb_gemm_ag_bf16.argtypes = [pvp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i64, i64, vp, vp, vp]
+    L.ttb_gemm_ag_bf16.argtypes = [pvp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i64, i64, vp, vp, i32, i32, i32, vp, vp]
     L.ttb_gemm_rs_bf16.argtypes = [vp, vp, pvp, i32, i32, i32, i32, i32, i32, i64, i64, i64, vp, vp]
-    L.ttb_rs_reduce.argtypes = [vp, vp, vp, vp, i32, i64, i32, i64, i64, i64, vp]
+    L.ttb_rs_reduce.argtypes = [vp, vp, vp, vp, i32, i64, i32, i64, i64, i64, vp, i32, i32, i32, i32, vp, vp]
+    L.ttb_dp_signal.argtypes = [pvp, i32, i32, i32, i32, vp]
+    L.ttb_dp_signal.restype = i32
+    L.ttb_dp_max_buckets.restype = i32
     for fn in (L.ttb_gemm_ag_bf16, L.ttb_gemm_rs_bf16, L.ttb_rs_reduce):
         fn.restype = i32
     L._tp_declared = True
@@ -70,6 +75,11 @@ class TensorParallelContext:
             shard_bytes = self.max_rows * self.max_width * 2
             self._gather = [PeerBuffer(shard_bytes, device, group) for _ in range(2)]
             self._stage = [PeerBuffer(self.world * shard_bytes, device, group) for _ in range(2)]
+            # readiness flags instead of collective barriers: slot 0/1 = gather buffers, 2/3 = staging buffers; a rank stores the
+            # operation's epoch into every peer's array once its part is in place, consumers wait inside their kernels (bounded)
+            self._flag_stride = lib().ttb_dp_max_buckets()
+            self._flags = PeerBuffer(self.world * self._flag_stride * 4, device, group)
+            self._epochs = [0, 0, 0, 0]
 
     # ------------------------------------------------------------------ plumbing
     def barrier(self) -> None:
@@ -80,8 +90,18 @@ class TensorParallelContext:
         if self.cuda:
             torch.cuda.synchronize(self.device)
             self.barrier()
-            for b in self._gather + self._stage:
+            for b in self._gather + self._stage + [self._flags]:
                 b.close()
+
+    def _signal(self, slot: int) -> int:
+        """Tell every peer that this rank's part of the operation using flag ``slot`` is in place (stream-ordered); returns the epoch
+        the consumers wait for."""
+        from ..ops._lib import check, lib, stream_ptr
+
+        self._epochs[slot] += 1
+        if self.world > 1:
+            check(lib().ttb_dp_signal(self._flags.pointer_array(), self.world, self.rank, slot, self._epochs[slot], stream_ptr()), "tp_signal")
+        return self._epochs[slot]
 
     def _check(self, rows: int, width: int) -> None:
         if rows > self.max_rows or width > self.max_width:
@@ -106,10 +126,11 @@ class TensorParallelContext:
         from ..ops._lib import check, err_word, lib, stream_ptr
 
         self._check(rows, k)
-        buf = self._gather[self._flip_g]
+        slot = self._flip_g
+        buf = self._gather[slot]
         self._flip_g ^= 1
         buf.tensor(_BF16, rows * k).view(rows, k).copy_(x_shard)
-        self.barrier()  # every rank's shard is in place
+        epoch = self._signal(slot)  # the copier warps of every peer wait for this flag before they read the shard
         out = torch.empty(self.world * rows, n, dtype=_BF16, device=self.device)
         gathered = torch.empty(self.world * rows, k, dtype=_BF16, device=self.device)
         sync = torch.empty(1 + self.world * rows // 128, dtype=torch.int32, device=self.device)
@@ -117,7 +138,8 @@ class TensorParallelContext:
         check(
             lib().ttb_gemm_ag_bf16(buf.pointer_array(), w.data_ptr(), out.data_ptr(), gathered.data_ptr(), sync.data_ptr(), int(return_gathered),
                                    self.world, self.rank, rows, n, k, int(b_mn), w.stride(0), n,
-                                   None if bias is None else bias.data_ptr(), err_word(self.device).data_ptr(), stream_ptr()),
+                                   None if bias is None else bias.data_ptr(), self._flags.local_ptr if self.world > 1 else None, self._flag_stride, slot, epoch,
+                                   err_word(self.device).data_ptr(), stream_ptr()),
             "gemm_ag",
         )
         return (out, gathered) if return_gathered else out
@@ -137,18 +159,20 @@ class TensorParallelContext:
         from ..ops._lib import check, err_word, lib, stream_ptr
 
         self._check(rows, n)
+        slot = 2 + self._flip_s
         buf = self._stage[self._flip_s]
         self._flip_s ^= 1
         xc = x if x.is_contiguous() else x.contiguous()
         w = weight if weight.is_contiguous() else weight.contiguous()
         L = lib()
         check(L.ttb_gemm_rs_bf16(xc.data_ptr(), w.data_ptr(), buf.pointer_array(), self.world, self.rank, rows, n, k, int(b_mn), k, w.stride(0), n, err_word(self.device).data_ptr(), stream_ptr()), "gemm_rs")
-        self.barrier()  # all partial tiles have landed in every owner's staging buffer
+        epoch = self._signal(slot)  # this rank's partial tiles have landed everywhere; the owner's sum waits for all peers' flags
         out = torch.empty(rows, n, dtype=_BF16, device=self.device)
         res = None if residual is None else (residual if residual.is_contiguous() else residual.contiguous())
         check(
             L.ttb_rs_reduce(buf.local_ptr, None if res is None else res.data_ptr(), None if bias is None else bias.data_ptr(), out.data_ptr(), self.world, rows, n, n,
-                            0 if res is None else res.stride(0), n, stream_ptr()),
+                            0 if res is None else res.stride(0), n, self._flags.local_ptr if self.world > 1 else None, self._flag_stride, slot, epoch, self.rank,
+                            err_word(self.device).data_ptr(), stream_ptr()),
             "rs_reduce",
         )
         return out

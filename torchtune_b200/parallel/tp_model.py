@@ -330,10 +330,20 @@ class TPDecoder(nn.Module):
         grads = [p.grad for p in self._replicated if p.grad is not None]
         if not grads or self.tp.world == 1:
             return
-        flat = torch.cat([g.reshape(-1).float() for g in grads])
+        # large tensors (embedding, output projection) are reduced in place; only the many small ones (norm scales) share a flat
+        # fp32 buffer — concatenating everything would stage gigabytes per step
+        small = []
+        for g in grads:
+            if g.numel() >= (1 << 20) and g.is_cuda and g.is_contiguous():
+                self.tp.all_reduce_(g)
+            else:
+                small.append(g)
+        if not small:
+            return
+        flat = torch.cat([g.reshape(-1).float() for g in small])
         self.tp.all_reduce_(flat)
         off = 0
-        for g in grads:
+        for g in small:
             g.copy_(flat[off : off + g.numel()].view_as(g))
             off += g.numel()
 

@@ -207,23 +207,31 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       tc_fence_after();
       const bool need_mask = (kv0 + kBlk - 1 > (p.causal ? q0 : p.s - 1)) || (kv0 < lo_last) || (kv0 + kBlk > p.s);
-      // pass 1: row maximum
-      float mx = -INFINITY;
-#pragma unroll 1
+      // The whole score row (128 fp32) is read from TMEM once — four loads issued back to back, one wait — and stays in
+      // registers for both the maximum and the exponentials.
+      uint32_t sv[4][32];
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) tmem_ld_32x32(tS[st] + lane_sel + ch * 32, sv[ch]);
+      tmem_ld_wait();
+      // S buffer free for the scores of block it+2 (its values now live in registers)
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_free[st]);
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four independent chains instead of one of length 128
+#pragma unroll
       for (int ch = 0; ch < 4; ++ch) {
-        uint32_t v[32];
-        tmem_ld_32x32(tS[st] + lane_sel + ch * 32, v);
-        tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float x = __uint_as_float(v[i]) * c;
+          float x = __uint_as_float(sv[ch][i]) * c;
           if (need_mask) {
             const int j = kv0 + ch * 32 + i;
             if (j < lo_row || j > hi_row || j >= p.s) x = -INFINITY;
           }
-          mx = fmaxf(mx, x);
+          sv[ch][i] = __float_as_uint(x);
+          mx4[i & 3] = fmaxf(mx4[i & 3], x);
         }
       }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       float alpha = 1.f;
       const float m_new = fmaxf(m_used, mx);
       bool rescale = false;
@@ -235,6 +243,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
       }
       const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
+      // exponentials and their running sum (four chains) are computed before the wait below, so only the stores into the
+      // single P buffer have to follow the previous P·V
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float e = fast_exp2(__uint_as_float(sv[ch][i]) - m_safe);
+          sum4[i & 3] += e;
+          sv[ch][i] = __float_as_uint(e);
+        }
+      }
+      const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       // P may only be overwritten (and O rescaled) once the previous P·V has retired
       if (it > 0) {
         if (!mbar_wait(pv_done, (it - 1) & 1)) {
@@ -243,39 +264,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         tc_fence_after();
       }
-      // pass 2: probabilities -> bf16 -> swizzled smem, running sum
-      float sum = 0.f;
-#pragma unroll 1
-      for (int ch = 0; ch < 4; ++ch) {
-        uint32_t v[32];
-        tmem_ld_32x32(tS[st] + lane_sel + ch * 32, v);
-        tmem_ld_wait();
-        float pr[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float x = __uint_as_float(v[i]) * c;
-          if (need_mask) {
-            const int j = kv0 + ch * 32 + i;
-            if (j < lo_row || j > hi_row || j >= p.s) x = -INFINITY;
-          }
-          pr[i] = fast_exp2(x - m_safe);
-          sum += pr[i];
-        }
+      for (int ch = 0; ch < 4; ++ch) {
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           uint4 u;
-          u.x = pack_bf16x2(pr[g * 8 + 0], pr[g * 8 + 1]);
-          u.y = pack_bf16x2(pr[g * 8 + 2], pr[g * 8 + 3]);
-          u.z = pack_bf16x2(pr[g * 8 + 4], pr[g * 8 + 5]);
-          u.w = pack_bf16x2(pr[g * 8 + 6], pr[g * 8 + 7]);
+          u.x = pack_bf16x2(__uint_as_float(sv[ch][g * 8 + 0]), __uint_as_float(sv[ch][g * 8 + 1]));
+          u.y = pack_bf16x2(__uint_as_float(sv[ch][g * 8 + 2]), __uint_as_float(sv[ch][g * 8 + 3]));
+          u.z = pack_bf16x2(__uint_as_float(sv[ch][g * 8 + 4]), __uint_as_float(sv[ch][g * 8 + 5]));
+          u.w = pack_bf16x2(__uint_as_float(sv[ch][g * 8 + 6]), __uint_as_float(sv[ch][g * 8 + 7]));
           *reinterpret_cast<uint4*>(sP + swz_offset(r, ch * 32 + g * 8)) = u;
         }
       }
       l = l * alpha + sum;
-      // S buffer free for the scores of block it+2
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_free[st]);
       // lazy correction of the running output
       if (it > 0 && __any_sync(0xffffffffu, rescale)) {
 #pragma unroll 1

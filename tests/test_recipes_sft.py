@@ -108,6 +108,30 @@ def test_full_distributed_tensor_parallel_matches_single_process(tmp_path, tune_
 
 
 @pytest.mark.timeout(900)
+def test_full_distributed_dp_times_tp_matches_single_process(tmp_path, tune_path, monkeypatch):
+    """A 2 × 2 mesh on four gloo ranks (tensor_parallel_dim=2, two model replicas with per-replica batch 2) trains like one
+    process with batch 4: shard gradients are summed over the replicas, replicated ones over all ranks."""
+    ckpt = tmp_path / "ckpt"
+    write_tiny_hf_checkpoint(ckpt)
+    common = f"checkpointer.checkpoint_dir={ckpt} metric_logger.filename=log.txt max_steps_per_epoch=3 dataset.num_samples=16 clip_grad_norm=1.0"
+    run_tune(tune_path, f"run full_finetune_single_device --config tiny/llama_full_single_device {common} output_dir={tmp_path / 'single'} batch_size=4", monkeypatch)
+    single = read_losses(tmp_path / "single" / "logs" / "log.txt")
+    _tune_subprocess(
+        ["run", "--nnodes=1", "--nproc_per_node=4", "--master-addr=127.0.0.1", "--master-port=29541", "full_finetune_distributed", "--config", "tiny/llama_full_distributed"]
+        + common.split()
+        + [f"output_dir={tmp_path / 'mesh'}", "tensor_parallel_dim=2", "batch_size=2"]
+    )
+    mesh_losses = read_losses(tmp_path / "mesh" / "logs" / "log.txt")
+    assert len(mesh_losses) == 3
+    torch.testing.assert_close(torch.tensor(mesh_losses), torch.tensor(single), rtol=2e-4, atol=2e-4)
+    a = load_file(str(tmp_path / "single" / "epoch_0" / "model-00001-of-00001.safetensors"))
+    b = load_file(str(tmp_path / "mesh" / "epoch_0" / "model-00001-of-00001.safetensors"))
+    assert set(a) == set(b)
+    for k in a:
+        torch.testing.assert_close(a[k], b[k], rtol=1e-3, atol=2e-5)
+
+
+@pytest.mark.timeout(900)
 def test_full_distributed_context_parallel_matches_single_process(tmp_path, tune_path, monkeypatch):
     """context_parallel_dim=2 on two gloo ranks: both ranks read the same batch, each owns half of every sequence."""
     ckpt = tmp_path / "ckpt"
@@ -160,6 +184,37 @@ def test_full_distributed_expert_parallel_matches_data_parallel(tmp_path):
         assert set(a) == set(b)
         for k in a:
             torch.testing.assert_close(a[k], b[k], rtol=1e-3, atol=2e-5)
+
+
+@pytest.mark.timeout(900)
+def test_full_distributed_dp_times_ep_matches_data_parallel(tmp_path):
+    """Four gloo ranks as two expert-parallel groups of two (expert_parallel_dim=2): expert gradients are summed over the two
+    ranks that own the same experts, dense gradients over all four; the run must match plain data parallelism on four ranks."""
+    from torchtune_b200.models.llama4 import llama4_decoder
+
+    ckpt = tmp_path / "ckpt"
+    ckpt.mkdir()
+    torch.manual_seed(0)
+    model = llama4_decoder(vocab_size=1024, num_layers=2, num_heads=4, num_kv_heads=2, embed_dim=128, hidden_dim=256, max_seq_len=256, num_experts=4, experts_per_token=2, rope_base=500000)
+    with torch.no_grad():
+        for prm in model.parameters():
+            prm.copy_(torch.randn_like(prm) * 0.05)
+    torch.save(model.state_dict(), ckpt / "model.pt")
+    common = [f"checkpointer.checkpoint_dir={ckpt}", "metric_logger.filename=log.txt", "max_steps_per_epoch=2", "dataset.num_samples=32", "clip_grad_norm=1.0", "optimizer.lr=1e-3"]
+    losses = {}
+    for name, port, extra in (("dp", 29542, []), ("mesh", 29543, ["expert_parallel_dim=2"])):
+        _tune_subprocess(
+            ["run", "--nnodes=1", "--nproc_per_node=4", "--master-addr=127.0.0.1", f"--master-port={port}", "full_finetune_distributed", "--config", "tiny/llama4_moe_full_distributed"]
+            + common + [f"output_dir={tmp_path / name}"] + extra
+        )
+        losses[name] = read_losses(tmp_path / name / "logs" / "log.txt")
+    assert len(losses["mesh"]) == 2
+    torch.testing.assert_close(torch.tensor(losses["mesh"]), torch.tensor(losses["dp"]), rtol=2e-4, atol=2e-4)
+    a = torch.load(tmp_path / "dp" / "epoch_0" / "model-00001-of-00001.bin", weights_only=True)
+    b = torch.load(tmp_path / "mesh" / "epoch_0" / "model-00001-of-00001.bin", weights_only=True)
+    assert set(a) == set(b)
+    for k in a:
+        torch.testing.assert_close(a[k], b[k], rtol=1e-3, atol=2e-5)
 
 
 @pytest.mark.timeout(900)

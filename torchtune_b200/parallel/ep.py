@@ -297,10 +297,13 @@ class ExpertParallelMoE(nn.Module):
 
 
 # ------------------------------------------------------------------------------------------- model level
-def expert_parallelize(model: nn.Module, ep: ExpertParallelContext) -> nn.Module:
+def expert_parallelize(model: nn.Module, ep: ExpertParallelContext, replica_group=None, replicas: int = 1) -> nn.Module:
     """Replace every :class:`MoE` layer of ``model`` by :class:`ExpertParallelMoE` (in place) and attach the small surface the
     sharded-model optimizer needs: ``_replicated`` (parameters every rank holds), ``sync_replicated_grads()`` and
-    ``full_state_dict()`` (checkpoint layout with all experts; collective)."""
+    ``full_state_dict()`` (checkpoint layout with all experts; collective).
+
+    When the expert-parallel group is smaller than the job (``replicas`` expert-parallel groups side by side), ``replica_group``
+    holds the ranks that own the *same* experts: expert gradients are summed over it, dense gradients over every rank."""
     from ..modules.moe import MoE
 
     def swap(parent: nn.Module) -> None:
@@ -315,22 +318,28 @@ def expert_parallelize(model: nn.Module, ep: ExpertParallelContext) -> nn.Module
     model._replicated = [p for p in model.parameters() if id(p) not in expert_params]
     model._ep = ep
 
-    def sync_replicated_grads() -> None:
-        grads = [p.grad for p in model._replicated if p.grad is not None]
-        if not grads or ep.world == 1:
-            return
+    def _sum(grads, group) -> None:
         big = [g for g in grads if g.numel() >= (1 << 20) and g.is_cuda and g.is_contiguous()]
         for g in big:  # large tensors are reduced in place; the many small ones share one flat fp32 buffer
-            dist.all_reduce(g, group=ep.group)
+            dist.all_reduce(g, group=group)
         grads = [g for g in grads if not any(g is b for b in big)]
         if not grads:
             return
         flat = torch.cat([g.reshape(-1).float() for g in grads])
-        dist.all_reduce(flat, group=ep.group)
+        dist.all_reduce(flat, group=group)
         off = 0
         for g in grads:
             g.copy_(flat[off : off + g.numel()].view_as(g))
             off += g.numel()
+
+    def sync_replicated_grads() -> None:
+        if ep.world * replicas == 1:
+            return
+        # every rank trains on its own batch: dense parameters sum over the whole job (the default group when there are
+        # several expert-parallel groups), experts over the ranks that hold the same ones
+        _sum([p.grad for p in model._replicated if p.grad is not None], ep.group if replicas == 1 else None)
+        if replicas > 1:
+            _sum([p.grad for p in model.parameters() if id(p) in expert_params and p.grad is not None], replica_group)
 
     def full_state_dict() -> Dict[str, torch.Tensor]:
         out: Dict[str, torch.Tensor] = {}

@@ -103,16 +103,29 @@ class TensorParallelOptimizer:
         """Optimizer state of *this rank's shard*; resuming requires the same tensor-parallel size."""
         return {"tp_rank_states": self._gather_states()} if is_rank_zero else (self._gather_states() and {})
 
+    def _shard_group(self):
+        """(group, size, rank) over which the model is split: the tensor- or expert-parallel group (under a dp × tp or dp × ep
+        mesh the replicas hold identical shards and optimizer state), every rank otherwise."""
+        ctx = self.strategy.tp if self.strategy.tp is not None else self.strategy.ep
+        if ctx is not None:
+            return ctx.group, ctx.world, ctx.rank
+        return None, self.strategy.world, self.strategy.rank
+
     def _gather_states(self):
-        states = [None] * self.strategy.world
-        dist.all_gather_object(states, self.optimizer.state_dict())
+        group, world, _ = self._shard_group()
+        states = [None] * world
+        if world > 1:
+            dist.all_gather_object(states, self.optimizer.state_dict(), group=group)
+        else:
+            states[0] = self.optimizer.state_dict()
         return states
 
     def load_full_state_dict(self, sd) -> None:
+        _, world, rank = self._shard_group()
         states = sd.get("tp_rank_states")
-        if states is None or len(states) != self.strategy.world:
+        if states is None or len(states) != world:
             raise ValueError("optimizer checkpoint was written with a different tensor-parallel size")
-        self.optimizer.load_state_dict(states[self.strategy.rank])
+        self.optimizer.load_state_dict(states[rank])
 
     def step(self, grad_scale=1.0, max_grad_norm: Optional[float] = None, group=None) -> None:
         model = self.model
@@ -126,8 +139,9 @@ class TensorParallelOptimizer:
             replicated = {id(p) for p in model._replicated}
             sharded_sq = sum((p.grad.float().pow(2).sum() for p in params if id(p) not in replicated), torch.zeros((), device=params[0].device))
             repl_sq = sum((p.grad.float().pow(2).sum() for p in params if id(p) in replicated), torch.zeros((), device=params[0].device))
-            if self.strategy.world > 1:
-                dist.all_reduce(sharded_sq)
+            group, world, _ = self._shard_group()
+            if world > 1:
+                dist.all_reduce(sharded_sq, group=group)
             norm = (sharded_sq + repl_sq).sqrt()
             self.last_grad_norm = norm
             coef = torch.clamp(float(max_grad_norm) / (norm + 1e-6), max=1.0)
@@ -170,12 +184,10 @@ class ParallelStrategy(DataParallelEngine):
             world_size=world,
         )
         self.ep_dim = int(get("expert_parallel_dim", 1) or 1)
-        if self.ep_dim > 1 and (self.ep_dim != world or self.dims.tp_enabled):
-            raise NotImplementedError("expert_parallel_dim > 1 currently requires expert_parallel_dim == world size and no tensor parallelism")
+        if self.ep_dim > 1 and (world % self.ep_dim or self.dims.tp_enabled):
+            raise NotImplementedError("expert_parallel_dim > 1 must divide the world size and does not combine with tensor parallelism (use expert tensor parallelism: tensor_parallel_dim on an MoE model)")
         if self.dims.cp_enabled and (self.dims.tp_enabled or self.ep_dim > 1):
             raise NotImplementedError("context_parallel_dim > 1 combines with data parallelism only (not with tensor or expert parallelism)")
-        if self.dims.tp_enabled and self.dims.dp_size > 1:
-            raise NotImplementedError("tensor_parallel_dim > 1 currently requires data_parallel_shard_dim = data_parallel_replicate_dim = 1 (tp == world size)")
         super().__init__(device=device, group=None)
         self.tp = None  # TensorParallelContext, created in shard_model
         self.ep = None  # ExpertParallelContext, created in shard_model
@@ -199,15 +211,12 @@ class ParallelStrategy(DataParallelEngine):
     # data-parallel coordinates: with tensor parallelism every rank reads the same batch ------------
     @property
     def dp_size(self) -> int:  # type: ignore[override]
-        if self.dims.tp_enabled:
-            return 1
-        return self.world // self.dims.cp  # the ranks of one context-parallel group read the same batch
+        # the ranks of one tensor- or context-parallel group (consecutive ranks) read the same batch
+        return self.world // (self.dims.tp * self.dims.cp)
 
     @property
     def dp_rank(self) -> int:  # type: ignore[override]
-        if self.dims.tp_enabled:
-            return 0
-        return self.rank // self.dims.cp
+        return self.rank // (self.dims.tp * self.dims.cp)
 
     def _attach_context_parallel(self, model: nn.Module) -> None:
         """Context-parallel groups are runs of ``cp`` consecutive ranks; for parameters they are data-parallel ranks (every
@@ -245,9 +254,17 @@ class ParallelStrategy(DataParallelEngine):
 
         core = model
         width = core.tok_embeddings.embedding_dim
-        self.tp = TensorParallelContext(self.device, None, max_rows_per_rank=self._tp_max_rows(cfg, core), max_width=width)
+        tp_group = dp_group = None
+        if self.dims.tp != self.world:
+            # dp × tp mesh, tensor-parallel ranks consecutive (they share NVLink peer buffers); the replicas of one shard
+            # (same tensor-parallel rank) form the data-parallel group that sums its gradients
+            groups = self.dims.build_groups(("dp", "tp"))
+            tp_group, dp_group = groups["tp"], groups["dp"]
+        self.tp = TensorParallelContext(self.device, tp_group, max_rows_per_rank=self._tp_max_rows(cfg, core), max_width=width)
         ac = any(isinstance(layer, CheckpointedLayer) for layer in core.layers)
-        return tensor_parallelize(core, self.tp, activation_checkpointing=ac)
+        out = tensor_parallelize(core, self.tp, activation_checkpointing=ac)
+        out.set_data_parallel_group(dp_group, self.world // self.dims.tp)
+        return out
 
     def _shard_model_ep(self, model: nn.Module, cfg) -> nn.Module:
         """Experts spread over the ranks (every rank keeps its own batch: expert parallel ranks are data parallel for the
@@ -261,9 +278,24 @@ class ParallelStrategy(DataParallelEngine):
         get = cfg.get if hasattr(cfg, "get") else (lambda k, d=None: d)
         router = moes[0].router
         tokens = self._tp_max_rows(cfg, model) * max(self.dims.tp, 1)
-        self.ep = ExpertParallelContext(self.device, None, num_experts=router.num_experts, dim=router.dim, max_pairs=tokens * router.experts_per_token,
+        ep, replicas = self.ep_dim, self.world // self.ep_dim
+        ep_group = replica_group = None
+        if replicas > 1:
+            # several expert-parallel groups of consecutive ranks; the ranks with the same position in their group own the same
+            # experts.  Every rank creates every group, in the same order.
+            for g in range(replicas):
+                ranks = list(range(g * ep, (g + 1) * ep))
+                handle = dist.new_group(ranks)
+                if self.rank in ranks:
+                    ep_group = handle
+            for j in range(ep):
+                ranks = list(range(j, self.world, ep))
+                handle = dist.new_group(ranks)
+                if self.rank in ranks:
+                    replica_group = handle
+        self.ep = ExpertParallelContext(self.device, ep_group, num_experts=router.num_experts, dim=router.dim, max_pairs=tokens * router.experts_per_token,
                                         capacity_factor=get("expert_capacity_factor"))
-        return expert_parallelize(model, self.ep)
+        return expert_parallelize(model, self.ep, replica_group, replicas)
 
     # model -------------------------------------------------------------------------------
     def shard_model(self, model: nn.Module, cfg, base_sd: Dict[str, Any], adapter_sd: Optional[Dict[str, Any]] = None, *, dtype: torch.dtype = torch.bfloat16, strict: bool = True) -> nn.Module:

@@ -20,6 +20,7 @@ from __future__ import annotations
 from typing import Any, Dict, List, Optional
 
 import torch
+import torch.distributed as dist
 from torch import nn
 
 from .. import ops
@@ -277,6 +278,12 @@ class TPDecoder(nn.Module):
                 self._replicated += layer.mlp.replicated_parameters()
         seen = set()
         self._replicated = [p for p in self._replicated if not (id(p) in seen or seen.add(id(p)))]
+        self._dp_group, self._dp_world = None, 1
+
+    def set_data_parallel_group(self, group, size: int) -> None:
+        """Under a dp × tp mesh: the process group of the ranks that hold the *same* shard (one per model replica) and its
+        size.  Their gradients are summed in :meth:`sync_replicated_grads`."""
+        self._dp_group, self._dp_world = group, int(size)
 
     def shard_rows(self, t: torch.Tensor) -> torch.Tensor:
         """``[b, s, …]`` → this rank's ``[1, b·s / tp, …]`` rows of the flattened token dimension."""
@@ -325,27 +332,41 @@ class TPDecoder(nn.Module):
             h = h + self.tp.all_reduce_(layer.mlp.forward_replicated(layer.mlp_norm(h)))
         return self.output(self.norm(h)).float()
 
-    def sync_replicated_grads(self) -> None:
-        """Sum the gradients of replicated parameters over the group (one collective on a flat buffer)."""
-        grads = [p.grad for p in self._replicated if p.grad is not None]
-        if not grads or self.tp.world == 1:
-            return
-        # large tensors (embedding, output projection) are reduced in place; only the many small ones (norm scales) share a flat
-        # fp32 buffer — concatenating everything would stage gigabytes per step
+    def _sum_grads(self, grads, reduce_) -> None:
+        # large tensors (embedding, output projection, projection shards) are reduced in place; only the many small ones (norm
+        # scales) share a flat fp32 buffer — concatenating everything would stage gigabytes per step
         small = []
         for g in grads:
             if g.numel() >= (1 << 20) and g.is_cuda and g.is_contiguous():
-                self.tp.all_reduce_(g)
+                reduce_(g)
             else:
                 small.append(g)
         if not small:
             return
         flat = torch.cat([g.reshape(-1).float() for g in small])
-        self.tp.all_reduce_(flat)
+        reduce_(flat)
         off = 0
         for g in small:
             g.copy_(flat[off : off + g.numel()].view_as(g))
             off += g.numel()
+
+    def sync_replicated_grads(self) -> None:
+        """Sum the gradients of replicated parameters over the tensor-parallel group, then — under a dp × tp mesh — every
+        gradient over the model replicas."""
+        if self.tp.world > 1:
+            self._sum_grads([p.grad for p in self._replicated if p.grad is not None], self.tp.all_reduce_)
+        if self._dp_world > 1:
+            group = self._dp_group
+
+            def over_replicas(t: torch.Tensor) -> None:
+                if t.device.type == "cpu" and t.dtype == torch.bfloat16:
+                    f = t.float()
+                    dist.all_reduce(f, group=group)
+                    t.copy_(f)
+                else:
+                    dist.all_reduce(t, group=group)
+
+            self._sum_grads([p.grad for p in self.parameters() if p.grad is not None], over_replicas)
 
     def full_state_dict(self) -> Dict[str, torch.Tensor]:
         """Checkpoint-layout state dict (every rank takes part in the gathers; all get the result)."""

@@ -132,6 +132,22 @@ def test_full_distributed_dp_times_tp_matches_single_process(tmp_path, tune_path
 
 
 @pytest.mark.timeout(900)
+def test_full_distributed_fp8_tensor_parallel_runs(tmp_path):
+    """enable_fp8_training with tensor_parallel_dim=2: the sharded projections run with fp8 operands (tensorwise scales)."""
+    import math
+
+    ckpt = tmp_path / "ckpt"
+    write_tiny_hf_checkpoint(ckpt)
+    _tune_subprocess(
+        ["run", "--nnodes=1", "--nproc_per_node=2", "--master-addr=127.0.0.1", "--master-port=29544", "full_finetune_distributed", "--config", "tiny/llama_full_distributed",
+         f"checkpointer.checkpoint_dir={ckpt}", "metric_logger.filename=log.txt", "epochs=3", "max_steps_per_epoch=1", "dataset.num_samples=2", "batch_size=2", f"output_dir={tmp_path / 'out'}",
+         "tensor_parallel_dim=2", "enable_fp8_training=True", "fp8_recipe_name=tensorwise", "optimizer.lr=1e-3"]
+    )
+    losses = read_losses(tmp_path / "out" / "logs" / "log.txt")
+    assert len(losses) == 3 and all(math.isfinite(x) for x in losses) and losses[-1] < losses[0]
+
+
+@pytest.mark.timeout(900)
 def test_full_distributed_context_parallel_matches_single_process(tmp_path, tune_path, monkeypatch):
     """context_parallel_dim=2 on two gloo ranks: both ranks read the same batch, each owns half of every sequence."""
     ckpt = tmp_path / "ckpt"

@@ -162,3 +162,61 @@ def test_tp_moe_decoder_matches_single_process():
         assert set(r["sd"]) == set(sd), set(r["sd"]) ^ set(sd)
         for key in sd:
             assert torch.equal(r["sd"][key], sd[key]), key
+
+
+# ----------------------------------------------------------------------------- fp8 training under tensor parallelism
+def _fp8_model():
+    from torchtune_b200.training.quantization import convert_to_float8_training
+
+    model = llama3_1(**ARCH)
+    fixed_init_(model, std=0.1)
+    return convert_to_float8_training(model, "tensorwise")
+
+
+def _fp8_worker(rank, world, port, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        tp = TensorParallelContext(torch.device("cpu"), max_rows_per_rank=8, max_width=48)
+        tpm = tensor_parallelize(_fp8_model(), tp)
+        assert all(layer.attn.fp8 and layer.mlp.fp8 for layer in tpm.layers)
+        tokens, labels = _data()
+        loss = F.cross_entropy(tpm(tokens).reshape(-1, 64), tpm.shard_rows(labels).reshape(-1), ignore_index=-100, reduction="sum")
+        loss.backward()
+        tpm.sync_replicated_grads()
+        total = loss.detach().clone()
+        dist.all_reduce(total)
+        l0 = tpm.layers[0]
+        results[rank] = dict(loss=total.item(), w13_grad=l0.mlp.w13.grad.clone(), wo_grad=l0.attn.wo.grad.clone(), emb_grad=tpm.tok_embeddings.weight.grad.clone())
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tp_fp8_decoder_tracks_single_process_fp8():
+    """Float8 linears under tensor parallelism: every rank scales its own weight shard, so the numbers differ from the
+    single-process fp8 model only by quantisation noise; a rowwise recipe is refused."""
+    import pytest
+
+    world = 2
+    results = mp.Manager().dict()
+    mp.spawn(_fp8_worker, args=(world, 29563, results), nprocs=world, join=True)
+    model = _fp8_model()
+    tokens, labels = _data()
+    loss = F.cross_entropy(model(tokens).reshape(-1, 64), labels.reshape(-1), ignore_index=-100, reduction="sum")
+    loss.backward()
+    grads = {k: p.grad for k, p in model.named_parameters()}
+    cos = lambda a, b: F.cosine_similarity(a.reshape(1, -1), b.reshape(1, -1)).item()
+    for rank in range(world):
+        r = results[rank]
+        assert abs(r["loss"] - loss.item()) < 2e-2 * abs(loss.item())
+        w1 = grads["layers.0.mlp.w1.weight"][rank * 24 : (rank + 1) * 24]
+        w3 = grads["layers.0.mlp.w3.weight"][rank * 24 : (rank + 1) * 24]
+        assert cos(r["w13_grad"], torch.cat([w1, w3])) > 0.98
+        assert cos(r["wo_grad"], grads["layers.0.attn.output_proj.weight"][:, rank * 16 : (rank + 1) * 16]) > 0.98
+        assert cos(r["emb_grad"], grads["tok_embeddings.weight"]) > 0.98
+
+    from torchtune_b200.training.quantization import convert_to_float8_training
+
+    rowwise = convert_to_float8_training(llama3_1(**ARCH), "rowwise")
+    with pytest.raises(ValueError, match="tensorwise"):
+        tensor_parallelize(rowwise, TensorParallelContext(torch.device("cpu"), max_rows_per_rank=8, max_width=48))

@@ -34,15 +34,51 @@ def _rows(t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
     return t[rank * n : (rank + 1) * n]
 
 
+def _wants_fp8(projs, what: str) -> bool:
+    """``True`` when every projection is an fp8-training linear (tensorwise scaling: the only recipe that combines with tensor
+    parallelism, as in the reference, torchtune/training/quantization.py:277), ``False`` when all are plain linears."""
+    kinds = {type(p).__name__ for p in projs}
+    if any(p is None or p.bias is not None for p in projs) or not kinds <= {"Linear", "Float8Linear"}:
+        raise NotImplementedError(f"tensor parallelism supports bias-free, un-adapted {what}")
+    if kinds == {"Linear"}:
+        return False
+    if kinds != {"Float8Linear"}:
+        raise NotImplementedError(f"tensor parallelism needs all {what} in the same precision")
+    if any(getattr(p, "recipe", "tensorwise") != "tensorwise" for p in projs):
+        raise ValueError("fp8 training with tensor parallelism supports only tensorwise scaling")
+    return True
+
+
+def _fp8_matmul(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``x @ w.T`` with dynamically scaled fp8 operands, one scale per tensor — here per *shard*: every rank scales the slice of
+    the weight it owns, a finer granularity than one scale for the whole matrix."""
+    y = ops.fp8_linear(x, w)
+    if y is None:
+        from ..training.quantization import _fp8_roundtrip
+
+        y = ops.linear(_fp8_roundtrip(x, None), _fp8_roundtrip(w, None))
+    return y
+
+
+def _column(x_shard: torch.Tensor, w: torch.Tensor, tp: TensorParallelContext, fp8: bool) -> torch.Tensor:
+    if fp8:  # NCCL gather + fp8 tensor-core GEMM (the fused gather → GEMM kernel is bf16)
+        return _fp8_matmul(_GatherRows.apply(x_shard, tp), w)
+    return column_parallel_linear(x_shard, w, tp)
+
+
+def _row(x: torch.Tensor, w: torch.Tensor, tp: TensorParallelContext, residual: torch.Tensor, fp8: bool) -> torch.Tensor:
+    if fp8:
+        return residual + _ScatterSumRows.apply(_fp8_matmul(x, w), tp)
+    return row_parallel_linear(x, w, tp, residual)
+
+
 class TPAttention(nn.Module):
     def __init__(self, attn: nn.Module, tp: TensorParallelContext):
         super().__init__()
         w, r = tp.world, tp.rank
         if attn.num_heads % w or attn.num_kv_heads % w:
             raise ValueError(f"tensor parallel size {w} must divide num_heads ({attn.num_heads}) and num_kv_heads ({attn.num_kv_heads})")
-        for proj in (attn.q_proj, attn.k_proj, attn.v_proj, attn.output_proj):
-            if type(proj).__name__ != "Linear" or proj.bias is not None:
-                raise NotImplementedError("tensor parallelism supports bias-free, un-adapted attention projections")
+        self.fp8 = _wants_fp8((attn.q_proj, attn.k_proj, attn.v_proj, attn.output_proj), "attention projections")
         self.tp = tp
         self.head_dim = attn.head_dim
         self.heads, self.kv_heads = attn.num_heads // w, attn.num_kv_heads // w
@@ -69,13 +105,13 @@ class TPAttention(nn.Module):
 
     def forward(self, hn: torch.Tensor, residual: torch.Tensor, b: int, s: int, mask, input_pos) -> torch.Tensor:
         hd = self.head_dim
-        qkv = column_parallel_linear(hn, self.wqkv, self.tp)  # [b·s, (h + 2·h_kv)·hd] for the local heads
+        qkv = _column(hn, self.wqkv, self.tp, self.fp8)  # [b·s, (h + 2·h_kv)·hd] for the local heads
         nq, nk = self.heads * hd, self.kv_heads * hd
         q = self._pos(qkv[:, :nq].reshape(b, s, self.heads, hd), self.q_norm, input_pos)
         k = self._pos(qkv[:, nq : nq + nk].reshape(b, s, self.kv_heads, hd), self.k_norm, input_pos)
         v = qkv[:, nq + nk :].reshape(b, s, self.kv_heads, hd)
         out = ops.attention(q.contiguous(), k.contiguous(), v.contiguous(), _as_mask(mask, default_causal=self.is_causal and mask is None), scale=self.scale, softcap=self.softcap)
-        return row_parallel_linear(out.reshape(b * s, nq), self.wo, self.tp, residual)
+        return _row(out.reshape(b * s, nq), self.wo, self.tp, residual, self.fp8)
 
     # inference (replicated activations, local-head KV cache) -------------------------------
     def setup_cache(self, batch_size: int, dtype: torch.dtype, max_seq_len: int) -> None:
@@ -117,9 +153,7 @@ class TPMLP(nn.Module):
     def __init__(self, mlp: nn.Module, tp: TensorParallelContext):
         super().__init__()
         w, r = tp.world, tp.rank
-        for proj in (mlp.w1, mlp.w2, mlp.w3):
-            if proj is None or type(proj).__name__ != "Linear" or proj.bias is not None:
-                raise NotImplementedError("tensor parallelism supports bias-free, un-adapted gated MLPs")
+        self.fp8 = _wants_fp8((mlp.w1, mlp.w2, mlp.w3), "gated MLP projections")
         if not isinstance(mlp.activation, nn.SiLU):
             raise NotImplementedError("tensor parallelism supports SwiGLU MLPs")
         hidden = mlp.w1.weight.shape[0]
@@ -131,9 +165,9 @@ class TPMLP(nn.Module):
         self.w2 = nn.Parameter(mlp.w2.weight.data[:, r * per : (r + 1) * per].contiguous())
 
     def forward(self, hn: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
-        gu = column_parallel_linear(hn, self.w13, self.tp)
+        gu = _column(hn, self.w13, self.tp, self.fp8)
         h = ops.swiglu(gu[:, : self.per].contiguous(), gu[:, self.per :].contiguous())
-        return row_parallel_linear(h, self.w2, self.tp, residual)
+        return _row(h, self.w2, self.tp, residual, self.fp8)
 
     def forward_replicated(self, hn: torch.Tensor) -> torch.Tensor:
         gu = ops.linear(hn, self.w13)

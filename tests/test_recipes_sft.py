@@ -262,3 +262,27 @@ def test_early_exit_recipe_runs_and_rotates_exits(tmp_path, tune_path, monkeypat
     losses = read_losses(tmp_path / "out" / "logs" / "log.txt")
     assert len(losses) == 4 and all(l == l and 5.0 < l < 9.0 for l in losses)
     assert (tmp_path / "out" / "epoch_0" / "model-00001-of-00001.safetensors").exists()
+
+
+@pytest.mark.timeout(900)
+def test_lora_distributed_sharded_base_matches_resident(tmp_path):
+    """LoRA with shard_parameters=True (frozen base weights split over the ranks, adapters replicated) trains like LoRA on the
+    resident data-parallel engine; adapters and the merged checkpoint agree."""
+    ckpt = tmp_path / "ckpt"
+    write_tiny_hf_checkpoint(ckpt)
+    common = [f"checkpointer.checkpoint_dir={ckpt}", "metric_logger.filename=log.txt", "dataset.num_samples=16", "max_steps_per_epoch=3", "optimizer.lr=1e-2", "clip_grad_norm=1.0"]
+    losses = {}
+    for name, port, extra in (("dp", 29545, []), ("z3", 29546, ["shard_parameters=True", "shard_parameters_min_numel=1"])):
+        _tune_subprocess(
+            ["run", "--nnodes=1", "--nproc_per_node=2", "--master-addr=127.0.0.1", f"--master-port={port}", "lora_finetune_distributed", "--config", "tiny/llama_lora_distributed"]
+            + common + [f"output_dir={tmp_path / name}"] + extra
+        )
+        losses[name] = read_losses(tmp_path / name / "logs" / "log.txt")
+    assert len(losses["z3"]) == 3
+    torch.testing.assert_close(torch.tensor(losses["z3"]), torch.tensor(losses["dp"]), rtol=2e-4, atol=2e-4)
+    for fname in ("adapter_model.safetensors", "model-00001-of-00001.safetensors"):
+        a = load_file(str(tmp_path / "dp" / "epoch_0" / fname))
+        b = load_file(str(tmp_path / "z3" / "epoch_0" / fname))
+        assert set(a) == set(b)
+        for k in a:
+            torch.testing.assert_close(a[k], b[k], rtol=1e-3, atol=2e-5)

@@ -186,31 +186,76 @@ class ShardedLinear(nn.Module):
         return self.sw.gather(self.weight.detach()).clone()
 
 
+class ShardedLoRALinear(nn.Module):
+    """LoRA linear (``modules/peft/lora.py::LoRALinear``, dense base) whose *frozen* base weight is split by rows over the ranks;
+    the rank-``r`` adapters stay replicated and their gradients are summed before the optimizer step.  The reference shards LoRA
+    base weights through FSDP (recipes/lora_finetune_distributed.py:548); this is what lets a 70B bf16 base fit next to
+    activations."""
+
+    def __init__(self, lora: nn.Module, sw: ShardedWeightContext):
+        super().__init__()
+        self.sw = sw
+        self.rank, self.alpha, self.in_dim, self.out_dim, self.use_bias = lora.rank, lora.alpha, lora.in_dim, lora.out_dim, lora.use_bias
+        rows = lora.out_dim // sw.world
+        self.weight = nn.Parameter(sw.place(lora.weight.data[sw.rank * rows : (sw.rank + 1) * rows]), requires_grad=False)
+        self.bias = lora.bias
+        self.dropout, self.lora_a, self.lora_b = lora.dropout, lora.lora_a, lora.lora_b
+        self.merged = False
+        self.disabled = False
+
+    def adapter_params(self):
+        return ["lora_a.weight", "lora_b.weight"]
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        from .. import ops
+
+        base = _WeightGatherLinear.apply(x, self.weight, self.bias, self.sw)
+        if self.disabled:
+            return base
+        a = ops.linear(self.dropout(x), self.lora_a.weight)
+        return base + (self.alpha / self.rank) * ops.linear(a, self.lora_b.weight)
+
+    def full_weight(self) -> torch.Tensor:
+        return self.sw.gather(self.weight.detach()).clone()
+
+
+def _dims(m: nn.Module):
+    """(out_features, in_features) of a module whose ``weight`` can be row-sharded, else ``None``."""
+    if type(m).__name__ == "Linear" and isinstance(m, nn.Linear):
+        return m.out_features, m.in_features
+    if type(m).__name__ == "LoRALinear" and not getattr(m, "_quantize_base", False) and getattr(m, "weight", None) is not None:
+        return m.out_dim, m.in_dim
+    return None
+
+
 def shard_linear_weights(model: nn.Module, device: torch.device, group=None, *, min_numel: int = 1 << 16, exclude=("output",)) -> nn.Module:
-    """Replace every plain ``nn.Linear`` with at least ``min_numel`` weights whose rows split evenly into whole n-tiles by a
-    :class:`ShardedLinear` (in place; module paths in ``exclude`` are left alone) and attach ``_replicated``, ``sync_replicated_grads()``, ``after_optimizer_step()`` and
+    """Replace every plain ``nn.Linear`` (and every dense-base ``LoRALinear``) with at least ``min_numel`` weights whose rows split
+    evenly into whole n-tiles by a :class:`ShardedLinear` (:class:`ShardedLoRALinear`) (in place; module paths in ``exclude`` and
+    the small adapter matrices inside LoRA modules are left alone) and attach ``_replicated``, ``sync_replicated_grads()``, ``after_optimizer_step()`` and
     ``full_state_dict()`` (checkpoint layout; collective) to ``model``."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
 
     def eligible(m: nn.Module) -> bool:
-        if type(m).__name__ != "Linear" or not isinstance(m, nn.Linear) or m.weight.numel() < min_numel:
+        dims = _dims(m)
+        if dims is None or m.weight.numel() < min_numel:
             return False
+        out_features, in_features = dims
         if device.type != "cuda":
-            return m.out_features % world == 0
-        rows = m.out_features // world
-        bn = 256 if m.out_features > 128 else (128 if m.out_features > 64 else 64)
-        return m.out_features % world == 0 and rows % bn == 0 and m.in_features % 8 == 0 and m.weight.dtype == _BF16
+            return out_features % world == 0
+        rows = out_features // world
+        bn = 256 if out_features > 128 else (128 if out_features > 64 else 64)
+        return out_features % world == 0 and rows % bn == 0 and in_features % 8 == 0 and m.weight.dtype == _BF16
 
     # the output projection stays whole: the fused linear + cross-entropy loss reads its weight directly
-    targets = [(parent, name, child) for pname, parent in model.named_modules() for name, child in parent.named_children()
-               if eligible(child) and (f"{pname}.{name}" if pname else name) not in exclude]
+    targets = [(parent, name, child) for pname, parent in model.named_modules() if not callable(getattr(parent, "adapter_params", None))
+               for name, child in parent.named_children() if eligible(child) and (f"{pname}.{name}" if pname else name) not in exclude]
     store = sum(((c.weight.numel() // world) + 7) // 8 * 8 for _, _, c in targets)
     sw = ShardedWeightContext(device, group, store_numel=store, max_weight_numel=max((c.weight.numel() for _, _, c in targets), default=8),
-                              max_out_features=max((c.out_features for _, _, c in targets), default=64))
+                              max_out_features=max((_dims(c)[0] for _, _, c in targets), default=64))
     for parent, name, child in targets:
-        setattr(parent, name, ShardedLinear(child, sw))
+        setattr(parent, name, ShardedLinear(child, sw) if isinstance(child, nn.Linear) else ShardedLoRALinear(child, sw))
         child.weight.data = torch.empty(0, dtype=child.weight.dtype, device=child.weight.device)
-    sharded = {id(m.weight) for m in model.modules() if isinstance(m, ShardedLinear)}
+    sharded = {id(m.weight) for m in model.modules() if isinstance(m, (ShardedLinear, ShardedLoRALinear))}
     model._replicated = [p for p in model.parameters() if id(p) not in sharded]
     model._sw = sw
 
@@ -233,7 +278,7 @@ def shard_linear_weights(model: nn.Module, device: torch.device, group=None, *, 
 
     def full_state_dict() -> Dict[str, torch.Tensor]:
         out: Dict[str, torch.Tensor] = {}
-        fulls = {f"{name}.weight": m.full_weight() for name, m in model.named_modules() if isinstance(m, ShardedLinear)}
+        fulls = {f"{name}.weight": m.full_weight() for name, m in model.named_modules() if isinstance(m, (ShardedLinear, ShardedLoRALinear))}
         for k, v in model.state_dict().items():
             out[k] = fulls.get(k, v.detach())
         return out

@@ -329,13 +329,21 @@ class ParallelStrategy(DataParallelEngine):
                 raise NotImplementedError("expert parallelism is implemented for full fine-tuning")
             return self._shard_model_ep(model, cfg)
         if self._shard_parameters:
-            if is_lora:
-                raise NotImplementedError("shard_parameters is implemented for full fine-tuning")
             from .fsdp import shard_linear_weights
 
             get = cfg.get if hasattr(cfg, "get") else (lambda k, d=None: d)
             model = shard_linear_weights(model, self.device, None, min_numel=int(get("shard_parameters_min_numel", 1 << 16)))
             self.zero3 = model._sw
+            if is_lora and self.world > 1:
+                # adapters are initialised with rank-dependent seeds: rank 0's values win
+                for p in model._replicated:
+                    if p.requires_grad:
+                        if p.device.type == "cpu" and p.dtype == torch.bfloat16:
+                            tmp = p.data.float()
+                            dist.broadcast(tmp, src=0)
+                            p.data.copy_(tmp)
+                        else:
+                            dist.broadcast(p.data, src=0)
             return model
         self.prepare(model)
         if self.dims.cp_enabled:

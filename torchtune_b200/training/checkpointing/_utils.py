@@ -143,7 +143,8 @@ def get_all_checkpoints_in_dir(dir: Path, *, pattern: str = r"^(epoch|step)_(\d+
     rx = re.compile(pattern)
     if not Path(dir).is_dir():
         return []
-    return [p for p in Path(dir).iterdir() if p.is_dir() and rx.match(p.name)]
+    # ``<name>.partial`` is a checkpoint whose writers had not all finished when the job stopped: never a candidate
+    return [p for p in Path(dir).iterdir() if p.is_dir() and rx.match(p.name) and not p.name.endswith(".partial")]
 
 
 def _ckpt_order(p: Path):

@@ -95,3 +95,31 @@ def test_sharded_checkpoint_of_another_world_size_is_refused(tmp_path):
     meta.write_text(meta.read_text().replace('"world_size": 1', '"world_size": 4'))
     with pytest.raises(ValueError, match="was written by 4 ranks"):
         ckpt.load_checkpoint()
+
+
+def test_restarted_job_resumes_from_the_newest_complete_checkpoint(tmp_path, tune_path, monkeypatch):
+    """What ``torchrun --max-restarts`` does after a worker failure is to run the same command again with
+    ``TORCHELASTIC_RESTART_COUNT`` raised: the recipe must then pick up the newest complete checkpoint by itself."""
+    import shutil
+
+    from helpers import read_losses, run_tune, write_tiny_hf_checkpoint
+
+    ckpt = tmp_path / "ckpt"
+    write_tiny_hf_checkpoint(ckpt)
+    base = f"run full_finetune_single_device --config tiny/llama_full_single_device checkpointer.checkpoint_dir={ckpt} metric_logger.filename=log.txt max_steps_per_epoch=3 epochs=2 dataset.num_samples=12 "
+    run_tune(tune_path, base + f"output_dir={tmp_path / 'full'}", monkeypatch)
+    full = read_losses(tmp_path / "full" / "logs" / "log.txt")
+    run_tune(tune_path, base + f"output_dir={tmp_path / 'part'}", monkeypatch)
+    shutil.rmtree(tmp_path / "part" / "epoch_1")  # as if the job had died during the second epoch
+    (tmp_path / "part" / "epoch_2.partial").mkdir()
+    (tmp_path / "part" / "logs" / "log.txt").unlink()
+    monkeypatch.setenv("TORCHELASTIC_RESTART_COUNT", "1")
+    run_tune(tune_path, base + f"output_dir={tmp_path / 'part'}", monkeypatch)  # same command line, no resume flag
+    resumed = read_losses(tmp_path / "part" / "logs" / "log.txt")
+    torch.testing.assert_close(torch.tensor(resumed), torch.tensor(full[3:]), rtol=1e-5, atol=1e-5)
+    # a first start (restart count 0) with the same leftovers starts from the beginning
+    monkeypatch.setenv("TORCHELASTIC_RESTART_COUNT", "0")
+    shutil.rmtree(tmp_path / "part" / "epoch_1")
+    (tmp_path / "part" / "logs" / "log.txt").unlink()
+    run_tune(tune_path, base + f"output_dir={tmp_path / 'part'}", monkeypatch)
+    assert len(read_losses(tmp_path / "part" / "logs" / "log.txt")) == 6

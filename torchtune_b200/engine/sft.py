@@ -40,6 +40,26 @@ from .timing import StepTimer
 log = utils.get_logger("DEBUG")
 
 
+
+def _restarted_with_checkpoint(cfg: DictConfig) -> bool:
+    """Elastic recovery: when torchrun has restarted the workers after a failure (``tune run --max-restarts N``; the restart
+    count is exported as ``TORCHELASTIC_RESTART_COUNT``) and the output directory already holds a complete intermediate
+    checkpoint, continue from it instead of starting over.  ``resume_after_restart: False`` switches this off."""
+    if int(os.environ.get("TORCHELASTIC_RESTART_COUNT", "0") or 0) <= 0 or not cfg.get("resume_after_restart", True):
+        return False
+    from pathlib import Path
+
+    from ..training.checkpointing._utils import get_most_recent_checkpoint
+
+    ckpt_cfg = cfg.get("checkpointer")
+    out = (ckpt_cfg.get("output_dir") if ckpt_cfg is not None else None) or cfg.get("output_dir")
+    recent = get_most_recent_checkpoint(Path(out)) if out else None
+    found = recent is not None and ((recent / "recipe_state.pt").exists() or (recent / "metadata.json").exists())
+    if found:
+        log.info(f"Restart {os.environ['TORCHELASTIC_RESTART_COUNT']} of this job: resuming from {recent}")
+    return found
+
+
 class SFTTrainer:
     """Full / LoRA / QLoRA / DoRA supervised fine-tuning.
 
@@ -71,7 +91,7 @@ class SFTTrainer:
             log.info("log_peak_memory_stats was set to True, however, training does not use cuda. Setting log_peak_memory_stats=False.")
             self._log_peak_memory_stats = False
 
-        self._resume_from_checkpoint = cfg.get("resume_from_checkpoint", False)
+        self._resume_from_checkpoint = cfg.get("resume_from_checkpoint", False) or _restarted_with_checkpoint(cfg)
         self._gradient_accumulation_steps = cfg.get("gradient_accumulation_steps", 1)
         self._optimizer_in_bwd = cfg.get("optimizer_in_bwd", False)
         self._clip_grad_norm = cfg.get("clip_grad_norm", None)

@@ -741,3 +741,36 @@ def test_gemm_split_k_matches_fp32(M, N, K, a_mn, b_mn):
     af = a.float().t() if a_mn else a.float()
     bf = b.float() if b_mn else b.float().t()
     _close(got, 0.5 * (af @ bf), 2e-2, 2e-2 * (K ** 0.5) * 0.1, "split-k")
+
+
+def test_peer_buffer_guard_regions_detect_writes_outside(monkeypatch):
+    """Debug aid for the peer-memory kernels: with TTB_PEER_GUARD_BYTES set, every peer buffer sits between two pattern-filled
+    regions of the same allocation; a data-parallel step must leave them intact, and a stray write next to the buffer is reported."""
+    from torchtune_b200.ops._lib import KernelError
+    from torchtune_b200.parallel.dp import DataParallelEngine
+    from torchtune_b200.parallel.fabric import PeerBuffer
+
+    monkeypatch.setenv("TTB_PEER_GUARD_BYTES", "1000")
+    dev = torch.device("cuda", 0)
+    buf = PeerBuffer(4096 + 24, dev)
+    assert buf.guard == 1024 and buf.local_ptr % 256 == 0
+    buf.tensor(torch.uint8).fill_(7)  # the whole usable range
+    buf.check_guards()
+    buf._whole[buf.guard + buf.nbytes + 5] = 1  # inside the allocation, outside the buffer
+    with pytest.raises(KernelError, match="above were overwritten"):
+        buf.check_guards()
+    with pytest.raises(KernelError):
+        buf.close()
+    assert buf.local_ptr == 0  # freed all the same
+
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(256, 512), torch.nn.Linear(512, 256)).to(dev).bfloat16()
+    engine = DataParallelEngine(device=dev, group=None)
+    engine.prepare(model)
+    opt = engine.build_optimizer(model, lr=1e-3)
+    for _ in range(2):
+        model(torch.randn(64, 256, device=dev, dtype=torch.bfloat16)).float().pow(2).mean().backward()
+        engine.optimizer_step(model, opt, 1.0, 1.0)
+    engine.flat.param_buf.check_guards()
+    engine.flat.grad_buf.check_guards()
+    engine.shutdown()

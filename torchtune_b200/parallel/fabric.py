@@ -9,6 +9,7 @@ FSDP2/DTensor, torchtune/training/_distributed.py:661-714).
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import List, Optional
 
 import torch
@@ -36,10 +37,23 @@ def _declare(L) -> None:
     L._fabric_declared = True
 
 
+_GUARD_BYTE = 0xA5
+
+
+def _guard_bytes() -> int:
+    """``TTB_PEER_GUARD_BYTES=<n>`` (debug aid, default 0) surrounds every peer buffer with ``n`` bytes (rounded up to 256) of a
+    known pattern; :meth:`PeerBuffer.check_guards` then tells whether any kernel of any rank wrote outside the buffer."""
+    n = int(os.environ.get("TTB_PEER_GUARD_BYTES", "0") or 0)
+    return (n + 255) // 256 * 256 if n > 0 else 0
+
+
 class PeerBuffer:
     def __init__(self, nbytes: int, device: torch.device, group: Optional[dist.ProcessGroup] = None):
         self.nbytes = int(nbytes)
         self.device = device
+        self.guard = _guard_bytes() if device.type == "cuda" else 0
+        self._base_ptr = 0
+        self._whole: Optional[torch.Tensor] = None
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self._opened: List[int] = []
@@ -53,15 +67,21 @@ class PeerBuffer:
         _declare(L)
         L.ttb_ensure_device(device.index if device.index is not None else torch.cuda.current_device())
         out = ctypes.c_void_p()
-        if L.ttb_ipc_alloc(self.nbytes, ctypes.byref(out)) != 0 or not out.value:
-            raise KernelError(f"cudaMalloc of {self.nbytes} bytes for a peer buffer failed")
-        self.local_ptr = out.value
-        self._local = torch.as_tensor(_RawCudaMemory(self.local_ptr, self.nbytes), device=device)
+        g = self.guard
+        if L.ttb_ipc_alloc(self.nbytes + 2 * g, ctypes.byref(out)) != 0 or not out.value:
+            raise KernelError(f"cudaMalloc of {self.nbytes + 2 * g} bytes for a peer buffer failed")
+        self._base_ptr = out.value
+        self.local_ptr = out.value + g
+        self._whole = torch.as_tensor(_RawCudaMemory(self._base_ptr, self.nbytes + 2 * g), device=device)
+        self._local = self._whole[g : g + self.nbytes]
         self._local.zero_()
+        if g:
+            self._whole[:g].fill_(_GUARD_BYTE)
+            self._whole[g + self.nbytes :].fill_(_GUARD_BYTE)
         self.peer_ptrs = [self.local_ptr]
         if self.world > 1:
             handle = ctypes.create_string_buffer(64)
-            if L.ttb_ipc_get_handle(self.local_ptr, handle) != 0:
+            if L.ttb_ipc_get_handle(self._base_ptr, handle) != 0:
                 raise KernelError("cudaIpcGetMemHandle failed")
             handles: List[Optional[bytes]] = [None] * self.world
             dist.all_gather_object(handles, handle.raw, group=group)
@@ -74,7 +94,7 @@ class PeerBuffer:
                 if L.ttb_ipc_open(h, ctypes.byref(p)) != 0 or not p.value:
                     raise KernelError(f"mapping the peer buffer of rank {r} failed (is peer access available?)")
                 self._opened.append(p.value)
-                self.peer_ptrs.append(p.value)
+                self.peer_ptrs.append(p.value + g)  # every rank runs with the same guard size
             torch.cuda.synchronize(device)
             dist.barrier(group=group)
 
@@ -82,18 +102,35 @@ class PeerBuffer:
         t = self._local[offset_bytes:].view(dtype)
         return t if numel is None else t[:numel]
 
+    def check_guards(self) -> None:
+        """Raise if the guard regions around this rank's buffer no longer hold their pattern (someone — a local kernel or a
+        peer's — wrote outside the buffer).  No-op without ``TTB_PEER_GUARD_BYTES``."""
+        if not self.guard or self._whole is None:
+            return
+        g = self.guard
+        torch.cuda.synchronize(self.device)
+        lo = int((self._whole[:g] != _GUARD_BYTE).sum().item())
+        hi = int((self._whole[g + self.nbytes :] != _GUARD_BYTE).sum().item())
+        if lo or hi:
+            raise KernelError(f"peer buffer of {self.nbytes} bytes on rank {self.rank}: {lo} guard bytes below and {hi} above were overwritten")
+
     def pointer_array(self):
         arr = (ctypes.c_void_p * len(self.peer_ptrs))(*self.peer_ptrs)
         return arr
 
     def close(self) -> None:
+        """Unmap the peers' buffers and free the own one; with guard regions enabled their pattern is verified first."""
         if self.device.type != "cuda":
             return
         L = lib()
-        for p in self._opened:
-            L.ttb_ipc_close(p)
-        self._opened = []
-        if self.local_ptr:
-            self._local = None
-            L.ttb_ipc_free(self.local_ptr)
-            self.local_ptr = 0
+        try:
+            if self.local_ptr:
+                self.check_guards()
+        finally:
+            for p in self._opened:
+                L.ttb_ipc_close(p)
+            self._opened = []
+            if self.local_ptr:
+                self._local = self._whole = None
+                L.ttb_ipc_free(self._base_ptr)
+                self.local_ptr = self._base_ptr = 0

@@ -98,3 +98,32 @@ def test_expert_parallel_recipe_on_two_gpus(tmp_path):
     # bf16 routing can flip near-ties between the two runs; the curves stay close
     for a, b in zip(runs["ep"], runs["dp"]):
         assert abs(a - b) < 0.05 * abs(b), (runs["ep"], runs["dp"])
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fp8_tensor_parallel_recipe_on_two_gpus(tmp_path):
+    """enable_fp8_training with tensor_parallel_dim=2: the sharded projections run on the fp8 tensor cores between the row gather
+    and the reduce-scatter; losses stay in the band of the bf16 run."""
+    ckpt = _tiny_ckpt(tmp_path)
+    out = tmp_path / "fp8tp"
+    _tune(["full_finetune_distributed", "--config", "tiny/llama_full_distributed", f"checkpointer.checkpoint_dir={ckpt}", f"output_dir={out}", "metric_logger.filename=log.txt",
+           "device=cuda", "dtype=bf16", "max_steps_per_epoch=4", "dataset.num_samples=32", "optimizer.lr=1e-3", "tensor_parallel_dim=2", "enable_fp8_training=True"], 29591)
+    losses = _losses(out / "logs" / "log.txt")
+    assert len(losses) == 4 and all(l == l and 4.0 < l < 9.0 for l in losses), losses
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_lora_over_sharded_base_weights_on_two_gpus(tmp_path):
+    """LoRA with shard_parameters=True (frozen base rows split over the GPUs, gathered inside the forward GEMM) follows the loss
+    curve of LoRA on the resident data-parallel engine."""
+    ckpt = _tiny_ckpt(tmp_path)
+    res = {}
+    for name, port, extra in (("dp", 29593, []), ("z3", 29595, ["shard_parameters=True", "shard_parameters_min_numel=1"])):
+        out = tmp_path / name
+        _tune(["lora_finetune_distributed", "--config", "tiny/llama_lora_distributed", f"checkpointer.checkpoint_dir={ckpt}", f"output_dir={out}", "metric_logger.filename=log.txt",
+               "device=cuda", "dtype=bf16", "max_steps_per_epoch=4", "dataset.num_samples=32", "optimizer.lr=1e-2"] + extra, port)
+        res[name] = _losses(out / "logs" / "log.txt")
+    assert len(res["z3"]) == 4
+    for a, b in zip(res["dp"], res["z3"]):
+        assert abs(a - b) < 0.02 * abs(a), res
+    assert (tmp_path / "z3" / "epoch_0" / "adapter_model.safetensors").exists()

@@ -4,6 +4,7 @@
     python -m torchtune_b200.ops.microbench attention --batch 4 --seq 2048 --doc 512
     python -m torchtune_b200.ops.microbench rmsnorm --rows 8192 --dim 4096
     python -m torchtune_b200.ops.microbench adamw --numel 268435456
+    python -m torchtune_b200.ops.microbench suite --tokens 8192      (norm, RoPE, SwiGLU, loss, embedding, LoRA, grouped GEMM, NF4, offload copies)
 
 Each command prints one JSON line: median milliseconds over ``--iters`` launches (an L2 flush
 of 256 MiB between launches), the algorithmic FLOP/s or bytes/s, and the same figure for the
@@ -141,6 +142,146 @@ def bench_adamw(args, flush):
     return {"op": "adamw", "numel": n, "ms": t, "gbs": nbytes / t / 1e6}
 
 
+def bench_suite(args, flush):
+    """The memory-bound and fused operators of one Llama-3.1-8B training step (``--tokens`` rows, width 4096, MLP 14336,
+    vocabulary 128256) and of a Llama-4-Scout MoE layer (16 experts, 5120 → 8192), each against the PyTorch library expression of
+    the same maths on identical inputs.  Prints one JSON line per operator."""
+    import torch.nn.functional as F
+
+    from . import embedding, grouped_matmul, linear_cross_entropy, lora_linear, rms_norm, rope, swiglu
+
+    T, D, H, V = args.tokens, 4096, 14336, 128256
+    bf = dict(device="cuda", dtype=torch.bfloat16)
+    it, wu = args.iters, args.warmup
+    rows = []
+
+    def emit(op, ours_ms, lib_ms, **kw):
+        r = {"op": op, "ms": round(ours_ms, 4), "lib_ms": round(lib_ms, 4), "speedup_vs_lib": round(lib_ms / ours_ms, 2), **kw}
+        for key in ("gbs", "tflops"):
+            if key in r:
+                r[key] = round(r[key], 1)
+        rows.append(r)
+        print(json.dumps(r), flush=True)
+
+    def fwd_bwd(fn, inputs, go):
+        def run():
+            for t in inputs:
+                t.grad = None
+            fn().backward(go)
+        return run
+
+    # RMSNorm forward + backward: x read twice, y and dx written, dy read
+    x = torch.randn(T, D, **bf).requires_grad_()
+    w = torch.ones(D, **bf).requires_grad_()
+    go = torch.randn(T, D, **bf)
+    t_o = _time(fwd_bwd(lambda: rms_norm(x, w, 1e-5), (x, w), go), it, wu, flush)
+    t_l = _time(fwd_bwd(lambda: F.rms_norm(x, (D,), w, 1e-5), (x, w), go), it, wu, flush)
+    emit("rmsnorm_fwd_bwd", t_o, t_l, rows=T, dim=D, gbs=5.0 * T * D * 2 / t_o / 1e6)
+
+    # RoPE forward on q ([b, s, 32, 128])
+    b, sq = T // 2048, 2048
+    q = torch.randn(b, sq, 32, 128, **bf)
+    half = torch.arange(64, device="cuda", dtype=torch.float32)
+    ang = torch.arange(sq, device="cuda", dtype=torch.float32)[:, None] * (500000.0 ** (-half / 64))[None]
+    cache = torch.stack([ang.cos(), ang.sin()], dim=-1).contiguous()
+
+    def rope_lib():
+        xf = q.float().reshape(b, sq, 32, 64, 2)
+        c = cache.view(1, sq, 1, 64, 2)
+        return torch.stack([xf[..., 0] * c[..., 0] - xf[..., 1] * c[..., 1], xf[..., 1] * c[..., 0] + xf[..., 0] * c[..., 1]], -1).flatten(3).to(q.dtype)
+
+    with torch.no_grad():
+        t_o = _time(lambda: rope(q, cache), it, wu, flush)
+        t_l = _time(rope_lib, it, wu, flush)
+    emit("rope_fwd", t_o, t_l, shape=[b, sq, 32, 128], gbs=2.0 * q.numel() * 2 / t_o / 1e6)
+
+    # SwiGLU forward + backward: gate, up, dy read; y, dgate, dup written (+ gate, up re-read in backward)
+    g1 = torch.randn(T, H, **bf).requires_grad_()
+    u1 = torch.randn(T, H, **bf).requires_grad_()
+    goh = torch.randn(T, H, **bf)
+    t_o = _time(fwd_bwd(lambda: swiglu(g1, u1), (g1, u1), goh), it, wu, flush)
+    t_l = _time(fwd_bwd(lambda: F.silu(g1) * u1, (g1, u1), goh), it, wu, flush)
+    emit("swiglu_fwd_bwd", t_o, t_l, rows=T, dim=H, gbs=8.0 * T * H * 2 / t_o / 1e6)
+    del g1, u1, goh
+
+    # fused linear + cross-entropy, forward + backward (3 GEMMs of 2·T·D·V)
+    hid = (torch.randn(T, D, **bf) * 0.5).requires_grad_()
+    wv = (torch.randn(V, D, **bf) * 0.02).requires_grad_()
+    labels = torch.randint(0, V, (T,), device="cuda")
+    one = torch.ones((), device="cuda")
+
+    def ce_ours():
+        hid.grad = wv.grad = None
+        linear_cross_entropy(hid, wv, labels)[0].backward(one)
+
+    def ce_lib():
+        hid.grad = wv.grad = None
+        F.cross_entropy(F.linear(hid, wv).float(), labels, reduction="sum").backward(one)
+
+    t_o = _time(ce_ours, it, wu, flush)
+    t_l = _time(ce_lib, it, wu, flush)
+    emit("linear_cross_entropy_fwd_bwd", t_o, t_l, tokens=T, dim=D, vocab=V, tflops=6.0 * T * D * V / t_o / 1e9)
+    del wv, hid
+
+    # embedding gather + gradient
+    table = (torch.randn(V, D, **bf) * 0.02).requires_grad_()
+    toks = torch.randint(0, V, (T,), device="cuda")
+    t_o = _time(fwd_bwd(lambda: embedding(toks, table), (table,), go), it, wu, flush)
+    t_l = _time(fwd_bwd(lambda: F.embedding(toks, table), (table,), go), it, wu, flush)
+    emit("embedding_fwd_bwd", t_o, t_l, tokens=T, dim=D, vocab=V)
+    del table
+
+    # LoRA-fused linear (rank 64) forward: base GEMM + adapter in one kernel
+    xl = torch.randn(T, D, **bf)
+    wl = torch.randn(D, D, **bf) * 0.02
+    la, lb = torch.randn(64, D, **bf) * 0.02, torch.randn(D, 64, **bf) * 0.02
+    with torch.no_grad():
+        t_o = _time(lambda: lora_linear(xl, xl, wl, None, la, lb, 2.0), it, wu, flush)
+        t_l = _time(lambda: F.linear(xl, wl) + 2.0 * F.linear(F.linear(xl, la), lb), it, wu, flush)
+    emit("lora_linear_fwd", t_o, t_l, m=T, n=D, k=D, rank=64, tflops=2.0 * T * D * (D + 128) / t_o / 1e9)
+
+    # grouped expert GEMM, Scout shapes: 16 experts, top-1, uneven loads
+    E, Dm, Hm = 16, 5120, 8192
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    assign = torch.multinomial(torch.rand(E, device="cuda", generator=gen) + 0.2, T, replacement=True, generator=gen)
+    counts = torch.bincount(assign, minlength=E).to(torch.int32)
+    xe = torch.randn(T, Dm, **bf)
+    we = torch.randn(E, Dm, Hm, **bf) * 0.02
+    sizes = counts.tolist()
+
+    def grouped_lib():
+        outs, st = [], 0
+        for e, n in enumerate(sizes):
+            outs.append(xe[st : st + n] @ we[e])
+            st += n
+        return torch.cat(outs)
+
+    with torch.no_grad():
+        t_o = _time(lambda: grouped_matmul(xe, we, counts), it, wu, flush)
+        t_l = _time(grouped_lib, it, wu, flush)
+    emit("grouped_gemm_fwd", t_o, t_l, tokens=T, experts=E, k=Dm, n=Hm, tflops=2.0 * T * Dm * Hm / t_o / 1e9)
+    del we, xe
+
+    # NF4 dequantise (4096 × 14336): 0.5 B read + 2 B written per element
+    from ..modules.low_precision.nf4 import NF4Weight
+
+    nf4 = NF4Weight(H, D, device="cuda")
+    nf4.quantize_(torch.randn(H, D, **bf) * 0.02)
+    t_o = _time(lambda: nf4.dequantize(torch.bfloat16), it, wu, flush)
+    emit("nf4_dequantize", t_o, t_o, shape=[H, D], gbs=2.53 * H * D / t_o / 1e6)
+
+    # activation offload path: pinned host <-> device copies of 1 GiB on a side stream
+    n = 1 << 30
+    dev_buf = torch.empty(n, dtype=torch.uint8, device="cuda")
+    host = torch.empty(n, dtype=torch.uint8, pin_memory=True)
+    t_d2h = _time(lambda: host.copy_(dev_buf, non_blocking=True), it, wu, flush)
+    t_h2d = _time(lambda: dev_buf.copy_(host, non_blocking=True), it, wu, flush)
+    r = {"op": "offload_copy_1GiB", "d2h_ms": round(t_d2h, 3), "h2d_ms": round(t_h2d, 3), "d2h_gbs": round(n / t_d2h / 1e6, 1), "h2d_gbs": round(n / t_h2d / 1e6, 1)}
+    print(json.dumps(r), flush=True)
+    rows.append(r)
+    return {"op": "suite", "tokens": T, "operators": len(rows)}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--iters", type=int, default=5)
@@ -168,11 +309,13 @@ def main() -> None:
     r.add_argument("--dim", type=int, default=4096)
     o = sub.add_parser("adamw")
     o.add_argument("--numel", type=int, default=1 << 28)
+    su = sub.add_parser("suite")
+    su.add_argument("--tokens", type=int, default=8192)
     args = ap.parse_args()
     from ._lib import check_device_errors
 
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
-    fn = {"gemm": bench_gemm, "gemm_fp8": bench_gemm_fp8, "attention": bench_attention, "rmsnorm": bench_rmsnorm, "adamw": bench_adamw}[args.op]
+    fn = {"gemm": bench_gemm, "gemm_fp8": bench_gemm_fp8, "attention": bench_attention, "rmsnorm": bench_rmsnorm, "adamw": bench_adamw, "suite": bench_suite}[args.op]
     res = fn(args, flush)
     check_device_errors()
     print(json.dumps(res), flush=True)

@@ -91,7 +91,7 @@ def test_linear_autograd():
 
 
 # ------------------------------------------------------------------ elementwise
-@pytest.mark.parametrize("rows,D", [(37, 256), (1024, 4096), (5, 8192)])
+@pytest.mark.parametrize("rows,D", [(37, 256), (1024, 4096), (5, 8192), (19, 1536), (7, 12288), (2051, 2048)])
 def test_rmsnorm(rows, D):
     x = _rand(rows, D, seed=1).requires_grad_()
     scale = (1 + 0.1 * _rand(D, seed=2).float()).to(torch.bfloat16).requires_grad_()

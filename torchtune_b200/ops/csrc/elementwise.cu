@@ -85,6 +85,53 @@ __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __
   }
 }
 
+// One CTA per row for model-width rows (D >= 1024): every thread loads its MAXV 16-byte pieces up front (all loads in
+// flight at once) and keeps them in registers between the sum of squares and the scaling, so x is read once.
+template <int THREADS, int MAXV>
+__global__ void __launch_bounds__(THREADS)
+rmsnorm_fwd_row_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ scale,
+                       __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out, int rows, int D, float eps) {
+  __shared__ float scratch[32];
+  const int row = blockIdx.x;
+  const int nvec = D >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<long long>(row) * D);
+  uint4 v[MAXV];
+#pragma unroll
+  for (int k = 0; k < MAXV; ++k) {
+    const int i = threadIdx.x + k * THREADS;
+    v[k] = i < nvec ? __ldg(xr + i) : make_uint4(0u, 0u, 0u, 0u);
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < MAXV; ++k) {
+    float f[8];
+    unpack8(v[k], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+  }
+  ss = block_sum<THREADS>(ss, scratch);
+  const float rstd = rsqrtf(ss / D + eps);
+  if (threadIdx.x == 0 && rstd_out != nullptr) rstd_out[row] = rstd;
+  uint4* yr = reinterpret_cast<uint4*>(y + static_cast<long long>(row) * D);
+  const uint4* sr = reinterpret_cast<const uint4*>(scale);
+#pragma unroll
+  for (int k = 0; k < MAXV; ++k) {
+    const int i = threadIdx.x + k * THREADS;
+    if (i < nvec) {
+      float f[8], s[8];
+      unpack8(v[k], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = __bfloat162float(__float2bfloat16_rn(f[j] * rstd));
+      if (scale != nullptr) {
+        unpack8(__ldg(sr + i), s);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] *= s[j];
+      }
+      yr[i] = pack8(f);
+    }
+  }
+}
+
 // Backward: dx = rstd * (g - xhat * mean(g * xhat)),  g = dy * scale,  xhat = x * rstd
 //           dscale_partial[cta, :] = sum over the CTA's rows of dy * xhat
 // One CTA (256 threads) walks rows blockIdx.x, +gridDim.x, ...; thread t owns columns
@@ -102,10 +149,33 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[v][j] = 0.f;
 
+  // The loads of the next row are issued before the reduction and the stores of the current one (for up to two pieces per
+  // thread; wider rows would spill), so a CTA always has a row in flight.
+  constexpr bool kPrefetch = MAXV <= 2;
+  uint4 ndy[MAXV], nx[MAXV];
+  float nrs = 0.f;
+  auto fetch = [&](int r) {
+    const uint4* dyr = reinterpret_cast<const uint4*>(dy + static_cast<long long>(r) * D);
+    const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<long long>(r) * D);
+#pragma unroll
+    for (int v = 0; v < MAXV; ++v) {
+      const int i = threadIdx.x + v * 256;
+      if (i < nvec) {
+        ndy[v] = __ldg(dyr + i);
+        nx[v] = __ldg(xr + i);
+      }
+    }
+    nrs = rstd[r];
+  };
+  if (kPrefetch && static_cast<int>(blockIdx.x) < rows) fetch(blockIdx.x);
+
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-    const uint4* dyr = reinterpret_cast<const uint4*>(dy + static_cast<long long>(row) * D);
-    const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<long long>(row) * D);
-    const float rs = rstd[row];
+    if (!kPrefetch) fetch(row);
+    uint4 cdy[MAXV], cx[MAXV];
+#pragma unroll
+    for (int v = 0; v < MAXV; ++v) cdy[v] = ndy[v], cx[v] = nx[v];
+    const float rs = nrs;
+    if (kPrefetch && row + static_cast<int>(gridDim.x) < rows) fetch(row + gridDim.x);
     float g[MAXV][8], xh[MAXV][8];
     float dot = 0.f;
 #pragma unroll
@@ -113,8 +183,8 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
       const int i = threadIdx.x + v * 256;
       if (i < nvec) {
         float a[8], b[8], s[8];
-        unpack8(__ldg(dyr + i), a);
-        unpack8(__ldg(xr + i), b);
+        unpack8(cdy[v], a);
+        unpack8(cx[v], b);
         if (scale != nullptr) unpack8(__ldg(reinterpret_cast<const uint4*>(scale) + i), s);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -281,6 +351,18 @@ extern "C" int ttb_rmsnorm_fwd(const void* x, const void* scale, void* y, float*
   if (D & 7) return kErrBadShape;
   const int warps = 4;
   TTB_COUNT_LAUNCH(1);
+  const int nvec_fwd = D >> 3;
+  if (nvec_fwd >= 128 && nvec_fwd <= 2048) {
+    auto st = static_cast<cudaStream_t>(stream);
+    auto xp = static_cast<const __nv_bfloat16*>(x);
+    auto sp = static_cast<const __nv_bfloat16*>(scale);
+    auto yp = static_cast<__nv_bfloat16*>(y);
+    if (nvec_fwd <= 256) rmsnorm_fwd_row_kernel<128, 2><<<rows, 128, 0, st>>>(xp, sp, yp, rstd, rows, D, eps);
+    else if (nvec_fwd <= 512) rmsnorm_fwd_row_kernel<128, 4><<<rows, 128, 0, st>>>(xp, sp, yp, rstd, rows, D, eps);
+    else if (nvec_fwd <= 1024) rmsnorm_fwd_row_kernel<256, 4><<<rows, 256, 0, st>>>(xp, sp, yp, rstd, rows, D, eps);
+    else rmsnorm_fwd_row_kernel<256, 8><<<rows, 256, 0, st>>>(xp, sp, yp, rstd, rows, D, eps);
+    return cudaGetLastError() == cudaSuccess ? kOk : kErrDriver;
+  }
   rmsnorm_fwd_kernel<<<(rows + warps - 1) / warps, warps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(scale), static_cast<__nv_bfloat16*>(y),
       rstd, rows, D, eps);

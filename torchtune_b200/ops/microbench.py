@@ -113,14 +113,28 @@ def bench_attention(args, flush):
 
 
 def bench_rmsnorm(args, flush):
+    import torch.nn.functional as F
+
     from . import rms_norm
 
-    x = torch.randn(args.rows, args.dim, device="cuda", dtype=torch.bfloat16)
-    w = torch.ones(args.dim, device="cuda", dtype=torch.bfloat16)
+    x = torch.randn(args.rows, args.dim, device="cuda", dtype=torch.bfloat16).requires_grad_()
+    w = torch.ones(args.dim, device="cuda", dtype=torch.bfloat16).requires_grad_()
+    go = torch.randn(args.rows, args.dim, device="cuda", dtype=torch.bfloat16)
     with torch.no_grad():
         t = _time(lambda: rms_norm(x, w, 1e-5), args.iters, args.warmup, flush)
+        t_lib = _time(lambda: F.rms_norm(x, (args.dim,), w, 1e-5), args.iters, args.warmup, flush)
+
+    def both(fn):
+        def run():
+            x.grad = w.grad = None
+            fn().backward(go)
+        return run
+
+    t2 = _time(both(lambda: rms_norm(x, w, 1e-5)), args.iters, args.warmup, flush)
+    t2_lib = _time(both(lambda: F.rms_norm(x, (args.dim,), w, 1e-5)), args.iters, args.warmup, flush)
     nbytes = 2.0 * x.numel() * 2
-    return {"op": "rmsnorm_fwd", "rows": args.rows, "dim": args.dim, "ms": t, "gbs": nbytes / t / 1e6}
+    return {"op": "rmsnorm", "rows": args.rows, "dim": args.dim, "ms": t, "gbs": nbytes / t / 1e6, "lib_ms": t_lib,
+            "fwd_bwd_ms": t2, "fwd_bwd_gbs": 2.5 * nbytes / t2 / 1e6, "lib_fwd_bwd_ms": t2_lib}
 
 
 def bench_adamw(args, flush):

@@ -80,3 +80,49 @@ def test_model_builders_resolve(family):
     mod = importlib.import_module(f"torchtune_b200.models.{family}")
     missing = [n for n in MODEL_BUILDERS[family] if not hasattr(mod, n)]
     assert not missing, f"models.{family} lacks {missing}"
+
+
+def test_recipe_facing_sharding_and_mask_helpers():
+    """Names that user recipes import from ``training`` / ``modules`` / ``modules.peft`` and what they do here."""
+    import contextlib
+
+    import torch
+
+    from torchtune_b200 import training
+    from torchtune_b200.models.llama3_1 import llama3_1
+    from torchtune_b200.modules import create_block_causal_mask, packed_block_causal_mask
+    from torchtune_b200.modules.peft import TrainableParams
+    from torchtune_b200.parallel.cp import ContextParallelContext
+    from torchtune_b200.training.checkpointing import get_largest_iter_folder  # noqa: F401
+
+    for name in ("DEFAULT_PROFILE_DIR", "DEFAULT_PROFILER_ACTIVITIES", "DEFAULT_SCHEDULE", "DEFAULT_TRACE_OPTS", "PROFILER_KEY"):
+        assert hasattr(training, name)
+    assert [p.value for p in TrainableParams] == ["full", "lora", "frozen"]
+
+    lens = [torch.tensor([2, 3]), torch.tensor([4, 1])]
+    dense = create_block_causal_mask(lens)
+    assert dense.shape == (2, 5, 5) and dense[0, 1].tolist() == [True, True, False, False, False] and dense[0, 4].tolist() == [False, False, True, True, True]
+    packed = packed_block_causal_mask(lens)
+    assert packed.causal and packed.doc_ids.tolist() == [[0, 0, 1, 1, 1], [0, 0, 0, 0, 1]]
+
+    assert training.get_shard_conditions("decoder.layers.3", None) and not training.get_shard_conditions("layers.3.attn", None)
+    assert training.get_shard_conditions("output", None, ["output"])
+
+    arch = dict(vocab_size=64, num_layers=1, num_heads=4, num_kv_heads=2, embed_dim=32, max_seq_len=32, intermediate_dim=48)
+    model = training.prepare_mha_for_tp(llama3_1(**arch), 2)
+    attn = model.layers[0].attn
+    assert (attn.num_heads, attn.num_kv_heads, attn.embed_dim) == (2, 1, 16)
+
+    x = torch.arange(16).view(2, 8)
+    cp = ContextParallelContext(None, world=2, rank=1)
+    with training.get_context_parallel_manager(enabled=True, cp=cp)([x]):
+        assert x.tolist() == [[4, 5, 6, 7], [12, 13, 14, 15]]
+    assert x.shape == (2, 8) and x[1, 0] == 8
+    with training.get_context_parallel_manager(enabled=False)([x]):
+        assert x.shape == (2, 8)
+    assert isinstance(training.get_train_context(True)(), contextlib.nullcontext)
+
+    sharded = training.shard_model(llama3_1(**arch), min_numel=1)  # one process: every shard is the whole weight
+    assert type(sharded.layers[0].attn.q_proj).__name__ == "ShardedLinear"
+    tokens = torch.randint(0, 64, (2, 8))
+    assert sharded(tokens).shape == (2, 8, 64)

@@ -1,4 +1,5 @@
 from .attention import MultiHeadAttention
+from .attention_utils import create_block_causal_mask, packed_block_causal_mask
 from .classifier import classifier_model
 from .common_utils import (
     delete_kv_caches,
@@ -32,6 +33,8 @@ from .vision_transformer import CLSEmbedding, CLSProjection, PatchEmbedding, Vis
 
 __all__ = [
     "MultiHeadAttention",
+    "create_block_causal_mask",
+    "packed_block_causal_mask",
     "LayerDropout",
     "ModuleLayerDropoutWrapper",
     "ScaleType",

@@ -10,13 +10,14 @@ from ._utils import (
     validate_missing_and_unexpected_for_lora,
 )
 from .dora import DoRALinear
-from .lora import LoRALinear, QATLoRALinear
+from .lora import LoRALinear, QATLoRALinear, TrainableParams
 
 __all__ = [
     "AdapterModule",
     "DoRALinear",
     "LoRALinear",
     "QATLoRALinear",
+    "TrainableParams",
     "LORA_ATTN_MODULES",
     "disable_adapter",
     "get_adapter_params",

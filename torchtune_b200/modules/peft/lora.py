@@ -1,6 +1,8 @@
 """LoRA linear layers (parity: torchtune/modules/peft/lora.py:27-320)."""
 from __future__ import annotations
 
+from enum import Enum
+
 import math
 from typing import List, Optional
 
@@ -10,6 +12,14 @@ from torch import nn
 
 from ... import ops
 from ..low_precision.nf4 import NF4Weight, linear_nf4
+
+
+class TrainableParams(Enum):
+    """How a model part is trained by the LoRA builders: every weight, adapters only, or nothing."""
+
+    FULL = "full"
+    LORA = "lora"
+    FROZEN = "frozen"
 
 
 class LoRALinear(nn.Module):

@@ -40,12 +40,17 @@ from .pooling import get_unmasked_sequence_lengths
 from .precision import get_dtype, set_default_dtype, validate_expected_param_dtype
 from .seed import set_seed
 from ._activation_offloading import NoOpManager, OffloadActivations, get_act_offloading_ctx_manager
-from ._profiler import DummyProfiler, setup_torch_profiler
+from ._profiler import DEFAULT_PROFILE_DIR, DEFAULT_PROFILER_ACTIVITIES, DEFAULT_SCHEDULE, DEFAULT_TRACE_OPTS, PROFILER_KEY, DummyProfiler, setup_torch_profiler
 from ._distributed import (
     VALID_BACKENDS_FOR_MEMORY_STATS,
     ParallelDims,
     gather_cpu_state_dict,
     get_distributed_backend,
+    get_context_parallel_manager,
+    get_shard_conditions,
+    get_train_context,
+    prepare_mha_for_tp,
+    shard_model,
     get_full_optimizer_state_dict,
     get_world_size_and_rank,
     init_distributed,

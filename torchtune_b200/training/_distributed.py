@@ -8,7 +8,7 @@ package's own peer-memory kernels (:mod:`torchtune_b200.parallel`).
 from __future__ import annotations
 
 import os
-from typing import Any, Dict, Optional
+from typing import Any, Dict, List, Optional
 
 import torch
 import torch.distributed as dist
@@ -141,3 +141,91 @@ __all__ = [
     "get_full_optimizer_state_dict",
     "load_from_full_optimizer_state_dict",
 ]
+
+
+# ------------------------------------------------------------------------------ sharding / parallel helpers (recipe-facing names)
+def get_shard_conditions(name: str, module: nn.Module, names_to_match: Optional[List[str]] = None, *args: Any, **kwargs: Any) -> bool:
+    """``True`` for the modules that form their own shard unit: every decoder layer (a module path ending in ``layers.<int>``)
+    and anything listed in ``names_to_match`` (torchtune/training/_distributed.py:612-658)."""
+    if names_to_match and name in names_to_match:
+        return True
+    parts = name.split(".")
+    return len(parts) >= 2 and parts[-2] == "layers" and parts[-1].isdigit()
+
+
+def shard_model(model: nn.Module, shard_conditions=None, *, cpu_offload: bool = False, reshard_after_forward: bool = True, dp_mesh=None,
+                device: Optional[torch.device] = None, min_numel: int = 1 << 16) -> nn.Module:
+    """Shard the parameters of ``model`` over the data-parallel ranks (the call the reference's recipes make,
+    torchtune/training/_distributed.py:661-714).  Here that means: the rows of every linear weight are split over the ranks in
+    one peer-visible store and gathered inside the consuming GEMM (:func:`torchtune_b200.parallel.fsdp.shard_linear_weights`).
+    ``shard_conditions`` / ``reshard_after_forward`` are accepted for signature parity: weights are always re-gathered per use,
+    and the unit of sharding is the linear layer.  ``dp_mesh`` may be a process group (or ``None`` for all ranks)."""
+    from ..parallel.fsdp import shard_linear_weights
+
+    if cpu_offload:
+        raise NotImplementedError("cpu_offload is not supported: 180 GB of device memory hold the sharded state")
+    if device is None:
+        first = next(model.parameters())
+        device = first.device
+    return shard_linear_weights(model, device, dp_mesh, min_numel=min_numel)
+
+
+def prepare_mha_for_tp(model: nn.Module, tp_mesh) -> nn.Module:
+    """Divide the head counts and width of every attention module by the tensor-parallel size so that reshapes inside
+    attention see local shapes (torchtune/training/_distributed.py:717-778).  ``tp_mesh``: an int, a process group or anything
+    with ``size()``.  (:func:`torchtune_b200.parallel.tp_model.tensor_parallelize` builds its own local attention modules and does
+    not need this; it is kept for code that shards projections by hand.)"""
+    from ..modules import MultiHeadAttention
+
+    if isinstance(tp_mesh, int):
+        size = tp_mesh
+    elif hasattr(tp_mesh, "size") and callable(tp_mesh.size):
+        size = tp_mesh.size()
+    else:
+        size = dist.get_world_size(tp_mesh)
+    for m in model.modules():
+        if isinstance(m, MultiHeadAttention):
+            if m.num_heads % size or m.num_kv_heads % size or m.embed_dim % size:
+                raise ValueError(f"tensor parallel size {size} must divide num_heads ({m.num_heads}), num_kv_heads ({m.num_kv_heads}) and embed_dim ({m.embed_dim})")
+            m.num_heads //= size
+            m.num_kv_heads //= size
+            m.embed_dim //= size
+    return model
+
+
+def get_context_parallel_manager(*, enabled: bool = False, world_mesh=None, model: Optional[nn.Module] = None, cp=None):
+    """Returns ``manager(buffers)``, a context manager that — when enabled — swaps every tensor in ``buffers`` for this rank's
+    slice of its sequence dimension (dim 1) for the duration of the block and restores it afterwards
+    (torchtune/training/_distributed.py:781-886).  ``cp``: a :class:`torchtune_b200.parallel.cp.ContextParallelContext` (the
+    model must have been prepared with :func:`torchtune_b200.parallel.cp.context_parallelize`); ``world_mesh`` is accepted for
+    signature parity."""
+    import contextlib
+
+    @contextlib.contextmanager
+    def manager(buffers: Optional[List[torch.Tensor]] = None):
+        if not enabled or cp is None or not buffers:
+            yield
+            return
+        saved = []
+        for t in buffers:
+            keep = torch.empty(0, dtype=t.dtype, device=t.device).set_(t)
+            saved.append(keep)
+            t.set_(cp.shard_seq(keep, dim=1).contiguous())
+        try:
+            yield
+        finally:
+            for t, keep in zip(buffers, saved):
+                t.set_(keep)
+
+    return manager
+
+
+def get_train_context(enable_loss_parallel: bool = False):
+    """Returns a factory of context managers for one training step (torchtune/training/_distributed.py:889-902).  Under tensor
+    parallelism the loss already runs on each rank's own token rows with the whole vocabulary, so there is nothing to switch on."""
+    import contextlib
+
+    def context():
+        return contextlib.nullcontext()
+
+    return context

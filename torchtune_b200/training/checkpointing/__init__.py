@@ -20,6 +20,7 @@ from ._utils import (
     VAL_DATALOADER_KEY,
     FormattedCheckpointFiles,
     ModelType,
+    get_largest_iter_folder,
     update_state_dict_for_classifier,
 )
 
@@ -35,6 +36,7 @@ __all__ = [
     "ModelType",
     "FormattedCheckpointFiles",
     "update_state_dict_for_classifier",
+    "get_largest_iter_folder",
     "ADAPTER_CONFIG",
     "ADAPTER_KEY",
     "EPOCHS_KEY",

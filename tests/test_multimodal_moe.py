@@ -231,3 +231,26 @@ def test_export_modules_match_training_modules():
     replace_tiled_token_positional_embedding(enc)
     got, _ = enc(images, ar)
     torch.testing.assert_close(got, want, rtol=1e-5, atol=1e-5)
+
+
+def test_lora_llama4_vision_encoder_builders():
+    """Adapters on the CLIP tower and / or the projection head: zero-initialised B matrices leave the output equal to the plain
+    encoder with the same base weights; the switches choose where adapters are attached."""
+    import torch
+
+    from torchtune_b200.models.llama4 import llama4_vision_encoder, lora_llama4_vision_encoder
+    from torchtune_b200.modules.peft import get_adapter_params
+
+    kw = dict(patch_size=14, num_heads=4, clip_embed_dim=64, clip_num_layers=2, projection_embed_dim=96, decoder_embed_dim=48, tile_size=56, max_num_tiles=1)
+    torch.manual_seed(0)
+    plain = llama4_vision_encoder(**kw)
+    lora = lora_llama4_vision_encoder(True, True, ["q_proj", "v_proj"], apply_lora_to_mlp=True, apply_lora_to_output=True, lora_rank=4, lora_alpha=8, **kw)
+    adapters = get_adapter_params(lora)
+    assert any(k.startswith("clip.") for k in adapters) and any(k.startswith("projection.") for k in adapters)
+    missing, unexpected = lora.load_state_dict(plain.state_dict(), strict=False)
+    assert not unexpected and all("lora_" in k for k in missing)
+    x = torch.randn(3, 3, 56, 56)
+    torch.testing.assert_close(lora(x), plain(x), rtol=1e-5, atol=1e-5)
+    head_only = lora_llama4_vision_encoder(False, True, ["q_proj"], apply_lora_to_output=True, lora_rank=4, lora_alpha=8, **kw)
+    assert all(k.startswith("projection.") for k in get_adapter_params(head_only)) and len(get_adapter_params(head_only)) == 6
+    assert len(get_adapter_params(lora_llama4_vision_encoder(False, True, ["q_proj"], apply_lora_to_output=False, lora_rank=4, lora_alpha=8, **kw))) == 0

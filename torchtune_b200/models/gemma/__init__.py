@@ -46,3 +46,12 @@ def gemma_tokenizer(path: str, max_seq_len: Optional[int] = None, prompt_templat
     from ._tokenizer import GemmaTokenizer
 
     return GemmaTokenizer(path=path, max_seq_len=max_seq_len, prompt_template=_get_prompt_template(prompt_template) if prompt_template is not None else None, truncation_type=truncation_type)
+
+
+def __getattr__(name):
+    # tokenizer classes are imported on first use (they pull in sentencepiece / regex tables)
+    if name == "GemmaTokenizer":
+        from ._tokenizer import GemmaTokenizer
+
+        return GemmaTokenizer
+    raise AttributeError(name)

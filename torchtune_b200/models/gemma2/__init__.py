@@ -44,3 +44,13 @@ for _n, _s in _S.items():
     globals()[f"gemma2_{_n}"] = preset(gemma2, f"gemma2_{_n}", f"Gemma-2 {_n}.", **_C, **_s)
     globals()[f"lora_gemma2_{_n}"] = lora_preset(_lora_gemma2, f"lora_gemma2_{_n}", f"Gemma-2 {_n} with adapters.", **_C, **_s)
     globals()[f"qlora_gemma2_{_n}"] = qlora_preset(globals()[f"lora_gemma2_{_n}"], f"qlora_gemma2_{_n}")
+
+from ..gemma import gemma_tokenizer  # gemma 2 uses the gemma tokenizer
+
+
+def __getattr__(name):
+    if name == "GemmaTokenizer":
+        from ..gemma._tokenizer import GemmaTokenizer
+
+        return GemmaTokenizer
+    raise AttributeError(name)

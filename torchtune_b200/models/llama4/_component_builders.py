@@ -9,6 +9,7 @@ from torch import nn
 
 from ...modules import FeedForward, Linear, Llama4ScaledRoPE, RotaryPositionalEmbeddings, TransformerDecoder, rms_norm
 from ...modules.moe import GroupedExperts, LoRAGroupedExperts, MoE, TokenChoiceTopKRouter
+from ...modules.peft import DoRALinear, LoRALinear
 from .._factory import AdapterSpec, DecoderArch, adapter_from_kwargs, build_decoder, build_mlp
 from ..clip import clip_vision_encoder
 from ._chunked_attention import chunked_mask_mod
@@ -102,3 +103,42 @@ def llama4_vision_encoder(*, patch_size: int, num_heads: int, clip_embed_dim: in
     clip = clip_vision_encoder(tile_size=tile_size, patch_size=patch_size, embed_dim=clip_embed_dim, num_layers=clip_num_layers, num_heads=num_heads, activation=nn.GELU, out_indices=clip_hidden_states,
                                max_num_tiles=max_num_tiles, in_channels=in_channels, attn_bias=True, output_cls_projection=False, append_cls_token=True, use_rope=True, use_tile_pos_embed=False)
     return Llama4VisionEncoder(clip=clip, projection_head=llama4_vision_projection_head(decoder_embed_dim=decoder_embed_dim, clip_embed_dim=clip_embed_dim, projection_embed_dim=projection_embed_dim))
+
+
+def lora_llama4_vision_projection_head(*, decoder_embed_dim: int, clip_embed_dim: int, projection_embed_dim: int, apply_lora_to_output: bool, lora_rank: int, lora_alpha: float,
+                                       lora_dropout: float = 0.0, use_dora: bool = False, quantize_base: bool = False, **quantization_kwargs) -> Llama4VisionProjectionHead:
+    """Projection head whose three linears carry adapters when ``apply_lora_to_output`` (they *are* the head's output path);
+    otherwise the plain head (parity: torchtune/models/llama4/_component_builders.py:783-860)."""
+    if not apply_lora_to_output:
+        return llama4_vision_projection_head(decoder_embed_dim=decoder_embed_dim, clip_embed_dim=clip_embed_dim, projection_embed_dim=projection_embed_dim)
+    factor = 0.5
+    cls = DoRALinear if use_dora else LoRALinear
+    mk = lambda i, o: cls(i, o, rank=lora_rank, alpha=lora_alpha, dropout=lora_dropout, use_bias=False, quantize_base=quantize_base, **quantization_kwargs)
+    output = nn.Sequential(mk(int(clip_embed_dim // (factor**2)), projection_embed_dim), nn.GELU(), mk(projection_embed_dim, projection_embed_dim), nn.GELU(),
+                           mk(projection_embed_dim, decoder_embed_dim))
+    return Llama4VisionProjectionHead(output=output, pixel_shuffle_scaling_factor=factor)
+
+
+def lora_llama4_vision_encoder(encoder_lora: bool, fusion_lora: bool, lora_attn_modules: List[str], apply_lora_to_mlp: bool = False, apply_lora_to_output: bool = False, *, patch_size: int,
+                               num_heads: int, clip_embed_dim: int, clip_num_layers: int, clip_hidden_states: Optional[List[int]] = None, projection_embed_dim: int, decoder_embed_dim: int,
+                               tile_size: int, max_num_tiles: int = 1, in_channels: int = 3, lora_rank: int = 8, lora_alpha: float = 16, lora_dropout: float = 0.0, use_dora: bool = False,
+                               quantize_base: bool = False, **quantization_kwargs) -> Llama4VisionEncoder:
+    """Llama-4 vision encoder with adapters on the CLIP tower (``encoder_lora``) and / or the projection head (``fusion_lora``)
+    (parity: torchtune/models/llama4/_component_builders.py:392-500)."""
+    from ..clip._component_builders import _vision_encoder
+
+    clip_kwargs = dict(tile_size=tile_size, patch_size=patch_size, embed_dim=clip_embed_dim, num_layers=clip_num_layers, num_heads=num_heads, activation=nn.GELU, cls_output_dim=512,
+                       attn_bias=True, use_rope=True, out_indices=clip_hidden_states, output_cls_projection=False, max_num_tiles=max_num_tiles, in_channels=in_channels,
+                       append_cls_token=True, use_tile_pos_embed=False)
+    if encoder_lora:
+        clip = _vision_encoder(**clip_kwargs, lora_modules=tuple(lora_attn_modules), lora=dict(rank=lora_rank, alpha=lora_alpha, dropout=lora_dropout, use_dora=use_dora),
+                               apply_lora_to_mlp=apply_lora_to_mlp, quantize_base=quantize_base)
+    else:
+        clip = _vision_encoder(**clip_kwargs)
+    if fusion_lora:
+        head = lora_llama4_vision_projection_head(decoder_embed_dim=decoder_embed_dim, clip_embed_dim=clip_embed_dim, projection_embed_dim=projection_embed_dim,
+                                                  apply_lora_to_output=apply_lora_to_output, lora_rank=lora_rank, lora_alpha=lora_alpha, lora_dropout=lora_dropout, use_dora=use_dora,
+                                                  quantize_base=quantize_base, **quantization_kwargs)
+    else:
+        head = llama4_vision_projection_head(decoder_embed_dim=decoder_embed_dim, clip_embed_dim=clip_embed_dim, projection_embed_dim=projection_embed_dim)
+    return Llama4VisionEncoder(clip=clip, projection_head=head)

@@ -27,3 +27,12 @@ def phi3_mini_tokenizer(path: str, special_tokens_path: Optional[str] = None, ma
     special = parse_hf_tokenizer_json(special_tokens_path) if special_tokens_path is not None else None
     template = _get_prompt_template(prompt_template) if prompt_template is not None else None
     return Phi3MiniTokenizer(path=path, special_tokens=special, max_seq_len=max_seq_len, prompt_template=template, truncation_type=truncation_type)
+
+
+def __getattr__(name):
+    # tokenizer classes are imported on first use (they pull in sentencepiece / regex tables)
+    if name == "Phi3MiniTokenizer":
+        from ._tokenizer import Phi3MiniTokenizer
+
+        return Phi3MiniTokenizer
+    raise AttributeError(name)

@@ -34,3 +34,12 @@ def qwen2_tokenizer(path: str, merges_file: str, special_tokens_path: Optional[s
     special = QWEN2_SPECIAL_TOKENS if special_tokens_path is None else parse_hf_tokenizer_json(special_tokens_path)
     template = _get_prompt_template(prompt_template) if prompt_template is not None else None
     return Qwen2Tokenizer(path=path, merges_file=merges_file, special_tokens=special, max_seq_len=max_seq_len, prompt_template=template, truncation_type=truncation_type, **kwargs)
+
+
+def __getattr__(name):
+    # tokenizer classes are imported on first use (they pull in sentencepiece / regex tables)
+    if name == "Qwen2Tokenizer":
+        from ._tokenizer import Qwen2Tokenizer
+
+        return Qwen2Tokenizer
+    raise AttributeError(name)

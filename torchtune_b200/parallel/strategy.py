@@ -253,6 +253,14 @@ class ParallelStrategy(DataParallelEngine):
         from .tp_model import tensor_parallelize
 
         core = model
+        get = cfg.get if hasattr(cfg, "get") else (lambda k, d=None: d)
+        plan_cfg = get("tensor_parallel_plan")
+        if plan_cfg is not None:
+            # the layout is built into the engine; a plan named by the config is checked against it, never silently ignored
+            from .. import config
+            from ..models.llama3._parallelism import validate_tp_plan
+
+            validate_tp_plan(config.instantiate(plan_cfg) if hasattr(plan_cfg, "get") and plan_cfg.get("_component_") else dict(plan_cfg))
         width = core.tok_embeddings.embedding_dim
         tp_group = dp_group = None
         if self.dims.tp != self.world:

@@ -126,3 +126,21 @@ def test_recipe_facing_sharding_and_mask_helpers():
     assert type(sharded.layers[0].attn.q_proj).__name__ == "ShardedLinear"
     tokens = torch.randint(0, 64, (2, 8))
     assert sharded(tokens).shape == (2, 8, 64)
+
+
+def test_tensor_parallel_plan_components_describe_the_built_in_layout():
+    import pytest
+
+    from torchtune_b200.models.llama3 import base_llama_tp_plan
+    from torchtune_b200.models.llama3._parallelism import validate_tp_plan
+    from torchtune_b200.models.llama4 import decoder_only_tp_plan
+
+    plan = base_llama_tp_plan()
+    assert plan["layers.*.attn.q_proj"] == "column_parallel" and plan["layers.*.mlp.w2"] == "row_parallel" and plan["norm"] == "sequence_parallel"
+    validate_tp_plan(plan)
+    validate_tp_plan(base_llama_tp_plan(enable_fp8_training=True))
+    validate_tp_plan(decoder_only_tp_plan())
+    with pytest.raises(ValueError, match="implements"):
+        validate_tp_plan({"layers.*.mlp.w2": "column_parallel"})
+    with pytest.raises(ValueError, match="does not shard"):
+        validate_tp_plan({"layers.*.attn.pos_embeddings": "row_parallel"})

@@ -141,7 +141,8 @@ def test_full_distributed_fp8_tensor_parallel_runs(tmp_path):
     _tune_subprocess(
         ["run", "--nnodes=1", "--nproc_per_node=2", "--master-addr=127.0.0.1", "--master-port=29544", "full_finetune_distributed", "--config", "tiny/llama_full_distributed",
          f"checkpointer.checkpoint_dir={ckpt}", "metric_logger.filename=log.txt", "epochs=3", "max_steps_per_epoch=1", "dataset.num_samples=2", "batch_size=2", f"output_dir={tmp_path / 'out'}",
-         "tensor_parallel_dim=2", "enable_fp8_training=True", "fp8_recipe_name=tensorwise", "optimizer.lr=1e-3"]
+         "tensor_parallel_dim=2", "enable_fp8_training=True", "fp8_recipe_name=tensorwise", "optimizer.lr=1e-3",
+         "tensor_parallel_plan._component_=torchtune_b200.models.llama3.base_llama_tp_plan"]
     )
     losses = read_losses(tmp_path / "out" / "logs" / "log.txt")
     assert len(losses) == 3 and all(math.isfinite(x) for x in losses) and losses[-1] < losses[0]

@@ -54,3 +54,39 @@ def test_grpo_recipe_single_process(tmp_path, tune_path, monkeypatch):
         vals = [float(x) for x in re.findall(rf"\b{name}:(\S+)", text)]
         assert len(vals) == 2 and all(v == v for v in vals), (name, vals)
     assert (out / "epoch_0" / "model-00001-of-00001.safetensors").exists()
+
+
+def test_grpo_chunked_output_loss_matches_unchunked_and_plain_formula():
+    """Chunked logits give the same loss, statistics, log-probs and gradients as the whole tensor, and both equal the formula
+    written out on full log-softmax."""
+    import torch
+
+    from torchtune_b200.dev.grpo import GRPOWithChunkedOutputLoss
+
+    torch.manual_seed(0)
+    bg, length, vocab = 6, 12, 40
+    logits = torch.randn(bg, length, vocab, requires_grad=True)
+    targets = torch.randint(0, vocab, (bg, length))
+    ref = torch.log_softmax(torch.randn(bg, length, vocab), -1).gather(-1, targets[..., None]).squeeze(-1)
+    adv = torch.randn(bg)
+    mask = torch.rand(bg, length) > 0.3
+    mask[:, 0] = True
+    fn = GRPOWithChunkedOutputLoss(num_output_chunks=4, kl_coeff=0.2)
+
+    whole = fn(logits, targets, ref, adv, mask)
+    g_whole, = torch.autograd.grad(whole[0], logits)
+    parts = fn(list(logits.chunk(4, dim=1)), targets, ref, adv, mask)
+    g_parts, = torch.autograd.grad(parts[0], logits)
+    for a, b in zip(whole, parts):
+        torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(g_whole, g_parts, rtol=1e-5, atol=1e-7)
+
+    logp = torch.log_softmax(logits.detach().double(), -1).gather(-1, targets[..., None]).squeeze(-1)
+    d = ref.double() - logp
+    kl = torch.exp(d) - d - 1
+    m = mask.double()
+    per_seq = ((-(adv.double()[:, None] - 0.2 * kl)) * m).sum(1) / m.sum(1)
+    torch.testing.assert_close(whole[0].double(), per_seq.mean(), rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(whole[2].double(), ((kl * m).sum(1) / m.sum(1)).mean(), rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(whole[5].double(), logp, rtol=1e-5, atol=1e-6)
+    assert whole[3].item() == 1.0 and whole[4].item() == 0.0

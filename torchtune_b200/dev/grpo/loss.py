@@ -70,3 +70,44 @@ class GRPOSimpleLoss(_Base):
         policy = _mean(policy_tok, padding_masks, dim=1).mean().detach()
         kl = _mean(kl_tok, padding_masks, dim=1).mean().detach()
         return loss, policy, kl, torch.tensor(1.0), torch.tensor(0.0)
+
+
+class GRPOWithChunkedOutputLoss(nn.Module):
+    """GRPO objective evaluated directly on (chunks of) the policy's logits, so the ``[B·G, L, vocab]`` fp32 log-softmax of a
+    whole response never exists at once (parity: torchtune/dev/grpo/loss.py:270-430).
+
+    Per token: ``-(exp(logp − stop_grad(logp)) · A − β · k3(ref, logp))``; each sequence is averaged over its unmasked tokens and
+    the batch over sequences.  The importance ratio is one by construction (a single policy update per batch of samples), so the
+    clipping range ``epsilon`` is unused and the returned ``ratios`` / ``clipfrac`` are the constants 1 and 0.
+
+    ``forward(pi_logits, targets, ref_logprobs, advantages, padding_masks)`` takes the logits whole or as a list of chunks along
+    the sequence dimension (what a decoder with ``num_output_chunks`` set returns) and gives back
+    ``(loss, policy_loss, kl_loss, ratios, clipfrac, pi_logprobs)``.
+    """
+
+    def __init__(self, num_output_chunks: int = 8, epsilon: float = 0.1, kl_coeff: float = 0.1):
+        super().__init__()
+        self.num_output_chunks, self.epsilon, self.kl_coeff = num_output_chunks, epsilon, kl_coeff
+
+    def compute_per_token_quantities(self, pi_logits_chunk: torch.Tensor, targets_chunk: torch.Tensor, ref_logprobs_chunk: torch.Tensor, advantages: torch.Tensor):
+        """One chunk ``[B·G, c, vocab]`` → per-token ``(loss, policy term, KL estimate, policy log-prob)``, each ``[B·G, c]``."""
+        logp = torch.log_softmax(pi_logits_chunk.float(), dim=-1).gather(-1, targets_chunk.unsqueeze(-1)).squeeze(-1)
+        kl = _k3(ref_logprobs_chunk.detach(), logp)
+        policy = torch.exp(logp - logp.detach()) * advantages[:, None]
+        return -(policy - self.kl_coeff * kl), policy, kl, logp
+
+    def forward(self, pi_logits, targets: torch.Tensor, ref_logprobs: torch.Tensor, advantages: torch.Tensor, padding_masks: Optional[torch.Tensor] = None):
+        chunks = [pi_logits] if isinstance(pi_logits, torch.Tensor) else list(pi_logits)
+        keep = torch.ones_like(targets, dtype=torch.bool) if padding_masks is None else padding_masks
+        n = len(chunks)
+        sums = torch.zeros(3, advantages.numel(), device=chunks[0].device)  # per sequence: loss, policy, kl
+        logps = []
+        for logits, tgt, ref, m in zip(chunks, targets.chunk(n, dim=1), ref_logprobs.chunk(n, dim=1), keep.chunk(n, dim=1)):
+            loss_t, policy_t, kl_t, logp = self.compute_per_token_quantities(logits, tgt, ref, advantages)
+            m = m.to(loss_t.dtype)
+            sums = sums + torch.stack([(loss_t * m).sum(1), (policy_t.detach() * m).sum(1), (kl_t.detach() * m).sum(1)])
+            logps.append(logp)
+        count = keep.sum(1).clamp(min=1e-9).to(sums.dtype)
+        per_seq = (sums / count).mean(1)
+        one = torch.ones((), device=sums.device)
+        return per_seq[0], per_seq[1].detach(), per_seq[2].detach(), one, torch.zeros_like(one), torch.cat(logps, dim=1)

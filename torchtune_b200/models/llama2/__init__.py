@@ -51,3 +51,5 @@ def __getattr__(name):
 
         return Llama2ChatTemplate
     raise AttributeError(name)
+
+from .._factory import scale_hidden_dim_for_mlp  # noqa: E402,F401

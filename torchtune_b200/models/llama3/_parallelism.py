@@ -61,3 +61,14 @@ def validate_tp_plan(plan: Optional[Dict[str, str]]) -> None:
             raise ValueError(f"tensor_parallel_plan names {key!r}, which the tensor-parallel engine does not shard")
         if str(style).replace("+fp8", "") != want:
             raise ValueError(f"tensor_parallel_plan wants {key!r} as {style!r}; the engine implements {want!r}")
+
+
+def decoder_only_tp_training_plan(model: Optional[nn.Module] = None, *, enable_fp8_training: bool = False) -> Dict[str, str]:
+    """Training plan of an early-fusion model's decoder (sequence-sharded activations)."""
+    return decoder_only_tp_plan(model, enable_fp8_training=enable_fp8_training)
+
+
+def decoder_only_tp_inference_plan(model: Optional[nn.Module] = None) -> Dict[str, str]:
+    """Inference plan: the same weight split; activations stay replicated and every row-parallel projection is followed by an
+    all-reduce (``TPDecoder.forward_inference``), so norms and embeddings are plain replicated modules."""
+    return {k: ("replicated" if v in (SEQUENCE, REPLICATED_ROWS) else v) for k, v in decoder_only_tp_plan(model).items()}

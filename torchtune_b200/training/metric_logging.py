@@ -30,6 +30,19 @@ def save_config(config: DictConfig) -> Path:
         return Path()
 
 
+def flatten_dict(d: Dict[str, Any], *, sep: str = ".", parent_key: str = "") -> Dict[str, Any]:
+    """``{"a": {"b": 1}, "c": 2}`` → ``{"a.b": 1, "c": 2}`` (dictionaries inside lists are left as they are); used to hand a nested
+    config to loggers that take flat hyper-parameter tables."""
+    out: Dict[str, Any] = {}
+    for key, value in d.items():
+        name = f"{parent_key}{sep}{key}" if parent_key else key
+        if isinstance(value, dict):
+            out.update(flatten_dict(value, sep=sep, parent_key=name))
+        else:
+            out[name] = value
+    return out
+
+
 def _scalar(v: Scalar) -> float:
     return v.item() if isinstance(v, torch.Tensor) else v
 

@@ -117,3 +117,8 @@ def is_sm100(device: Optional[torch.device] = None) -> bool:
     if not torch.cuda.is_available():
         return False
     return torch.cuda.get_device_capability(device)[0] == 10
+
+
+def is_torch_hpu_available() -> bool:
+    """This build targets NVIDIA B200 only: there is no Habana path."""
+    return False

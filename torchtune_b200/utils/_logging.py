@@ -52,3 +52,22 @@ def deprecated(msg: str = "") -> Callable[[T], T]:
         return wrapper
 
     return decorator
+
+
+def deprecate_parameter(param_name: str, msg: str = "") -> Callable[[T], T]:
+    """Decorator that warns (once) when the decorated callable is given the keyword argument ``param_name``."""
+
+    @functools.lru_cache(maxsize=1)
+    def _warn(obj) -> None:
+        warnings.warn(f"{param_name} is deprecated for {obj.__name__} and will be removed in future versions. {msg}", category=FutureWarning, stacklevel=3)
+
+    def decorator(obj):
+        @functools.wraps(obj)
+        def wrapper(*args, **kwargs):
+            if param_name in kwargs:
+                _warn(obj)
+            return obj(*args, **kwargs)
+
+        return wrapper
+
+    return decorator

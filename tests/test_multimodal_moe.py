@@ -57,6 +57,9 @@ def test_permute_indices_match_loop_oracle():
         start = counts.cumsum(0) - counts
         want = fill_indices_cpu(counts, start, offsets - sizes, experts, ranks, 256)
         assert torch.equal(perm, want)
+        from torchtune_b200.modules.moe.indices import fill_indices_wrapper
+
+        assert torch.equal(fill_indices_wrapper(counts, start, offsets - sizes, experts, ranks, 256), want)
         assert (sizes % align == 0).all() and (sizes >= counts.view(ranks, experts).sum(0)).all()
 
 

@@ -60,3 +60,26 @@ def fill_indices_cpu(tokens_per_expert_group: torch.Tensor, start_index_values: 
                 out[w : w + n] = torch.arange(s, s + n, dtype=torch.int32)
             w += n
     return out
+
+
+def fill_indices_wrapper(tokens_per_expert_group: torch.Tensor, start_index_values: torch.Tensor, write_offsets: torch.Tensor, experts_per_rank: int, num_ranks: int, total_size: int,
+                         block_size: int = 128, max_blocks: int = 1024) -> torch.Tensor:
+    """Fill the permutation from precomputed run starts and per-expert write offsets, on the tensors' own device and without a
+    host loop (the reference launches a Triton kernel here, torchtune/modules/moe/indices.py:75-108; ``block_size`` and
+    ``max_blocks`` are its launch parameters and have no meaning for this vectorised form).  Run ``(r, e)`` — ``tokens[r·E + e]``
+    consecutive source rows from ``start_index_values[r·E + e]`` — is written after the runs of lower ranks for the same expert,
+    beginning at ``write_offsets[e]``; unwritten slots stay ``-1``."""
+    dev = tokens_per_expert_group.device
+    counts = tokens_per_expert_group.to(torch.int64).view(num_ranks, experts_per_rank)
+    starts = start_index_values.to(torch.int64).view(num_ranks, experts_per_rank)
+    dst0 = write_offsets.to(torch.int64).view(1, experts_per_rank) + (counts.cumsum(0) - counts)
+    out = torch.full((total_size,), -1, dtype=torch.int32, device=dev)
+    run_len = counts.reshape(-1)
+    total = int(run_len.sum())
+    if total:
+        run_id = torch.repeat_interleave(torch.arange(run_len.numel(), device=dev), run_len)
+        pos = torch.arange(total, device=dev) - torch.repeat_interleave(run_len.cumsum(0) - run_len, run_len)
+        dst = dst0.reshape(-1)[run_id] + pos
+        keep = dst < total_size
+        out[dst[keep]] = (starts.reshape(-1)[run_id] + pos)[keep].to(torch.int32)
+    return out

@@ -46,9 +46,9 @@ def _tiny_ckpt(tmp_path):
     return ckpt
 
 
-def _tune(args, port, timeout=600):
+def _tune(args, port, timeout=600, nproc=2):
     env = dict(os.environ, PYTHONPATH=f"{ROOT}:{ROOT / 'tests'}", MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0")
-    cmd = [sys.executable, str(ROOT / "tune"), "run", "--nnodes=1", "--nproc_per_node=2", "--master-addr=127.0.0.1", f"--master-port={port}"] + args
+    cmd = [sys.executable, str(ROOT / "tune"), "run", "--nnodes=1", f"--nproc_per_node={nproc}", "--master-addr=127.0.0.1", f"--master-port={port}"] + args
     res = subprocess.run(cmd, cwd=str(ROOT), env=env, capture_output=True, text=True, timeout=timeout)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
 
@@ -127,3 +127,43 @@ def test_lora_over_sharded_base_weights_on_two_gpus(tmp_path):
     for a, b in zip(res["dp"], res["z3"]):
         assert abs(a - b) < 0.02 * abs(a), res
     assert (tmp_path / "z3" / "epoch_0" / "adapter_model.safetensors").exists()
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 4, reason="needs 4 GPUs")
+def test_dp_times_tp_mesh_on_four_gpus(tmp_path):
+    """tensor_parallel_dim=2 on four GPUs (two tensor-parallel groups of consecutive ranks, two model replicas) follows the loss
+    curve of plain data parallelism on the same global batch."""
+    ckpt = _tiny_ckpt(tmp_path)
+    res = {}
+    for name, port, extra in (("dp", 29601, ["batch_size=2"]), ("mesh", 29603, ["batch_size=4", "tensor_parallel_dim=2"])):
+        out = tmp_path / name
+        _tune(["full_finetune_distributed", "--config", "tiny/llama_full_distributed", f"checkpointer.checkpoint_dir={ckpt}", f"output_dir={out}", "metric_logger.filename=log.txt",
+               "device=cuda", "dtype=bf16", "max_steps_per_epoch=4", "dataset.num_samples=64", "optimizer.lr=1e-3"] + extra, port, nproc=4)
+        res[name] = _losses(out / "logs" / "log.txt")
+    assert len(res["mesh"]) == 4
+    for a, b in zip(res["dp"], res["mesh"]):
+        assert abs(a - b) < 0.02 * abs(a), res
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 4, reason="needs 4 GPUs")
+def test_dp_times_ep_mesh_on_four_gpus(tmp_path):
+    """expert_parallel_dim=2 on four GPUs (two expert-parallel groups side by side) follows plain data parallelism."""
+    from torchtune_b200.models.llama4 import llama4_decoder
+
+    ckpt = tmp_path / "ckpt"
+    ckpt.mkdir()
+    torch.manual_seed(0)
+    model = llama4_decoder(vocab_size=1024, num_layers=2, num_heads=4, num_kv_heads=2, embed_dim=128, hidden_dim=256, max_seq_len=256, num_experts=4, experts_per_token=2, rope_base=500000)
+    with torch.no_grad():
+        for prm in model.parameters():
+            prm.copy_(torch.randn_like(prm) * 0.05)
+    torch.save(model.state_dict(), ckpt / "model.pt")
+    res = {}
+    for name, port, extra in (("dp", 29605, []), ("mesh", 29607, ["expert_parallel_dim=2"])):
+        out = tmp_path / name
+        _tune(["full_finetune_distributed", "--config", "tiny/llama4_moe_full_distributed", f"checkpointer.checkpoint_dir={ckpt}", f"output_dir={out}", "metric_logger.filename=log.txt",
+               "device=cuda", "dtype=bf16", "max_steps_per_epoch=3", "dataset.num_samples=32", "optimizer.lr=1e-3"] + extra, port, nproc=4)
+        res[name] = _losses(out / "logs" / "log.txt")
+    assert len(res["mesh"]) == 3
+    for a, b in zip(res["dp"], res["mesh"]):
+        assert abs(a - b) < 0.02 * abs(a), res

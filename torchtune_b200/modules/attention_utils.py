@@ -30,3 +30,14 @@ def create_block_causal_mask(seq_lens: List[torch.Tensor]) -> torch.Tensor:
 def packed_block_causal_mask(seq_lens: List[torch.Tensor]) -> AttentionMask:
     """Block-causal mask of a packed batch in the form the attention kernel consumes (document ids per token)."""
     return AttentionMask.from_seq_lens(seq_lens)
+
+
+def causal_mask_flex(b, h, q_idx, kv_idx):
+    """Mask predicate ``(batch, head, query index, key index) → visible?`` of a plain causal mask — the calling convention of
+    flex-attention mask mods, usable with index tensors (broadcasting) to materialise a mask for the eager path."""
+    return q_idx >= kv_idx
+
+
+def kv_offset_mask_flex(b, h, q_idx, kv_idx, offset):
+    """Mask predicate for decoding one token at cache position ``offset``: every key up to and including it is visible."""
+    return kv_idx <= offset

@@ -217,7 +217,7 @@ def run_ours(args) -> dict:
     clocks = sampler.stop() if rank == 0 else {}
     check_device_errors()
     h2d = sum(t.numel() * t.element_size() for t in host_batches[0].values())
-    peak_gib = torch.cuda.max_memory_allocated() / 2**30
+    peak_gib = (torch.cuda.max_memory_allocated() + par.PeerBuffer.peak_bytes) / 2**30  # torch's allocator + cudaMalloc'ed peer buffers
     final_loss = float(losses[-1]) if losses else float("nan")
     value = tokens_per_step * args.steps / t_kernel
     out = {

@@ -156,9 +156,11 @@ def test_penalty_mask_and_whiten():
     assert rlhf.get_reward_penalty_mask(pad, lens, penalise_no_eos=True).tolist() == [False, True]
     assert rlhf.get_reward_penalty_mask(pad, lens, penalise_no_eos=False, min_response_length=3).tolist() == [True, False]
     x = torch.randn(4, 9) * 3 + 2
-    w = rlhf.whiten(x)
+    w = rlhf.whiten(x, shift_mean=False)
     assert w.mean().abs() < 1e-5 and w.var().item() == pytest.approx(1.0, abs=1e-4)
-    assert rlhf.whiten(x, shift_mean=False).mean().item() == pytest.approx(x.mean().item(), abs=1e-4)
+    assert rlhf.whiten(x).mean().item() == pytest.approx(x.mean().item(), abs=1e-4)  # default adds the mean back (reference semantics)
+    m = torch.ones_like(x, dtype=torch.bool)
+    assert torch.allclose(rlhf.whiten(x, m), rlhf.whiten(x), atol=1e-5)  # second positional argument is the mask
 
 
 def test_reward_codec_roundtrip():

@@ -61,6 +61,28 @@ def test_noalloc_matches_regular_entry_point_twice():
     _run_both(L, 300, 8192, seed=3)
 
 
+def test_noalloc_without_scale_matches_regular_entry_point():
+    """Weight-less norm: no partial sums, no finalize pass, ``dscale`` may be null."""
+    from torchtune_b200.ops._lib import check, lib, stream_ptr
+
+    L = lib()
+    fn = L.ttb_rmsnorm_bwd_noalloc
+    vp = ctypes.c_void_p
+    fn.argtypes = [vp, vp, vp, vp, vp, vp, ctypes.c_int, ctypes.c_int, vp]
+    fn.restype = ctypes.c_int
+    for rows, D, seed in ((513, 1024, 4), (64, 4096, 5)):
+        x, dy, _ = _inputs(rows, D, seed)
+        y = torch.empty_like(x)
+        rstd = torch.empty(rows, dtype=torch.float32, device="cuda")
+        check(L.ttb_rmsnorm_fwd(x.data_ptr(), None, y.data_ptr(), rstd.data_ptr(), rows, D, 1e-5, stream_ptr()), "fwd")
+        dx_ref = torch.empty_like(x)
+        check(L.ttb_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), None, rstd.data_ptr(), dx_ref.data_ptr(), None, rows, D, stream_ptr()), "bwd")
+        dx = torch.empty_like(x)
+        assert fn(dy.data_ptr(), x.data_ptr(), None, rstd.data_ptr(), dx.data_ptr(), None, rows, D, stream_ptr()) == 0
+        torch.cuda.synchronize()
+        torch.testing.assert_close(dx.float(), dx_ref.float(), rtol=2e-2, atol=2e-2)
+
+
 def test_noalloc_rejects_oversized_rows():
     from torchtune_b200.ops._lib import lib
 

@@ -304,7 +304,7 @@ class PPOTrainer:
                 traj_time = time.perf_counter() - t0
                 rewards, kl, kl_rewards = rlhf.get_rewards_ppo(trajectory.scores, trajectory.logprobs, trajectory.ref_logprobs, self._kl_coeff, trajectory.value_seq_idxs)
                 if self._whiten_rewards:
-                    rewards = rlhf.whiten(rewards, shift_mean=False, mask=~trajectory.response_padding_masks)
+                    rewards = rlhf.whiten(rewards, ~trajectory.response_padding_masks, shift_mean=True)  # unit variance, mean kept
                 advantages, returns = rlhf.estimate_advantages(trajectory.values, rewards, self._gamma, self._lmbda, masks=~trajectory.response_padding_masks)
                 t0 = time.perf_counter()
                 stats: List[PPOStats] = []

@@ -3,11 +3,17 @@
 Every operator has two statements: the sm_100a CUDA kernel (``_cuda``,
 compiled from ``csrc/``) used for CUDA tensors, and the plain PyTorch one in
 :mod:`.reference` used on CPU and as the numerical oracle.  On a CUDA device a
-missing extension is an error, never a silent fallback.
+missing extension is an error.  A bf16 CUDA call whose *shape or options* the
+kernels do not cover takes the PyTorch statement instead; every such call is
+counted in :data:`fallback_counts`, logged once per (operator, reason), and raises
+:class:`KernelFallbackError` when ``TTB_STRICT=1`` (set by the benchmark and the
+GPU tests) so a configuration cannot run on library or eager math unnoticed.
 """
 from __future__ import annotations
 
-from typing import Optional, Tuple
+import os
+import warnings
+from typing import Dict, Optional, Tuple
 
 import torch
 import torch.nn.functional as F
@@ -37,6 +43,26 @@ __all__ = [
 
 _FORCE_REFERENCE = False
 
+fallback_counts: Dict[Tuple[str, str], int] = {}
+
+
+class KernelFallbackError(RuntimeError):
+    """A bf16 CUDA operator call would have left the sm_100a kernels while ``TTB_STRICT=1``."""
+
+
+def _fallback(op: str, reason: str, t: torch.Tensor) -> None:
+    """Record that ``op`` runs its PyTorch statement for bf16 CUDA input ``t`` (no-op for CPU / fp32 tensors and inside
+    :class:`use_reference_ops`, where the PyTorch statement is the intended one)."""
+    if not (t.is_cuda and t.dtype == torch.bfloat16) or _FORCE_REFERENCE:
+        return
+    key = (op, reason)
+    n = fallback_counts.get(key, 0)
+    fallback_counts[key] = n + 1
+    if os.environ.get("TTB_STRICT", "0") == "1":
+        raise KernelFallbackError(f"ops.{op}: {reason} — not covered by the sm_100a kernels (TTB_STRICT=1 forbids the PyTorch fallback)")
+    if n == 0:
+        warnings.warn(f"ops.{op}: {reason}; running the PyTorch statement instead of the sm_100a kernel", RuntimeWarning, stacklevel=3)
+
 
 class use_reference_ops:
     """Context manager that forces the PyTorch statements (used by parity tests)."""
@@ -64,7 +90,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     if _native(x) and weight.dtype == torch.bfloat16:
         from . import _cuda
 
-        return _cuda.linear(x, weight, bias)
+        if x.shape[-1] % 8 == 0 and weight.shape[0] % 8 == 0:
+            return _cuda.linear(x, weight, bias)
+        _fallback("linear", f"K={x.shape[-1]} or N={weight.shape[0]} is not a multiple of 8 (TMA row pitch)", x)
     return F.linear(x, weight, bias)
 
 
@@ -88,6 +116,7 @@ def lora_linear(x: torch.Tensor, xd: torch.Tensor, weight: torch.Tensor, bias: O
         from . import _cuda
 
         return _cuda.lora_linear(x, xd, weight, bias, lora_a, lora_b, scale)
+    _fallback("lora_linear", f"rank {rank} / K / N not multiples of 8 or mixed dtypes", x)
     return F.linear(x, weight, bias) + scale * F.linear(F.linear(xd, lora_a), lora_b)
 
 
@@ -109,6 +138,8 @@ def grouped_matmul(x: torch.Tensor, w: torch.Tensor, counts: torch.Tensor) -> to
         from . import _cuda
 
         return _cuda.grouped_matmul(x, w, counts)
+    if x.shape[0] > 0:
+        _fallback("grouped_matmul", "non-contiguous operands, host-side counts or K / N not multiples of 8", x)
     outs, start = [], 0
     for e, n in enumerate(counts.tolist()):
         if n:
@@ -123,6 +154,8 @@ def matmul(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
         from . import _cuda
 
         return _cuda.matmul_kn(x, w)
+    if x.numel() > 0:
+        _fallback("matmul", "operands are not contiguous 2-D matrices with K / N multiples of 8", x)
     return x @ w
 
 
@@ -176,6 +209,7 @@ def attention(
         from . import _cuda
 
         return _cuda.attention(q, k, v, mask, scale, softcap)
+    _fallback("attention", _attention_fallback_reason(q, k, mask, dropout_p), q)
     return reference.attention(
         q,
         k,
@@ -189,6 +223,16 @@ def attention(
         softcap=softcap,
         dropout_p=dropout_p,
     )
+
+
+def _attention_fallback_reason(q, k, mask, dropout_p) -> str:
+    if mask.bool_mask is not None:
+        return "dense boolean mask"
+    if dropout_p != 0.0:
+        return "attention dropout"
+    if q.shape[-1] not in (64, 128):
+        return f"head_dim {q.shape[-1]}"
+    return f"query length {q.shape[1]} differs from key length {k.shape[1]}"
 
 
 def linear_cross_entropy(

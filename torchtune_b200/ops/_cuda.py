@@ -291,10 +291,16 @@ class _GroupedMatmul(torch.autograd.Function):
             # one launch for all experts; the ragged reduction ranges come from the device-resident counts (no host read)
             E, K, N = w.shape
             xc = x if (x.stride(1) == 1 and x.stride(0) % 8 == 0) else x.contiguous()
-            dw = torch.empty_like(w)
+            owner = grad_window_owner(w)  # expert stack in a flat store: the epilogue writes its window of the flat gradient buffer
+            accumulate = 0
+            if owner is not None:
+                out, dw = owner._grad_buffer, None
+                accumulate, owner._grad_written = int(bool(owner._grad_written)), True
+            else:
+                out = dw = torch.empty_like(w)
             cnt = counts.to(torch.int64).contiguous()
-            check(lib().ttb_gemm_grouped_wgrad_bf16(xc.data_ptr(), dy.data_ptr(), dw.data_ptr(), cnt.data_ptr(), x.shape[0], E, K, N, xc.stride(0), dy.stride(0),
-                                                    N, K * N, 0, err_word(x.device).data_ptr(), stream_ptr()), "gemm_grouped_wgrad")
+            check(lib().ttb_gemm_grouped_wgrad_bf16(xc.data_ptr(), dy.data_ptr(), out.data_ptr(), cnt.data_ptr(), x.shape[0], E, K, N, xc.stride(0), dy.stride(0),
+                                                    N, K * N, accumulate, err_word(x.device).data_ptr(), stream_ptr()), "gemm_grouped_wgrad")
         return dx, dw, None
 
 
@@ -746,8 +752,9 @@ class _LinearCE(torch.autograd.Function):
 
 def linear_cross_entropy(hidden, weight, labels, ignore_index: int, num_chunks: int):
     if hidden.shape[-1] % 8 or weight.shape[0] % 8:
-        from . import reference
+        from . import _fallback, reference
 
+        _fallback("linear_cross_entropy", f"width {hidden.shape[-1]} or vocabulary {weight.shape[0]} is not a multiple of 8", hidden)
         return reference.linear_cross_entropy(hidden, weight, labels, ignore_index, num_chunks)
     return _LinearCE.apply(hidden, weight, labels, ignore_index, num_chunks)
 

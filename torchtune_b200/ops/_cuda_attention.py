@@ -77,8 +77,9 @@ def attention(q, k, v, mask: AttentionMask, scale: Optional[float], softcap: flo
     b, s, hq, d = q.shape
     structured = mask.doc_ids is not None or mask.chunk > 0 or mask.window > 0
     if softcap > 0 or (structured and not mask.causal) or hq % k.shape[2]:
-        from . import reference
+        from . import _fallback, reference
 
+        _fallback("attention", "soft-capping" if softcap > 0 else ("structured mask without causality" if structured and not mask.causal else "query heads not a multiple of key heads"), q)
         return reference.attention(q, k, v, causal=mask.causal, doc_ids=mask.doc_ids, chunk=mask.chunk, window=mask.window, scale=scale, softcap=softcap)
     lo = lower_bounds(mask, b, s, q.device)
     return _FlashAttention.apply(q, k, v, lo, (1.0 / math.sqrt(d)) if scale is None else scale, mask.causal)

@@ -16,6 +16,9 @@
 //     rows.  Larger D is refused with the "size beyond a static limit" code (-3).
 //   * The scratch array holds TTB_RMSNORM_NOALLOC_MAX_CTAS x TTB_RMSNORM_NOALLOC_MAX_D floats
 //     (4 MiB).  Every GPU that loads the library carries it until the process exits.
+//   * The library links its own copy of the CUDA runtime, whose "current device" is per host thread and starts at
+//     device 0.  A caller working on another device binds the calling thread first with ttb_ensure_device(dev);
+//     otherwise the lookup below returns device 0's copy of the array and the launch goes there.
 //   * The first call on a device looks up the array's device address (cudaGetSymbolAddress)
 //     and remembers it; make that first call outside of any stream capture.
 //   * Nothing in the scratch needs to start at zero: each call overwrites every partial row it

@@ -58,7 +58,7 @@ class FlatParameters:
     of each.  ``bucket_keys[b]`` is the module path of the decoder layer a bucket belongs to
     (``None`` for the parameters before / after the layers)."""
 
-    def __init__(self, params: List[Tuple[str, nn.Parameter]], world: int, device: torch.device, group=None):
+    def __init__(self, params: List[Tuple[str, nn.Parameter]], world: int, device: torch.device, group=None, min_bucket_numel: int = 0):
         dtypes = {p.dtype for _, p in params}
         if len(dtypes) != 1:
             raise ValueError(f"all trainable parameters must share one dtype, found {dtypes}")
@@ -74,6 +74,8 @@ class FlatParameters:
         cursor, start, prev_key = 0, 0, object()
         for name, p in params:
             key = _bucket_key(name)
+            if key != prev_key and self.bucket_params and cursor - start < min_bucket_numel:
+                key = prev_key  # the running bucket is still small (e.g. only norm scales): the next layer joins it
             if key != prev_key and self.bucket_params:  # close the running bucket at a multiple of 8·world
                 cursor = start + _round_up(cursor - start, unit)
                 self.buckets.append((start, cursor - start))
@@ -165,8 +167,8 @@ class ShardedAdamW:
     and the fused kernel distributes the result.  ``step`` handles all buckets that were not
     already processed during backward (:meth:`begin_step` / :meth:`process_bucket`)."""
 
-    def __init__(self, flat: FlatParameters, rank: int, world: int, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 1e-2):
-        self.flat, self.rank, self.world = flat, rank, world
+    def __init__(self, flat: FlatParameters, rank: int, world: int, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 1e-2, group=None):
+        self.flat, self.rank, self.world, self.group = flat, rank, world, group
         self.param_groups = [dict(lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay, params=flat.params)]
         dev = flat.flat_param.device
         self.exp_avg = torch.zeros(flat.shard, dtype=flat.dtype, device=dev)
@@ -199,11 +201,14 @@ class ShardedAdamW:
         """Moments of the whole model as one CPU tensor each, in flat-parameter order, plus the parameter
         layout, so a checkpoint written at one world size can be read at another."""
         flat = self.flat
+        group = group if group is not None else self.group
         out = {}
         for key, shard in (("exp_avg", self.exp_avg), ("exp_avg_sq", self.exp_avg_sq)):
             if self.world > 1:
-                parts = [torch.empty_like(shard) for _ in range(self.world)]
-                dist.all_gather(parts, shard, group=group)
+                src = shard.float() if (shard.device.type == "cpu" and shard.dtype == torch.bfloat16) else shard  # gloo has no bf16 all_gather
+                parts = [torch.empty_like(src) for _ in range(self.world)]
+                dist.all_gather(parts, src, group=group)
+                parts = [p.to(shard.dtype) for p in parts]
             else:
                 parts = [shard]
             out[key] = flat.shards_to_full([p.cpu() for p in parts]) if is_rank_zero else None
@@ -292,51 +297,89 @@ class ShardedAdamW:
             "dp_reduce_adamw_bcast",
         )
 
-    def step(self, grad_scale: Union[float, torch.Tensor] = 1.0, max_grad_norm: Optional[float] = None, group=None) -> None:
-        if self._open is None:
-            self.begin_step(grad_scale, max_grad_norm)
+    # The step in three collective-free pieces, so that several stores with different reduction groups can share one clipping
+    # norm (:class:`~torchtune_b200.parallel.stores.MultiStoreAdamW`); :meth:`step` strings them together for a single store.
+    def reduce_all(self, group=None) -> None:
+        """Sum every bucket over the store's ranks.  Without clipping the CUDA kernels also update and broadcast here."""
+        st = self._open
+        if not self.flat.flat_param.is_cuda:
+            self._host_reduce(st, group if group is not None else self.group)
+            return
+        for b in range(len(self.flat.buckets)):
+            self.process_bucket(b)
+
+    def local_sumsq(self) -> torch.Tensor:
+        """Sum of squares of the reduced (unscaled) gradient over *this rank's* slices; summed over the store's ranks it is the
+        squared norm of the whole store."""
+        st = self._open
+        if not self.flat.flat_param.is_cuda:
+            return st["gsum"][st["mine"]].pow(2).sum()
+        return self._partials.sum()
+
+    def finish(self, total_sumsq: Optional[torch.Tensor]) -> None:
+        """Apply the update; ``total_sumsq`` is the squared global gradient norm (required when the step clips)."""
         st = self._open
         self.last_grad_norm = None
-        flat = self.flat
         try:
+            flat = self.flat
+            if st["scale_dev"] is not None:
+                s = st["scale_dev"].to(flat.flat_param.device)
+            else:
+                s = torch.tensor([st["scale_host"]], dtype=torch.float32, device=flat.flat_param.device)
+            coef = None
+            if st["clip"] is not None:
+                norm = total_sumsq.to(torch.float32).sqrt() * s
+                self.last_grad_norm = norm.reshape(())
+                coef = (torch.clamp(float(st["clip"]) / (norm + 1e-6), max=1.0) * s).reshape(1).float()
             if not flat.flat_param.is_cuda:
-                self._step_host(grad_scale, max_grad_norm, group)
-                return
-            for b in range(len(flat.buckets)):
-                self.process_bucket(b)
-            if st["clip"] is None:
-                return
-            sumsq = self._partials.sum()
-            if self.world > 1:
-                dist.all_reduce(sumsq, group=group)
-            s = st["scale_dev"] if st["scale_dev"] is not None else torch.tensor([st["scale_host"]], device=sumsq.device)
-            norm = sumsq.sqrt() * s
-            self.last_grad_norm = norm.reshape(())
-            coef = (torch.clamp(float(st["clip"]) / (norm + 1e-6), max=1.0) * s).reshape(1).float()
-            for b in range(len(flat.buckets)):
-                self._launch(b, 2, st, coef, 1.0)
+                self._host_apply(st, float((coef if coef is not None else s).item()))
+            elif coef is not None:
+                for b in range(len(flat.buckets)):
+                    self._launch(b, 2, st, coef, 1.0)
         finally:
             self._open = None
 
-    def _step_host(self, grad_scale, max_grad_norm, group) -> None:
-        """gloo implementation of the same algorithm (sum of all ranks' gradients in fp32,
-        update of the owned slices, broadcast of the result)."""
-        flat, g = self.flat, self.param_groups[0]
+    def step(self, grad_scale: Union[float, torch.Tensor] = 1.0, max_grad_norm: Optional[float] = None, group=None) -> None:
+        if self._open is None:
+            self.begin_step(grad_scale, max_grad_norm)
+        group = group if group is not None else self.group
+        try:
+            self.reduce_all(group)
+            total = None
+            if self._open["clip"] is not None:
+                total = self.local_sumsq()
+                if self.world > 1:
+                    dist.all_reduce(total, group=group)
+        except BaseException:
+            self._open = None
+            raise
+        self.finish(total)
+
+    def _host_reduce(self, st: Dict[str, Any], group) -> None:
+        """gloo statement of the reduction: fp32 sum of all ranks' gradients; ``mine`` indexes this rank's slices."""
+        flat = self.flat
         gsum = flat.flat_grad.float()
         if self.world > 1:
             dist.all_reduce(gsum, group=group)
-        scale = float(grad_scale) if not isinstance(grad_scale, torch.Tensor) else float(grad_scale.item())
-        if max_grad_norm is not None:
-            norm = gsum.norm() * scale
-            self.last_grad_norm = norm
-            scale *= float(torch.clamp(float(max_grad_norm) / (norm + 1e-6), max=1.0))
+        st["gsum"] = gsum
+        st["mine"] = torch.cat([torch.arange(begin, begin + count) for begin, count, _ in (flat.owned(b, self.rank) for b in range(len(flat.buckets)))])
+        st["group"] = group
+
+    def _host_apply(self, st: Dict[str, Any], scale: float) -> None:
+        """gloo statement of update + broadcast: AdamW on the owned slices, then every rank collects all slices."""
+        flat, g = self.flat, self.param_groups[0]
         b1, b2 = g["betas"]
-        mine = torch.cat([torch.arange(begin, begin + count) for begin, count, _ in (flat.owned(b, self.rank) for b in range(len(flat.buckets)))])
+        mine = st["mine"]
         new = flat.flat_param[mine].clone()
-        _ref.adamw_step(new, gsum[mine], self.exp_avg, self.exp_avg_sq, self.step_count, float(g["lr"]), b1, b2, g["eps"], g["weight_decay"], scale)
+        _ref.adamw_step(new, st["gsum"][mine], self.exp_avg, self.exp_avg_sq, self.step_count, float(g["lr"]), b1, b2, g["eps"], g["weight_decay"], scale)
         if self.world > 1:
             gathered = [torch.empty_like(new) for _ in range(self.world)]
-            dist.all_gather(gathered, new, group=group)
+            if new.dtype == torch.bfloat16:  # gloo has no bf16 all_gather
+                parts = [torch.empty(new.shape, dtype=torch.float32) for _ in range(self.world)]
+                dist.all_gather(parts, new.float(), group=st["group"])
+                gathered = [p.to(new.dtype) for p in parts]
+            else:
+                dist.all_gather(gathered, new, group=st["group"])
             flat.flat_param.copy_(flat.shards_to_full(gathered))
         else:
             flat.flat_param[mine] = new

@@ -39,6 +39,10 @@ def _declare(L) -> None:
 
 _GUARD_BYTE = 0xA5
 
+# Pass as ``group`` to get a buffer that no peer maps (a store whose reduction group is this rank alone, e.g. the
+# tensor-parallel shards when there is a single model replica) while the job has a default process group.
+SOLO = object()
+
 
 def _guard_bytes() -> int:
     """``TTB_PEER_GUARD_BYTES=<n>`` (debug aid, default 0) surrounds every peer buffer with ``n`` bytes (rounded up to 256) of a
@@ -48,14 +52,20 @@ def _guard_bytes() -> int:
 
 
 class PeerBuffer:
+    # Device bytes held by live peer buffers of this process and their high-water mark.  These allocations bypass torch's
+    # caching allocator, so ``torch.cuda.max_memory_allocated()`` does not see them; memory reports add ``peak_bytes``.
+    live_bytes = 0
+    peak_bytes = 0
+
     def __init__(self, nbytes: int, device: torch.device, group: Optional[dist.ProcessGroup] = None):
         self.nbytes = int(nbytes)
         self.device = device
         self.guard = _guard_bytes() if device.type == "cuda" else 0
         self._base_ptr = 0
         self._whole: Optional[torch.Tensor] = None
-        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
-        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        solo = group is SOLO or not dist.is_initialized()
+        self.world = 1 if solo else dist.get_world_size(group)
+        self.rank = 0 if solo else dist.get_rank(group)
         self._opened: List[int] = []
         if device.type != "cuda":
             # host stand-in used by the CPU (gloo) implementation of the same algorithms
@@ -72,6 +82,8 @@ class PeerBuffer:
             raise KernelError(f"cudaMalloc of {self.nbytes + 2 * g} bytes for a peer buffer failed")
         self._base_ptr = out.value
         self.local_ptr = out.value + g
+        PeerBuffer.live_bytes += self.nbytes + 2 * g
+        PeerBuffer.peak_bytes = max(PeerBuffer.peak_bytes, PeerBuffer.live_bytes)
         self._whole = torch.as_tensor(_RawCudaMemory(self._base_ptr, self.nbytes + 2 * g), device=device)
         self._local = self._whole[g : g + self.nbytes]
         self._local.zero_()
@@ -133,4 +145,5 @@ class PeerBuffer:
             if self.local_ptr:
                 self._local = self._whole = None
                 L.ttb_ipc_free(self._base_ptr)
+                PeerBuffer.live_bytes -= self.nbytes + 2 * self.guard
                 self.local_ptr = self._base_ptr = 0

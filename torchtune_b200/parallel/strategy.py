@@ -192,6 +192,8 @@ class ParallelStrategy(DataParallelEngine):
         self.tp = None  # TensorParallelContext, created in shard_model
         self.ep = None  # ExpertParallelContext, created in shard_model
         self.cp = None  # ContextParallelContext, created in shard_model
+        self._replica_group = None  # ranks holding the same tensor- / expert-parallel shard (None: a single replica)
+        self._stores = None  # MultiStoreAdamW of a sharded model (fused optimizer over two flat stores)
         self.zero3 = None  # ShardedWeightContext when `shard_parameters: True` (linear weights sharded over the ranks)
         self._shard_parameters = bool(get("shard_parameters", False))
         if self._shard_parameters and (self.dims.tp_enabled or self.ep_dim > 1 or self.dims.cp_enabled):
@@ -272,6 +274,7 @@ class ParallelStrategy(DataParallelEngine):
         ac = any(isinstance(layer, CheckpointedLayer) for layer in core.layers)
         out = tensor_parallelize(core, self.tp, activation_checkpointing=ac)
         out.set_data_parallel_group(dp_group, self.world // self.dims.tp)
+        self._replica_group = dp_group
         return out
 
     def _shard_model_ep(self, model: nn.Module, cfg) -> nn.Module:
@@ -303,6 +306,7 @@ class ParallelStrategy(DataParallelEngine):
                     replica_group = handle
         self.ep = ExpertParallelContext(self.device, ep_group, num_experts=router.num_experts, dim=router.dim, max_pairs=tokens * router.experts_per_token,
                                         capacity_factor=get("expert_capacity_factor"))
+        self._replica_group = replica_group
         return expert_parallelize(model, self.ep, replica_group, replicas)
 
     # model -------------------------------------------------------------------------------
@@ -368,10 +372,45 @@ class ParallelStrategy(DataParallelEngine):
         return model
 
     # optimizer ---------------------------------------------------------------------------
+    def _store_specs(self, model: nn.Module):
+        """The two flat stores of a sharded model: parameters every rank holds (summed over the job) and this rank's shards
+        (summed over the ranks that hold the same shard)."""
+        from .fabric import SOLO
+        from .stores import StoreSpec
+
+        replicated = {id(p) for p in model._replicated}
+        named = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
+        local_group = getattr(self, "_replica_group", None)
+        if local_group is None:
+            local_group = SOLO  # one replica of every shard (also: row shards whose gradients arrive already reduce-scattered)
+        ctx = self.tp if self.tp is not None else self.ep
+        shard_group = ctx.group if ctx is not None else None
+        return [StoreSpec("replicated", [(n, p) for n, p in named if id(p) in replicated], None),
+                StoreSpec("local", [(n, p) for n, p in named if id(p) not in replicated], local_group)], shard_group
+
     def build_optimizer(self, model: nn.Module, cfg_optimizer=None, opt_state: Optional[Dict[str, Any]] = None, **kwargs: Any):
         if self.tp is not None or self.ep is not None or self.zero3 is not None:
             from .. import config
 
+            target = cfg_optimizer.get("_component_", "torch.optim.AdamW") if hasattr(cfg_optimizer, "get") else "torch.optim.AdamW"
+            target = target.replace("torchtune.", "torchtune_b200.", 1) if target.startswith("torchtune.") else target
+            params = {k: v for k, v in cfg_optimizer.items() if k != "_component_"} if hasattr(cfg_optimizer, "items") else dict(kwargs)
+            dtypes = {p.dtype for p in model.parameters() if p.requires_grad}
+            if self.zero3 is None and target in _FUSED_ADAMW and not params.get("amsgrad", False) and not params.get("maximize", False) and len(dtypes) == 1:
+                # fused path: moments of the replicated parameters sharded over every rank, those of a shard over its replicas
+                from .stores import MultiStoreAdamW
+
+                specs, shard_group = self._store_specs(model)
+                if self.device.type == "cuda":
+                    from ..ops import _cuda
+
+                    _cuda.enable_direct_wgrad(True)
+                opt = MultiStoreAdamW(self.device, specs, lr=float(params.get("lr", 1e-3)), betas=tuple(params.get("betas", (0.9, 0.999))),
+                                      eps=float(params.get("eps", 1e-8)), weight_decay=float(params.get("weight_decay", 1e-2)), shard_group=shard_group)
+                self._stores = opt
+                if opt_state:
+                    opt.load_full_state_dict(opt_state)
+                return opt
             opt = TensorParallelOptimizer(self, model, config.instantiate(cfg_optimizer, [p for p in model.parameters() if p.requires_grad]))
             if opt_state:
                 opt.load_full_state_dict(opt_state)
@@ -407,6 +446,22 @@ class ParallelStrategy(DataParallelEngine):
     def optimizer_step(self, model: nn.Module, optimizer, grad_scale, clip_grad_norm: Optional[float] = None):
         clip = float(clip_grad_norm) if clip_grad_norm is not None else None
         if self.tp is not None or self.ep is not None or self.zero3 is not None:
+            from .stores import MultiStoreAdamW
+
+            if isinstance(optimizer, MultiStoreAdamW):
+                if self.device.type == "cuda":
+                    from ..ops import _cuda
+
+                    _cuda.join_wgrad_stream()
+                optimizer.collect_grads()
+                cuda_peers = self.world > 1 and self.device.type == "cuda"
+                if cuda_peers:
+                    self.barrier()  # every rank's gradient buffers are complete before any peer pulls from them
+                optimizer.step(grad_scale=grad_scale, max_grad_norm=clip, group=self.group)
+                if cuda_peers:
+                    self.barrier()  # pushed parameters have landed everywhere; gradient buffers may be overwritten
+                optimizer.zero_grad()
+                return optimizer.last_grad_norm
             optimizer.step(grad_scale=grad_scale, max_grad_norm=clip)
             optimizer.zero_grad()
             return optimizer.last_grad_norm
@@ -426,6 +481,12 @@ class ParallelStrategy(DataParallelEngine):
         return optimizer.full_state_dict(self.rank == 0, group=self.group)
 
     def shutdown(self) -> None:
+        if self._stores is not None:
+            if self.device.type == "cuda":
+                torch.cuda.synchronize(self.device)
+            self.barrier()
+            self._stores.close()
+            self._stores = None
         if self.tp is not None:
             self.tp.close()
             self.tp = None

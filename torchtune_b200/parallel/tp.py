@@ -237,7 +237,7 @@ class _ColumnParallel(torch.autograd.Function):
             dx = tp.gemm_rs(dy, weight, b_mn=True)
         if ctx.needs_input_grad[1]:
             x_full = x_shard if ctx.gathered else tp.all_gather_rows(x_shard)
-            dw = _wgrad(dy, x_full)
+            dw = _wgrad(dy, x_full, weight)
         return dx, dw, None
 
 
@@ -267,15 +267,19 @@ class _RowParallel(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             if dy_full is None:
                 dy_full = tp.all_gather_rows(dy_shard)
-            dw = _wgrad(dy_full, x)
+            dw = _wgrad(dy_full, x, weight)
         return dx, dw, (dy_shard if ctx.has_residual and ctx.needs_input_grad[2] else None), None
 
 
-def _wgrad(dy: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
-    """``dyᵀ · x`` → ``[N, K]`` on the tcgen05 GEMM (TN form) when possible."""
+def _wgrad(dy: torch.Tensor, x: torch.Tensor, weight: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """``dyᵀ · x`` → ``[N, K]`` on the tcgen05 GEMM (TN form) when possible.  When ``weight`` lives in a flat parameter store the
+    GEMM epilogue writes (or accumulates) straight into its window of the flat gradient buffer and ``None`` is returned."""
     if dy.is_cuda and dy.dtype == _BF16 and x.dtype == _BF16:
+        from ..ops import _cuda
         from ..ops._cuda import gemm
 
+        if weight is not None and _cuda.grad_window_owner(weight) is not None:
+            return _cuda._wgrad(weight, dy if dy.is_contiguous() else dy.contiguous(), x if x.is_contiguous() else x.contiguous())
         return gemm(dy if dy.is_contiguous() else dy.contiguous(), x if x.is_contiguous() else x.contiguous(), a_mn=True, b_mn=True)
     return dy.t() @ x
 

@@ -49,15 +49,17 @@ def masked_var(centered: torch.Tensor, mask: torch.Tensor, unbiased: bool = True
     return var
 
 
-def whiten(x: torch.Tensor, shift_mean: bool = True, mask: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Normalise to unit variance (and zero mean unless ``shift_mean=False``), optionally over a mask."""
+def whiten(x: torch.Tensor, mask: Optional[torch.Tensor] = None, shift_mean: bool = True) -> torch.Tensor:
+    """Normalise to unit variance, optionally over a mask.  Same signature and meaning as the reference
+    (torchtune/rlhf/rewards.py:157-179): the mean is removed for the scaling and *added back* when ``shift_mean`` is
+    true, so ``shift_mean=False`` gives zero-mean values."""
     if mask is not None:
         mean = masked_mean(x, mask)
         var = masked_var(x - mean, mask) if mask.any() else x.var()
     else:
         mean, var = x.mean(), x.var()
     out = (x - mean) * torch.rsqrt(var + 1e-8)
-    return out if shift_mean else out + mean
+    return out + mean if shift_mean else out
 
 
 def estimate_advantages(values: torch.Tensor, rewards: torch.Tensor, gamma: float, lmbda: float, masks: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:

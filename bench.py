@@ -36,6 +36,17 @@ MODEL = dict(vocab_size=128_256, num_layers=32, num_heads=32, num_kv_heads=8, em
 SEQ_LEN, DOC_LEN, BATCH_PER_GPU, LR = 2048, 512, 4, 2e-5
 BASELINE_TOKENS_PER_S = None  # the reference publishes no B200 number for this config
 
+# The other benchmark configurations (``--config``); the default above stays the headline.
+MODEL_70B = dict(vocab_size=128_256, num_layers=80, num_heads=64, num_kv_heads=8, embed_dim=8192, max_seq_len=8192, intermediate_dim=28672, norm_eps=1e-5, rope_base=500_000)
+MODEL_SCOUT = dict(vocab_size=202_048, num_layers=48, num_heads=40, num_kv_heads=8, embed_dim=5120, hidden_dim=8192, max_seq_len=8192, rope_base=500_000, norm_eps=1e-5, num_experts=16,
+                   use_shared_expert=True, skip_rope_interval=4, attention_chunk_size=8192, use_scaled_rope=True)
+SHARDED_CONFIGS = {
+    # name: model, builder, tensor-parallel size (0 = none), expert-parallel size, seq, doc length, batch per data-parallel rank, activation offload
+    "70b_tp8": dict(model=MODEL_70B, family="llama3_1", tp=8, ep=0, seq=4096, doc=4096, batch=1, offload=True, label="llama3_3_70b"),
+    "70b_tp4dp2": dict(model=MODEL_70B, family="llama3_1", tp=4, ep=0, seq=4096, doc=4096, batch=1, offload=True, label="llama3_3_70b"),
+    "scout_ep8": dict(model=MODEL_SCOUT, family="llama4", tp=0, ep=8, seq=2048, doc=2048, batch=2, offload=False, label="llama4_scout_17b_16e (text decoder)"),
+}
+
 
 class ClockSampler:
     """Polls nvidia-smi during the timed region (SM clock, throttle reasons)."""
@@ -75,15 +86,15 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def synthetic_batch(torch, batch: int, seed: int):
+def synthetic_batch(torch, batch: int, seed: int, vocab: int = MODEL["vocab_size"], seq_len: int = SEQ_LEN, doc_len: int = DOC_LEN):
     """Host-side (pinned) packed batch: uniform tokens, shifted labels, per-document positions."""
     g = torch.Generator().manual_seed(seed)
-    tokens = torch.randint(0, MODEL["vocab_size"], (batch, SEQ_LEN), generator=g, dtype=torch.long)
+    tokens = torch.randint(0, vocab, (batch, seq_len), generator=g, dtype=torch.long)
     labels = torch.roll(tokens, -1, dims=1)
-    labels[:, DOC_LEN - 1 :: DOC_LEN] = -100
-    n_docs = SEQ_LEN // DOC_LEN
-    pos = torch.arange(DOC_LEN).repeat(n_docs).unsqueeze(0).expand(batch, SEQ_LEN).contiguous()
-    doc_ids = torch.arange(n_docs, dtype=torch.int32).repeat_interleave(DOC_LEN).unsqueeze(0).expand(batch, SEQ_LEN).contiguous()
+    labels[:, doc_len - 1 :: doc_len] = -100
+    n_docs = seq_len // doc_len
+    pos = torch.arange(doc_len).repeat(n_docs).unsqueeze(0).expand(batch, seq_len).contiguous()
+    doc_ids = torch.arange(n_docs, dtype=torch.int32).repeat_interleave(doc_len).unsqueeze(0).expand(batch, seq_len).contiguous()
     pin = (lambda t: t.pin_memory()) if torch.cuda.is_available() else (lambda t: t)
     return {"tokens": pin(tokens), "labels": pin(labels), "input_pos": pin(pos), "doc_ids": pin(doc_ids)}
 
@@ -138,6 +149,7 @@ def run_ours(args) -> dict:
     from torchtune_b200.ops.mask import AttentionMask
     from torchtune_b200.optim import AdamW
 
+    os.environ.setdefault("TTB_STRICT", "1")  # a bf16 CUDA op that would leave the sm_100a kernels raises instead of falling back
     rank, world, local = dist_env()
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
@@ -341,6 +353,114 @@ def run_ours_tp(args) -> dict:
     return out if rank == 0 else {}
 
 
+def run_ours_sharded(args) -> dict:
+    """``--config 70b_tp8 | 70b_tp4dp2 | scout_ep8``: whole training steps of the models that do not fit one GPU.
+
+    The model is built on the meta device and given storage layer by layer while it is sliced (tensor parallel: fused
+    all-gather → GEMM / GEMM → reduce-scatter kernels; expert parallel: peer-memory dispatch / combine + grouped GEMMs).  The
+    optimizer is the fused pull-reduce → AdamW → push kernel over two flat stores (replicated parameters sharded over every
+    rank, shards over their replicas), driven through the same public ``TrainStep`` as the headline."""
+    import torch
+    import torch.distributed as dist
+
+    os.environ.setdefault("TTB_STRICT", "1")
+    from torchtune_b200 import parallel as par
+    from torchtune_b200 import training
+    from torchtune_b200.engine.train_step import TrainStep
+    from torchtune_b200.modules import TransformerSelfAttentionLayer
+    from torchtune_b200.modules.loss import LinearCrossEntropyLoss
+    from torchtune_b200.ops._lib import check_device_errors, lib
+    from torchtune_b200.ops.mask import AttentionMask
+
+    spec = SHARDED_CONFIGS[args.config]
+    rank, world, local = dist_env()
+    tp = min(spec["tp"], world) if spec["tp"] else 1
+    ep = min(spec["ep"], world) if spec["ep"] else 1
+    if world < 2:
+        return {"impl": "ours", "config": {"model": spec["label"]}, "unavailable": f"--config {args.config} needs at least 2 GPUs (the model does not fit one)"}
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    cfg = {"tensor_parallel_dim": tp, "expert_parallel_dim": ep, "batch_size": spec["batch"], "tensor_parallel_max_tokens": spec["batch"] * spec["seq"]}
+    strategy = par.ParallelStrategy(cfg, device)
+    model_kwargs = dict(spec["model"])
+    if args.debug_layers:
+        model_kwargs["num_layers"] = args.debug_layers
+    with training.set_default_dtype(torch.bfloat16), torch.device("meta"):
+        if spec["family"] == "llama4":
+            from torchtune_b200.models.llama4 import llama4_decoder
+
+            model = llama4_decoder(**model_kwargs)
+        else:
+            from torchtune_b200.models.llama3_1 import llama3_1
+
+            model = llama3_1(**model_kwargs)
+    training.set_activation_checkpointing(model, {TransformerSelfAttentionLayer})
+    model = strategy.shard_model(model, cfg, None)  # no checkpoint: normal(0, 0.02) weights, identical on every rank
+    torch.cuda.empty_cache()
+    loss_fn = LinearCrossEntropyLoss(num_output_chunks=8)
+    loss_fn.set_model_output(model)
+    optimizer = strategy.build_optimizer(model, {"_component_": "torch.optim.AdamW", "lr": LR})
+    torch.cuda.empty_cache()
+    offload = training.get_act_offloading_ctx_manager(model, True) if spec["offload"] else None
+    step = TrainStep(model, loss_fn, optimizer, device, parallel=strategy, activations_ctx=offload)
+    vocab, seq, doc, batch = model_kwargs["vocab_size"], spec["seq"], spec["doc"], spec["batch"]
+
+    def to_model_batch(host):
+        dev = step.upload(host)
+        dev["mask"] = AttentionMask(causal=True, doc_ids=dev.pop("doc_ids")) if doc < seq else AttentionMask(causal=True)
+        if doc >= seq:
+            dev.pop("doc_ids", None)
+        return dev
+
+    # the ranks of one tensor-parallel group read the same batch; data-parallel (and expert-parallel) ranks read their own
+    host_batches = [synthetic_batch(torch, batch, seed=1000 * strategy.dp_rank + i, vocab=vocab, seq_len=seq, doc_len=doc) for i in range(4)]
+    dev_batches = [to_model_batch(h) for h in host_batches]
+    tokens_per_step = batch * seq * strategy.dp_size
+    L = lib()
+    losses = []
+    for i in range(args.warmup):
+        losses.append(step.compute(dev_batches[i % 4]))
+    torch.cuda.synchronize()
+    check_device_errors()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = L.ttb_launch_count()
+    t_kernel = timed_loop(torch, dist, world, lambda i: losses.append(step.compute(dev_batches[i % 4])), args.steps)
+    launches = L.ttb_launch_count() - launches0
+
+    def e2e_step(i):
+        losses.append(float(step.compute(to_model_batch(host_batches[i % 4])).item()))
+
+    t_e2e = timed_loop(torch, dist, world, e2e_step, args.steps)
+    clocks = sampler.stop() if rank == 0 else {}
+    check_device_errors()
+    extra = {}
+    if ep > 1:
+        from torchtune_b200.modules.moe import expert_load_imbalance
+
+        imb = expert_load_imbalance(model)
+        extra["expert_load_imbalance_max_over_mean"] = None if imb is None else round(float(imb), 3)
+    h2d = sum(t.numel() * t.element_size() for t in host_batches[0].values())
+    peak = torch.tensor([(torch.cuda.max_memory_allocated() + par.PeerBuffer.peak_bytes) / 2**30], device=device)
+    dist.all_reduce(peak, op=dist.ReduceOp.MAX)
+    value = tokens_per_step * args.steps / t_kernel
+    mode = f"tp{tp}" + (f" x dp{world // tp}" if world // tp > 1 else "") + " + sequence parallel" if tp > 1 else f"ep{ep}" + (f" x dp{world // ep}" if world // ep > 1 else "") + ", dense parameters replicated with optimizer state sharded over all ranks"
+    out = {
+        "metric": "tokens_per_second", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * t_kernel / args.steps, "higher_is_better": True, "scaling": "strong" if tp > 1 else "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic uniform tokens, random-init weights", "impl": "ours",
+        "config": {"model": spec["label"], "bench_config": args.config, "global_batch": batch * strategy.dp_size, "seq_len": seq, "doc_len": doc, "parallelism": mode,
+                   "activation_checkpointing": True, "activation_offloading": bool(spec["offload"]),
+                   "optimizer": "AdamW lr 2e-5 (bf16 moments), fused reduce+update+broadcast kernel over two flat peer stores",
+                   "l2": "inputs larger than L2 (tens of GB of weights streamed every step)", **({"debug_layers": args.debug_layers, "invalid": "reduced layer count: a functional check, not a benchmark number"} if args.debug_layers else {})},
+        "clocks": clocks, "e2e": {"value": tokens_per_step * args.steps / t_e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
+        "gpu_launches": int(launches), "peak_mem_gib": round(float(peak.item()), 2), "final_loss": float(losses[-1]) if losses else float("nan"), **extra,
+    }
+    strategy.shutdown()
+    return out if rank == 0 else {}
+
+
 def run_reference(args) -> dict:
     from baseline.reference_arm import run as run_ref
 
@@ -354,6 +474,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--variant", choices=["full", "lora", "qlora", "tp"], default="full", help="off-headline variants; the headline is always the full fine-tune")
+    ap.add_argument("--config", choices=["8b"] + sorted(SHARDED_CONFIGS), default="8b", help="8b: the headline (Llama-3.1-8B); the others are the 70B tensor-parallel and Scout expert-parallel configurations")
+    ap.add_argument("--debug-layers", type=int, default=0, help="functional check of a --config on few GPUs: build only this many layers (the printed line is marked invalid)")
     ap.add_argument("--fp8", action="store_true", help="variant: fp8 decoder linears (the headline number is always bf16)")
     args = ap.parse_args()
     rank, world, _ = dist_env()
@@ -364,7 +486,10 @@ def main() -> None:
     if args.impl == "reference":
         result = run_reference(args)
     else:
-        result = run_ours_tp(args) if args.variant == "tp" else run_ours(args)
+        if args.config != "8b":
+            result = run_ours_sharded(args)
+        else:
+            result = run_ours_tp(args) if args.variant == "tp" else run_ours(args)
     if rank == 0:
         print(json.dumps(result), flush=True)
 

@@ -299,7 +299,7 @@ def test_dp_reduce_adamw_bcast_emulated_ranks(world):
     pp = (ctypes.c_void_p * world)(*[t.data_ptr() for t in params])
     lr, b1, b2, eps, wd, scale = 1e-2, 0.9, 0.999, 1e-8, 0.1, 0.25
     for r in range(world):
-        check(L.ttb_dp_reduce_adamw_bcast(gp, pp, world, r, r * shard, shard, m[r].data_ptr(), v[r].data_ptr(), None, None, None, scale, lr, b1, b2, eps, wd, 1.0 / (1 - b1), 1.0 / math.sqrt(1 - b2), 0, None, 0, 0, None, stream_ptr()), "dp kernel")
+        check(L.ttb_dp_reduce_adamw_bcast(gp, pp, world, r, r * shard, shard, m[r].data_ptr(), v[r].data_ptr(), None, None, None, scale, lr, b1, b2, eps, wd, 1.0 / (1 - b1), 1.0 / math.sqrt(1 - b2), 0, None, 0, 0, None, 0, 1, 0, stream_ptr()), "dp kernel")
     torch.cuda.synchronize()
     gsum = torch.stack([t.float() for t in grads]).sum(0) * scale
     want = p0.float().clone()
@@ -317,12 +317,12 @@ def test_dp_reduce_adamw_bcast_emulated_ranks(world):
     gs = [torch.empty(shard, dtype=torch.float32, device="cuda") for _ in range(world)]
     parts = [torch.empty(L.ttb_dp_grid(), dtype=torch.float32, device="cuda") for _ in range(world)]
     for r in range(world):
-        check(L.ttb_dp_reduce_adamw_bcast(gp, pp2, world, r, r * shard, shard, m2[r].data_ptr(), v2[r].data_ptr(), gs[r].data_ptr(), parts[r].data_ptr(), None, 1.0, lr, b1, b2, eps, wd, 1.0, 1.0, 1, None, 0, 0, None, stream_ptr()), "dp reduce")
+        check(L.ttb_dp_reduce_adamw_bcast(gp, pp2, world, r, r * shard, shard, m2[r].data_ptr(), v2[r].data_ptr(), gs[r].data_ptr(), parts[r].data_ptr(), None, 1.0, lr, b1, b2, eps, wd, 1.0, 1.0, 1, None, 0, 0, None, 0, 1, 0, stream_ptr()), "dp reduce")
     norm = torch.stack([p.sum() for p in parts]).sum().sqrt() * scale
     _close(norm, gsum.norm(), 1e-3, 1e-3, "global norm")
     coef = (torch.clamp(1.0 / (norm + 1e-6), max=1.0) * scale).reshape(1).float()
     for r in range(world):
-        check(L.ttb_dp_reduce_adamw_bcast(gp, pp2, world, r, r * shard, shard, m2[r].data_ptr(), v2[r].data_ptr(), gs[r].data_ptr(), None, coef.data_ptr(), 1.0, lr, b1, b2, eps, wd, 1.0 / (1 - b1), 1.0 / math.sqrt(1 - b2), 2, None, 0, 0, None, stream_ptr()), "dp update")
+        check(L.ttb_dp_reduce_adamw_bcast(gp, pp2, world, r, r * shard, shard, m2[r].data_ptr(), v2[r].data_ptr(), gs[r].data_ptr(), None, coef.data_ptr(), 1.0, lr, b1, b2, eps, wd, 1.0 / (1 - b1), 1.0 / math.sqrt(1 - b2), 2, None, 0, 0, None, 7, 1, 0, stream_ptr()), "dp update")
     want2 = p0.float().clone()
     mm, vv = torch.zeros(total, device="cuda"), torch.zeros(total, device="cuda")
     ref.adamw_step(want2, gsum * float(torch.clamp(1.0 / (gsum.norm() + 1e-6), max=1.0)), mm, vv, 1, lr, b1, b2, eps, wd)
@@ -636,8 +636,9 @@ def test_fp8_linear_forward_backward_close_to_bf16(rowwise):
 
 # ----------------------------------------------------------------------------- failure detection: a bounded device wait that runs out
 def test_dp_bucket_wait_times_out_with_error_status_and_leaves_state_untouched():
-    """A peer that never declares its bucket final: the bucket kernel gives up after its cycle budget, stores an error code that the
-    host turns into an exception, and neither parameters nor optimizer state are modified.  The context stays usable."""
+    """A peer that never declares its bucket final: the wait in front of the bucket kernel gives up after its cycle budget and stores
+    an error code, every CTA of the bucket kernel sees it and returns, the host turns the code into an exception, and neither
+    parameters nor optimizer state are modified.  The context stays usable."""
     import ctypes
 
     from torchtune_b200.ops._lib import KernelError, check, check_device_errors, err_word, lib, stream_ptr
@@ -656,7 +657,7 @@ def test_dp_bucket_wait_times_out_with_error_status_and_leaves_state_untouched()
     L.ttb_dp_set_wait_cycles(200_000_000)  # ≈ 0.1 s
     try:
         check(L.ttb_dp_reduce_adamw_bcast(gp, pp, world, 0, 0, n // 2, m.data_ptr(), v.data_ptr(), None, None, None, 1.0, 1e-3, 0.9, 0.999, 1e-8, 0.01, 10.0, 31.6, 0,
-                                          flags.data_ptr(), 3, 1, err_word(flags.device).data_ptr(), stream_ptr()), "dp kernel")
+                                          flags.data_ptr(), 3, 1, err_word(flags.device).data_ptr(), 0, 1, 0, stream_ptr()), "dp kernel")
         with pytest.raises(KernelError, match="201"):
             check_device_errors()
     finally:

@@ -221,7 +221,11 @@ class SFTTrainer:
         t0 = time.perf_counter()
         # parameters stay resident on every rank (180 GB parts), so the model is built directly on
         # the device; there is no meta-device / deferred-init stage to undo
-        with training.set_default_dtype(self._dtype), self._device:
+        # … except under tensor / expert parallelism, where the full model may exceed one GPU: it is built on the meta device
+        # and the strategy gives each layer storage (from the checkpoint) right before slicing it
+        deferred = (not self.is_lora and self.parallel is not None and not cfg.get("resize_token_embeddings")
+                    and (int(cfg.get("tensor_parallel_dim", 1) or 1) > 1 or int(cfg.get("expert_parallel_dim", 1) or 1) > 1))
+        with training.set_default_dtype(self._dtype), (torch.device("meta") if deferred else self._device):
             model = config.instantiate(cfg.model)
         if cfg.get("resize_token_embeddings") and self._tokenizer_vocab(cfg) is not None:
             modules.resize_token_embeddings(model, self._tokenizer_vocab(cfg))

@@ -22,8 +22,10 @@ from ..utils import batch_to_device
 
 
 class TrainStep:
-    def __init__(self, model: nn.Module, loss_fn, optimizer, device: torch.device, parallel=None, clip_grad_norm: Optional[float] = None):
+    def __init__(self, model: nn.Module, loss_fn, optimizer, device: torch.device, parallel=None, clip_grad_norm: Optional[float] = None, activations_ctx=None):
         self.model, self.loss_fn, self.optimizer = model, loss_fn, optimizer
+        # context entered around the forward pass (``training.get_act_offloading_ctx_manager``: pinned-host activation offload)
+        self.activations_ctx = activations_ctx
         self.device = device
         self.parallel = parallel
         self.clip_grad_norm = clip_grad_norm
@@ -61,8 +63,15 @@ class TrainStep:
             if len(self._in_flight) >= self.max_steps_in_flight:
                 self._in_flight.pop(0).synchronize()
         self._mark()
-        hidden = self.model(**batch)
-        loss_sum, n_valid = self.loss_fn.compute_sum(hidden, labels)
+        if hasattr(self.model, "shard_rows"):  # tensor + sequence parallel model: the loss runs on this rank's token rows
+            labels = self.model.shard_rows(labels)
+        if self.activations_ctx is not None:
+            with self.activations_ctx:
+                hidden = self.model(**batch)
+                loss_sum, n_valid = self.loss_fn.compute_sum(hidden, labels)
+        else:
+            hidden = self.model(**batch)
+            loss_sum, n_valid = self.loss_fn.compute_sum(hidden, labels)
         self._mark()
         n_tokens = n_valid.to(torch.float32)
         if self.parallel is not None:

@@ -351,6 +351,11 @@ def register_grad_window(param: torch.Tensor) -> None:
     _grad_windows[param.data_ptr()] = param
 
 
+def unregister_grad_window(ptr: int) -> None:
+    """Forget the window registered for the parameter at address ``ptr`` (its storage is being released)."""
+    _grad_windows.pop(ptr, None)
+
+
 def grad_window_owner(weight: torch.Tensor) -> Optional[torch.Tensor]:
     if not _direct_wgrad:
         return None

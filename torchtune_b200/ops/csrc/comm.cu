@@ -62,41 +62,43 @@ __global__ void dp_signal_kernel(FlagTable t, int world, int rank, int slot, int
   }
 }
 
+// Bounded wait of one rank for its peers' flags (one warp; lane p watches peer p's entry).  Runs as a launch of its own in
+// front of the kernel that consumes the peers' data, so that giving up is a decision for the whole grid: on timeout it stores
+// 201 in the error word, and every CTA of the consumer returns at once when it finds the error word set.
+__global__ void dp_wait_kernel(const int* __restrict__ my_flags, int world, int rank, int slot, int epoch, int* __restrict__ err,
+                               long long wait_cycles) {
+  if (threadIdx.x < world && threadIdx.x != rank) {
+    const int* f = my_flags + threadIdx.x * kMaxBuckets + slot;
+    const long long t0 = clock64();
+    int v;
+    unsigned spins = 0;
+    while (true) {
+      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+      if (v >= epoch) break;
+      if ((++spins & 0xff) == 0 && clock64() - t0 > wait_cycles) {
+        atomicExch(err, 201);
+        break;
+      }
+    }
+  }
+}
+
 // mode 0: reduce + AdamW + broadcast in one pass.
 // mode 1: reduce only -> reduced fp32 gradient into `gsum` (shard-local) and per-block partial
 //         sums of squares into `sumsq_partials` (for global-norm clipping).
 // mode 2: AdamW + broadcast reading the already reduced `gsum`.
+// `guard` (optional): the device error word.  When it is set — a preceding dp_wait_kernel gave up, or any earlier kernel
+// reported an error — every CTA returns without touching parameters, moments or partial sums, so a failed step leaves the
+// optimizer state as it was.
 template <int WORLD>
 __global__ void __launch_bounds__(256, 4)
 dp_reduce_adamw_bcast_kernel(PeerTable peers, int rank, long long begin, long long count, __nv_bfloat16* __restrict__ m,
                              __nv_bfloat16* __restrict__ v, float* __restrict__ gsum, float* __restrict__ sumsq_partials,
                              const float* __restrict__ scale_dev, float scale_host, float lr, float beta1, float beta2,
                              float eps, float weight_decay, float inv_bc1, float inv_sqrt_bc2, int mode,
-                             const int* __restrict__ my_flags, int slot, int epoch, int* __restrict__ err,
-                             long long wait_cycles) {
+                             const int* __restrict__ guard, int bcast, int accumulate) {
   __shared__ float red[8];
-  __shared__ int give_up;
-  if (my_flags != nullptr) {  // wait until every peer has declared this bucket final
-    if (threadIdx.x == 0) give_up = 0;
-    __syncthreads();
-    if (threadIdx.x < WORLD && threadIdx.x != rank) {
-      const int* f = my_flags + threadIdx.x * kMaxBuckets + slot;
-      const long long t0 = clock64();
-      int v;
-      unsigned spins = 0;
-      while (true) {
-        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
-        if (v >= epoch) break;
-        if ((++spins & 0xff) == 0 && clock64() - t0 > wait_cycles) {
-          give_up = 1;
-          atomicExch(err, 201);
-          break;
-        }
-      }
-    }
-    __syncthreads();
-    if (give_up) return;
-  }
+  if (guard != nullptr && *reinterpret_cast<const volatile int*>(guard) != 0) return;
   const float gs = scale_host * (scale_dev != nullptr ? *scale_dev : 1.f);
   const long long nvec = count >> 3;  // shards are multiples of 8 elements
   float sq = 0.f;
@@ -127,6 +129,11 @@ dp_reduce_adamw_bcast_kernel(PeerTable peers, int rank, long long begin, long lo
       }
     }
     if (mode == 1) {
+      if (accumulate) {  // a further micro-batch: add to the reduced gradient of the earlier ones
+        const float4 a = *reinterpret_cast<const float4*>(gsum + i * 8);
+        const float4 b = *reinterpret_cast<const float4*>(gsum + i * 8 + 4);
+        g[0] += a.x, g[1] += a.y, g[2] += a.z, g[3] += a.w, g[4] += b.x, g[5] += b.y, g[6] += b.z, g[7] += b.w;
+      }
 #pragma unroll
       for (int j = 0; j < 8; ++j) sq += g[j] * g[j];
       *reinterpret_cast<float4*>(gsum + i * 8) = make_float4(g[0], g[1], g[2], g[3]);
@@ -148,6 +155,10 @@ dp_reduce_adamw_bcast_kernel(PeerTable peers, int rank, long long begin, long lo
     *reinterpret_cast<uint4*>(m + i * 8) = pack8f(m1);
     *reinterpret_cast<uint4*>(v + i * 8) = pack8f(v1);
     const uint4 out = pack8f(w);
+    if (!bcast) {  // sharded parameters: the owner keeps the only copy
+      *reinterpret_cast<uint4*>(peers.param[rank] + e) = out;
+      continue;
+    }
 #pragma unroll
     for (int r = 0; r < WORLD; ++r) {
       const int dst = (rank + r) % WORLD;
@@ -166,6 +177,33 @@ dp_reduce_adamw_bcast_kernel(PeerTable peers, int rank, long long begin, long lo
     }
   }
   __threadfence_system();  // peer stores visible before the host-side barrier that follows
+}
+
+// Parameter all-gather of a sharded-parameter (ZeRO-3) bucket as a pull over peer memory: dst[r · piece + i] = shard_r[i] for
+// every rank r (16-byte peer loads, local stores).  `guard` as above.
+struct ShardTable {
+  const __nv_bfloat16* shard[kMaxRanks];
+};
+
+template <int WORLD>
+__global__ void __launch_bounds__(256, 4)
+zero3_gather_kernel(ShardTable t, int rank, long long piece, __nv_bfloat16* __restrict__ dst, const int* __restrict__ guard) {
+  if (guard != nullptr && *reinterpret_cast<const volatile int*>(guard) != 0) return;
+  const long long nvec = piece >> 3;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    uint4 raw[WORLD];
+#pragma unroll
+    for (int r = 0; r < WORLD; ++r) {
+      const int src = (rank + 1 + r) % WORLD;  // every rank starts with a different peer
+      raw[r] = *reinterpret_cast<const uint4*>(t.shard[src] + i * 8);
+    }
+#pragma unroll
+    for (int r = 0; r < WORLD; ++r) {
+      const int src = (rank + 1 + r) % WORLD;
+      *reinterpret_cast<uint4*>(dst + src * piece + i * 8) = raw[r];
+    }
+  }
 }
 
 }  // namespace ttb
@@ -199,12 +237,19 @@ extern "C" int ttb_dp_grid() { return sm_count() * 4; }
 
 // grad_ptrs / param_ptrs: host arrays of `world` device pointers (peer-mapped flat buffers).
 // [begin, begin+count) is this rank's shard (count % 8 == 0, begin % 8 == 0).
+// bcast = 0: the new parameters are stored to param_ptrs[rank] only (sharded parameters; the other entries are not touched).
+// accumulate = 1 (mode 1): add the reduced gradient to what `gsum` already holds (gradient accumulation over micro-batches;
+// the partial sums of squares then describe the accumulated gradient).
+// my_flags != null: first wait (bounded, one warp, its own launch) until every peer's entry [peer][slot] of this rank's flag
+// array has reached `epoch`.  grid_ctas > 0 limits the kernel to that many CTAs (a bucket processed *during* backward is bound
+// by NVLink, not HBM: a few dozen CTAs keep the links busy and leave the SMs' issue slots and the HBM to the GEMMs they run
+// beside; the kernel uses no shared memory, so its CTAs fit next to a resident GEMM CTA).
 extern "C" int ttb_dp_reduce_adamw_bcast(void* const* grad_ptrs, void* const* param_ptrs, int world, int rank,
                                          long long begin, long long count, void* m, void* v, float* gsum,
                                          float* sumsq_partials, const float* scale_dev, float scale_host, float lr,
                                          float beta1, float beta2, float eps, float weight_decay, float inv_bc1,
                                          float inv_sqrt_bc2, int mode, const int* my_flags, int slot, int epoch, int* err,
-                                         void* stream) {
+                                         int grid_ctas, int bcast, int accumulate, void* stream) {
   if (world < 1 || world > kMaxRanks || (begin & 7) || (count & 7)) return kErrBadShape;
   if (my_flags != nullptr && (slot < 0 || slot >= kMaxBuckets || err == nullptr)) return kErrBadShape;
   if (count == 0) return kOk;
@@ -213,17 +258,23 @@ extern "C" int ttb_dp_reduce_adamw_bcast(void* const* grad_ptrs, void* const* pa
     t.grad[r] = static_cast<const __nv_bfloat16*>(grad_ptrs[r]);
     t.param[r] = static_cast<__nv_bfloat16*>(param_ptrs[r]);
   }
-  const int grid = ttb_dp_grid();
+  const int full = ttb_dp_grid();
+  const int grid = (grid_ctas > 0 && grid_ctas < full) ? grid_ctas : full;
   auto s = static_cast<cudaStream_t>(stream);
   auto mm = static_cast<__nv_bfloat16*>(m);
   auto vv = static_cast<__nv_bfloat16*>(v);
+  const int* guard = nullptr;
+  if (my_flags != nullptr && world > 1) {
+    TTB_COUNT_LAUNCH(1);
+    dp_wait_kernel<<<1, 32, 0, s>>>(my_flags, world, rank, slot, epoch, err, g_flag_wait_cycles);
+    guard = err;
+  }
   TTB_COUNT_LAUNCH(1);
 #define TTB_DP_CASE(W)                                                                                              \
   case W:                                                                                                           \
     dp_reduce_adamw_bcast_kernel<W><<<grid, 256, 0, s>>>(t, rank, begin, count, mm, vv, gsum, sumsq_partials,       \
                                                          scale_dev, scale_host, lr, beta1, beta2, eps, weight_decay, \
-                                                         inv_bc1, inv_sqrt_bc2, mode, my_flags, slot, epoch, err,    \
-                                                         g_flag_wait_cycles);                                        \
+                                                         inv_bc1, inv_sqrt_bc2, mode, guard, bcast, accumulate);     \
     break;
   switch (world) {
     TTB_DP_CASE(1)
@@ -240,6 +291,56 @@ extern "C" int ttb_dp_reduce_adamw_bcast(void* const* grad_ptrs, void* const* pa
   return cudaGetLastError() == cudaSuccess ? kOk : kErrDriver;
 }
 
+// shard_ptrs: `world` device pointers to the ranks' shards of one bucket (piece elements each, piece % 8 == 0); dst: local
+// buffer of world · piece elements.  my_flags != null: wait first (bounded) until every peer's entry [peer][slot] has reached
+// `epoch` (the peers' optimizer updates of this bucket are complete).
+extern "C" int ttb_zero3_gather(void* const* shard_ptrs, int world, int rank, long long piece, void* dst, const int* my_flags, int slot,
+                                int epoch, int* err, int grid_ctas, void* stream) {
+  if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world || piece <= 0 || (piece & 7)) return kErrBadShape;
+  if (my_flags != nullptr && (slot < 0 || slot >= kMaxBuckets || err == nullptr)) return kErrBadShape;
+  ShardTable t{};
+  for (int r = 0; r < world; ++r) t.shard[r] = static_cast<const __nv_bfloat16*>(shard_ptrs[r]);
+  const int full = ttb_dp_grid();
+  const int grid = (grid_ctas > 0 && grid_ctas < full) ? grid_ctas : full;
+  auto s = static_cast<cudaStream_t>(stream);
+  const int* guard = nullptr;
+  if (my_flags != nullptr && world > 1) {
+    TTB_COUNT_LAUNCH(1);
+    dp_wait_kernel<<<1, 32, 0, s>>>(my_flags, world, rank, slot, epoch, err, g_flag_wait_cycles);
+    guard = err;
+  }
+  TTB_COUNT_LAUNCH(1);
+  auto d = static_cast<__nv_bfloat16*>(dst);
+#define TTB_Z3_CASE(W) \
+  case W:              \
+    zero3_gather_kernel<W><<<grid, 256, 0, s>>>(t, rank, piece, d, guard); \
+    break;
+  switch (world) {
+    TTB_Z3_CASE(1)
+    TTB_Z3_CASE(2)
+    TTB_Z3_CASE(3)
+    TTB_Z3_CASE(4)
+    TTB_Z3_CASE(6)
+    TTB_Z3_CASE(8)
+    TTB_Z3_CASE(16)
+    default:
+      return kErrBadShape;
+  }
+#undef TTB_Z3_CASE
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrDriver;
+}
+
+// Bounded wait on this rank's flag array as a launch of its own: returns (in stream order) once every peer's entry
+// [peer][slot] has reached `epoch`, or stores 201 in the error word when the cycle budget runs out.  Together with
+// ttb_dp_signal this is a barrier between the ranks that needs no collective library.
+extern "C" int ttb_dp_wait(const int* my_flags, int world, int rank, int slot, int epoch, int* err, void* stream) {
+  if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world || slot < 0 || slot >= kMaxBuckets || err == nullptr) return kErrBadShape;
+  if (world == 1) return kOk;
+  TTB_COUNT_LAUNCH(1);
+  dp_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(my_flags, world, rank, slot, epoch, err, g_flag_wait_cycles);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrDriver;
+}
+
 // flag_ptrs: `world` device pointers, rank q's flag array int[world][4096] (peer-mapped).  Stores `epoch` into entry [rank][slot]
 // of every peer's array; stream order makes it follow the work that completes this rank's gradients of that bucket.
 extern "C" int ttb_dp_signal(void* const* flag_ptrs, int world, int rank, int slot, int epoch, void* stream) {
@@ -252,6 +353,6 @@ extern "C" int ttb_dp_signal(void* const* flag_ptrs, int world, int rank, int sl
 }
 extern "C" int ttb_dp_max_buckets() { return kMaxBuckets; }
 
-// Cycle budget of the cross-rank flag wait (default 4e9 ≈ 2–3 s).  When it runs out the kernel stores 201 in the error word and
-// returns without touching parameters or optimizer state; the host raises on its next check.
+// Cycle budget of the cross-rank flag wait (default 4e9 ≈ 2–3 s).  When it runs out the wait kernel stores 201 in the error word
+// and the kernels that follow it return without touching parameters or optimizer state; the host raises on its next check.
 extern "C" void ttb_dp_set_wait_cycles(long long cycles) { g_flag_wait_cycles = cycles > 0 ? cycles : 4000000000LL; }

@@ -49,16 +49,15 @@ def _bucket_key(name: str) -> Optional[str]:
     return m.group(1) if m else None
 
 
-class FlatParameters:
-    """Re-homes the trainable parameters of ``model`` into one flat buffer (and gives each a
-    same-shaped window of a flat gradient buffer, exposed as ``param._grad_buffer``).
+class FlatLayout:
+    """Index arithmetic of a flat parameter space cut into buckets (no storage).
 
     ``buckets[b] = (start, size)`` are consecutive ranges of the flat index space whose sizes
     are multiples of ``8 · world``; rank ``r`` owns ``[start + r·size/world, start + (r+1)·size/world)``
     of each.  ``bucket_keys[b]`` is the module path of the decoder layer a bucket belongs to
     (``None`` for the parameters before / after the layers)."""
 
-    def __init__(self, params: List[Tuple[str, nn.Parameter]], world: int, device: torch.device, group=None, min_bucket_numel: int = 0):
+    def __init__(self, params: List[Tuple[str, nn.Parameter]], world: int, min_bucket_numel: int = 0):
         dtypes = {p.dtype for _, p in params}
         if len(dtypes) != 1:
             raise ValueError(f"all trainable parameters must share one dtype, found {dtypes}")
@@ -95,23 +94,6 @@ class FlatParameters:
         for piece in self.pieces:
             self.state_offsets.append(self.state_offsets[-1] + piece)
         self.shard = self.state_offsets[-1]  # elements of optimizer state per rank
-        esize = torch.empty(0, dtype=self.dtype).element_size()
-        self.param_buf = PeerBuffer(self.total * esize, device, group)
-        self.grad_buf = PeerBuffer(self.total * esize, device, group)
-        self.flat_param = self.param_buf.tensor(self.dtype, self.total)
-        self.flat_grad = self.grad_buf.tensor(self.dtype, self.total)
-        with torch.no_grad():
-            for p, off in zip(self.params, self.offsets):
-                window = self.flat_param[off : off + p.numel()].view(p.shape)
-                window.copy_(p.data)
-                p.data = window
-                p._grad_buffer = self.flat_grad[off : off + p.numel()].view(p.shape)
-                p._grad_written = False
-        if device.type == "cuda":
-            from ..ops import _cuda
-
-            for p in self.params:
-                _cuda.register_grad_window(p)
 
     # ownership -----------------------------------------------------------------------------
     def owned(self, bucket: int, rank: int) -> Tuple[int, int, int]:
@@ -137,6 +119,7 @@ class FlatParameters:
             if end > begin:
                 out[off : off + end - begin].copy_(full[begin:end])
 
+
     # gradients -----------------------------------------------------------------------------
     def collect_autograd_grads(self, bucket: Optional[int] = None) -> None:
         """Move gradients that autograd produced as separate tensors into the flat buffer and
@@ -156,6 +139,31 @@ class FlatParameters:
     def reset_grad_flags(self) -> None:
         for p in self.params:
             p._grad_written = False
+
+
+class FlatParameters(FlatLayout):
+    """Re-homes the trainable parameters of ``model`` into one flat buffer (and gives each a
+    same-shaped window of a flat gradient buffer, exposed as ``param._grad_buffer``); layout: :class:`FlatLayout`."""
+
+    def __init__(self, params: List[Tuple[str, nn.Parameter]], world: int, device: torch.device, group=None, min_bucket_numel: int = 0):
+        super().__init__(params, world, min_bucket_numel)
+        esize = torch.empty(0, dtype=self.dtype).element_size()
+        self.param_buf = PeerBuffer(self.total * esize, device, group)
+        self.grad_buf = PeerBuffer(self.total * esize, device, group)
+        self.flat_param = self.param_buf.tensor(self.dtype, self.total)
+        self.flat_grad = self.grad_buf.tensor(self.dtype, self.total)
+        with torch.no_grad():
+            for p, off in zip(self.params, self.offsets):
+                window = self.flat_param[off : off + p.numel()].view(p.shape)
+                window.copy_(p.data)
+                p.data = window
+                p._grad_buffer = self.flat_grad[off : off + p.numel()].view(p.shape)
+                p._grad_written = False
+        if device.type == "cuda":
+            from ..ops import _cuda
+
+            for p in self.params:
+                _cuda.register_grad_window(p)
 
     def close(self) -> None:
         self.param_buf.close()
@@ -293,7 +301,7 @@ class ShardedAdamW:
                                         self.exp_avg.data_ptr() + esz * off, self.exp_avg_sq.data_ptr() + esz * off, gsum, partials,
                                         None if sdev is None else sdev.data_ptr(), shost, float(g["lr"]), b1, b2, g["eps"], g["weight_decay"],
                                         st["inv_bc1"], st["inv_sqrt_bc2"], mode, None if wait is None else wait[0], bucket, 0 if wait is None else wait[1],
-                                        err_word(flat.flat_param.device).data_ptr(), stream_ptr()),
+                                        err_word(flat.flat_param.device).data_ptr(), int(st.get("grid_ctas", 0)) if mode != 2 else 0, 1, 0, stream_ptr()),
             "dp_reduce_adamw_bcast",
         )
 
@@ -389,10 +397,14 @@ def _declare_dp(L) -> None:
     if getattr(L, "_dp_declared", False):
         return
     vp, i32, i64, f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
-    L.ttb_dp_reduce_adamw_bcast.argtypes = [ctypes.POINTER(vp), ctypes.POINTER(vp), i32, i32, i64, i64, vp, vp, vp, vp, vp, f32, f32, f32, f32, f32, f32, f32, f32, i32, vp, i32, i32, vp, vp]
+    L.ttb_dp_reduce_adamw_bcast.argtypes = [ctypes.POINTER(vp), ctypes.POINTER(vp), i32, i32, i64, i64, vp, vp, vp, vp, vp, f32, f32, f32, f32, f32, f32, f32, f32, i32, vp, i32, i32, vp, i32, i32, i32, vp]
     L.ttb_dp_reduce_adamw_bcast.restype = i32
     L.ttb_dp_signal.argtypes = [ctypes.POINTER(vp), i32, i32, i32, i32, vp]
     L.ttb_dp_signal.restype = i32
+    L.ttb_zero3_gather.argtypes = [ctypes.POINTER(vp), i32, i32, i64, vp, vp, i32, i32, vp, i32, vp]
+    L.ttb_zero3_gather.restype = i32
+    L.ttb_dp_wait.argtypes = [vp, i32, i32, i32, i32, vp, vp]
+    L.ttb_dp_wait.restype = i32
     L.ttb_dp_grid.restype = i32
     L.ttb_dp_max_buckets.restype = i32
     L.ttb_dp_set_wait_cycles.argtypes = [i64]
@@ -428,6 +440,10 @@ class DataParallelEngine:
         # measured on the 8B model it lost on 1 and 2 GPUs (the HBM-bound update competes with the backward GEMMs) and
         # made no difference on 4 (≈ 484 ms per step either way), so the simpler after-backward protocol is the default.
         self.min_world_for_overlap = int(os.environ.get("TTB_DP_OVERLAP_MIN_WORLD", "1000000"))
+        # CTAs of a bucket kernel that runs beside the backward GEMMs (NVLink-bound: a few dozen CTAs saturate the links and leave
+        # HBM bandwidth and issue slots to the GEMMs); 0 = the full grid
+        self.overlap_ctas = int(os.environ.get("TTB_DP_OVERLAP_CTAS", "48"))
+        self._barrier_epoch = 0
 
     # sizes the recipes ask for ------------------------------------------------------------
     dp_size = property(lambda self: self.world)
@@ -446,7 +462,7 @@ class DataParallelEngine:
 
             L = lib()
             _declare_dp(L)
-            if len(self.flat.buckets) <= L.ttb_dp_max_buckets():
+            if len(self.flat.buckets) < L.ttb_dp_max_buckets():
                 self._comm_stream = torch.cuda.Stream(device=self.device)
                 self._flags = PeerBuffer(self.world * L.ttb_dp_max_buckets() * 4, self.device, self.group)  # int32 [world][max buckets]
                 self._epoch = 0
@@ -497,6 +513,7 @@ class DataParallelEngine:
         optimizer.begin_step(grad_scale, clip_grad_norm)
         self._epoch += 1
         optimizer._open["wait"] = (self._flags.local_ptr, self._epoch)
+        optimizer._open["grid_ctas"] = self.overlap_ctas
         self._armed = optimizer
         return True
 
@@ -544,6 +561,24 @@ class DataParallelEngine:
         if self.world > 1:
             dist.all_reduce(self._barrier_token, group=self.group)
 
+    def _step_barrier(self) -> None:
+        """Stream-ordered barrier between the ranks on peer-memory flags (two one-warp kernels of the kernel library: store the
+        epoch into every peer's flag array, then wait — bounded — until all peers' entries have arrived).  Everything this rank
+        enqueued before is complete (and its peer stores visible) when a peer gets past its wait.  Falls back to a 4-byte
+        all-reduce when the flag array does not exist (CPU, or more buckets than flag slots)."""
+        if self.world == 1:
+            return
+        if self._flags is None:
+            self.barrier()
+            return
+        from ..ops._lib import check, err_word, lib, stream_ptr
+
+        L = lib()
+        self._barrier_epoch += 1
+        slot = L.ttb_dp_max_buckets() - 1  # the last slot is never a bucket's (prepare() keeps bucket counts below it)
+        check(L.ttb_dp_signal(self._flags.pointer_array(), self.world, self.rank, slot, self._barrier_epoch, stream_ptr()), "dp_signal")
+        check(L.ttb_dp_wait(self._flags.local_ptr, self.world, self.rank, slot, self._barrier_epoch, err_word(self.device).data_ptr(), stream_ptr()), "dp_wait")
+
     def optimizer_step(self, model: nn.Module, optimizer: ShardedAdamW, grad_scale, clip_grad_norm: Optional[float] = None):
         if self._armed is not None:
             if self._armed is not optimizer:
@@ -555,7 +590,7 @@ class DataParallelEngine:
             self._armed = None
             optimizer.step(grad_scale=grad_scale, max_grad_norm=clip_grad_norm, group=self.group)  # with clipping: norm + update
             if self.world > 1:
-                self.barrier()  # pushes have landed; gradients may be overwritten
+                self._step_barrier()  # pushes have landed; gradients may be overwritten
             optimizer.zero_grad()
             return optimizer.last_grad_norm
         if self.device.type == "cuda":
@@ -564,10 +599,10 @@ class DataParallelEngine:
             _cuda.join_wgrad_stream()
         self.flat.collect_autograd_grads()
         if self.world > 1 and self.device.type == "cuda":
-            self.barrier()  # every rank's gradient buffer is complete
+            self._step_barrier()  # every rank's gradient buffer is complete
         optimizer.step(grad_scale=grad_scale, max_grad_norm=clip_grad_norm, group=self.group)
         if self.world > 1 and self.device.type == "cuda":
-            self.barrier()  # pushes have landed; gradients may be overwritten
+            self._step_barrier()  # pushes have landed; gradients may be overwritten
         optimizer.zero_grad()
         return optimizer.last_grad_norm
 

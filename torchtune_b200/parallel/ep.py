@@ -297,7 +297,7 @@ class ExpertParallelMoE(nn.Module):
 
 
 # ------------------------------------------------------------------------------------------- model level
-def expert_parallelize(model: nn.Module, ep: ExpertParallelContext, replica_group=None, replicas: int = 1) -> nn.Module:
+def expert_parallelize(model: nn.Module, ep: ExpertParallelContext, replica_group=None, replicas: int = 1, prepare_layer=None) -> nn.Module:
     """Replace every :class:`MoE` layer of ``model`` by :class:`ExpertParallelMoE` (in place) and attach the small surface the
     sharded-model optimizer needs: ``_replicated`` (parameters every rank holds), ``sync_replicated_grads()`` and
     ``full_state_dict()`` (checkpoint layout with all experts; collective).
@@ -313,6 +313,16 @@ def expert_parallelize(model: nn.Module, ep: ExpertParallelContext, replica_grou
             else:
                 swap(child)
 
+    if prepare_layer is not None and hasattr(model, "layers"):
+        # a model still on the meta device: every decoder layer gets storage and values (``prepare_layer(module, prefix)``, e.g.
+        # training.LayerwisePreparer) right before its experts are cut down to this rank's, so the full expert stacks of at most
+        # one layer are alive at a time
+        for i, layer in enumerate(model.layers):
+            prepare_layer(layer, f"layers.{i}.")
+            swap(layer)
+        for name, child in model.named_children():
+            if name != "layers":
+                prepare_layer(child, f"{name}.")
     swap(model)
     expert_params = {id(p) for m in model.modules() if isinstance(m, ExpertParallelMoE) for p in m.experts.parameters()}
     model._replicated = [p for p in model.parameters() if id(p) not in expert_params]

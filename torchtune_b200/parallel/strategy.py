@@ -249,7 +249,7 @@ class ParallelStrategy(DataParallelEngine):
         seq = int(seq or getattr(model, "max_seq_len", 2048))
         return -(-(int(get("batch_size", 1)) * seq) // self.dims.tp)
 
-    def _shard_model_tp(self, model: nn.Module, cfg) -> nn.Module:
+    def _shard_model_tp(self, model: nn.Module, cfg, prepare_layer=None) -> nn.Module:
         from ..training.memory import CheckpointedLayer
         from .tp import TensorParallelContext
         from .tp_model import tensor_parallelize
@@ -272,12 +272,12 @@ class ParallelStrategy(DataParallelEngine):
             tp_group, dp_group = groups["tp"], groups["dp"]
         self.tp = TensorParallelContext(self.device, tp_group, max_rows_per_rank=self._tp_max_rows(cfg, core), max_width=width)
         ac = any(isinstance(layer, CheckpointedLayer) for layer in core.layers)
-        out = tensor_parallelize(core, self.tp, activation_checkpointing=ac)
+        out = tensor_parallelize(core, self.tp, activation_checkpointing=ac, prepare_layer=prepare_layer)
         out.set_data_parallel_group(dp_group, self.world // self.dims.tp)
         self._replica_group = dp_group
         return out
 
-    def _shard_model_ep(self, model: nn.Module, cfg) -> nn.Module:
+    def _shard_model_ep(self, model: nn.Module, cfg, prepare_layer=None) -> nn.Module:
         """Experts spread over the ranks (every rank keeps its own batch: expert parallel ranks are data parallel for the
         dense part, whose gradients are summed before the optimizer step)."""
         from ..modules.moe import MoE
@@ -307,14 +307,23 @@ class ParallelStrategy(DataParallelEngine):
         self.ep = ExpertParallelContext(self.device, ep_group, num_experts=router.num_experts, dim=router.dim, max_pairs=tokens * router.experts_per_token,
                                         capacity_factor=get("expert_capacity_factor"))
         self._replica_group = replica_group
-        return expert_parallelize(model, self.ep, replica_group, replicas)
+        return expert_parallelize(model, self.ep, replica_group, replicas, prepare_layer=prepare_layer)
 
     # model -------------------------------------------------------------------------------
     def shard_model(self, model: nn.Module, cfg, base_sd: Dict[str, Any], adapter_sd: Optional[Dict[str, Any]] = None, *, dtype: torch.dtype = torch.bfloat16, strict: bool = True) -> nn.Module:
         from ..training._distributed import materialize, validate_no_params_on_meta_device
 
-        materialize(model, self.device)
         is_lora = not strict
+        layerwise = None
+        if (self.dims.tp_enabled or self.ep_dim > 1) and not is_lora and any(p.is_meta for p in model.parameters()):
+            # a model built on the meta device is given storage layer by layer while it is sharded: it never exists in full
+            from ..training._distributed import LayerwisePreparer
+
+            layerwise = LayerwisePreparer(self.device, state_dict=base_sd)
+            if self.dims.tp_enabled:
+                return self._shard_model_tp(model, cfg, layerwise)
+            return self._shard_model_ep(model, cfg, layerwise)
+        materialize(model, self.device)
         if is_lora:
             from ..modules.peft import validate_missing_and_unexpected_for_lora
 

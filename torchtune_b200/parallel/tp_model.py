@@ -291,16 +291,23 @@ class TPDecoder(nn.Module):
     """Forward returns the hidden states (or logits) of *this rank's* token rows, shaped ``[1, rows, ·]``;
     use :meth:`shard_rows` to cut labels the same way."""
 
-    def __init__(self, model: TransformerDecoder, tp: TensorParallelContext, activation_checkpointing: bool = False):
+    def __init__(self, model: TransformerDecoder, tp: TensorParallelContext, activation_checkpointing: bool = False, prepare_layer=None):
         super().__init__()
         self.tp = tp
         self.tok_embeddings, self.norm, self.output = model.tok_embeddings, model.norm, model.output
         layers = []
-        for layer in model.layers:
+        for i, layer in enumerate(model.layers):
             inner = getattr(layer, "inner", layer)  # unwrap activation-checkpoint wrappers
             if not isinstance(inner, TransformerSelfAttentionLayer):
                 raise NotImplementedError(f"tensor parallelism supports self-attention decoder layers, got {type(inner).__name__}")
+            if prepare_layer is not None:  # the layer gets storage and values only now; its full weights are dropped right after slicing
+                prepare_layer(inner, f"layers.{i}.")
             layers.append(TPLayer(inner, tp))
+            _release_full_weights(inner)
+        if prepare_layer is not None:
+            for name in ("tok_embeddings", "norm", "output"):
+                if isinstance(getattr(model, name), nn.Module):  # a tied output projection has no storage of its own
+                    prepare_layer(getattr(model, name), f"{name}.")
         self.layers = nn.ModuleList(layers)
         self.max_seq_len = model.max_seq_len
         self.skip_output_layer = model.skip_output_layer
@@ -422,21 +429,24 @@ class TPDecoder(nn.Module):
         return out
 
 
-def tensor_parallelize(model: TransformerDecoder, tp: TensorParallelContext, activation_checkpointing: bool = False) -> TPDecoder:
-    """Build the tensor-parallel model from a fully materialised (every rank: identical) decoder.  The full
-    projection weights are released as each layer is converted."""
-    out = TPDecoder(model, tp, activation_checkpointing)
-    for layer in model.layers:
-        inner = getattr(layer, "inner", layer)
-        projs = [inner.attn.q_proj, inner.attn.k_proj, inner.attn.v_proj, inner.attn.output_proj]
-        mlp = inner.mlp
-        if hasattr(mlp, "experts"):  # mixture of experts: the full expert stacks and the shared expert were copied in slices
-            for name in ("gate_proj", "up_proj", "down_proj"):
-                w = getattr(mlp.experts, name)
-                w.data = torch.empty(0, dtype=w.dtype, device=w.device)
-            mlp = mlp.shared_expert
-        if mlp is not None:
-            projs += [mlp.w1, mlp.w2, mlp.w3]
-        for proj in projs:
-            proj.weight.data = torch.empty(0, dtype=proj.weight.dtype, device=proj.weight.device)
-    return out
+def _release_full_weights(inner: nn.Module) -> None:
+    """Drop the unsharded projection weights of a converted layer (their slices were copied)."""
+    projs = [inner.attn.q_proj, inner.attn.k_proj, inner.attn.v_proj, inner.attn.output_proj]
+    mlp = inner.mlp
+    if hasattr(mlp, "experts"):  # mixture of experts: the full expert stacks and the shared expert were copied in slices
+        for name in ("gate_proj", "up_proj", "down_proj"):
+            w = getattr(mlp.experts, name)
+            w.data = torch.empty(0, dtype=w.dtype, device=w.device)
+        mlp = mlp.shared_expert
+    if mlp is not None:
+        projs += [mlp.w1, mlp.w2, mlp.w3]
+    for proj in projs:
+        proj.weight.data = torch.empty(0, dtype=proj.weight.dtype, device=proj.weight.device)
+
+
+def tensor_parallelize(model: TransformerDecoder, tp: TensorParallelContext, activation_checkpointing: bool = False, prepare_layer=None) -> TPDecoder:
+    """Build the tensor-parallel model from a decoder that is either fully materialised (every rank: identical) or still on the
+    meta device; in the second case ``prepare_layer(module, prefix)`` (e.g. :class:`training.LayerwisePreparer`) gives each
+    layer storage and values right before it is sliced.  Full projection weights are released as each layer is converted, so
+    at most one unsharded layer is alive at a time."""
+    return TPDecoder(model, tp, activation_checkpointing, prepare_layer)

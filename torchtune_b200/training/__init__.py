@@ -43,6 +43,7 @@ from ._activation_offloading import NoOpManager, OffloadActivations, get_act_off
 from ._profiler import DEFAULT_PROFILE_DIR, DEFAULT_PROFILER_ACTIVITIES, DEFAULT_SCHEDULE, DEFAULT_TRACE_OPTS, PROFILER_KEY, DummyProfiler, setup_torch_profiler
 from ._distributed import (
     VALID_BACKENDS_FOR_MEMORY_STATS,
+    LayerwisePreparer,
     ParallelDims,
     gather_cpu_state_dict,
     get_distributed_backend,

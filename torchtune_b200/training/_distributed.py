@@ -91,6 +91,45 @@ def materialize(model: nn.Module, device: torch.device) -> nn.Module:
     return model
 
 
+class LayerwisePreparer:
+    """Gives storage and values to one sub-module at a time of a model built under ``torch.device('meta')``.
+
+    The tensor- and expert-parallel conversions call it with every decoder layer right before they slice that layer
+    (``prepare(module, "layers.3.")``) and once more for what is not a layer, so a model far larger than one GPU (70B dense,
+    109B mixture of experts) never exists in full: at most one unsharded layer is alive next to the shards.  Values come
+    from a full checkpoint state dict (``state_dict``; keys are model-level names) or, without one, from
+    ``normal(0, init_std)`` drawn from a generator seeded by ``seed`` and the module's name — identical on every rank, so the
+    ranks' shards are slices of the same matrices."""
+
+    def __init__(self, device: torch.device, state_dict: Optional[Dict[str, Any]] = None, init_std: float = 0.02, seed: int = 1234):
+        self.device, self.state_dict, self.init_std, self.seed = device, state_dict, init_std, seed
+
+    def __call__(self, module: nn.Module, prefix: str = "") -> nn.Module:
+        if any(t.is_meta for t in list(module.parameters()) + list(module.buffers())):
+            module.to_empty(device=self.device)
+            with self.device:
+                for m in module.modules():
+                    if hasattr(m, "rope_init"):
+                        m.rope_init()
+        if self.state_dict is not None:
+            own = {k[len(prefix):]: v for k, v in self.state_dict.items() if k.startswith(prefix)} if prefix else {
+                k: v for k, v in self.state_dict.items() if k in module.state_dict()}
+            module.load_state_dict(own, strict=bool(prefix))
+            return module
+        import zlib
+
+        gen = torch.Generator(device=self.device).manual_seed(self.seed + zlib.crc32(prefix.encode()))
+        with torch.no_grad():
+            for name, p in module.named_parameters():
+                if p.dim() > 1:
+                    p.normal_(0.0, self.init_std, generator=gen)
+                elif "scale" in name or "norm" in name:
+                    p.fill_(1.0)
+                else:
+                    p.zero_()
+        return module
+
+
 def load_from_full_model_state_dict(model: nn.Module, full_sd: Dict[str, Any], device: torch.device, strict: bool = False, cpu_offload: bool = False):
     """Load a full (unsharded, CPU) state dict into a resident model; every rank reads the
     same tensors, so no collective is needed.  NF4 base weights are quantised on the way in

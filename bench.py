@@ -157,10 +157,16 @@ def run_ours(args) -> dict:
 
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-    parallel = par.DataParallelEngine(device=device)  # world 1: same flat store, no peers
+    zero3 = args.variant == "zero3"
+    if zero3:  # every parameter, gradient and moment sharded (what the reference's FSDP2 arm does); off-headline until it wins
+        from torchtune_b200.parallel.zero3 import Zero3Engine
+
+        parallel = Zero3Engine(device)
+    else:
+        parallel = par.DataParallelEngine(device=device)  # world 1: same flat store, no peers
     torch.manual_seed(1234)  # identical initial weights on every rank
-    with training.set_default_dtype(torch.bfloat16), device:
-        if args.variant == "full":
+    with training.set_default_dtype(torch.bfloat16), (torch.device("meta") if zero3 else device):
+        if args.variant in ("full", "zero3"):
             model = llama3_1(**MODEL)
         else:  # off-headline variants: LoRA r=64 / alpha=128 on q, k, v, output projections and the MLP; QLoRA adds an NF4 base
             from torchtune_b200.models.llama3_1 import lora_llama3_1_8b
@@ -169,16 +175,17 @@ def run_ours(args) -> dict:
             model = lora_llama3_1_8b(lora_attn_modules=["q_proj", "k_proj", "v_proj", "output_proj"], apply_lora_to_mlp=True, lora_rank=64, lora_alpha=128,
                                      quantize_base=args.variant == "qlora")
         for name, p in model.named_parameters():
-            if p.dim() > 1 and p.is_floating_point() and "lora_b" not in name:
+            if p.dim() > 1 and p.is_floating_point() and "lora_b" not in name and not p.is_meta:
                 torch.nn.init.normal_(p, std=0.02)
-    if args.variant != "full":
+    if args.variant not in ("full", "zero3"):
         set_trainable_params(model, get_adapter_params(model))
     if args.fp8:  # optional variant, never the default: decoder linears (not the output head) on the fp8 tensor cores
         training.convert_to_float8_training(model, "tensorwise")
     training.set_activation_checkpointing(model, {TransformerSelfAttentionLayer})
     loss_fn = LinearCrossEntropyLoss(num_output_chunks=8)
     loss_fn.set_model_output(model)
-    model = parallel.prepare(model)
+    # zero3: the model is still on the meta device; every layer is given normal(0, 0.02) values right before it is cut into shards
+    model = parallel.prepare(model, training.LayerwisePreparer(device)) if zero3 else parallel.prepare(model)
     optimizer = parallel.build_optimizer(model, lr=LR)
     step = TrainStep(model, loss_fn, optimizer, device, parallel=parallel)
 
@@ -247,13 +254,13 @@ def run_ours(args) -> dict:
         "data": "synthetic uniform tokens, random-init weights",
         "impl": "ours",
         "config": {
-            "model": "llama3_1_8b" if args.variant == "full" else f"llama3_1_8b {args.variant} r64 (variant, not the headline)",
+            "model": "llama3_1_8b" if args.variant in ("full", "zero3") else f"llama3_1_8b {args.variant} r64 (variant, not the headline)",
             "global_batch": BATCH_PER_GPU * world,
             "seq_len": SEQ_LEN,
             "doc_len": DOC_LEN,
-            "parallelism": f"dp{world}" if world > 1 else "single",
+            "parallelism": (f"zero3 x{world} (parameters, gradients and moments sharded; per-layer peer-memory gather)" if zero3 else f"dp{world}") if world > 1 else "single",
             "activation_checkpointing": True,
-            "optimizer": "AdamW lr 2e-5, fused reduce+update+broadcast kernel over flat peer buffers",
+            "optimizer": "AdamW lr 2e-5, fused reduce-scatter+update kernel per layer during backward" if zero3 else "AdamW lr 2e-5, fused reduce+update+broadcast kernel over flat peer buffers",
             "l2": "inputs larger than L2 (16 GB of weights streamed every step)",
         },
         "clocks": clocks,
@@ -262,6 +269,8 @@ def run_ours(args) -> dict:
         "peak_mem_gib": round(peak_gib, 2),
         "final_loss": final_loss,
     }
+    if zero3:
+        parallel.shutdown()
     if world > 1:
         dist.destroy_process_group()
     return out if rank == 0 else {}
@@ -473,7 +482,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--variant", choices=["full", "lora", "qlora", "tp"], default="full", help="off-headline variants; the headline is always the full fine-tune")
+    ap.add_argument("--variant", choices=["full", "zero3", "lora", "qlora", "tp"], default="full", help="off-headline variants; the headline is always the full fine-tune")
     ap.add_argument("--config", choices=["8b"] + sorted(SHARDED_CONFIGS), default="8b", help="8b: the headline (Llama-3.1-8B); the others are the 70B tensor-parallel and Scout expert-parallel configurations")
     ap.add_argument("--debug-layers", type=int, default=0, help="functional check of a --config on few GPUs: build only this many layers (the printed line is marked invalid)")
     ap.add_argument("--fp8", action="store_true", help="variant: fp8 decoder linears (the headline number is always bf16)")

@@ -170,3 +170,74 @@ def test_grouped_matmul_matches_loop(counts, K, N):
     assert _rel_err(y, yf) < 1e-2
     assert _rel_err(x.grad, xf.grad) < 1e-2
     assert _rel_err(w.grad, wf.grad) < 2e-2
+
+
+# ----------------------------------------------------------------------------- sharded-parameter (ZeRO-3) engine on one GPU
+@pytest.mark.parametrize("mode", ["fused", "deferred"])
+def test_zero3_engine_single_gpu_tracks_fp32_adamw(mode):
+    """World size 1 runs every kernel of the engine (bucket gather into a released buffer, reduce → AdamW on the shard store, the
+    deferred update after clipping) with nothing to wait for: three bf16 steps must follow an fp32 AdamW run, and no parameter
+    may stay resident between steps."""
+    from torchtune_b200 import training
+    from torchtune_b200.models.llama3_1 import llama3_1
+    from torchtune_b200.modules import TransformerSelfAttentionLayer
+    from torchtune_b200.parallel.zero3 import Zero3Engine
+
+    arch = dict(vocab_size=512, num_layers=3, num_heads=4, num_kv_heads=2, embed_dim=256, max_seq_len=128, intermediate_dim=512)
+    dev = torch.device("cuda")
+    torch.manual_seed(0)
+    ref = llama3_1(**arch).to(dev)
+    for p in ref.parameters():
+        if p.dim() > 1:
+            torch.nn.init.normal_(p, std=0.05)
+    with training.set_default_dtype(torch.bfloat16), dev:
+        model = llama3_1(**arch)
+    model.load_state_dict({k: v.bfloat16() for k, v in ref.state_dict().items()})
+    ref.load_state_dict({k: v.float() for k, v in model.state_dict().items()})  # same bf16-rounded starting point
+    training.set_activation_checkpointing(model, {TransformerSelfAttentionLayer})
+    engine = Zero3Engine(dev)
+    model = engine.prepare(model)
+    opt = engine.build_optimizer(model, lr=1e-3, weight_decay=0.01)
+    ref_opt = torch.optim.AdamW(ref.parameters(), lr=1e-3, weight_decay=0.01)
+    clip = 1.0 if mode == "deferred" else None
+    g = torch.Generator(device="cuda").manual_seed(1)
+    for step in range(3):
+        tokens = torch.randint(0, 512, (2, 128), generator=g, device=dev)
+        labels = torch.randint(0, 512, (2, 128), generator=g, device=dev)
+        loss = F.cross_entropy(model(tokens).float().reshape(-1, 512), labels.reshape(-1), reduction="sum")
+        if mode == "fused":
+            assert engine.arm_backward_overlap(opt, 1.0 / 256, None)
+        loss.backward()
+        norm = engine.optimizer_step(model, opt, 1.0 / 256, clip)
+        want = F.cross_entropy(ref(tokens).reshape(-1, 512), labels.reshape(-1), reduction="sum")
+        (want / 256).backward()
+        if clip is not None:
+            want_norm = torch.nn.utils.clip_grad_norm_(ref.parameters(), clip)
+            assert abs(float(norm) - float(want_norm)) / float(want_norm) < 3e-2
+        ref_opt.step()
+        ref_opt.zero_grad()
+        assert abs(loss.item() - want.item()) / want.item() < 2e-2, (step, loss.item(), want.item())
+        assert all(p.untyped_storage().size() == 0 for p in model.parameters())
+    got = engine.full_state_dict(model)
+    for k, v in ref.state_dict().items():
+        assert _rel_err(got[k], v.cpu()) < 2e-2, k
+    engine.shutdown()
+
+
+def test_zero3_gather_kernel_emulated_ranks():
+    """``ttb_zero3_gather`` with the shards of four ranks held in four buffers of one device (peer mappings on a real group)."""
+    import ctypes
+
+    from torchtune_b200.ops._lib import check, lib, stream_ptr
+    from torchtune_b200.parallel.dp import _declare_dp
+
+    L = lib()
+    _declare_dp(L)
+    world, piece = 4, 8 * 1031
+    shards = [torch.randn(piece, device="cuda").bfloat16() for _ in range(world)]
+    ptrs = (ctypes.c_void_p * world)(*[s.data_ptr() for s in shards])
+    for rank in range(world):
+        for ctas in (0, 3):
+            dst = torch.zeros(world * piece, dtype=torch.bfloat16, device="cuda")
+            check(L.ttb_zero3_gather(ptrs, world, rank, piece, dst.data_ptr(), None, 0, 0, None, ctas, stream_ptr()), "gather")
+            assert torch.equal(dst, torch.cat(shards))

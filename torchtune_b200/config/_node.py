@@ -21,6 +21,31 @@ _INTERP = re.compile(r"\$\{([^${}]+)\}")
 _RESOLVERS: Dict[str, Callable[..., Any]] = {}
 
 
+def _arithmetic(expr: Any) -> Any:
+    """``${eval:'<expr>'}``: numbers combined with ``+ - * / // % **`` and parentheses (the async GRPO configs derive queue and
+    batch sizes this way).  Evaluated on the syntax tree — names, calls and attribute access are rejected."""
+    import ast
+    import operator as op
+
+    ops = {ast.Add: op.add, ast.Sub: op.sub, ast.Mult: op.mul, ast.Div: op.truediv, ast.FloorDiv: op.floordiv, ast.Mod: op.mod, ast.Pow: op.pow, ast.USub: op.neg, ast.UAdd: op.pos}
+
+    def ev(node):
+        if isinstance(node, ast.Constant) and isinstance(node.value, (int, float)):
+            return node.value
+        if isinstance(node, ast.BinOp) and type(node.op) in ops:
+            return ops[type(node.op)](ev(node.left), ev(node.right))
+        if isinstance(node, ast.UnaryOp) and type(node.op) in ops:
+            return ops[type(node.op)](ev(node.operand))
+        raise InterpolationError(f"eval resolver accepts arithmetic on numbers only, got {expr!r}")
+
+    if isinstance(expr, (int, float)):
+        return expr
+    return ev(ast.parse(str(expr).strip().strip("'\""), mode="eval").body)
+
+
+_RESOLVERS["eval"] = _arithmetic
+
+
 class ConfigKeyError(KeyError, AttributeError):
     """Raised for missing keys through either access style."""
 

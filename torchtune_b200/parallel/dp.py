@@ -442,7 +442,7 @@ class DataParallelEngine:
         self.min_world_for_overlap = int(os.environ.get("TTB_DP_OVERLAP_MIN_WORLD", "1000000"))
         # CTAs of a bucket kernel that runs beside the backward GEMMs (NVLink-bound: a few dozen CTAs saturate the links and leave
         # HBM bandwidth and issue slots to the GEMMs); 0 = the full grid
-        self.overlap_ctas = int(os.environ.get("TTB_DP_OVERLAP_CTAS", "48"))
+        self.overlap_ctas = int(os.environ.get("TTB_DP_OVERLAP_CTAS", "0")) or max(48, 592 // max(self.world, 1))
         self._barrier_epoch = 0
 
     # sizes the recipes ask for ------------------------------------------------------------

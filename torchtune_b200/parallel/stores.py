@@ -53,6 +53,8 @@ class MultiStoreAdamW:
         for spec in self.specs:
             world, rank = spec.size()
             flat = FlatParameters(spec.params, world, device, spec.group, min_bucket_numel=1 << 22)
+            if device.type == "cuda":
+                torch.cuda.empty_cache()  # the parameters' old storage goes back to the driver before the next store is allocated
             self.flats.append(flat)
             self.opts.append(ShardedAdamW(flat, rank, world, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, group=None if spec.group is SOLO else spec.group))
         self.last_grad_norm: Optional[torch.Tensor] = None

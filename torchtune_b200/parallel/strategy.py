@@ -194,9 +194,11 @@ class ParallelStrategy(DataParallelEngine):
         self.cp = None  # ContextParallelContext, created in shard_model
         self._replica_group = None  # ranks holding the same tensor- / expert-parallel shard (None: a single replica)
         self._stores = None  # MultiStoreAdamW of a sharded model (fused optimizer over two flat stores)
-        self.zero3 = None  # ShardedWeightContext when `shard_parameters: True` (linear weights sharded over the ranks)
-        self._shard_parameters = bool(get("shard_parameters", False))
-        if self._shard_parameters and (self.dims.tp_enabled or self.ep_dim > 1 or self.dims.cp_enabled):
+        self.zero3 = None  # ShardedWeightContext: linear weights sharded, fused weight-gather GEMM (`shard_parameters: linear`, LoRA bases)
+        self.z3 = None  # Zero3Engine: every trainable parameter sharded (`shard_parameters: True` with an AdamW optimizer)
+        self._shard_parameters = bool(get("shard_parameters", False)) and str(get("shard_parameters")).lower() not in ("false", "none", "0", "")
+        self._shard_mode = str(get("shard_parameters", "")).lower()
+        if (self._shard_parameters or self._shard_mode == "linear") and (self.dims.tp_enabled or self.ep_dim > 1 or self.dims.cp_enabled):
             raise NotImplementedError("shard_parameters combines with plain data parallelism only")
         self._cfg = cfg
         self._cpu_offload = bool(get("fsdp_cpu_offload", False))
@@ -349,6 +351,22 @@ class ParallelStrategy(DataParallelEngine):
             if is_lora:
                 raise NotImplementedError("expert parallelism is implemented for full fine-tuning")
             return self._shard_model_ep(model, cfg)
+        if self._shard_parameters and self._wants_full_sharding(cfg, is_lora):
+            from .zero3 import Zero3Engine
+
+            if self.world > 1:  # identical initial values on every rank before they are cut into shards
+                for p in model.parameters():
+                    if p.device.type == "cpu" and p.dtype == torch.bfloat16:
+                        tmp = p.data.float()
+                        dist.broadcast(tmp, src=0)
+                        p.data.copy_(tmp)
+                    else:
+                        dist.broadcast(p.data, src=0)
+            self.z3 = Zero3Engine(self.device, None)
+            model = self.z3.prepare(model)
+            if self.rank == 0:
+                _log.info(f"ZeRO-3 engine: every trainable parameter is sharded over {self.world} ranks ({self.z3.nb} buckets, {self.z3.sp.shard} elements per rank)")
+            return model
         if self._shard_parameters:
             from .fsdp import shard_linear_weights
 
@@ -380,6 +398,30 @@ class ParallelStrategy(DataParallelEngine):
                 dist.broadcast(flat, src=0)
         return model
 
+    def _wants_full_sharding(self, cfg, is_lora: bool) -> bool:
+        """Every parameter sharded (ZeRO-3 engine) for full fine-tuning with an AdamW-family optimizer and one parameter dtype;
+        ``shard_parameters: linear``, LoRA (whose frozen base is what needs sharding) and other optimizers keep the
+        sharded-linear-weight path."""
+        if is_lora or self._shard_mode == "linear":
+            return False
+        get = cfg.get if hasattr(cfg, "get") else (lambda k, d=None: d)
+        opt = get("optimizer")
+        target = opt.get("_component_", "torch.optim.AdamW") if hasattr(opt, "get") else "torch.optim.AdamW"
+        target = target.replace("torchtune.", "torchtune_b200.", 1) if target.startswith("torchtune.") else target
+        if get("optimizer_in_bwd", False):
+            return False
+        return target in _FUSED_ADAMW and not (hasattr(opt, "get") and (opt.get("amsgrad", False) or opt.get("maximize", False)))
+
+    def wants_backward_overlap(self, optimizer) -> bool:
+        if self.z3 is not None:
+            return self.z3.wants_backward_overlap(optimizer)
+        return super().wants_backward_overlap(optimizer)
+
+    def arm_backward_overlap(self, optimizer, grad_scale, clip_grad_norm: Optional[float] = None) -> bool:
+        if self.z3 is not None:
+            return self.z3.arm_backward_overlap(optimizer, grad_scale, clip_grad_norm)
+        return super().arm_backward_overlap(optimizer, grad_scale, clip_grad_norm)
+
     # optimizer ---------------------------------------------------------------------------
     def _store_specs(self, model: nn.Module):
         """The two flat stores of a sharded model: parameters every rank holds (summed over the job) and this rank's shards
@@ -398,6 +440,15 @@ class ParallelStrategy(DataParallelEngine):
                 StoreSpec("local", [(n, p) for n, p in named if id(p) not in replicated], local_group)], shard_group
 
     def build_optimizer(self, model: nn.Module, cfg_optimizer=None, opt_state: Optional[Dict[str, Any]] = None, **kwargs: Any):
+        if self.z3 is not None:
+            params = {k: v for k, v in cfg_optimizer.items() if k != "_component_"} if hasattr(cfg_optimizer, "items") else dict(kwargs)
+            if isinstance(cfg_optimizer, (int, float)):
+                params["lr"] = float(cfg_optimizer)
+            opt = self.z3.build_optimizer(model, lr=float(params.get("lr", 1e-3)), betas=tuple(params.get("betas", (0.9, 0.999))), eps=float(params.get("eps", 1e-8)),
+                                          weight_decay=float(params.get("weight_decay", 1e-2)))
+            if opt_state:
+                opt.load_full_state_dict(opt_state)
+            return opt
         if self.tp is not None or self.ep is not None or self.zero3 is not None:
             from .. import config
 
@@ -454,6 +505,8 @@ class ParallelStrategy(DataParallelEngine):
 
     def optimizer_step(self, model: nn.Module, optimizer, grad_scale, clip_grad_norm: Optional[float] = None):
         clip = float(clip_grad_norm) if clip_grad_norm is not None else None
+        if self.z3 is not None:
+            return self.z3.optimizer_step(model, optimizer, grad_scale, clip)
         if self.tp is not None or self.ep is not None or self.zero3 is not None:
             from .stores import MultiStoreAdamW
 
@@ -480,6 +533,9 @@ class ParallelStrategy(DataParallelEngine):
     def gather_full_state_dict(self, model: nn.Module) -> Dict[str, Any]:
         from ..training._distributed import gather_cpu_state_dict
 
+        if self.z3 is not None:
+            full = self.z3.full_state_dict(model)  # collective: every rank gathers every bucket
+            return full if self.rank == 0 else {}
         if self.tp is not None or self.ep is not None or self.zero3 is not None:
             full = model.full_state_dict()  # collective: every rank takes part
             return {k: v.cpu() for k, v in full.items()} if self.rank == 0 else {}
@@ -505,6 +561,9 @@ class ParallelStrategy(DataParallelEngine):
         if self.zero3 is not None:
             self.zero3.close()
             self.zero3 = None
+        if self.z3 is not None:
+            self.z3.shutdown()
+            self.z3 = None
         super().shutdown()
         if self._owns_group and dist.is_initialized():
             dist.destroy_process_group()

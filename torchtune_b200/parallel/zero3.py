@@ -53,7 +53,10 @@ def _bf16_safe_all_reduce(t: torch.Tensor, group) -> None:
 class ShardedParameters(FlatLayout):
     """Storage side of the engine: the shard store, the two gradient slots and one releasable full buffer per bucket."""
 
-    def __init__(self, params: List[Tuple[str, nn.Parameter]], world: int, rank: int, device: torch.device, group=None):
+    def __init__(self, params: List[Tuple[str, nn.Parameter]], world: int, rank: int, device: torch.device, group=None, materialize=None):
+        """``materialize(bucket) -> {name: parameter}`` (optional): for a model still on the meta device, gives the bucket's
+        modules storage and values and returns their (new) parameter objects; buckets are then materialised one at a time and cut
+        into shards at once, so the full model never exists on the device."""
         super().__init__(params, world)
         self.rank, self.device = rank, device
         esize = torch.empty(0, dtype=self.dtype).element_size()
@@ -70,6 +73,13 @@ class ShardedParameters(FlatLayout):
         index = {id(p): i for i, p in enumerate(self.params)}
         with torch.no_grad():
             for b, (start, size) in enumerate(self.buckets):
+                if materialize is not None:
+                    fresh = materialize(b)
+                    for j, p in enumerate(self.bucket_params[b]):
+                        i = index.pop(id(p))
+                        new = fresh[self.names[i]]
+                        self.params[i] = self.bucket_params[b][j] = new
+                        index[id(new)] = i
                 full = torch.zeros(size, dtype=self.dtype, device=device)
                 slot = self.grad_slots[b % 2].tensor(self.dtype, self.max_bucket)
                 cursor, gaps = 0, []
@@ -256,8 +266,10 @@ class Zero3Engine:
         self._comm = None
         self._flags: Optional[PeerBuffer] = None
         self._token = torch.zeros(1, device=device if self.cuda else "cpu")
-        # CTAs of the kernels that run beside the layers' GEMMs (they are NVLink-bound); 0 = full grid
-        self.comm_ctas = int(os.environ.get("TTB_ZERO3_CTAS", "48"))
+        # CTAs of the kernels that run beside the layers' GEMMs; 0 = full grid.  The bytes a rank moves per bucket shrink with the
+        # world size (1/world of the gradients and moments, NVLink-bound pulls), so fewer CTAs keep up on more ranks and leave
+        # more of the SMs' issue slots and of the HBM to the GEMMs.
+        self.comm_ctas = int(os.environ.get("TTB_ZERO3_CTAS", "0")) or max(48, 592 // max(self.world, 1))
 
     dp_size = property(lambda self: self.world)
     dp_rank = property(lambda self: self.rank)
@@ -265,9 +277,36 @@ class Zero3Engine:
     min_seq_len_divisor = 1
 
     # ------------------------------------------------------------------ setup
-    def prepare(self, model: nn.Module) -> nn.Module:
+    def prepare(self, model: nn.Module, prepare_layer=None) -> nn.Module:
+        """Shard ``model`` in place.  ``prepare_layer(module, prefix)`` (e.g. :class:`training.LayerwisePreparer`): the model is still
+        on the meta device and every bucket's modules get storage and values right before they are cut into shards."""
         named = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
-        self.sp = sp = ShardedParameters(named, self.world, self.rank, self.device, self.group)
+        materialize = None
+        if prepare_layer is not None:
+            layout = FlatLayout(named, self.world)
+
+            def materialize(b: int) -> Dict[str, nn.Parameter]:
+                key = layout.bucket_keys[b]
+                if key is not None:
+                    prepare_layer(model.get_submodule(key), key + ".")
+                else:  # direct owner modules of the parameters before / after the layers
+                    owners = {n.rsplit(".", 1)[0] if "." in n else "" for n, p in named if any(p is q for q in layout.bucket_params[b])}
+                    for path in sorted(owners):
+                        prepare_layer(model.get_submodule(path) if path else model, path + "." if path else "")
+                return dict(model.named_parameters())
+
+        self.sp = sp = ShardedParameters(named, self.world, self.rank, self.device, self.group, materialize)
+        if prepare_layer is not None:
+            for mod in model.modules():  # buffers outside every bucket's modules (e.g. a shared RoPE table)
+                meta = [k for k, buf in mod._buffers.items() if buf is not None and buf.is_meta]
+                for k in meta:
+                    mod._buffers[k] = torch.empty_like(mod._buffers[k], device=self.device)
+                if meta and hasattr(mod, "rope_init"):
+                    with self.device:
+                        mod.rope_init()
+            left = [n for n, p in model.named_parameters() if p.is_meta]
+            if left:
+                raise NotImplementedError(f"frozen parameters of a meta-device model are not materialised by the sharded-parameter engine: {left[:4]}")
         nb = len(sp.buckets)
         self.nb = nb
         self._gather_event: List[Any] = [None] * nb
@@ -290,7 +329,8 @@ class Zero3Engine:
             if 3 * nb >= L.ttb_dp_max_buckets():
                 raise ValueError(f"{nb} parameter buckets exceed the flag array of the sharded-parameter engine")
             _cuda.enable_direct_wgrad(True)
-            self._comm = torch.cuda.Stream(device=self.device)
+            self._comm = torch.cuda.Stream(device=self.device)  # reduce-scatter → AdamW kernels
+            self._gstream = torch.cuda.Stream(device=self.device)  # parameter gathers (never queued behind a reduction)
             self._flags = PeerBuffer(self.world * L.ttb_dp_max_buckets() * 4, self.device, self.group)
         self._install_hooks(model)
         self._model = model
@@ -423,14 +463,16 @@ class Zero3Engine:
         from ..ops._lib import check, err_word, lib, stream_ptr
 
         main = torch.cuda.current_stream(self.device)
-        self._comm.wait_stream(main)  # the buffer may be a block the compute stream has just freed; also orders behind updates issued there
-        with torch.cuda.stream(self._comm):
+        self._gstream.wait_stream(main)  # the buffer may be a block the compute stream has just freed; also orders behind updates issued there
+        if self._reduce_event[b] is not None:
+            self._gstream.wait_event(self._reduce_event[b])  # this rank's own update of the bucket's shard
+        with torch.cuda.stream(self._gstream):
             ptrs = (ctypes.c_void_p * self.world)(*[p + sp.esize * soff for p in sp.store.peer_ptrs])
             wait = self._flags.local_ptr if (self.world > 1 and self._updates[b] > 0) else None
             check(lib().ttb_zero3_gather(ptrs, self.world, self.rank, piece, full.data_ptr(), wait, 3 * b + self.UPD, self._updates[b],
                                          err_word(self.device).data_ptr(), self.comm_ctas if self.world > 1 else 0, stream_ptr()), "zero3 gather")
             ev = torch.cuda.Event()
-            ev.record(self._comm)
+            ev.record(self._gstream)
         self._gather_event[b] = ev
 
     # ------------------------------------------------------------------ backward

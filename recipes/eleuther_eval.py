@@ -6,8 +6,11 @@
 Parity: recipes/eleuther_eval.py:60-580 of the reference (config keys ``tasks``, ``limit``,
 ``batch_size``, ``max_seq_length``, ``enable_kv_cache``, ``quantizer``, ``include_path``).
 Task names are run through the EleutherAI harness when it is installed; entries ending in
-``.jsonl`` are multiple-choice files scored by the built-in evaluator, which needs no extra
-package.  Both paths go through :class:`torchtune_b200.evaluation.EvalLM`.
+``.jsonl`` are files scored by the built-in evaluators, which need no extra package.  Text models
+go through :class:`torchtune_b200.evaluation.EvalLM` (multiple-choice log-likelihood tasks),
+vision-language models (deep-fusion, e.g. Llama-3.2-Vision with ``llama3_2_vision/11B_evaluation``)
+through :class:`torchtune_b200.evaluation.EvalVLM` (greedy generation from text + images; config
+keys ``image_tag``, ``max_images_per_sample``).
 """
 import sys
 import time
@@ -17,7 +20,8 @@ import torch
 
 from torchtune_b200 import config, training, utils
 from torchtune_b200.config import DictConfig
-from torchtune_b200.evaluation import EvalLM, evaluate_jsonl_task, run_lm_eval
+from torchtune_b200.evaluation import EvalLM, EvalVLM, evaluate_jsonl_task, evaluate_multimodal_jsonl, run_lm_eval, run_lm_eval_multimodal
+from torchtune_b200.modules.model_fusion import DeepFusionModel
 
 logger = utils.get_logger("DEBUG")
 
@@ -50,6 +54,13 @@ class EleutherEvalRecipe:
         self.logger.info(f"Model is initialized with precision {self.dtype}.")
         self.model = model.eval()
         self.tokenizer = config.instantiate(cfg.tokenizer)
+        self.multimodal = isinstance(self.model, DeepFusionModel)
+        if self.multimodal:
+            if mode is not None:
+                raise ValueError("quantized evaluation is implemented for text models")
+            self.eval_lm = EvalVLM(self.model, self.tokenizer, device=self.device, dtype=self.dtype, max_seq_length=self.max_seq_length, batch_size=self.batch_size,
+                                   image_tag=cfg.get("image_tag", "<image>"), max_images_per_sample=cfg.get("max_images_per_sample", 7))
+            return
         self.eval_lm = EvalLM(self.model, self.tokenizer, device=self.device, dtype=self.dtype, max_seq_length=self.max_seq_length, batch_size=self.batch_size, enable_kv_cache=self.enable_kv_cache)
 
     def evaluate(self) -> Dict[str, Any]:
@@ -58,10 +69,10 @@ class EleutherEvalRecipe:
         harness_tasks = [t for t in self.tasks if not str(t).endswith(".jsonl")]
         for t in self.tasks:
             if str(t).endswith(".jsonl"):
-                results[str(t)] = evaluate_jsonl_task(self.eval_lm, str(t), self.limit)
+                results[str(t)] = (evaluate_multimodal_jsonl if self.multimodal else evaluate_jsonl_task)(self.eval_lm, str(t), self.limit)
         if harness_tasks:
             self.logger.info(f"Running evaluation on the following tasks: {harness_tasks}")
-            out = run_lm_eval(self.eval_lm, harness_tasks, limit=self.limit, include_path=self.include_path)
+            out = (run_lm_eval_multimodal if self.multimodal else run_lm_eval)(self.eval_lm, harness_tasks, limit=self.limit, include_path=self.include_path)
             results.update(out.get("results", out))
         self.logger.info(f"Eval completed in {time.time() - t0:.02f} seconds.")
         if self.device.type == "cuda":

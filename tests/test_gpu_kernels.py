@@ -775,3 +775,70 @@ def test_peer_buffer_guard_regions_detect_writes_outside(monkeypatch):
     engine.flat.param_buf.check_guards()
     engine.flat.grad_buf.check_guards()
     engine.shutdown()
+
+
+def _attn_general(b, s, sk, hq, hkv, d, mask, softcap=0.0, seed=0, grads=True):
+    """Native attention against the fp32 PyTorch statement for query length ≠ key length, boolean masks and soft-capping."""
+    q = _rand(b, s, hq, d, seed=seed).requires_grad_(grads)
+    k = _rand(b, sk, hkv, d, seed=seed + 1).requires_grad_(grads)
+    v = _rand(b, sk, hkv, d, seed=seed + 2).requires_grad_(grads)
+    before = dict(ops.fallback_counts)
+    o = ops.attention(q, k, v, mask, softcap=softcap)
+    assert dict(ops.fallback_counts) == before, "the call left the sm_100a kernels"
+    qr, kr, vr = (t.detach().float().requires_grad_(grads) for t in (q, k, v))
+    orf = ref.attention(qr, kr, vr, causal=mask.causal, doc_ids=mask.doc_ids, chunk=mask.chunk, window=mask.window, bool_mask=mask.bool_mask, softcap=softcap)
+    _close(o, orf, 2e-2, 2e-2, "attn out")
+    if grads:
+        go = _rand(b, s, hq, d, seed=seed + 3)
+        o.backward(go)
+        orf.backward(go.float())
+        _close(v.grad, vr.grad, 3e-2, 3e-2, "attn dv")
+        _close(k.grad, kr.grad, 3e-2, 5e-2, "attn dk")
+        _close(q.grad, qr.grad, 3e-2, 5e-2, "attn dq")
+
+
+def test_attention_benchmark_shape_packed_512_token_documents():
+    """The headline benchmark's own attention call: 4 × 2048 tokens, 32 / 8 heads, documents of 512 tokens."""
+    doc_ids = torch.arange(4, dtype=torch.int32, device="cuda").repeat_interleave(512).view(1, 2048).expand(4, 2048).contiguous()
+    _attn_case(4, 2048, 32, 8, 128, AttentionMask(causal=True, doc_ids=doc_ids), seed=11)
+
+
+@pytest.mark.parametrize("d", [128, 64])
+def test_attention_cross_attention_unmasked_and_masked(d):
+    """Query length ≠ key length (Llama-3.2-Vision cross-attention): no mask, then a boolean mask that hides whole key ranges
+    per query (each text token sees the tiles of its own image only) including rows that see nothing."""
+    _attn_general(2, 200, 333, 8, 2, d, AttentionMask(causal=False))
+    g = torch.Generator().manual_seed(3)
+    m = torch.zeros(2, 200, 333, dtype=torch.bool)
+    for bi in range(2):
+        for start in range(0, 200, 50):
+            lo = int(torch.randint(0, 200, (1,), generator=g))
+            m[bi, start : start + 50, lo : lo + 120] = True
+    m[0, 7] = False  # a query without any visible key: output and gradients are zero
+    _attn_general(2, 200, 333, 8, 2, d, AttentionMask(causal=False, bool_mask=m.cuda()), seed=4)
+
+
+def test_attention_cached_decoding_steps():
+    """One and a few new tokens against a partly filled KV cache: boolean ``[b, s_q, max_seq]`` masks as the decoder builds them
+    (rows of the causal matrix picked by position), and the causal flag with fewer queries than keys."""
+    max_seq, filled = 640, 301
+    causal = torch.tril(torch.ones(max_seq, max_seq, dtype=torch.bool))
+    for s_q in (1, 5):
+        pos = torch.arange(filled - s_q, filled)
+        m = causal[pos].unsqueeze(0).expand(3, s_q, max_seq).contiguous().cuda()
+        _attn_general(3, s_q, max_seq, 8, 2, 128, AttentionMask(causal=False, bool_mask=m), seed=20 + s_q, grads=False)
+    _attn_general(2, 5, 261, 4, 4, 64, AttentionMask(causal=True), seed=30)
+
+
+def test_attention_arbitrary_boolean_mask_with_gradients():
+    g = torch.Generator().manual_seed(5)
+    m = torch.rand(2, 256, 256, generator=g) < 0.3
+    m |= torch.eye(256, dtype=torch.bool)
+    _attn_general(2, 256, 256, 4, 2, 128, AttentionMask(causal=False, bool_mask=m.cuda()), seed=40)
+
+
+@pytest.mark.parametrize("mask", [AttentionMask(causal=True), AttentionMask(causal=True, window=100)])
+def test_attention_softcap(mask):
+    """Gemma-2 style soft-capped scores (tanh inside the softmax warps; its derivative in the backward pass)."""
+    _attn_general(2, 384, 384, 4, 2, 128, mask, softcap=30.0, seed=50)
+    _attn_general(1, 200, 200, 4, 4, 64, mask, softcap=5.0, seed=51)

@@ -70,3 +70,36 @@ def test_eleuther_eval_recipe_jsonl(tmp_path, tune_path, monkeypatch, caplog):
     task.write_text("\n".join(json.dumps(d) for d in docs))
     run_tune(tune_path, f"run eleuther_eval --config eleuther_evaluation {common} tokenizer.path={sp} tasks=[{task}] batch_size=4 limit=5", monkeypatch)
     assert "acc_norm" in caplog.text and "'n': 5" in caplog.text
+
+
+def test_generate_v2_recipe_and_its_tensor_parallel_twin_decode_the_same_text(tmp_path, tune_path, monkeypatch, caplog):
+    """dev/generate_v2 on one process, then dev/generate_v2_distributed on two gloo ranks (decoder split over the ranks, per-rank
+    KV caches): greedy decoding must give the same completion."""
+    import os
+    import re
+    import subprocess
+    import sys
+
+    common, sp = _common(tmp_path)
+    args = f"{common} tokenizer.path={sp} tokenizer.max_seq_len=128 max_new_tokens=10 prompt.user=hello prompt.system=null temperature=0.0 top_k=null"
+    run_tune(tune_path, f"run dev/generate_v2 --config llama2/generation_v2 {args}", monkeypatch)
+    assert "tokens/sec" in caplog.text
+    single = re.findall(r"\n\n(.*)\n\n", caplog.text)[-1]
+    root = Path(tune_path).resolve().parents[2]
+    env = dict(os.environ, PYTHONPATH=str(root), MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="2")
+    res = subprocess.run([sys.executable, str(root / "tune"), "run", "--nnodes=1", "--nproc_per_node=2", "--master-addr=127.0.0.1", "--master-port=29597", "dev/generate_v2_distributed",
+                          "--config", "llama2/generation_v2"] + args.split(), cwd=str(root), env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert len(single) > 0 and f"\n\n{single}\n" in res.stdout + res.stderr, (single, (res.stdout + res.stderr)[-1500:])
+
+
+def test_prompt_to_messages_and_step_visibility():
+    from torchtune_b200.engine.inference import CachedDecoder, prompt_to_messages
+
+    msgs = prompt_to_messages({"system": "be brief", "user": {"text": "hi"}, "ipython": None})
+    assert [m.role for m in msgs] == ["system", "user", "assistant"] and msgs[-1].text_content == ""
+    with pytest.raises(ValueError):
+        prompt_to_messages({"user": {"image": "x.png"}})
+    dec = CachedDecoder(lambda *a, **k: None, torch.device("cpu"), total=6, temperature=0.0, top_k=None, stop_tokens=[])
+    assert dec.visibility(0, 3)[0].tolist() == torch.tril(torch.ones(6, 6, dtype=torch.bool))[:3].tolist()
+    assert dec.visibility(4, 1)[0, 0].tolist() == [True] * 5 + [False]

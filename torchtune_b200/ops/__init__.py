@@ -199,17 +199,19 @@ def attention(
 ) -> torch.Tensor:
     """Grouped-query attention on ``[b, s, h, d]`` without materialising expanded KV heads."""
     mask = mask if mask is not None else AttentionMask(causal=False)
-    if (
-        _native(q)
-        and mask.bool_mask is None
-        and dropout_p == 0.0
-        and q.shape[-1] in (64, 128)
-        and q.shape[1] == k.shape[1]
-    ):
-        from . import _cuda
+    if _native(q):
+        from . import _cuda_attention
 
-        return _cuda.attention(q, k, v, mask, scale, softcap)
-    _fallback("attention", _attention_fallback_reason(q, k, mask, dropout_p), q)
+        why = None
+        if dropout_p != 0.0:
+            why = "attention dropout"
+        elif q.shape[-1] not in (64, 128):
+            why = f"head_dim {q.shape[-1]}"
+        else:
+            why = _cuda_attention.unsupported_reason(q, k, mask)
+        if why is None:
+            return _cuda_attention.attention(q, k, v, mask, scale, softcap)
+        _fallback("attention", why, q)
     return reference.attention(
         q,
         k,
@@ -223,16 +225,6 @@ def attention(
         softcap=softcap,
         dropout_p=dropout_p,
     )
-
-
-def _attention_fallback_reason(q, k, mask, dropout_p) -> str:
-    if mask.bool_mask is not None:
-        return "dense boolean mask"
-    if dropout_p != 0.0:
-        return "attention dropout"
-    if q.shape[-1] not in (64, 128):
-        return f"head_dim {q.shape[-1]}"
-    return f"query length {q.shape[1]} differs from key length {k.shape[1]}"
 
 
 def linear_cross_entropy(

@@ -50,8 +50,9 @@ def _declare(L: ctypes.CDLL) -> None:
     L.ttb_adamw.argtypes = [vp, i32, i64, i32, f32, f32, f32, f32, f32, f32, f32, vp, f32, vp]
     L.ttb_grad_sumsq.argtypes = [vp, i32, i64, i32, vp, vp]
     L.ttb_softmax_ce.argtypes = [vp, vp, vp, vp, i32, i32, i64, i64, i32, vp]
-    L.ttb_attn_fwd.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, vp, vp]
-    L.ttb_attn_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, vp, vp]
+    L.ttb_attn_fwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, i32, f32, vp, vp]
+    L.ttb_attn_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, i32, f32, vp, vp]
+    L.ttb_attn_bwd.restype = i32
     L.ttb_attn_fwd.restype = i32
     L.ttb_ensure_device.argtypes = [i32]
     L.ttb_gemm_grouped_bf16.argtypes = [vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, i64, i64, i64, i64, vp, vp]

@@ -26,9 +26,14 @@ static constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 struct AttnParams {
   int b, s, hq, hkv, d;
+  int sk;            // key / value length (s is the query length; cross-attention and cached decoding have sk != s)
   float scale;       // softmax scale (1/sqrt(d) by default)
-  int causal;
+  int causal;        // hi[q] = q when no `hi` array is given (requires sk == s)
   const int* lo;     // [b, s] lower visible key index per query, or nullptr (= 0)
+  const int* hi;     // [b, s] upper visible key index per query, or nullptr (= q if causal, else sk - 1)
+  const uint8_t* kmask;  // [b, s, sk] 1 = visible, or nullptr; applied on top of lo / hi (arbitrary boolean masks)
+  int monotone;      // lo and hi are non-decreasing along the sequence (structured masks): block ranges can be cut at tile borders
+  float softcap;     // > 0: scores pass through softcap * tanh(score / softcap) before the softmax
   __nv_bfloat16* o;  // fwd out [b, s, hq, d]
   float* lse;        // [b, hq, s] log2-domain log-sum-exp of scaled scores
   // backward only
@@ -57,13 +62,20 @@ __device__ __forceinline__ uint32_t swz_offset(int row, int col) {
   return panel * kPanelBytes + row * 128 + ((chunk ^ (row & 7)) << 4) + (col & 7) * 2;
 }
 
+__device__ __forceinline__ float fast_tanh(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ void fail(volatile int* abort_flag, int* err, int code) {
   *abort_flag = 1;
   atomicExch(err, code);
 }
 
 // ===================================================================================== forward
-template <int D>
+// EXTRA compiles in soft-capping and the element-wise boolean mask; the plain instantiation keeps the hot loop free of both.
+template <int D, bool EXTRA>
 __global__ void __launch_bounds__(256, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, AttnParams p) {
@@ -85,17 +97,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* pv_done = bars + 10;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* range = reinterpret_cast<int*>(tmem_slot + 2);  // [0] smallest lo, [1] largest hi over the tile's rows
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qblk = blockIdx.x, h = blockIdx.y, bi = blockIdx.z;
   const int hk = h / (p.hq / p.hkv);
   const int q0 = qblk * kBlk;
-  const int row_base = bi * p.s;  // row of token 0 of this batch entry in the [b*s, h*d] view
+  const int row_base = bi * p.s;    // row of token 0 of this batch entry in the [b*s, h*d] view of Q / O
+  const int krow_base = bi * p.sk;  // the same for K / V
+  const int q_last = min(q0 + kBlk, p.s) - 1;
 
-  int kv_begin = 0;
-  if (p.lo != nullptr) kv_begin = p.lo[row_base + q0] / kBlk;
-  const int kv_end_tok = p.causal ? min(p.s, q0 + kBlk) : p.s;
-  const int n_blocks = (kv_end_tok + kBlk - 1) / kBlk - kv_begin;
+  // Key blocks this tile visits: [min lo, max hi] over its rows.  Structured masks are monotone, so the first and last row
+  // give the bounds; arbitrary masks reduce over all rows (threads 128..255 below).
+  if (threadIdx.x == 0) {
+    range[0] = (p.lo != nullptr && p.monotone) ? p.lo[row_base + q0] : (p.lo != nullptr ? p.sk : 0);
+    range[1] = (p.hi != nullptr) ? (p.monotone ? p.hi[row_base + q_last] : -1) : (p.causal ? q_last : p.sk - 1);
+  }
+  __syncthreads();
+  if (!p.monotone && threadIdx.x >= 128 && q0 + static_cast<int>(threadIdx.x) - 128 <= q_last) {
+    const int row = row_base + q0 + threadIdx.x - 128;
+    if (p.lo != nullptr) atomicMin(&range[0], p.lo[row]);
+    if (p.hi != nullptr) atomicMax(&range[1], p.hi[row]);
+  }
+  __syncthreads();
+  const int kv_begin = max(range[0], 0) / kBlk;
+  const int kv_end_tok = min(p.sk, range[1] + 1);
+  const int n_blocks = max((kv_end_tok + kBlk - 1) / kBlk - kv_begin, 0);
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -138,8 +165,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const int kv0 = (kv_begin + it) * kBlk;
         mbar_arrive_expect_tx(&kv_full[st], 2 * kTileBytes);
         for (int j = 0; j < kPanels; ++j) {
-          tma_load_2d(sK[st] + j * kPanelBytes, &tmK, &kv_full[st], hk * D + j * 64, row_base + kv0);
-          tma_load_2d(sV[st] + j * kPanelBytes, &tmV, &kv_full[st], hk * D + j * 64, row_base + kv0);
+          tma_load_2d(sK[st] + j * kPanelBytes, &tmK, &kv_full[st], hk * D + j * 64, krow_base + kv0);
+          tma_load_2d(sV[st] + j * kPanelBytes, &tmV, &kv_full[st], hk * D + j * 64, krow_base + kv0);
         }
       }
       __syncwarp();
@@ -192,10 +219,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int r = quarter * 32 + lane;  // row inside the tile
     const int q_idx = q0 + r;
     const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
-    const int lo_row = (p.lo != nullptr && q_idx < p.s) ? p.lo[row_base + q_idx] : 0;
-    const int hi_row = p.causal ? q_idx : p.s - 1;
-    const int lo_last = (p.lo != nullptr) ? p.lo[row_base + min(q0 + kBlk, p.s) - 1] : 0;
+    const bool row_valid = q_idx < p.s;
+    const int lo_row = (p.lo != nullptr && row_valid) ? p.lo[row_base + q_idx] : 0;
+    const int hi_row = (p.hi != nullptr) ? (row_valid ? p.hi[row_base + q_idx] : -1) : (p.causal ? q_idx : p.sk - 1);
+    // a block needs element-wise masking unless every key in it is visible to every row of the tile
+    const int lo_max = (p.lo == nullptr) ? 0 : (p.monotone ? p.lo[row_base + q_last] : p.sk);
+    const int hi_min = (p.hi != nullptr) ? (p.monotone ? p.hi[row_base + q0] : -1) : (p.causal ? q0 : p.sk - 1);
+    const uint8_t* mrow = (EXTRA && p.kmask != nullptr && row_valid) ? p.kmask + static_cast<long long>(row_base + q_idx) * p.sk : nullptr;
     const float c = p.scale * kLog2e;
+    const float cap_in = p.softcap > 0.f ? p.scale / p.softcap : 0.f;  // score → tanh argument
+    const float cap_out = p.softcap * kLog2e;                           // tanh → log2-domain logit
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
     for (int it = 0; it < n_blocks && !*abort_flag; ++it) {
@@ -206,7 +239,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         break;
       }
       tc_fence_after();
-      const bool need_mask = (kv0 + kBlk - 1 > (p.causal ? q0 : p.s - 1)) || (kv0 < lo_last) || (kv0 + kBlk > p.s);
+      const bool need_mask = (kv0 + kBlk - 1 > hi_min) || (kv0 < lo_max) || (kv0 + kBlk > p.sk) || (EXTRA && p.kmask != nullptr);
       // The whole score row (128 fp32) is read from TMEM once — four loads issued back to back, one wait — and stays in
       // registers for both the maximum and the exponentials.
       uint32_t sv[4][32];
@@ -222,10 +255,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       for (int ch = 0; ch < 4; ++ch) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float x = __uint_as_float(sv[ch][i]) * c;
+          float x = (EXTRA && p.softcap > 0.f) ? fast_tanh(__uint_as_float(sv[ch][i]) * cap_in) * cap_out : __uint_as_float(sv[ch][i]) * c;
           if (need_mask) {
             const int j = kv0 + ch * 32 + i;
-            if (j < lo_row || j > hi_row || j >= p.s) x = -INFINITY;
+            if (j < lo_row || j > hi_row || j >= p.sk || (mrow != nullptr && !mrow[min(j, p.sk - 1)])) x = -INFINITY;
           }
           sv[ch][i] = __float_as_uint(x);
           mx4[i & 3] = fmaxf(mx4[i & 3], x);
@@ -360,7 +393,7 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __n
   }
 }
 
-template <int D>
+template <int D, bool EXTRA>
 __global__ void __launch_bounds__(256, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, AttnParams p) {
@@ -390,16 +423,22 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int group = p.hq / p.hkv;
   const int kv0 = kvblk * kBlk;
   const int row_base = bi * p.s;
+  const int krow_base = bi * p.sk;
   const int nq_blocks = (p.s + kBlk - 1) / kBlk;
-  const int qb_begin = p.causal ? kvblk : 0;
-  // last query block that can still see this key block: lo[] is non-decreasing, so stop at the
-  // first block whose first row already starts after the end of this key block.
+  // Query blocks that can see this key block.  With monotone bounds: from the first block whose last row reaches the key
+  // block (hi) to the last block whose first row has not yet moved past it (lo).  Arbitrary masks visit every block.
+  int qb_begin = (p.hi == nullptr && p.causal) ? kvblk : 0;
   int qb_end = nq_blocks;
-  if (p.lo != nullptr) {
-    for (int qb = qb_begin; qb < nq_blocks; ++qb) {
-      if (p.lo[row_base + qb * kBlk] > kv0 + kBlk - 1) {
-        qb_end = qb;
-        break;
+  if (p.monotone) {
+    if (p.hi != nullptr) {
+      while (qb_begin < nq_blocks && p.hi[row_base + min((qb_begin + 1) * kBlk, p.s) - 1] < kv0) ++qb_begin;
+    }
+    if (p.lo != nullptr) {
+      for (int qb = qb_begin; qb < nq_blocks; ++qb) {
+        if (p.lo[row_base + qb * kBlk] > kv0 + kBlk - 1) {
+          qb_end = qb;
+          break;
+        }
       }
     }
   }
@@ -435,8 +474,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (lane == 0) {
       mbar_arrive_expect_tx(kv_full, 2 * kTileBytes);
       for (int j = 0; j < kPanels; ++j) {
-        tma_load_2d(sK + j * kPanelBytes, &tmK, kv_full, hk * D + j * 64, row_base + kv0);
-        tma_load_2d(sV + j * kPanelBytes, &tmV, kv_full, hk * D + j * 64, row_base + kv0);
+        tma_load_2d(sK + j * kPanelBytes, &tmK, kv_full, hk * D + j * 64, krow_base + kv0);
+        tma_load_2d(sV + j * kPanelBytes, &tmV, kv_full, hk * D + j * 64, krow_base + kv0);
       }
     }
     for (int it = 0; it < n_iters && !*abort_flag; ++it) {
@@ -502,6 +541,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int r = quarter * 32 + lane;
     const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
     const float c = p.scale * kLog2e;
+    const float cap_in = p.softcap > 0.f ? p.scale / p.softcap : 0.f;
+    const float cap_out = p.softcap * kLog2e;
     bool ok = true;
     for (int it = 0; it < n_iters && !*abort_flag; ++it) {
       const uint32_t ph = it & 1;
@@ -513,7 +554,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const float lse = row_ok ? p.lse[stat] : 0.f;
       const float dlt = row_ok ? p.delta[stat] : 0.f;
       const int lo_row = (p.lo != nullptr && row_ok) ? p.lo[row_base + q_idx] : 0;
-      const int hi_row = p.causal ? q_idx : p.s - 1;
+      const int hi_row = (p.hi != nullptr) ? (row_ok ? p.hi[row_base + q_idx] : -1) : (p.causal ? q_idx : p.sk - 1);
+      const uint8_t* mrow = (EXTRA && p.kmask != nullptr && row_ok) ? p.kmask + static_cast<long long>(row_base + q_idx) * p.sk : nullptr;
       if (!mbar_wait(sdp_full, ph)) {
         ok = false;
         break;
@@ -529,9 +571,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const int j = kv0 + ch * 32 + i;
-          const bool vis = row_ok && j >= lo_row && j <= hi_row && j < p.s && lse != -INFINITY;
-          pr[i] = vis ? fast_exp2(__uint_as_float(sv[i]) * c - lse) : 0.f;
-          ds[i] = pr[i] * (__uint_as_float(dv[i]) - dlt) * p.scale;
+          const bool vis = row_ok && j >= lo_row && j <= hi_row && j < p.sk && lse != -INFINITY && (mrow == nullptr || mrow[min(j, p.sk - 1)]);
+          if (EXTRA && p.softcap > 0.f) {  // logit = softcap · tanh(score / softcap): the chain rule adds the factor 1 − tanh²
+            const float th = fast_tanh(__uint_as_float(sv[i]) * cap_in);
+            pr[i] = vis ? fast_exp2(th * cap_out - lse) : 0.f;
+            ds[i] = pr[i] * (__uint_as_float(dv[i]) - dlt) * p.scale * (1.f - th * th);
+          } else {
+            pr[i] = vis ? fast_exp2(__uint_as_float(sv[i]) * c - lse) : 0.f;
+            ds[i] = pr[i] * (__uint_as_float(dv[i]) - dlt) * p.scale;
+          }
         }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
@@ -582,8 +630,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     } else {
       // all MMAs of the last iteration retired when dq_full fired; write dK and dV
       const int kv_idx = kv0 + r;
-      __nv_bfloat16* dkrow = p.dk + (static_cast<long long>(row_base + kv_idx) * p.hkv + hk) * D;
-      __nv_bfloat16* dvrow = p.dv + (static_cast<long long>(row_base + kv_idx) * p.hkv + hk) * D;
+      __nv_bfloat16* dkrow = p.dk + (static_cast<long long>(krow_base + kv_idx) * p.hkv + hk) * D;
+      __nv_bfloat16* dvrow = p.dv + (static_cast<long long>(krow_base + kv_idx) * p.hkv + hk) * D;
 #pragma unroll 1
       for (int ch = 0; ch < D / 32; ++ch) {
         uint32_t a[32], bb[32];
@@ -595,7 +643,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
           for (int i = 0; i < 32; ++i) a[i] = 0, bb[i] = 0;
         }
-        if (kv_idx < p.s) {
+        if (kv_idx < p.sk) {
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             uint4 u, w;
@@ -638,13 +686,14 @@ static int launch_fwd(const void* q, const void* k, const void* v, const AttnPar
   CUtensorMap tq, tk, tv;
   int rc;
   if ((rc = make_head_map(&tq, q, p.b, p.s, p.hq, D)) != kOk) return rc;
-  if ((rc = make_head_map(&tk, k, p.b, p.s, p.hkv, D)) != kOk) return rc;
-  if ((rc = make_head_map(&tv, v, p.b, p.s, p.hkv, D)) != kOk) return rc;
-  auto kern = attn_fwd_kernel<D>;
-  static bool attr = false;
-  if (!attr) {
+  if ((rc = make_head_map(&tk, k, p.b, p.sk, p.hkv, D)) != kOk) return rc;
+  if ((rc = make_head_map(&tv, v, p.b, p.sk, p.hkv, D)) != kOk) return rc;
+  const bool extra = p.softcap > 0.f || p.kmask != nullptr;
+  auto kern = extra ? attn_fwd_kernel<D, true> : attn_fwd_kernel<D, false>;
+  static bool attr[2] = {false, false};
+  if (!attr[extra]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem_bytes<D>()) != cudaSuccess) return kErrDriver;
-    attr = true;
+    attr[extra] = true;
   }
   dim3 grid((p.s + kBlk - 1) / kBlk, p.hq, p.b);
   TTB_COUNT_LAUNCH(1);
@@ -657,16 +706,17 @@ static int launch_bwd(const void* q, const void* k, const void* v, const void* d
   CUtensorMap tq, tk, tv, tdo;
   int rc;
   if ((rc = make_head_map(&tq, q, p.b, p.s, p.hq, D)) != kOk) return rc;
-  if ((rc = make_head_map(&tk, k, p.b, p.s, p.hkv, D)) != kOk) return rc;
-  if ((rc = make_head_map(&tv, v, p.b, p.s, p.hkv, D)) != kOk) return rc;
+  if ((rc = make_head_map(&tk, k, p.b, p.sk, p.hkv, D)) != kOk) return rc;
+  if ((rc = make_head_map(&tv, v, p.b, p.sk, p.hkv, D)) != kOk) return rc;
   if ((rc = make_head_map(&tdo, d_o, p.b, p.s, p.hq, D)) != kOk) return rc;
-  auto kern = attn_bwd_kernel<D>;
-  static bool attr = false;
-  if (!attr) {
+  const bool extra = p.softcap > 0.f || p.kmask != nullptr;
+  auto kern = extra ? attn_bwd_kernel<D, true> : attn_bwd_kernel<D, false>;
+  static bool attr[2] = {false, false};
+  if (!attr[extra]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bwd_smem_bytes<D>()) != cudaSuccess) return kErrDriver;
-    attr = true;
+    attr[extra] = true;
   }
-  dim3 grid((p.s + kBlk - 1) / kBlk, p.hkv, p.b);
+  dim3 grid((p.sk + kBlk - 1) / kBlk, p.hkv, p.b);
   TTB_COUNT_LAUNCH(1);
   kern<<<grid, 256, bwd_smem_bytes<D>(), st>>>(tq, tk, tv, tdo, p);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrDriver;
@@ -676,28 +726,40 @@ static int launch_bwd(const void* q, const void* k, const void* v, const void* d
 
 using namespace ttb;
 
-extern "C" int ttb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* lo, int b, int s,
-                            int hq, int hkv, int d, float scale, int causal, int* err, void* stream) {
-  if ((d != 64 && d != 128) || hq % hkv) return kErrBadShape;
+// Optional mask description shared by forward and backward (all pointers may be null):
+//   lo, hi   int32 [b, s]: key j is visible to query q iff lo[q] <= j <= hi[q]; without `hi` the upper bound is q when `causal`
+//            (needs sk == s), else sk - 1; `monotone` != 0 promises both arrays are non-decreasing along the sequence
+//   kmask    uint8 [b, s, sk], 1 = visible, applied on top of the bounds (arbitrary boolean masks; pass lo / hi = first / last
+//            visible key per row with monotone = 0 so that key blocks outside every row's range are skipped)
+//   softcap  > 0: scores pass through softcap * tanh(score * scale / softcap)
+extern "C" int ttb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* lo, const int* hi,
+                            const void* kmask, int monotone, int b, int s, int sk, int hq, int hkv, int d, float scale, int causal,
+                            float softcap, int* err, void* stream) {
+  if ((d != 64 && d != 128) || hq % hkv || s <= 0 || sk <= 0) return kErrBadShape;
+  if (causal && hi == nullptr && s != sk) return kErrBadShape;
   AttnParams p{};
-  p.b = b, p.s = s, p.hq = hq, p.hkv = hkv, p.d = d, p.scale = scale, p.causal = causal, p.lo = lo;
+  p.b = b, p.s = s, p.sk = sk, p.hq = hq, p.hkv = hkv, p.d = d, p.scale = scale, p.causal = causal, p.lo = lo, p.hi = hi;
+  p.kmask = static_cast<const uint8_t*>(kmask), p.monotone = monotone, p.softcap = softcap;
   p.o = static_cast<__nv_bfloat16*>(o), p.lse = lse, p.err = err;
   auto st = static_cast<cudaStream_t>(stream);
   return d == 128 ? launch_fwd<128>(q, k, v, p, st) : launch_fwd<64>(q, k, v, p, st);
 }
 
-// delta: [b, hq, s] fp32 scratch, dq_accum: [b, s, hq, d] fp32 zero-filled by the caller.
+// delta: [b, hq, s] fp32 scratch, dq_accum: [b, s, hq, d] fp32 zero-filled by the caller; dk, dv: [b, sk, hkv, d].
 extern "C" int ttb_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
-                            const float* lse, float* delta, float* dq_accum, void* dk, void* dv, const int* lo, int b,
-                            int s, int hq, int hkv, int d, float scale, int causal, int* err, void* stream) {
-  if ((d != 64 && d != 128) || hq % hkv) return kErrBadShape;
+                            const float* lse, float* delta, float* dq_accum, void* dk, void* dv, const int* lo, const int* hi,
+                            const void* kmask, int monotone, int b, int s, int sk, int hq, int hkv, int d, float scale, int causal,
+                            float softcap, int* err, void* stream) {
+  if ((d != 64 && d != 128) || hq % hkv || s <= 0 || sk <= 0) return kErrBadShape;
+  if (causal && hi == nullptr && s != sk) return kErrBadShape;
   auto st = static_cast<cudaStream_t>(stream);
   const long long warps = static_cast<long long>(b) * s * hq;
   TTB_COUNT_LAUNCH(1);
   attn_delta_kernel<<<static_cast<unsigned>((warps * 32 + 255) / 256), 256, 0, st>>>(
       static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(d_o), delta, b, s, hq, d);
   AttnParams p{};
-  p.b = b, p.s = s, p.hq = hq, p.hkv = hkv, p.d = d, p.scale = scale, p.causal = causal, p.lo = lo;
+  p.b = b, p.s = s, p.sk = sk, p.hq = hq, p.hkv = hkv, p.d = d, p.scale = scale, p.causal = causal, p.lo = lo, p.hi = hi;
+  p.kmask = static_cast<const uint8_t*>(kmask), p.monotone = monotone, p.softcap = softcap;
   p.lse = const_cast<float*>(lse), p.delta = delta, p.dq_accum = dq_accum;
   p.dk = static_cast<__nv_bfloat16*>(dk), p.dv = static_cast<__nv_bfloat16*>(dv), p.err = err;
   return d == 128 ? launch_bwd<128>(q, k, v, d_o, p, st) : launch_bwd<64>(q, k, v, d_o, p, st);

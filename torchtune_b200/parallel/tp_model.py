@@ -362,13 +362,14 @@ class TPDecoder(nn.Module):
                 layer.attn.kv_cache.reset()
 
     @torch.no_grad()
-    def forward_inference(self, tokens: torch.Tensor, *, mask=None, input_pos: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def forward_inference(self, tokens: Optional[torch.Tensor], *, mask=None, input_pos: Optional[torch.Tensor] = None, input_embeds: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Decoding-time forward: activations are replicated (any batch / sequence length, including one token), attention uses
         this rank's heads and KV cache, and the two row-parallel projections of every layer are followed by an all-reduce.
+        ``input_embeds`` (``[b, s, d]``) replaces the embedding lookup (early-fusion models splice image embeddings in).
         Returns fp32 logits ``[b, s, vocab]``, identical on every rank."""
-        h = ops.embed_tokens(self.tok_embeddings, tokens)
+        h = ops.embed_tokens(self.tok_embeddings, tokens) if input_embeds is None else input_embeds
         for layer in self.layers:
-            m = layer.mask_mod(mask, tokens.shape[0], tokens.shape[1]) if layer.mask_mod is not None else mask
+            m = layer.mask_mod(mask, h.shape[0], h.shape[1]) if layer.mask_mod is not None else mask
             h = h + self.tp.all_reduce_(layer.attn.forward_replicated(layer.sa_norm(h), m, input_pos))
             h = h + self.tp.all_reduce_(layer.mlp.forward_replicated(layer.mlp_norm(h)))
         return self.output(self.norm(h)).float()

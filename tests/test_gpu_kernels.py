@@ -74,6 +74,44 @@ def test_gemm_large_matches_matmul():
     _close(gemm(a, b), want, 2e-2, 0.5, "large")
 
 
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (520, 776, 136), (1000, 264, 72), (2304, 4352, 1088)])
+def test_gemm_cta_pair_kernel(M, N, K, a_mn, b_mn):
+    """``tcgen05.mma.cta_group::2`` kernel (two SMs per 256 × 256 tile) through its exported symbol: all four operand layouts,
+    sizes that are not tile multiples, bias and bf16 accumulation into an existing output."""
+    from torchtune_b200.ops._lib import check, check_device_errors, err_word, lib, stream_ptr
+
+    a, b = _rand(M, K, seed=1), _rand(N, K, seed=2)
+    bias, prev = _rand(N, seed=3), _rand(M, N, seed=4)
+    want = a.float() @ b.float().t()
+    a_in = a.t().contiguous() if a_mn else a
+    b_in = b.t().contiguous() if b_mn else b
+    L = lib()
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    check(L.ttb_gemm_bf16_2sm(a_in.data_ptr(), b_in.data_ptr(), out.data_ptr(), M, N, K, int(a_mn), int(b_mn), a_in.stride(0), b_in.stride(0), N, 0, None, 1.0,
+                              err_word(out.device).data_ptr(), stream_ptr()), "pair gemm")
+    acc = prev.clone()
+    check(L.ttb_gemm_bf16_2sm(a_in.data_ptr(), b_in.data_ptr(), acc.data_ptr(), M, N, K, int(a_mn), int(b_mn), a_in.stride(0), b_in.stride(0), N, 1, bias.data_ptr(), 0.5,
+                              err_word(out.device).data_ptr(), stream_ptr()), "pair gemm accumulate")
+    torch.cuda.synchronize()
+    check_device_errors()
+    tol = 2e-2 * math.sqrt(K) / 8
+    _close(out, want, 2e-2, tol, f"pair gemm {M}x{N}x{K} a_mn={a_mn} b_mn={b_mn}")
+    _close(acc, 0.5 * want + bias.float() + prev.float(), 3e-2, tol + 0.05, "pair gemm accumulate + bias + alpha")
+
+
+def test_gemm_benchmark_shapes_match_matmul():
+    """The projections of the benchmark model (4 × 2048 tokens, width 4096, MLP 14336) in the three GEMM forms of a step."""
+    from torchtune_b200.ops._cuda import gemm
+
+    x, w = _rand(8192, 4096, seed=21, scale=0.5), _rand(14336, 4096, seed=22, scale=0.05)
+    y = gemm(x, w)  # forward
+    _close(y, torch.matmul(x, w.t()), 2e-2, 0.3, "fwd 8192x14336x4096")
+    dy = _rand(8192, 14336, seed=23, scale=0.1)
+    _close(gemm(dy, w, b_mn=True), torch.matmul(dy, w), 2e-2, 0.3, "dgrad 8192x4096x14336")
+    _close(gemm(dy, x, a_mn=True, b_mn=True), torch.matmul(dy.t(), x), 2e-2, 1.0, "wgrad 14336x4096x8192")
+
+
 def test_linear_autograd():
     x = _rand(3, 40, 256, seed=8).requires_grad_()
     w = _rand(512, 256, seed=9, scale=0.05).requires_grad_()
@@ -144,7 +182,7 @@ def test_swiglu():
 
 
 # ------------------------------------------------------------------ loss
-@pytest.mark.parametrize("T,D,V", [(300, 256, 1024), (1000, 512, 32000)])
+@pytest.mark.parametrize("T,D,V", [(300, 256, 1024), (1000, 512, 32000), (2048, 1024, 128256)])  # last: the benchmark model's vocabulary
 def test_linear_cross_entropy(T, D, V):
     h = _rand(T, D, seed=1).requires_grad_()
     w = _rand(V, D, seed=2, scale=0.05).requires_grad_()

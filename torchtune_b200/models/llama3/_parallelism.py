@@ -54,9 +54,14 @@ def validate_tp_plan(plan: Optional[Dict[str, str]]) -> None:
     """Raise if ``plan`` asks for a layout other than the built-in one (after dropping a ``decoder.`` prefix and ``+fp8``)."""
     if not plan:
         return
+    import re
+
+    moe = {"layers.*.mlp": "gather_rows_in_scatter_sum_rows_out", "layers.*.mlp.router.gate": "replicated", "layers.*.mlp.experts": "expert_tensor_parallel",
+           "layers.*.mlp.shared_expert.w1": COLUMN, "layers.*.mlp.shared_expert.w3": COLUMN, "layers.*.mlp.shared_expert.w2": ROW}
     for key, style in plan.items():
         k = key[len("decoder."):] if key.startswith("decoder.") else key
-        want = _BASE.get(k)
+        k = re.sub(r"^layers\.\d+\.", "layers.*.", k)  # plans may name every layer (mixture-of-experts models differ per layer)
+        want = _BASE.get(k, moe.get(k))
         if want is None:
             raise ValueError(f"tensor_parallel_plan names {key!r}, which the tensor-parallel engine does not shard")
         if str(style).replace("+fp8", "") != want:

@@ -7,7 +7,7 @@ from ._encoder import Llama4VisionEncoder, Llama4VisionProjectionHead
 from ._model_builders import llama4_maverick_17b_128e, llama4_scout_17b_16e, llama4_transform, lora_llama4_maverick_17b_128e, lora_llama4_scout_17b_16e
 from ._tokenizer import LLAMA4_SPECIAL_TOKENS, Llama4Tokenizer
 from ._transform import Llama4Transform
-from ..llama3._parallelism import decoder_only_tp_inference_plan, decoder_only_tp_plan, decoder_only_tp_training_plan
+from ._parallelism import decoder_only_tp_inference_plan, decoder_only_tp_plan, decoder_only_tp_training_plan
 
 __all__ = [
     "lora_llama4_vision_encoder",

@@ -3,6 +3,7 @@ kernels in ``csrc/`` (loaded through :mod:`._lib`)."""
 from __future__ import annotations
 
 import ctypes
+import os
 import math
 from typing import Any, Dict, List, Optional, Sequence, Tuple, Union
 
@@ -20,6 +21,21 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
 
 
 # ======================================================================= GEMM
+_PAIR_KERNEL = os.environ.get("TTB_GEMM_2SM", "1") != "0"
+_SM_PAIRS = None
+
+
+def _use_pair_kernel(M: int, N: int, K: int, out: torch.Tensor) -> bool:
+    """The CTA-pair kernel (``tcgen05.mma.cta_group::2``, 256 × 256 tiles, ``csrc/gemm2sm.cu``) takes bf16-output problems with
+    at least one 256 × 256 tile per SM pair; smaller ones keep 128-row tiles, which spread over more SMs."""
+    global _SM_PAIRS
+    if not _PAIR_KERNEL or out.dtype != _BF16:
+        return False
+    if _SM_PAIRS is None:
+        _SM_PAIRS = max(1, torch.cuda.get_device_properties(out.device).multi_processor_count // 2)
+    return K >= 128 and (-(-M // 256)) * (-(-N // 256)) >= _SM_PAIRS
+
+
 def gemm(
     a: torch.Tensor,
     b: torch.Tensor,
@@ -57,6 +73,11 @@ def gemm(
         return out
     if K == 0:
         return out if accumulate else out.zero_()
+    if _use_pair_kernel(M, N, K, out):
+        rc = lib().ttb_gemm_bf16_2sm(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, int(a_mn), int(b_mn), a.stride(0), b.stride(0), out.stride(0), int(accumulate),
+                                     _ptr(bias), float(alpha), err_word(a.device).data_ptr(), stream_ptr())
+        check(rc, f"gemm (CTA pairs) M={M} N={N} K={K} a_mn={a_mn} b_mn={b_mn}")
+        return out
     rc = lib().ttb_gemm_bf16(
         a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, int(a_mn), int(b_mn),
         a.stride(0), b.stride(0), out.stride(0), int(out.dtype == torch.float32), int(accumulate),

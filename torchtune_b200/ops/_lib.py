@@ -54,6 +54,8 @@ def _declare(L: ctypes.CDLL) -> None:
     L.ttb_attn_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, i32, f32, vp, vp]
     L.ttb_attn_bwd.restype = i32
     L.ttb_attn_fwd.restype = i32
+    L.ttb_gemm_bf16_2sm.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i64, i64, i64, i32, vp, f32, vp, vp]
+    L.ttb_gemm_bf16_2sm.restype = i32
     L.ttb_ensure_device.argtypes = [i32]
     L.ttb_gemm_grouped_bf16.argtypes = [vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, i64, i64, i64, i64, vp, vp]
     L.ttb_gemm_grouped_bf16.restype = i32

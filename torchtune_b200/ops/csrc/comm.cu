@@ -90,79 +90,101 @@ __global__ void dp_wait_kernel(const int* __restrict__ my_flags, int world, int 
 // `guard` (optional): the device error word.  When it is set — a preceding dp_wait_kernel gave up, or any earlier kernel
 // reported an error — every CTA returns without touching parameters, moments or partial sums, so a failed step leaves the
 // optimizer state as it was.
-template <int WORLD>
-__global__ void __launch_bounds__(256, 4)
+template <int WORLD, int mode>
+__global__ void __launch_bounds__(256, 3)
 dp_reduce_adamw_bcast_kernel(PeerTable peers, int rank, long long begin, long long count, __nv_bfloat16* __restrict__ m,
                              __nv_bfloat16* __restrict__ v, float* __restrict__ gsum, float* __restrict__ sumsq_partials,
                              const float* __restrict__ scale_dev, float scale_host, float lr, float beta1, float beta2,
-                             float eps, float weight_decay, float inv_bc1, float inv_sqrt_bc2, int mode,
+                             float eps, float weight_decay, float inv_bc1, float inv_sqrt_bc2,
                              const int* __restrict__ guard, int bcast, int accumulate) {
   __shared__ float red[8];
   if (guard != nullptr && *reinterpret_cast<const volatile int*>(guard) != 0) return;
   const float gs = scale_host * (scale_dev != nullptr ? *scale_dev : 1.f);
   const long long nvec = count >> 3;  // shards are multiples of 8 elements
   float sq = 0.f;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long e = begin + i * 8;
-    float g[8];
-    if (mode == 2) {
-      const float4 a = *reinterpret_cast<const float4*>(gsum + i * 8);
-      const float4 b = *reinterpret_cast<const float4*>(gsum + i * 8 + 4);
-      g[0] = a.x, g[1] = a.y, g[2] = a.z, g[3] = a.w, g[4] = b.x, g[5] = b.y, g[6] = b.z, g[7] = b.w;
-    } else {
-      uint4 raw[WORLD];
+  // U vectors per thread and trip, all loads issued before the first dependent instruction: with one or two ranks the kernel is
+  // bound by this GPU's HBM and needs the extra bytes in flight (more ranks are NVLink-bound and short of registers instead).
+  constexpr int U = WORLD <= 2 ? 2 : 1;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < nvec; i0 += stride * U) {
+    uint4 raw[U][WORLD], wq[U], mq[U], vq[U];
+    float4 ga[U], gb[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i >= nvec) continue;
+      const long long e = begin + i * 8;
+      if (mode == 2 || (mode == 1 && accumulate)) {
+        ga[u] = *reinterpret_cast<const float4*>(gsum + i * 8);
+        gb[u] = *reinterpret_cast<const float4*>(gsum + i * 8 + 4);
+      }
+      if (mode != 2) {
+#pragma unroll
+        for (int r = 0; r < WORLD; ++r) {
+          // start with the next rank so that the 8 ranks do not all hit the same peer at once
+          const int src = (rank + 1 + r) % WORLD;
+          raw[u][r] = *reinterpret_cast<const uint4*>(peers.grad[src] + e);
+        }
+      }
+      if (mode != 1) {
+        wq[u] = *reinterpret_cast<const uint4*>(peers.param[rank] + e);
+        mq[u] = *reinterpret_cast<const uint4*>(m + i * 8);
+        vq[u] = *reinterpret_cast<const uint4*>(v + i * 8);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i >= nvec) continue;
+      const long long e = begin + i * 8;
+      float g[8];
+      if (mode == 2) {
+        g[0] = ga[u].x, g[1] = ga[u].y, g[2] = ga[u].z, g[3] = ga[u].w, g[4] = gb[u].x, g[5] = gb[u].y, g[6] = gb[u].z, g[7] = gb[u].w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) g[j] = 0.f;
+#pragma unroll
+        for (int r = 0; r < WORLD; ++r) {
+          float f[8];
+          unpack8f(raw[u][r], f);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) g[j] += f[j];
+        }
+      }
+      if (mode == 1) {
+        if (accumulate) {  // a further micro-batch: add to the reduced gradient of the earlier ones
+          g[0] += ga[u].x, g[1] += ga[u].y, g[2] += ga[u].z, g[3] += ga[u].w, g[4] += gb[u].x, g[5] += gb[u].y, g[6] += gb[u].z, g[7] += gb[u].w;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sq += g[j] * g[j];
+        *reinterpret_cast<float4*>(gsum + i * 8) = make_float4(g[0], g[1], g[2], g[3]);
+        *reinterpret_cast<float4*>(gsum + i * 8 + 4) = make_float4(g[4], g[5], g[6], g[7]);
+        continue;
+      }
+      float w[8], m1[8], v1[8];
+      unpack8f(wq[u], w);
+      unpack8f(mq[u], m1);
+      unpack8f(vq[u], v1);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float grad = g[j] * gs;
+        m1[j] = beta1 * m1[j] + (1.f - beta1) * grad;
+        v1[j] = beta2 * v1[j] + (1.f - beta2) * grad * grad;
+        w[j] *= (1.f - lr * weight_decay);
+        w[j] -= lr * inv_bc1 * m1[j] / (sqrtf(v1[j]) * inv_sqrt_bc2 + eps);
+      }
+      *reinterpret_cast<uint4*>(m + i * 8) = pack8f(m1);
+      *reinterpret_cast<uint4*>(v + i * 8) = pack8f(v1);
+      const uint4 out = pack8f(w);
+      if (!bcast) {  // sharded parameters: the owner keeps the only copy
+        *reinterpret_cast<uint4*>(peers.param[rank] + e) = out;
+        continue;
+      }
 #pragma unroll
       for (int r = 0; r < WORLD; ++r) {
-        // start with the next rank so that the 8 ranks do not all hit the same peer at once
-        const int src = (rank + 1 + r) % WORLD;
-        raw[r] = *reinterpret_cast<const uint4*>(peers.grad[src] + e);
+        const int dst = (rank + r) % WORLD;
+        *reinterpret_cast<uint4*>(peers.param[dst] + e) = out;
       }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) g[j] = 0.f;
-#pragma unroll
-      for (int r = 0; r < WORLD; ++r) {
-        float f[8];
-        unpack8f(raw[r], f);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) g[j] += f[j];
-      }
-    }
-    if (mode == 1) {
-      if (accumulate) {  // a further micro-batch: add to the reduced gradient of the earlier ones
-        const float4 a = *reinterpret_cast<const float4*>(gsum + i * 8);
-        const float4 b = *reinterpret_cast<const float4*>(gsum + i * 8 + 4);
-        g[0] += a.x, g[1] += a.y, g[2] += a.z, g[3] += a.w, g[4] += b.x, g[5] += b.y, g[6] += b.z, g[7] += b.w;
-      }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) sq += g[j] * g[j];
-      *reinterpret_cast<float4*>(gsum + i * 8) = make_float4(g[0], g[1], g[2], g[3]);
-      *reinterpret_cast<float4*>(gsum + i * 8 + 4) = make_float4(g[4], g[5], g[6], g[7]);
-      continue;
-    }
-    float w[8], m1[8], v1[8];
-    unpack8f(*reinterpret_cast<const uint4*>(peers.param[rank] + e), w);
-    unpack8f(*reinterpret_cast<const uint4*>(m + i * 8), m1);
-    unpack8f(*reinterpret_cast<const uint4*>(v + i * 8), v1);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float grad = g[j] * gs;
-      m1[j] = beta1 * m1[j] + (1.f - beta1) * grad;
-      v1[j] = beta2 * v1[j] + (1.f - beta2) * grad * grad;
-      w[j] *= (1.f - lr * weight_decay);
-      w[j] -= lr * inv_bc1 * m1[j] / (sqrtf(v1[j]) * inv_sqrt_bc2 + eps);
-    }
-    *reinterpret_cast<uint4*>(m + i * 8) = pack8f(m1);
-    *reinterpret_cast<uint4*>(v + i * 8) = pack8f(v1);
-    const uint4 out = pack8f(w);
-    if (!bcast) {  // sharded parameters: the owner keeps the only copy
-      *reinterpret_cast<uint4*>(peers.param[rank] + e) = out;
-      continue;
-    }
-#pragma unroll
-    for (int r = 0; r < WORLD; ++r) {
-      const int dst = (rank + r) % WORLD;
-      *reinterpret_cast<uint4*>(peers.param[dst] + e) = out;
     }
   }
   if (mode == 1) {
@@ -233,7 +255,7 @@ extern "C" int ttb_ipc_open(const void* handle, void** out) {
   return kOk;
 }
 extern "C" int ttb_ipc_close(void* p) { return cudaIpcCloseMemHandle(p) == cudaSuccess ? kOk : kErrDriver; }
-extern "C" int ttb_dp_grid() { return sm_count() * 4; }
+extern "C" int ttb_dp_grid() { return sm_count() * 3; }
 
 // grad_ptrs / param_ptrs: host arrays of `world` device pointers (peer-mapped flat buffers).
 // [begin, begin+count) is this rank's shard (count % 8 == 0, begin % 8 == 0).
@@ -250,7 +272,7 @@ extern "C" int ttb_dp_reduce_adamw_bcast(void* const* grad_ptrs, void* const* pa
                                          float beta1, float beta2, float eps, float weight_decay, float inv_bc1,
                                          float inv_sqrt_bc2, int mode, const int* my_flags, int slot, int epoch, int* err,
                                          int grid_ctas, int bcast, int accumulate, void* stream) {
-  if (world < 1 || world > kMaxRanks || (begin & 7) || (count & 7)) return kErrBadShape;
+  if (world < 1 || world > kMaxRanks || (begin & 7) || (count & 7) || mode < 0 || mode > 2) return kErrBadShape;
   if (my_flags != nullptr && (slot < 0 || slot >= kMaxBuckets || err == nullptr)) return kErrBadShape;
   if (count == 0) return kOk;
   PeerTable t{};
@@ -270,11 +292,15 @@ extern "C" int ttb_dp_reduce_adamw_bcast(void* const* grad_ptrs, void* const* pa
     guard = err;
   }
   TTB_COUNT_LAUNCH(1);
-#define TTB_DP_CASE(W)                                                                                              \
-  case W:                                                                                                           \
-    dp_reduce_adamw_bcast_kernel<W><<<grid, 256, 0, s>>>(t, rank, begin, count, mm, vv, gsum, sumsq_partials,       \
-                                                         scale_dev, scale_host, lr, beta1, beta2, eps, weight_decay, \
-                                                         inv_bc1, inv_sqrt_bc2, mode, guard, bcast, accumulate);     \
+#define TTB_DP_LAUNCH(W, MODE)                                                                                         \
+  dp_reduce_adamw_bcast_kernel<W, MODE><<<grid, 256, 0, s>>>(t, rank, begin, count, mm, vv, gsum, sumsq_partials, scale_dev,   \
+                                                             scale_host, lr, beta1, beta2, eps, weight_decay, inv_bc1,     \
+                                                             inv_sqrt_bc2, guard, bcast, accumulate)
+#define TTB_DP_CASE(W)                   \
+  case W:                                \
+    if (mode == 0) TTB_DP_LAUNCH(W, 0);  \
+    else if (mode == 1) TTB_DP_LAUNCH(W, 1); \
+    else TTB_DP_LAUNCH(W, 2);            \
     break;
   switch (world) {
     TTB_DP_CASE(1)
@@ -288,6 +314,7 @@ extern "C" int ttb_dp_reduce_adamw_bcast(void* const* grad_ptrs, void* const* pa
       return kErrBadShape;
   }
 #undef TTB_DP_CASE
+#undef TTB_DP_LAUNCH
   return cudaGetLastError() == cudaSuccess ? kOk : kErrDriver;
 }
 

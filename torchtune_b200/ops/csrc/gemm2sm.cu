@@ -14,6 +14,7 @@
 // Barriers: `full` lives in the even CTA and counts the bytes of both CTAs' loads; `empty` and `tfull` exist in both
 // CTAs and are signalled by multicast commits; `tempty` lives in the even CTA and collects the eight epilogue warps.
 // Every wait is bounded (error word + abort flag), the two CTAs meet at a cluster barrier before TMEM is released.
+#include <cstdlib>
 #include <cstring>
 
 #include "common/ptx.cuh"
@@ -27,7 +28,7 @@ static constexpr int PM = 256;   // rows per CTA pair
 static constexpr int BN = 256;   // columns per pair tile (each CTA loads 128 of them)
 static constexpr int BK = 64;
 static constexpr int kThreads = 256;
-static constexpr int kGroupM = 8;  // pair-tiles in m per scheduling group
+static constexpr int kGroupM = 16;  // default number of pair-tiles in m per scheduling group (L2 reuse of the B panel)
 static constexpr int kABytes = BM * BK * 2;
 static constexpr int kBBytes = (BN / 2) * BK * 2;
 static constexpr int kStageBytes = kABytes + kBBytes;  // 32 KB per CTA and stage
@@ -44,6 +45,7 @@ struct Params {
   float alpha;
   int accumulate;
   int tma_store;
+  int group_m;  // pair-tiles in m per scheduling group
   int* err;
 };
 
@@ -95,11 +97,11 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
                : "memory");
 }
 
-__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_blk, int& n_blk) {
-  const int per_group = kGroupM * num_n;
+__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int group_m, int& m_blk, int& n_blk) {
+  const int per_group = group_m * num_n;
   const int group = t / per_group;
-  const int first_m = group * kGroupM;
-  const int gsize = min(kGroupM, num_m - first_m);
+  const int first_m = group * group_m;
+  const int gsize = min(group_m, num_m - first_m);
   const int r = t - group * per_group;
   m_blk = first_m + r % gsize;
   n_blk = r / gsize;
@@ -161,7 +163,7 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint32_t phase = 0;
     for (int t = pair; t < num_tiles && !*abort_flag; t += num_pairs) {
       int m_blk, n_blk;
-      tile_coords(t, num_m, num_n, m_blk, n_blk);
+      tile_coords(t, num_m, num_n, p.group_m, m_blk, n_blk);
       const int a_row = m_blk * PM + static_cast<int>(cta) * BM;
       const int b_row = n_blk * BN + static_cast<int>(cta) * (BN / 2);
       for (int kb = 0; kb < num_kb; ++kb) {
@@ -255,7 +257,7 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint8_t* my_stage = epi + quarter * 8192;
     for (int t = pair; t < num_tiles && !*abort_flag; t += num_pairs) {
       int m_blk, n_blk;
-      tile_coords(t, num_m, num_n, m_blk, n_blk);
+      tile_coords(t, num_m, num_n, p.group_m, m_blk, n_blk);
       if (!mbar_wait(&tfull[acc], acc_phase)) {
         *abort_flag = 1;
         if (lane == 0) atomicExch(p.err, 114);
@@ -414,6 +416,12 @@ extern "C" int ttb_gemm_bf16_2sm(const void* A, const void* B, void* C, int M, i
   g2::Params p;
   p.M = M, p.N = N, p.K = K, p.C = C, p.ldc = ldc, p.bias = static_cast<const __nv_bfloat16*>(bias), p.alpha = alpha;
   p.accumulate = accumulate, p.tma_store = 0, p.err = err;
+  static int group_m = 0;
+  if (group_m == 0) {
+    const char* e = getenv("TTB_G2_GROUP_M");
+    group_m = (e != nullptr && atoi(e) > 0) ? atoi(e) : g2::kGroupM;
+  }
+  p.group_m = group_m;
   auto s = static_cast<cudaStream_t>(stream);
   if (a_mn) return b_mn ? g2::launch<true, true>(A, B, p, lda, ldb, s) : g2::launch<true, false>(A, B, p, lda, ldb, s);
   return b_mn ? g2::launch<false, true>(A, B, p, lda, ldb, s) : g2::launch<false, false>(A, B, p, lda, ldb, s);

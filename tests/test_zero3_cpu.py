@@ -40,7 +40,7 @@ def _single_process(mode: str, world: int):
             for rank in range(world):
                 total = total + _loss(model, *_batch(rank, step, micro))
         (total / (16 * world * micros)).backward()
-        if mode == "deferred":
+        if mode in ("deferred", "hsdp"):
             norms.append(float(torch.nn.utils.clip_grad_norm_(model.parameters(), CLIP)))
         opt.step()
         opt.zero_grad()
@@ -55,12 +55,20 @@ def _worker(rank, world, port, mode, ac, results):
         fixed_init_(model, std=0.1)
         if ac:
             training.set_activation_checkpointing(model, {TransformerSelfAttentionLayer})
-        engine = Zero3Engine(torch.device("cpu"))
+        if mode == "hsdp":  # 2 shard groups of 2 ranks: parameters cut in two, the halves replicated across the groups
+            from torchtune_b200.parallel.mesh import ParallelDims
+
+            groups = ParallelDims(dp_replicate=2, dp_shard=2, world_size=world).build_groups(("dp_shard", "dp_replicate"))
+            engine = Zero3Engine(torch.device("cpu"), groups["dp_shard"], groups["dp_replicate"])
+            assert engine.dp_size == 4 and engine.world == 2 and not engine.wants_backward_overlap(None)
+        else:
+            engine = Zero3Engine(torch.device("cpu"))
         model = engine.prepare(model)
         opt = engine.build_optimizer(model, lr=LR, weight_decay=0.01)
         assert all(p.untyped_storage().size() == 0 for p in model.parameters()), "parameters must not be resident between steps"
         micros = 2 if mode == "deferred" else 1
         scale = 1.0 / (16 * world * micros)
+        clipped = mode in ("deferred", "hsdp")
         norms = []
         for step in range(STEPS):
             for micro in range(micros):
@@ -68,7 +76,7 @@ def _worker(rank, world, port, mode, ac, results):
                 if mode == "fused":
                     assert engine.arm_backward_overlap(opt, scale, None)
                 loss.backward()
-            norm = engine.optimizer_step(model, opt, scale, CLIP if mode == "deferred" else None)
+            norm = engine.optimizer_step(model, opt, scale, CLIP if clipped else None)
             if norm is not None:
                 norms.append(float(norm))
             if step == 1:
@@ -81,13 +89,13 @@ def _worker(rank, world, port, mode, ac, results):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode,ac", [("fused", True), ("fused", False), ("deferred", True)])
+@pytest.mark.parametrize("mode,ac", [("fused", True), ("fused", False), ("deferred", True), ("hsdp", True)])
 def test_zero3_engine_matches_single_process(mode, ac):
-    world = 2
+    world = 4 if mode == "hsdp" else 2
     want_sd, want_norms = _single_process(mode, world)
     mgr = mp.Manager()
     results = mgr.dict()
-    mp.spawn(_worker, args=(world, 29581 + (mode == "deferred") + 2 * ac, mode, ac, results), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, 29581 + (mode == "deferred") + 2 * ac + 5 * (mode == "hsdp"), mode, ac, results), nprocs=world, join=True)
     for rank in range(world):
         got = results[rank]
         if want_norms:

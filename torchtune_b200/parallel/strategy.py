@@ -216,7 +216,7 @@ class ParallelStrategy(DataParallelEngine):
     @property
     def dp_size(self) -> int:  # type: ignore[override]
         # the ranks of one tensor- or context-parallel group (consecutive ranks) read the same batch
-        return self.world // (self.dims.tp * self.dims.cp)
+        return self.world // (self.dims.tp * self.dims.cp)  # (replicate × shard: every data-parallel rank reads its own batch)
 
     @property
     def dp_rank(self) -> int:  # type: ignore[override]
@@ -362,7 +362,13 @@ class ParallelStrategy(DataParallelEngine):
                         p.data.copy_(tmp)
                     else:
                         dist.broadcast(p.data, src=0)
-            self.z3 = Zero3Engine(self.device, None)
+            shard_group = replica_group = None
+            if self.dims.dp_replicate > 1:
+                # hybrid sharding: parameters are cut over runs of `dp_shard` consecutive ranks; the ranks at the same position
+                # of every run hold the same slices and sum their reduced gradients once per step
+                groups = self.dims.build_groups(("dp_shard", "dp_replicate"))
+                shard_group, replica_group = groups["dp_shard"], groups["dp_replicate"]
+            self.z3 = Zero3Engine(self.device, shard_group, replica_group)
             model = self.z3.prepare(model)
             if self.rank == 0:
                 _log.info(f"ZeRO-3 engine: every trainable parameter is sharded over {self.world} ranks ({self.z3.nb} buckets, {self.z3.sp.shard} elements per rank)")

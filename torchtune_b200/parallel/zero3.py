@@ -255,10 +255,16 @@ class Zero3Engine:
 
     RDY, CONS, UPD = 0, 1, 2  # flag kinds; bucket b uses slots 3·b + kind
 
-    def __init__(self, device: torch.device, group=None):
-        self.device, self.group = device, group
+    def __init__(self, device: torch.device, group=None, replica_group=None):
+        """``group``: the ranks the parameters are sharded over (``None`` = every rank).  ``replica_group`` (hybrid sharding,
+        ``data_parallel_replicate_dim`` > 1): the ranks that hold the *same* shard in the other shard groups; their reduced
+        gradients are summed with one all-reduce of the fp32 shard per step before the update (so the update is never fused
+        into backward in this mode)."""
+        self.device, self.group, self.replica_group = device, group, replica_group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.replicas = dist.get_world_size(replica_group) if (replica_group is not None and dist.is_initialized()) else 1
+        self.global_rank = dist.get_rank() if dist.is_initialized() else 0
         self.cuda = device.type == "cuda"
         self.sp: Optional[ShardedParameters] = None
         self.optimizer: Optional[Zero3AdamW] = None
@@ -271,8 +277,8 @@ class Zero3Engine:
         # more of the SMs' issue slots and of the HBM to the GEMMs.
         self.comm_ctas = int(os.environ.get("TTB_ZERO3_CTAS", "0")) or max(48, 592 // max(self.world, 1))
 
-    dp_size = property(lambda self: self.world)
-    dp_rank = property(lambda self: self.rank)
+    dp_size = property(lambda self: self.world * self.replicas)  # every rank reads its own batches
+    dp_rank = property(lambda self: self.global_rank if self.replicas > 1 else self.rank)
     non_data_parallel_size = 1
     min_seq_len_divisor = 1
 
@@ -570,7 +576,7 @@ class Zero3Engine:
         return self.optimizer
 
     def wants_backward_overlap(self, optimizer) -> bool:
-        return optimizer is self.optimizer and not self._armed and optimizer._open is None
+        return self.replicas == 1 and optimizer is not None and optimizer is self.optimizer and not self._armed and optimizer._open is None
 
     def arm_backward_overlap(self, optimizer, grad_scale, clip_grad_norm: Optional[float] = None) -> bool:
         """Call between forward and ``backward()`` of the step's only (or last) micro-batch with the final gradient scale: every
@@ -582,19 +588,21 @@ class Zero3Engine:
         return True
 
     def all_reduce_sum_(self, *tensors: torch.Tensor) -> None:
-        if self.world == 1:
+        """Sum over every data-parallel rank (all shard groups)."""
+        if self.world * self.replicas == 1:
             return
+        everyone = self.group if self.replicas == 1 else None
         if len(tensors) == 1:
-            dist.all_reduce(tensors[0], group=self.group)
+            dist.all_reduce(tensors[0], group=everyone)
             return
         packed = torch.stack([t.reshape(()).to(torch.float32) for t in tensors])
-        dist.all_reduce(packed, group=self.group)
+        dist.all_reduce(packed, group=everyone)
         for t, v in zip(tensors, packed):
             t.copy_(v)
 
     def barrier(self) -> None:
-        if self.world > 1:
-            dist.all_reduce(self._token, group=self.group)
+        if self.world * self.replicas > 1:
+            dist.all_reduce(self._token, group=self.group if self.replicas == 1 else None)
 
     def optimizer_step(self, model: nn.Module, optimizer: Zero3AdamW, grad_scale, clip_grad_norm: Optional[float] = None):
         if optimizer is not self.optimizer:
@@ -613,9 +621,11 @@ class Zero3Engine:
                 else:
                     st["scale_host"] = float(grad_scale)
                 st["clip"] = clip_grad_norm
+            if self.replicas > 1:  # hybrid sharding: the same slices of the other shard groups
+                dist.all_reduce(optimizer._gsum, group=self.replica_group)
             total = None
             if st["clip"] is not None:
-                total = optimizer.local_sumsq()
+                total = optimizer._gsum.pow(2).sum() if self.replicas > 1 else optimizer.local_sumsq()
                 if self.world > 1:
                     dist.all_reduce(total, group=self.group)
             updated = sorted(optimizer.reduced)

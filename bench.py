@@ -166,19 +166,10 @@ def run_ours(args) -> dict:
         parallel = par.DataParallelEngine(device=device)  # world 1: same flat store, no peers
     torch.manual_seed(1234)  # identical initial weights on every rank
     with training.set_default_dtype(torch.bfloat16), (torch.device("meta") if zero3 else device):
-        if args.variant in ("full", "zero3"):
-            model = llama3_1(**MODEL)
-        else:  # off-headline variants: LoRA r=64 / alpha=128 on q, k, v, output projections and the MLP; QLoRA adds an NF4 base
-            from torchtune_b200.models.llama3_1 import lora_llama3_1_8b
-            from torchtune_b200.modules.peft import get_adapter_params, set_trainable_params
-
-            model = lora_llama3_1_8b(lora_attn_modules=["q_proj", "k_proj", "v_proj", "output_proj"], apply_lora_to_mlp=True, lora_rank=64, lora_alpha=128,
-                                     quantize_base=args.variant == "qlora")
+        model = llama3_1(**MODEL)
         for name, p in model.named_parameters():
-            if p.dim() > 1 and p.is_floating_point() and "lora_b" not in name and not p.is_meta:
+            if p.dim() > 1 and p.is_floating_point() and not p.is_meta:
                 torch.nn.init.normal_(p, std=0.02)
-    if args.variant not in ("full", "zero3"):
-        set_trainable_params(model, get_adapter_params(model))
     if args.fp8:  # optional variant, never the default: decoder linears (not the output head) on the fp8 tensor cores
         training.convert_to_float8_training(model, "tensorwise")
     training.set_activation_checkpointing(model, {TransformerSelfAttentionLayer})
@@ -254,7 +245,7 @@ def run_ours(args) -> dict:
         "data": "synthetic uniform tokens, random-init weights",
         "impl": "ours",
         "config": {
-            "model": "llama3_1_8b" if args.variant in ("full", "zero3") else f"llama3_1_8b {args.variant} r64 (variant, not the headline)",
+            "model": "llama3_1_8b",
             "global_batch": BATCH_PER_GPU * world,
             "seq_len": SEQ_LEN,
             "doc_len": DOC_LEN,
@@ -271,6 +262,120 @@ def run_ours(args) -> dict:
     }
     if zero3:
         parallel.shutdown()
+    if world > 1:
+        dist.destroy_process_group()
+    return out if rank == 0 else {}
+
+
+PEFT_BATCH_PER_GPU = 8  # adapter fine-tuning configurations: 8 sequences of 2048 (LoRA / QLoRA), 8 preference pairs of 2 x 1024 (DPO)
+DPO_LEN, DPO_PROMPT, DPO_BETA = 1024, 256, 0.1
+
+
+def peft_host_batch(torch, variant: str, seed: int, vocab: int = MODEL["vocab_size"]):
+    """Pinned host batch of the adapter configurations.  ``lora`` / ``qlora``: 8 unpacked causal sequences of 2048 tokens.
+    ``dpo``: 8 chosen then 8 rejected sequences of 1024 tokens; each pair shares its first 256 tokens (the prompt), whose labels
+    are masked."""
+    g = torch.Generator().manual_seed(seed)
+    pin = (lambda t: t.pin_memory()) if torch.cuda.is_available() else (lambda t: t)
+    if variant == "dpo":
+        prompt = torch.randint(0, vocab, (PEFT_BATCH_PER_GPU, DPO_PROMPT), generator=g, dtype=torch.long)
+        tails = torch.randint(0, vocab, (2 * PEFT_BATCH_PER_GPU, DPO_LEN - DPO_PROMPT), generator=g, dtype=torch.long)
+        tokens = torch.cat([torch.cat([prompt, prompt]), tails], dim=1)
+        labels = tokens.clone()
+        labels[:, :DPO_PROMPT] = -100
+        return {"tokens": pin(tokens), "labels": pin(labels)}
+    tokens = torch.randint(0, vocab, (PEFT_BATCH_PER_GPU, SEQ_LEN), generator=g, dtype=torch.long)
+    labels = torch.roll(tokens, -1, dims=1)
+    labels[:, -1] = -100
+    return {"tokens": pin(tokens), "labels": pin(labels)}
+
+
+def run_ours_peft(args) -> dict:
+    """Adapter fine-tuning configurations (``--variant lora | qlora | dpo``): Llama-3.1-8B with LoRA r=64 / alpha=128 on the q, k,
+    v, output projections and the MLP, frozen bf16 (``qlora``: NF4) base weights, per-GPU batch 8, data parallel over all ranks.
+    ``dpo`` trains the adapters with the DPO loss (beta 0.1); its reference log-probabilities come from the same model with the
+    adapters switched off, computed inside the timed step."""
+    import torch
+    import torch.distributed as dist
+
+    from torchtune_b200 import parallel as par
+    from torchtune_b200 import training
+    from torchtune_b200.engine.preference import PreferenceStep
+    from torchtune_b200.engine.train_step import TrainStep
+    from torchtune_b200.models.llama3_1 import lora_llama3_1_8b
+    from torchtune_b200.modules import TransformerSelfAttentionLayer
+    from torchtune_b200.modules.loss import LinearCrossEntropyLoss
+    from torchtune_b200.modules.peft import get_adapter_params, set_trainable_params
+    from torchtune_b200.ops._lib import check_device_errors, lib
+    from torchtune_b200.rlhf.loss import DPOLoss
+
+    os.environ.setdefault("TTB_STRICT", "1")
+    rank, world, local = dist_env()
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    parallel = par.DataParallelEngine(device=device)
+    torch.manual_seed(1234)
+    with training.set_default_dtype(torch.bfloat16), device:
+        model = lora_llama3_1_8b(lora_attn_modules=["q_proj", "k_proj", "v_proj", "output_proj"], apply_lora_to_mlp=True, lora_rank=64, lora_alpha=128,
+                                 quantize_base=args.variant == "qlora")
+        for name, p in model.named_parameters():
+            if p.dim() > 1 and p.is_floating_point() and "lora_b" not in name:
+                torch.nn.init.normal_(p, std=0.02)
+    set_trainable_params(model, get_adapter_params(model))
+    training.set_activation_checkpointing(model, {TransformerSelfAttentionLayer})
+    model = parallel.prepare(model)
+    optimizer = parallel.build_optimizer(model, lr=LR)
+    if args.variant == "dpo":
+        step = PreferenceStep(model, DPOLoss(beta=DPO_BETA), optimizer, device, parallel=parallel)
+    else:
+        loss_fn = LinearCrossEntropyLoss(num_output_chunks=8)
+        loss_fn.set_model_output(model)
+        step = TrainStep(model, loss_fn, optimizer, device, parallel=parallel)
+
+    host_batches = [peft_host_batch(torch, args.variant, seed=1000 * rank + i) for i in range(4)]
+    dev_batches = [step.upload(h) for h in host_batches]
+    tokens_per_step = host_batches[0]["tokens"].numel() * world  # every token of the batch, as both reference recipes count them
+    L = lib()
+    losses = []
+    for i in range(args.warmup):
+        losses.append(step.compute(dev_batches[i % 4]))
+    torch.cuda.synchronize()
+    check_device_errors()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = L.ttb_launch_count()
+    t_kernel = timed_loop(torch, dist, world, lambda i: losses.append(step.compute(dev_batches[i % 4])), args.steps)
+    launches = L.ttb_launch_count() - launches0
+    t_e2e = timed_loop(torch, dist, world, lambda i: losses.append(float(step(host_batches[i % 4]).item())), args.steps)
+    clocks = sampler.stop() if rank == 0 else {}
+    check_device_errors()
+    h2d = sum(t.numel() * t.element_size() for t in host_batches[0].values())
+    value = tokens_per_step * args.steps / t_kernel
+    shape = f"{2 * PEFT_BATCH_PER_GPU} x {DPO_LEN} (8 pairs, shared {DPO_PROMPT}-token prompt)" if args.variant == "dpo" else f"{PEFT_BATCH_PER_GPU} x {SEQ_LEN}"
+    out = {
+        "metric": "tokens_per_second", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * t_kernel / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 (NF4 base weights, block 64, double-quantised scales)" if args.variant == "qlora" else "bf16",
+        "data": "synthetic uniform tokens, random-init weights", "impl": "ours",
+        "config": {
+            "model": f"llama3_1_8b {'LoRA-DPO' if args.variant == 'dpo' else ('QLoRA' if args.variant == 'qlora' else 'LoRA')} r64 alpha128 on q,k,v,o + w1,w2,w3",
+            "global_batch": PEFT_BATCH_PER_GPU * world, "per_gpu_tokens": shape, "seq_len": DPO_LEN if args.variant == "dpo" else SEQ_LEN,
+            "parallelism": f"dp{world}" if world > 1 else "single", "activation_checkpointing": True,
+            "optimizer": "AdamW lr 2e-5 over the adapter parameters (fused reduce+update+broadcast kernel)",
+            "l2": "inputs larger than L2 (the base weights are streamed every step)",
+        },
+        "clocks": clocks,
+        "e2e": {"value": tokens_per_step * args.steps / t_e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
+        "gpu_launches": int(launches),
+        "peak_mem_gib": round((torch.cuda.max_memory_allocated() + par.PeerBuffer.peak_bytes) / 2**30, 2),
+        "final_loss": float(losses[-1]) if losses else float("nan"),
+    }
+    if args.variant == "dpo":
+        out["config"]["loss"] = f"DPO beta {DPO_BETA}, reference = adapters disabled"
+    parallel.shutdown()
     if world > 1:
         dist.destroy_process_group()
     return out if rank == 0 else {}
@@ -472,7 +577,16 @@ def run_ours_sharded(args) -> dict:
 
 def run_reference(args) -> dict:
     from baseline.reference_arm import run as run_ref
+    from baseline.reference_arm import run_peft
 
+    if args.config != "8b":
+        from baseline.reference_arm import run_tensor_parallel
+
+        return run_tensor_parallel(args, args.config, SHARDED_CONFIGS[args.config], LR, ClockSampler, timed_loop, dist_env)
+    if args.variant in ("zero3", "tp") or args.fp8:
+        return {"impl": "reference", "unavailable": "the reference arm covers the full fine-tune (default), --variant lora | qlora | dpo and --config 70b_tp8 | 70b_tp4dp2"}
+    if args.variant in ("lora", "qlora", "dpo"):
+        return run_peft(args, MODEL, SEQ_LEN, PEFT_BATCH_PER_GPU, DPO_LEN, DPO_PROMPT, DPO_BETA, LR, ClockSampler, timed_loop, dist_env)
     return run_ref(args, MODEL, SEQ_LEN, DOC_LEN, BATCH_PER_GPU, LR, ClockSampler, timed_loop, dist_env)
 
 
@@ -482,9 +596,11 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--variant", choices=["full", "zero3", "lora", "qlora", "tp"], default="full", help="off-headline variants; the headline is always the full fine-tune")
+    ap.add_argument("--variant", choices=["full", "zero3", "lora", "qlora", "dpo", "tp"], default="full",
+                    help="off-headline variants; the headline is always the full fine-tune.  lora / qlora / dpo: the adapter configurations at per-GPU batch 8")
     ap.add_argument("--config", choices=["8b"] + sorted(SHARDED_CONFIGS), default="8b", help="8b: the headline (Llama-3.1-8B); the others are the 70B tensor-parallel and Scout expert-parallel configurations")
     ap.add_argument("--debug-layers", type=int, default=0, help="functional check of a --config on few GPUs: build only this many layers (the printed line is marked invalid)")
+    ap.add_argument("--ref-compile", action="store_true", help="with --impl reference: the reference's `compile: True` path (informational; the default arm stays on the stock eager path)")
     ap.add_argument("--fp8", action="store_true", help="variant: fp8 decoder linears (the headline number is always bf16)")
     args = ap.parse_args()
     rank, world, _ = dist_env()
@@ -498,7 +614,7 @@ def main() -> None:
         if args.config != "8b":
             result = run_ours_sharded(args)
         else:
-            result = run_ours_tp(args) if args.variant == "tp" else run_ours(args)
+            result = run_ours_tp(args) if args.variant == "tp" else (run_ours_peft(args) if args.variant in ("lora", "qlora", "dpo") else run_ours(args))
     if rank == 0:
         print(json.dumps(result), flush=True)
 

@@ -38,7 +38,7 @@ def _absent_rank_worker(rank, world, port, results):
 @pytest.mark.timeout(120)
 def test_rank_that_never_joins_ends_the_collective_with_an_error():
     results = mp.Manager().dict()
-    mp.spawn(_absent_rank_worker, args=(2, 29571, results), nprocs=2, join=True)
+    mp.spawn(_absent_rank_worker, args=(2, 29613, results), nprocs=2, join=True)
     assert results[1] == "absent"
     assert results[0].startswith("error after"), results[0]
     assert float(results[0].split()[2].rstrip("s:")) < 11.0, results[0]

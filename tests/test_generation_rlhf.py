@@ -179,3 +179,33 @@ def test_reward_codec_roundtrip():
     assert back.keys() == sd.keys()
     for k in sd:
         assert torch.equal(back[k], sd[k])
+
+
+def test_preference_step_trains_adapters_only():
+    """One DPO step through the engine's PreferenceStep: the reference pass runs with adapters disabled, only adapter
+    parameters move, and the loss of the first step equals -log(sigmoid(0)) because policy and reference coincide (LoRA B = 0)."""
+    from torchtune_b200.engine.preference import PreferenceStep
+    from torchtune_b200.models.llama3 import lora_llama3
+    from torchtune_b200.modules.peft import get_adapter_params, set_trainable_params
+    from torchtune_b200.rlhf.loss import DPOLoss
+
+    torch.manual_seed(0)
+    model = lora_llama3(lora_attn_modules=["q_proj", "v_proj"], apply_lora_to_mlp=True, vocab_size=64, num_layers=2, num_heads=4, num_kv_heads=2, embed_dim=32,
+                        max_seq_len=64, intermediate_dim=64, lora_rank=4, lora_alpha=8.0)
+    set_trainable_params(model, get_adapter_params(model))
+    frozen = {n: p.detach().clone() for n, p in model.named_parameters() if not p.requires_grad}
+    opt = torch.optim.AdamW([p for p in model.parameters() if p.requires_grad], lr=1e-2)
+    step = PreferenceStep(model, DPOLoss(beta=0.1), opt, torch.device("cpu"))
+    prompt = torch.randint(0, 64, (3, 5))
+    tokens = torch.cat([torch.cat([prompt, prompt]), torch.randint(0, 64, (6, 11))], dim=1)
+    labels = tokens.clone()
+    labels[:, :5] = -100
+    first = step({"tokens": tokens, "labels": labels})
+    assert abs(float(first) - 0.6931472) < 1e-4
+    for _ in range(5):
+        last = step({"tokens": tokens, "labels": labels})
+    assert float(last) < float(first)  # the adapters learn to prefer the chosen halves
+    assert float(step.last_stats["rewards/accuracies"]) > 0.5
+    for n, p in model.named_parameters():
+        if not p.requires_grad:
+            assert torch.equal(p, frozen[n])

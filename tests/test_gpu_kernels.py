@@ -112,12 +112,14 @@ def test_gemm_benchmark_shapes_match_matmul():
     _close(gemm(dy, x, a_mn=True, b_mn=True), torch.matmul(dy.t(), x), 2e-2, 1.0, "wgrad 14336x4096x8192")
 
 
-def test_linear_autograd():
+@pytest.mark.parametrize("n_out", [512, 4, 1])  # 4 and 1: output widths that are not a multiple of 8 (router over 4 experts, scalar head)
+def test_linear_autograd(n_out):
     x = _rand(3, 40, 256, seed=8).requires_grad_()
-    w = _rand(512, 256, seed=9, scale=0.05).requires_grad_()
-    bias = _rand(512, seed=10).requires_grad_()
+    w = _rand(n_out, 256, seed=9, scale=0.05).requires_grad_()
+    bias = _rand(n_out, seed=10).requires_grad_()
     y = ops.linear(x, w, bias)
-    gy = _rand(3, 40, 512, seed=11)
+    assert y.shape == (3, 40, n_out)
+    gy = _rand(3, 40, n_out, seed=11)
     y.backward(gy)
     xr, wr, br = (t.detach().float().requires_grad_() for t in (x, w, bias))
     yr = torch.nn.functional.linear(xr, wr, br)
@@ -738,7 +740,8 @@ def test_gemm_weight_gather_fused_emulated_ranks(world, rows, K, M):
 
 
 # ----------------------------------------------------------------------------- two operand pairs, one accumulator (LoRA-fused GEMM)
-@pytest.mark.parametrize("M,N,K,K2", [(256, 320, 192, 64), (1000, 512, 1024, 8), (2048, 4096, 512, 96)])
+@pytest.mark.parametrize("M,N,K,K2", [(256, 320, 192, 64), (1000, 512, 1024, 8), (2048, 4096, 512, 96),
+                                      (8192, 4096, 1024, 64), (4100, 6152, 512, 24)])  # the last two are large enough for the CTA-pair kernel
 @pytest.mark.parametrize("b_mn", [False, True])
 def test_gemm_dual_matches_sum_of_products(M, N, K, K2, b_mn):
     from torchtune_b200.ops._cuda import gemm_dual
@@ -880,3 +883,78 @@ def test_attention_softcap(mask):
     """Gemma-2 style soft-capped scores (tanh inside the softmax warps; its derivative in the backward pass)."""
     _attn_general(2, 384, 384, 4, 2, 128, mask, softcap=30.0, seed=50)
     _attn_general(1, 200, 200, 4, 4, 64, mask, softcap=5.0, seed=51)
+
+
+# ------------------------------------------------------------------ gate / up projections with SwiGLU in the GEMM epilogue
+@pytest.mark.parametrize("M,K,N", [(2048, 512, 4864), (4096, 1024, 2688), (2304, 328, 4104)])
+def test_gate_up_swiglu_fused_gemm(M, K, N):
+    """One CTA-pair GEMM whose two B halves are the gate and the up projection, SwiGLU in the epilogue: forward value with and
+    without gradients, and the gradients of x, W1, W3 against fp32."""
+    from torchtune_b200.ops._cuda import gate_up_swiglu
+
+    x = _rand(M, K, seed=1, scale=0.5).requires_grad_()
+    w1 = _rand(N, K, seed=2, scale=0.05).requires_grad_()
+    w3 = _rand(N, K, seed=3, scale=0.05).requires_grad_()
+    with torch.no_grad():
+        h0 = gate_up_swiglu(x, w1, w3)
+    assert h0 is not None, "shape was expected to qualify for the fused kernel"
+    h = gate_up_swiglu(x, w1, w3)
+    assert torch.equal(h, h0)  # the gradient-free pass (no pre-activations stored) computes the same values
+    dh = _rand(M, N, seed=4, scale=0.1)
+    h.backward(dh)
+    xr, w1r, w3r = (t.detach().float().requires_grad_() for t in (x, w1, w3))
+    g, u = xr @ w1r.t(), xr @ w3r.t()
+    hr = torch.nn.functional.silu(g) * u
+    hr.backward(dh.float())
+    _close(h, hr, 3e-2, 3e-2, "fused swiglu fwd")
+    _close(x.grad, xr.grad, 3e-2, 5e-2, "fused swiglu dx")
+    _close(w1.grad, w1r.grad, 3e-2, 0.3, "fused swiglu dw1")
+    _close(w3.grad, w3r.grad, 3e-2, 0.3, "fused swiglu dw3")
+
+
+# ------------------------------------------------------------------ MoE routing and row kernels
+@pytest.mark.parametrize("T,E,k", [(1000, 16, 1), (513, 8, 2), (64, 128, 4)])
+def test_moe_route_kernel_matches_sigmoid_topk(T, E, k):
+    from torchtune_b200.ops._cuda import moe_route
+
+    logits = _rand(T, E, seed=1, scale=2.0).requires_grad_()
+    scores, selected = moe_route(logits, k)
+    ref_scores = torch.sigmoid(logits.detach().float()).to(torch.bfloat16)
+    want_s, want_i = torch.topk(ref_scores, k=k, dim=1)
+    assert torch.equal(scores, want_s)  # values are unique up to ties; tied experts may differ in index, never in score
+    assert torch.equal(ref_scores.gather(1, selected), want_s)
+    dscores = _rand(T, k, seed=2)
+    scores.backward(dscores)
+    lr = logits.detach().float().requires_grad_()
+    torch.sigmoid(lr).gather(1, selected).backward(dscores.float())
+    _close(logits.grad, lr.grad, 3e-2, 1e-3, "router logit gradient")
+
+
+def test_moe_gather_and_combine_row_kernels():
+    """Permute·score and un-permute + sum against index_select / index_add, forward and backward, top-2 routing."""
+    from torchtune_b200.ops._cuda import moe_combine, moe_gather, moe_route_sort
+
+    T, D, E, k = 300, 256, 8, 2
+    x = _rand(T, D, seed=1).requires_grad_()
+    sel = torch.stack([torch.randperm(E, device="cuda")[:k] for _ in range(T)])
+    scores = torch.rand(T, k, device="cuda").to(torch.bfloat16).requires_grad_()
+    counts, order, inv = moe_route_sort(sel.reshape(-1), E, with_inverse=True)
+    assert torch.equal(inv[order], torch.arange(T * k, device="cuda")) and counts.sum().item() == T * k
+    token_idx = order // k
+    top = scores.reshape(-1)[order]
+    routed = moe_gather(x, token_idx, top, inv, k)
+    base = _rand(T, D, seed=3).requires_grad_()
+    w = _rand(T * k, D, seed=4, scale=0.5)
+    out = moe_combine(routed * w, inv, token_idx, base, k)
+    go = _rand(T, D, seed=5)
+    out.backward(go)
+
+    xr, sr, br = (t.detach().float().requires_grad_() for t in (x, scores, base))
+    routed_r = xr.index_select(0, token_idx) * sr.reshape(-1)[order].reshape(-1, 1)
+    out_r = br.index_add(0, token_idx, routed_r * w.float())
+    out_r.backward(go.float())
+    _close(routed, routed_r, 2e-2, 2e-2, "gather·score")
+    _close(out, out_r, 3e-2, 5e-2, "combine")
+    _close(x.grad, xr.grad, 3e-2, 5e-2, "dx")
+    _close(base.grad, br.grad, 1e-2, 1e-2, "dbase")
+    _close(scores.grad, sr.grad, 5e-2, 0.3, "dscores")

@@ -83,7 +83,7 @@ def test_multi_store_adamw_on_a_2x2_mesh_matches_single_process():
     want_sd, want_norms = _single_process()
     mgr = mp.Manager()
     results = mgr.dict()
-    mp.spawn(_worker, args=(4, 29571, results), nprocs=4, join=True)
+    mp.spawn(_worker, args=(4, 29611, results), nprocs=4, join=True)
     for rank in range(4):
         got = results[rank]
         torch.testing.assert_close(torch.tensor(got["norms"]), torch.tensor(want_norms), rtol=1e-4, atol=1e-5)

@@ -257,3 +257,36 @@ def test_lora_llama4_vision_encoder_builders():
     head_only = lora_llama4_vision_encoder(False, True, ["q_proj"], apply_lora_to_output=True, lora_rank=4, lora_alpha=8, **kw)
     assert all(k.startswith("projection.") for k in get_adapter_params(head_only)) and len(get_adapter_params(head_only)) == 6
     assert len(get_adapter_params(lora_llama4_vision_encoder(False, True, ["q_proj"], apply_lora_to_output=False, lora_rank=4, lora_alpha=8, **kw))) == 0
+
+
+def test_whole_decoder_exports_with_and_without_kv_cache():
+    """``torch.export`` of the complete decoder after the export-friendly attention swap: the exported program reproduces eager
+    logits, and — with KV caches set up — a prefill followed by single-token steps through the *exported* module (whose cache
+    buffers are graph state) reproduces the cache-free forward pass."""
+    from torchtune_b200.models.llama2 import llama2
+    from torchtune_b200.modules._export import replace_mha_with_inference_mha
+
+    torch.manual_seed(0)
+    model = llama2(vocab_size=64, num_layers=2, num_heads=4, num_kv_heads=2, embed_dim=32, max_seq_len=32, intermediate_dim=48).eval()
+    replace_mha_with_inference_mha(model)
+    tokens = torch.randint(0, 64, (2, 9))
+    with torch.no_grad():
+        want = model(tokens)
+        program = torch.export.export(model, (tokens,))
+        torch.testing.assert_close(program.module()(tokens), want, rtol=1e-5, atol=1e-5)
+
+        model.setup_caches(batch_size=2, dtype=torch.float32, decoder_max_seq_len=12)
+        causal = torch.tril(torch.ones(12, 12, dtype=torch.bool))
+        pos = torch.arange(12)
+        prefill_kwargs = {"mask": causal[None, :5].expand(2, -1, -1), "input_pos": pos[None, :5].expand(2, -1)}
+        step_kwargs = {"mask": causal[None, 5:6].expand(2, -1, -1), "input_pos": pos[None, 5:6].expand(2, -1)}
+        prefill = torch.export.export(model, (tokens[:, :5],), prefill_kwargs).module()
+        step = torch.export.export(model, (tokens[:, 5:6],), step_kwargs).module()
+        # the two exported programs own separate copies of the cache buffers: carry the state over explicitly
+        out = [prefill(tokens[:, :5], **prefill_kwargs)]
+        step.load_state_dict(prefill.state_dict(), strict=False)
+        for name, buf in prefill.named_buffers():
+            dict(step.named_buffers())[name].copy_(buf)
+        for t in range(5, 9):
+            out.append(step(tokens[:, t : t + 1], mask=causal[None, t : t + 1].expand(2, -1, -1), input_pos=pos[None, t : t + 1].expand(2, -1)))
+        torch.testing.assert_close(torch.cat(out, dim=1), want, rtol=1e-4, atol=1e-4)

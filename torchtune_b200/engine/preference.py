@@ -67,6 +67,66 @@ def sequence_logprobs(model: nn.Module, tokens: torch.Tensor, labels: torch.Tens
     return per_token.sum(-1), mean_logit
 
 
+class PreferenceStep:
+    """One preference-optimisation step on a batch that already lives on the device: concatenated policy forward, reference
+    forward (a frozen ``ref_model``, or the policy itself with its adapters switched off), preference loss, backward, update.
+
+    ``tokens`` / ``labels`` are ``[2B, L]`` with the chosen sequences first (recipes/lora_dpo_distributed.py:592-640).  The
+    returned loss is the mean over this rank's pairs (a device scalar; nothing is read back here).  With a ``parallel`` engine
+    the gradients are averaged over its data-parallel ranks by the engine's fused update.
+    """
+
+    def __init__(self, model: nn.Module, loss_fn, optimizer, device: torch.device, parallel=None, ref_model: Optional[nn.Module] = None,
+                 clip_grad_norm: Optional[float] = None, activations_ctx=None):
+        self.model, self.loss_fn, self.optimizer, self.device = model, loss_fn, optimizer, device
+        self.parallel, self.ref_model, self.clip_grad_norm = parallel, ref_model, clip_grad_norm
+        self.activations_ctx = activations_ctx
+        self._params = [p for p in model.parameters() if p.requires_grad]
+        self.last_stats: Dict[str, torch.Tensor] = {}
+
+    def upload(self, batch: Dict[str, Any]) -> Dict[str, Any]:
+        return {k: (v.to(self.device, non_blocking=True) if torch.is_tensor(v) else v) for k, v in batch.items()}
+
+    def _logps(self, model: nn.Module, tokens: torch.Tensor, labels: torch.Tensor) -> ChosenRejectedOutputs:
+        n = tokens.shape[0] // 2
+        if self.activations_ctx is not None:
+            with self.activations_ctx:
+                logps, _ = sequence_logprobs(model, tokens, labels)
+        else:
+            logps, _ = sequence_logprobs(model, tokens, labels)
+        return ChosenRejectedOutputs(chosen_logps=logps[:n], rejected_logps=logps[n:])
+
+    def reference(self, tokens: torch.Tensor, labels: torch.Tensor) -> ChosenRejectedOutputs:
+        if getattr(self.loss_fn, "is_reference_free", lambda: False)() is True:
+            return ChosenRejectedOutputs(None, None)
+        with torch.no_grad():
+            if self.ref_model is not None:
+                return self._logps(self.ref_model, tokens, labels)
+            with disable_adapter(self.model):
+                return self._logps(self.model, tokens, labels)
+
+    def compute(self, batch: Dict[str, Any]) -> torch.Tensor:
+        tokens, labels = batch["tokens"], batch["labels"]
+        policy = self._logps(self.model, tokens, labels)
+        reference = self.reference(tokens, labels)
+        losses, chosen_rewards, rejected_rewards = self.loss_fn(policy, reference)
+        loss = losses.mean()
+        loss.backward()
+        self.last_stats = {"rewards/chosen": chosen_rewards.mean(), "rewards/rejected": rejected_rewards.mean(),
+                           "rewards/accuracies": (chosen_rewards > rejected_rewards).float().mean()}
+        if self.parallel is not None:
+            self.parallel.optimizer_step(self.model, self.optimizer, 1.0 / self.parallel.dp_size, self.clip_grad_norm)
+        else:
+            if self.clip_grad_norm is not None:
+                torch.nn.utils.clip_grad_norm_(self._params, max_norm=float(self.clip_grad_norm))
+            self.optimizer.step()
+            self.optimizer.zero_grad(set_to_none=True)
+        return loss.detach()
+
+    def __call__(self, host_batch: Dict[str, Any]) -> torch.Tensor:
+        return self.compute(self.upload(host_batch))
+
+
 class DPOTrainer(SFTTrainer):
     def __init__(self, cfg: DictConfig, *, distributed: bool = False, lora: bool = True) -> None:
         super().__init__(cfg, distributed=distributed, lora=lora)

@@ -29,7 +29,18 @@ class FeedForward(nn.Module):
         self.activation = activation
         self._silu = isinstance(activation, nn.SiLU)
 
+    def _fusable(self) -> bool:
+        """Plain bias-free bf16 linears on both sides of a SiLU gate: the gate / up projections and the activation run as one GEMM."""
+        lin = (type(self.w1), type(self.w3))
+        return self._silu and all(t.__name__ == "Linear" and issubclass(t, nn.Linear) for t in lin) and self.w1.bias is None and self.w3.bias is None
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.w3 is not None and ops.cuda_ops_enabled(x) and x.dtype == torch.bfloat16 and self._fusable():
+            from ..ops._cuda import gate_up_swiglu
+
+            h = gate_up_swiglu(x, self.w1.weight, self.w3.weight)
+            if h is not None:
+                return self.w2(h)
         g = self.w1(x)
         if self.w3 is None:
             return self.w2(self.activation(g))

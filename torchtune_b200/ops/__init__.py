@@ -92,7 +92,15 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
 
         if x.shape[-1] % 8 == 0 and weight.shape[0] % 8 == 0:
             return _cuda.linear(x, weight, bias)
-        _fallback("linear", f"K={x.shape[-1]} or N={weight.shape[0]} is not a multiple of 8 (TMA row pitch)", x)
+        if x.shape[-1] % 8 == 0:
+            # an output width that is not a multiple of 8 (a router over 4 experts, a scalar reward head): rows of zeros are
+            # appended to the weight so the output row pitch is a multiple of 16 bytes, and the extra columns are cut off again;
+            # autograd carries the padding and the slice through the backward pass
+            n = weight.shape[0]
+            pad = (-n) % 8
+            y = _cuda.linear(x, F.pad(weight, (0, 0, 0, pad)), None if bias is None else F.pad(bias, (0, pad)))
+            return y[..., :n]
+        _fallback("linear", f"K={x.shape[-1]} is not a multiple of 8 (TMA row pitch)", x)
     return F.linear(x, weight, bias)
 
 

@@ -98,6 +98,11 @@ def gemm_dual(a: torch.Tensor, b: torch.Tensor, a2: torch.Tensor, b2: torch.Tens
     K2 = a2.shape[1]
     N = b.shape[1] if b_mn else b.shape[0]
     out = torch.empty(M, N, dtype=_BF16, device=a.device)
+    if K % 8 == 0 and K2 % 8 == 0 and _use_pair_kernel(M, N, K, out):
+        rc = lib().ttb_gemm_bf16_dual_2sm(a.data_ptr(), b.data_ptr(), a2.data_ptr(), b2.data_ptr(), out.data_ptr(), M, N, K, K2, int(b_mn), a.stride(0), b.stride(0),
+                                          a2.stride(0), b2.stride(0), out.stride(0), _ptr(bias), 1.0, err_word(a.device).data_ptr(), stream_ptr())
+        check(rc, f"gemm_dual (CTA pairs) M={M} N={N} K={K} K2={K2} b_mn={b_mn}")
+        return out
     rc = lib().ttb_gemm_bf16_dual(a.data_ptr(), b.data_ptr(), a2.data_ptr(), b2.data_ptr(), out.data_ptr(), M, N, K, K2, 0, int(b_mn), a.stride(0), b.stride(0),
                                   a2.stride(0), b2.stride(0), out.stride(0), 0, 0, _ptr(bias), 1.0, err_word(a.device).data_ptr(), stream_ptr())
     check(rc, f"gemm_dual M={M} N={N} K={K} K2={K2} b_mn={b_mn}")
@@ -475,14 +480,137 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, padding_idx: Optional[int]
     return _Embedding.apply(ids, table, padding_idx)
 
 
-def moe_route_sort(expert_ids: torch.Tensor, num_experts: int) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Stable counting sort of ``expert_ids`` (int64, flat): ``(counts[E], order[n])`` with ``expert_ids[order]`` ascending."""
-    ids = expert_ids.reshape(-1).contiguous()
+def moe_route_sort(expert_ids: torch.Tensor, num_experts: int, with_inverse: bool = False):
+    """Stable counting sort of routed pairs by expert: ``(counts [E], order [n])`` (+ ``inverse [n]``: where each pair went)."""
+    ids = expert_ids.to(torch.int64).contiguous()
     n = ids.numel()
     counts = torch.empty(num_experts, dtype=torch.int64, device=ids.device)
     order = torch.empty(n, dtype=torch.int64, device=ids.device)
-    check(lib().ttb_moe_route_sort(ids.data_ptr(), n, num_experts, counts.data_ptr(), order.data_ptr(), stream_ptr()), "moe_route_sort")
-    return counts, order
+    inverse = torch.empty(n, dtype=torch.int64, device=ids.device) if with_inverse else None
+    L = lib()
+    L.ttb_moe_route_sort.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+    check(L.ttb_moe_route_sort(ids.data_ptr(), n, num_experts, counts.data_ptr(), order.data_ptr(), _ptr(inverse), stream_ptr()), "moe_route_sort")
+    return (counts, order, inverse) if with_inverse else (counts, order)
+
+
+def _declare_route(L) -> None:
+    if getattr(L, "_route_declared", False):
+        return
+    vp, i32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+    L.ttb_moe_route.argtypes = [vp, i32, i64, i32, i32, vp, vp, vp]
+    L.ttb_moe_route_bwd.argtypes = [vp, i32, vp, vp, i64, i32, i32, vp, vp]
+    L.ttb_moe_gather_rows.argtypes = [vp, vp, vp, vp, i64, i32, i64, vp]
+    L.ttb_moe_combine_rows.argtypes = [vp, vp, vp, vp, vp, i64, i32, i32, i64, vp]
+    L.ttb_moe_row_dots.argtypes = [vp, vp, vp, vp, i64, i32, i64, vp]
+    for fn in (L.ttb_moe_route, L.ttb_moe_route_bwd, L.ttb_moe_gather_rows, L.ttb_moe_combine_rows, L.ttb_moe_row_dots):
+        fn.restype = i32
+    L._route_declared = True
+
+
+class _MoERoute(torch.autograd.Function):
+    """Gate logits ``[T, E]`` → ``(scores [T, k] bf16, selected [T, k] int64)``: sigmoid and top-k in one kernel, one warp per token."""
+
+    @staticmethod
+    def forward(ctx, logits, k):
+        T, E = logits.shape
+        L = lib()
+        _declare_route(L)
+        lg = logits.contiguous()
+        scores = torch.empty(T, k, dtype=_BF16, device=lg.device)
+        selected = torch.empty(T, k, dtype=torch.int64, device=lg.device)
+        check(L.ttb_moe_route(lg.data_ptr(), int(lg.dtype == torch.float32), T, E, k, scores.data_ptr(), selected.data_ptr(), stream_ptr()), "moe_route")
+        ctx.save_for_backward(lg, selected)
+        ctx.k = k
+        ctx.mark_non_differentiable(selected)
+        return scores, selected
+
+    @staticmethod
+    def backward(ctx, dscores, _dsel):
+        lg, selected = ctx.saved_tensors
+        T, E = lg.shape
+        dl = torch.empty_like(lg)
+        check(lib().ttb_moe_route_bwd(lg.data_ptr(), int(lg.dtype == torch.float32), selected.data_ptr(), dscores.to(_BF16).contiguous().data_ptr(), T, E, ctx.k, dl.data_ptr(), stream_ptr()),
+              "moe_route_bwd")
+        return dl, None
+
+
+def moe_route(logits: torch.Tensor, k: int):
+    return _MoERoute.apply(logits, k)
+
+
+def _gather_rows(x, idx, scale):
+    P, D = idx.numel(), x.shape[1]
+    out = torch.empty(P, D, dtype=_BF16, device=x.device)
+    if P:
+        check(lib().ttb_moe_gather_rows(x.data_ptr(), idx.data_ptr(), _ptr(scale), out.data_ptr(), P, D, x.shape[0], stream_ptr()), "moe_gather_rows")
+    return out
+
+
+def _combine_rows(src, inv, scale, base, T, k):
+    D = src.shape[1]
+    out = torch.empty(T, D, dtype=_BF16, device=src.device)
+    check(lib().ttb_moe_combine_rows(src.data_ptr(), inv.data_ptr(), _ptr(scale), _ptr(base), out.data_ptr(), T, k, D, src.shape[0], stream_ptr()), "moe_combine_rows")
+    return out
+
+
+class _MoEGather(torch.autograd.Function):
+    """``out[j] = x[idx[j]] · scale[j]`` for the pairs in expert order; ``inv [T·k]`` is the position of pair (t, s) in that order,
+    which turns the gradient with respect to ``x`` into a pull (no atomics)."""
+
+    @staticmethod
+    def forward(ctx, x, idx, scale, inv, k):
+        _declare_route(lib())
+        x, idx, inv = x.contiguous(), idx.contiguous(), inv.contiguous()
+        scale = None if scale is None else scale.to(_BF16).contiguous()
+        ctx.save_for_backward(x, idx, scale, inv)
+        ctx.k = k
+        return _gather_rows(x, idx, scale)
+
+    @staticmethod
+    def backward(ctx, dout):
+        x, idx, scale, inv = ctx.saved_tensors
+        dout = dout.contiguous()
+        dx = dscale = None
+        if ctx.needs_input_grad[0]:
+            dx = _combine_rows(dout, inv, scale, None, x.shape[0], ctx.k)
+        if scale is not None and ctx.needs_input_grad[2]:
+            dscale = torch.empty(idx.numel(), dtype=_BF16, device=x.device)
+            if idx.numel():
+                check(lib().ttb_moe_row_dots(x.data_ptr(), idx.data_ptr(), dout.data_ptr(), dscale.data_ptr(), idx.numel(), x.shape[1], x.shape[0], stream_ptr()), "moe_row_dots")
+        return dx, None, dscale, None, None
+
+
+class _MoECombine(torch.autograd.Function):
+    """``out[t] = base[t] + Σ_s src[inv[t·k + s]]`` — the expert outputs back in token order, summed over the token's experts."""
+
+    @staticmethod
+    def forward(ctx, src, inv, idx, base, k):
+        _declare_route(lib())
+        src, inv, idx = src.contiguous(), inv.contiguous(), idx.contiguous()
+        base = None if base is None else base.contiguous()
+        T = inv.numel() // k
+        ctx.save_for_backward(idx)
+        ctx.rows = src.shape[0]
+        ctx.has_base = base is not None
+        return _combine_rows(src, inv, None, base, T, k)
+
+    @staticmethod
+    def backward(ctx, dout):
+        (idx,) = ctx.saved_tensors
+        dout = dout.contiguous()
+        dsrc = None
+        if ctx.needs_input_grad[0]:
+            g = _gather_rows(dout, idx, None)
+            dsrc = g if g.shape[0] == ctx.rows else torch.cat([g, g.new_zeros(ctx.rows - g.shape[0], g.shape[1])])
+        return dsrc, None, None, (dout if ctx.has_base and ctx.needs_input_grad[3] else None), None
+
+
+def moe_gather(x, idx, scale, inv, k):
+    return _MoEGather.apply(x, idx, scale, inv, k)
+
+
+def moe_combine(src, inv, idx, base, k):
+    return _MoECombine.apply(src, inv, idx, base, k)
 
 
 def moe_permute_indices(tokens_per_expert_group: torch.Tensor, experts_per_rank: int, num_ranks: int, max_len: int, alignment: int):
@@ -687,6 +815,76 @@ class _SwiGLU(torch.autograd.Function):
         du = torch.empty(rows, H, dtype=g2.dtype, device=g2.device)
         check(lib().ttb_swiglu_bwd(dy2.data_ptr(), g2.data_ptr(), u2.data_ptr(), dg.data_ptr(), du.data_ptr(), rows, H, dy2.stride(0), g2.stride(0), u2.stride(0), H, H, stream_ptr()), "swiglu_bwd")
         return dg.view(dy.shape), du.view(dy.shape)
+
+
+class _GateUpSwiGLU(torch.autograd.Function):
+    """``silu(x · W1ᵀ) ⊙ (x · W3ᵀ)`` as one launch of the CTA-pair GEMM: the even CTA of a pair loads rows of ``W1``, the odd one the same
+    rows of ``W3``, and the epilogue applies the activation (``csrc/gemm2sm.cu``, SWIGLU form).  In a gradient-free pass (the first forward
+    under activation checkpointing) the two pre-activations never reach HBM; otherwise the epilogue also stores them for backward, which
+    is the existing SwiGLU-backward kernel followed by the usual input- and weight-gradient GEMMs."""
+
+    @staticmethod
+    def forward(ctx, x, w1, w3):
+        K, N = x.shape[-1], w1.shape[0]
+        x2 = x.reshape(-1, K)
+        if x2.stride(1) != 1 or x2.stride(0) % 8 or x2.data_ptr() % 16:
+            x2 = x2.contiguous()
+        M = x2.shape[0]
+        keep = any(ctx.needs_input_grad)
+        h = torch.empty(M, N, dtype=_BF16, device=x.device)
+        g = torch.empty(M, N, dtype=_BF16, device=x.device) if keep else None
+        u = torch.empty(M, N, dtype=_BF16, device=x.device) if keep else None
+        L = lib()
+        if not getattr(L, "_swiglu_gemm_declared", False):
+            vp, i32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+            L.ttb_gemm_swiglu_bf16_2sm.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, vp, vp]
+            L.ttb_gemm_swiglu_bf16_2sm.restype = i32
+            L._swiglu_gemm_declared = True
+        check(L.ttb_gemm_swiglu_bf16_2sm(x2.data_ptr(), w1.data_ptr(), w3.data_ptr(), h.data_ptr(), _ptr(g), _ptr(u), M, N, K, x2.stride(0), w1.stride(0), N,
+                                         err_word(x.device).data_ptr(), stream_ptr()), f"gate/up GEMM + SwiGLU M={M} N={N} K={K}")
+        ctx.save_for_backward(x2, w1, w3, g, u)
+        ctx.x_shape = x.shape
+        return h.view(*x.shape[:-1], N)
+
+    @staticmethod
+    def backward(ctx, dh):
+        x2, w1, w3, g, u = ctx.saved_tensors
+        M, N = g.shape
+        dh2 = dh.reshape(M, N)
+        if dh2.stride(1) != 1:
+            dh2 = dh2.contiguous()
+        dg = torch.empty(M, N, dtype=_BF16, device=g.device)
+        du = torch.empty(M, N, dtype=_BF16, device=g.device)
+        check(lib().ttb_swiglu_bwd(dh2.data_ptr(), g.data_ptr(), u.data_ptr(), dg.data_ptr(), du.data_ptr(), M, N, dh2.stride(0), N, N, N, N, stream_ptr()), "swiglu_bwd")
+        dx = dw1 = dw3 = None
+        if ctx.needs_input_grad[1]:
+            dw1 = _wgrad(w1, dg, x2)
+        if ctx.needs_input_grad[2]:
+            dw3 = _wgrad(w3, du, x2)
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dg, w1, b_mn=True)
+            gemm(du, w3, b_mn=True, out=dx, accumulate=True)
+            dx = dx.view(ctx.x_shape)
+        return dx, dw1, dw3
+
+
+def gate_up_swiglu(x: torch.Tensor, w1: torch.Tensor, w3: torch.Tensor) -> Optional[torch.Tensor]:
+    """Fused gate / up projections + SwiGLU, or ``None`` when the shapes do not suit the CTA-pair kernel (the caller then runs the three
+    separate operators)."""
+    if not _PAIR_KERNEL or os.environ.get("TTB_FUSE_SWIGLU", "1") == "0":
+        return None
+    K, N = x.shape[-1], w1.shape[0]
+    M = x.numel() // K
+    if w1.shape != w3.shape or w1.dtype != _BF16 or w3.dtype != _BF16 or K % 8 or N % 8 or not (w1.is_contiguous() and w3.is_contiguous()):
+        return None
+    if w1.data_ptr() % 16 or w3.data_ptr() % 16:
+        return None
+    global _SM_PAIRS
+    if _SM_PAIRS is None:
+        _SM_PAIRS = max(1, torch.cuda.get_device_properties(x.device).multi_processor_count // 2)
+    if K < 128 or (-(-M // 256)) * (-(-N // 128)) < _SM_PAIRS:
+        return None
+    return _GateUpSwiGLU.apply(x, w1, w3)
 
 
 def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:

@@ -36,9 +36,14 @@ static constexpr int kStages = 6;
 static constexpr int kEpiBytes = 4 * 2 * 4096;  // per epilogue warp two 32 x 64 bf16 staging tiles
 static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*barriers*/ + kEpiBytes + 1024 /*align slack*/;
 static_assert(kSmemBytes <= 232448, "shared memory budget of one CTA");
+// the SwiGLU form gives one pipeline stage to two more staging tiles per epilogue warp
+static constexpr int kStagesSwiglu = 5;
+static constexpr int kSmemBytesSwiglu = kStagesSwiglu * kStageBytes + 1024 + 2 * kEpiBytes + 1024;
+static_assert(kSmemBytesSwiglu <= 232448, "shared memory budget of one CTA");
 
 struct Params {
   int M, N, K;
+  int K2;  // > 0: a second operand pair (tmA2, tmB2) with K2 contraction columns extends the main loop (LoRA: one accumulator)
   void* C;
   long long ldc;
   const __nv_bfloat16* bias;
@@ -46,6 +51,8 @@ struct Params {
   int accumulate;
   int tma_store;
   int group_m;  // pair-tiles in m per scheduling group
+  int tile_mult;  // 1, or an odd multiplier coprime to the tile count: tile t is replaced by (t · tile_mult) mod tiles (debug aid)
+  int save_gate_up;  // SWIGLU form: also store the two pre-activations (the backward pass needs them)
   int* err;
 };
 
@@ -107,19 +114,28 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int gro
   n_blk = r / gsize;
 }
 
-template <bool A_MN, bool B_MN>
+// SWIGLU: the pair's two B halves come from *two* weight matrices — the even CTA loads 128 rows of the gate projection (tmB), the odd
+// CTA the same 128 rows of the up projection (tmB2) — so accumulator columns [0, 128) hold the gate and [128, 256) the up pre-activations
+// of the same 128 hidden units, in both CTAs' tensor memory.  The epilogue writes h = silu(gate) · up ([M, N], N = hidden width; tmC) and,
+// when the backward pass will need them, gate and up as well (tmG, tmU).  The separate SwiGLU kernel and its re-read of both
+// pre-activations disappear; in a gradient-free forward pass the pre-activations never reach HBM at all.
+template <bool A_MN, bool B_MN, bool SWIGLU>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
-gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC, Params p) {
+gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC,
+               const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ CUtensorMap tmG, const __grid_constant__ CUtensorMap tmU,
+               const __grid_constant__ CUtensorMap tmA2, Params p) {
+  constexpr int kNS = SWIGLU ? kStagesSwiglu : kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
-  uint64_t* full = bars;                 // [kStages]  used in the even CTA
-  uint64_t* empty = bars + kStages;      // [kStages]  both CTAs
-  uint64_t* tfull = bars + 2 * kStages;  // [2]        both CTAs
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kNS * kStageBytes);
+  uint64_t* full = bars;                 // [kNS]  used in the even CTA
+  uint64_t* empty = bars + kNS;      // [kNS]  both CTAs
+  uint64_t* tfull = bars + 2 * kNS;  // [2]        both CTAs
   uint64_t* tempty = tfull + 2;          // [2]        used in the even CTA
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  uint8_t* epi = smem + kStages * kStageBytes + 1024;
+  uint8_t* epi = smem + kNS * kStageBytes + 1024;
+  uint8_t* epi_extra = epi + kEpiBytes;  // SWIGLU: per epilogue warp one more pair of staging tiles (gate, up)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -127,12 +143,15 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
   const int num_m = (p.M + PM - 1) / PM;
-  const int num_n = (p.N + BN - 1) / BN;
+  constexpr int kTileN = SWIGLU ? BN / 2 : BN;  // output columns per tile
+  const int num_n = (p.N + kTileN - 1) / kTileN;
   const int num_tiles = num_m * num_n;
-  const int num_kb = (p.K + BK - 1) / BK;
+  // without SWIGLU, tmA2 / tmB2 are the second operand pair: its k-blocks (zero-filled past K2 by the tensor maps) follow the first pair's
+  const int num_kb1 = (p.K + BK - 1) / BK;
+  const int num_kb = num_kb1 + ((!SWIGLU && p.K2 > 0) ? (p.K2 + BK - 1) / BK : 0);
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kStages; ++i) {
+    for (int i = 0; i < kNS; ++i) {
       mbar_init(&full[i], 1);
       mbar_init(&empty[i], 1);
     }
@@ -146,6 +165,8 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   if (warp == 0 && lane == 0) {
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
+    if (SWIGLU || p.K2 > 0) prefetch_tmap(&tmB2);
+    if (!SWIGLU && p.K2 > 0) prefetch_tmap(&tmA2);
   }
   __syncthreads();
   if (warp == 2) {
@@ -163,9 +184,10 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint32_t phase = 0;
     for (int t = pair; t < num_tiles && !*abort_flag; t += num_pairs) {
       int m_blk, n_blk;
-      tile_coords(t, num_m, num_n, p.group_m, m_blk, n_blk);
+      tile_coords(p.tile_mult == 1 ? t : static_cast<int>((static_cast<long long>(t) * p.tile_mult) % num_tiles), num_m, num_n, p.group_m, m_blk, n_blk);
       const int a_row = m_blk * PM + static_cast<int>(cta) * BM;
-      const int b_row = n_blk * BN + static_cast<int>(cta) * (BN / 2);
+      const int b_row = SWIGLU ? n_blk * (BN / 2) : n_blk * BN + static_cast<int>(cta) * (BN / 2);
+      const CUtensorMap* mapB = (SWIGLU && cta == 1) ? &tmB2 : &tmB;
       for (int kb = 0; kb < num_kb; ++kb) {
         if (!mbar_wait(&empty[stage], phase ^ 1)) {
           *abort_flag = 1;
@@ -177,21 +199,25 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           uint8_t* sb = sa + kABytes;
           if (cta == 0) mbar_arrive_expect_tx(&full[stage], 2 * kStageBytes);  // the bytes of both CTAs' loads
           const uint32_t bar = map_to_cta(&full[stage], 0);
+          const bool second = !SWIGLU && kb >= num_kb1;
+          const CUtensorMap* mA = second ? &tmA2 : &tmA;
+          const CUtensorMap* mB = second ? &tmB2 : mapB;
+          const int k0 = (second ? kb - num_kb1 : kb) * BK;
           if (A_MN) {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sa + j * 8192, &tmA, bar, a_row + j * 64, kb * BK);
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sa + j * 8192, mA, bar, a_row + j * 64, k0);
           } else {
-            tma_load_2d_pair(sa, &tmA, bar, kb * BK, a_row);
+            tma_load_2d_pair(sa, mA, bar, k0, a_row);
           }
           if (B_MN) {
 #pragma unroll
-            for (int j = 0; j < (BN / 2) / 64; ++j) tma_load_2d_pair(sb + j * 8192, &tmB, bar, b_row + j * 64, kb * BK);
+            for (int j = 0; j < (BN / 2) / 64; ++j) tma_load_2d_pair(sb + j * 8192, mB, bar, b_row + j * 64, k0);
           } else {
-            tma_load_2d_pair(sb, &tmB, bar, kb * BK, b_row);
+            tma_load_2d_pair(sb, mB, bar, k0, b_row);
           }
         }
         __syncwarp();
-        if (++stage == kStages) {
+        if (++stage == kNS) {
           stage = 0;
           phase ^= 1;
         }
@@ -231,7 +257,7 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           umma_commit_pair(&empty[stage]);  // both CTAs' producers may refill the stage once these MMAs retire
         }
         __syncwarp();
-        if (++stage == kStages) {
+        if (++stage == kNS) {
           stage = 0;
           phase ^= 1;
         }
@@ -257,7 +283,7 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint8_t* my_stage = epi + quarter * 8192;
     for (int t = pair; t < num_tiles && !*abort_flag; t += num_pairs) {
       int m_blk, n_blk;
-      tile_coords(t, num_m, num_n, p.group_m, m_blk, n_blk);
+      tile_coords(p.tile_mult == 1 ? t : static_cast<int>((static_cast<long long>(t) * p.tile_mult) % num_tiles), num_m, num_n, p.group_m, m_blk, n_blk);
       if (!mbar_wait(&tfull[acc], acc_phase)) {
         *abort_flag = 1;
         if (lane == 0) atomicExch(p.err, 114);
@@ -267,7 +293,58 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int row0 = m_blk * PM + static_cast<int>(cta) * BM + quarter * 32;
       const int row = row0 + lane;
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
-      if (p.tma_store) {
+      if (SWIGLU) {
+        // gate = columns [0, 128), up = columns [128, 256) of this CTA's rows; 64 output columns per staged sub-tile
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          const int col0 = n_blk * (BN / 2) + c * 64;
+          if (col0 >= p.N || row0 >= p.M) break;
+          uint8_t* buf_h = my_stage + (buf_toggle & 1) * 4096;
+          if (lane == 0) tma_store_wait_read<0>();  // the three stores of the previous sub-tile have read their buffers
+          __syncwarp();
+          uint8_t* buf_g = epi_extra + quarter * 8192;
+          uint8_t* buf_u = buf_g + 4096;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t rg[32], ru[32];
+            tmem_ld_32x32(taddr + c * 64 + h * 32, rg);
+            tmem_ld_32x32(taddr + 128 + c * 64 + h * 32, ru);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              float g[8], u[8], o[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                // round the pre-activations to bf16 first: the unfused path computes SwiGLU from the stored bf16 values
+                g[i] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(rg[j * 8 + i])));
+                u[i] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(ru[j * 8 + i])));
+                o[i] = g[i] / (1.f + __expf(-g[i])) * u[i];
+              }
+              const int chunk = (h * 4 + j) ^ (lane & 7);
+              uint4 v;
+              v.x = pack_bf16x2(o[0], o[1]), v.y = pack_bf16x2(o[2], o[3]), v.z = pack_bf16x2(o[4], o[5]), v.w = pack_bf16x2(o[6], o[7]);
+              *reinterpret_cast<uint4*>(buf_h + lane * 128 + chunk * 16) = v;
+              if (p.save_gate_up) {
+                v.x = pack_bf16x2(g[0], g[1]), v.y = pack_bf16x2(g[2], g[3]), v.z = pack_bf16x2(g[4], g[5]), v.w = pack_bf16x2(g[6], g[7]);
+                *reinterpret_cast<uint4*>(buf_g + lane * 128 + chunk * 16) = v;
+                v.x = pack_bf16x2(u[0], u[1]), v.y = pack_bf16x2(u[2], u[3]), v.z = pack_bf16x2(u[4], u[5]), v.w = pack_bf16x2(u[6], u[7]);
+                *reinterpret_cast<uint4*>(buf_u + lane * 128 + chunk * 16) = v;
+              }
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmC, buf_h, col0, row0);
+            if (p.save_gate_up) {
+              tma_store_2d(&tmG, buf_g, col0, row0);
+              tma_store_2d(&tmU, buf_u, col0, row0);
+            }
+            tma_store_commit();
+          }
+          ++buf_toggle;
+        }
+      } else if (p.tma_store) {
 #pragma unroll 1
         for (int c = 0; c < BN / 64; ++c) {
           const int col0 = n_blk * BN + c * 64;
@@ -368,38 +445,94 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   if (warp == 2) tmem_dealloc_pair(tmem_base, 512);
 }
 
-template <bool A_MN, bool B_MN>
-static int launch(const void* A, const void* B, const Params& p, long long lda, long long ldb, cudaStream_t stream) {
-  CUtensorMap tmA, tmB, tmC;
+// TTB_SHUFFLE_TILES=<n> (debug aid, default off): tiles are visited in the order (t · m) mod tiles with m the first odd number ≥ n
+// that is coprime to the tile count.  Results must not depend on the order tiles are computed in; a test that passes with and
+// without the variable shows that no tile reads what another one has not written yet.
+static int shuffle_multiplier(int num_tiles) {
+  static int want = -1;
+  if (want < 0) {
+    const char* e = getenv("TTB_SHUFFLE_TILES");
+    want = (e != nullptr && atoi(e) > 1) ? atoi(e) : 0;
+  }
+  if (want == 0 || num_tiles < 3) return 1;
+  auto gcd = [](int a, int b) {
+    while (b) {
+      const int t = a % b;
+      a = b, b = t;
+    }
+    return a;
+  };
+  int m = (want % num_tiles) | 1;
+  while (gcd(m, num_tiles) != 1) m += 2;
+  return m;
+}
+
+template <bool A_MN, bool B_MN, bool SWIGLU>
+static int launch(const void* A, const void* B, const void* B2, void* G, void* U, const Params& p, long long lda, long long ldb, cudaStream_t stream,
+                  const void* A2 = nullptr, long long lda2 = 0, long long ldb2 = 0) {
+  CUtensorMap tmA, tmB, tmB2, tmC, tmG, tmU, tmA2;
+  memset(&tmA2, 0, sizeof(tmA2));
+  memset(&tmB2, 0, sizeof(tmB2));
+  memset(&tmG, 0, sizeof(tmG));
+  memset(&tmU, 0, sizeof(tmU));
   int rc;
   if (A_MN)
     rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.K, p.M, lda, BK, 64, CU_TENSOR_MAP_SWIZZLE_128B);
   else
     rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.M, p.K, lda, BM, BK, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != kOk) return rc;
-  if (B_MN)
-    rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.K, p.N, ldb, BK, 64, CU_TENSOR_MAP_SWIZZLE_128B);
-  else
-    rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.N, p.K, ldb, BN / 2, BK, CU_TENSOR_MAP_SWIZZLE_128B);
-  if (rc != kOk) return rc;
+  auto map_b = [&](CUtensorMap* m, const void* ptr) {
+    return B_MN ? make_tmap_2d(m, ptr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.K, p.N, ldb, BK, 64, CU_TENSOR_MAP_SWIZZLE_128B)
+                : make_tmap_2d(m, ptr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.N, p.K, ldb, BN / 2, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  };
+  if ((rc = map_b(&tmB, B)) != kOk) return rc;
+  if (SWIGLU && (rc = map_b(&tmB2, B2)) != kOk) return rc;
+  if (!SWIGLU && p.K2 > 0) {  // second operand pair: same layouts as the first, its own pitches and contraction length
+    if (A_MN)
+      rc = make_tmap_2d(&tmA2, A2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.K2, p.M, lda2, BK, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+    else
+      rc = make_tmap_2d(&tmA2, A2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.M, p.K2, lda2, BM, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != kOk) return rc;
+    rc = B_MN ? make_tmap_2d(&tmB2, B2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.K2, p.N, ldb2, BK, 64, CU_TENSOR_MAP_SWIZZLE_128B)
+              : make_tmap_2d(&tmB2, B2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.N, p.K2, ldb2, BN / 2, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != kOk) return rc;
+  }
   Params q = p;
   memset(&tmC, 0, sizeof(tmC));
-  q.tma_store = (!p.accumulate && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0 &&
-                 make_tmap_2d(&tmC, p.C, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.M, p.N, p.ldc, 32, 64, CU_TENSOR_MAP_SWIZZLE_128B) == kOk)
-                    ? 1
-                    : 0;
-  auto kern = gemm2sm_kernel<A_MN, B_MN>;
+  auto map_c = [&](CUtensorMap* m, void* ptr) {
+    return make_tmap_2d(m, ptr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.M, p.N, p.ldc, 32, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+  };
+  if (SWIGLU) {
+    if ((reinterpret_cast<uintptr_t>(p.C) & 15) || map_c(&tmC, p.C) != kOk) return kErrBadShape;
+    q.save_gate_up = (G != nullptr && U != nullptr) ? 1 : 0;
+    if (q.save_gate_up && (map_c(&tmG, G) != kOk || map_c(&tmU, U) != kOk)) return kErrBadShape;
+    q.tma_store = 1;
+  } else {
+    q.tma_store = (!p.accumulate && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0 && map_c(&tmC, p.C) == kOk) ? 1 : 0;
+  }
+  auto kern = gemm2sm_kernel<A_MN, B_MN, SWIGLU>;
+  constexpr int smem = SWIGLU ? kSmemBytesSwiglu : kSmemBytes;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) return kErrDriver;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return kErrDriver;
     attr_set = true;
   }
-  const int num_tiles = ((p.M + PM - 1) / PM) * ((p.N + BN - 1) / BN);
+  const int num_tiles = ((p.M + PM - 1) / PM) * ((p.N + (SWIGLU ? BN / 2 : BN) - 1) / (SWIGLU ? BN / 2 : BN));
+  q.tile_mult = shuffle_multiplier(num_tiles);
   const int max_pairs = sm_count() / 2;
   const int pairs = num_tiles < max_pairs ? num_tiles : max_pairs;
   TTB_COUNT_LAUNCH(1);
-  kern<<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmA, tmB, tmC, q);
+  kern<<<2 * pairs, kThreads, smem, stream>>>(tmA, tmB, tmC, tmB2, tmG, tmU, tmA2, q);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrDriver;
+}
+
+static int group_setting() {
+  static int group_m = 0;
+  if (group_m == 0) {
+    const char* e = getenv("TTB_G2_GROUP_M");
+    group_m = (e != nullptr && atoi(e) > 0) ? atoi(e) : kGroupM;
+  }
+  return group_m;
 }
 
 }  // namespace g2
@@ -415,14 +548,43 @@ extern "C" int ttb_gemm_bf16_2sm(const void* A, const void* B, void* C, int M, i
   if ((a_mn ? (M & 7) : (K & 7)) || (b_mn ? (N & 7) : (K & 7))) return kErrBadShape;
   g2::Params p;
   p.M = M, p.N = N, p.K = K, p.C = C, p.ldc = ldc, p.bias = static_cast<const __nv_bfloat16*>(bias), p.alpha = alpha;
-  p.accumulate = accumulate, p.tma_store = 0, p.err = err;
-  static int group_m = 0;
-  if (group_m == 0) {
-    const char* e = getenv("TTB_G2_GROUP_M");
-    group_m = (e != nullptr && atoi(e) > 0) ? atoi(e) : g2::kGroupM;
-  }
-  p.group_m = group_m;
+  p.accumulate = accumulate, p.tma_store = 0, p.save_gate_up = 0, p.tile_mult = 1, p.err = err, p.K2 = 0;
+  p.group_m = g2::group_setting();
   auto s = static_cast<cudaStream_t>(stream);
-  if (a_mn) return b_mn ? g2::launch<true, true>(A, B, p, lda, ldb, s) : g2::launch<true, false>(A, B, p, lda, ldb, s);
-  return b_mn ? g2::launch<false, true>(A, B, p, lda, ldb, s) : g2::launch<false, false>(A, B, p, lda, ldb, s);
+  if (a_mn) return b_mn ? g2::launch<true, true, false>(A, B, nullptr, nullptr, nullptr, p, lda, ldb, s) : g2::launch<true, false, false>(A, B, nullptr, nullptr, nullptr, p, lda, ldb, s);
+  return b_mn ? g2::launch<false, true, false>(A, B, nullptr, nullptr, nullptr, p, lda, ldb, s) : g2::launch<false, false, false>(A, B, nullptr, nullptr, nullptr, p, lda, ldb, s);
+}
+
+// C[M,N] = alpha · (A·op(B) + A2·op(B2)) (+ bias) on CTA pairs: the second pair's k-blocks (K2 columns, zero-filled up to a multiple of
+// 64 by the tensor maps) extend the main loop, so base and adapter products of a LoRA linear share one accumulator
+// (torchtune/modules/peft/lora.py:128-147).  A and A2 are [M, K] / [M, K2] row-major; b_mn = 0: B [N, K], B2 [N, K2]; 1: B [K, N], B2 [K2, N].
+extern "C" int ttb_gemm_bf16_dual_2sm(const void* A, const void* B, const void* A2, const void* B2, void* C, int M, int N, int K, int K2, int b_mn,
+                                      long long lda, long long ldb, long long lda2, long long ldb2, long long ldc, const void* bias, float alpha,
+                                      int* err, void* stream) {
+  using namespace ttb;
+  if (M <= 0 || N <= 0 || K <= 0 || K2 <= 0 || A2 == nullptr || B2 == nullptr) return kErrBadShape;
+  if ((lda & 7) || (ldb & 7) || (lda2 & 7) || (ldb2 & 7) || (ldc & 7) || (N & 7) || (K & 7) || (K2 & 7)) return kErrBadShape;
+  g2::Params p;
+  p.M = M, p.N = N, p.K = K, p.K2 = K2, p.C = C, p.ldc = ldc, p.bias = static_cast<const __nv_bfloat16*>(bias), p.alpha = alpha;
+  p.accumulate = 0, p.tma_store = 0, p.save_gate_up = 0, p.tile_mult = 1, p.err = err;
+  p.group_m = g2::group_setting();
+  auto s = static_cast<cudaStream_t>(stream);
+  return b_mn ? g2::launch<false, true, false>(A, B, B2, nullptr, nullptr, p, lda, ldb, s, A2, lda2, ldb2)
+              : g2::launch<false, false, false>(A, B, B2, nullptr, nullptr, p, lda, ldb, s, A2, lda2, ldb2);
+}
+
+// Gated MLP up-projection with the activation in the epilogue: H[M, N] = silu(X · W1ᵀ) ⊙ (X · W3ᵀ) with X [M, K], W1 and W3 [N, K]
+// (row pitches lda, ldb; all bf16).  gate_out / up_out (both or neither; [M, N], row pitch ldc) receive the two pre-activations
+// rounded to bf16, which is what the backward pass of the unfused form would have read.
+extern "C" int ttb_gemm_swiglu_bf16_2sm(const void* X, const void* W1, const void* W3, void* H, void* gate_out, void* up_out, int M, int N, int K,
+                                        long long lda, long long ldb, long long ldc, int* err, void* stream) {
+  using namespace ttb;
+  if (M <= 0 || N <= 0 || K <= 0) return kErrBadShape;
+  if ((lda & 7) || (ldb & 7) || (ldc & 7) || (N & 7) || (K & 7)) return kErrBadShape;
+  if ((gate_out == nullptr) != (up_out == nullptr)) return kErrBadShape;
+  g2::Params p;
+  p.M = M, p.N = N, p.K = K, p.C = H, p.ldc = ldc, p.bias = nullptr, p.alpha = 1.f;
+  p.accumulate = 0, p.tma_store = 1, p.save_gate_up = 0, p.tile_mult = 1, p.err = err, p.K2 = 0;
+  p.group_m = g2::group_setting();
+  return g2::launch<false, false, true>(X, W1, W3, gate_out, up_out, p, lda, ldb, static_cast<cudaStream_t>(stream));
 }

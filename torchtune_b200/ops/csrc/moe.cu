@@ -20,7 +20,7 @@ constexpr int kMaxExperts = 256;
 // Pass 0 counts, an exclusive scan turns counts into bases, pass 1 scatters.
 __global__ void __launch_bounds__(kSortThreads)
 moe_route_sort_kernel(const long long* __restrict__ ids, int n, int num_experts, long long* __restrict__ counts,
-                      long long* __restrict__ order) {
+                      long long* __restrict__ order, long long* __restrict__ inverse) {
   __shared__ int base[kMaxExperts];                 // running output position per expert
   __shared__ int warp_cnt[kSortWarps][kMaxExperts]; // per-round, per-warp counts
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -60,6 +60,7 @@ moe_route_sort_kernel(const long long* __restrict__ ids, int n, int num_experts,
       int pos = base[e] + rank_in_warp;
       for (int w = 0; w < warp; ++w) pos += warp_cnt[w][e];
       order[pos] = i;
+      if (inverse != nullptr) inverse[i] = pos;  // position of entry i in expert order (entries with invalid ids keep their old value)
     }
     __syncthreads();
     for (int x = tid; x < num_experts; x += kSortThreads) {
@@ -127,12 +128,13 @@ moe_permute_indices_kernel(const long long* __restrict__ counts, int experts_per
 
 }  // namespace ttb
 
-extern "C" int ttb_moe_route_sort(const void* expert_ids, int n, int num_experts, void* counts, void* order, void* stream) {
+// inverse (optional, [n] int64): inverse[i] = position of entry i in the sorted order.
+extern "C" int ttb_moe_route_sort(const void* expert_ids, int n, int num_experts, void* counts, void* order, void* inverse, void* stream) {
   using namespace ttb;
   if (n < 0 || num_experts <= 0 || num_experts > kMaxExperts) return kErrBadShape;
   TTB_COUNT_LAUNCH(1);
   moe_route_sort_kernel<<<1, kSortThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const long long*>(expert_ids), n, num_experts, static_cast<long long*>(counts), static_cast<long long*>(order));
+      static_cast<const long long*>(expert_ids), n, num_experts, static_cast<long long*>(counts), static_cast<long long*>(order), static_cast<long long*>(inverse));
   return cudaGetLastError() == cudaSuccess ? kOk : kErrDriver;
 }
 

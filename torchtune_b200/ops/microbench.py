@@ -4,6 +4,7 @@
     python -m torchtune_b200.ops.microbench attention --batch 4 --seq 2048 --doc 512
     python -m torchtune_b200.ops.microbench rmsnorm --rows 8192 --dim 4096
     python -m torchtune_b200.ops.microbench adamw --numel 268435456
+    python -m torchtune_b200.ops.microbench gate_up --tokens 8192 --dim 4096 --hidden 14336
     python -m torchtune_b200.ops.microbench suite --tokens 8192      (norm, RoPE, SwiGLU, loss, embedding, LoRA, grouped GEMM, NF4, offload copies)
 
 Each command prints one JSON line: median milliseconds over ``--iters`` launches (an L2 flush
@@ -154,6 +155,34 @@ def bench_adamw(args, flush):
     t = _time(run, args.iters, args.warmup, flush)
     nbytes = n * (2 + 2 + 2 + 4 * 2)  # p r/w, g r, m and v r/w (all bf16)
     return {"op": "adamw", "numel": n, "ms": t, "gbs": nbytes / t / 1e6}
+
+
+def bench_gate_up(args, flush):
+    """Gate / up projections + SwiGLU of one MLP: the fused CTA-pair kernel against two GEMMs followed by the SwiGLU kernel,
+    without (inference / first checkpointed forward) and with (recomputed forward) the pre-activations kept for backward."""
+    from . import _cuda
+
+    T, D, H = args.tokens, args.dim, args.hidden
+    x = torch.randn(T, D, device="cuda", dtype=torch.bfloat16) * 0.5
+    w1 = torch.randn(H, D, device="cuda", dtype=torch.bfloat16) * 0.02
+    w3 = torch.randn(H, D, device="cuda", dtype=torch.bfloat16) * 0.02
+    flops = 2 * 2.0 * T * D * H
+    out = {"op": "gate_up", "tokens": T, "dim": D, "hidden": H}
+
+    def unfused():
+        return _cuda.swiglu(_cuda.gemm(x, w1), _cuda.gemm(x, w3))
+
+    with torch.no_grad():
+        t = _time(lambda: _cuda.gate_up_swiglu(x, w1, w3), args.iters, args.warmup, flush)
+        out["fused_nograd_ms"], out["fused_nograd_tflops"] = t, flops / t / 1e9
+        t = _time(unfused, args.iters, args.warmup, flush)
+        out["unfused_nograd_ms"], out["unfused_nograd_tflops"] = t, flops / t / 1e9
+    xg, w1g, w3g = x.clone().requires_grad_(), w1.clone().requires_grad_(), w3.clone().requires_grad_()
+    t = _time(lambda: _cuda.gate_up_swiglu(xg, w1g, w3g), args.iters, args.warmup, flush)
+    out["fused_grad_ms"], out["fused_grad_tflops"] = t, flops / t / 1e9
+    t = _time(lambda: _cuda.swiglu(_cuda.linear(xg, w1g, None), _cuda.linear(xg, w3g, None)), args.iters, args.warmup, flush)
+    out["unfused_grad_ms"], out["unfused_grad_tflops"] = t, flops / t / 1e9
+    return out
 
 
 def bench_suite(args, flush):
@@ -323,13 +352,17 @@ def main() -> None:
     r.add_argument("--dim", type=int, default=4096)
     o = sub.add_parser("adamw")
     o.add_argument("--numel", type=int, default=1 << 28)
+    gu = sub.add_parser("gate_up")
+    gu.add_argument("--tokens", type=int, default=8192)
+    gu.add_argument("--dim", type=int, default=4096)
+    gu.add_argument("--hidden", type=int, default=14336)
     su = sub.add_parser("suite")
     su.add_argument("--tokens", type=int, default=8192)
     args = ap.parse_args()
     from ._lib import check_device_errors
 
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
-    fn = {"gemm": bench_gemm, "gemm_fp8": bench_gemm_fp8, "attention": bench_attention, "rmsnorm": bench_rmsnorm, "adamw": bench_adamw, "suite": bench_suite}[args.op]
+    fn = {"gemm": bench_gemm, "gemm_fp8": bench_gemm_fp8, "attention": bench_attention, "rmsnorm": bench_rmsnorm, "adamw": bench_adamw, "gate_up": bench_gate_up, "suite": bench_suite}[args.op]
     res = fn(args, flush)
     check_device_errors()
     print(json.dumps(res), flush=True)

@@ -171,7 +171,7 @@ def run_ours(args) -> dict:
             if p.dim() > 1 and p.is_floating_point() and not p.is_meta:
                 torch.nn.init.normal_(p, std=0.02)
     if args.fp8:  # optional variant, never the default: decoder linears (not the output head) on the fp8 tensor cores
-        training.convert_to_float8_training(model, "tensorwise")
+        training.convert_to_float8_training(model, args.fp8_recipe)
     training.set_activation_checkpointing(model, {TransformerSelfAttentionLayer})
     loss_fn = LinearCrossEntropyLoss(num_output_chunks=8)
     loss_fn.set_model_output(model)
@@ -241,7 +241,8 @@ def run_ours(args) -> dict:
         "higher_is_better": True,
         "scaling": "weak",
         "vs_baseline": (value / BASELINE_TOKENS_PER_S) if BASELINE_TOKENS_PER_S else None,
-        "dtype": "fp8 linears (e4m3 / e5m2 operands, dynamic tensorwise scales), bf16 elsewhere" if args.fp8 else "bf16",
+        "dtype": ("fp8 linears (e4m3 values, one power-of-two scale per 32 values along each contraction, applied in the tensor core), bf16 elsewhere" if args.fp8_recipe == "blockwise"
+                  else "fp8 linears (e4m3 / e5m2 operands, dynamic tensorwise scales), bf16 elsewhere") if args.fp8 else "bf16",
         "data": "synthetic uniform tokens, random-init weights",
         "impl": "ours",
         "config": {
@@ -601,6 +602,7 @@ def main() -> None:
     ap.add_argument("--config", choices=["8b"] + sorted(SHARDED_CONFIGS), default="8b", help="8b: the headline (Llama-3.1-8B); the others are the 70B tensor-parallel and Scout expert-parallel configurations")
     ap.add_argument("--debug-layers", type=int, default=0, help="functional check of a --config on few GPUs: build only this many layers (the printed line is marked invalid)")
     ap.add_argument("--ref-compile", action="store_true", help="with --impl reference: the reference's `compile: True` path (informational; the default arm stays on the stock eager path)")
+    ap.add_argument("--fp8-recipe", choices=["tensorwise", "blockwise"], default="tensorwise", help="with --fp8: one scale per tensor, or MX block scales (32 values per scale)")
     ap.add_argument("--fp8", action="store_true", help="variant: fp8 decoder linears (the headline number is always bf16)")
     args = ap.parse_args()
     rank, world, _ = dist_env()

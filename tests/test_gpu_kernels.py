@@ -958,3 +958,53 @@ def test_moe_gather_and_combine_row_kernels():
     _close(x.grad, xr.grad, 3e-2, 5e-2, "dx")
     _close(base.grad, br.grad, 1e-2, 1e-2, "dbase")
     _close(scores.grad, sr.grad, 5e-2, 0.3, "dscores")
+
+
+# ----------------------------------------------------------------------------- block-scaled (MX) fp8
+@pytest.mark.parametrize("R,C,transpose", [(256, 512, False), (130, 96, False), (8, 4096, False), (256, 512, True), (160, 200, True), (4096, 24, True)])
+def test_mx_quantize_matches_oracle(R, C, transpose):
+    from torchtune_b200.ops._cuda import mx_quantize, mx_unpack_scales
+
+    x = _rand(R, C, seed=3, scale=2.0)
+    x[0, :] = 0  # all-zero blocks
+    x[1, 5] = 300.0  # an outlier that only its own block pays for
+    q, sf = mx_quantize(x, transpose=transpose)
+    want_q, want_e = ref.mx_quantize(x, transpose=transpose)
+    rows, k = want_q.shape
+    assert q.shape == (rows, k)
+    assert torch.equal(mx_unpack_scales(sf, rows, k), want_e)
+    assert torch.equal(q.view(torch.float8_e4m3fn).float(), want_q)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (256, 512, 4096), (520, 264, 160), (8192, 4096, 1024), (96, 40, 32)])
+def test_gemm_mxfp8_matches_dequantized_matmul(M, N, K):
+    from torchtune_b200.ops._cuda import gemm_mxfp8, mx_quantize
+    from torchtune_b200.ops._lib import check_device_errors
+
+    a, b = _rand(M, K, seed=1, scale=1.5), _rand(N, K, seed=2, scale=0.1)
+    a[:, : K // 2] *= 40.0  # very different magnitudes between blocks: a wrong scale id or row mapping shows up at once
+    bias = _rand(N, seed=3, scale=0.5)
+    aq, asf = mx_quantize(a)
+    bq, bsf = mx_quantize(b)
+    got = gemm_mxfp8(aq, asf, bq, bsf, bias=bias)
+    check_device_errors()
+    want = ref.mx_roundtrip(a) @ ref.mx_roundtrip(b).t() + bias.float()
+    _close(got, want, 1e-2, 1e-2 * want.abs().max().item(), "gemm_mxfp8")
+    again = gemm_mxfp8(aq, asf, bq, bsf, out=got.clone(), accumulate=True)
+    _close(again, 2 * want - bias.float(), 2e-2, 2e-2 * want.abs().max().item(), "gemm_mxfp8 accumulate")
+
+
+def test_mxfp8_linear_autograd_close_to_bf16():
+    x = _rand(4, 64, 512, seed=8).requires_grad_()
+    w = _rand(768, 512, seed=9, scale=0.05).requires_grad_()
+    bias = _rand(768, seed=10).requires_grad_()
+    y = ops.mxfp8_linear(x, w, bias)
+    assert y is not None
+    gy = _rand(4, 64, 768, seed=11)
+    y.backward(gy)
+    xr, wr, br = (t.detach().float().requires_grad_() for t in (x, w, bias))
+    yr = torch.nn.functional.linear(xr, wr, br)
+    yr.backward(gy.float())
+    for name, got, want in (("y", y, yr), ("dx", x.grad, xr.grad), ("dw", w.grad, wr.grad), ("db", bias.grad, br.grad)):
+        rel = (got.float() - want).norm() / want.norm()
+        assert rel < 0.06, (name, rel.item())  # e4m3 has 3 mantissa bits: about 3 % relative error per operand

@@ -12,6 +12,9 @@ gradients are divided by the all-reduced token count inside the optimizer update
 """
 from __future__ import annotations
 
+import gc
+import os
+import weakref
 from typing import Any, Dict, Optional
 
 import torch
@@ -19,6 +22,41 @@ from torch import nn
 
 from ..ops.mask import AttentionMask
 from ..utils import batch_to_device
+
+
+class HostGarbageControl:
+    """Keeps the cyclic garbage collector from pausing the host in the middle of a step.  Python's generational collector starts
+    whenever allocation counts cross a threshold; a full collection with a model's worth of live objects can hold the launching
+    thread for long enough that the device queue runs dry.  Training state is not cyclic garbage, so automatic collection is
+    switched off and a generation-1 collection runs every ``period`` steps at a step boundary instead.  ``TTB_HOST_GC=auto``
+    leaves Python's own schedule in place."""
+
+    def __init__(self, active: bool = True, period: int = 50):
+        self.period = period
+        self.enabled = active and os.environ.get("TTB_HOST_GC", "manual") != "auto" and gc.isenabled()
+        self._count = 0
+        if self.enabled:
+            gc.collect()
+            gc.freeze()  # what is alive now (model, optimizer, data) is never scanned again
+            gc.disable()
+            weakref.finalize(self, HostGarbageControl._restore)
+
+    @staticmethod
+    def _restore() -> None:
+        gc.enable()
+        gc.unfreeze()
+
+    def step(self) -> None:
+        if not self.enabled:
+            return
+        self._count += 1
+        if self._count % self.period == 0:
+            gc.collect(1)
+
+    def close(self) -> None:
+        if self.enabled:
+            self._restore()
+            self.enabled = False
 
 
 class TrainStep:
@@ -33,8 +71,10 @@ class TrainStep:
         self.max_steps_in_flight = 2
         self._in_flight: list = []
         self.trace_events = None  # set to a list to collect one CUDA event per phase boundary of every step
+        self.host_gc = HostGarbageControl(active=device.type == "cuda")  # CPU runs (tests) keep Python's own schedule
 
     def _step_done(self) -> None:
+        self.host_gc.step()
         if self.device.type == "cuda":
             ev = torch.cuda.Event()
             ev.record()

@@ -26,6 +26,7 @@ __all__ = [
     "lora_linear",
     "lora_linear_nf4",
     "fp8_linear",
+    "mxfp8_linear",
     "matmul",
     "linear",
     "rms_norm",
@@ -115,6 +116,19 @@ def fp8_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tenso
     from . import _cuda
 
     return _cuda.fp8_linear(x, weight, bias, rowwise)
+
+
+def mxfp8_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """Block-scaled (MX: e4m3 values, one power-of-two scale per 32 values along each contraction) fp8 tensor-core linear; ``None``
+    when the inputs do not qualify (not bf16 CUDA, or tokens / in / out features not multiples of 32)."""
+    if not (_native(x) and weight.dtype == torch.bfloat16 and weight.is_contiguous()):
+        return None
+    tokens = x.numel() // x.shape[-1]
+    if x.shape[-1] % 32 or weight.shape[0] % 32 or tokens % 32 or tokens == 0:
+        return None
+    from . import _cuda
+
+    return _cuda.mxfp8_linear(x, weight, bias)
 
 
 def lora_linear(x: torch.Tensor, xd: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], lora_a: torch.Tensor, lora_b: torch.Tensor, scale: float) -> torch.Tensor:

@@ -711,6 +711,89 @@ def fp8_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tenso
     return _Fp8Linear.apply(x, weight, bias, rowwise)
 
 
+# ======================================================================= block-scaled (MX) fp8 linear
+def mx_quantize(x2: torch.Tensor, transpose: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """e4m3 values (uint8 storage) and the packed scale buffer of a bf16 ``[R, C]`` operand, blocks of 32 along ``C``; with
+    ``transpose`` the operand is ``x2.T`` (``[C, R]``, blocks along ``R``).  Scale buffer layout: gemm_mxfp8.cu."""
+    assert x2.dim() == 2 and x2.dtype == _BF16 and x2.stride(1) == 1
+    R, C = x2.shape
+    rows, k = (C, R) if transpose else (R, C)
+    q = torch.empty(rows, k, dtype=torch.uint8, device=x2.device)
+    sf = torch.zeros(lib().ttb_mx_scale_bytes(rows, k), dtype=torch.uint8, device=x2.device)
+    check(lib().ttb_mx_quantize(x2.data_ptr(), x2.stride(0), q.data_ptr(), q.stride(0), sf.data_ptr(), R, C, int(transpose), stream_ptr()), f"mx_quantize {R}x{C} transpose={transpose}")
+    return q, sf
+
+
+def mx_unpack_scales(sf: torch.Tensor, rows: int, k: int) -> torch.Tensor:
+    """``[rows, k / 32]`` exponent bytes read back from the packed scale buffer (tests and debugging)."""
+    r = torch.arange(rows, device=sf.device).unsqueeze(1)
+    b = torch.arange(k // 32, device=sf.device).unsqueeze(0)
+    chunks_per_row = (k + 127) // 128
+    off = ((r >> 7) * chunks_per_row + (b >> 2)) * 512 + (r & 31) * 16 + ((r & 127) >> 5) * 4 + (b & 3)
+    return sf[off]
+
+
+def gemm_mxfp8(aq: torch.Tensor, asf: torch.Tensor, bq: torch.Tensor, bsf: torch.Tensor, *, bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+               accumulate: bool = False) -> torch.Tensor:
+    """``aq[M, K] · bq[N, K]ᵀ`` with per-32 block scales applied by the tensor core (+ bias) → bf16 ``[M, N]``."""
+    M, K = aq.shape
+    N = bq.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=_BF16, device=aq.device)
+    check(lib().ttb_gemm_mxfp8(aq.data_ptr(), bq.data_ptr(), asf.data_ptr(), bsf.data_ptr(), out.data_ptr(), M, N, K, aq.stride(0), bq.stride(0), out.stride(0), _ptr(bias),
+                               int(accumulate), err_word(aq.device).data_ptr(), stream_ptr()), f"gemm_mxfp8 M={M} N={N} K={K}")
+    return out
+
+
+class _MXFp8Linear(torch.autograd.Function):
+    """``x @ Wᵀ (+ bias)`` with forward, input-gradient and weight-gradient products on the block-scaled fp8 tensor-core path.  Every
+    operand is quantised along its own contraction dimension (six quantisations per layer and step); only fp8 copies and their
+    scales are kept for backward."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        K, N = x.shape[-1], weight.shape[0]
+        x2 = x.reshape(-1, K)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        xq, xs = mx_quantize(x2)
+        wq, ws = mx_quantize(weight)
+        y = gemm_mxfp8(xq, xs, wq, ws, bias=bias)
+        need_dw, need_dx = weight.requires_grad, x.requires_grad
+        xt = mx_quantize(x2, transpose=True) if need_dw else (None, None)  # [K, T], blocks along tokens
+        wt = mx_quantize(weight, transpose=True) if need_dx else (None, None)  # [K, N], blocks along N
+        ctx.has_bias = bias is not None
+        ctx.save_for_backward(xt[0], xt[1], wt[0], wt[1], weight)
+        return y.view(*x.shape[:-1], N)
+
+    @staticmethod
+    def backward(ctx, dy):
+        xtq, xts, wtq, wts, weight = ctx.saved_tensors
+        N = dy.shape[-1]
+        dy2 = dy.reshape(-1, N)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = dw = db = None
+        if wtq is not None:
+            dyq, dys = mx_quantize(dy2)  # blocks along N
+            dx = gemm_mxfp8(dyq, dys, wtq, wts).view(*dy.shape[:-1], wtq.shape[0])
+        if xtq is not None:
+            dytq, dyts = mx_quantize(dy2, transpose=True)  # [N, T], blocks along tokens
+            owner = grad_window_owner(weight)
+            if owner is None:
+                dw = gemm_mxfp8(dytq, dyts, xtq, xts)
+            else:
+                gemm_mxfp8(dytq, dyts, xtq, xts, out=owner._grad_buffer, accumulate=bool(owner._grad_written))
+                owner._grad_written = True
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.sum(0)
+        return dx, dw, db
+
+
+def mxfp8_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    return _MXFp8Linear.apply(x, weight, bias)
+
+
 # ======================================================================= RMSNorm
 class _RMSNorm(torch.autograd.Function):
     @staticmethod

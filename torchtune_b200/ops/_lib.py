@@ -80,6 +80,12 @@ def _declare(L: ctypes.CDLL) -> None:
     L.ttb_gemm_fp8.argtypes = [vp, vp, vp, i32, i32, i32, i64, i64, i64, i32, i32, vp, i32, vp, i32, vp, i32, vp, vp]
     L.ttb_fp8_cast_transpose.argtypes = [vp, i64, i32, i32, vp, i32, vp, vp, i32, vp, i32, vp]
     L.ttb_gemm_fp8.restype = i32
+    L.ttb_mx_scale_bytes.argtypes = [i64, i64]
+    L.ttb_mx_scale_bytes.restype = i64
+    L.ttb_mx_quantize.argtypes = [vp, i64, vp, i64, vp, i64, i64, i32, vp]
+    L.ttb_mx_quantize.restype = i32
+    L.ttb_gemm_mxfp8.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, vp, i32, vp, vp]
+    L.ttb_gemm_mxfp8.restype = i32
     L.ttb_fp8_cast_transpose.restype = i32
     for fn in (L.ttb_moe_route_sort, L.ttb_moe_permute_indices, L.ttb_embedding_fwd, L.ttb_embedding_bwd):
         fn.restype = i32

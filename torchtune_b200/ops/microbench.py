@@ -87,6 +87,27 @@ def bench_gemm_fp8(args, flush):
             "cast_gbs": (m * k * 4) / t_cast / 1e6, "fp8_linear_fwd_ms": t_lin, "bf16_gemm_ms": t_bf16, "bf16_tflops": flops / t_bf16 / 1e9}
 
 
+def bench_gemm_mxfp8(args, flush):
+    """Block-scaled fp8 GEMM alone, its two quantisers, and the whole linear forward (2 quantisations + GEMM) against the bf16 GEMM."""
+    from ._cuda import gemm, gemm_mxfp8, mx_quantize, mxfp8_linear
+
+    m, n, k = args.m, args.n, args.k
+    bf = dict(device="cuda", dtype=torch.bfloat16)
+    a, b = torch.randn(m, k, **bf), torch.randn(n, k, **bf) * 0.05
+    aq, asf = mx_quantize(a)
+    bq, bsf = mx_quantize(b)
+    out = torch.empty(m, n, **bf)
+    flops = 2.0 * m * n * k
+    t = _time(lambda: gemm_mxfp8(aq, asf, bq, bsf, out=out), args.iters, args.warmup, flush)
+    t_q = _time(lambda: mx_quantize(a), args.iters, args.warmup, flush)
+    t_qt = _time(lambda: mx_quantize(a, transpose=True), args.iters, args.warmup, flush)
+    with torch.no_grad():
+        t_lin = _time(lambda: mxfp8_linear(a, b, None), args.iters, args.warmup, flush)
+    t_bf16 = _time(lambda: gemm(a, b, out=out), args.iters, args.warmup, flush)
+    return {"op": "gemm_mxfp8_nt", "m": m, "n": n, "k": k, "ms": t, "tflops": flops / t / 1e9, "quantize_ms": t_q, "quantize_gbs": (m * k * 3) / t_q / 1e6,
+            "quantize_transposed_ms": t_qt, "mxfp8_linear_fwd_ms": t_lin, "bf16_gemm_ms": t_bf16, "bf16_tflops": flops / t_bf16 / 1e9}
+
+
 def bench_attention(args, flush):
     from . import attention
     from .mask import AttentionMask
@@ -340,6 +361,10 @@ def main() -> None:
     f.add_argument("--m", type=int, default=8192)
     f.add_argument("--n", type=int, default=4096)
     f.add_argument("--k", type=int, default=4096)
+    fm = sub.add_parser("gemm_mxfp8")
+    fm.add_argument("--m", type=int, default=8192)
+    fm.add_argument("--n", type=int, default=4096)
+    fm.add_argument("--k", type=int, default=4096)
     a = sub.add_parser("attention")
     a.add_argument("--batch", type=int, default=4)
     a.add_argument("--seq", type=int, default=2048)
@@ -362,7 +387,7 @@ def main() -> None:
     from ._lib import check_device_errors
 
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
-    fn = {"gemm": bench_gemm, "gemm_fp8": bench_gemm_fp8, "attention": bench_attention, "rmsnorm": bench_rmsnorm, "adamw": bench_adamw, "gate_up": bench_gate_up, "suite": bench_suite}[args.op]
+    fn = {"gemm": bench_gemm, "gemm_fp8": bench_gemm_fp8, "gemm_mxfp8": bench_gemm_mxfp8, "attention": bench_attention, "rmsnorm": bench_rmsnorm, "adamw": bench_adamw, "gate_up": bench_gate_up, "suite": bench_suite}[args.op]
     res = fn(args, flush)
     check_device_errors()
     print(json.dumps(res), flush=True)

@@ -263,3 +263,42 @@ def nf4_dequantize(
     scales = (scaler_q.float().view(-1, scaler_block_size) / scaler_factor.view(-1, 1)).view(-1) + scaler_mean
     w = code[idx].view(-1, block_size) * scales.unsqueeze(1)
     return w.view(shape).to(dtype)
+
+
+# ----------------------------------------------------------------------------- MX (block-scaled) fp8
+MX_BLOCK = 32
+
+
+def mx_quantize(x: torch.Tensor, transpose: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """OCP MX quantisation of a 2-D tensor to e4m3 with one power-of-two scale per 32 values of the last dimension
+    (of ``x.T`` when ``transpose``).  Returns ``(q, e)``: ``q`` fp32 values on the e4m3 grid (same shape as the operand) and
+    ``e`` the biased scale exponents (uint8, ``[rows, k / 32]``); the operand is ``q * 2^(e - 127)`` blockwise.
+    Scale rule: ``2^(floor(log2 amax) - 8)``; quotients round to nearest even and saturate at +-448; an all-zero block gets
+    exponent byte 0."""
+    v = x.detach().float()
+    if transpose:
+        v = v.t()
+    rows, k = v.shape
+    if k % MX_BLOCK:
+        raise ValueError(f"the blocked dimension ({k}) must be a multiple of {MX_BLOCK}")
+    blocks = v.reshape(rows, k // MX_BLOCK, MX_BLOCK)
+    amax = blocks.abs().amax(-1)
+    _, ex = torch.frexp(amax)  # amax = m * 2^ex with m in [0.5, 1)  =>  floor(log2 amax) = ex - 1
+    e = (ex - 1 - 8).clamp(-127, 127)
+    scale = torch.ldexp(torch.ones_like(amax), e)
+    q = (blocks / scale.unsqueeze(-1)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).float()
+    nz = (amax > 0).unsqueeze(-1)
+    q = torch.where(nz, q, torch.zeros_like(q))
+    e_byte = torch.where(amax > 0, e + 127, torch.zeros_like(e)).to(torch.uint8)
+    return q.reshape(rows, k), e_byte
+
+
+def mx_dequantize(q: torch.Tensor, e_byte: torch.Tensor) -> torch.Tensor:
+    rows, k = q.shape
+    scale = torch.ldexp(torch.ones(e_byte.shape, dtype=torch.float32, device=q.device), e_byte.to(torch.int32) - 127)
+    return (q.reshape(rows, k // MX_BLOCK, MX_BLOCK) * scale.unsqueeze(-1)).reshape(rows, k)
+
+
+def mx_roundtrip(x: torch.Tensor, transpose: bool = False) -> torch.Tensor:
+    """Quantise and dequantise (fp32 result, shape of the operand)."""
+    return mx_dequantize(*mx_quantize(x, transpose))

@@ -290,7 +290,9 @@ def is_fp8_tensorwise_scaling(fp8_recipe_name: Optional[str]) -> bool:
 
 
 class Float8Linear(nn.Linear):
-    """Linear with dynamically scaled fp8 operands (one scale per tensor, or per row with the ``rowwise`` recipe).
+    """Linear with dynamically scaled fp8 operands: one scale per tensor (``tensorwise``), per row (``rowwise``), or per block of 32
+    values along each contraction dimension (``blockwise``: the MX format, scales applied inside the tensor core by
+    ``tcgen05.mma.kind::mxf8f6f4.block_scale``).
 
     bf16 CUDA inputs run on the fp8 tensor cores (``ops.fp8_linear``: cast+transpose kernel, tcgen05 ``kind::f8f6f4`` GEMM for
     forward, input gradient and weight gradient; e5m2 output gradients with tensorwise scaling).  Elsewhere the forward
@@ -301,6 +303,18 @@ class Float8Linear(nn.Linear):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         from .. import ops
 
+        if self.recipe == "blockwise":
+            y = ops.mxfp8_linear(x, self.weight, self.bias)
+            if y is not None:
+                return y
+            from ..ops import reference
+
+            if x.shape[-1] % reference.MX_BLOCK:
+                return ops.linear(x, self.weight, self.bias)
+            x2 = x.reshape(-1, x.shape[-1])
+            xq = x + (reference.mx_roundtrip(x2).view_as(x).to(x.dtype) - x).detach()
+            wq = self.weight + (reference.mx_roundtrip(self.weight).to(self.weight.dtype) - self.weight).detach()
+            return ops.linear(xq, wq, self.bias)
         y = ops.fp8_linear(x, self.weight, self.bias, rowwise=self.recipe != "tensorwise")
         if y is not None:
             return y
@@ -324,11 +338,14 @@ def convert_to_float8_training(model: nn.Module, fp8_recipe_name: Optional[str] 
     """Swap every linear layer except the final vocabulary projection (and layers whose
     dimensions are not multiples of 16) for :class:`Float8Linear`."""
     recipe = fp8_recipe_name or "tensorwise"
-    if recipe not in ("tensorwise", "rowwise", "rowwise_with_gw_hp"):
+    if recipe in ("mxfp8", "mx"):
+        recipe = "blockwise"
+    if recipe not in ("tensorwise", "rowwise", "rowwise_with_gw_hp", "blockwise"):
         raise ValueError(f"unknown fp8 recipe {recipe!r}")
 
     def eligible(m: nn.Module, fqn: str) -> bool:
-        return _is_plain_linear(m) and fqn != "output" and not fqn.endswith(".output") and m.in_features % 16 == 0 and m.out_features % 16 == 0
+        mult = 32 if recipe == "blockwise" else 16
+        return _is_plain_linear(m) and fqn != "output" and not fqn.endswith(".output") and m.in_features % mult == 0 and m.out_features % mult == 0
 
     def make(lin: nn.Linear) -> Float8Linear:
         with torch.device("meta"):
@@ -336,7 +353,7 @@ def convert_to_float8_training(model: nn.Module, fp8_recipe_name: Optional[str] 
         new.weight = lin.weight
         if lin.bias is not None:
             new.bias = lin.bias
-        new.recipe = "tensorwise" if recipe == "tensorwise" else "rowwise"
+        new.recipe = recipe if recipe in ("tensorwise", "blockwise") else "rowwise"
         return new
 
     return _swap(model, eligible, make)

@@ -11,6 +11,9 @@ if str(ROOT) not in sys.path:
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200)")
+    # On a GPU box a bf16 CUDA operator that would leave the sm_100a kernels for a PyTorch statement raises instead of falling back,
+    # so a test cannot pass on a silent fallback (TTB_STRICT=0 in the environment switches this off).
+    os.environ.setdefault("TTB_STRICT", "1")
 
 
 def pytest_collection_modifyitems(config, items):

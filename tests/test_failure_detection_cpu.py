@@ -85,6 +85,30 @@ def test_unfinished_checkpoint_directory_is_never_resumed_from(tmp_path):
     assert sorted(p.name for p in get_all_checkpoints_in_dir(tmp_path)) == ["step_2", "step_6"]
 
 
+def test_stale_partial_directory_and_markers_of_a_dead_attempt_are_discarded(tmp_path):
+    """A job that died in mid-save leaves ``step_4.partial`` with the rank files and ``.done`` markers of that attempt.  The next
+    process clears it before its first save, and its own markers carry a per-save nonce, so the old ones could never stand in
+    for a rank that has not written yet."""
+    from torchtune_b200.training.checkpointing._sharded import DistributedCheckpointer
+
+    out = tmp_path / "out"
+    stale = out / "step_4.partial"
+    stale.mkdir(parents=True)
+    (stale / "rank_0.pt").write_bytes(b"torn")
+    (stale / "rank_0.done").write_text("ok")
+    (stale / "rank_1.done").write_text("ok")
+    nested = out / "epoch_0" / "adapter_model.partial"
+    nested.mkdir(parents=True)
+    (nested / "rank_0.done").write_text("ok")
+    ckpt = DistributedCheckpointer(str(tmp_path), str(out))
+    ckpt.save_checkpoint({"w": torch.arange(4.0)}, epoch=0, step=4, dir_prefix="step")
+    ckpt.wait()
+    assert not stale.exists() and not nested.exists()
+    done = out / "step_4"
+    assert sorted(p.name for p in done.iterdir()) == ["metadata.json", "rank_0.pt"]  # no marker survives the publish
+    assert torch.equal(torch.load(done / "rank_0.pt")["w"], torch.arange(4.0))
+
+
 def test_sharded_checkpoint_of_another_world_size_is_refused(tmp_path):
     from torchtune_b200.training.checkpointing._sharded import DistributedCheckpointer
 

@@ -1008,3 +1008,33 @@ def test_mxfp8_linear_autograd_close_to_bf16():
     for name, got, want in (("y", y, yr), ("dx", x.grad, xr.grad), ("dw", w.grad, wr.grad), ("db", bias.grad, br.grad)):
         rel = (got.float() - want).norm() / want.norm()
         assert rel < 0.06, (name, rel.item())  # e4m3 has 3 mantissa bits: about 3 % relative error per operand
+
+
+def test_mxfp8_linear_shares_the_quantised_activation_between_projections():
+    from torchtune_b200.ops import _cuda
+
+    x = _rand(256, 512, seed=21)
+    w1, w2 = _rand(384, 512, seed=22, scale=0.05), _rand(640, 512, seed=23, scale=0.05)
+    _cuda.mx_clear_shared()
+    y1 = ops.mxfp8_linear(x, w1)
+    hit = _cuda._MX_LAST[False][2]
+    y2 = ops.mxfp8_linear(x, w2)  # same activation, other weight: served from the shared entry
+    assert _cuda._MX_LAST[False][2] is hit
+    _cuda.mx_clear_shared()
+    assert torch.equal(y2, ops.mxfp8_linear(x, w2)) and torch.equal(y1, ops.mxfp8_linear(x, w1))
+    x.add_(1.0)  # an in-place change must not be served from the entry
+    y3 = ops.mxfp8_linear(x, w2)
+    _cuda.mx_clear_shared()
+    assert torch.equal(y3, ops.mxfp8_linear(x, w2))
+
+
+@pytest.mark.parametrize("R,C", [(256, 512), (96, 32), (8192, 1024)])
+def test_mx_quantize_both_matches_the_two_single_passes(R, C):
+    from torchtune_b200.ops._cuda import mx_quantize, mx_quantize_both
+
+    x = _rand(R, C, seed=31, scale=3.0)
+    x[5, :] = 0
+    (q, sf), (qt, sft) = mx_quantize_both(x)
+    q1, sf1 = mx_quantize(x)
+    qt1, sft1 = mx_quantize(x, transpose=True)
+    assert torch.equal(q, q1) and torch.equal(sf, sf1) and torch.equal(qt, qt1) and torch.equal(sft, sft1)

@@ -76,7 +76,8 @@ def test_vision_encoder_bf16_matches_fp32():
     from torchtune_b200.models.clip import clip_vision_encoder
 
     torch.manual_seed(0)
-    enc = clip_vision_encoder(tile_size=56, patch_size=14, embed_dim=128, num_layers=2, num_heads=4, max_num_tiles=4).cuda()
+    # head dim 64 (2 heads of a 128-wide encoder) keeps the attention on the sm_100a kernel, as the CLIP presets' 64 / 80-wide heads do not all do
+    enc = clip_vision_encoder(tile_size=56, patch_size=14, embed_dim=128, num_layers=2, num_heads=2, max_num_tiles=4).cuda()
     images = torch.randn(2, 1, 4, 3, 56, 56, device="cuda")
     ar = torch.tensor([[[2, 2]], [[1, 3]]], device="cuda")
     with ops.use_reference_ops():

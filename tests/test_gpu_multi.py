@@ -12,7 +12,8 @@ ROOT = Path(__file__).resolve().parent.parent
 
 
 def _torchrun(script: str, nproc: int, port: int, timeout: int = 600):
-    env = dict(os.environ, PYTHONPATH=f"{ROOT}:{ROOT / 'tests'}", MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0")
+    # the tiny checkpoints have head dims the attention kernel does not cover (16, 32), so the children may take PyTorch statements
+    env = dict(os.environ, PYTHONPATH=f"{ROOT}:{ROOT / 'tests'}", MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0", TTB_STRICT="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1", "--master-port", str(port), script]
     res = subprocess.run(cmd, cwd=str(ROOT), env=env, capture_output=True, text=True, timeout=timeout)
     assert res.returncode == 0, res.stdout[-4000:] + res.stderr[-4000:]
@@ -47,7 +48,8 @@ def _tiny_ckpt(tmp_path):
 
 
 def _tune(args, port, timeout=600, nproc=2):
-    env = dict(os.environ, PYTHONPATH=f"{ROOT}:{ROOT / 'tests'}", MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0")
+    # the tiny checkpoints have head dims the attention kernel does not cover (16, 32), so the children may take PyTorch statements
+    env = dict(os.environ, PYTHONPATH=f"{ROOT}:{ROOT / 'tests'}", MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0", TTB_STRICT="0")
     cmd = [sys.executable, str(ROOT / "tune"), "run", "--nnodes=1", f"--nproc_per_node={nproc}", "--master-addr=127.0.0.1", f"--master-port={port}"] + args
     res = subprocess.run(cmd, cwd=str(ROOT), env=env, capture_output=True, text=True, timeout=timeout)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]

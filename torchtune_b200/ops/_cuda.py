@@ -724,6 +724,19 @@ def mx_quantize(x2: torch.Tensor, transpose: bool = False) -> Tuple[torch.Tensor
     return q, sf
 
 
+def mx_quantize_both(x2: torch.Tensor) -> Tuple[Tuple[torch.Tensor, torch.Tensor], Tuple[torch.Tensor, torch.Tensor]]:
+    """``(mx_quantize(x2), mx_quantize(x2, transpose=True))`` from one pass over ``x2`` (both dimensions multiples of 32)."""
+    assert x2.dim() == 2 and x2.dtype == _BF16 and x2.stride(1) == 1
+    R, C = x2.shape
+    q = torch.empty(R, C, dtype=torch.uint8, device=x2.device)
+    qt = torch.empty(C, R, dtype=torch.uint8, device=x2.device)
+    sf = torch.zeros(lib().ttb_mx_scale_bytes(R, C), dtype=torch.uint8, device=x2.device)
+    sft = torch.zeros(lib().ttb_mx_scale_bytes(C, R), dtype=torch.uint8, device=x2.device)
+    check(lib().ttb_mx_quantize_both(x2.data_ptr(), x2.stride(0), q.data_ptr(), q.stride(0), sf.data_ptr(), qt.data_ptr(), qt.stride(0), sft.data_ptr(), R, C, stream_ptr()),
+          f"mx_quantize_both {R}x{C}")
+    return (q, sf), (qt, sft)
+
+
 def mx_unpack_scales(sf: torch.Tensor, rows: int, k: int) -> torch.Tensor:
     """``[rows, k / 32]`` exponent bytes read back from the packed scale buffer (tests and debugging)."""
     r = torch.arange(rows, device=sf.device).unsqueeze(1)
@@ -745,6 +758,47 @@ def gemm_mxfp8(aq: torch.Tensor, asf: torch.Tensor, bq: torch.Tensor, bsf: torch
     return out
 
 
+# The most recent activation quantised in each orientation.  Projections that read the same tensor (q / k / v, gate / up) hit it
+# instead of quantising again; the entry keeps that tensor alive, so its address cannot be handed to another tensor meanwhile,
+# and the version counter catches in-place changes.
+_MX_LAST: dict = {}
+
+
+def _mx_quantize_shared(x2: torch.Tensor, transpose: bool) -> Tuple[torch.Tensor, torch.Tensor]:
+    ent = _MX_LAST.get(transpose)
+    if ent is not None:
+        t, version, q, sf = ent
+        if t.data_ptr() == x2.data_ptr() and t.shape == x2.shape and t.stride() == x2.stride() and version == x2._version and t.device == x2.device:
+            return q, sf
+    q, sf = mx_quantize(x2, transpose)
+    _MX_LAST[transpose] = (x2, x2._version, q, sf)
+    return q, sf
+
+
+def _mx_entry(x2: torch.Tensor, transpose: bool):
+    ent = _MX_LAST.get(transpose)
+    if ent is not None:
+        t, version, q, sf = ent
+        if t.data_ptr() == x2.data_ptr() and t.shape == x2.shape and t.stride() == x2.stride() and version == x2._version and t.device == x2.device:
+            return q, sf
+    return None
+
+
+def _mx_quantize_shared_pair(x2: torch.Tensor):
+    """Both orientations of an activation; one fused pass when neither is in the shared entries yet."""
+    plain, transposed = _mx_entry(x2, False), _mx_entry(x2, True)
+    if plain is None and transposed is None and x2.shape[0] % 32 == 0 and x2.shape[1] % 32 == 0:
+        plain, transposed = mx_quantize_both(x2)
+        _MX_LAST[False] = (x2, x2._version, *plain)
+        _MX_LAST[True] = (x2, x2._version, *transposed)
+        return plain, transposed
+    return (plain or _mx_quantize_shared(x2, False)), (transposed or _mx_quantize_shared(x2, True))
+
+
+def mx_clear_shared() -> None:
+    _MX_LAST.clear()
+
+
 class _MXFp8Linear(torch.autograd.Function):
     """``x @ Wᵀ (+ bias)`` with forward, input-gradient and weight-gradient products on the block-scaled fp8 tensor-core path.  Every
     operand is quantised along its own contraction dimension (six quantisations per layer and step); only fp8 copies and their
@@ -756,11 +810,13 @@ class _MXFp8Linear(torch.autograd.Function):
         x2 = x.reshape(-1, K)
         if not x2.is_contiguous():
             x2 = x2.contiguous()
-        xq, xs = mx_quantize(x2)
+        need_dw, need_dx = weight.requires_grad, x.requires_grad
+        if need_dw:
+            (xq, xs), xt = _mx_quantize_shared_pair(x2)  # xt: [K, T], blocks along tokens
+        else:
+            (xq, xs), xt = _mx_quantize_shared(x2, False), (None, None)
         wq, ws = mx_quantize(weight)
         y = gemm_mxfp8(xq, xs, wq, ws, bias=bias)
-        need_dw, need_dx = weight.requires_grad, x.requires_grad
-        xt = mx_quantize(x2, transpose=True) if need_dw else (None, None)  # [K, T], blocks along tokens
         wt = mx_quantize(weight, transpose=True) if need_dx else (None, None)  # [K, N], blocks along N
         ctx.has_bias = bias is not None
         ctx.save_for_backward(xt[0], xt[1], wt[0], wt[1], weight)
@@ -774,11 +830,16 @@ class _MXFp8Linear(torch.autograd.Function):
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
         dx = dw = db = None
+        both = wtq is not None and xtq is not None and dy2.shape[0] % 32 == 0 and dy2.shape[1] % 32 == 0
+        if both:
+            (dyq, dys), (dytq, dyts) = mx_quantize_both(dy2)
         if wtq is not None:
-            dyq, dys = mx_quantize(dy2)  # blocks along N
+            if not both:
+                dyq, dys = mx_quantize(dy2)  # blocks along N
             dx = gemm_mxfp8(dyq, dys, wtq, wts).view(*dy.shape[:-1], wtq.shape[0])
         if xtq is not None:
-            dytq, dyts = mx_quantize(dy2, transpose=True)  # [N, T], blocks along tokens
+            if not both:
+                dytq, dyts = mx_quantize(dy2, transpose=True)  # [N, T], blocks along tokens
             owner = grad_window_owner(weight)
             if owner is None:
                 dw = gemm_mxfp8(dytq, dyts, xtq, xts)

@@ -4,6 +4,8 @@ from __future__ import annotations
 import math
 from typing import Optional, Tuple
 
+import os
+
 import torch
 
 from ._lib import check, err_word, lib, stream_ptr
@@ -70,11 +72,20 @@ class _FlashAttention(torch.autograd.Function):
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         o = torch.empty_like(q)
         lse = torch.empty(b, hq, s, dtype=torch.float32, device=q.device)
-        check(
-            lib().ttb_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), _p(lo), _p(hi), _p(kmask), int(monotone), b, s, sk, hq, hkv, d,
-                               float(scale), int(causal), float(softcap), err_word(q.device).data_ptr(), stream_ptr()),
-            "attention forward",
-        )
+        # head dim 128 with structured (monotone) bounds: two query tiles per CTA, probabilities kept in tensor memory
+        two_tile = d == 128 and kmask is None and softcap == 0.0 and (monotone or (lo is None and hi is None)) and os.environ.get("TTB_ATTN_TWO_TILE", "1") != "0"
+        if two_tile:
+            check(
+                lib().ttb_attn_fwd2(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), _p(lo), _p(hi), b, s, sk, hq, hkv, float(scale), int(causal),
+                                    err_word(q.device).data_ptr(), stream_ptr()),
+                "attention forward (two query tiles)",
+            )
+        else:
+            check(
+                lib().ttb_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), _p(lo), _p(hi), _p(kmask), int(monotone), b, s, sk, hq, hkv, d,
+                                   float(scale), int(causal), float(softcap), err_word(q.device).data_ptr(), stream_ptr()),
+                "attention forward",
+            )
         ctx.save_for_backward(q, k, v, o, lse, lo, hi, kmask)
         ctx.meta = (scale, causal, softcap, monotone)
         return o

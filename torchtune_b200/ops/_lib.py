@@ -54,6 +54,8 @@ def _declare(L: ctypes.CDLL) -> None:
     L.ttb_attn_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, i32, f32, vp, vp]
     L.ttb_attn_bwd.restype = i32
     L.ttb_attn_fwd.restype = i32
+    L.ttb_attn_fwd2.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, vp, vp]
+    L.ttb_attn_fwd2.restype = i32
     L.ttb_gemm_bf16_2sm.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i64, i64, i64, i32, vp, f32, vp, vp]
     L.ttb_gemm_bf16_2sm.restype = i32
     L.ttb_ensure_device.argtypes = [i32]
@@ -84,6 +86,8 @@ def _declare(L: ctypes.CDLL) -> None:
     L.ttb_mx_scale_bytes.restype = i64
     L.ttb_mx_quantize.argtypes = [vp, i64, vp, i64, vp, i64, i64, i32, vp]
     L.ttb_mx_quantize.restype = i32
+    L.ttb_mx_quantize_both.argtypes = [vp, i64, vp, i64, vp, vp, i64, vp, i64, i64, vp]
+    L.ttb_mx_quantize_both.restype = i32
     L.ttb_gemm_mxfp8.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, vp, i32, vp, vp]
     L.ttb_gemm_mxfp8.restype = i32
     L.ttb_fp8_cast_transpose.restype = i32

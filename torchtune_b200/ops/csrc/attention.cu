@@ -68,6 +68,36 @@ __device__ __forceinline__ float fast_tanh(float x) {
   return y;
 }
 
+// two-wide fp32 arithmetic (one instruction per pair of values held in a 64-bit register)
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+  return d;
+}
+__device__ __forceinline__ uint64_t pack_u32x2(uint32_t lo, uint32_t hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+  return d;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
 __device__ __forceinline__ void fail(volatile int* abort_flag, int* err, int code) {
   *abort_flag = 1;
   atomicExch(err, code);
@@ -561,12 +591,44 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         break;
       }
       tc_fence_after();
+      // A block every row of which sees every key (the interior of a causal or packed mask) needs no per-element test: the bounds
+      // are monotone, so the tile's largest lo and smallest hi decide.  Such blocks take the two-wide fp32 path below.
+      bool interior = !EXTRA && (p.monotone || (p.lo == nullptr && p.hi == nullptr)) && q0 + kBlk <= p.s && kv0 + kBlk <= p.sk;
+      if (interior) {
+        const int lo_max = p.lo != nullptr ? p.lo[row_base + q0 + kBlk - 1] : 0;
+        const int hi_min = p.hi != nullptr ? p.hi[row_base + q0] : (p.causal ? q0 : p.sk - 1);
+        interior = lo_max <= kv0 && hi_min >= kv0 + kBlk - 1;
+      }
 #pragma unroll 1
       for (int ch = 0; ch < 4; ++ch) {
         uint32_t sv[32], dv[32];
         tmem_ld_32x32(tS + lane_sel + ch * 32, sv);
         tmem_ld_32x32(tdP + lane_sel + ch * 32, dv);
         tmem_ld_wait();
+        if (interior) {
+          // p = exp2(s·c − lse),  dS = p · (dP − delta) · scale, two elements per instruction
+          const uint64_t c2 = pack_f32x2(c, c), nl2 = pack_f32x2(-lse, -lse), nd2 = pack_f32x2(-dlt, -dlt), sc2 = pack_f32x2(p.scale, p.scale);
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint32_t pu[4], du[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int e = g * 8 + 2 * i;
+              float t0, t1;
+              unpack_f32x2(fma_f32x2(pack_u32x2(sv[e], sv[e + 1]), c2, nl2), t0, t1);
+              const float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
+              const uint64_t p2 = pack_f32x2(p0, p1);
+              float d0, d1;
+              unpack_f32x2(mul_f32x2(mul_f32x2(p2, sc2), add_f32x2(pack_u32x2(dv[e], dv[e + 1]), nd2)), d0, d1);
+              pu[i] = pack_bf16x2(p0, p1);
+              du[i] = pack_bf16x2(d0, d1);
+            }
+            const uint32_t off = swz_offset(r, ch * 32 + g * 8);
+            *reinterpret_cast<uint4*>(sP + off) = make_uint4(pu[0], pu[1], pu[2], pu[3]);
+            *reinterpret_cast<uint4*>(sdS + off) = make_uint4(du[0], du[1], du[2], du[3]);
+          }
+          continue;
+        }
         float pr[32], ds[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
@@ -608,22 +670,25 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       tc_fence_after();
       float* dq_row = p.dq_accum + (static_cast<long long>(row_base + q_idx) * p.hq + h) * D;
-#pragma unroll 1
-      for (int ch = 0; ch < D / 32; ++ch) {
-        uint32_t v[32];
-        tmem_ld_32x32(tS + lane_sel + ch * 32, v);
-        tmem_ld_wait();
-        if (row_ok) {
+      // The whole partial tile is pulled into registers first and the buffer handed back, so the next iteration's Q·Kᵀ and dO·Vᵀ
+      // run while this one's atomics drain.
+      uint32_t dqv[D / 32][32];
 #pragma unroll
-          for (int i = 0; i < 8; ++i)
-            atomicAdd(reinterpret_cast<float4*>(dq_row + ch * 32 + i * 4),
-                      make_float4(__uint_as_float(v[i * 4]), __uint_as_float(v[i * 4 + 1]),
-                                  __uint_as_float(v[i * 4 + 2]), __uint_as_float(v[i * 4 + 3])));
-        }
-      }
+      for (int ch = 0; ch < D / 32; ++ch) tmem_ld_32x32(tS + lane_sel + ch * 32, dqv[ch]);
+      tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(dq_free);
+      if (row_ok) {
+#pragma unroll
+        for (int ch = 0; ch < D / 32; ++ch) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            atomicAdd(reinterpret_cast<float4*>(dq_row + ch * 32 + i * 4),
+                      make_float4(__uint_as_float(dqv[ch][i * 4]), __uint_as_float(dqv[ch][i * 4 + 1]),
+                                  __uint_as_float(dqv[ch][i * 4 + 2]), __uint_as_float(dqv[ch][i * 4 + 3])));
+        }
+      }
     }
     if (!ok) {
       fail(abort_flag, p.err, 303);

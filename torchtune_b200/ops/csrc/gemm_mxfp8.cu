@@ -18,8 +18,11 @@
 //
 // Pipeline per CTA (persistent over 128 × 256 output tiles): warp 0 producer (TMA tiles of A and B plus three 512-byte bulk
 // copies of scale chunks per 128-wide k-block), warp 1 issues per k-block three tcgen05.cp and four MMAs of K = 32, warp 2 owns
-// tensor memory, warps 4-7 drain the accumulator.  Tensor memory: 256 accumulator columns + 12 scale columns per pipeline
-// stage; the accumulator is single-buffered because two 256-column accumulators would leave no room for the scales.
+// tensor memory, warps 4-11 drain the accumulator.  Tensor memory: 256 accumulator columns + 12 scale columns per pipeline
+// stage; two 256-column accumulators would leave no room for the scales (and a 192-wide tile with two accumulators measured slower:
+// the main loop is bound by the shared-memory fill rate, which a narrower tile makes worse).  Instead the single accumulator is
+// handed back early: eight epilogue warps (two per lane quarter, 128 columns each) pull their part into registers with four
+// back-to-back tcgen05.ld, signal the MMA warp, and only then convert and store, so the next tile's main loop overlaps the stores.
 // Every wait is bounded and reports through the error word.
 #include <cuda_fp8.h>
 
@@ -34,7 +37,7 @@ namespace mx {
 static constexpr int BM = 128;
 static constexpr int BN = 256;
 static constexpr int BK = 128;  // fp8 values = bytes per k-block: four MMAs of K = 32, four scale blocks
-static constexpr int kThreads = 256;
+static constexpr int kThreads = 384;  // warps 0-3: producer, MMA, tensor-memory owner, spare; warps 4-11: epilogue
 static constexpr int kGroupM = 16;
 static constexpr int kStages = 4;
 static constexpr int kABytes = BM * BK;          // 16 KB
@@ -131,7 +134,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       mbar_init(&empty[i], 1);
     }
     mbar_init(tfull, 1);
-    mbar_init(tempty, 4);
+    mbar_init(tempty, 8);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -237,8 +240,9 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       acc_phase ^= 1;
     }
   } else if (warp >= 4) {
-    // ------------------------------------------------------------------ epilogue
+    // ------------------------------------------------------------------ epilogue (8 warps: lane quarter x column half)
     const int quarter = warp & 3;
+    const int half = (warp - 4) >> 2;
     uint32_t acc_phase = 0;
     for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x) {
       int m_blk, n_blk;
@@ -251,50 +255,55 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       tc_fence_after();
       const int row = m_blk * BM + quarter * 32 + lane;
       const bool row_ok = row < p.M;
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + c * 32, r);
-        tmem_ld_wait();
-        const int col0 = n_blk * BN + c * 32;
+      const uint32_t taddr = tmem_base + half * 128 + (static_cast<uint32_t>(quarter * 32) << 16);
+      uint32_t r[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32(taddr + c * 32, r[c]);
+      tmem_ld_wait();
+      // the accumulator is free for the next tile as soon as its values sit in registers
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty);
+      acc_phase ^= 1;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int col0 = n_blk * BN + half * 128 + c * 32;
         if (row_ok && col0 < p.N) {
-          float v[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-          if (p.bias != nullptr) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (col0 + i < p.N) v[i] += __bfloat162float(__ldg(p.bias + col0 + i));
-          }
           __nv_bfloat16* dst = p.C + static_cast<long long>(row) * p.ldc + col0;
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             if (col0 + g * 8 + 8 <= p.N) {
+              float v[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[c][g * 8 + i]);
+              if (p.bias != nullptr) {
+                const uint4 bq = __ldg(reinterpret_cast<const uint4*>(p.bias + col0 + g * 8));
+                const __nv_bfloat162* bb = reinterpret_cast<const __nv_bfloat162*>(&bq);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const float2 f = __bfloat1622float2(bb[i]);
+                  v[2 * i] += f.x, v[2 * i + 1] += f.y;
+                }
+              }
               if (p.accumulate) {
                 const uint4 old = *reinterpret_cast<const uint4*>(dst + g * 8);
                 const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&old);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                   const float2 f = __bfloat1622float2(ob[i]);
-                  v[g * 8 + 2 * i] += f.x;
-                  v[g * 8 + 2 * i + 1] += f.y;
+                  v[2 * i] += f.x, v[2 * i + 1] += f.y;
                 }
               }
               uint4 o;
-              o.x = pack_bf16x2(v[g * 8 + 0], v[g * 8 + 1]);
-              o.y = pack_bf16x2(v[g * 8 + 2], v[g * 8 + 3]);
-              o.z = pack_bf16x2(v[g * 8 + 4], v[g * 8 + 5]);
-              o.w = pack_bf16x2(v[g * 8 + 6], v[g * 8 + 7]);
+              o.x = pack_bf16x2(v[0], v[1]);
+              o.y = pack_bf16x2(v[2], v[3]);
+              o.z = pack_bf16x2(v[4], v[5]);
+              o.w = pack_bf16x2(v[6], v[7]);
               *reinterpret_cast<uint4*>(dst + g * 8) = o;
             }
           }
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(tempty);
-      acc_phase ^= 1;
     }
   }
 
@@ -396,6 +405,73 @@ mx_quantize_cols_kernel(const __nv_bfloat16* __restrict__ src, long long ld, uin
   }
 }
 
+// Both orientations in one pass over the source: q[r, c] with blocks along the columns and qT[c, r] with blocks along the rows.
+// One warp per 32 × 32 tile: lane l loads row l (64 bytes), quantises it as a block of q, parks the fp32 values in shared memory
+// and then quantises column l of the tile as a block of qT.  R and C are multiples of 32.
+__global__ void __launch_bounds__(256)
+mx_quantize_both_kernel(const __nv_bfloat16* __restrict__ src, long long ld, uint8_t* __restrict__ q, long long ldq, uint8_t* __restrict__ sf,
+                        uint8_t* __restrict__ qT, long long ldqT, uint8_t* __restrict__ sfT, long long R, long long C) {
+  __shared__ float tile[8][32][33];
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long tiles_c = C >> 5;
+  const long long total = (R >> 5) * tiles_c;
+  const long long chunks_q = (C + 127) / 128, chunks_qT = (R + 127) / 128;
+  for (long long t = blockIdx.x * 8LL + w; t < total; t += static_cast<long long>(gridDim.x) * 8) {
+    const long long tr = t / tiles_c, tc = t - tr * tiles_c;
+    const long long r = tr * 32 + lane;
+    const uint4* s4 = reinterpret_cast<const uint4*>(src + r * ld + tc * 32);
+    uint4 raw[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) raw[j] = s4[j];
+    float v[32];
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[j]);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(h[k]);
+        v[j * 8 + 2 * k] = f.x, v[j * 8 + 2 * k + 1] = f.y;
+        amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 32; ++j) tile[w][lane][j] = v[j];
+    float inv;
+    sf[sf_offset(r, tc, chunks_q)] = block_scale_byte(amax, inv);
+    uint32_t out[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * j] * inv, v[4 * j + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+      const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * j + 2] * inv, v[4 * j + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+      out[j] = lo | (hi << 16);
+    }
+    uint4* d = reinterpret_cast<uint4*>(q + r * ldq + tc * 32);
+    d[0] = make_uint4(out[0], out[1], out[2], out[3]);
+    d[1] = make_uint4(out[4], out[5], out[6], out[7]);
+    __syncwarp();
+    // column `lane` of the tile: 32 source rows = one block of the transposed operand
+    amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      v[j] = tile[w][j][lane];
+      amax = fmaxf(amax, fabsf(v[j]));
+    }
+    const long long c = tc * 32 + lane;
+    sfT[sf_offset(c, tr, chunks_qT)] = block_scale_byte(amax, inv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * j] * inv, v[4 * j + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+      const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * j + 2] * inv, v[4 * j + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+      out[j] = lo | (hi << 16);
+    }
+    d = reinterpret_cast<uint4*>(qT + c * ldqT + tr * 32);
+    d[0] = make_uint4(out[0], out[1], out[2], out[3]);
+    d[1] = make_uint4(out[4], out[5], out[6], out[7]);
+    __syncwarp();
+  }
+}
+
 }  // namespace mx
 }  // namespace ttb
 
@@ -428,6 +504,22 @@ extern "C" int ttb_mx_quantize(const void* src, long long ld, void* q, long long
   return cudaGetLastError() == cudaSuccess ? kOk : kErrDriver;
 }
 
+// Both operands of a tensor in one pass: q [R, C] with blocks along C and qT [C, R] with blocks along R (scale buffers sf / sfT
+// zero-filled by the caller, sized by ttb_mx_scale_bytes(R, C) / (C, R)).  R and C are multiples of 32.
+extern "C" int ttb_mx_quantize_both(const void* src, long long ld, void* q, long long ldq, void* sf, void* qT, long long ldqT, void* sfT, long long R, long long C,
+                                    void* stream) {
+  using namespace ttb;
+  if (R <= 0 || C <= 0 || (R & 31) || (C & 31) || (ld & 7) || (ldq & 15) || (ldqT & 15)) return kErrBadShape;
+  if ((reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(qT) & 15)) return kErrBadShape;
+  const long long tiles = (R >> 5) * (C >> 5);
+  long long grid = (tiles + 7) / 8;
+  if (grid > sm_count() * 8LL) grid = sm_count() * 8LL;
+  TTB_COUNT_LAUNCH(1);
+  mx::mx_quantize_both_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(src), ld, static_cast<uint8_t*>(q), ldq, static_cast<uint8_t*>(sf), static_cast<uint8_t*>(qT), ldqT, static_cast<uint8_t*>(sfT), R, C);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrDriver;
+}
+
 // A: [M, K] e4m3, B: [N, K] e4m3 (row pitches lda / ldb in bytes, multiples of 16), sfa / sfb: scale buffers as written by
 // ttb_mx_quantize for these operands, C: [M, N] bf16 (ldc multiple of 8; accumulate != 0 adds to its contents).  K is a multiple of 32.
 extern "C" int ttb_gemm_mxfp8(const void* A, const void* B, const void* sfa, const void* sfb, void* C, int M, int N, int K, long long lda, long long ldb,
@@ -435,7 +527,7 @@ extern "C" int ttb_gemm_mxfp8(const void* A, const void* B, const void* sfa, con
   using namespace ttb;
   if (M <= 0 || N <= 0 || K <= 0 || sfa == nullptr || sfb == nullptr) return kErrBadShape;
   if ((lda & 15) || (ldb & 15) || (ldc & 7) || (N & 7) || (K & 31)) return kErrBadShape;
-  if ((reinterpret_cast<uintptr_t>(sfa) & 15) || (reinterpret_cast<uintptr_t>(sfb) & 15)) return kErrBadShape;
+  if ((reinterpret_cast<uintptr_t>(sfa) & 15) || (reinterpret_cast<uintptr_t>(sfb) & 15) || (reinterpret_cast<uintptr_t>(bias) & 15)) return kErrBadShape;
   mx::Params p;
   p.M = M, p.N = N, p.K = K, p.C = static_cast<__nv_bfloat16*>(C), p.ldc = ldc;
   p.sfa = static_cast<const uint8_t*>(sfa), p.sfb = static_cast<const uint8_t*>(sfb);

@@ -101,11 +101,14 @@ def bench_gemm_mxfp8(args, flush):
     t = _time(lambda: gemm_mxfp8(aq, asf, bq, bsf, out=out), args.iters, args.warmup, flush)
     t_q = _time(lambda: mx_quantize(a), args.iters, args.warmup, flush)
     t_qt = _time(lambda: mx_quantize(a, transpose=True), args.iters, args.warmup, flush)
+    from ._cuda import mx_quantize_both
+
+    t_qb = _time(lambda: mx_quantize_both(a), args.iters, args.warmup, flush)
     with torch.no_grad():
         t_lin = _time(lambda: mxfp8_linear(a, b, None), args.iters, args.warmup, flush)
     t_bf16 = _time(lambda: gemm(a, b, out=out), args.iters, args.warmup, flush)
     return {"op": "gemm_mxfp8_nt", "m": m, "n": n, "k": k, "ms": t, "tflops": flops / t / 1e9, "quantize_ms": t_q, "quantize_gbs": (m * k * 3) / t_q / 1e6,
-            "quantize_transposed_ms": t_qt, "mxfp8_linear_fwd_ms": t_lin, "bf16_gemm_ms": t_bf16, "bf16_tflops": flops / t_bf16 / 1e9}
+            "quantize_transposed_ms": t_qt, "quantize_both_ms": t_qb, "mxfp8_linear_fwd_ms": t_lin, "bf16_gemm_ms": t_bf16, "bf16_tflops": flops / t_bf16 / 1e9}
 
 
 def bench_attention(args, flush):

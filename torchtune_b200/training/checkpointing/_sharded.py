@@ -67,6 +67,8 @@ class DistributedCheckpointer:
         self._adapter_dir = "adapter_model"
         self._pool = ThreadPoolExecutor(max_workers=1, thread_name_prefix="ckpt-writer")
         self._checkpoint_future: Optional[Future] = None
+        self._save_seq = 0  # saves issued by this process; identical on every rank because saves are collective
+        self._stale_cleared = False
 
     @property
     def output_dir(self) -> Path:
@@ -83,22 +85,37 @@ class DistributedCheckpointer:
             self._checkpoint_future = None
 
     # ------------------------------------------------------------------ save
-    def _write(self, host_state: Dict[str, Any], final: Path, step_info: Dict[str, Any]) -> None:
+    def _clear_stale_partials(self) -> None:
+        """Once per process, before the first writer runs: rank 0 removes ``*.partial`` directories that an interrupted job left
+        behind (their ``rank_r.pt`` files and markers belong to a dead attempt), then every rank passes a barrier."""
+        if self._stale_cleared:
+            return
+        self._stale_cleared = True
+        if self._rank == 0 and self._output_dir.is_dir():
+            for pattern in ("*.partial", "*/*.partial"):
+                for stale in self._output_dir.glob(pattern):
+                    if stale.is_dir():
+                        shutil.rmtree(stale, ignore_errors=True)
+        self._barrier()
+
+    def _write(self, host_state: Dict[str, Any], final: Path, step_info: Dict[str, Any], nonce: str) -> None:
         tmp = final.with_name(final.name + ".partial")
         tmp.mkdir(parents=True, exist_ok=True)
         torch.save(host_state, tmp / f"rank_{self._rank}.pt")
-        (tmp / f"rank_{self._rank}.done").write_text("ok")
+        # the marker name carries this save's nonce (step, restart count, save counter), so a marker left by an earlier attempt
+        # at the same step can never count as "rank r has finished writing"
+        (tmp / f"rank_{self._rank}.{nonce}.done").write_text("ok")
         if self._rank == 0:
             # rank 0 publishes the directory once every rank's marker is present (file-system rendezvous:
             # the writer thread must not issue collectives that could interleave with training collectives)
             deadline = time.time() + 3600
-            while any(not (tmp / f"rank_{r}.done").exists() for r in range(self._world)):
+            while any(not (tmp / f"rank_{r}.{nonce}.done").exists() for r in range(self._world)):
                 if time.time() > deadline:
                     raise TimeoutError(f"not all ranks finished writing {tmp}")
                 time.sleep(0.05)
             (tmp / "metadata.json").write_text(json.dumps({"world_size": self._world, "keys": sorted(host_state.keys()), **step_info}))
-            for r in range(self._world):
-                (tmp / f"rank_{r}.done").unlink()
+            for marker in tmp.glob("rank_*.done"):
+                marker.unlink()
             if final.exists():
                 shutil.rmtree(final)
             os.replace(tmp, final)
@@ -121,11 +138,14 @@ class DistributedCheckpointer:
             self._checkpoint_future.result()
             logger.info(f"Rank {self._rank}: waited {time.perf_counter() - t0:.2f} seconds for previous checkpoint to finish")
         self._checkpoint_future = None
+        self._clear_stale_partials()
+        self._save_seq += 1
+        nonce = f"e{epoch}-s{step}-r{os.environ.get('TORCHELASTIC_RESTART_COUNT', '0')}-n{self._save_seq}"
         t0 = time.perf_counter()
         host_state = _to_host(state_dict)  # the only step that must finish before training continues
         info = {"epoch": epoch, "step": step}
         if save_async:
-            self._checkpoint_future = self._pool.submit(self._write, host_state, final, info)
+            self._checkpoint_future = self._pool.submit(self._write, host_state, final, info, nonce)
 
             def _report(f: Future) -> None:
                 if f.exception() is None:
@@ -136,7 +156,7 @@ class DistributedCheckpointer:
             self._checkpoint_future.add_done_callback(_report)
             logger.info(f"Rank {self._rank}: Trainer was blocked for {time.perf_counter() - t0:.2f} seconds for checkpointing to finish...")
         else:
-            self._write(host_state, final, info)
+            self._write(host_state, final, info, nonce)
             if self._rank != 0:  # wait for rank 0 to publish the directory
                 deadline = time.time() + 3600
                 while not (final / "metadata.json").exists():

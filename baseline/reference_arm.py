@@ -409,7 +409,8 @@ def run_tensor_parallel(args, name, spec, lr, ClockSampler, timed_loop, dist_env
                     m.rope_init()
     loss_fn.set_model_output(model)
     optimizer = torch.optim.AdamW(model.parameters(), lr=lr, fused=True)
-    offload_ctx = training.get_act_offloading_ctx_manager(model, bool(spec["offload"]))
+    offload = bool(spec["offload"]) and not getattr(args, "ref_no_offload", False)
+    offload_ctx = training.get_act_offloading_ctx_manager(model, offload)
     train_context = training.get_train_context(enable_loss_parallel=True)
 
     seq_len, doc_len, batch = spec["seq"], spec["doc"], spec["batch"]
@@ -468,7 +469,7 @@ def run_tensor_parallel(args, name, spec, lr, ClockSampler, timed_loop, dist_env
         "data": "synthetic uniform tokens, random-init weights", "impl": "reference",
         "config": {"model": spec["label"], "bench_config": name, "global_batch": batch * dp_size, "seq_len": seq_len, "doc_len": doc_len,
                    "parallelism": f"tp{tp}" + (f" x fsdp{dp_size}" if dp_size > 1 else "") + " (DTensor, sequence parallel norms, loss parallel)",
-                   "activation_checkpointing": True, "activation_offloading": bool(spec["offload"]), "optimizer": "torch.optim.AdamW fused lr 2e-5",
+                   "activation_checkpointing": True, "activation_offloading": offload, "optimizer": "torch.optim.AdamW fused lr 2e-5",
                    "l2": "inputs larger than L2 (tens of GB of weights streamed every step)",
                    **({"debug_layers": args.debug_layers, "invalid": "reduced layer count: a functional check, not a benchmark number"} if args.debug_layers else {})},
         "clocks": clocks, "e2e": {"value": tokens_per_step * args.steps / t_e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},

@@ -601,6 +601,7 @@ def main() -> None:
                     help="off-headline variants; the headline is always the full fine-tune.  lora / qlora / dpo: the adapter configurations at per-GPU batch 8")
     ap.add_argument("--config", choices=["8b"] + sorted(SHARDED_CONFIGS), default="8b", help="8b: the headline (Llama-3.1-8B); the others are the 70B tensor-parallel and Scout expert-parallel configurations")
     ap.add_argument("--debug-layers", type=int, default=0, help="functional check of a --config on few GPUs: build only this many layers (the printed line is marked invalid)")
+    ap.add_argument("--ref-no-offload", action="store_true", help="with --impl reference --config 70b_*: run the reference without its activation offloading (diagnostic)")
     ap.add_argument("--ref-compile", action="store_true", help="with --impl reference: the reference's `compile: True` path (informational; the default arm stays on the stock eager path)")
     ap.add_argument("--fp8-recipe", choices=["tensorwise", "blockwise"], default="tensorwise", help="with --fp8: one scale per tensor, or MX block scales (32 values per scale)")
     ap.add_argument("--fp8", action="store_true", help="variant: fp8 decoder linears (the headline number is always bf16)")

@@ -1038,3 +1038,52 @@ def test_mx_quantize_both_matches_the_two_single_passes(R, C):
     q1, sf1 = mx_quantize(x)
     qt1, sft1 = mx_quantize(x, transpose=True)
     assert torch.equal(q, q1) and torch.equal(sf, sf1) and torch.equal(qt, qt1) and torch.equal(sft, sft1)
+
+
+def test_out_of_range_user_indices_are_replaced_and_counted(monkeypatch):
+    """Token ids, labels and positions outside their tables never reach an address computation: row 0 / an ignored row / position 0
+    stand in, the event is counted, and TTB_DEBUG_BOUNDS=1 turns the count into an exception at the next device check."""
+    from torchtune_b200.ops import _lib
+
+    _lib.index_violations()  # clear
+    table = _rand(64, 128, seed=1)
+    ids = torch.tensor([[3, 64, -1, 5]], device="cuda")
+    out = ops.embedding(ids, table)
+    assert torch.equal(out[0, 1], table[0]) and torch.equal(out[0, 2], table[0]) and torch.equal(out[0, 0], table[3])
+    assert _lib.index_violations() == 2
+    hidden, w = _rand(8, 256, seed=2), _rand(128, 256, seed=3, scale=0.05)
+    labels = torch.tensor([1, 2, 128, -5, -100, 7, 0, 127], device="cuda")
+    loss_sum, n_valid = ops.linear_cross_entropy(hidden, w, labels, num_chunks=1)
+    ref_labels = labels.clone()
+    ref_labels[2:4] = -100
+    want, _ = ops.linear_cross_entropy(hidden, w, ref_labels, num_chunks=1)
+    assert torch.isfinite(loss_sum) and torch.allclose(loss_sum.float(), want.float(), rtol=1e-3)
+    assert _lib.index_violations() == 2
+    monkeypatch.setenv("TTB_DEBUG_BOUNDS", "1")
+    _lib.err_word(torch.device("cuda"))
+    ops.embedding(ids, table)
+    with pytest.raises(_lib.KernelError, match="out-of-range"):
+        _lib.check_device_errors()
+    _lib.check_device_errors()  # the count was cleared by the failed check
+
+
+@pytest.mark.parametrize("kind", ["forward", "reverse", "symmetric"])
+def test_kd_divergence_kernel_matches_fp32_statement(kind):
+    from torchtune_b200.modules.loss import ForwardKLLoss, ReverseKLLoss, SymmetricKLLoss
+
+    loss = {"forward": ForwardKLLoss(), "reverse": ReverseKLLoss(), "symmetric": SymmetricKLLoss(sym_kd_ratio=0.3)}[kind]
+    rows, V = 37, 1000
+    student = _rand(rows, V, seed=41, scale=2.0).requires_grad_()
+    teacher = _rand(rows, V, seed=42, scale=2.0)
+    labels = torch.randint(0, V, (rows,), device="cuda")
+    labels[::5] = -100
+    for normalize in (True, False):
+        student.grad = None
+        got = loss(student, teacher, labels, normalize=normalize)
+        got.backward()
+        s32 = student.detach().float().requires_grad_()
+        want = loss(s32, teacher.float(), labels, normalize=normalize)  # fp32 inputs take the PyTorch statement
+        want.backward()
+        assert abs(got.item() - want.item()) < 2e-3 * max(1.0, abs(want.item())), (kind, got.item(), want.item())
+        _close(student.grad, s32.grad, 2e-2, 2e-2 * s32.grad.abs().max().item(), f"kd {kind} grad")
+        assert (student.grad[::5] == 0).all()

@@ -13,6 +13,19 @@ import torch.nn.functional as F
 from torch import nn
 
 
+def _fused(student_logits, teacher_logits, labels, w_fwd: float, w_rev: float, ignore_index: int, normalize: bool):
+    """bf16 CUDA logits: the fused divergence kernel (``None`` otherwise)."""
+    from ... import ops
+
+    total = ops.kd_divergence(student_logits, teacher_logits, labels, w_fwd, w_rev, ignore_index)
+    if total is None:
+        return None
+    if not normalize:
+        return total
+    n = (labels != ignore_index).sum()
+    return total / torch.clamp(n, min=1)
+
+
 def _masked_token_mean(per_token: torch.Tensor, mask: torch.Tensor, normalize: bool) -> torch.Tensor:
     total = -(per_token * mask).sum()
     if not normalize:
@@ -31,6 +44,9 @@ class ForwardKLLoss(nn.Module):
         self.ignore_index = ignore_index
 
     def forward(self, student_logits, teacher_logits, labels, normalize: bool = True) -> torch.Tensor:
+        fused = _fused(student_logits, teacher_logits, labels, 1.0, 0.0, self.ignore_index, normalize)
+        if fused is not None:
+            return fused
         t_prob = F.softmax(teacher_logits.float(), dim=-1)
         s_logp = F.log_softmax(student_logits.float(), dim=-1)
         inf_mask = torch.isinf(student_logits)
@@ -47,6 +63,9 @@ class ReverseKLLoss(nn.Module):
         self.ignore_index = ignore_index
 
     def forward(self, student_logits, teacher_logits, labels, normalize: bool = True) -> torch.Tensor:
+        fused = _fused(student_logits, teacher_logits, labels, 0.0, 1.0, self.ignore_index, normalize)
+        if fused is not None:
+            return fused
         s_prob = F.softmax(student_logits.float(), dim=-1)
         s_logp = F.log_softmax(student_logits.float(), dim=-1)
         t_logp = F.log_softmax(teacher_logits.float(), dim=-1)
@@ -68,6 +87,9 @@ class SymmetricKLLoss(nn.Module):
         self.rkl = ReverseKLLoss(ignore_index)
 
     def forward(self, student_logits, teacher_logits, labels, normalize: bool = True) -> torch.Tensor:
+        fused = _fused(student_logits, teacher_logits, labels, self.sym_kd_ratio, 1.0 - self.sym_kd_ratio, self.ignore_index, normalize)
+        if fused is not None:
+            return fused
         return self.sym_kd_ratio * self.fkl(student_logits, teacher_logits, labels, normalize) + (
             1 - self.sym_kd_ratio
         ) * self.rkl(student_logits, teacher_logits, labels, normalize)

@@ -274,6 +274,19 @@ def token_logprobs(
     return reference.token_logprobs(hidden, weight, labels, ignore_index, num_chunks)
 
 
+def kd_divergence(student_logits: torch.Tensor, teacher_logits: torch.Tensor, labels: torch.Tensor, w_fwd: float, w_rev: float,
+                  ignore_index: int = -100) -> Optional[torch.Tensor]:
+    """Summed distillation divergence ``w_fwd · forward-KL term + w_rev · reverse KL`` over the rows whose label is not
+    ``ignore_index`` (fused kernel: both softmaxes, the loss and the student gradient in one launch); ``None`` when the inputs are
+    not bf16 CUDA logits with a vocabulary width that is a multiple of 8."""
+    if not (_native(student_logits) and teacher_logits.is_cuda and teacher_logits.dtype == torch.bfloat16 and student_logits.shape[-1] % 8 == 0
+            and student_logits.shape == teacher_logits.shape and labels.is_cuda):
+        return None
+    from . import _cuda
+
+    return _cuda.kd_divergence(student_logits, teacher_logits, labels, w_fwd, w_rev, ignore_index)
+
+
 def embedding(tokens: torch.Tensor, weight: torch.Tensor, padding_idx: Optional[int] = None) -> torch.Tensor:
     """``weight[tokens]``; bf16 CUDA tables use the gather kernel and the sorted, fp32-accumulating gradient kernel."""
     if _native(weight) and tokens.is_cuda and weight.dim() == 2 and weight.shape[1] % 8 == 0 and weight.is_contiguous():

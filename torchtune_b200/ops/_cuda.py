@@ -896,13 +896,43 @@ def rms_norm(x: torch.Tensor, scale: Optional[torch.Tensor], eps: float) -> torc
     return _RMSNorm.apply(x, scale, eps)
 
 
+# ======================================================================= distillation divergences
+class _KDDivergence(torch.autograd.Function):
+    """Sum over rows of ``w_fwd · (−Σ p_t log p_s) + w_rev · Σ p_s (log p_s − log p_t)`` for bf16 ``[rows, V]`` student / teacher logits;
+    rows whose label equals ``ignore_index`` are skipped.  The gradient with respect to the student logits is produced by the same
+    kernel launch (bf16), so neither softmax is ever materialised in fp32."""
+
+    @staticmethod
+    def forward(ctx, student, teacher, labels, w_fwd: float, w_rev: float, ignore_index: int):
+        rows, V = student.shape
+        loss_rows = torch.empty(rows, dtype=torch.float32, device=student.device)
+        grad = torch.empty_like(student) if student.requires_grad else None
+        check(lib().ttb_kd_divergence(student.data_ptr(), teacher.data_ptr(), labels.data_ptr(), loss_rows.data_ptr(), _ptr(grad), rows, V, student.stride(0), teacher.stride(0),
+                                      grad.stride(0) if grad is not None else 0, int(ignore_index), float(w_fwd), float(w_rev), stream_ptr()), "kd_divergence")
+        ctx.save_for_backward(grad)
+        return loss_rows.sum()
+
+    @staticmethod
+    def backward(ctx, g):
+        (grad,) = ctx.saved_tensors
+        return (grad * g.to(grad.dtype)) if grad is not None else None, None, None, None, None, None
+
+
+def kd_divergence(student: torch.Tensor, teacher: torch.Tensor, labels: torch.Tensor, w_fwd: float, w_rev: float, ignore_index: int) -> torch.Tensor:
+    def rows2d(t):
+        t = t.reshape(-1, t.shape[-1])
+        return t if (t.stride(1) == 1 and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0) else t.contiguous()
+
+    return _KDDivergence.apply(rows2d(student), rows2d(teacher.detach()), labels.reshape(-1).contiguous(), w_fwd, w_rev, ignore_index)
+
+
 # ======================================================================= RoPE
 def _rope_launch(x: torch.Tensor, cache: torch.Tensor, pos: Optional[torch.Tensor], interleaved: bool, inverse: bool) -> torch.Tensor:
     b, s, h, d = x.shape
     if not x.is_contiguous():
         x = x.contiguous()
     y = torch.empty_like(x)
-    check(lib().ttb_rope(x.data_ptr(), y.data_ptr(), cache.data_ptr(), _ptr(pos), b * s, h, d, s, int(interleaved), int(inverse), stream_ptr()), "rope")
+    check(lib().ttb_rope(x.data_ptr(), y.data_ptr(), cache.data_ptr(), _ptr(pos), b * s, h, d, s, int(interleaved), int(inverse), int(cache.shape[0]), stream_ptr()), "rope")
     return y
 
 

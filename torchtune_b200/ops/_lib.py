@@ -7,6 +7,7 @@ loader is simply never invoked.
 from __future__ import annotations
 
 import ctypes
+import os
 from pathlib import Path
 from typing import Optional
 
@@ -44,7 +45,11 @@ def _declare(L: ctypes.CDLL) -> None:
     L.ttb_rmsnorm_fwd.argtypes = [vp, vp, vp, vp, i32, i32, f32, vp]
     L.ttb_rmsnorm_bwd_partials.argtypes = [i32]
     L.ttb_rmsnorm_bwd.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, vp]
-    L.ttb_rope.argtypes = [vp, vp, vp, vp, i64, i32, i32, i32, i32, i32, vp]
+    L.ttb_rope.argtypes = [vp, vp, vp, vp, i64, i32, i32, i32, i32, i32, i32, vp]
+    L.ttb_kd_divergence.argtypes = [vp, vp, vp, vp, vp, i32, i32, i64, i64, i64, i64, f32, f32, vp]
+    L.ttb_kd_divergence.restype = i32
+    L.ttb_index_violations.argtypes = [i32]
+    L.ttb_index_violations.restype = ctypes.c_uint32
     L.ttb_swiglu_fwd.argtypes = [vp, vp, vp, i64, i32, i64, i64, i64, vp]
     L.ttb_swiglu_bwd.argtypes = [vp, vp, vp, vp, vp, i64, i32, i64, i64, i64, i64, i64, vp]
     L.ttb_adamw.argtypes = [vp, i32, i64, i32, f32, f32, f32, f32, f32, f32, f32, vp, f32, vp]
@@ -121,8 +126,19 @@ def err_word(device: torch.device) -> torch.Tensor:
     return _err_words[key]
 
 
+def index_violations(reset: bool = True) -> int:
+    """Out-of-range token ids, labels and positions that kernels replaced by a safe value (row 0 / ignored / position 0) since the
+    last reset, on the current device.  Synchronises."""
+    return int(lib().ttb_index_violations(int(reset)))
+
+
 def check_device_errors(device: Optional[torch.device] = None) -> None:
-    """Synchronising check of the device error word; raises if any kernel timed out."""
+    """Synchronising check of the device error word; raises if any kernel timed out.  With ``TTB_DEBUG_BOUNDS=1`` an out-of-range
+    user index seen by a kernel raises too."""
+    if os.environ.get("TTB_DEBUG_BOUNDS", "0") == "1" and _err_words:
+        n = index_violations()
+        if n:
+            raise KernelError(f"{n} out-of-range token ids / labels / positions were replaced by safe values (TTB_DEBUG_BOUNDS=1)")
     for key, word in _err_words.items():
         code = int(word.item())
         if code != 0:

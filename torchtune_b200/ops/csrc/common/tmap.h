@@ -10,6 +10,22 @@
 extern "C" long long ttb_launch_counter;
 #define TTB_COUNT_LAUNCH(n) (ttb_launch_counter += (n))
 
+// Index values that come from user data (token ids, labels, positions) are never used out of range: the kernel substitutes a
+// safe value and counts the event in a per-file device counter, which the host reads through ttb_index_violations().  With
+// TTB_DEBUG_BOUNDS=1 the Python layer turns a non-zero count into an exception at its next device check.
+#define TTB_DEFINE_VIOLATION_COUNTER(name)                                          \
+  static __device__ unsigned int g_violations_##name;                               \
+  extern "C" unsigned int ttb_violations_##name(int reset) {                        \
+    unsigned int v = 0;                                                             \
+    if (cudaMemcpyFromSymbol(&v, g_violations_##name, sizeof(v)) != cudaSuccess) return 0xffffffffu; \
+    if (reset && v != 0) {                                                          \
+      const unsigned int z = 0;                                                     \
+      cudaMemcpyToSymbol(g_violations_##name, &z, sizeof(z));                       \
+    }                                                                               \
+    return v;                                                                       \
+  }
+#define TTB_NOTE_VIOLATION(name) atomicAdd(&g_violations_##name, 1u)
+
 namespace ttb {
 
 enum : int {

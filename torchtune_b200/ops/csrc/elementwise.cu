@@ -8,6 +8,8 @@
 
 #include "common/tmap.h"
 
+TTB_DEFINE_VIOLATION_COUNTER(rope)
+
 namespace ttb {
 
 __device__ __forceinline__ float warp_sum(float v) {
@@ -227,7 +229,7 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
 template <bool INTERLEAVED>
 __global__ void rope_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
                             const float* __restrict__ cache, const int* __restrict__ pos, long long tokens, int heads,
-                            int d, int seq_len, int inverse) {
+                            int d, int seq_len, int inverse, int cache_len) {
   // one thread handles 8 consecutive elements (interleaved) or 4+4 mirrored elements (half split)
   const int per_head = INTERLEAVED ? d / 8 : d / 16;
   const long long total = tokens * heads * per_head;
@@ -236,7 +238,11 @@ __global__ void rope_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* 
     const int v = static_cast<int>(idx % per_head);
     const long long th = idx / per_head;
     const long long tok = th / heads;
-    const int p = pos != nullptr ? pos[tok] : static_cast<int>(tok % seq_len);
+    int p = pos != nullptr ? pos[tok] : static_cast<int>(tok % seq_len);
+    if (p < 0 || p >= cache_len) {  // a position the cache does not hold: position 0 stands in and the event is counted
+      if (v == 0 && th % heads == 0) TTB_NOTE_VIOLATION(rope);
+      p = 0;
+    }
     const float* c = cache + static_cast<long long>(p) * d;  // (d/2) * 2 floats per position
     const __nv_bfloat16* xp = x + th * d;
     __nv_bfloat16* yp = y + th * d;
@@ -397,21 +403,21 @@ extern "C" int ttb_rmsnorm_bwd(const void* dy, const void* x, const void* scale,
 }
 
 extern "C" int ttb_rope(const void* x, void* y, const float* cache, const int* pos, long long tokens, int heads, int d,
-                        int seq_len, int interleaved, int inverse, void* stream) {
-  if (d % 16) return kErrBadShape;
+                        int seq_len, int interleaved, int inverse, int cache_len, void* stream) {
+  if (d % 16 || cache_len <= 0) return kErrBadShape;
   auto s = static_cast<cudaStream_t>(stream);
   if (interleaved) {
     const long long total = tokens * heads * (d / 8);
     TTB_COUNT_LAUNCH(1);
     rope_kernel<true><<<grid_for(total, 256), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x),
                                                           static_cast<__nv_bfloat16*>(y), cache, pos, tokens, heads, d,
-                                                          seq_len, inverse);
+                                                          seq_len, inverse, cache_len);
   } else {
     const long long total = tokens * heads * (d / 16);
     TTB_COUNT_LAUNCH(1);
     rope_kernel<false><<<grid_for(total, 256), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x),
                                                            static_cast<__nv_bfloat16*>(y), cache, pos, tokens, heads, d,
-                                                           seq_len, inverse);
+                                                           seq_len, inverse, cache_len);
   }
   return cudaGetLastError() == cudaSuccess ? kOk : kErrDriver;
 }
@@ -500,4 +506,13 @@ extern "C" int ttb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void
     if (cudaGetLastError() != cudaSuccess) return kErrDriver;
   }
   return kOk;
+}
+
+
+extern "C" unsigned int ttb_violations_embedding(int reset);
+extern "C" unsigned int ttb_violations_loss(int reset);
+
+// Out-of-range user indices (token ids, labels, positions) that kernels replaced by a safe value since the last reset.
+extern "C" unsigned int ttb_index_violations(int reset) {
+  return ttb_violations_rope(reset) + ttb_violations_embedding(reset) + ttb_violations_loss(reset);
 }

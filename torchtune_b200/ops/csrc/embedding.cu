@@ -7,6 +7,8 @@
 #include "common/ptx.cuh"
 #include "common/tmap.h"
 
+TTB_DEFINE_VIOLATION_COUNTER(embedding)
+
 namespace ttb {
 
 __global__ void __launch_bounds__(256)
@@ -14,7 +16,10 @@ embedding_fwd_kernel(const long long* __restrict__ ids, const uint4* __restrict_
                      long long n_tokens, int vec_per_row, long long vocab) {
   for (long long t = blockIdx.x; t < n_tokens; t += gridDim.x) {
     long long id = ids[t];
-    if (id < 0 || id >= vocab) id = 0;  // ids are validated on the host; never read out of bounds
+    if (id < 0 || id >= vocab) {  // never read out of bounds: row 0 stands in and the event is counted
+      if (threadIdx.x == 0) TTB_NOTE_VIOLATION(embedding);
+      id = 0;
+    }
     const uint4* src = table + id * vec_per_row;
     uint4* dst = out + t * vec_per_row;
     for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) dst[v] = src[v];

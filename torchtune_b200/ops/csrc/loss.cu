@@ -13,6 +13,8 @@
 
 #include "common/tmap.h"
 
+TTB_DEFINE_VIOLATION_COUNTER(loss)
+
 namespace ttb {
 
 static constexpr int kCEThreads = 512;
@@ -42,7 +44,9 @@ softmax_ce_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restric
   if (row >= rows) return;
   __nv_bfloat16* lr = logits + static_cast<long long>(row) * ld;
   const long long label = labels[row];
-  const bool ignored = label == ignore_index;
+  const bool out_of_range = label != ignore_index && (label < 0 || label >= V);  // treated like an ignored row, and counted
+  if (out_of_range && threadIdx.x == 0) TTB_NOTE_VIOLATION(loss);
+  const bool ignored = label == ignore_index || out_of_range;
   const int nvec = V >> 3;
 
   if (ignored) {
@@ -109,6 +113,144 @@ softmax_ce_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restric
   }
 }
 
+// ----------------------------------------------------------------------------- distillation divergences
+// Per row, with p_s = softmax(student), p_t = softmax(teacher) over V columns (fp32 math on bf16 logits):
+//   forward KL term   F = −Σ p_t · log p_s          d F / d s_j = p_s(j) − p_t(j)
+//   reverse KL        R =  Σ p_s · (log p_s − log p_t)   d R / d s_j = p_s(j) · ((log p_s(j) − log p_t(j)) − R)
+// loss_out[row] = w_fwd · F + w_rev · R, grad[row, :] = the same combination of the two gradients (bf16; may alias nothing).
+// Columns whose student logit is ±inf contribute nothing (the reference masks them, torchtune/modules/loss/kd_losses.py:54-60,
+// 129-140); rows whose label equals ignore_index give loss 0 and a zero gradient row.
+static constexpr int kKDThreads = 512;
+
+__device__ __forceinline__ float kd_block_sum(float v, float* scratch) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int w = 0; w < kKDThreads / 32; ++w) t += scratch[w];
+  return t;
+}
+__device__ __forceinline__ float kd_block_max(float v, float* scratch) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = -INFINITY;
+  for (int w = 0; w < kKDThreads / 32; ++w) t = fmaxf(t, scratch[w]);
+  return t;
+}
+
+__global__ void __launch_bounds__(kKDThreads)
+kd_divergence_kernel(const __nv_bfloat16* __restrict__ student, const __nv_bfloat16* __restrict__ teacher, const long long* __restrict__ labels,
+                     float* __restrict__ loss_out, __nv_bfloat16* __restrict__ grad, int rows, int V, long long ld_s, long long ld_t, long long ld_g,
+                     long long ignore_index, float w_fwd, float w_rev) {
+  __shared__ float scratch[kKDThreads / 32];
+  const int row = blockIdx.x;
+  if (row >= rows) return;
+  const int nvec = V >> 3;
+  const uint4* sr = reinterpret_cast<const uint4*>(student + static_cast<long long>(row) * ld_s);
+  const uint4* tr = reinterpret_cast<const uint4*>(teacher + static_cast<long long>(row) * ld_t);
+  uint4* gr = grad != nullptr ? reinterpret_cast<uint4*>(grad + static_cast<long long>(row) * ld_g) : nullptr;
+  if (labels[row] == ignore_index) {
+    if (gr != nullptr) {
+      const uint4 z = make_uint4(0, 0, 0, 0);
+      for (int i = threadIdx.x; i < nvec; i += kKDThreads) gr[i] = z;
+    }
+    if (threadIdx.x == 0) loss_out[row] = 0.f;
+    return;
+  }
+  auto unpack = [](const uint4& u, float (&f)[8]) {
+    const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 t = __bfloat1622float2(b[j]);
+      f[2 * j] = t.x, f[2 * j + 1] = t.y;
+    }
+  };
+  // pass 1: row maxima (finite values only for the student, whose ±inf columns are masked out)
+  float ms = -INFINITY, mt = -INFINITY;
+  for (int i = threadIdx.x; i < nvec; i += kKDThreads) {
+    float a[8], b[8];
+    unpack(sr[i], a);
+    unpack(tr[i], b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (!isinf(a[j])) ms = fmaxf(ms, a[j]);
+      mt = fmaxf(mt, b[j]);
+    }
+  }
+  ms = kd_block_max(ms, scratch);
+  mt = kd_block_max(mt, scratch);
+  // pass 2: partition sums and the two cross terms
+  float zs = 0.f, zt = 0.f, c_fwd = 0.f, c_rev = 0.f;
+  for (int i = threadIdx.x; i < nvec; i += kKDThreads) {
+    float a[8], b[8];
+    unpack(sr[i], a);
+    unpack(tr[i], b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float et = __expf(b[j] - mt);
+      zt += et;
+      if (isinf(a[j])) {
+        if (a[j] > 0.f) zs = INFINITY;  // +inf student logit: the softmax is degenerate, as in the eager statement
+        continue;
+      }
+      const float ds = a[j] - ms;
+      const float es = __expf(ds);
+      zs += es;
+      c_fwd += et * ds;
+      if (!isinf(b[j])) c_rev += es * ((b[j] - mt) - ds);
+    }
+  }
+  zs = kd_block_sum(zs, scratch);
+  zt = kd_block_sum(zt, scratch);
+  c_fwd = kd_block_sum(c_fwd, scratch);
+  c_rev = kd_block_sum(c_rev, scratch);
+  const float log_zs = __logf(zs), log_zt = __logf(zt);
+  // Σ p_t log p_s over unmasked columns needs the teacher mass on those columns; with no masked column it is exactly 1
+  float pt_mass = 0.f;
+  if (w_fwd != 0.f) {
+    for (int i = threadIdx.x; i < nvec; i += kKDThreads) {
+      float a[8], b[8];
+      unpack(sr[i], a);
+      unpack(tr[i], b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (!isinf(a[j])) pt_mass += __expf(b[j] - mt);
+    }
+    pt_mass = kd_block_sum(pt_mass, scratch) / zt;
+  }
+  const float fwd = -(c_fwd / zt - log_zs * pt_mass);          // −Σ p_t log p_s
+  const float rev = -(c_rev / zs - (log_zt - log_zs));          // Σ p_s (log p_s − log p_t)
+  if (threadIdx.x == 0) loss_out[row] = w_fwd * fwd + w_rev * rev;
+  if (gr == nullptr) return;
+  for (int i = threadIdx.x; i < nvec; i += kKDThreads) {
+    float a[8], b[8], g[8];
+    unpack(sr[i], a);
+    unpack(tr[i], b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (isinf(a[j])) {
+        g[j] = 0.f;
+        continue;
+      }
+      const float lps = a[j] - ms - log_zs, lpt = b[j] - mt - log_zt;
+      const float ps = __expf(lps), pt = __expf(lpt);
+      float v = w_fwd * (ps * pt_mass - pt);
+      if (w_rev != 0.f) v += w_rev * ps * ((isinf(b[j]) ? 0.f : (lps - lpt)) - rev);
+      g[j] = v;
+    }
+    uint4 u;
+    __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) ob[j] = __floats2bfloat162_rn(g[2 * j], g[2 * j + 1]);
+    gr[i] = u;
+  }
+}
+
 }  // namespace ttb
 
 using namespace ttb;
@@ -120,5 +262,19 @@ extern "C" int ttb_softmax_ce(void* logits, const long long* labels, float* loss
   TTB_COUNT_LAUNCH(1);
   softmax_ce_kernel<<<rows, kCEThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<__nv_bfloat16*>(logits), labels, loss_out, row_scale, rows, V, ld, ignore_index, mode);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrDriver;
+}
+
+
+// student, teacher: [rows, V] bf16 (row pitches ld_s / ld_t, multiples of 8); labels: [rows] int64; loss_out: [rows] fp32;
+// grad: [rows, V] bf16 (pitch ld_g) or null.  loss = w_fwd · forward-KL term + w_rev · reverse KL per row (see the kernel).
+extern "C" int ttb_kd_divergence(const void* student, const void* teacher, const long long* labels, float* loss_out, void* grad, int rows, int V, long long ld_s,
+                                 long long ld_t, long long ld_g, long long ignore_index, float w_fwd, float w_rev, void* stream) {
+  if ((V & 7) || (ld_s & 7) || (ld_t & 7) || (grad != nullptr && (ld_g & 7))) return kErrBadShape;
+  if (rows <= 0) return kOk;
+  TTB_COUNT_LAUNCH(1);
+  kd_divergence_kernel<<<rows, kKDThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(student), static_cast<const __nv_bfloat16*>(teacher), labels, loss_out, static_cast<__nv_bfloat16*>(grad), rows, V, ld_s, ld_t,
+      ld_g, ignore_index, w_fwd, w_rev);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrDriver;
 }

@@ -90,3 +90,47 @@ def test_expert_parallel_single_rank_and_bounded_capacity():
     # a bounded capacity keeps the buffers small; with world 1 nothing can overflow, the result is unchanged
     ep2 = ExpertParallelContext(torch.device("cpu"), num_experts=E, dim=DIM, max_pairs=TOK * K, capacity_factor=4.0)
     torch.testing.assert_close(ExpertParallelMoE(_moe(), ep2)(x), want, rtol=1e-5, atol=1e-6)
+
+
+def _layerwise_worker(rank, world, port, results):
+    import weakref
+
+    from torchtune_b200 import parallel as par
+    from torchtune_b200 import training
+    from torchtune_b200.models.llama4 import llama4_decoder
+    from torchtune_b200.modules.moe import GroupedExperts
+    from torchtune_b200.training import _distributed as td
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        cfg = {"expert_parallel_dim": 2, "batch_size": 1}
+        strategy = par.ParallelStrategy(cfg, torch.device("cpu"))
+        with training.set_default_dtype(torch.float32), torch.device("meta"):
+            model = llama4_decoder(vocab_size=64, num_layers=4, num_heads=2, num_kv_heads=1, embed_dim=16, hidden_dim=24, max_seq_len=32, num_experts=4)
+        seen, alive_before = [], []
+        original = td.LayerwisePreparer.__call__
+
+        def counting(self, module, prefix=""):
+            # full-size expert stacks of the layers prepared so far that are still alive when the next layer gets its storage
+            alive_before.append(sum(1 for r in seen if r() is not None and not any(p.is_meta for p in r().parameters())))
+            out = original(self, module, prefix)
+            seen.extend(weakref.ref(m) for m in module.modules() if isinstance(m, GroupedExperts) and m.num_experts == 4)
+            return out
+
+        td.LayerwisePreparer.__call__ = counting
+        try:
+            strategy.shard_model(model, cfg, None)
+        finally:
+            td.LayerwisePreparer.__call__ = original
+        results[rank] = max(alive_before)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_layerwise_expert_sharding_keeps_no_full_expert_stack_alive():
+    """While a meta-device MoE model is cut into expert-parallel shards layer by layer, the full expert stacks of an earlier
+    layer must be gone before the next layer gets storage (a 109B model never exists in full on one GPU)."""
+    results = mp.Manager().dict()
+    mp.spawn(_layerwise_worker, args=(2, 29615, results), nprocs=2, join=True)
+    assert results[0] == 0 and results[1] == 0

@@ -317,9 +317,14 @@ def expert_parallelize(model: nn.Module, ep: ExpertParallelContext, replica_grou
         # a model still on the meta device: every decoder layer gets storage and values (``prepare_layer(module, prefix)``, e.g.
         # training.LayerwisePreparer) right before its experts are cut down to this rank's, so the full expert stacks of at most
         # one layer are alive at a time
+        import gc
+
         for i, layer in enumerate(model.layers):
             prepare_layer(layer, f"layers.{i}.")
             swap(layer)
+            # the replaced MoE module (with the full expert stacks of this layer, 4 GB for a Scout layer) can sit in a reference
+            # cycle; without a collection here the stacks of all layers pile up until the allocator runs out
+            gc.collect()
         for name, child in model.named_children():
             if name != "layers":
                 prepare_layer(child, f"{name}.")

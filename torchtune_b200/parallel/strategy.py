@@ -285,11 +285,15 @@ class ParallelStrategy(DataParallelEngine):
         from ..modules.moe import MoE
         from .ep import ExpertParallelContext, expert_parallelize
 
-        moes = [m for m in model.modules() if isinstance(m, MoE)]
-        if not moes:
+        first = next((m for m in model.modules() if isinstance(m, MoE)), None)
+        if first is None:
             raise ValueError("expert_parallel_dim > 1 needs a model with MoE layers")
         get = cfg.get if hasattr(cfg, "get") else (lambda k, d=None: d)
-        router = moes[0].router
+        router = first.router
+        # no reference to a MoE module may survive into expert_parallelize: it would keep that layer's full expert stacks alive
+        # after they have been cut down to this rank's experts (4 GB per Scout layer)
+        num_experts, router_dim, experts_per_token = router.num_experts, router.dim, router.experts_per_token
+        del first, router
         tokens = self._tp_max_rows(cfg, model) * max(self.dims.tp, 1)
         ep, replicas = self.ep_dim, self.world // self.ep_dim
         ep_group = replica_group = None
@@ -306,7 +310,7 @@ class ParallelStrategy(DataParallelEngine):
                 handle = dist.new_group(ranks)
                 if self.rank in ranks:
                     replica_group = handle
-        self.ep = ExpertParallelContext(self.device, ep_group, num_experts=router.num_experts, dim=router.dim, max_pairs=tokens * router.experts_per_token,
+        self.ep = ExpertParallelContext(self.device, ep_group, num_experts=num_experts, dim=router_dim, max_pairs=tokens * experts_per_token,
                                         capacity_factor=get("expert_capacity_factor"))
         self._replica_group = replica_group
         return expert_parallelize(model, self.ep, replica_group, replicas, prepare_layer=prepare_layer)

@@ -1087,3 +1087,50 @@ def test_kd_divergence_kernel_matches_fp32_statement(kind):
         assert abs(got.item() - want.item()) < 2e-3 * max(1.0, abs(want.item())), (kind, got.item(), want.item())
         _close(student.grad, s32.grad, 2e-2, 2e-2 * s32.grad.abs().max().item(), f"kd {kind} grad")
         assert (student.grad[::5] == 0).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("top_k", [None, 1, 50, 300])
+def test_sampling_kernel_matches_the_eager_statement(dtype, top_k):
+    from torchtune_b200 import generation
+
+    g = torch.Generator(device="cuda").manual_seed(7)
+    logits = (torch.randn(6, 4099, generator=g, device="cuda") * 3).to(dtype)
+    logits[0, 17] = logits[0].max() + 5  # a dominant token
+    u = torch.rand(6, 4099, generator=g, device="cuda")
+    q = -torch.log(torch.clamp(1.0 - u, min=1e-7))
+    got = generation.sample(logits.clone(), temperature=0.7, top_k=top_k, q=q)
+    assert got.shape == (6, 1) and got.dtype == torch.int32
+    # the eager statement in fp32 on the same scaled logits (bf16 logits are divided in bf16, as the eager statement does)
+    t = (logits / 0.7).float()
+    if top_k is not None:
+        kth = torch.topk(t, top_k).values[:, -1:]
+        t = torch.where(t < kth, torch.full_like(t, float("-inf")), t)
+    race = torch.softmax(t, dim=-1) / q
+    picked = race.gather(1, got.long())
+    assert (picked >= race.max(-1, keepdim=True).values * (1 - 1e-4)).all()  # the winner of the race, up to fp32 rounding of near-ties
+    assert torch.isfinite(t.gather(1, got.long())).all()  # always a kept column
+    with ops.use_reference_ops():
+        want = generation.sample(logits.clone(), temperature=0.7, top_k=top_k, q=q)
+    assert (got.long() == want.long()).float().mean() >= (1.0 if dtype == torch.float32 else 0.5)
+    if top_k == 1:
+        assert torch.equal(got.long(), logits.float().argmax(-1, keepdim=True))
+
+
+@pytest.mark.parametrize("temperature", [1.0, 0.7])
+def test_logits_to_logprobs_fused_matches_fp32(temperature):
+    from torchtune_b200 import rlhf
+
+    logits = _rand(3, 17, 2048, seed=51, scale=2.0).requires_grad_()
+    tokens = torch.randint(0, 2048, (3, 17), device="cuda")
+    got = rlhf.logits_to_logprobs(logits, tokens, temperature)
+    assert got.dtype == torch.float32 and got.shape == (3, 17)
+    w = torch.randn(3, 17, device="cuda")
+    (got * w).sum().backward()
+    l32 = logits.detach().float().requires_grad_()
+    want = rlhf.logits_to_logprobs(l32, tokens, temperature)
+    (want * w).sum().backward()
+    _close(got, want, 2e-2, 2e-2, "logprobs")
+    _close(logits.grad, l32.grad, 2e-2, 2e-2 * l32.grad.abs().max().item(), "logprobs grad")
+    with torch.no_grad():
+        _close(rlhf.logits_to_logprobs(logits, tokens, temperature), want, 2e-2, 2e-2, "logprobs (no grad)")

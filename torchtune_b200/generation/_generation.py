@@ -21,6 +21,14 @@ def _exponential_like(shape, device, rng: Optional[torch.Generator] = None) -> t
 
 def sample(logits: torch.Tensor, *, temperature: float = 1.0, top_k: Optional[int] = None, q: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Temperature + optional top-k, then one draw per row; returns ``[..., 1]`` int tokens."""
+    if logits.is_cuda:
+        from .. import ops
+
+        qq = q if q is not None else _exponential_like(logits.shape, logits.device)
+        tokens = ops.sample_tokens(logits, qq.float() if qq.dtype != torch.float32 else qq, temperature, top_k)
+        if tokens is not None:
+            return tokens
+        q = qq
     logits = logits / max(temperature, 1e-5)
     if top_k is not None:
         kth = torch.topk(logits, min(top_k, logits.size(-1))).values[..., -1:]

@@ -274,6 +274,33 @@ def token_logprobs(
     return reference.token_logprobs(hidden, weight, labels, ignore_index, num_chunks)
 
 
+def logits_logprobs(logits: torch.Tensor, tokens: torch.Tensor, temperature: float = 1.0) -> Optional[torch.Tensor]:
+    """``log_softmax(logits / T)`` gathered at ``tokens`` (fp32, shape of ``tokens``) for bf16 CUDA logits whose vocabulary width is a
+    multiple of 8, without an fp32 ``[..., V]`` intermediate; ``None`` otherwise."""
+    if not (_native(logits) and logits.shape[-1] % 8 == 0 and tokens.is_cuda and tokens.dtype == torch.int64 and logits.shape[:-1] == tokens.shape and logits.numel() > 0):
+        return None
+    from . import _cuda
+
+    return _cuda.logits_logprobs(logits, tokens, temperature)
+
+
+def sample_tokens(logits: torch.Tensor, q: torch.Tensor, temperature: float, top_k: Optional[int]) -> Optional[torch.Tensor]:
+    """Fused temperature / top-k / exponential-race draw for CUDA logits (``[..., V]`` bf16 or fp32, ``q`` fp32 of the same shape);
+    int32 tokens ``[..., 1]``, or ``None`` when the inputs do not qualify."""
+    if not (logits.is_cuda and logits.dtype in (torch.bfloat16, torch.float32) and q.is_cuda and q.dtype == torch.float32 and q.shape == logits.shape
+            and logits.dim() >= 1 and logits.numel() > 0 and not _FORCE_REFERENCE):
+        return None
+    from . import _cuda
+
+    V = logits.shape[-1]
+    l2, q2 = logits.reshape(-1, V), q.reshape(-1, V)
+    if l2.stride(1) != 1:
+        l2 = l2.contiguous()
+    if q2.stride(1) != 1:
+        q2 = q2.contiguous()
+    return _cuda.sample(l2, q2, temperature, top_k).view(*logits.shape[:-1], 1)
+
+
 def kd_divergence(student_logits: torch.Tensor, teacher_logits: torch.Tensor, labels: torch.Tensor, w_fwd: float, w_rev: float,
                   ignore_index: int = -100) -> Optional[torch.Tensor]:
     """Summed distillation divergence ``w_fwd · forward-KL term + w_rev · reverse KL`` over the rows whose label is not

@@ -896,6 +896,50 @@ def rms_norm(x: torch.Tensor, scale: Optional[torch.Tensor], eps: float) -> torc
     return _RMSNorm.apply(x, scale, eps)
 
 
+# ======================================================================= log-probabilities of given tokens from logits
+class _LogitsLogprobs(torch.autograd.Function):
+    """``log_softmax(logits / T)[token]`` per row through the cross-entropy kernel: the only [rows, V] tensor is one bf16 copy of the
+    scaled logits, which the kernel overwrites with ``softmax − onehot`` for the backward pass."""
+
+    @staticmethod
+    def forward(ctx, logits2d, tokens, temperature: float):
+        rows, V = logits2d.shape
+        need_grad = logits2d.requires_grad
+        scaled = (logits2d / temperature) if temperature != 1.0 else (logits2d.clone() if need_grad else logits2d)
+        if not scaled.is_contiguous():
+            scaled = scaled.contiguous()
+        loss_rows = torch.empty(rows, dtype=torch.float32, device=logits2d.device)
+        check(lib().ttb_softmax_ce(scaled.data_ptr(), tokens.data_ptr(), loss_rows.data_ptr(), None, rows, V, scaled.stride(0), -(1 << 62), 0 if need_grad else 1, stream_ptr()),
+              "softmax_ce (log-probabilities)")
+        ctx.temperature = temperature
+        ctx.save_for_backward(scaled if need_grad else None)
+        return -loss_rows
+
+    @staticmethod
+    def backward(ctx, g):
+        (grad,) = ctx.saved_tensors
+        if grad is None:
+            return None, None, None
+        return grad * (-g / ctx.temperature).to(grad.dtype).unsqueeze(-1), None, None
+
+
+def logits_logprobs(logits: torch.Tensor, tokens: torch.Tensor, temperature: float) -> torch.Tensor:
+    V = logits.shape[-1]
+    out = _LogitsLogprobs.apply(logits.reshape(-1, V), tokens.reshape(-1).contiguous(), float(temperature))
+    return out.view(tokens.shape)
+
+
+# ======================================================================= sampling
+def sample(logits: torch.Tensor, q: torch.Tensor, temperature: float, top_k: Optional[int]) -> torch.Tensor:
+    """One token per row of ``logits`` (``[rows, V]``, bf16 or fp32): temperature, optional top-k and the exponential-race draw
+    ``argmax(softmax(logits / T) / q)`` in one kernel; ``q``: fp32 ``[rows, V]`` draws from Exp(1).  Returns int32 ``[rows]``."""
+    rows, V = logits.shape
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    check(lib().ttb_sample(logits.data_ptr(), logits.stride(0), int(logits.dtype == _BF16), q.data_ptr(), q.stride(0), out.data_ptr(), rows, V, float(temperature),
+                           int(top_k or 0), stream_ptr()), "sample")
+    return out
+
+
 # ======================================================================= distillation divergences
 class _KDDivergence(torch.autograd.Function):
     """Sum over rows of ``w_fwd · (−Σ p_t log p_s) + w_rev · Σ p_s (log p_s − log p_t)`` for bf16 ``[rows, V]`` student / teacher logits;

@@ -48,6 +48,8 @@ def _declare(L: ctypes.CDLL) -> None:
     L.ttb_rope.argtypes = [vp, vp, vp, vp, i64, i32, i32, i32, i32, i32, i32, vp]
     L.ttb_kd_divergence.argtypes = [vp, vp, vp, vp, vp, i32, i32, i64, i64, i64, i64, f32, f32, vp]
     L.ttb_kd_divergence.restype = i32
+    L.ttb_sample.argtypes = [vp, i64, i32, vp, i64, vp, i32, i32, f32, i32, vp]
+    L.ttb_sample.restype = i32
     L.ttb_index_violations.argtypes = [i32]
     L.ttb_index_violations.restype = ctypes.c_uint32
     L.ttb_swiglu_fwd.argtypes = [vp, vp, vp, i64, i32, i64, i64, i64, vp]

@@ -21,7 +21,12 @@ def truncate_sequence_at_first_stop_token(sequences: torch.Tensor, stop_tokens: 
 
 
 def logits_to_logprobs(logits: torch.Tensor, sequences: torch.Tensor, temperature: float = 1.0) -> torch.Tensor:
-    """``log_softmax(logits / T)`` gathered at ``sequences`` → ``[b, s]``."""
+    """``log_softmax(logits / T)`` gathered at ``sequences`` → ``[b, s]`` (bf16 CUDA logits: fused kernel, fp32 result)."""
+    from .. import ops
+
+    fused = ops.logits_logprobs(logits, sequences, temperature)
+    if fused is not None:
+        return fused
     return torch.gather(F.log_softmax(logits / temperature, dim=-1), 2, sequences.unsqueeze(-1)).squeeze(-1)
 
 

@@ -5,6 +5,7 @@
     python -m torchtune_b200.ops.microbench rmsnorm --rows 8192 --dim 4096
     python -m torchtune_b200.ops.microbench adamw --numel 268435456
     python -m torchtune_b200.ops.microbench gate_up --tokens 8192 --dim 4096 --hidden 14336
+    python -m torchtune_b200.ops.microbench comm --world 8 --numel 268435456             (peer-memory kernels, ranks emulated on one GPU)
     python -m torchtune_b200.ops.microbench suite --tokens 8192      (norm, RoPE, SwiGLU, loss, embedding, LoRA, grouped GEMM, NF4, offload copies)
 
 Each command prints one JSON line: median milliseconds over ``--iters`` launches (an L2 flush
@@ -209,6 +210,45 @@ def bench_gate_up(args, flush):
     return out
 
 
+def bench_comm(args, flush):
+    """The two peer-memory communication kernels with every rank's buffers on this one GPU (no peer sits behind NVLink here, so the
+    figures are the kernels' own HBM efficiency): the fused reduce → AdamW → broadcast bucket kernel of rank 0 over ``--world``
+    gradient / parameter buffers, its reduce-scatter → AdamW form (no broadcast: the ZeRO-3 update) and the ZeRO-3 bucket gather."""
+    import ctypes
+    import math
+
+    from ..parallel.dp import _declare_dp
+    from ._lib import check, lib, stream_ptr
+
+    L = lib()
+    _declare_dp(L)
+    world, shard = args.world, args.numel // args.world // 8 * 8
+    total = shard * world
+    params = [torch.randn(total, device="cuda", dtype=torch.bfloat16) * 0.1 for _ in range(world)]
+    grads = [torch.randn(total, device="cuda", dtype=torch.bfloat16) for _ in range(world)]
+    m, v = torch.zeros(shard, device="cuda", dtype=torch.bfloat16), torch.zeros(shard, device="cuda", dtype=torch.bfloat16)
+    gp = (ctypes.c_void_p * world)(*[t.data_ptr() for t in grads])
+    pp = (ctypes.c_void_p * world)(*[t.data_ptr() for t in params])
+
+    def update(bcast):
+        check(L.ttb_dp_reduce_adamw_bcast(gp, pp, world, 0, 0, shard, m.data_ptr(), v.data_ptr(), None, None, None, 1.0, 1e-4, 0.9, 0.999, 1e-8, 0.01, 10.0, 1.0 / math.sqrt(1 - 0.999), 0,
+                                          None, 0, 0, None, 0, int(bcast), 0, stream_ptr()), "dp kernel")
+
+    out = {"op": "comm", "world": world, "shard_numel": shard}
+    t = _time(lambda: update(True), args.iters, args.warmup, flush)
+    nbytes = shard * 2 * (world + 3 + 2 + world)  # gradient rows of all ranks, own parameter + moments read; moments + parameter copies of all ranks written
+    out["reduce_adamw_bcast_ms"], out["reduce_adamw_bcast_gbs"] = t, nbytes / t / 1e6
+    t = _time(lambda: update(False), args.iters, args.warmup, flush)
+    nbytes = shard * 2 * (world + 3 + 3)
+    out["reduce_scatter_adamw_ms"], out["reduce_scatter_adamw_gbs"] = t, nbytes / t / 1e6
+    dst = torch.empty(total, device="cuda", dtype=torch.bfloat16)
+    shards = [p[:shard] for p in params]
+    sp = (ctypes.c_void_p * world)(*[t_.data_ptr() for t_ in shards])
+    t = _time(lambda: check(L.ttb_zero3_gather(sp, world, 0, shard, dst.data_ptr(), None, 0, 0, None, 0, stream_ptr()), "gather"), args.iters, args.warmup, flush)
+    out["zero3_gather_ms"], out["zero3_gather_gbs"] = t, 2 * total * 2 / t / 1e6
+    return out
+
+
 def bench_suite(args, flush):
     """The memory-bound and fused operators of one Llama-3.1-8B training step (``--tokens`` rows, width 4096, MLP 14336,
     vocabulary 128256) and of a Llama-4-Scout MoE layer (16 experts, 5120 → 8192), each against the PyTorch library expression of
@@ -384,13 +424,16 @@ def main() -> None:
     gu.add_argument("--tokens", type=int, default=8192)
     gu.add_argument("--dim", type=int, default=4096)
     gu.add_argument("--hidden", type=int, default=14336)
+    co = sub.add_parser("comm")
+    co.add_argument("--world", type=int, default=8)
+    co.add_argument("--numel", type=int, default=1 << 28)
     su = sub.add_parser("suite")
     su.add_argument("--tokens", type=int, default=8192)
     args = ap.parse_args()
     from ._lib import check_device_errors
 
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
-    fn = {"gemm": bench_gemm, "gemm_fp8": bench_gemm_fp8, "gemm_mxfp8": bench_gemm_mxfp8, "attention": bench_attention, "rmsnorm": bench_rmsnorm, "adamw": bench_adamw, "gate_up": bench_gate_up, "suite": bench_suite}[args.op]
+    fn = {"gemm": bench_gemm, "gemm_fp8": bench_gemm_fp8, "gemm_mxfp8": bench_gemm_mxfp8, "attention": bench_attention, "rmsnorm": bench_rmsnorm, "adamw": bench_adamw, "gate_up": bench_gate_up, "comm": bench_comm, "suite": bench_suite}[args.op]
     res = fn(args, flush)
     check_device_errors()
     print(json.dumps(res), flush=True)

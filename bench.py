@@ -64,6 +64,14 @@ class ClockSampler:
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
+            return
+        # nvidia-smi needs a moment to attach to the driver; during that time kernel launches of this process can stall.  The timed
+        # region starts only once the first sample has arrived (the device is idle here: the caller has just synchronised), and the
+        # samples taken before that are dropped.
+        deadline = time.time() + 15.0
+        while not self.rows and time.time() < deadline and self.proc.poll() is None:
+            time.sleep(0.02)
+        self.rows.clear()
 
     def _read(self) -> None:
         for line in self.proc.stdout:

@@ -1134,3 +1134,42 @@ def test_logits_to_logprobs_fused_matches_fp32(temperature):
     _close(logits.grad, l32.grad, 2e-2, 2e-2 * l32.grad.abs().max().item(), "logprobs grad")
     with torch.no_grad():
         _close(rlhf.logits_to_logprobs(logits, tokens, temperature), want, 2e-2, 2e-2, "logprobs (no grad)")
+
+
+@pytest.mark.parametrize("M,N,K", [(8192, 4096, 1024), (4100, 6152, 512), (256, 512, 256)])  # the last one is too small for the CTA-pair kernel
+def test_linear_residual_adds_in_the_epilogue(M, N, K):
+    x = _rand(M, K, seed=61, scale=0.5).requires_grad_()
+    w = _rand(N, K, seed=62, scale=0.05).requires_grad_()
+    bias = _rand(N, seed=63, scale=0.2).requires_grad_()
+    res = _rand(M, N, seed=64).requires_grad_()
+    y = ops.linear_residual(x, w, bias, res)
+    gy = _rand(M, N, seed=65)
+    y.backward(gy)
+    xr, wr, br, rr = (t.detach().float().requires_grad_() for t in (x, w, bias, res))
+    yr = torch.nn.functional.linear(xr, wr, br) + rr
+    yr.backward(gy.float())
+    _close(y, yr, 2e-2, 2e-2, "linear_residual fwd")
+    _close(res.grad, rr.grad, 0, 0, "linear_residual d residual")
+    _close(x.grad, xr.grad, 2e-2, 5e-2, "linear_residual dx")
+    _close(w.grad, wr.grad, 2e-2, 1.0, "linear_residual dw")
+
+
+def test_decoder_layer_with_fused_residuals_matches_separate_additions(monkeypatch):
+    from torchtune_b200.models.llama3_1 import llama3_1
+
+    torch.manual_seed(0)
+    model = llama3_1(vocab_size=512, num_layers=2, num_heads=8, num_kv_heads=2, embed_dim=1024, max_seq_len=2048, intermediate_dim=4096).cuda().bfloat16()
+    tokens = torch.randint(0, 512, (4, 2048), device="cuda")
+
+    def run():
+        model.zero_grad(set_to_none=True)
+        out = model(tokens)
+        out.float().square().mean().backward()
+        return out.detach().clone(), model.layers[0].attn.q_proj.weight.grad.detach().clone()
+
+    assert model.layers[0]._fuse_residual_attn and model.layers[0]._fuse_residual_mlp
+    fused_out, fused_grad = run()
+    monkeypatch.setenv("TTB_FUSE_RESIDUAL", "0")
+    plain_out, plain_grad = run()
+    _close(fused_out, plain_out, 2e-2, 2e-2 * plain_out.abs().max().item(), "fused residual forward")
+    _close(fused_grad, plain_grad, 5e-2, 5e-2 * plain_grad.abs().max().item(), "fused residual backward")

@@ -105,7 +105,10 @@ class MultiHeadAttention(nn.Module):
         *,
         mask: MaskLike = None,
         input_pos: Optional[torch.Tensor] = None,
+        residual: Optional[torch.Tensor] = None,
     ) -> torch.Tensor:
+        """``residual``: a tensor of the output's shape that is added to the result; with a plain output projection the addition
+        happens in that projection's GEMM epilogue (a decoder layer passes its residual stream)."""
         b, s_x, _ = x.shape
         q = self.q_proj(x).view(b, s_x, self.num_heads, self.head_dim)
         if self.q_norm is not None and self.qk_norm_before_rope:
@@ -148,4 +151,9 @@ class MultiHeadAttention(nn.Module):
         )
         if cp is not None and plain:
             out = cp.heads_to_seq(out)
-        return self.output_proj(out.reshape(b, s_x, self.num_heads * self.head_dim))
+        out = out.reshape(b, s_x, self.num_heads * self.head_dim)
+        if residual is None:
+            return self.output_proj(out)
+        if type(self.output_proj) is nn.Linear:
+            return ops.linear_residual(out, self.output_proj.weight, self.output_proj.bias, residual)
+        return self.output_proj(out) + residual

@@ -50,11 +50,29 @@ class TransformerSelfAttentionLayer(nn.Module):
     def reset_cache(self) -> None:
         self.attn.reset_cache()
 
+    @property
+    def _fuse_residual_attn(self) -> bool:
+        # exact types only: converted or derived modules (tensor-parallel attention, adapters on the whole block) keep the plain path
+        return type(self.sa_scale) is nn.Identity and type(self.attn) is MultiHeadAttention
+
+    @property
+    def _fuse_residual_mlp(self) -> bool:
+        from .feed_forward import FeedForward
+
+        return type(self.mlp_scale) is nn.Identity and type(self.mlp) is FeedForward
+
     def forward(self, x: torch.Tensor, *, mask: MaskLike = None, input_pos: Optional[torch.Tensor] = None, **kwargs) -> torch.Tensor:
         if self.mask_mod is not None:
             mask = self.mask_mod(mask, x.shape[0], x.shape[1])
         normed = self.sa_norm(x)
-        h = self.sa_scale(self.attn(normed, normed, mask=mask, input_pos=input_pos)) + x
+        # Without layer scales the two residual additions ride in the epilogues of the attention output projection and of the MLP down
+        # projection (modules that take a ``residual`` argument); otherwise they are separate additions.
+        if self._fuse_residual_attn:
+            h = self.attn(normed, normed, mask=mask, input_pos=input_pos, residual=x)
+        else:
+            h = self.sa_scale(self.attn(normed, normed, mask=mask, input_pos=input_pos)) + x
+        if self._fuse_residual_mlp:
+            return self.mlp(self.mlp_norm(h), residual=h)
         return h + self.mlp_scale(self.mlp(self.mlp_norm(h)))
 
 

@@ -29,6 +29,7 @@ __all__ = [
     "mxfp8_linear",
     "matmul",
     "linear",
+    "linear_residual",
     "rms_norm",
     "rope",
     "swiglu",
@@ -103,6 +104,16 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
             return y[..., :n]
         _fallback("linear", f"K={x.shape[-1]} is not a multiple of 8 (TMA row pitch)", x)
     return F.linear(x, weight, bias)
+
+
+def linear_residual(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], residual: torch.Tensor) -> torch.Tensor:
+    """``x @ weight.T (+ bias) + residual``; bf16 CUDA inputs add the residual in the GEMM epilogue (no separate element-wise pass)."""
+    if (_native(x) and weight.dtype == torch.bfloat16 and residual.dtype == torch.bfloat16 and residual.is_cuda and x.shape[-1] % 8 == 0 and weight.shape[0] % 8 == 0
+            and residual.shape == (*x.shape[:-1], weight.shape[0]) and os.environ.get("TTB_FUSE_RESIDUAL", "1") != "0"):
+        from . import _cuda
+
+        return _cuda.linear_residual(x, weight, bias, residual)
+    return linear(x, weight, bias) + residual
 
 
 def fp8_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, rowwise: bool = False) -> Optional[torch.Tensor]:

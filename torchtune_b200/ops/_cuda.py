@@ -130,6 +130,56 @@ def gemm_skinny(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: b
     return out.to(_BF16)
 
 
+def gemm_residual(a: torch.Tensor, b: torch.Tensor, residual: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``a[M, K] · b[N, K]ᵀ (+ bias) + residual[M, N]`` with the addition in the GEMM epilogue (CTA-pair kernel); problems too small for that
+    kernel run the plain GEMM followed by an add."""
+    def ok(t):
+        return t if (t.stride(1) == 1 and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0) else t.contiguous()
+
+    a, b, residual = ok(a), ok(b), ok(residual)
+    M, K = a.shape
+    N = b.shape[0]
+    out = torch.empty(M, N, dtype=_BF16, device=a.device)
+    if K % 8 == 0 and _use_pair_kernel(M, N, K, out):
+        rc = lib().ttb_gemm_bf16_2sm_residual(a.data_ptr(), b.data_ptr(), out.data_ptr(), residual.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0), residual.stride(0),
+                                              _ptr(bias), err_word(a.device).data_ptr(), stream_ptr())
+        check(rc, f"gemm_residual M={M} N={N} K={K}")
+        return out
+    return gemm(a, b, out=out, bias=bias).add_(residual)
+
+
+class _LinearResidual(torch.autograd.Function):
+    """``x @ Wᵀ (+ b) + residual``: the residual gradient is the incoming gradient itself, the other two as in :class:`_Linear`."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, residual):
+        x2 = x.reshape(-1, x.shape[-1])
+        ctx.save_for_backward(x2, weight)
+        ctx.has_bias = bias is not None
+        ctx.x_shape = x.shape
+        y = gemm_residual(x2, weight, residual.reshape(-1, weight.shape[0]), bias)
+        return y.view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if dy2.stride(1) != 1 or dy2.stride(0) % 8:
+            dy2 = dy2.contiguous()
+        dx = dw = db = None
+        if ctx.needs_input_grad[1]:
+            dw = _wgrad(weight, dy2, x2)
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, weight, b_mn=True).view(ctx.x_shape)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.sum(0)
+        return dx, dw, db, (dy if ctx.needs_input_grad[3] else None)
+
+
+def linear_residual(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], residual: torch.Tensor) -> torch.Tensor:
+    return _LinearResidual.apply(x, weight, bias, residual)
+
+
 class _Linear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias):

@@ -72,6 +72,8 @@ def _declare(L: ctypes.CDLL) -> None:
     L.ttb_gemm_bf16_dual.restype = i32
     L.ttb_gemm_bf16_dual_2sm.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i64, i64, i64, i64, i64, vp, f32, vp, vp]
     L.ttb_gemm_bf16_dual_2sm.restype = i32
+    L.ttb_gemm_bf16_2sm_residual.argtypes = [vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i64, vp, vp, vp]
+    L.ttb_gemm_bf16_2sm_residual.restype = i32
     L.ttb_gemm_bf16_splitk.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, i64, i64, i64, i32, f32, vp, vp]
     L.ttb_gemm_bf16_splitk.restype = i32
     L.ttb_gemm_grouped_wgrad_bf16.argtypes = [vp, vp, vp, vp, i64, i32, i32, i32, i64, i64, i64, i64, i32, vp, vp]

@@ -47,6 +47,8 @@ struct Params {
   void* C;
   long long ldc;
   const __nv_bfloat16* bias;
+  const __nv_bfloat16* residual;  // [M, N] (row pitch ldr) added to the product in the epilogue (the residual stream of a decoder layer), or null
+  long long ldr;
   float alpha;
   int accumulate;
   int tma_store;
@@ -368,6 +370,18 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 for (int i = 0; i < 8; ++i)
                   if (cb + i < p.N) f[i] += __bfloat162float(__ldg(p.bias + cb + i));
               }
+              if (p.residual != nullptr) {
+                const int cb = col0 + h * 32 + j * 8;
+                if (row < p.M && cb + 8 <= p.N) {
+                  const uint4 rq = __ldg(reinterpret_cast<const uint4*>(p.residual + static_cast<long long>(row) * p.ldr + cb));
+                  const __nv_bfloat162* rb = reinterpret_cast<const __nv_bfloat162*>(&rq);
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    const float2 t = __bfloat1622float2(rb[i]);
+                    f[2 * i] += t.x, f[2 * i + 1] += t.y;
+                  }
+                }
+              }
               uint4 o;
               o.x = pack_bf16x2(f[0], f[1]);
               o.y = pack_bf16x2(f[2], f[3]);
@@ -400,6 +414,21 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
               for (int i = 0; i < 32; ++i)
                 if (col0 + i < p.N) v[i] += __bfloat162float(__ldg(p.bias + col0 + i));
+            }
+            if (p.residual != nullptr) {
+              const __nv_bfloat16* rr = p.residual + static_cast<long long>(row) * p.ldr + col0;
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                if (col0 + g * 8 + 8 <= p.N) {
+                  const uint4 rq = __ldg(reinterpret_cast<const uint4*>(rr + g * 8));
+                  const __nv_bfloat162* rb = reinterpret_cast<const __nv_bfloat162*>(&rq);
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    const float2 t = __bfloat1622float2(rb[i]);
+                    v[g * 8 + 2 * i] += t.x, v[g * 8 + 2 * i + 1] += t.y;
+                  }
+                }
+              }
             }
             __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
 #pragma unroll
@@ -549,6 +578,7 @@ extern "C" int ttb_gemm_bf16_2sm(const void* A, const void* B, void* C, int M, i
   g2::Params p;
   p.M = M, p.N = N, p.K = K, p.C = C, p.ldc = ldc, p.bias = static_cast<const __nv_bfloat16*>(bias), p.alpha = alpha;
   p.accumulate = accumulate, p.tma_store = 0, p.save_gate_up = 0, p.tile_mult = 1, p.err = err, p.K2 = 0;
+  p.residual = nullptr, p.ldr = 0;
   p.group_m = g2::group_setting();
   auto s = static_cast<cudaStream_t>(stream);
   if (a_mn) return b_mn ? g2::launch<true, true, false>(A, B, nullptr, nullptr, nullptr, p, lda, ldb, s) : g2::launch<true, false, false>(A, B, nullptr, nullptr, nullptr, p, lda, ldb, s);
@@ -566,6 +596,7 @@ extern "C" int ttb_gemm_bf16_dual_2sm(const void* A, const void* B, const void* 
   if ((lda & 7) || (ldb & 7) || (lda2 & 7) || (ldb2 & 7) || (ldc & 7) || (N & 7) || (K & 7) || (K2 & 7)) return kErrBadShape;
   g2::Params p;
   p.M = M, p.N = N, p.K = K, p.K2 = K2, p.C = C, p.ldc = ldc, p.bias = static_cast<const __nv_bfloat16*>(bias), p.alpha = alpha;
+  p.residual = nullptr, p.ldr = 0;
   p.accumulate = 0, p.tma_store = 0, p.save_gate_up = 0, p.tile_mult = 1, p.err = err;
   p.group_m = g2::group_setting();
   auto s = static_cast<cudaStream_t>(stream);
@@ -584,7 +615,25 @@ extern "C" int ttb_gemm_swiglu_bf16_2sm(const void* X, const void* W1, const voi
   if ((gate_out == nullptr) != (up_out == nullptr)) return kErrBadShape;
   g2::Params p;
   p.M = M, p.N = N, p.K = K, p.C = H, p.ldc = ldc, p.bias = nullptr, p.alpha = 1.f;
+  p.residual = nullptr, p.ldr = 0;
   p.accumulate = 0, p.tma_store = 1, p.save_gate_up = 0, p.tile_mult = 1, p.err = err, p.K2 = 0;
   p.group_m = g2::group_setting();
   return g2::launch<false, false, true>(X, W1, W3, gate_out, up_out, p, lda, ldb, static_cast<cudaStream_t>(stream));
+}
+
+
+// C[M,N] = A[M,K] · B[N,K]ᵀ (+ bias) + R[M,N]: a linear layer whose output is added to the residual stream in the GEMM epilogue (the
+// attention output projection and the MLP down projection of a decoder layer, torchtune/modules/transformer.py:119-135), so the separate
+// element-wise add and its re-read of both tensors disappear.  R: bf16, row pitch ldr (multiple of 8), 16-byte aligned; R may not alias C.
+extern "C" int ttb_gemm_bf16_2sm_residual(const void* A, const void* B, void* C, const void* R, int M, int N, int K, long long lda, long long ldb, long long ldc,
+                                          long long ldr, const void* bias, int* err, void* stream) {
+  using namespace ttb;
+  if (M <= 0 || N <= 0 || K <= 0 || R == nullptr) return kErrBadShape;
+  if ((lda & 7) || (ldb & 7) || (ldc & 7) || (ldr & 7) || (N & 7) || (K & 7) || (reinterpret_cast<uintptr_t>(R) & 15)) return kErrBadShape;
+  g2::Params p;
+  p.M = M, p.N = N, p.K = K, p.K2 = 0, p.C = C, p.ldc = ldc, p.bias = static_cast<const __nv_bfloat16*>(bias), p.alpha = 1.f;
+  p.residual = static_cast<const __nv_bfloat16*>(R), p.ldr = ldr;
+  p.accumulate = 0, p.tma_store = 0, p.save_gate_up = 0, p.tile_mult = 1, p.err = err;
+  p.group_m = g2::group_setting();
+  return g2::launch<false, false, false>(A, B, nullptr, nullptr, nullptr, p, lda, ldb, static_cast<cudaStream_t>(stream));
 }

@@ -38,6 +38,12 @@ def test_sharded_parameters_two_gpus():
     assert "ZERO3_OK" in out
 
 
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_context_parallel_exchange_over_peer_memory_two_gpus():
+    out = _torchrun(str(ROOT / "tests" / "multi_gpu_cp_worker.py"), 2, 29577)
+    assert "CP_OK" in out
+
+
 def _tiny_ckpt(tmp_path):
     sys.path.insert(0, str(ROOT / "tests"))
     from helpers import write_tiny_hf_checkpoint

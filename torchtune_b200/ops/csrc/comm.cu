@@ -228,6 +228,43 @@ zero3_gather_kernel(ShardTable t, int rank, long long piece, __nv_bfloat16* __re
   }
 }
 
+// Context-parallel head / sequence exchange as a push over peer memory (the all-to-all around attention).
+//   mode 0 (sequence → heads): src is this rank's [b, s_l, W, h_l, dv] view of its sequence block (all heads); rank j receives the
+//          h_l heads it owns, placed at sequence block `rank` of its [b, W·s_l, h_l, dv] buffer.
+//   mode 1 (heads → sequence): src is this rank's [b, W, s_l, h_l, dv] view of the whole sequence (its h_l heads); rank j receives its
+//          sequence block, placed at head group `rank` of its [b, s_l, W·h_l, dv] buffer.
+// dv counts 16-byte vectors per (token, head).  One launch writes every peer's buffer, each thread starting with a different peer.
+struct CpTable {
+  uint4* dst[kMaxRanks];
+};
+
+__global__ void __launch_bounds__(256)
+cp_exchange_kernel(const uint4* __restrict__ src, CpTable t, int world, int rank, int mode, long long b, long long s_l, long long h_l, long long dv) {
+  const long long per_peer = b * s_l * h_l * dv;
+  const long long total = per_peer * world;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int jj = static_cast<int>(i / per_peer);
+    const int j = (rank + 1 + jj) % world;  // the ranks do not all start on the same peer
+    long long r = i - jj * per_peer;
+    const long long v = r % dv;
+    r /= dv;
+    const long long hi = r % h_l;
+    r /= h_l;
+    const long long si = r % s_l;
+    const long long bi = r / s_l;
+    long long so, dof;
+    if (mode == 0) {
+      so = (((bi * s_l + si) * world + j) * h_l + hi) * dv + v;
+      dof = ((bi * (world * s_l) + rank * s_l + si) * h_l + hi) * dv + v;
+    } else {
+      so = (((bi * world + j) * s_l + si) * h_l + hi) * dv + v;
+      dof = ((bi * s_l + si) * (world * h_l) + rank * h_l + hi) * dv + v;
+    }
+    t.dst[j][dof] = src[so];
+  }
+  __threadfence_system();  // peer stores visible before the signal that follows in stream order
+}
+
 }  // namespace ttb
 
 using namespace ttb;
@@ -383,3 +420,23 @@ extern "C" int ttb_dp_max_buckets() { return kMaxBuckets; }
 // Cycle budget of the cross-rank flag wait (default 4e9 ≈ 2–3 s).  When it runs out the wait kernel stores 201 in the error word
 // and the kernels that follow it return without touching parameters or optimizer state; the host raises on its next check.
 extern "C" void ttb_dp_set_wait_cycles(long long cycles) { g_flag_wait_cycles = cycles > 0 ? cycles : 4000000000LL; }
+
+
+// dst_ptrs: `world` device pointers (rank j's receive buffer, peer-mapped; entry `rank` is the own buffer).  Shapes in the kernel comment;
+// every pointer 16-byte aligned.  The caller orders the launch between a "receive buffers are free" wait and a "data has arrived" signal.
+extern "C" int ttb_cp_exchange(const void* src, void* const* dst_ptrs, int world, int rank, int mode, long long b, long long s_l, long long h_l, long long dv, void* stream) {
+  if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world || (mode != 0 && mode != 1) || b <= 0 || s_l <= 0 || h_l <= 0 || dv <= 0) return kErrBadShape;
+  CpTable t{};
+  for (int r = 0; r < world; ++r) {
+    if (reinterpret_cast<uintptr_t>(dst_ptrs[r]) & 15) return kErrBadShape;
+    t.dst[r] = static_cast<uint4*>(dst_ptrs[r]);
+  }
+  if (reinterpret_cast<uintptr_t>(src) & 15) return kErrBadShape;
+  const long long total = b * s_l * h_l * dv * world;
+  long long grid = (total + 255) / 256;
+  const long long cap = static_cast<long long>(ttb_dp_grid());
+  if (grid > cap) grid = cap;
+  TTB_COUNT_LAUNCH(1);
+  cp_exchange_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint4*>(src), t, world, rank, mode, b, s_l, h_l, dv);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrDriver;
+}

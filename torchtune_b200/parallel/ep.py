@@ -24,6 +24,8 @@ import ctypes
 from dataclasses import dataclass
 from typing import Dict, List, Optional
 
+import os
+
 import torch
 import torch.distributed as dist
 from torch import nn
@@ -81,21 +83,39 @@ class ExpertParallelContext:
             self._counts = PeerBuffer(num_experts * 8, device, group)
             self._recv = PeerBuffer(self.capacity * dim * 2, device, group)
             self._result = PeerBuffer(self.capacity * dim * 2, device, group)
+            # barriers between the ranks are a flag exchange over peer memory: store the next epoch into every peer's flag array
+            # (release), then wait — bounded — until every peer's entry has arrived (acquire); in stream order, no collective library
+            from .dp import _declare_dp
+
+            _declare_dp(lib())
+            self._flags = PeerBuffer(self.world * lib().ttb_dp_max_buckets() * 4, device, group) if self.world > 1 else None
+            self._epoch = 0
         else:
             self._recv_cpu = torch.zeros(self.capacity, dim)
             self._result_cpu = torch.zeros(self.capacity, dim)
 
     # ------------------------------------------------------------------ plumbing
     def barrier(self) -> None:
-        if self.world > 1:
-            dist.all_reduce(self._token, group=self.group)
+        if self.world == 1:
+            return
+        if self.cuda and self._flags is not None and os.environ.get("TTB_EP_FLAG_BARRIER", "1") != "0":
+            from ..ops._lib import check, err_word, lib, stream_ptr
+
+            L = lib()
+            self._epoch += 1
+            check(L.ttb_dp_signal(self._flags.pointer_array(), self.world, self.rank, 0, self._epoch, stream_ptr()), "ep barrier (signal)")
+            check(L.ttb_dp_wait(self._flags.local_ptr, self.world, self.rank, 0, self._epoch, err_word(self.device).data_ptr(), stream_ptr()), "ep barrier (wait)")
+            return
+        dist.all_reduce(self._token, group=self.group)
 
     def close(self) -> None:
         if self.cuda:
             torch.cuda.synchronize(self.device)
             self.barrier()
-            for b in (self._counts, self._recv, self._result):
-                b.close()
+            torch.cuda.synchronize(self.device)  # the flag barrier is enqueued work: it must have run before the buffers go away
+            for b in (self._counts, self._recv, self._result, self._flags):
+                if b is not None:
+                    b.close()
 
     def recv_rows(self, dtype: torch.dtype) -> torch.Tensor:
         """Private copy of the rows other ranks pushed here (``[capacity, dim]``; rows past the received count are unspecified)."""

@@ -82,7 +82,10 @@ def test_parameter_server_versions_and_replay_buffer():
 
 
 @pytest.mark.timeout(600)
-def test_async_grpo_recipe_end_to_end(tmp_path, tune_path, monkeypatch):
+@pytest.mark.parametrize("backend", ["thread", "process"])
+def test_async_grpo_recipe_end_to_end(tmp_path, tune_path, monkeypatch, backend):
+    """``process``: the inference workers are child processes feeding a multiprocessing queue and pulling weights from the
+    shared-memory parameter server; ``thread``: every role is a thread of the controller."""
     ckpt = tmp_path / "policy"
     write_tiny_hf_checkpoint(ckpt, arch=ARCH, builder=llama2)
     (tmp_path / "tok").mkdir()
@@ -90,11 +93,14 @@ def test_async_grpo_recipe_end_to_end(tmp_path, tune_path, monkeypatch):
     qa = tmp_path / "qa.json"
     qa.write_text(json.dumps([{"question": f"what is {i} plus {i}", "answer": str(2 * i)} for i in range(8)]))
     out = tmp_path / "out"
+    # child processes run truly in parallel and fill the queues before the first weights are published, so that run is longer:
+    # later batches are then sampled after a publish
+    steps = 3 if backend == "thread" else 10
     run_tune(tune_path, f"run dev/async_grpo_full_finetune_distributed --config tiny/async_grpo base_model_path={ckpt} tokenizer.path={sp} dataset.data_files={qa} output_dir={out} "
-                        f"metric_logger.filename=log.txt", monkeypatch)
+                        f"metric_logger.filename=log.txt orchestration.backend={backend} orchestration.num_steps={steps}", monkeypatch)
     text = (out / "logs" / "log.txt").read_text()
     losses = [float(x) for x in re.findall(r"train/loss:(\S+)", text)]
-    assert len(losses) == 3 and all(v == v for v in losses), losses
+    assert len(losses) == steps and all(v == v for v in losses), losses
     for name in ("train/kl_loss", "train/policy_staleness", "postprocessing/groups", "rewards/formatting", "rewards/math_correctness", "inference/worker_0/policy_version"):
         assert re.search(rf"{re.escape(name)}:", text), name
     # weights were published and picked up: some inference worker reports a policy version above zero

@@ -97,3 +97,59 @@ class SyncLLMCollector:
             if self.metric_logger is not None:
                 self.metric_logger.log_dict({f"inference/worker_{self.worker_id}/batches": self.batches_done,
                                              f"inference/worker_{self.worker_id}/policy_version": self.receiver.version if self.receiver else 0}, step=self.batches_done)
+
+
+class GeneratorWeightWorker:
+    """Receiving end of :class:`~torchtune_b200.dev.rl.workers.parameter_servers.BroadcastParameterServer`
+    (parity: torchtune/dev/rl/workers/datacollectors/sync.py:368-411, the worker the reference plugs into its inference engine).
+
+    Wraps the model this package's own generator runs.  ``init_weight_update_group`` joins the update group at rank
+    ``local_rank + rank_offset`` (the server is rank 0, so the offset is at least 1); ``update_weight`` receives one tensor and loads
+    it; ``update_policy_version`` receives the version.  ``receive`` does a whole push: the version, then every tensor of the model's
+    state dict in sorted-name order."""
+
+    def __init__(self, model: nn.Module, device: Optional[torch.device] = None, local_rank: int = 0):
+        self.model, self.local_rank = model, int(local_rank)
+        self.device = torch.device(device) if device is not None else next(model.parameters()).device
+        self.version = 0
+        self._group = None
+
+    def init_weight_update_group(self, master_address: str, master_port: int, rank_offset: int, world_size: int, timeout_s: float = 600.0) -> None:
+        from ..utils import stateless_init_process_group
+
+        if rank_offset < 1:
+            raise ValueError("rank 0 of the update group belongs to the parameter server")
+        self._group = stateless_init_process_group(master_address, master_port, self.local_rank + rank_offset, world_size,
+                                                   self.device if self.device.type == "cuda" else None, timeout_s)
+
+    def update_weight(self, name: str, dtype: torch.dtype, shape) -> None:
+        buf = torch.empty(tuple(shape), dtype=dtype, device=self._group.device)
+        self._group.broadcast(buf, src=0)
+        target = self.model.state_dict(keep_vars=True)[name]
+        with torch.no_grad():
+            target.copy_(buf)
+
+    def update_policy_version(self) -> int:
+        v = torch.zeros(1, dtype=torch.int64, device=self._group.device)
+        self._group.broadcast(v, src=0)
+        self.version = int(v.item())
+        return self.version
+
+    def receive(self) -> int:
+        """One whole push from the server; returns the new policy version."""
+        if self._group is None:
+            raise RuntimeError("init_weight_update_group() has not been called")
+        self.update_policy_version()
+        state = self.model.state_dict(keep_vars=True)
+        for name in sorted(state):
+            self.update_weight(name, state[name].dtype, state[name].shape)
+        return self.version
+
+    def close(self) -> None:
+        if self._group is not None:
+            self._group.close()
+            self._group = None
+
+
+# the reference's name for this role
+VLLMWorkerWrapper = GeneratorWeightWorker

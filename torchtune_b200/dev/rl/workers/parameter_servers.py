@@ -51,3 +51,48 @@ class ParameterServer:
             return None
         with self._lock:
             return self.version, {k: v.clone() for k, v in self._weights.items()}
+
+
+class BroadcastParameterServer(ParameterServer):
+    """Push protocol for inference workers that live in another job (parity: torchtune/dev/rl/workers/parameter_servers/vllm.py:67-111).
+
+    The pull protocol above needs the roles to share host memory.  When the inference workers are separate processes on other GPUs
+    (or other hosts), the server takes rank 0 of a :class:`~torchtune_b200.dev.rl.utils.StatelessGroup`, the workers take ranks
+    ``1..``, and :meth:`push` broadcasts the version and then every tensor in sorted-name order;
+    :class:`~torchtune_b200.dev.rl.workers.datacollectors.GeneratorWeightWorker` receives in the same order.  Tensors are staged on the
+    group's device one at a time, so the transfer never holds a second copy of the model."""
+
+    def __init__(self, template: Dict[str, torch.Tensor], shared: bool = False, lock=None, version=None):
+        super().__init__(template, shared=shared, lock=lock, version=version)
+        self._group = None
+
+    def init_update_group(self, master_address: str, master_port: int, world_size: int, device: Optional[torch.device] = None,
+                          timeout_s: float = 600.0) -> None:
+        from ..utils import stateless_init_process_group
+
+        self._group = stateless_init_process_group(master_address, master_port, 0, world_size, device, timeout_s)
+
+    def manifest(self):
+        """``[(name, dtype, shape)]`` in the order :meth:`push` sends them."""
+        return [(k, self._weights[k].dtype, tuple(self._weights[k].shape)) for k in sorted(self._weights)]
+
+    def push(self) -> int:
+        """Broadcast the current version and weights to every worker of the update group; returns the version sent."""
+        if self._group is None:
+            raise RuntimeError("init_update_group() has not been called")
+        dev = self._group.device
+        with self._lock:
+            version = self.version
+            self._group.broadcast(torch.tensor([version], dtype=torch.int64, device=dev), src=0)
+            for k in sorted(self._weights):
+                self._group.broadcast(self._weights[k].to(dev, copy=True), src=0)
+        return version
+
+    def close(self) -> None:
+        if self._group is not None:
+            self._group.close()
+            self._group = None
+
+
+# the reference's name for the server that feeds its inference engine
+VLLMParameterServer = BroadcastParameterServer

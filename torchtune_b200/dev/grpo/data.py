@@ -2,7 +2,7 @@
 from __future__ import annotations
 
 import re
-from typing import Any, Callable, Dict, List, Mapping, Optional, Union
+from typing import Any, Callable, Dict, List, Mapping, Optional, TypedDict, Union
 
 import torch
 from torch.nn.utils.rnn import pad_sequence
@@ -17,6 +17,14 @@ BASE_PROMPT = (
     "The reasoning process and answer are enclosed within <think></think> and <answer></answer> tags, respectively, "
     "i.e., <think>reasoning process here</think> <answer>answer here</answer>. User: %s. Assistant: <think>"
 )
+
+
+class ReasoningProblem(TypedDict):
+    """What a ``problem_transform`` returns: the question, the worked solution and the final answer."""
+
+    question: str
+    cot: str
+    answer: str
 
 
 class RLDataset(Dataset):
@@ -43,7 +51,7 @@ def padded_collate_rl(batch: List[Dict[str, Any]], padding_idx: int = 0, ignore_
     return {"tokens": tokens.long(), "answers": [x["answer"] for x in batch], "text": [x["question"] for x in batch]}
 
 
-def normalize_gsm(problem: Mapping[str, str]) -> Dict[str, str]:
+def normalize_gsm(problem: Mapping[str, str]) -> ReasoningProblem:
     """GSM8K rows end with ``#### <answer>``; the text before it is the worked solution."""
     cot, _, answer = problem["answer"].partition("#### ")
     return {"question": problem["question"], "cot": cot.strip(), "answer": answer.strip()}

@@ -81,11 +81,18 @@ def generate(
     stop_tokens: Optional[List[int]] = None,
     rng: Optional[torch.Generator] = None,
     custom_generate_next_token: Optional[Callable] = None,
-) -> Tuple[torch.Tensor, torch.Tensor]:
+    return_logits: bool = True,
+    stop_group=None,
+) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """Sample up to ``max_generated_tokens`` continuations of ``prompt`` (``[b, s]`` or ``[s]``,
     left-padded with ``pad_id`` when lengths differ).  With KV caches enabled on the model each
     step feeds only the new token.  Returns ``(tokens [b, s + n], logits [b, n, vocab])``;
-    tokens after a stop token are replaced by ``pad_id`` and their logits zeroed."""
+    tokens after a stop token are replaced by ``pad_id`` and their logits zeroed.
+
+    ``return_logits=False`` keeps no per-step logits (the second result is ``None``), which is what a rollout needs when the
+    log-probabilities are recomputed afterwards.  ``stop_group`` is a process group (``True`` for the default one): the loop then
+    ends only when every rank of the group has seen a stop token in every row, so ranks that hold shards of one model keep
+    issuing the same number of forward passes (parity: torchtune/dev/rl/generation.py:29-190)."""
     prompt = prompt.view(1, -1) if prompt.ndim == 1 else prompt
     bsz, prompt_len = prompt.shape
     total_len = prompt_len + max_generated_tokens
@@ -108,15 +115,22 @@ def generate(
     first_mask = masks[:, :prompt_len] if incremental else masks[:, :prompt_len, :prompt_len]
     tokens, logits = generate_next_token(model, input_pos=input_pos[:, :prompt_len].squeeze(), mask=first_mask, x=prompt, temperature=temperature, top_k=top_k, q=draw_q())
     out_tokens = torch.cat([prompt, tokens], dim=-1)
-    all_logits = logits
+    all_logits = logits if return_logits else None
     pos = prompt_len
+
+    def everyone_done(flags: torch.Tensor) -> bool:
+        done = flags.all()
+        if stop_group is not None and torch.distributed.is_available() and torch.distributed.is_initialized():
+            done = done.to(torch.int32)
+            torch.distributed.all_reduce(done, op=torch.distributed.ReduceOp.MIN, group=None if stop_group is True else stop_group)
+        return bool(done)
 
     stop = torch.tensor(stop_tokens, device=device, dtype=tokens.dtype) if stop_tokens else None
     reached = torch.zeros(bsz, dtype=torch.bool, device=device)
     keep = torch.ones(bsz, prompt_len + 1, dtype=torch.int32, device=device)
     if stop is not None:
         reached = update_stop_tokens_tracker(tokens, stop, reached)
-        if reached.all():
+        if everyone_done(reached):
             return out_tokens, all_logits
 
     step_fn = custom_generate_next_token or generate_next_token
@@ -129,14 +143,16 @@ def generate(
             cur_pos, cur_mask, x = input_pos[:, : pos + 1], masks[:, : pos + 1, : pos + 1], out_tokens.clone()
         tokens, logits = step_fn(model, input_pos=cur_pos, x=x, mask=cur_mask, temperature=temperature, top_k=top_k, q=draw_q())
         out_tokens = torch.cat([out_tokens, tokens], dim=-1)
-        all_logits = torch.cat([all_logits, logits], dim=1)
+        if return_logits:
+            all_logits = torch.cat([all_logits, logits], dim=1)
         pos += 1
         if stop is not None:
             reached = update_stop_tokens_tracker(tokens, stop, reached)
-            if reached.all():
+            if everyone_done(reached):
                 break
 
     if stop is not None:
         out_tokens = out_tokens * keep + pad_id * (1 - keep) if keep.shape == out_tokens.shape else out_tokens
-        all_logits = all_logits * keep[:, -all_logits.shape[1] :, None]
+        if return_logits:
+            all_logits = all_logits * keep[:, -all_logits.shape[1] :, None]
     return out_tokens, all_logits

@@ -65,3 +65,47 @@ def classifier_builders(name: str, arch_fn: Callable[..., DecoderArch], doc: str
     lora_builder.__name__ = f"lora_{name}_classifier"
     builder.__doc__ = lora_builder.__doc__ = doc + "  Classification head instead of the vocabulary projection."
     return builder, lora_builder
+
+
+def layer_builders(arch_fn: Callable[..., DecoderArch]) -> Tuple[Callable, Callable, Callable]:
+    """``(mlp, lora_self_attention, lora_mlp)`` for one family: single-layer pieces with the family's activation, biases, head
+    width, rotary embedding and per-head norms, for callers who assemble their own decoder (the reference writes these out per
+    family, e.g. torchtune/models/llama3/_component_builders.py:129-147, 300-380, 467-510).
+
+    The pieces come from the same :class:`DecoderArch` the whole-model builder uses, so a layer built here matches a layer of the
+    full model weight for weight."""
+    from ._factory import AdapterSpec, build_attention, build_mlp
+
+    params = inspect.signature(arch_fn).parameters
+
+    def _arch(embed_dim: int, hidden: int, num_heads: int = 1, num_kv_heads: int = 1, max_seq_len: int = 1, **extra: Any) -> DecoderArch:
+        kw = dict(vocab_size=1, num_layers=1, num_heads=num_heads, num_kv_heads=num_kv_heads, embed_dim=embed_dim, max_seq_len=max_seq_len)
+        if "intermediate_dim" in params:
+            kw["intermediate_dim"] = hidden
+        if "head_dim" in params and params["head_dim"].default is inspect.Parameter.empty and "head_dim" not in extra:
+            kw["head_dim"] = embed_dim // num_heads
+        unknown = set(extra) - set(params)
+        if unknown:
+            raise TypeError(f"unexpected keyword arguments {sorted(unknown)}")
+        kw.update(extra)
+        return arch_fn(**kw)
+
+    def mlp(dim: int, hidden_dim: int, quantize_base: bool = False):
+        arch = _arch(dim, hidden_dim)
+        return build_mlp(dim, hidden_dim, AdapterSpec(quantize_base=quantize_base), arch.activation(), arch.mlp_bias)
+
+    def lora_mlp(*, dim: int, hidden_dim: int, lora_rank: int, lora_alpha: float, lora_dropout: float = 0.0, quantize_base: bool = False, use_dora: bool = False):
+        arch = _arch(dim, hidden_dim)
+        ad = AdapterSpec(apply_to_mlp=True, rank=lora_rank, alpha=lora_alpha, dropout=lora_dropout, use_dora=use_dora, quantize_base=quantize_base)
+        return build_mlp(dim, hidden_dim, ad, arch.activation(), arch.mlp_bias)
+
+    def lora_self_attention(lora_modules: List[str], *, embed_dim: int, num_heads: int, num_kv_heads: int, max_seq_len: int, lora_rank: int, lora_alpha: float,
+                            lora_dropout: float = 0.0, quantize_base: bool = False, use_dora: bool = False, **arch_kwargs: Any):
+        if not lora_modules:
+            raise ValueError("lora_modules is empty: name at least one of q_proj, k_proj, v_proj, output_proj")
+        arch = _arch(embed_dim, embed_dim, num_heads, num_kv_heads, max_seq_len, **arch_kwargs)
+        ad = AdapterSpec(attn_modules=tuple(lora_modules), rank=lora_rank, alpha=lora_alpha, dropout=lora_dropout, use_dora=use_dora, quantize_base=quantize_base)
+        rope = arch.rope(arch.resolved_head_dim(), arch.max_seq_len) if arch.rope else None
+        return build_attention(arch, ad, rope)
+
+    return mlp, lora_self_attention, lora_mlp

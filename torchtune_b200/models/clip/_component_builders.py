@@ -100,3 +100,35 @@ def clip_text_encoder(embed_dim: int, num_heads: int, num_layers: int, vocab_siz
     )
     layer = TransformerSelfAttentionLayer(attn=attn, mlp=clip_mlp(embed_dim, embed_dim, embed_dim * 4, QuickGELU()), sa_norm=nn.LayerNorm(embed_dim, eps=norm_eps), mlp_norm=nn.LayerNorm(embed_dim, eps=norm_eps))
     return CLIPTextEncoder(layer=layer, final_norm=nn.LayerNorm(embed_dim, eps=norm_eps), vocab_size=vocab_size, max_seq_len=max_seq_len, embed_dim=embed_dim, num_layers=num_layers)
+
+
+def _check_modules(lora_modules) -> tuple:
+    if not lora_modules:
+        raise ValueError("lora_modules is empty: name at least one of q_proj, k_proj, v_proj, output_proj")
+    unknown = set(lora_modules) - {"q_proj", "k_proj", "v_proj", "output_proj"}
+    if unknown:
+        raise ValueError(f"unknown attention modules for LoRA: {sorted(unknown)}")
+    return tuple(lora_modules)
+
+
+def lora_clip_attention(lora_modules: List[str], *, embed_dim: int, head_dim: int, num_heads: int, num_kv_heads: int, attn_dropout: float = 0.0, attn_bias: bool = False,
+                        lora_rank: int, lora_alpha: float, lora_dropout: float = 0.0, use_dora: bool = False, quantize_base: bool = False) -> MultiHeadAttention:
+    """One bidirectional attention block of the vision tower with adapters on the listed projections
+    (parity: torchtune/models/clip/_component_builders.py:440-600)."""
+    mods = _check_modules(lora_modules)
+    lora = dict(rank=lora_rank, alpha=lora_alpha, dropout=lora_dropout, use_dora=use_dora)
+    return MultiHeadAttention(
+        embed_dim=embed_dim, num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim,
+        q_proj=_proj(embed_dim, num_heads * head_dim, attn_bias, "q_proj" in mods, lora, quantize_base),
+        k_proj=_proj(embed_dim, num_kv_heads * head_dim, attn_bias, "k_proj" in mods, lora, quantize_base),
+        v_proj=_proj(embed_dim, num_kv_heads * head_dim, attn_bias, "v_proj" in mods, lora, quantize_base),
+        output_proj=_proj(num_heads * head_dim, embed_dim, attn_bias, "output_proj" in mods, lora, quantize_base),
+        pos_embeddings=None, attn_dropout=attn_dropout, is_causal=False,
+    )
+
+
+def lora_clip_mlp(*, in_dim: int, out_dim: int, hidden_dim: int, activation: nn.Module, lora_rank: int, lora_alpha: float, lora_dropout: float = 0.0,
+                  use_dora: bool = False, quantize_base: bool = False) -> FeedForward:
+    """The tower's two-layer MLP with adapters on both projections (parity: torchtune/models/clip/_component_builders.py:603-660)."""
+    return clip_mlp(in_dim, out_dim, hidden_dim, activation, quantize_base=quantize_base,
+                    _lora=dict(rank=lora_rank, alpha=lora_alpha, dropout=lora_dropout, use_dora=use_dora))

@@ -7,7 +7,7 @@ from torch import nn
 from ...modules import RotaryPositionalEmbeddings
 from .._factory import DecoderArch
 from .._family import lora_preset, preset, qlora_preset
-from .._generic import component_builders
+from .._generic import component_builders, layer_builders
 from ._modules import GemmaNormEmbeddings, GemmaRMSNorm, TanhSoftCapping  # noqa: F401
 
 
@@ -21,6 +21,7 @@ def _arch(vocab_size: int, num_layers: int, num_heads: int, head_dim: int, num_k
 
 
 gemma, _lora_gemma = component_builders("gemma", _arch, "Gemma decoder.")
+gemma_mlp, lora_gemma_self_attention, lora_gemma_mlp = layer_builders(_arch)
 
 
 def lora_gemma(lora_attn_modules, apply_lora_to_mlp: bool = False, **kwargs):

@@ -10,7 +10,7 @@ from torch import nn
 from ...modules import RotaryPositionalEmbeddings
 from .._factory import DecoderArch
 from .._family import lora_preset, preset, qlora_preset
-from .._generic import component_builders
+from .._generic import component_builders, layer_builders
 from ..gemma._modules import Gemma2FinalNorm, GemmaNormEmbeddings, GemmaRMSNorm, TanhSoftCapping  # noqa: F401
 from ._convert_weights import gemma2_hf_to_tune, gemma2_tune_to_hf  # noqa: F401
 
@@ -28,6 +28,7 @@ def _arch(vocab_size: int, num_layers: int, num_heads: int, head_dim: int, num_k
 
 
 gemma2, _lora_gemma2 = component_builders("gemma2", _arch, "Gemma-2 decoder.")
+gemma2_mlp, lora_gemma2_self_attention, lora_gemma2_mlp = layer_builders(_arch)
 
 
 def lora_gemma2(lora_attn_modules, apply_lora_to_mlp: bool = False, **kwargs):

@@ -4,7 +4,7 @@ from typing import Optional
 from ...modules import RotaryPositionalEmbeddings
 from .._factory import DecoderArch
 from .._family import lora_preset, preset, qlora_preset
-from .._generic import classifier_builders, component_builders
+from .._generic import classifier_builders, component_builders, layer_builders
 
 
 def _arch(vocab_size: int, num_layers: int, num_heads: int, num_kv_heads: int, embed_dim: int, max_seq_len: int, attn_dropout: float = 0.0, intermediate_dim: Optional[int] = None, norm_eps: float = 1e-5, rope_base: int = 10_000) -> DecoderArch:
@@ -12,6 +12,7 @@ def _arch(vocab_size: int, num_layers: int, num_heads: int, num_kv_heads: int, e
 
 
 llama2, lora_llama2 = component_builders("llama2", _arch, "Llama-2 decoder: MHA/GQA, SwiGLU, RMSNorm, interleaved RoPE, untied output.")
+llama2_mlp, lora_llama2_self_attention, lora_llama2_mlp = layer_builders(_arch)
 llama2_classifier, lora_llama2_classifier = classifier_builders("llama2", _arch, "Llama-2 decoder.")
 
 _C = dict(vocab_size=32_000, max_seq_len=4096, attn_dropout=0.0, norm_eps=1e-5)

@@ -4,7 +4,7 @@ from typing import Optional
 from ...modules import RotaryPositionalEmbeddings
 from .._factory import DecoderArch, scale_hidden_dim_for_mlp  # noqa: F401
 from .._family import lora_preset, preset, qlora_preset
-from .._generic import component_builders
+from .._generic import component_builders, layer_builders
 
 
 def _arch(vocab_size: int, num_layers: int, num_heads: int, num_kv_heads: int, embed_dim: int, max_seq_len: int, attn_dropout: float = 0.0, rope_base: int = 500_000, intermediate_dim: Optional[int] = None, norm_eps: float = 1e-5) -> DecoderArch:
@@ -12,6 +12,7 @@ def _arch(vocab_size: int, num_layers: int, num_heads: int, num_kv_heads: int, e
 
 
 llama3, lora_llama3 = component_builders("llama3", _arch, "Llama-3 decoder: GQA, SwiGLU, RMSNorm, interleaved RoPE (base 500k), 128k vocabulary.")
+llama3_mlp, lora_llama3_self_attention, lora_llama3_mlp = layer_builders(_arch)
 
 _C = dict(vocab_size=128_256, max_seq_len=8192, attn_dropout=0.0, norm_eps=1e-5, rope_base=500_000)
 _S = {

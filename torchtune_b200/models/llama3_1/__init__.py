@@ -1,5 +1,5 @@
 from ...modules.position_embeddings import Llama3ScaledRoPE
-from ._component_builders import llama3_1, lora_llama3_1
+from ._component_builders import llama3_1, llama3_mlp, lora_llama3_1, lora_llama3_attention, lora_llama3_mlp
 from ._model_builders import (
     llama3_1_405b,
     llama3_1_70b,
@@ -25,4 +25,7 @@ __all__ = [
     "qlora_llama3_1_70b",
     "qlora_llama3_1_405b",
     "Llama3ScaledRoPE",
+    "llama3_mlp",
+    "lora_llama3_attention",
+    "lora_llama3_mlp",
 ]

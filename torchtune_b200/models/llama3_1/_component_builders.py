@@ -65,3 +65,18 @@ def lora_llama3_1(
     arch = _arch(vocab_size, num_layers, num_heads, num_kv_heads, embed_dim, max_seq_len, attn_dropout, rope_base, intermediate_dim, norm_eps, scale_factor)
     ad = adapter_from_kwargs(lora_attn_modules, apply_lora_to_mlp, apply_lora_to_output, lora_rank, lora_alpha, lora_dropout, use_dora, quantize_base)
     return build_decoder(arch, ad)
+
+
+def _layer_arch(vocab_size: int, num_layers: int, num_heads: int, num_kv_heads: int, embed_dim: int, max_seq_len: int, attn_dropout: float = 0.0,
+                rope_base: int = 500_000, intermediate_dim: Optional[int] = None, norm_eps: float = 1e-5, scale_factor: int = 8) -> DecoderArch:
+    return _arch(vocab_size, num_layers, num_heads, num_kv_heads, embed_dim, max_seq_len, attn_dropout, rope_base, intermediate_dim, norm_eps, scale_factor)
+
+
+def _layer_builders():
+    from .._generic import layer_builders
+
+    return layer_builders(_layer_arch)
+
+
+# single-layer pieces under the reference's names (torchtune/models/llama3_1/_component_builders.py:127-145, 296-376, 379-420)
+llama3_mlp, lora_llama3_attention, lora_llama3_mlp = _layer_builders()

@@ -4,7 +4,7 @@ from typing import Optional
 from ...modules import Llama3ScaledRoPE
 from .._factory import DecoderArch
 from .._family import lora_preset, preset, qlora_preset
-from .._generic import component_builders
+from .._generic import component_builders, layer_builders
 
 
 def _arch(vocab_size: int, num_layers: int, num_heads: int, num_kv_heads: int, embed_dim: int, max_seq_len: int, attn_dropout: float = 0.0, rope_base: int = 500_000, intermediate_dim: Optional[int] = None, norm_eps: float = 1e-5, scale_factor: int = 32, tie_word_embeddings: bool = True) -> DecoderArch:
@@ -12,6 +12,7 @@ def _arch(vocab_size: int, num_layers: int, num_heads: int, num_kv_heads: int, e
 
 
 llama3_2, lora_llama3_2 = component_builders("llama3_2", _arch, "Llama-3.2 decoder: Llama-3.1 architecture with scale factor 32 and (by default) the output projection tied to the token embeddings.")
+llama3_mlp, lora_llama3_2_self_attention, lora_llama3_mlp = layer_builders(_arch)
 
 _C = dict(vocab_size=128_256, max_seq_len=131072, attn_dropout=0.0, norm_eps=1e-5, rope_base=500_000, scale_factor=32)
 _S = {

@@ -142,3 +142,30 @@ def lora_llama4_vision_encoder(encoder_lora: bool, fusion_lora: bool, lora_attn_
     else:
         head = llama4_vision_projection_head(decoder_embed_dim=decoder_embed_dim, clip_embed_dim=clip_embed_dim, projection_embed_dim=projection_embed_dim)
     return Llama4VisionEncoder(clip=clip, projection_head=head)
+
+
+def lora_llama4_self_attention(lora_modules: List[str], pos_embeddings: Optional[nn.Module], q_norm: Optional[nn.Module] = None, k_norm: Optional[nn.Module] = None, *,
+                               head_dim: int, embed_dim: int, num_heads: int, num_kv_heads: int, max_seq_len: int, attn_dropout: float = 0.0,
+                               lora_rank: int, lora_alpha: float, lora_dropout: float = 0.0, use_dora: bool = False, quantize_base: bool = False):
+    """One decoder attention block with adapters on the listed projections; the caller passes the rotary embedding (``None`` on the
+    layers that skip it) and the q/k norms (parity: torchtune/models/llama4/_component_builders.py:875-1017)."""
+    from ...modules import MultiHeadAttention
+
+    if not lora_modules:
+        raise ValueError("lora_modules is empty: name at least one of q_proj, k_proj, v_proj, output_proj")
+    ad = AdapterSpec(attn_modules=tuple(lora_modules), rank=lora_rank, alpha=lora_alpha, dropout=lora_dropout, use_dora=use_dora, quantize_base=quantize_base)
+    mods = set(lora_modules)
+    unknown = mods - {"q_proj", "k_proj", "v_proj", "output_proj"}
+    if unknown:
+        raise ValueError(f"unknown attention modules for LoRA: {sorted(unknown)}")
+    return MultiHeadAttention(
+        embed_dim=embed_dim, num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim,
+        q_proj=ad.make(embed_dim, num_heads * head_dim, "q_proj" in mods), k_proj=ad.make(embed_dim, num_kv_heads * head_dim, "k_proj" in mods),
+        v_proj=ad.make(embed_dim, num_kv_heads * head_dim, "v_proj" in mods), output_proj=ad.make(num_heads * head_dim, embed_dim, "output_proj" in mods),
+        pos_embeddings=pos_embeddings, q_norm=q_norm, k_norm=k_norm, max_seq_len=max_seq_len, attn_dropout=attn_dropout,
+    )
+
+
+def lora_llama4_mlp(*, dim: int, hidden_dim: int, lora_rank: int, lora_alpha: float, lora_dropout: float = 0.0, quantize_base: bool = False, use_dora: bool = False) -> FeedForward:
+    """Dense SwiGLU feed-forward with adapters on all three projections (parity: torchtune/models/llama4/_component_builders.py:1020-1060)."""
+    return build_mlp(dim, hidden_dim, AdapterSpec(apply_to_mlp=True, rank=lora_rank, alpha=lora_alpha, dropout=lora_dropout, use_dora=use_dora, quantize_base=quantize_base))

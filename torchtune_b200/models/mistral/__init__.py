@@ -4,7 +4,7 @@ from typing import Optional
 from ...modules import RotaryPositionalEmbeddings
 from .._factory import DecoderArch
 from .._family import lora_preset, preset, qlora_preset
-from .._generic import classifier_builders, component_builders
+from .._generic import classifier_builders, component_builders, layer_builders
 
 
 def _arch(vocab_size: int, num_layers: int, num_heads: int, num_kv_heads: int, embed_dim: int, intermediate_dim: int, max_seq_len: int, attn_dropout: float = 0.0, norm_eps: float = 1e-5, rope_base: int = 10_000) -> DecoderArch:
@@ -12,6 +12,7 @@ def _arch(vocab_size: int, num_layers: int, num_heads: int, num_kv_heads: int, e
 
 
 mistral, lora_mistral = component_builders("mistral", _arch, "Mistral decoder: GQA, SwiGLU, RMSNorm, interleaved RoPE (the sliding window of the original is not applied).")
+mistral_mlp, lora_mistral_self_attention, lora_mistral_mlp = layer_builders(_arch)
 mistral_classifier, lora_mistral_classifier = classifier_builders("mistral", _arch, "Mistral decoder.")
 
 _C = dict(vocab_size=32_000, num_layers=32, num_heads=32, num_kv_heads=8, embed_dim=4096, intermediate_dim=14336, max_seq_len=32768, attn_dropout=0.0, norm_eps=1e-5)

@@ -4,7 +4,7 @@ from typing import Optional
 from ...modules import Phi3RotaryPositionalEmbeddings
 from .._factory import DecoderArch
 from .._family import lora_preset, preset, qlora_preset
-from .._generic import component_builders
+from .._generic import component_builders, layer_builders
 from ._convert_weights import phi3_hf_to_tune, phi3_tune_to_hf  # noqa: F401
 
 
@@ -13,6 +13,7 @@ def _arch(vocab_size: int, num_layers: int, num_heads: int, num_kv_heads: int, e
 
 
 phi3, lora_phi3 = component_builders("phi3", _arch, "Phi-3 decoder.")
+phi3_mlp, lora_phi3_self_attention, lora_phi3_mlp = layer_builders(_arch)
 _C = dict(vocab_size=32_064, num_layers=32, num_heads=32, num_kv_heads=32, embed_dim=3072, intermediate_dim=8192, max_seq_len=4096, attn_dropout=0.0, norm_eps=1e-5)
 phi3_mini = preset(phi3, "phi3_mini", "Phi-3 mini 4k instruct (3.8B).", **_C)
 lora_phi3_mini = lora_preset(lora_phi3, "lora_phi3_mini", "Phi-3 mini with adapters.", **_C)

@@ -5,7 +5,7 @@ from typing import Optional
 from ...modules import Qwen2RotaryPositionalEmbeddings
 from .._factory import DecoderArch
 from .._family import lora_preset, preset
-from .._generic import component_builders
+from .._generic import component_builders, layer_builders
 from ._convert_weights import qwen2_hf_to_tune, qwen2_tune_to_hf  # noqa: F401
 
 
@@ -14,6 +14,7 @@ def _arch(vocab_size: int, num_layers: int, num_heads: int, num_kv_heads: int, e
 
 
 qwen2, lora_qwen2 = component_builders("qwen2", _arch, "Qwen2 decoder: GQA with q/k/v bias, SwiGLU, RMSNorm, half-split RoPE.")
+qwen2_mlp, lora_qwen2_self_attention, lora_qwen2_mlp = layer_builders(_arch)
 
 _C = dict(max_seq_len=32768, attn_dropout=0.0, norm_eps=1e-6, rope_base=1_000_000.0)
 SIZES = {

@@ -5,7 +5,7 @@ from typing import Optional
 from ...modules import Qwen2RotaryPositionalEmbeddings, RMSNorm
 from .._factory import DecoderArch
 from .._family import lora_preset, preset
-from .._generic import component_builders
+from .._generic import component_builders, layer_builders
 from ..qwen2._convert_weights import qwen3_hf_to_tune, qwen3_tune_to_hf  # noqa: F401
 
 
@@ -16,6 +16,7 @@ def _arch(vocab_size: int, num_layers: int, num_heads: int, num_kv_heads: int, e
 
 
 qwen3, lora_qwen3 = component_builders("qwen3", _arch, "Qwen3 decoder: GQA with per-head q/k RMSNorm before RoPE, SwiGLU, RMSNorm.")
+qwen3_mlp, lora_qwen3_self_attention, lora_qwen3_mlp = layer_builders(_arch)
 
 _B = dict(vocab_size=151936, head_dim=128, attn_dropout=0.0, norm_eps=1e-6, rope_base=1_000_000.0, q_proj_bias=False, k_proj_bias=False, v_proj_bias=False, q_norm=True, k_norm=True)
 _ARCHS = {

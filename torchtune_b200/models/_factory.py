@@ -83,6 +83,7 @@ class DecoderArch:
     post_norms: bool = False  # Gemma-2: extra norms on the attention / MLP outputs (sa_scale, mlp_scale)
     final_norm: Optional[Callable[[int, float], nn.Module]] = None  # defaults to `norm`
     attn_softcap: float = 0.0
+    logit_softcap: float = 0.0  # cap·tanh(logits/cap) on the output logits (Gemma-2)
     attn_scale: Optional[float] = None
     sliding_window: Optional[Callable[[int], int]] = None  # layer index -> window (0 = global)
     # per-layer overrides (Llama-4): feed-forward module, whether the layer rotates/normalises q and k,
@@ -197,6 +198,7 @@ def build_decoder(arch: DecoderArch, adapter: Optional[AdapterSpec] = None) -> T
         norm=(arch.final_norm or arch.norm)(arch.embed_dim, arch.norm_eps),
         output=output,
     )
+    model.logit_softcap = float(arch.logit_softcap)
     if ad.quantize_base:
         # checkpoints of a quantised-base model are written in bf16 on CPU
         _register_reparametrize_state_dict_hooks(model, dtype=tok.weight.dtype)

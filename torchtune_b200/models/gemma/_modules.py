@@ -40,13 +40,21 @@ class TanhSoftCapping(nn.Module):
 
 
 class Gemma2FinalNorm(nn.Module):
-    """Final RMS norm followed by soft capping (parity: torchtune/models/gemma2/_component_builders.py)."""
+    """Final RMS norm of Gemma-2, optionally followed by soft capping of the normalised hidden state.
 
-    def __init__(self, capping_value: float, embed_dim: int, eps: float):
+    The reference caps here, on the hidden state that then goes through the output projection
+    (torchtune/models/gemma2/_component_builders.py:56-72).  The published model caps the *logits*, after the projection, which
+    is not the same function; this package's builders therefore pass ``cap_hidden=False`` and set the decoder's
+    ``logit_softcap`` instead.  ``cap_hidden=True`` reproduces the reference's graph.  The parameter name
+    (``rms_norm.scale``) is the same either way, so checkpoints are interchangeable."""
+
+    def __init__(self, capping_value: float, embed_dim: int, eps: float, cap_hidden: bool = True):
         super().__init__()
         self.capping_value = capping_value
+        self.cap_hidden = cap_hidden
         self.rms_norm = GemmaRMSNorm(embed_dim, eps=eps)
         self.logit_capping = TanhSoftCapping(capping_value)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.logit_capping(self.rms_norm(x))
+        x = self.rms_norm(x)
+        return self.logit_capping(x) if self.cap_hidden else x

@@ -196,6 +196,9 @@ class TransformerDecoder(nn.Module):
         self.causal_mask = None
         self.num_output_chunks = 0
         self.skip_output_layer = False
+        # cap·tanh(logits/cap) applied to the logits (Gemma-2); 0 = none.  A loss that takes the hidden states instead
+        # (``skip_output_layer``) reads this attribute and applies the cap itself.
+        self.logit_softcap = 0.0
         self.encoder_max_cache_seq_len = None
         self.decoder_max_cache_seq_len = None
 
@@ -240,8 +243,12 @@ class TransformerDecoder(nn.Module):
             layer.reset_cache()
 
     # -- forward ---------------------------------------------------------------
+    def _cap(self, logits: torch.Tensor) -> torch.Tensor:
+        cap = float(self.logit_softcap)
+        return logits if cap <= 0.0 else torch.tanh(logits / cap) * cap
+
     def chunked_output(self, last_hidden_state: torch.Tensor) -> List[torch.Tensor]:
-        return [self.output(chunk) for chunk in last_hidden_state.tensor_split(self.num_output_chunks, dim=1)]
+        return [self._cap(self.output(chunk)) for chunk in last_hidden_state.tensor_split(self.num_output_chunks, dim=1)]
 
     def _validate_inputs(self, seq_len, mask=None, encoder_input=None, encoder_mask=None, input_pos=None) -> None:
         if seq_len > self.max_seq_len:
@@ -286,11 +293,11 @@ class TransformerDecoder(nn.Module):
         return output if not hidden else [*hidden, output]
 
     def unembed_normed(self, h: torch.Tensor) -> torch.Tensor:
-        return self.output(h).float()
+        return self._cap(self.output(h).float())
 
     def unembed(self, h: torch.Tensor) -> torch.Tensor:
         """Final norm + output projection of a hidden state (fp32 logits)."""
         h = self.norm(h)
         if self.num_output_chunks > 0:
             return self.chunked_output(h)
-        return self.output(h).float()
+        return self._cap(self.output(h).float())

@@ -193,3 +193,56 @@ def test_text_rows_without_an_image_pass_through_the_fusion_layer():
         out = fusion(x, encoder_input=enc, encoder_mask=mask)
     assert torch.equal(out[:, :2], x[:, :2])
     assert not torch.allclose(out[:, 2:], x[:, 2:])
+
+
+def test_llama4_early_fusion_matches_transformers():
+    """Whole Llama-4 model: the vision tower (2-D rotary embedding per tile, pixel shuffle, adapter MLP), the projector, the image
+    tokens scattered into the text sequence, and the mixture-of-experts decoder — through the checkpoint converter in both
+    directions."""
+    from transformers.models.llama4.configuration_llama4 import Llama4Config, Llama4TextConfig, Llama4VisionConfig
+
+    from torchtune_b200.models.llama4 import llama4_decoder, llama4_vision_encoder
+    from torchtune_b200.models.llama4._convert_weights import llama4_hf_to_tune, llama4_tune_to_hf
+    from torchtune_b200.modules.model_fusion import EarlyFusionModel
+
+    torch.manual_seed(0)
+    vision = Llama4VisionConfig(hidden_size=32, num_hidden_layers=2, num_attention_heads=4, intermediate_size=128, vision_output_dim=48, image_size=16, patch_size=4, norm_eps=1e-5,
+                                pixel_shuffle_ratio=0.5, projector_input_dim=48, projector_output_dim=48, rope_parameters=dict(rope_type="default", rope_theta=10000.0))
+    text = Llama4TextConfig(vocab_size=136, hidden_size=64, intermediate_size=48, intermediate_size_mlp=96, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                            num_local_experts=4, num_experts_per_tok=1, interleave_moe_layer_step=1, max_position_embeddings=64, rms_norm_eps=1e-5, rope_theta=500000.0, rope_scaling=None,
+                            no_rope_layers=[1, 1, 1, 0], attention_chunk_size=8, use_qk_norm=True, attn_temperature_tuning=False, tie_word_embeddings=False, pad_token_id=0)
+    cfg = Llama4Config(vision_config=vision, text_config=text, image_token_index=130, boi_token_index=131, eoi_token_index=132)
+    cfg._attn_implementation = "eager"
+    hf = transformers.Llama4ForConditionalGeneration(cfg).eval().float()
+    with torch.no_grad():
+        for name, p in hf.named_parameters():
+            if "layernorm" in name.lower() or name.endswith("norm.weight"):
+                p.copy_(1.0 + 0.1 * torch.randn_like(p)) if name.endswith("weight") else torch.nn.init.normal_(p, std=0.1)
+            else:
+                torch.nn.init.normal_(p, std=0.08)
+
+    released = dict(hf.state_dict())  # this model's module tree already has the layout of the released checkpoint
+    native = llama4_hf_to_tune(released)
+    decoder = llama4_decoder(vocab_size=136, num_layers=4, num_heads=4, num_kv_heads=2, embed_dim=64, hidden_dim=48, max_seq_len=64, rope_base=500000, norm_eps=1e-5, num_experts=4,
+                             experts_per_token=1, use_shared_expert=True, use_qk_norm=True, skip_rope_interval=4, attention_chunk_size=8)
+    tower = llama4_vision_encoder(patch_size=4, num_heads=4, clip_embed_dim=32, clip_num_layers=2, clip_hidden_states=None, projection_embed_dim=48, decoder_embed_dim=64, tile_size=16,
+                                  max_num_tiles=1, in_channels=3)
+    mine = EarlyFusionModel(decoder, encoders={"vision": tower}, encoder_tokens={"vision": 130}).eval()
+    mine.load_state_dict(native)  # strict
+
+    back = llama4_tune_to_hf(native)
+    assert set(back) == set(released) and all(torch.equal(back[k], released[k]) for k in released)
+
+    # two tiles of 4 image tokens each in the first sequence, one in the second
+    tokens = torch.randint(3, 128, (2, 19))
+    tokens[0, 2:6] = 130
+    tokens[0, 9:13] = 130
+    tokens[1, 5:9] = 130
+    images = torch.randn(3, 3, 16, 16)
+    with torch.no_grad():
+        want = hf(input_ids=tokens, pixel_values=images).logits
+        got = mine(tokens, encoder_input={"vision": {"images": images}})
+    assert torch.allclose(got, want, atol=2e-5), (got - want).abs().max()
+    with torch.no_grad():
+        text_only = torch.randint(3, 128, (2, 19))
+        assert torch.allclose(mine(text_only), hf(input_ids=text_only).logits, atol=2e-5)

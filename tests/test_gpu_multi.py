@@ -137,6 +137,23 @@ def test_lora_over_sharded_base_weights_on_two_gpus(tmp_path):
     assert (tmp_path / "z3" / "epoch_0" / "adapter_model.safetensors").exists()
 
 
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_qlora_over_sharded_nf4_base_on_two_gpus(tmp_path):
+    """QLoRA with shard_parameters=True (each GPU keeps half of every 4-bit base weight's codes and scales; a weight is gathered and
+    expanded right before its GEMM; the model is built without storage first) follows QLoRA with a resident 4-bit base."""
+    ckpt = _tiny_ckpt(tmp_path)
+    res = {}
+    for name, port, extra in (("dp", 29647, []), ("z3", 29649, ["shard_parameters=True", "shard_parameters_min_numel=1"])):
+        out = tmp_path / name
+        _tune(["lora_finetune_distributed", "--config", "tiny/llama_lora_distributed", f"checkpointer.checkpoint_dir={ckpt}", f"output_dir={out}", "metric_logger.filename=log.txt",
+               "device=cuda", "dtype=bf16", "max_steps_per_epoch=4", "dataset.num_samples=32", "optimizer.lr=1e-2", "model.quantize_base=True", "save_adapter_weights_only=True"] + extra, port)
+        res[name] = _losses(out / "logs" / "log.txt")
+    assert len(res["z3"]) == 4
+    for a, b in zip(res["dp"], res["z3"]):
+        assert abs(a - b) < 0.02 * abs(a), res
+    assert (tmp_path / "z3" / "epoch_0" / "adapter_model.safetensors").exists()
+
+
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 4, reason="needs 4 GPUs")
 def test_dp_times_tp_mesh_on_four_gpus(tmp_path):
     """tensor_parallel_dim=2 on four GPUs (two tensor-parallel groups of consecutive ranks, two model replicas) follows the loss

@@ -228,12 +228,44 @@ def _dims(m: nn.Module):
     return None
 
 
+def shard_nf4_bases(model: nn.Module, device: torch.device, group=None, *, min_numel: int = 1 << 16) -> int:
+    """Cut every frozen 4-bit base weight (``LoRALinear(quantize_base=True)``, ``FrozenNF4Linear``) into one part per rank
+    (:class:`~torchtune_b200.modules.low_precision.ShardedNF4Weight`); returns how many were cut.
+
+    Works on a model built under ``torch.device('meta')`` as well: a part is then allocated directly, so the whole 4-bit weight
+    never exists on this rank, and the values arrive when the checkpoint is loaded (each dense weight is coded as a whole and this
+    rank's part kept).  Weights that do not split at a boundary of their scale groups stay whole."""
+    from ..modules.low_precision import NF4Weight, ShardedNF4Weight
+
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    if world == 1:
+        return 0
+    cut = 0
+    for owner in list(model.modules()):
+        full = getattr(owner, "nf4", None)
+        if type(full) is not NF4Weight:
+            continue
+        out_dim, in_dim = full.shape
+        if out_dim * in_dim < min_numel or not ShardedNF4Weight.divisible(out_dim, in_dim, world, full.block_size, full.scaler_block_size):
+            continue
+        if full.weight_nf4.is_meta:
+            part = ShardedNF4Weight(out_dim, in_dim, rank=rank, world=world, group=group, block_size=full.block_size, scaler_block_size=full.scaler_block_size,
+                                    dtype=full.dtype, device=device)
+        else:
+            part = ShardedNF4Weight.from_full(full, rank=rank, world=world, group=group)
+        owner.nf4 = part
+        cut += 1
+    return cut
+
+
 def shard_linear_weights(model: nn.Module, device: torch.device, group=None, *, min_numel: int = 1 << 16, exclude=("output",)) -> nn.Module:
     """Replace every plain ``nn.Linear`` (and every dense-base ``LoRALinear``) with at least ``min_numel`` weights whose rows split
     evenly into whole n-tiles by a :class:`ShardedLinear` (:class:`ShardedLoRALinear`) (in place; module paths in ``exclude`` and
     the small adapter matrices inside LoRA modules are left alone) and attach ``_replicated``, ``sync_replicated_grads()``, ``after_optimizer_step()`` and
     ``full_state_dict()`` (checkpoint layout; collective) to ``model``."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
+    shard_nf4_bases(model, device, group, min_numel=min_numel)  # 4-bit bases: parts of the codes, gathered and expanded per use
 
     def eligible(m: nn.Module) -> bool:
         dims = _dims(m)

@@ -329,6 +329,12 @@ class ParallelStrategy(DataParallelEngine):
             if self.dims.tp_enabled:
                 return self._shard_model_tp(model, cfg, layerwise)
             return self._shard_model_ep(model, cfg, layerwise)
+        if is_lora and self._shard_parameters and any(b.is_meta for b in model.buffers()):
+            # a 4-bit base larger than one GPU: its parts get storage before anything else does, so that the whole never exists here
+            from .fsdp import shard_nf4_bases
+
+            get_ = cfg.get if hasattr(cfg, "get") else (lambda k, d=None: d)
+            shard_nf4_bases(model, self.device, None, min_numel=int(get_("shard_parameters_min_numel", 1 << 16)))
         materialize(model, self.device)
         if is_lora:
             from ..modules.peft import validate_missing_and_unexpected_for_lora

@@ -201,6 +201,26 @@ def test_linear_cross_entropy(T, D, V):
     _close(w.grad, wr.grad, 5e-2, 2e-4, "ce dw")
 
 
+@pytest.mark.parametrize("T,D,V,cap", [(300, 256, 1024, 2.0), (1000, 512, 32000, 30.0)])
+def test_linear_cross_entropy_with_soft_capped_logits(T, D, V, cap):
+    """Gemma-2: softmax over cap·tanh(logits/cap); the small cap puts most logits on the curved part of the tanh."""
+    h = _rand(T, D, seed=1).requires_grad_()
+    w = _rand(V, D, seed=2, scale=0.25).requires_grad_()
+    labels = torch.randint(0, V, (T,), device="cuda")
+    labels[::7] = -100
+    loss, n = ops.linear_cross_entropy(h, w, labels, -100, 8, softcap=cap)
+    (loss / n).backward()
+    hr, wr = h.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    lr, nr = ref.linear_cross_entropy(hr, wr, labels, -100, 8, softcap=cap)
+    (lr / nr).backward()
+    assert n.item() == nr.item()
+    uncapped, _ = ref.linear_cross_entropy(hr.detach(), wr.detach(), labels, -100, 8)
+    assert abs((uncapped / nr - lr / nr).item()) > 1e-2  # the cap changes this loss, so the comparison below means something
+    _close(loss / n, lr / nr, 5e-3, 5e-3, "capped ce loss")
+    _close(h.grad, hr.grad, 5e-2, 3e-4, "capped ce dh")
+    _close(w.grad, wr.grad, 5e-2, 3e-4, "capped ce dw")
+
+
 def test_token_logprobs():
     T, D, V = 200, 256, 2048
     h = _rand(T, D, seed=1).requires_grad_()

@@ -67,6 +67,8 @@ class StatelessGroup:
         if self._pg is not None:
             try:
                 self._pg.barrier().wait()
+                if hasattr(self._pg, "shutdown"):
+                    self._pg.shutdown()  # releases the communicator now instead of at interpreter exit
             finally:
                 self._pg = None
                 self._store = None

@@ -53,36 +53,14 @@ class LinearCrossEntropyLoss(nn.Module, SFTLoss):
         need for global token normalisation."""
         proj = self.linear_projection
         if self.logit_softcap > 0.0:
-            return self._capped_sum(outputs, targets)
+            # Gemma-2: the cap sits between the projection and the softmax; the fused op applies it inside its softmax kernel
+            if proj is not None and hasattr(proj, "linear_cross_entropy"):
+                raise NotImplementedError("soft-capped logits with a sharded output projection")
+            return ops.linear_cross_entropy(outputs, self._weight(), targets, self.ignore_index, self.num_output_chunks, softcap=self.logit_softcap)
         if proj is not None and hasattr(proj, "linear_cross_entropy"):
             # sharded / tensor-parallel projections own their fused loss
             return proj.linear_cross_entropy(outputs, targets, self.ignore_index, self.num_output_chunks)
         return ops.linear_cross_entropy(outputs, self._weight(), targets, self.ignore_index, self.num_output_chunks)
-
-    def _capped_sum(self, outputs: torch.Tensor, targets: torch.Tensor):
-        """Soft-capped logits (Gemma-2): the cap sits between the projection and the softmax, so the fused kernel (which never
-        forms the logits) does not apply.  Each chunk's logits are formed, capped and reduced inside a checkpoint, so only one
-        chunk of ``[tokens, vocab]`` exists at a time, in forward and in backward."""
-        from torch.utils.checkpoint import checkpoint
-
-        proj = self.linear_projection
-        if hasattr(proj, "linear_cross_entropy"):
-            raise NotImplementedError("soft-capped logits with a sharded output projection")
-        cap, ignore = self.logit_softcap, self.ignore_index
-        weight = self._weight()
-
-        def chunk_sum(h: torch.Tensor, w: torch.Tensor, t: torch.Tensor) -> torch.Tensor:
-            logits = ops.linear(h, w).float()
-            logits = torch.tanh(logits / cap) * cap
-            return torch.nn.functional.cross_entropy(logits, t, ignore_index=ignore, reduction="sum")
-
-        h = outputs.reshape(-1, outputs.shape[-1])
-        t = targets.reshape(-1)
-        total = h.new_zeros((), dtype=torch.float32)
-        for hc, tc in zip(h.tensor_split(self.num_output_chunks), t.tensor_split(self.num_output_chunks)):
-            if hc.shape[0]:
-                total = total + (checkpoint(chunk_sum, hc, weight, tc, use_reentrant=False) if torch.is_grad_enabled() else chunk_sum(hc, weight, tc))
-        return total, (t != ignore).sum()
 
     def forward(self, outputs: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         total, n_valid = self.compute_sum(outputs, targets)

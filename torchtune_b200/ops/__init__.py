@@ -266,13 +266,15 @@ def linear_cross_entropy(
     labels: torch.Tensor,
     ignore_index: int = -100,
     num_chunks: int = 8,
+    softcap: float = 0.0,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
-    """``(sum of CE, number of valid tokens)`` of ``hidden @ weight.T`` vs ``labels``."""
+    """``(sum of CE, number of valid tokens)`` of ``hidden @ weight.T`` vs ``labels``; with ``softcap > 0`` the softmax runs over
+    ``softcap · tanh(logits / softcap)`` (Gemma-2)."""
     if _native(hidden) and weight.dtype == torch.bfloat16:
         from . import _cuda
 
-        return _cuda.linear_cross_entropy(hidden, weight, labels, ignore_index, num_chunks)
-    return reference.linear_cross_entropy(hidden, weight, labels, ignore_index, num_chunks)
+        return _cuda.linear_cross_entropy(hidden, weight, labels, ignore_index, num_chunks, softcap)
+    return reference.linear_cross_entropy(hidden, weight, labels, ignore_index, num_chunks, softcap=softcap)
 
 
 def token_logprobs(

@@ -1187,7 +1187,7 @@ class _LinearCE(torch.autograd.Function):
     only used when the full logits buffer would exceed ``_CE_SINGLE_PASS_BYTES``."""
 
     @staticmethod
-    def forward(ctx, hidden, weight, labels, ignore_index, num_chunks):
+    def forward(ctx, hidden, weight, labels, ignore_index, num_chunks, softcap=0.0):
         D = hidden.shape[-1]
         h2 = hidden.reshape(-1, D)
         if not h2.is_contiguous():
@@ -1215,7 +1215,11 @@ class _LinearCE(torch.autograd.Function):
             lg = buf[:n]
             gemm(hc, weight, out=lg)
             mode = 0 if (need_h or need_w) else 1
-            check(L.ttb_softmax_ce(lg.data_ptr(), y[start : start + n].data_ptr(), loss_rows[start : start + n].data_ptr(), None, n, V, lg.stride(0), int(ignore_index), mode, stream_ptr()), "softmax_ce")
+            if softcap > 0.0:  # Gemma-2: softmax over cap·tanh(logit/cap); the kernel writes the gradient w.r.t. the raw logit
+                check(L.ttb_softmax_ce_capped(lg.data_ptr(), y[start : start + n].data_ptr(), loss_rows[start : start + n].data_ptr(), None, n, V, lg.stride(0), int(ignore_index), mode,
+                                              float(softcap), stream_ptr()), "softmax_ce_capped")
+            else:
+                check(L.ttb_softmax_ce(lg.data_ptr(), y[start : start + n].data_ptr(), loss_rows[start : start + n].data_ptr(), None, n, V, lg.stride(0), int(ignore_index), mode, stream_ptr()), "softmax_ce")
             if need_h:
                 gemm(lg, weight, b_mn=True, out=dh[start : start + n])
             if direct:
@@ -1239,16 +1243,16 @@ class _LinearCE(torch.autograd.Function):
         # only valid for an upstream factor of one (the recipes back-propagate the sum itself).
         gh = (dh * g_loss.to(dh.dtype)).view(ctx.h_shape) if dh is not None else None
         gw = (dw * g_loss).to(ctx.w_dtype) if dw is not None else None
-        return gh, gw, None, None, None
+        return gh, gw, None, None, None, None
 
 
-def linear_cross_entropy(hidden, weight, labels, ignore_index: int, num_chunks: int):
+def linear_cross_entropy(hidden, weight, labels, ignore_index: int, num_chunks: int, softcap: float = 0.0):
     if hidden.shape[-1] % 8 or weight.shape[0] % 8:
         from . import _fallback, reference
 
         _fallback("linear_cross_entropy", f"width {hidden.shape[-1]} or vocabulary {weight.shape[0]} is not a multiple of 8", hidden)
-        return reference.linear_cross_entropy(hidden, weight, labels, ignore_index, num_chunks)
-    return _LinearCE.apply(hidden, weight, labels, ignore_index, num_chunks)
+        return reference.linear_cross_entropy(hidden, weight, labels, ignore_index, num_chunks, softcap=softcap)
+    return _LinearCE.apply(hidden, weight, labels, ignore_index, num_chunks, float(softcap))
 
 
 class _TokenLogprobs(torch.autograd.Function):

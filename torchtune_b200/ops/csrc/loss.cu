@@ -34,10 +34,13 @@ __device__ __forceinline__ void online_merge(float& m, float& s, float m2, float
 
 // mode 0: loss + in-place gradient;  mode 1: loss only;  mode 2: in-place gradient scaled by
 // row_scale[row] of the *negative* loss (i.e. gradient of log p(label)), for DPO backward.
+// CAP: the softmax runs over z = cap · tanh(x / cap) (Gemma-2 logit soft cap) and the gradient written back is the one with
+// respect to the raw logit x: (softmax(z) − onehot) · (1 − (z / cap)²).
+template <bool CAP>
 __global__ void __launch_bounds__(kCEThreads)
 softmax_ce_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restrict__ labels,
                   float* __restrict__ loss_out, const float* __restrict__ row_scale, int rows, int V, long long ld,
-                  long long ignore_index, int mode) {
+                  long long ignore_index, int mode, float cap, float inv_cap) {
   __shared__ float sm_m[kCEThreads / 32], sm_s[kCEThreads / 32];
   __shared__ float sh_m, sh_s;
   const int row = blockIdx.x;
@@ -68,6 +71,10 @@ softmax_ce_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restric
       const float2 t = __bfloat1622float2(b[j]);
       f[2 * j] = t.x, f[2 * j + 1] = t.y;
     }
+    if (CAP) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = cap * tanhf(f[j] * inv_cap);
+    }
     float lm = f[0];
 #pragma unroll
     for (int j = 1; j < 8; ++j) lm = fmaxf(lm, f[j]);
@@ -92,7 +99,11 @@ softmax_ce_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restric
   __syncthreads();
   const float row_max = sh_m;
   const float lse = row_max + __logf(sh_s);
-  if (threadIdx.x == 0 && loss_out != nullptr) loss_out[row] = lse - __bfloat162float(lr[label]);
+  if (threadIdx.x == 0 && loss_out != nullptr) {
+    float at_label = __bfloat162float(lr[label]);
+    if (CAP) at_label = cap * tanhf(at_label * inv_cap);
+    loss_out[row] = lse - at_label;
+  }
   if (mode == 1) return;
   __syncthreads();  // the label logit was read above, before anything is overwritten
 
@@ -103,11 +114,17 @@ softmax_ce_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restric
     const long long c0 = static_cast<long long>(i) * 8;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const float2 t = __bfloat1622float2(b[j]);
+      float2 t = __bfloat1622float2(b[j]);
+      float d0 = 1.f, d1 = 1.f;  // dz/dx
+      if (CAP) {
+        const float u0 = tanhf(t.x * inv_cap), u1 = tanhf(t.y * inv_cap);
+        t.x = cap * u0, t.y = cap * u1;
+        d0 = 1.f - u0 * u0, d1 = 1.f - u1 * u1;
+      }
       float g0 = __expf(t.x - lse), g1 = __expf(t.y - lse);
       if (c0 + 2 * j == label) g0 -= 1.f;
       if (c0 + 2 * j + 1 == label) g1 -= 1.f;
-      b[j] = __floats2bfloat162_rn(g0 * sign_scale, g1 * sign_scale);
+      b[j] = __floats2bfloat162_rn(g0 * d0 * sign_scale, g1 * d1 * sign_scale);
     }
     reinterpret_cast<uint4*>(lr)[i] = u;
   }
@@ -260,8 +277,19 @@ extern "C" int ttb_softmax_ce(void* logits, const long long* labels, float* loss
   if ((V & 7) || (ld & 7)) return kErrBadShape;
   if (rows <= 0) return kOk;
   TTB_COUNT_LAUNCH(1);
-  softmax_ce_kernel<<<rows, kCEThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<__nv_bfloat16*>(logits), labels, loss_out, row_scale, rows, V, ld, ignore_index, mode);
+  softmax_ce_kernel<false><<<rows, kCEThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16*>(logits), labels, loss_out, row_scale, rows, V, ld, ignore_index, mode, 0.f, 0.f);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrDriver;
+}
+
+// The same with the logits soft-capped at `softcap` (> 0) before the softmax; see the kernel.
+extern "C" int ttb_softmax_ce_capped(void* logits, const long long* labels, float* loss_out, const float* row_scale, int rows,
+                                     int V, long long ld, long long ignore_index, int mode, float softcap, void* stream) {
+  if ((V & 7) || (ld & 7) || !(softcap > 0.f)) return kErrBadShape;
+  if (rows <= 0) return kOk;
+  TTB_COUNT_LAUNCH(1);
+  softmax_ce_kernel<true><<<rows, kCEThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16*>(logits), labels, loss_out, row_scale, rows, V, ld, ignore_index, mode, softcap, 1.f / softcap);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrDriver;
 }
 

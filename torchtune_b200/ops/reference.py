@@ -130,8 +130,9 @@ def linear_cross_entropy(
     ignore_index: int = -100,
     num_chunks: int = 8,
     bias: Optional[torch.Tensor] = None,
+    softcap: float = 0.0,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Sum of token cross entropies of ``hidden @ weight.T`` without keeping the
+    """Sum of token cross entropies of ``hidden @ weight.T`` (soft-capped at ``softcap`` when that is positive) without keeping the
     ``[T, V]`` logits: tokens are processed in ``num_chunks`` pieces, logits upcast
     to fp32 (torchtune/modules/loss/cross_entropy_loss.py:87-188).
     Returns ``(loss_sum fp32, n_valid int64)``."""
@@ -142,6 +143,8 @@ def linear_cross_entropy(
         if hc.shape[0] == 0:
             continue
         logits = F.linear(hc, weight, bias).float()
+        if softcap > 0.0:
+            logits = torch.tanh(logits / softcap) * softcap
         total = total + F.cross_entropy(logits, yc, reduction="sum", ignore_index=ignore_index)
     return total, (y != ignore_index).sum()
 

@@ -38,6 +38,7 @@ class EleutherEvalRecipe:
         self.enable_kv_cache = cfg.get("enable_kv_cache", True)
         self.include_path = cfg.get("include_path")
         self.max_seq_length = cfg.get("max_seq_length", 4096)
+        self.apply_chat_template = bool(cfg.get("chat_template", False))
 
     def setup(self, cfg: DictConfig) -> None:
         quantizer = config.instantiate(cfg.quantizer) if cfg.get("quantizer") is not None else None
@@ -72,7 +73,7 @@ class EleutherEvalRecipe:
                 results[str(t)] = (evaluate_multimodal_jsonl if self.multimodal else evaluate_jsonl_task)(self.eval_lm, str(t), self.limit)
         if harness_tasks:
             self.logger.info(f"Running evaluation on the following tasks: {harness_tasks}")
-            out = (run_lm_eval_multimodal if self.multimodal else run_lm_eval)(self.eval_lm, harness_tasks, limit=self.limit, include_path=self.include_path)
+            out = (run_lm_eval_multimodal if self.multimodal else run_lm_eval)(self.eval_lm, harness_tasks, limit=self.limit, include_path=self.include_path, **({"apply_chat_template": True} if self.apply_chat_template else {}))
             results.update(out.get("results", out))
         self.logger.info(f"Eval completed in {time.time() - t0:.02f} seconds.")
         if self.device.type == "cuda":

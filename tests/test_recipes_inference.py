@@ -103,3 +103,20 @@ def test_prompt_to_messages_and_step_visibility():
     dec = CachedDecoder(lambda *a, **k: None, torch.device("cpu"), total=6, temperature=0.0, top_k=None, stop_tokens=[])
     assert dec.visibility(0, 3)[0].tolist() == torch.tril(torch.ones(6, 6, dtype=torch.bool))[:3].tolist()
     assert dec.visibility(4, 1)[0, 0].tolist() == [True] * 5 + [False]
+
+
+def test_eval_lm_chat_template(tmp_path):
+    """The harness' chat mode: turns are wrapped by the tokenizer's prompt template, a generation prompt is opened, and a tokenizer
+    without any template is refused."""
+    (tmp_path / "tok").mkdir(exist_ok=True)
+    sp = write_sentencepiece_model(tmp_path / "tok", vocab_size=200)
+    model = llama2(**ARCH)
+    lm = EvalLM(model, llama2_tokenizer(str(sp)), device=torch.device("cpu"), dtype=torch.float32)  # Llama-2 tokenizers carry the [INST] template
+    text = lm.apply_chat_template([{"role": "system", "content": "be brief"}, {"role": "user", "content": "hello"}])
+    assert text.startswith("[INST] <<SYS>>\nbe brief\n<</SYS>>\n\nhello [/INST]")
+    assert lm.chat_template() == "Llama2ChatTemplate" and lm.tokenizer_name == "Llama2Tokenizer"
+
+    bare = llama2_tokenizer(str(sp), prompt_template=None)
+    bare.prompt_template = None
+    with pytest.raises(ValueError, match="prompt template"):
+        EvalLM(model, bare, device=torch.device("cpu"), dtype=torch.float32).apply_chat_template([{"role": "user", "content": "x"}])

@@ -18,6 +18,22 @@ def log_config(recipe_name: str, cfg: DictConfig) -> None:
         return
     text = OmegaConf.to_yaml(cfg, resolve=True, sort_keys=True)
     get_logger("DEBUG").info(msg=f"Running {recipe_name} with resolved config:\n\n{text}")
+    for key, why in REFERENCE_ONLY_KEYS.items():
+        if key in cfg and cfg.get(key) not in (None, False):
+            get_logger("DEBUG").info(msg=f"config key `{key}` is accepted for configs written for the reference and has no effect here: {why}")
+
+
+# Top-level keys of the reference's recipes that steer machinery this framework does not have.  A config that sets one still runs.
+REFERENCE_ONLY_KEYS: Dict[str, str] = {
+    "fsdp_reshard_after_forward": "the sharded-parameter engine always frees a layer's gathered parameters after use (set `shard_parameters: False` for resident parameters)",
+    "custom_sharded_layers": "every parameter is sharded bucket by bucket, no layer needs a sharding unit of its own",
+    "fsdp_cpu_offload": "parameters, gradients and optimizer state stay in the 180 GB of device memory",
+    "enable_expandable_segments": "the large buffers (flat parameter / gradient stores, peer buffers) are allocated once, outside the caching allocator",
+    "low_cpu_ram": "checkpoints are memory-mapped and copied to the device tensor by tensor",
+    "use_distributed_state_dict": "sharded models load from the full state dict layer by layer",
+    "use_flex": "attention masks are structured descriptions lowered inside the attention kernel",
+    "compile": "the hot path is hand-written kernels; there is no tracing compiler step",
+}
 
 
 def _remove_key_by_dotpath(tree: Dict[str, Any], dotpath: str) -> None:

@@ -34,6 +34,31 @@ class EvalLM:
         self.pad_id = getattr(tokenizer, "pad_id", 0)
         self.eos_id = getattr(tokenizer, "eos_id", None)
 
+    # -- chat formatting (the harness calls these when a task is run with ``apply_chat_template``) -----------------------
+    @property
+    def tokenizer_name(self) -> str:
+        return type(self.tokenizer).__name__
+
+    def chat_template(self, chat_template: Any = False) -> str:
+        """Identifies the template in the harness' result cache; the text itself comes from :meth:`apply_chat_template`."""
+        template = getattr(self.tokenizer, "prompt_template", None)
+        return type(template).__name__ if template is not None else ""
+
+    def apply_chat_template(self, chat_history: List[Dict[str, str]], add_generation_prompt: bool = True) -> str:
+        """One string for a list of ``{"role", "content"}`` turns (parity: recipes/eleuther_eval.py:392-403): the tokenizer's prompt
+        template wraps each turn, or a Hugging Face tokenizer renders its own chat template."""
+        template = getattr(self.tokenizer, "prompt_template", None)
+        if template is not None:
+            from ..data import Message
+
+            turns = [Message(role=t["role"], content=t["content"]) for t in chat_history]
+            if add_generation_prompt and (not turns or turns[-1].role != "assistant"):
+                turns.append(Message(role="assistant", content=""))
+            return "".join(m.text_content for m in template(turns, inference=True))
+        if hasattr(self.tokenizer, "render_template"):
+            return self.tokenizer.render_template(chat_history, add_eos=False)
+        raise ValueError("You can't use a tokenizer without a prompt template and apply_chat_template: True. Use HuggingFaceModelTokenizer if you do not require a custom one.")
+
     # -- tokenisation -------------------------------------------------------------------
     def tok_encode(self, text: str, add_bos: bool = False) -> List[int]:
         return self.tokenizer.encode(text, add_bos=add_bos, add_eos=False)
@@ -182,6 +207,16 @@ def run_lm_eval(lm: EvalLM, tasks: List[str], limit: Optional[int] = None, **kwa
 
         def generate_until(self, requests):
             return lm.generate_until([r.args for r in requests])
+
+        @property
+        def tokenizer_name(self):
+            return lm.tokenizer_name
+
+        def chat_template(self, chat_template=False):
+            return lm.chat_template(chat_template)
+
+        def apply_chat_template(self, chat_history, add_generation_prompt=True):
+            return lm.apply_chat_template(chat_history, add_generation_prompt)
 
     task_dict = get_task_dict(tasks, TaskManager(include_path=kwargs.pop("include_path", None)))
     return evaluate(_Adapter(), task_dict, limit=limit, **kwargs)

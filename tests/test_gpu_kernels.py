@@ -221,6 +221,56 @@ def test_linear_cross_entropy_with_soft_capped_logits(T, D, V, cap):
     _close(w.grad, wr.grad, 5e-2, 3e-4, "capped ce dw")
 
 
+@pytest.mark.parametrize("dtype,n", [(torch.bfloat16, 256 * 64), (torch.bfloat16, 1000 * 7), (torch.float32, 4096 + 8)])
+def test_adamw8bit_kernel_matches_statement(dtype, n):
+    """Five steps of the 8-bit-moment AdamW kernel against the PyTorch statement of the same arithmetic on the same inputs: codes may
+    differ by one step where the fp32 rounding of a square root falls on a tie; parameters stay within bf16 / fp32 rounding."""
+    from torchtune_b200.ops import _cuda
+
+    torch.manual_seed(0)
+    p0 = (torch.randn(n, device="cuda") * 0.1).to(dtype)
+    state = lambda: (torch.zeros(n, dtype=torch.int8, device="cuda"), torch.zeros(n, dtype=torch.uint8, device="cuda"),
+                     torch.zeros((n + 255) // 256, device="cuda"), torch.zeros((n + 255) // 256, device="cuda"))
+    pk, (mq, vq, ms, vs) = p0.clone(), state()
+    pr, (mqr, vqr, msr, vsr) = p0.clone().float(), state()
+    scale = torch.tensor(0.5, device="cuda")
+    for step in range(1, 6):
+        g = (torch.randn(n, device="cuda") * torch.logspace(-3, 0, n, device="cuda")).to(dtype)
+        _cuda.adamw8bit(pk, g, mq, vq, ms, vs, step, 1e-2, 0.9, 0.95, 1e-8, 0.1, scale)
+        # the statement continues from the kernel's state, so that one differing code cannot compound over the steps
+        ref.adamw8bit_step(pr, g.float(), mqr, vqr, msr, vsr, step, 1e-2, 0.9, 0.95, 1e-8, 0.1, 0.5)
+        assert (mq.int() - mqr.int()).abs().max() <= 1 and (vq.int() - vqr.int()).abs().max() <= 1
+        assert ((mq != mqr).float().mean() < 0.01) and ((vq != vqr).float().mean() < 0.01)
+        torch.testing.assert_close(ms, msr, rtol=1e-5, atol=0)
+        torch.testing.assert_close(vs, vsr, rtol=1e-5, atol=0)
+        torch.testing.assert_close(pk.float(), pr.to(dtype).float(), rtol=2e-2 if dtype == torch.bfloat16 else 1e-5, atol=1e-6)
+        mqr.copy_(mq), vqr.copy_(vq), msr.copy_(ms), vsr.copy_(vs), pr.copy_(pk.float())
+    m, v = ref.adamw8bit_decode(mq, vq, ms, vs, n)
+    assert torch.isfinite(m).all() and torch.isfinite(v).all() and (v >= 0).all() and float(m.abs().max()) > 0
+
+
+def test_adamw8bit_optimizer_trains_a_bf16_layer():
+    from torchtune_b200.optim import AdamW8bit
+
+    torch.manual_seed(0)
+    x = torch.randn(512, 256, device="cuda", dtype=torch.bfloat16)
+    w_true = torch.randn(256, 128, device="cuda", dtype=torch.bfloat16) * 0.2
+    y = x @ w_true
+    results = {}
+    for name, cls in (("fp", torch.optim.AdamW), ("q", AdamW8bit)):
+        torch.manual_seed(1)
+        w = torch.nn.Parameter(torch.zeros(256, 128, device="cuda", dtype=torch.bfloat16))
+        opt = cls([w], lr=3e-3, weight_decay=0.0)
+        for _ in range(300):
+            loss = ((x @ w - y).float() ** 2).mean()
+            opt.zero_grad()
+            loss.backward()
+            opt.step()
+        results[name] = (loss.item(), opt)
+    assert results["q"][0] < 1.5 * results["fp"][0] + 1e-3, (results["q"][0], results["fp"][0])
+    assert results["q"][1].state_bytes() == 256 * 128 * 2 + 128 * 8
+
+
 def test_token_logprobs():
     T, D, V = 200, 256, 2048
     h = _rand(T, D, seed=1).requires_grad_()

@@ -14,6 +14,17 @@ from ._errors import InstantiationError
 
 _ALIASES = {"torchtune": "torchtune_b200"}
 
+# Components of packages that are not part of this framework and have a built-in counterpart.  They are used only when the named
+# package cannot be imported: with it installed, the config gets exactly what it names.
+_STAND_INS = {
+    "bitsandbytes.optim.PagedAdamW8bit": "torchtune_b200.optim.AdamW8bit",
+    "bitsandbytes.optim.AdamW8bit": "torchtune_b200.optim.AdamW8bit",
+    "bitsandbytes.optim.PagedAdamW": "torchtune_b200.optim.AdamW",
+    "torchao.optim.AdamW8bit": "torchtune_b200.optim.AdamW8bit",
+    "torchao.optim.AdamW4bit": "torchtune_b200.optim.AdamW8bit",
+    "torchao.optim.AdamWFp8": "torchtune_b200.optim.AdamW8bit",
+}
+
 
 def _alias(path: str) -> str:
     head, _, tail = path.partition(".")
@@ -58,6 +69,11 @@ def get_component_from_path(path: str, caller_globals: Optional[Dict[str, Any]] 
     try:
         module = importlib.import_module(module_name)
     except ImportError as exc:
+        if path in _STAND_INS:
+            import logging
+
+            logging.getLogger(__name__).warning(f"{path} is not installed: using {_STAND_INS[path]} in its place")
+            return get_component_from_path(_STAND_INS[path], caller_globals)
         # allow "pkg.module.Class.method"-style paths one level deep
         if len(pieces) > 2:
             try:

@@ -1361,6 +1361,16 @@ def adamw_multi(items, lr: float, beta1: float, beta2: float, eps: float, weight
         check(lib().ttb_adamw(tbl.dev.data_ptr(), tbl.n, tbl.chunks, int(dtype == _BF16), lr, beta1, beta2, eps, weight_decay, inv_bc1, inv_sqrt_bc2, _ptr(scale_dev), scale_host, stream_ptr()), "adamw")
 
 
+def adamw8bit(p: torch.Tensor, g: torch.Tensor, mq: torch.Tensor, vq: torch.Tensor, mscale: torch.Tensor, vscale: torch.Tensor, step: int, lr: float, beta1: float,
+              beta2: float, eps: float, weight_decay: float, grad_scale: Union[float, torch.Tensor] = 1.0) -> None:
+    """AdamW update of one tensor whose moments are stored as one-byte codes with a scale per 256 elements (``optim.cu``)."""
+    if p.dtype not in (_BF16, torch.float32) or g.dtype != p.dtype or not p.is_contiguous() or not g.is_contiguous():
+        raise _lib.KernelError("adamw8bit needs contiguous bf16/fp32 params with same-dtype grads")
+    scale_dev, scale_host = (grad_scale.to(torch.float32).reshape(1), 1.0) if isinstance(grad_scale, torch.Tensor) else (None, float(grad_scale))
+    check(lib().ttb_adamw8bit(p.data_ptr(), g.data_ptr(), mq.data_ptr(), vq.data_ptr(), mscale.data_ptr(), vscale.data_ptr(), p.numel(), int(p.dtype == _BF16), lr, beta1, beta2,
+                              eps, weight_decay, 1.0 / (1.0 - beta1**step), 1.0 / math.sqrt(1.0 - beta2**step), _ptr(scale_dev), scale_host, stream_ptr()), "adamw8bit")
+
+
 def grad_sumsq(items, tag: int = 1) -> torch.Tensor:
     """Sum of squared gradient entries over all items (0-d fp32 tensor, no host sync)."""
     groups: Dict[torch.dtype, list] = {}

@@ -55,6 +55,7 @@ def _declare(L: ctypes.CDLL) -> None:
     L.ttb_swiglu_fwd.argtypes = [vp, vp, vp, i64, i32, i64, i64, i64, vp]
     L.ttb_swiglu_bwd.argtypes = [vp, vp, vp, vp, vp, i64, i32, i64, i64, i64, i64, i64, vp]
     L.ttb_adamw.argtypes = [vp, i32, i64, i32, f32, f32, f32, f32, f32, f32, f32, vp, f32, vp]
+    L.ttb_adamw8bit.argtypes = [vp, vp, vp, vp, vp, vp, i64, i32, f32, f32, f32, f32, f32, f32, f32, vp, f32, vp]
     L.ttb_grad_sumsq.argtypes = [vp, i32, i64, i32, vp, vp]
     L.ttb_softmax_ce.argtypes = [vp, vp, vp, vp, i32, i32, i64, i64, i32, vp]
     L.ttb_softmax_ce_capped.argtypes = [vp, vp, vp, vp, i32, i32, i64, i64, i32, ctypes.c_float, vp]

@@ -4,6 +4,7 @@
     python -m torchtune_b200.ops.microbench attention --batch 4 --seq 2048 --doc 512
     python -m torchtune_b200.ops.microbench rmsnorm --rows 8192 --dim 4096
     python -m torchtune_b200.ops.microbench adamw --numel 268435456
+    python -m torchtune_b200.ops.microbench adamw8bit --numel 268435456
     python -m torchtune_b200.ops.microbench gate_up --tokens 8192 --dim 4096 --hidden 14336
     python -m torchtune_b200.ops.microbench comm --world 8 --numel 268435456             (peer-memory kernels, ranks emulated on one GPU)
     python -m torchtune_b200.ops.microbench suite --tokens 8192      (norm, RoPE, SwiGLU, loss, embedding, LoRA, grouped GEMM, NF4, offload copies)
@@ -180,6 +181,25 @@ def bench_adamw(args, flush):
     t = _time(run, args.iters, args.warmup, flush)
     nbytes = n * (2 + 2 + 2 + 4 * 2)  # p r/w, g r, m and v r/w (all bf16)
     return {"op": "adamw", "numel": n, "ms": t, "gbs": nbytes / t / 1e6}
+
+
+def bench_adamw8bit(args, flush):
+    from ._cuda import adamw8bit
+
+    n = args.numel
+    p = torch.randn(n, device="cuda", dtype=torch.bfloat16)
+    g = torch.randn(n, device="cuda", dtype=torch.bfloat16)
+    mq, vq = torch.zeros(n, device="cuda", dtype=torch.int8), torch.zeros(n, device="cuda", dtype=torch.uint8)
+    ms, vs = torch.zeros((n + 255) // 256, device="cuda"), torch.zeros((n + 255) // 256, device="cuda")
+    step = [0]
+
+    def run():
+        step[0] += 1
+        adamw8bit(p, g, mq, vq, ms, vs, step[0], 1e-4, 0.9, 0.999, 1e-8, 0.01)
+
+    t = _time(run, args.iters, args.warmup, flush)
+    nbytes = n * (2 * 2 + 2 + 2 * 2) + 4 * ms.numel() * 4  # p r/w, g r, one-byte codes of both moments r/w, block scales r/w
+    return {"op": "adamw8bit", "numel": n, "ms": t, "gbs": nbytes / t / 1e6, "state_bytes_per_param": 2 + 8 / 256}
 
 
 def bench_gate_up(args, flush):
@@ -420,6 +440,8 @@ def main() -> None:
     r.add_argument("--dim", type=int, default=4096)
     o = sub.add_parser("adamw")
     o.add_argument("--numel", type=int, default=1 << 28)
+    o8 = sub.add_parser("adamw8bit")
+    o8.add_argument("--numel", type=int, default=1 << 28)
     gu = sub.add_parser("gate_up")
     gu.add_argument("--tokens", type=int, default=8192)
     gu.add_argument("--dim", type=int, default=4096)
@@ -433,7 +455,7 @@ def main() -> None:
     from ._lib import check_device_errors
 
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
-    fn = {"gemm": bench_gemm, "gemm_fp8": bench_gemm_fp8, "gemm_mxfp8": bench_gemm_mxfp8, "attention": bench_attention, "rmsnorm": bench_rmsnorm, "adamw": bench_adamw, "gate_up": bench_gate_up, "comm": bench_comm, "suite": bench_suite}[args.op]
+    fn = {"gemm": bench_gemm, "gemm_fp8": bench_gemm_fp8, "gemm_mxfp8": bench_gemm_mxfp8, "attention": bench_attention, "rmsnorm": bench_rmsnorm, "adamw": bench_adamw, "adamw8bit": bench_adamw8bit, "gate_up": bench_gate_up, "comm": bench_comm, "suite": bench_suite}[args.op]
     res = fn(args, flush)
     check_device_errors()
     print(json.dumps(res), flush=True)

@@ -169,6 +169,44 @@ def token_logprobs(
     return torch.cat(outs).view(shape)
 
 
+ADAMW8BIT_BLOCK = 256
+
+
+def adamw8bit_decode(mq: torch.Tensor, vq: torch.Tensor, mscale: torch.Tensor, vscale: torch.Tensor, numel: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """fp32 moments from their one-byte codes: ``m = sign(q)·(|q|/127)²·scale`` and ``v = (q/255)⁴·scale`` with one scale per block
+    of 256 elements (the block's largest magnitude)."""
+    idx = torch.arange(numel, device=mq.device) // ADAMW8BIT_BLOCK
+    um = mq.float().abs() / 127.0
+    m = torch.sign(mq.float()) * um * um * mscale[idx]
+    uv = vq.float() / 255.0
+    v = (uv * uv) * (uv * uv) * vscale[idx]
+    return m, v
+
+
+def adamw8bit_step(p: torch.Tensor, g: torch.Tensor, mq: torch.Tensor, vq: torch.Tensor, mscale: torch.Tensor, vscale: torch.Tensor, step: int, lr: float,
+                   beta1: float, beta2: float, eps: float, weight_decay: float, grad_scale: float = 1.0) -> None:
+    """AdamW with 8-bit moments (flat views of all tensors; statement of ``optim.cu::adamw8bit_kernel``)."""
+    n = p.numel()
+    pf, gf = p.reshape(-1).float(), g.reshape(-1).float() * grad_scale
+    m, v = adamw8bit_decode(mq, vq, mscale, vscale, n)
+    m = beta1 * m + (1 - beta1) * gf
+    v = beta2 * v + (1 - beta2) * gf * gf
+    bc1, bc2 = 1 - beta1**step, 1 - beta2**step
+    pf = pf * (1 - lr * weight_decay) - (lr / bc1) * m / (v.sqrt() / math.sqrt(bc2) + eps)
+    nb = mscale.numel()
+    pad = nb * ADAMW8BIT_BLOCK - n
+    m_max = torch.nn.functional.pad(m.abs(), (0, pad)).view(nb, -1).amax(1)
+    v_max = torch.nn.functional.pad(v, (0, pad)).view(nb, -1).amax(1)
+    idx = torch.arange(n, device=p.device) // ADAMW8BIT_BLOCK
+    inv_m = torch.where(m_max > 0, 1.0 / m_max, torch.zeros_like(m_max))[idx]
+    inv_v = torch.where(v_max > 0, 1.0 / v_max, torch.zeros_like(v_max))[idx]
+    mq.copy_((torch.sign(m) * torch.round(127.0 * (m.abs() * inv_m).sqrt())).to(torch.int8))
+    vq.copy_(torch.round(255.0 * (v * inv_v).sqrt().sqrt()).to(torch.uint8))
+    mscale.copy_(m_max)
+    vscale.copy_(v_max)
+    p.copy_(pf.view_as(p))
+
+
 def adamw_step(
     p: torch.Tensor,
     g: torch.Tensor,

@@ -2,6 +2,7 @@
 linear-CE, HF-safetensors save and reload with identical logits; then resume equivalence."""
 from pathlib import Path
 
+import pytest
 import torch
 
 from helpers import TINY, read_losses, run_tune, write_tiny_hf_checkpoint
@@ -65,6 +66,35 @@ def test_tiny_llama_cpu_10_steps_and_hf_round_trip(tmp_path, tune_path, monkeypa
     sd2 = again.load_checkpoint()["model"]
     for k, v in reloaded.state_dict().items():
         assert torch.equal(v, sd2[k]), k
+
+
+def test_config_naming_an_8bit_optimizer_of_an_absent_package_trains_and_resumes(tmp_path, tune_path, monkeypatch):
+    """A config written for the reference's low-memory recipe names `bitsandbytes.optim.PagedAdamW8bit`; without that package the
+    built-in 8-bit AdamW takes its place, trains, and its coded state survives a checkpoint."""
+    try:
+        import bitsandbytes  # noqa: F401
+
+        pytest.skip("bitsandbytes is installed here")
+    except ImportError:
+        pass
+    ckpt = tmp_path / "ckpt"
+    write_tiny_hf_checkpoint(ckpt)
+    base = (f"run full_finetune_single_device --config tiny/llama_full_single_device checkpointer.checkpoint_dir={ckpt} metric_logger.filename=log.txt "
+            "optimizer._component_=bitsandbytes.optim.PagedAdamW8bit optimizer.lr=1e-3 max_steps_per_epoch=3 epochs=2 dataset.num_samples=12 ")
+    run_tune(tune_path, base + f"output_dir={tmp_path / 'run'}", monkeypatch)
+    losses = read_losses(tmp_path / "run" / "logs" / "log.txt")
+    assert len(losses) == 6 and losses[-1] < losses[0]
+    state = torch.load(tmp_path / "run" / "epoch_0" / "recipe_state.pt", weights_only=False)
+    kinds = {v.dtype for st in state["optimizer"]["state"].values() for k, v in st.items() if isinstance(v, torch.Tensor) and k.endswith("_q")}
+    assert kinds == {torch.int8, torch.uint8}
+    # the second epoch again, from the checkpoint of the first: the same losses
+    import shutil
+
+    shutil.rmtree(tmp_path / "run" / "epoch_1")
+    (tmp_path / "run" / "logs" / "log.txt").unlink()
+    run_tune(tune_path, base + f"output_dir={tmp_path / 'run'} resume_from_checkpoint=True", monkeypatch)
+    resumed = read_losses(tmp_path / "run" / "logs" / "log.txt")
+    torch.testing.assert_close(torch.tensor(resumed), torch.tensor(losses[3:]), rtol=1e-5, atol=1e-5)
 
 
 def test_resume_matches_uninterrupted(tmp_path, tune_path, monkeypatch):

@@ -103,3 +103,16 @@ def test_stands_in_for_packages_that_are_not_installed():
         assert isinstance(opt, AdamW8bit) and opt.param_groups[0]["lr"] == 2e-5
     with pytest.raises(config.InstantiationError if hasattr(config, "InstantiationError") else Exception):
         config.instantiate(config.OmegaConf.create({"_component_": "bitsandbytes.optim.SomethingElse"}))
+
+
+def test_host_offload_wrapper_of_an_absent_package_builds_the_inner_optimizer_on_the_device():
+    try:
+        import torchao  # noqa: F401
+
+        pytest.skip("torchao is installed here")
+    except ImportError:
+        pass
+    cfg = config.OmegaConf.create({"optimizer": {"_component_": "torchao.optim.CPUOffloadOptimizer", "optimizer_class": "torch.optim.AdamW", "offload_gradients": True, "lr": 3e-4}})
+    p = torch.nn.Parameter(torch.zeros(4))
+    opt = config.instantiate(cfg.optimizer, [p])
+    assert type(opt) is torch.optim.AdamW and opt.param_groups[0]["lr"] == 3e-4

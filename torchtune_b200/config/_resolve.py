@@ -23,6 +23,7 @@ _STAND_INS = {
     "torchao.optim.AdamW8bit": "torchtune_b200.optim.AdamW8bit",
     "torchao.optim.AdamW4bit": "torchtune_b200.optim.AdamW8bit",
     "torchao.optim.AdamWFp8": "torchtune_b200.optim.AdamW8bit",
+    "torchao.optim.CPUOffloadOptimizer": "torchtune_b200.optim.resident_optimizer",
 }
 
 

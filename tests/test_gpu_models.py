@@ -101,6 +101,61 @@ def test_llama4_tiny_train_step_bf16():
     assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in model.parameters())
 
 
+def test_llama3_1_bf16_on_native_kernels_matches_transformers_fp32():
+    """The flagship architecture end to end on the sm_100a kernels (bf16, head dim 128, grouped-query attention, scaled rotary
+    embedding) against the `transformers` implementation in fp32 on the same random weights."""
+    transformers = pytest.importorskip("transformers")
+    from torchtune_b200.models.convert_weights import hf_to_tune
+    from torchtune_b200.models.llama3_1 import llama3_1
+
+    torch.manual_seed(0)
+    cfg = transformers.LlamaConfig(vocab_size=4096, hidden_size=512, intermediate_size=1024, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                                   max_position_embeddings=16384, rms_norm_eps=1e-5, rope_theta=500000.0, tie_word_embeddings=False,
+                                   rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0, original_max_position_embeddings=8192))
+    hf = transformers.LlamaForCausalLM(cfg).eval().float().cuda()
+    with torch.device("cuda"):
+        mine = llama3_1(vocab_size=4096, num_layers=2, num_heads=4, num_kv_heads=2, embed_dim=512, max_seq_len=1024, intermediate_dim=1024, rope_base=500000, scale_factor=8)
+    mine.load_state_dict(hf_to_tune({k: v for k, v in hf.state_dict().items()}, num_heads=4, num_kv_heads=2, dim=512))
+    mine = mine.to(torch.bfloat16).eval()
+    tokens = torch.randint(0, 4096, (2, 512), device="cuda")
+    with torch.no_grad():
+        want = hf(input_ids=tokens).logits
+        got = mine(tokens)
+    assert _rel_err(got, want) < 3e-2
+    assert (got.float().argmax(-1) == want.argmax(-1)).float().mean() > 0.9
+
+
+def test_gemma2_tiny_bf16_capped_loss_matches_capped_logits():
+    """Gemma-2 on the native kernels (head dim 128, soft-capped attention scores, sliding window on even layers): the loss taken
+    from the hidden states — soft cap inside the fused linear + cross-entropy kernel — equals cross entropy over the decoder's own
+    capped logits, and so do the gradients."""
+    from torchtune_b200.models.gemma2 import gemma2
+    from torchtune_b200.modules.loss import LinearCrossEntropyLoss
+
+    torch.manual_seed(0)
+    with torch.device("cuda"):
+        model = gemma2(vocab_size=4096, num_layers=2, num_heads=4, head_dim=128, num_kv_heads=2, embed_dim=512, intermediate_dim=1024, max_seq_len=512,
+                       hidden_capping_value=50.0, final_capping_value=30.0, sliding_window_size=128).to(torch.bfloat16)
+    with torch.no_grad():
+        model.tok_embeddings.weight.mul_(30.0)  # drives the logits onto the flat part of the tanh
+    tokens = torch.randint(0, 4096, (2, 256), device="cuda")
+    labels = torch.randint(0, 4096, (2, 256), device="cuda")
+    labels[:, :5] = -100
+    logits = model(tokens)
+    assert float(logits.detach().abs().max()) <= 30.0 and float(logits.detach().abs().max()) > 25.0
+    want = F.cross_entropy(logits.float().reshape(-1, 4096), labels.reshape(-1), ignore_index=-100)
+    want.backward()
+    want_grad = model.layers[0].mlp.w1.weight.grad.float().clone()
+    model.zero_grad()
+    loss_fn = LinearCrossEntropyLoss()
+    loss_fn.set_model_output(model)
+    assert loss_fn.logit_softcap == 30.0
+    got = loss_fn(model(tokens), labels)
+    got.backward()
+    assert abs(got.item() - want.item()) < 2e-3 * abs(want.item())
+    assert _rel_err(model.layers[0].mlp.w1.weight.grad, want_grad) < 2e-2
+
+
 @pytest.mark.parametrize("rank,dropout_input", [(8, False), (64, True)])
 def test_lora_linear_fused_matches_reference(rank, dropout_input):
     g = torch.Generator(device="cuda").manual_seed(0)

@@ -271,18 +271,23 @@ def test_adamw8bit_optimizer_trains_a_bf16_layer():
     assert results["q"][1].state_bytes() == 256 * 128 * 2 + 128 * 8
 
 
-def test_token_logprobs():
+@pytest.mark.parametrize("cap,scale", [(0.0, 0.05), (3.0, 0.4)])
+def test_token_logprobs(cap, scale):
+    """``cap > 0``: log-softmax over cap·tanh(logits/cap) (Gemma-2), with weights large enough to put logits on the curved part."""
     T, D, V = 200, 256, 2048
     h = _rand(T, D, seed=1).requires_grad_()
-    w = _rand(V, D, seed=2, scale=0.05)
+    w = _rand(V, D, seed=2, scale=scale)
     labels = torch.randint(0, V, (4, 50), device="cuda")
     labels[:, :10] = -100
-    lp = ops.token_logprobs(h.view(4, 50, D), w, labels, -100, 4)
+    lp = ops.token_logprobs(h.view(4, 50, D), w, labels, -100, 4, softcap=cap)
     g = _rand(4, 50, seed=3, dtype=torch.float32)
     (lp * g).sum().backward()
     hr = h.detach().float().requires_grad_()
-    lpr = ref.token_logprobs(hr.view(4, 50, D), w.float(), labels, -100, 4)
+    lpr = ref.token_logprobs(hr.view(4, 50, D), w.float(), labels, -100, 4, softcap=cap)
     (lpr * g).sum().backward()
+    if cap:
+        plain = ref.token_logprobs(hr.detach().view(4, 50, D), w.float(), labels, -100, 4)
+        assert (plain - lpr.detach()).abs().max() > 0.5  # the cap changes these values, so the comparison below means something
     _close(lp, lpr, 1e-2, 2e-2, "logprobs")
     _close(h.grad, hr.grad, 5e-2, 5e-3, "logprobs dh")
 

@@ -160,3 +160,60 @@ def test_gemma2_logit_cap_in_the_fused_loss_and_the_reference_graph():
     assert set(ref_graph.state_dict()) == set(model.state_dict())
     hidden = ref_graph.norm(torch.randn(1, 3, 64) * 50)
     assert float(hidden.abs().max()) <= 2.0
+
+
+def test_every_consumer_of_hidden_states_applies_the_logit_cap():
+    """Several paths skip the decoder's output layer and project hidden states themselves (preference optimisation, evaluation
+    log-likelihoods, early-exit loss, distillation, the GRPO loss).  With a soft-capped decoder each must give what the decoder's own
+    capped logits give."""
+    import torch.nn.functional as F
+
+    from torchtune_b200 import ops, rlhf
+    from torchtune_b200.dev.rl import LinearGRPOLoss
+    from torchtune_b200.engine.preference import sequence_logprobs
+    from torchtune_b200.models.gemma2 import gemma2
+    from torchtune_b200.modules.early_exit_loss import early_exit_loss, uniform_loss_scale
+
+    kw = dict(**_T, head_dim=32, num_kv_heads=2, hidden_capping_value=20.0, final_capping_value=2.0, sliding_window_size=8, query_pre_attn_scalar=24)
+    torch.manual_seed(0)
+    model = gemma2(**kw).eval()
+    with torch.no_grad():
+        model.tok_embeddings.weight.mul_(40.0)
+    tokens = torch.randint(0, 128, (2, 12))
+    labels = tokens.clone()
+    labels[:, :3] = -100
+    assert ops.logit_softcap_of(model) == 2.0
+
+    with torch.no_grad():
+        logits = model(tokens)
+        model.skip_output_layer = True
+        hidden = model(tokens)
+        model.skip_output_layer = False
+    uncapped = F.linear(hidden, model.tok_embeddings.weight)
+    assert float(uncapped.abs().max()) > 4.0 and float(logits.abs().max()) <= 2.0  # the cap matters here
+
+    # preference optimisation
+    want = rlhf.get_batch_log_probs(logits, labels, label_pad_token_id=-100)
+    got, _ = sequence_logprobs(model, tokens, labels)
+    assert torch.allclose(got, want, atol=1e-4)
+
+    # operator level, and the GRPO loss built on it
+    lp = ops.token_logprobs(hidden[:, :-1], model.tok_embeddings.weight, labels[:, 1:], -100, 4, softcap=2.0)
+    ref_lp = torch.log_softmax(logits[:, :-1].float(), -1).gather(-1, labels[:, 1:].clamp_min(0).unsqueeze(-1)).squeeze(-1) * (labels[:, 1:] != -100)
+    assert torch.allclose(lp, ref_lp, atol=1e-5)
+    grpo = LinearGRPOLoss()
+    grpo.set_model_output(model)
+    model.skip_output_layer = False
+    assert grpo.logit_softcap == 2.0
+    out = grpo(hidden[:, :-1], labels[:, 1:].clamp_min(0), ref_lp, torch.ones(2), padding_masks=labels[:, 1:] != -100)
+    assert torch.allclose(out[-1] * (labels[:, 1:] != -100), ref_lp, atol=1e-5)
+
+    # early-exit loss over the last layer only equals plain cross entropy over the capped logits
+    with torch.no_grad():
+        pre_norm = model.layers[1](model.layers[0](model.tok_embeddings(tokens), mask=model.layers[0].mask_mod(None, 2, 12)))
+        ee = early_exit_loss(model, {1: pre_norm}, labels, torch.nn.CrossEntropyLoss(ignore_index=-100), loss_scale_fn=uniform_loss_scale)
+    ce = F.cross_entropy(logits.reshape(-1, 128), labels.reshape(-1), ignore_index=-100)
+    assert torch.allclose(ee, ce, atol=1e-4)
+
+    # what distillation uses for both student and teacher
+    assert torch.allclose(model.unembed_normed(hidden), logits, atol=1e-5)

@@ -31,6 +31,7 @@ class LinearGRPOLoss(nn.Module):
     def set_model_output(self, model: nn.Module) -> None:
         model.skip_output_layer = True
         self.linear_projection = model.output
+        self.logit_softcap = ops.logit_softcap_of(model)
 
     def _weight(self) -> torch.Tensor:
         proj = self.linear_projection
@@ -52,7 +53,8 @@ class LinearGRPOLoss(nn.Module):
         targets = pi_outputs
         if self.mask_pre_projection:  # ignored positions cost no softmax work and get a log-probability of exactly zero
             targets = torch.where(keep, pi_outputs, torch.full_like(pi_outputs, self.ignore_index))
-        logp = ops.token_logprobs(pi_old_outputs, self._weight(), targets, ignore_index=self.ignore_index, num_chunks=self.num_output_chunks).float()
+        logp = ops.token_logprobs(pi_old_outputs, self._weight(), targets, ignore_index=self.ignore_index, num_chunks=self.num_output_chunks,
+                                  softcap=getattr(self, "logit_softcap", 0.0)).float()
         ref = ref_outputs.detach().float()
         d = ref - logp
         kl = torch.exp(d) - d - 1

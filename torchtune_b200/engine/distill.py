@@ -77,8 +77,9 @@ class KDTrainer(SFTTrainer):
             hs = _trunk(self._model, batch)
         with torch.no_grad():
             ht = _trunk(self._teacher_model, batch)
-        self._student_out = getattr(self._model, "decoder", self._model).output
-        self._teacher_out = getattr(self._teacher_model, "decoder", self._teacher_model).output
+        # projection of already normalised hidden states, with whatever the decoder does to its logits (Gemma-2 soft cap)
+        self._student_out = getattr(self._model, "decoder", self._model).unembed_normed
+        self._teacher_out = getattr(self._teacher_model, "decoder", self._teacher_model).unembed_normed
         hs2, ht2, y = hs.reshape(-1, hs.shape[-1]), ht.reshape(-1, ht.shape[-1]), labels.reshape(-1)
         ce_sum = hs.new_zeros((), dtype=torch.float32)
         kd_sum = hs.new_zeros((), dtype=torch.float32)

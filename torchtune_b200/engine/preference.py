@@ -61,7 +61,7 @@ def sequence_logprobs(model: nn.Module, tokens: torch.Tensor, labels: torch.Tens
         hidden = model(tokens, **fwd)
     finally:
         core.skip_output_layer = prev
-    per_token = ops.token_logprobs(hidden[:, :-1].contiguous(), weight, labels[:, 1:].contiguous(), ignore_index)
+    per_token = ops.token_logprobs(hidden[:, :-1].contiguous(), weight, labels[:, 1:].contiguous(), ignore_index, softcap=ops.logit_softcap_of(core))
     with torch.no_grad():
         mean_logit = hidden.detach().float().mean(dim=1) @ weight.detach().float().mean(dim=0)
     return per_token.sum(-1), mean_logit

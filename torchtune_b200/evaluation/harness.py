@@ -105,7 +105,7 @@ class EvalLM:
                 core.skip_output_layer = prev
             weight = core.output.weight if hasattr(core.output, "weight") else core.output.tied_module.weight
             h, y = hidden[:, :-1].contiguous(), labels[:, 1:].contiguous()
-            logp = ops.token_logprobs(h, weight, y, -100)
+            logp = ops.token_logprobs(h, weight, y, -100, softcap=ops.logit_softcap_of(core))
             sums = logp.sum(-1).tolist()
             # greedy check on the continuation positions only
             mask = y != -100

@@ -55,7 +55,7 @@ def early_exit_loss(model, hidden_states_dict: Dict[int, torch.Tensor], labels: 
     n_valid = (labels != ignore).sum().clamp_min(1)
     losses = []
     for h in hidden_states_dict.values():
-        total, _ = ops.linear_cross_entropy(model.norm(h), weight, labels, ignore_index=ignore, num_chunks=8)
+        total, _ = ops.linear_cross_entropy(model.norm(h), weight, labels, ignore_index=ignore, num_chunks=8, softcap=ops.logit_softcap_of(model))
         losses.append(total.float() / n_valid)
     losses = torch.stack(losses)
     scales = loss_scale_fn(torch.tensor(ids, dtype=torch.float32, device=losses.device), len(model.layers), e_scale)

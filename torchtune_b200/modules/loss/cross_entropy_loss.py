@@ -32,8 +32,7 @@ class LinearCrossEntropyLoss(nn.Module, SFTLoss):
     def set_model_output(self, model: nn.Module) -> None:
         model.skip_output_layer = True
         self.linear_projection = model.output
-        decoder = getattr(model, "decoder", model)  # a fusion model keeps the cap on its decoder
-        self.logit_softcap = float(getattr(decoder, "logit_softcap", 0.0) or 0.0)
+        self.logit_softcap = ops.logit_softcap_of(model)  # a fusion model keeps the cap on its decoder
 
     def patch_tp_plan(self, tp_plan) -> dict:
         self.tp_enabled = True

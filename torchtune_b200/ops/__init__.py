@@ -278,13 +278,21 @@ def linear_cross_entropy(
 
 
 def token_logprobs(
-    hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100, num_chunks: int = 8
+    hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100, num_chunks: int = 8, softcap: float = 0.0
 ) -> torch.Tensor:
+    """Per-token ``log_softmax(hidden @ weight.T)[label]``; with ``softcap > 0`` over ``softcap · tanh(logits / softcap)``."""
     if _native(hidden) and weight.dtype == torch.bfloat16:
         from . import _cuda
 
-        return _cuda.token_logprobs(hidden, weight, labels, ignore_index, num_chunks)
-    return reference.token_logprobs(hidden, weight, labels, ignore_index, num_chunks)
+        return _cuda.token_logprobs(hidden, weight, labels, ignore_index, num_chunks, softcap)
+    return reference.token_logprobs(hidden, weight, labels, ignore_index, num_chunks, softcap=softcap)
+
+
+def logit_softcap_of(model) -> float:
+    """The soft cap a decoder applies to its logits (0 = none); callers that take hidden states and do the output projection
+    themselves pass it on to :func:`linear_cross_entropy` / :func:`token_logprobs`."""
+    core = getattr(model, "decoder", model)
+    return float(getattr(core, "logit_softcap", 0.0) or 0.0)
 
 
 def logits_logprobs(logits: torch.Tensor, tokens: torch.Tensor, temperature: float = 1.0) -> Optional[torch.Tensor]:

@@ -1255,12 +1255,21 @@ def linear_cross_entropy(hidden, weight, labels, ignore_index: int, num_chunks: 
     return _LinearCE.apply(hidden, weight, labels, ignore_index, num_chunks, float(softcap))
 
 
+def _softmax_ce(buf, labels, loss_out, row_scale, n, V, ignore_index, mode, softcap=0.0):
+    """One launch of the softmax / cross-entropy kernel over ``buf[:n]`` (see ``loss.cu``), with the logits soft-capped when asked."""
+    args = (buf.data_ptr(), labels.data_ptr(), _ptr(loss_out), _ptr(row_scale), n, V, buf.stride(0), int(ignore_index), mode)
+    if softcap > 0.0:
+        check(lib().ttb_softmax_ce_capped(*args, float(softcap), stream_ptr()), "softmax_ce_capped")
+    else:
+        check(lib().ttb_softmax_ce(*args, stream_ptr()), "softmax_ce")
+
+
 class _TokenLogprobs(torch.autograd.Function):
     """Per-token log p(label) through the output projection; backward recomputes each logits
     chunk and scales the in-place softmax gradient by the incoming per-token gradient."""
 
     @staticmethod
-    def forward(ctx, hidden, weight, labels, ignore_index, num_chunks):
+    def forward(ctx, hidden, weight, labels, ignore_index, num_chunks, softcap=0.0):
         D = hidden.shape[-1]
         h2 = hidden.reshape(-1, D).contiguous()
         y = labels.reshape(-1).to(torch.int64).contiguous()
@@ -1271,9 +1280,10 @@ class _TokenLogprobs(torch.autograd.Function):
         for start in range(0, T, rows):
             n = min(rows, T - start)
             gemm(h2[start : start + n], weight, out=buf[:n])
-            check(lib().ttb_softmax_ce(buf.data_ptr(), y[start : start + n].data_ptr(), nll[start : start + n].data_ptr(), None, n, V, buf.stride(0), int(ignore_index), 1, stream_ptr()), "softmax_ce")
+            _softmax_ce(buf, y[start : start + n], nll[start : start + n], None, n, V, ignore_index, 1, softcap)
         ctx.save_for_backward(h2, weight, y)
         ctx.meta = (ignore_index, rows, hidden.shape, labels.shape)
+        ctx.softcap = float(softcap)
         return (-nll).view(labels.shape)
 
     @staticmethod
@@ -1290,15 +1300,15 @@ class _TokenLogprobs(torch.autograd.Function):
             n = min(rows, T - start)
             hc = h2[start : start + n]
             gemm(hc, weight, out=buf[:n])
-            check(lib().ttb_softmax_ce(buf.data_ptr(), y[start : start + n].data_ptr(), None, gs[start : start + n].data_ptr(), n, V, buf.stride(0), int(ignore_index), 2, stream_ptr()), "softmax_ce")
+            _softmax_ce(buf, y[start : start + n], None, gs[start : start + n], n, V, ignore_index, 2, ctx.softcap)
             gemm(buf[:n], weight, b_mn=True, out=dh[start : start + n])
             if need_w:
                 gemm(buf[:n], hc, a_mn=True, b_mn=True, out=dw, accumulate=True)
-        return dh.view(h_shape), (dw.to(weight.dtype) if need_w else None), None, None, None
+        return dh.view(h_shape), (dw.to(weight.dtype) if need_w else None), None, None, None, None
 
 
-def token_logprobs(hidden, weight, labels, ignore_index: int, num_chunks: int):
-    return _TokenLogprobs.apply(hidden, weight, labels, ignore_index, num_chunks)
+def token_logprobs(hidden, weight, labels, ignore_index: int, num_chunks: int, softcap: float = 0.0):
+    return _TokenLogprobs.apply(hidden, weight, labels, ignore_index, num_chunks, float(softcap))
 
 
 # ======================================================================= optimizer

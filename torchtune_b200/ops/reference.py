@@ -150,7 +150,7 @@ def linear_cross_entropy(
 
 
 def token_logprobs(
-    hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100, num_chunks: int = 8
+    hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100, num_chunks: int = 8, softcap: float = 0.0
 ) -> torch.Tensor:
     """Per-token ``log_softmax(hidden @ weight.T)[label]`` (0 where ignored) without the
     full logits tensor; the building block of the DPO sequence log-prob
@@ -163,6 +163,8 @@ def token_logprobs(
         if hc.shape[0] == 0:
             continue
         logits = F.linear(hc, weight).float()
+        if softcap > 0.0:
+            logits = torch.tanh(logits / softcap) * softcap
         valid = yc != ignore_index
         lp = torch.log_softmax(logits, -1).gather(-1, yc.clamp_min(0).unsqueeze(-1)).squeeze(-1)
         outs.append(torch.where(valid, lp, torch.zeros_like(lp)))

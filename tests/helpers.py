@@ -55,3 +55,15 @@ def run_tune(tune_path: str, argv: str, monkeypatch) -> None:
 
 def read_losses(log_file: Path):
     return [float(m) for m in re.findall(r"loss:(\S+)", Path(log_file).read_text())]
+
+
+def tiny_early_fusion_llama4():
+    """A Llama-4-shaped early-fusion model small enough for CPU tests (configs name it as ``helpers.tiny_early_fusion_llama4``)."""
+    from torchtune_b200.models.llama4 import llama4_decoder, llama4_vision_encoder
+    from torchtune_b200.modules.model_fusion import EarlyFusionModel
+
+    decoder = llama4_decoder(vocab_size=72, num_layers=2, num_heads=4, num_kv_heads=2, embed_dim=32, hidden_dim=48, max_seq_len=64, num_experts=4, experts_per_token=1, rope_base=10000,
+                             skip_rope_interval=2, attention_chunk_size=16)
+    tower = llama4_vision_encoder(patch_size=4, num_heads=4, clip_embed_dim=32, clip_num_layers=1, clip_hidden_states=None, projection_embed_dim=48, decoder_embed_dim=32, tile_size=16,
+                                  max_num_tiles=1, in_channels=3)
+    return EarlyFusionModel(decoder, encoders={"vision": tower}, encoder_tokens={"vision": 70})

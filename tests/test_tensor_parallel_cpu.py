@@ -220,3 +220,56 @@ def test_tp_fp8_decoder_tracks_single_process_fp8():
     rowwise = convert_to_float8_training(llama3_1(**ARCH), "rowwise")
     with pytest.raises(ValueError, match="tensorwise"):
         tensor_parallelize(rowwise, TensorParallelContext(torch.device("cpu"), max_rows_per_rank=8, max_width=48))
+
+
+# ----------------------------------------------------------------------------- tensor-parallel generation of an early-fusion model
+def _fusion_reference():
+    from helpers import tiny_early_fusion_llama4
+
+    torch.manual_seed(5)
+    model = tiny_early_fusion_llama4()
+    fixed_init_(model, std=0.1)
+    return model.eval()
+
+
+def _fusion_inputs():
+    g = torch.Generator().manual_seed(9)
+    tokens = torch.randint(0, 64, (2, 12), generator=g)
+    tokens[0, 2:6] = 70
+    tokens[1, 4:8] = 70
+    return tokens, torch.randn(2, 3, 16, 16, generator=g)
+
+
+def _fusion_worker(rank, world, port, results, state_dict):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from torchtune_b200.config import OmegaConf
+        from torchtune_b200.engine.inference import SingleTurnGenerator
+
+        gen = SingleTurnGenerator.__new__(SingleTurnGenerator)  # the part of the generator that builds the model, without a recipe around it
+        gen._device, gen._dtype, gen._tp = torch.device("cpu"), torch.float32, None
+        model = gen._build_tensor_parallel(OmegaConf.create({"model": {"_component_": "helpers.tiny_early_fusion_llama4"}}), state_dict)
+        tokens, images = _fusion_inputs()
+        with torch.no_grad():
+            logits = model(tokens, encoder_input={"vision": {"images": images}})
+        local = model.decoder.tp_decoder.layers[0].mlp.experts.gate_proj
+        results[rank] = dict(logits=logits, expert_cols=local.shape[-1], meta_left=[n for n, p in model.named_parameters() if p.is_meta])
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tp_generation_model_of_an_early_fusion_model_is_built_layer_by_layer():
+    world = 2
+    reference = _fusion_reference()
+    state = {k: v.clone() for k, v in reference.state_dict().items()}
+    results = mp.Manager().dict()
+    mp.spawn(_fusion_worker, args=(world, 29651, results, state), nprocs=world, join=True)
+    tokens, images = _fusion_inputs()
+    with torch.no_grad():
+        want = reference(tokens, encoder_input={"vision": {"images": images}})
+    for rank in range(world):
+        r = results[rank]
+        assert not r["meta_left"]
+        assert r["expert_cols"] == 48 // world  # the experts' columns are split, the vision tower is whole
+        torch.testing.assert_close(r["logits"].float(), want.float(), rtol=1e-4, atol=1e-4)

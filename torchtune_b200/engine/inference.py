@@ -117,25 +117,40 @@ class SingleTurnGenerator:
 
     def setup(self, cfg: DictConfig) -> None:
         ckpt = config.instantiate(cfg.checkpointer).load_checkpoint()
-        with training.set_default_dtype(self._dtype), self._device:
-            model = config.instantiate(cfg.model)
-        model.load_state_dict(ckpt[training.MODEL_KEY])
-        model = model.eval()
         if self._tensor_parallel:
-            from ..parallel.tp import TensorParallelContext
-            from ..parallel.tp_model import tensor_parallelize
-
-            decoder = model.decoder if isinstance(model, EarlyFusionModel) else model
-            self._tp = TensorParallelContext(self._device, max_rows_per_rank=128, max_width=decoder.tok_embeddings.embedding_dim)
-            sliced = tensor_parallelize(decoder, self._tp).eval()
-            if isinstance(model, EarlyFusionModel):
-                model.decoder = _TPDecoderShim(sliced)  # encoders stay whole on every rank; the decoder is split
-            else:
-                model = sliced
+            model = self._build_tensor_parallel(cfg, ckpt[training.MODEL_KEY])
+        else:
+            with training.set_default_dtype(self._dtype), self._device:
+                model = config.instantiate(cfg.model)
+            model.load_state_dict(ckpt[training.MODEL_KEY])
+            model = model.eval()
         self.model = model
         self.model_transform = config.instantiate(cfg.tokenizer)
         if self._rank == 0:
             self._logger.info(f"Model was initialized with precision {self._dtype}" + (f" over {self._tp.world} ranks." if self._tp is not None else "."))
+
+    def _build_tensor_parallel(self, cfg: DictConfig, state_dict: Dict[str, Any]) -> nn.Module:
+        """The model is built without storage and the decoder is given storage and values layer by layer while it is split, so a
+        decoder larger than one GPU (Llama-4 Scout: 218 GB in bf16) never exists in full on a rank; the encoders of an early-fusion
+        model stay whole on every rank."""
+        from ..parallel.tp import TensorParallelContext
+        from ..parallel.tp_model import tensor_parallelize
+        from ..training._distributed import LayerwisePreparer
+
+        with training.set_default_dtype(self._dtype), torch.device("meta"):
+            model = config.instantiate(cfg.model)
+        fusion = isinstance(model, EarlyFusionModel)
+        decoder = model.decoder if fusion else model
+        decoder_state = {k[len("decoder."):]: v for k, v in state_dict.items() if k.startswith("decoder.")} if fusion else state_dict
+        self._tp = TensorParallelContext(self._device, max_rows_per_rank=128, max_width=decoder.tok_embeddings.embedding_dim)
+        sliced = tensor_parallelize(decoder, self._tp, prepare_layer=LayerwisePreparer(self._device, state_dict=decoder_state)).eval()
+        if not fusion:
+            return sliced
+        whole = LayerwisePreparer(self._device, state_dict=state_dict)
+        for name, encoder in model.encoders.items():
+            whole(encoder, f"encoders.{name}.")
+        model.decoder = _TPDecoderShim(sliced)
+        return model.eval()
 
     # ------------------------------------------------------------------ batches
     def _multimodal_extras(self, inputs: Dict[str, Any], seq_len: int):

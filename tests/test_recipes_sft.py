@@ -297,9 +297,7 @@ def test_lora_distributed_sharded_base_matches_resident(tmp_path):
 @pytest.mark.timeout(900)
 def test_qlora_distributed_sharded_nf4_base_matches_resident(tmp_path):
     """QLoRA with shard_parameters=True: the model is built without storage, every rank keeps half of each 4-bit base weight
-    (codes and block scales), gathers and expands it per use.  The first loss (adapters still inactive: ``lora_b`` starts at zero)
-    must equal QLoRA with a resident 4-bit base; later ones follow it closely — the two builds draw ``lora_a`` from different points
-    of the random stream, because only the resident build also draws throw-away base weights."""
+    (codes and block scales), gathers and expands it per use.  Losses and adapters must follow QLoRA with a resident 4-bit base."""
     ckpt = tmp_path / "ckpt"
     write_tiny_hf_checkpoint(ckpt)
     common = [f"checkpointer.checkpoint_dir={ckpt}", "metric_logger.filename=log.txt", "dataset.num_samples=16", "max_steps_per_epoch=3", "optimizer.lr=1e-2", "clip_grad_norm=1.0",
@@ -312,9 +310,9 @@ def test_qlora_distributed_sharded_nf4_base_matches_resident(tmp_path):
         )
         losses[name] = read_losses(tmp_path / name / "logs" / "log.txt")
     assert len(losses["z3"]) == 3
-    assert abs(losses["z3"][0] - losses["dp"][0]) < 2e-4
-    torch.testing.assert_close(torch.tensor(losses["z3"]), torch.tensor(losses["dp"]), rtol=1e-2, atol=1e-2)
-    assert losses["z3"][-1] < losses["z3"][0]
+    torch.testing.assert_close(torch.tensor(losses["z3"]), torch.tensor(losses["dp"]), rtol=2e-4, atol=2e-4)
     a = load_file(str(tmp_path / "dp" / "epoch_0" / "adapter_model.safetensors"))
     b = load_file(str(tmp_path / "z3" / "epoch_0" / "adapter_model.safetensors"))
-    assert set(a) == set(b) and all(a[k].shape == b[k].shape for k in a)
+    assert set(a) == set(b)
+    for k in a:
+        torch.testing.assert_close(a[k], b[k], rtol=1e-3, atol=2e-5)

@@ -64,3 +64,46 @@ def test_sharded_linear_weights_match_single_process():
         assert set(r["sd"]) == set(sd)
         for k in sd:
             assert torch.equal(r["sd"][k], sd[k]), k
+
+
+def test_fusion_model_built_without_storage_is_sharded_from_the_checkpoint():
+    """Llama-3.2-Vision-shaped model on the meta device: every linear weight goes from the checkpoint straight into a shard (fusion
+    layers keep the ``layer.`` level out of their state-dict keys, which the sharding has to look through), the rest is given
+    storage and loaded afterwards, and the result computes what the ordinary model computes."""
+    from torchtune_b200.models.llama3_2_vision import llama3_2_vision_decoder, llama3_2_vision_encoder
+    from torchtune_b200.modules.model_fusion import DeepFusionModel
+    from torchtune_b200.training._distributed import materialize
+
+    def build():
+        enc = llama3_2_vision_encoder(patch_size=4, num_heads=4, clip_embed_dim=32, clip_num_layers=2, clip_hidden_states=[1], num_layers_projection=1, decoder_embed_dim=64, tile_size=16,
+                                      max_num_tiles=4, in_channels=3)
+        dec = llama3_2_vision_decoder(vocab_size=128, num_layers=4, fusion_interval=2, num_special_tokens=8, num_heads=4, num_kv_heads=2, embed_dim=64, max_seq_len=64, encoder_max_seq_len=68,
+                                      rope_base=500000, intermediate_dim=96)
+        return DeepFusionModel(encoder=enc, decoder=dec)
+
+    torch.manual_seed(0)
+    whole = build().eval()
+    with torch.no_grad():
+        for name, p in whole.named_parameters():
+            if p.numel() == 1:
+                p.fill_(0.7)  # open the gates
+    state = {k: v.clone() for k, v in whole.state_dict().items()}
+
+    with torch.device("meta"):
+        late = build()
+    late = shard_linear_weights(late, torch.device("cpu"), min_numel=1, state_dict=state)
+    fused_layer = late.decoder.layers[1]
+    assert isinstance(fused_layer.layer.attn.q_proj, ShardedLinear) and isinstance(fused_layer.fusion_layer.attn.q_proj, ShardedLinear)
+    assert "decoder.layers.1.attn.q_proj.weight" in late._sharded_keys  # found under the key without `layer.`
+    rest = {k: v for k, v in state.items() if k not in late._sharded_keys}
+    materialize(late, torch.device("cpu"))
+    missing, unexpected = late.load_state_dict(rest, strict=False)
+    assert not unexpected and set(missing) <= late._sharded_keys, (missing, unexpected)
+    late.refresh_replicated()
+    assert not any(p.is_meta for p in late.parameters())
+
+    tokens = torch.randint(0, 128, (2, 9))
+    images = torch.randn(2, 1, 4, 3, 16, 16)
+    kwargs = dict(encoder_input={"images": images, "aspect_ratio": torch.tensor([[[2, 2]], [[2, 2]]])}, encoder_mask=torch.ones(2, 9, 68, dtype=torch.bool))
+    with torch.no_grad():
+        torch.testing.assert_close(late.eval()(tokens, **kwargs), whole(tokens, **kwargs), rtol=1e-5, atol=1e-5)

@@ -227,7 +227,10 @@ class SFTTrainer:
                     and (int(cfg.get("tensor_parallel_dim", 1) or 1) > 1 or int(cfg.get("expert_parallel_dim", 1) or 1) > 1))
         # … and for a sharded 4-bit base (QLoRA with `shard_parameters`): the whole base may not fit one GPU either
         sharded = cfg.get("shard_parameters", False) and str(cfg.get("shard_parameters")).lower() not in ("false", "none", "0", "")
-        deferred = deferred or bool(self.is_lora and self.parallel is not None and sharded and (cfg.model.get("quantize_base", False) or "qlora" in str(cfg.model.get("_component_", ""))))
+        # … and for sharded frozen bases (LoRA / QLoRA with `shard_parameters`) and `shard_parameters: linear`: the whole base may not
+        # fit one GPU either, so each rank copies its rows of every weight from the checkpoint straight into its shard
+        linear_only = str(cfg.get("shard_parameters", "")).lower() == "linear"
+        deferred = deferred or bool(self.parallel is not None and sharded and (self.is_lora or linear_only) and not cfg.get("resize_token_embeddings"))
         with training.set_default_dtype(self._dtype), (torch.device("meta") if deferred else self._device):
             model = config.instantiate(cfg.model)
         if cfg.get("resize_token_embeddings") and self._tokenizer_vocab(cfg) is not None:

@@ -170,12 +170,14 @@ class _WeightGatherLinear(torch.autograd.Function):
 class ShardedLinear(nn.Module):
     """``nn.Linear`` whose weight rows are split over the ranks (``weight``: this rank's ``[out / world, in]`` rows)."""
 
-    def __init__(self, lin: nn.Linear, sw: ShardedWeightContext):
+    def __init__(self, lin: nn.Linear, sw: ShardedWeightContext, shard: Optional[torch.Tensor] = None):
+        """``shard``: this rank's rows when ``lin`` has no storage (a model built on the meta device)."""
         super().__init__()
         self.sw = sw
         self.in_features, self.out_features = lin.in_features, lin.out_features
         rows = lin.out_features // sw.world
-        shard = lin.weight.data[sw.rank * rows : (sw.rank + 1) * rows]
+        if shard is None:
+            shard = lin.weight.data[sw.rank * rows : (sw.rank + 1) * rows]
         self.weight = nn.Parameter(sw.place(shard), requires_grad=lin.weight.requires_grad)
         self.bias = lin.bias
 
@@ -192,12 +194,14 @@ class ShardedLoRALinear(nn.Module):
     base weights through FSDP (recipes/lora_finetune_distributed.py:548); this is what lets a 70B bf16 base fit next to
     activations."""
 
-    def __init__(self, lora: nn.Module, sw: ShardedWeightContext):
+    def __init__(self, lora: nn.Module, sw: ShardedWeightContext, shard: Optional[torch.Tensor] = None):
         super().__init__()
         self.sw = sw
         self.rank, self.alpha, self.in_dim, self.out_dim, self.use_bias = lora.rank, lora.alpha, lora.in_dim, lora.out_dim, lora.use_bias
         rows = lora.out_dim // sw.world
-        self.weight = nn.Parameter(sw.place(lora.weight.data[sw.rank * rows : (sw.rank + 1) * rows]), requires_grad=False)
+        if shard is None:
+            shard = lora.weight.data[sw.rank * rows : (sw.rank + 1) * rows]
+        self.weight = nn.Parameter(sw.place(shard), requires_grad=False)
         self.bias = lora.bias
         self.dropout, self.lora_a, self.lora_b = lora.dropout, lora.lora_a, lora.lora_b
         self.merged = False
@@ -205,6 +209,13 @@ class ShardedLoRALinear(nn.Module):
 
     def adapter_params(self):
         return ["lora_a.weight", "lora_b.weight"]
+
+    def initialize_parameters(self) -> None:
+        """Adapter initialisation for a module whose adapters were given storage after construction (meta-device build)."""
+        from ..modules.peft.lora import _lora_a_init_params, _lora_b_init_params
+
+        _lora_a_init_params(self.lora_a)
+        _lora_b_init_params(self.lora_b)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         from .. import ops
@@ -259,11 +270,17 @@ def shard_nf4_bases(model: nn.Module, device: torch.device, group=None, *, min_n
     return cut
 
 
-def shard_linear_weights(model: nn.Module, device: torch.device, group=None, *, min_numel: int = 1 << 16, exclude=("output",)) -> nn.Module:
+def shard_linear_weights(model: nn.Module, device: torch.device, group=None, *, min_numel: int = 1 << 16, exclude=("output",),
+                         state_dict: Optional[Dict[str, torch.Tensor]] = None) -> nn.Module:
     """Replace every plain ``nn.Linear`` (and every dense-base ``LoRALinear``) with at least ``min_numel`` weights whose rows split
     evenly into whole n-tiles by a :class:`ShardedLinear` (:class:`ShardedLoRALinear`) (in place; module paths in ``exclude`` and
     the small adapter matrices inside LoRA modules are left alone) and attach ``_replicated``, ``sync_replicated_grads()``, ``after_optimizer_step()`` and
-    ``full_state_dict()`` (checkpoint layout; collective) to ``model``."""
+    ``full_state_dict()`` (checkpoint layout; collective) to ``model``.
+
+    A model built on the meta device is sharded without ever holding a whole weight on the device: with ``state_dict`` (the full
+    checkpoint, model-level keys) each target's rows for this rank are copied from there straight into the store, one weight at a
+    time; ``model._sharded_keys`` then names the checkpoint keys that have been consumed, and everything else is still to be
+    given storage and loaded by the caller."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     shard_nf4_bases(model, device, group, min_numel=min_numel)  # 4-bit bases: parts of the codes, gathered and expanded per use
 
@@ -281,14 +298,46 @@ def shard_linear_weights(model: nn.Module, device: torch.device, group=None, *, 
     # the output projection stays whole: the fused linear + cross-entropy loss reads its weight directly
     targets = [(parent, name, child) for pname, parent in model.named_modules() if not callable(getattr(parent, "adapter_params", None))
                for name, child in parent.named_children() if eligible(child) and (f"{pname}.{name}" if pname else name) not in exclude]
+    paths = {id(child): (f"{pname}.{name}" if pname else name) for pname, parent in model.named_modules() for name, child in parent.named_children()}
+
+    def checkpoint_key(child: nn.Module) -> Optional[str]:
+        """Key of this module's weight in ``state_dict``: its module path, or that path without the ``layer.`` level that fusion
+        layers leave out of their state dicts."""
+        if state_dict is None:
+            return None
+        key = paths[id(child)] + ".weight"
+        for cand in (key, key.replace(".layer.", ".")):
+            if cand in state_dict:
+                return cand
+        return None
+
+    # a weight without storage can only be sharded from a checkpoint value; one that has none stays whole (the caller gives it
+    # storage and loads it like any other parameter)
+    targets = [t for t in targets if not t[2].weight.is_meta or checkpoint_key(t[2]) is not None]
     store = sum(((c.weight.numel() // world) + 7) // 8 * 8 for _, _, c in targets)
     sw = ShardedWeightContext(device, group, store_numel=store, max_weight_numel=max((c.weight.numel() for _, _, c in targets), default=8),
                               max_out_features=max((_dims(c)[0] for _, _, c in targets), default=64))
+    consumed = set()
     for parent, name, child in targets:
-        setattr(parent, name, ShardedLinear(child, sw) if isinstance(child, nn.Linear) else ShardedLoRALinear(child, sw))
-        child.weight.data = torch.empty(0, dtype=child.weight.dtype, device=child.weight.device)
+        shard = None
+        if child.weight.is_meta:
+            key = checkpoint_key(child)
+            rows = _dims(child)[0] // world
+            rank = dist.get_rank(group) if dist.is_initialized() else 0
+            shard = state_dict[key][rank * rows : (rank + 1) * rows].to(device=device, dtype=child.weight.dtype)
+            consumed.update((key, paths[id(child)] + ".weight"))  # as the checkpoint names it and as load_state_dict reports it
+        setattr(parent, name, ShardedLinear(child, sw, shard) if isinstance(child, nn.Linear) else ShardedLoRALinear(child, sw, shard))
+        if not child.weight.is_meta:
+            child.weight.data = torch.empty(0, dtype=child.weight.dtype, device=child.weight.device)
+    model._sharded_keys = consumed
     sharded = {id(m.weight) for m in model.modules() if isinstance(m, (ShardedLinear, ShardedLoRALinear))}
-    model._replicated = [p for p in model.parameters() if id(p) not in sharded]
+    def refresh_replicated() -> None:
+        """Parameters that every rank holds whole.  Giving a meta-device parameter storage makes a new parameter object, so a
+        caller that materialises the rest of the model after the sharding calls this again."""
+        model._replicated = [p for p in model.parameters() if id(p) not in sharded]
+
+    refresh_replicated()
+    model.refresh_replicated = refresh_replicated
     model._sw = sw
 
     def sync_replicated_grads() -> None:

@@ -329,17 +329,23 @@ class ParallelStrategy(DataParallelEngine):
             if self.dims.tp_enabled:
                 return self._shard_model_tp(model, cfg, layerwise)
             return self._shard_model_ep(model, cfg, layerwise)
-        if is_lora and self._shard_parameters and any(b.is_meta for b in model.buffers()):
-            # a 4-bit base larger than one GPU: its parts get storage before anything else does, so that the whole never exists here
-            from .fsdp import shard_nf4_bases
+        presharded = None
+        if self._shard_parameters and not self._wants_full_sharding(cfg, is_lora) and any(t.is_meta for t in list(model.parameters()) + list(model.buffers())):
+            # a base larger than one GPU (dense or 4-bit): this rank's rows of every weight go from the checkpoint straight into the
+            # peer-visible store (parts of a 4-bit base get their storage) before anything else exists, so no whole weight ever does
+            from .fsdp import shard_linear_weights
 
             get_ = cfg.get if hasattr(cfg, "get") else (lambda k, d=None: d)
-            shard_nf4_bases(model, self.device, None, min_numel=int(get_("shard_parameters_min_numel", 1 << 16)))
+            model = shard_linear_weights(model, self.device, None, min_numel=int(get_("shard_parameters_min_numel", 1 << 16)), state_dict=base_sd)
+            presharded = set(model._sharded_keys)
+            base_sd = {k: v for k, v in base_sd.items() if k not in presharded}
         materialize(model, self.device)
         if is_lora:
             from ..modules.peft import validate_missing_and_unexpected_for_lora
 
             base_missing, base_unexpected = model.load_state_dict(base_sd, strict=False)
+            if presharded:
+                base_missing = [k for k in base_missing if k not in presharded]
             lora_missing = lora_unexpected = None
             if adapter_sd is not None:
                 lora_missing, lora_unexpected = model.load_state_dict(adapter_sd, strict=False)
@@ -347,12 +353,27 @@ class ParallelStrategy(DataParallelEngine):
                 state_dict_keys=list(model.state_dict().keys()), base_missing=base_missing, base_unexpected=base_unexpected, lora_missing=lora_missing, lora_unexpected=lora_unexpected
             )
             if adapter_sd is None:
+                # fresh adapters are drawn here, in module order from the job's seed, so that their values do not depend on how the
+                # model came to exist (built on the device, where the throw-away base weights also consume random numbers, or on
+                # the meta device)
+                with torch.random.fork_rng(devices=[self.device] if self.device.type == "cuda" else []):
+                    torch.manual_seed(torch.initial_seed())
+                    for m in model.modules():
+                        if callable(getattr(m, "adapter_params", None)) and callable(getattr(m, "initialize_parameters", None)):
+                            m.initialize_parameters()
                 for m in model.modules():
                     if hasattr(m, "initialize_dora_magnitude"):
                         m.initialize_dora_magnitude()
+        elif presharded:
+            missing, unexpected = model.load_state_dict(base_sd, strict=False)
+            left = [k for k in missing if k not in presharded]
+            if left or unexpected:
+                raise RuntimeError(f"checkpoint does not match the model: missing {left[:4]}, unexpected {list(unexpected)[:4]}")
         else:
             model.load_state_dict(base_sd, strict=True)
         validate_no_params_on_meta_device(model)
+        if presharded is not None:
+            model.refresh_replicated()
         if self.dims.tp_enabled:
             if is_lora:
                 raise NotImplementedError("tensor parallelism is implemented for full fine-tuning")
@@ -387,7 +408,8 @@ class ParallelStrategy(DataParallelEngine):
             from .fsdp import shard_linear_weights
 
             get = cfg.get if hasattr(cfg, "get") else (lambda k, d=None: d)
-            model = shard_linear_weights(model, self.device, None, min_numel=int(get("shard_parameters_min_numel", 1 << 16)))
+            if presharded is None:
+                model = shard_linear_weights(model, self.device, None, min_numel=int(get("shard_parameters_min_numel", 1 << 16)))
             self.zero3 = model._sw
             if is_lora and self.world > 1:
                 # adapters are initialised with rank-dependent seeds: rank 0's values win

@@ -81,7 +81,15 @@ def materialize(model: nn.Module, device: torch.device) -> nn.Module:
     """Give storage to a model built under ``torch.device('meta')`` and rebuild derived
     buffers (RoPE tables, KV caches keep their lazily-built state)."""
     if any(p.is_meta for p in model.parameters()) or any(b.is_meta for b in model.buffers()):
-        model.to_empty(device=device)
+        # only what has no storage yet: tensors that already live somewhere (shards placed in a peer-visible store, parts of a
+        # 4-bit base) keep their storage and their values
+        for module in model.modules():
+            for name, p in list(module._parameters.items()):
+                if p is not None and p.is_meta:
+                    module._parameters[name] = torch.nn.Parameter(torch.empty_like(p, device=device), requires_grad=p.requires_grad)
+            for name, b in list(module._buffers.items()):
+                if b is not None and b.is_meta:
+                    module._buffers[name] = torch.empty_like(b, device=device)
         with device:
             for m in model.modules():
                 if hasattr(m, "rope_init"):

@@ -127,3 +127,19 @@ def test_dataset_builders_on_local_json(tmp_path):
     pref.write_text(json.dumps([{"chosen": [{"role": "user", "content": "q q"}, {"role": "assistant", "content": "good"}], "rejected": [{"role": "user", "content": "q q"}, {"role": "assistant", "content": "bad one"}]}]))
     p = preference_dataset(WordTokenizer(), source="json", data_files=str(pref), split="train")[0]
     assert p["chosen_labels"][:3] == [-100, -100, -100] and p["chosen_labels"][3] == 4 and len(p["rejected_input_ids"]) == 6
+
+
+def test_torchdata_guards(monkeypatch):
+    from torchtune_b200.data import _torchdata
+
+    @_torchdata.requires_torchdata
+    def build():
+        return "built"
+
+    monkeypatch.setattr(_torchdata, "_installed", lambda: True)
+    assert build() == "built" and build.__name__ == "build"
+    monkeypatch.setattr(_torchdata, "_installed", lambda: False)
+    import pytest as _pytest
+
+    with _pytest.raises(ImportError, match="torchdata"):
+        build()

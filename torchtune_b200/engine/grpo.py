@@ -141,7 +141,8 @@ class GRPOTrainer:
         self._model.setup_caches(batch_size=b * g, dtype=self._dtype, decoder_max_seq_len=ctx + self._max_generated_tokens)
         try:
             query_responses, _ = generation.generate(model=self._model, prompt=batch, max_generated_tokens=self._max_generated_tokens, temperature=self._temperature, top_k=self._top_k,
-                                                     pad_id=self._pad_id, rng=self._rng, stop_tokens=self._stop_token_ids.tolist() or None)
+                                                     pad_id=self._pad_id, rng=self._rng, stop_tokens=self._stop_token_ids.tolist() or None,
+                                                     return_logits=False)  # log-probabilities are recomputed below; no [b, n, vocab] tensor is kept
         finally:
             delete_kv_caches(self._model)
         not_pad = query_responses != self._pad_id

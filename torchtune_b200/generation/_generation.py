@@ -115,7 +115,7 @@ def generate(
     first_mask = masks[:, :prompt_len] if incremental else masks[:, :prompt_len, :prompt_len]
     tokens, logits = generate_next_token(model, input_pos=input_pos[:, :prompt_len].squeeze(), mask=first_mask, x=prompt, temperature=temperature, top_k=top_k, q=draw_q())
     out_tokens = torch.cat([prompt, tokens], dim=-1)
-    all_logits = logits if return_logits else None
+    logit_steps = [logits] if return_logits else None  # joined once at the end: joining every step copies the whole history each time
     pos = prompt_len
 
     def everyone_done(flags: torch.Tensor) -> bool:
@@ -131,7 +131,7 @@ def generate(
     if stop is not None:
         reached = update_stop_tokens_tracker(tokens, stop, reached)
         if everyone_done(reached):
-            return out_tokens, all_logits
+            return out_tokens, (logits if return_logits else None)
 
     step_fn = custom_generate_next_token or generate_next_token
     for _ in range(max_generated_tokens - 1):
@@ -144,13 +144,14 @@ def generate(
         tokens, logits = step_fn(model, input_pos=cur_pos, x=x, mask=cur_mask, temperature=temperature, top_k=top_k, q=draw_q())
         out_tokens = torch.cat([out_tokens, tokens], dim=-1)
         if return_logits:
-            all_logits = torch.cat([all_logits, logits], dim=1)
+            logit_steps.append(logits)
         pos += 1
         if stop is not None:
             reached = update_stop_tokens_tracker(tokens, stop, reached)
             if everyone_done(reached):
                 break
 
+    all_logits = torch.cat(logit_steps, dim=1) if return_logits else None
     if stop is not None:
         out_tokens = out_tokens * keep + pad_id * (1 - keep) if keep.shape == out_tokens.shape else out_tokens
         if return_logits:

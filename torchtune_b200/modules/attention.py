@@ -91,6 +91,10 @@ class MultiHeadAttention(nn.Module):
             logger.warning("Key value caches are already setup. You cannot call ``setup_caches()`` twice. Skipping.")
             return
         self.kv_cache = KVCache(batch_size, max_seq_len, self.num_kv_heads, self.head_dim, dtype)
+        # a cache created outside a device context lands on the CPU; it belongs where this module's weights are
+        home = next((t.device for t in list(self.parameters()) + list(self.buffers()) if t.device.type != "meta"), None)
+        if home is not None and home.type != "cpu" and self.kv_cache.k_cache.device.type == "cpu":
+            self.kv_cache.to(home)
         self.cache_enabled = True
 
     def reset_cache(self) -> None:

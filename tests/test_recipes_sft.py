@@ -243,7 +243,8 @@ def test_full_distributed_sharded_parameters_matches_data_parallel(tmp_path):
     write_tiny_hf_checkpoint(ckpt)
     common = [f"checkpointer.checkpoint_dir={ckpt}", "metric_logger.filename=log.txt", "max_steps_per_epoch=3", "dataset.num_samples=16", "clip_grad_norm=1.0", "optimizer.lr=1e-3"]
     losses = {}
-    for name, port, extra in (("dp", 29539, []), ("z3", 29540, ["shard_parameters=True"]), ("lin", 29541, ["shard_parameters=linear", "shard_parameters_min_numel=1"])):
+    for name, port, extra in (("dp", 29539, []), ("z3", 29540, ["shard_parameters=True"]), ("lin", 29541, ["shard_parameters=linear", "shard_parameters_min_numel=1"]),
+                              ("z3meta", 29542, ["shard_parameters=True", "shard_parameters_layerwise=True"])):
         res = _tune_subprocess(
             ["run", "--nnodes=1", "--nproc_per_node=2", "--master-addr=127.0.0.1", f"--master-port={port}", "full_finetune_distributed", "--config", "tiny/llama_full_distributed"]
             + common + [f"output_dir={tmp_path / name}"] + extra
@@ -251,7 +252,7 @@ def test_full_distributed_sharded_parameters_matches_data_parallel(tmp_path):
         (tmp_path / f"{name}.out").write_text(res.stdout + res.stderr)
         losses[name] = read_losses(tmp_path / name / "logs" / "log.txt")
     a = load_file(str(tmp_path / "dp" / "epoch_0" / "model-00001-of-00001.safetensors"))
-    for name in ("z3", "lin"):
+    for name in ("z3", "lin", "z3meta"):
         assert len(losses[name]) == 3
         torch.testing.assert_close(torch.tensor(losses[name]), torch.tensor(losses["dp"]), rtol=2e-4, atol=2e-4)
         b = load_file(str(tmp_path / name / "epoch_0" / "model-00001-of-00001.safetensors"))
@@ -259,6 +260,7 @@ def test_full_distributed_sharded_parameters_matches_data_parallel(tmp_path):
         for k in a:
             torch.testing.assert_close(a[k], b[k], rtol=1e-3, atol=2e-5)
     assert "every trainable parameter is sharded" in (tmp_path / "z3.out").read_text()
+    assert "built layer by layer" in (tmp_path / "z3meta.out").read_text()  # the model had no storage until each bucket was cut
 
 
 def test_early_exit_recipe_runs_and_rotates_exits(tmp_path, tune_path, monkeypatch):

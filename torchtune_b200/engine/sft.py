@@ -230,7 +230,8 @@ class SFTTrainer:
         # … and for sharded frozen bases (LoRA / QLoRA with `shard_parameters`) and `shard_parameters: linear`: the whole base may not
         # fit one GPU either, so each rank copies its rows of every weight from the checkpoint straight into its shard
         linear_only = str(cfg.get("shard_parameters", "")).lower() == "linear"
-        deferred = deferred or bool(self.parallel is not None and sharded and (self.is_lora or linear_only) and not cfg.get("resize_token_embeddings"))
+        deferred = deferred or bool(self.parallel is not None and sharded and (self.is_lora or linear_only or cfg.get("shard_parameters_layerwise", False))
+                                    and not cfg.get("resize_token_embeddings"))
         with training.set_default_dtype(self._dtype), (torch.device("meta") if deferred else self._device):
             model = config.instantiate(cfg.model)
         if cfg.get("resize_token_embeddings") and self._tokenizer_vocab(cfg) is not None:

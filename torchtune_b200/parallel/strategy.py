@@ -329,6 +329,22 @@ class ParallelStrategy(DataParallelEngine):
             if self.dims.tp_enabled:
                 return self._shard_model_tp(model, cfg, layerwise)
             return self._shard_model_ep(model, cfg, layerwise)
+        if self._shard_parameters and self._wants_full_sharding(cfg, is_lora) and any(p.is_meta for p in model.parameters()):
+            # every parameter sharded, model still without storage (`shard_parameters_layerwise: True`, for models whose bf16
+            # parameters do not fit one GPU): each bucket's modules get storage and checkpoint values right before they are cut
+            from ..training._distributed import LayerwisePreparer
+            from .zero3 import Zero3Engine
+
+            shard_group = replica_group = None
+            if self.dims.dp_replicate > 1:
+                groups = self.dims.build_groups(("dp_shard", "dp_replicate"))
+                shard_group, replica_group = groups["dp_shard"], groups["dp_replicate"]
+            self.z3 = Zero3Engine(self.device, shard_group, replica_group)
+            model = self.z3.prepare(model, prepare_layer=LayerwisePreparer(self.device, state_dict=base_sd))
+            validate_no_params_on_meta_device(model)
+            if self.rank == 0:
+                _log.info(f"ZeRO-3 engine: every trainable parameter is sharded over {self.world} ranks ({self.z3.nb} buckets, {self.z3.sp.shard} elements per rank), built layer by layer")
+            return model
         presharded = None
         if self._shard_parameters and not self._wants_full_sharding(cfg, is_lora) and any(t.is_meta for t in list(model.parameters()) + list(model.buffers())):
             # a base larger than one GPU (dense or 4-bit): this rank's rows of every weight go from the checkpoint straight into the
